@@ -1,0 +1,651 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a built on tcgen05.mma with TMEM accumulators
+// and TMA-fed shared-memory operands, plus the fused epilogues the decomposition step needs.
+//
+//   D[b][M,N] = sum over up to two K-phases of A_p[b] * B_p[b]
+//
+// Each operand is described by a tensor map and a "major": K-major means the matrix is stored with
+// K contiguous ([M,K] or [N,K] row-major); MN-major means it is stored transposed ([K,M] or [K,N]
+// row-major). All four combinations run on the same kernel, so forward, input-gradient and
+// weight-gradient products all read the tensors exactly as they sit in memory, no transposed copies.
+//
+// Two K-phases let one accumulator take  (xV .* coef) U  +  (d .* x) W^T  without a second pass:
+// phase 0 walks the component axis, phase 1 walks d_in, and the sum never leaves TMEM.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + single-thread MMA issuer,
+// warps 2..5 = epilogue (each owns the TMEM lane quarter warp_id % 4). Two accumulators of BN columns
+// alternate so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Epilogues:
+//   EPI_PLAIN     out0 = act(alpha * acc + bias)          bf16 or fp32, optional reduce-add (split-K
+//                                                         and gradient accumulation)
+//   EPI_MASK_FWD  out0 = bf16(acc .* coef), out1 = bf16(acc) (optional)
+//                 coef = rowscale * (m - delta),  m = ci + (1 - ci) * u,  u ~ Philox(seed, stream, row, col)
+//                 or m read from memory when mask_mode == 1
+//   EPI_MASK_BWD  acc = dA;  out0 = bf16(acc .* coef);  dci (+)= acc .* H .* rowscale .* dm/dci
+//
+// Every wait is bounded (see common.cuh); on time-out the kernel stores a code to *status and returns.
+#include "common.cuh"
+
+namespace pd {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kNumThreads = 192;
+constexpr int kStageBytesA = BM * BK * 2;  // 16 KiB
+constexpr int kOutBoxBytes = 32 * 128;     // one 32-row x 128-byte staging box
+
+enum Epi : int { EPI_PLAIN = 0, EPI_MASK_FWD = 1, EPI_MASK_BWD = 2 };
+enum Act : int { ACT_NONE = 0, ACT_GELU = 1, ACT_SILU = 2, ACT_RELU = 3 };
+
+struct GemmArgs {
+  int M, N, batch;
+  int kblocks0, kblocks1;
+  int split_k;
+  int a_mn0, b_mn0, a_mn1, b_mn1;
+  int accumulate;
+  int out_fp32;
+  int has_out1;
+  float alpha;
+  const float* bias;
+  long long bias_bs;
+  int act;
+  const __nv_bfloat16* ci;
+  long long ld_ci;
+  const __nv_bfloat16* H;
+  long long ld_h;
+  const float* delta;
+  const float* rowscale;
+  float* dci;
+  long long ld_dci;
+  int dci_accumulate;
+  unsigned long long seed;
+  unsigned int stream;
+  int mask_mode;
+  int* status;
+};
+
+template <int BN, int NOUT>
+struct SmemPlan {
+  static constexpr int kStageBytesB = BN * BK * 2;
+  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kOutBytes = 4 * NOUT * 2 * kOutBoxBytes;
+  static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/;
+  static constexpr int kStagesRaw = (kBudget - kOutBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + 256 + 1024;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case ACT_GELU:
+      return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    case ACT_SILU:
+      return v / (1.0f + __expf(-v));
+    case ACT_RELU:
+      return fmaxf(v, 0.0f);
+    default:
+      return v;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// Write 32 bf16 values (half of a 64-column box) of this thread's row into the swizzled staging box.
+__device__ __forceinline__ void stage_bf16_half(uint32_t box, int lane, int half,
+                                                const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int idx = half * 4 + j;
+    const uint32_t addr = box + lane * 128 + ((idx ^ (lane & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                 "r"(pack_bf16(v[8 * j + 0], v[8 * j + 1])),
+                 "r"(pack_bf16(v[8 * j + 2], v[8 * j + 3])),
+                 "r"(pack_bf16(v[8 * j + 4], v[8 * j + 5])),
+                 "r"(pack_bf16(v[8 * j + 6], v[8 * j + 7]))
+                 : "memory");
+  }
+}
+__device__ __forceinline__ void stage_fp32(uint32_t box, int lane, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t addr = box + lane * 128 + ((j ^ (lane & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                 "r"(__float_as_uint(v[4 * j + 0])), "r"(__float_as_uint(v[4 * j + 1])),
+                 "r"(__float_as_uint(v[4 * j + 2])), "r"(__float_as_uint(v[4 * j + 3]))
+                 : "memory");
+  }
+}
+
+template <int BN, int EPI, int NOUT>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+            const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+            const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
+            const GemmArgs args) {
+  using Plan = SmemPlan<BN, NOUT>;
+  constexpr int kStages = Plan::kStages;
+  constexpr int kStageBytesB = Plan::kStageBytesB;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two as tcgen05.alloc requires
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a = smem_base;
+  const uint32_t smem_b = smem_a + kStages * kStageBytesA;
+  const uint32_t smem_out = smem_b + kStages * kStageBytesB;
+  const uint32_t smem_bar = smem_out + Plan::kOutBytes;
+  // barrier layout: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then two words
+  const uint32_t bar_full = smem_bar;
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  const uint32_t tmem_slot = bar_tempty + 16;
+  uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      generic_base + (tmem_slot - smem_base));
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(generic_base + (tmem_slot + 4 - smem_base));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (args.M + BM - 1) / BM;
+  const int num_n = (args.N + BN - 1) / BN;
+  const int kb_total = args.kblocks0 + args.kblocks1;
+  const int split = args.split_k;
+  const int kb_per_split = (kb_total + split - 1) / split;
+  const long long num_tiles = static_cast<long long>(num_m) * num_n * split * args.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA0);
+    tma_prefetch_desc(&tmB0);
+    tma_prefetch_desc(&tmOut0);
+    if (args.kblocks1 > 0) {
+      tma_prefetch_desc(&tmA1);
+      tma_prefetch_desc(&tmB1);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // Tile decode: m fastest so the CTAs of one wave share the B block (kept hot in L2).
+  auto decode = [&](long long t, int& b, int& mb, int& nb, int& sp) {
+    mb = static_cast<int>(t % num_m);
+    t /= num_m;
+    nb = static_cast<int>(t % num_n);
+    t /= num_n;
+    sp = static_cast<int>(t % split);
+    b = static_cast<int>(t / split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int b, mb, nb, sp;
+        decode(t, b, mb, nb, sp);
+        const int kb_lo = sp * kb_per_split;
+        const int kb_hi = min(kb_total, kb_lo + kb_per_split);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
+            if (args.status) atomicCAS(args.status, 0, kTimeoutProducer);
+            ok = false;
+            break;
+          }
+          const bool p1 = kb >= args.kblocks0;
+          const int k0 = (p1 ? kb - args.kblocks0 : kb) * BK;
+          const CUtensorMap* ta = p1 ? &tmA1 : &tmA0;
+          const CUtensorMap* tb = p1 ? &tmB1 : &tmB0;
+          const int a_mn = p1 ? args.a_mn1 : args.a_mn0;
+          const int b_mn = p1 ? args.b_mn1 : args.b_mn0;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, kStageBytesA + kStageBytesB);
+          const uint32_t sa = smem_a + stage * kStageBytesA;
+          const uint32_t sb = smem_b + stage * kStageBytesB;
+          if (!a_mn) {
+            tma_load_3d(sa, ta, full, k0, mb * BM, b);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_3d(sa + i * (BK * 128), ta, full, mb * BM + 64 * i, k0, b);
+          }
+          if (!b_mn) {
+            tma_load_3d(sb, tb, full, k0, nb * BN, b);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_3d(sb + i * (BK * 128), tb, full, nb * BN + 64 * i, k0, b);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int b, mb, nb, sp;
+        decode(t, b, mb, nb, sp);
+        const int kb_lo = sp * kb_per_split;
+        const int kb_hi = min(kb_total, kb_lo + kb_per_split);
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) {
+          if (args.status) atomicCAS(args.status, 0, kTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+            if (args.status) atomicCAS(args.status, 0, kTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const bool p1 = kb >= args.kblocks0;
+          const int a_mn = p1 ? args.a_mn1 : args.a_mn0;
+          const int b_mn = p1 ? args.b_mn1 : args.b_mn0;
+          const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn, b_mn);
+          const uint32_t sa = smem_a + stage * kStageBytesA;
+          const uint32_t sb = smem_b + stage * kStageBytesB;
+          const uint64_t adesc = make_smem_desc(sa, a_mn ? BK * 128 : 16, 1024);
+          const uint64_t bdesc = make_smem_desc(sb, b_mn ? BK * 128 : 16, 1024);
+          // One instruction covers K = 16: 32 B along a K-major swizzle row, or two 8-row groups
+          // (2048 B) of an MN-major tile. The address field counts 16-byte units.
+          const uint64_t a_step = a_mn ? (2048 >> 4) : (32 >> 4);
+          const uint64_t b_step = b_mn ? (2048 >> 4) : (32 >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_bf16(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc,
+                      (kb > kb_lo || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + 8 * acc);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t my_out = smem_out + q * (NOUT * 2 * kOutBoxBytes);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int b, mb, nb, sp;
+      decode(t, b, mb, nb, sp);
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+        if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t tmem_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+
+      float delta = 0.0f, rs = 1.0f;
+      if constexpr (EPI != EPI_PLAIN) {
+        if (row_ok) {
+          if (args.delta) delta = args.delta[row];
+          if (args.rowscale) rs = args.rowscale[row];
+        }
+      }
+
+      const bool box64 = (EPI != EPI_PLAIN) || !args.out_fp32;  // bf16 outputs use 64-col boxes
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = nb * BN + c * 32;
+        if (col0 >= args.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_row + c * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+
+        const int half = box64 ? (c & 1) : 0;
+        const bool new_box = box64 ? (half == 0) : true;
+        if (new_box) {
+          // The boxes of `buf` were handed to TMA two steps ago: make sure they have been read.
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        const uint32_t box0 = my_out + (0 * 2 + buf) * kOutBoxBytes;
+        const uint32_t box1 = my_out + ((NOUT - 1) * 2 + buf) * kOutBoxBytes;
+
+        if constexpr (EPI == EPI_PLAIN) {
+          const float* bias = args.bias ? args.bias + b * args.bias_bs : nullptr;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = v[i] * args.alpha;
+            if (bias && col0 + i < args.N) x += bias[col0 + i];
+            v[i] = apply_act(x, args.act);
+          }
+          if (args.out_fp32)
+            stage_fp32(box0, lane, v);
+          else
+            stage_bf16_half(box0, lane, half, v);
+        } else {
+          // ---- mask epilogues: coef[i] for this row and 32 columns ----
+          float coef[32], dmdci[32];
+          const __nv_bfloat16* ci_row = args.ci + static_cast<long long>(row) * args.ld_ci + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float cf[8];
+            const bool ok = row_ok && (col0 + 8 * g < args.N);
+            if (ok) {
+              unpack8(*reinterpret_cast<const uint4*>(ci_row + 8 * g), cf);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) cf[i] = 0.0f;
+            }
+            if (args.mask_mode == 0) {
+              float u[8];
+              philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(row),
+                              static_cast<uint32_t>((col0 >> 3) + g), u);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                coef[8 * g + i] = rs * (cf[i] + (1.0f - cf[i]) * u[i] - delta);
+                dmdci[8 * g + i] = rs * (1.0f - u[i]);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                coef[8 * g + i] = rs * (cf[i] - delta);
+                dmdci[8 * g + i] = rs;
+              }
+            }
+          }
+          if constexpr (EPI == EPI_MASK_FWD) {
+            if (NOUT == 2 && args.has_out1) stage_bf16_half(box1, lane, half, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= coef[i];
+            stage_bf16_half(box0, lane, half, v);
+          } else {
+            // backward: v = dA. dci gets dA * H * dm/dci; out0 = dA * coef.
+            if (args.dci != nullptr && row_ok) {
+              const __nv_bfloat16* h_row = args.H + static_cast<long long>(row) * args.ld_h + col0;
+              float* d_row = args.dci + static_cast<long long>(row) * args.ld_dci + col0;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (col0 + 8 * g < args.N) {
+                  float hf[8];
+                  unpack8(*reinterpret_cast<const uint4*>(h_row + 8 * g), hf);
+                  float4 o0, o1;
+                  float* dst = d_row + 8 * g;
+                  if (args.dci_accumulate) {
+                    o0 = *reinterpret_cast<float4*>(dst);
+                    o1 = *reinterpret_cast<float4*>(dst + 4);
+                  } else {
+                    o0 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    o1 = o0;
+                  }
+                  o0.x += v[8 * g + 0] * hf[0] * dmdci[8 * g + 0];
+                  o0.y += v[8 * g + 1] * hf[1] * dmdci[8 * g + 1];
+                  o0.z += v[8 * g + 2] * hf[2] * dmdci[8 * g + 2];
+                  o0.w += v[8 * g + 3] * hf[3] * dmdci[8 * g + 3];
+                  o1.x += v[8 * g + 4] * hf[4] * dmdci[8 * g + 4];
+                  o1.y += v[8 * g + 5] * hf[5] * dmdci[8 * g + 5];
+                  o1.z += v[8 * g + 6] * hf[6] * dmdci[8 * g + 6];
+                  o1.w += v[8 * g + 7] * hf[7] * dmdci[8 * g + 7];
+                  *reinterpret_cast<float4*>(dst) = o0;
+                  *reinterpret_cast<float4*>(dst + 4) = o1;
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= coef[i];
+            stage_bf16_half(box0, lane, half, v);
+          }
+        }
+
+        const bool box_done = box64 ? (half == 1 || col0 + 32 >= args.N) : true;
+        if (box_done) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int ccol = box64 ? (col0 - half * 32) : col0;
+            const int crow = mb * BM + q * 32;
+            if (crow < args.M) {
+              if (args.accumulate)
+                tma_reduce_add_3d(&tmOut0, box0, ccol, crow, b);
+              else
+                tma_store_3d(&tmOut0, box0, ccol, crow, b);
+              if constexpr (EPI == EPI_MASK_FWD && NOUT == 2) {
+                if (args.has_out1) tma_store_3d(&tmOut1, box1, ccol, crow, b);
+              }
+            }
+            tma_store_commit();
+          }
+          buf ^= 1;
+        }
+      }
+      // Accumulator drained: hand it back to the MMA warp.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // Unwind: every role has left its loop (all waits are bounded). A producer that gave up may
+  // still have loads in flight; give them a bounded grace period before the CTA's smem goes away.
+  if (*abort_flag && warp == 0 && lane == 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct OperandDesc {
+  const void* ptr;      // bf16
+  long long ld;         // elements between rows of the stored matrix
+  long long batch_stride;
+  int mn_major;         // 0: stored [rows=M|N, K]; 1: stored [rows=K, M|N]
+};
+
+static int g_num_sms = 0;
+
+static int encode_operand(CUtensorMap* tm, const OperandDesc& op, int mn_extent, int k_extent,
+                          int batch, int box_rows_k_major) {
+  if (!op.mn_major) {
+    return encode_tmap(tm, op.ptr, 2, false, k_extent, mn_extent, op.ld, batch,
+                       op.batch_stride, 64, box_rows_k_major);
+  }
+  return encode_tmap(tm, op.ptr, 2, false, mn_extent, k_extent, op.ld, batch, op.batch_stride, 64,
+                     BK);
+}
+
+template <int BN, int EPI, int NOUT>
+static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
+                       const CUtensorMap& b1, const CUtensorMap& o0, const CUtensorMap& o1,
+                       const GemmArgs& args, int max_ctas, cudaStream_t stream) {
+  using Plan = SmemPlan<BN, NOUT>;
+  auto kern = gemm_kernel<BN, EPI, NOUT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Plan::kTotal);
+    if (e != cudaSuccess) return 300 + static_cast<int>(e);
+    configured = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const long long tiles = static_cast<long long>((args.M + BM - 1) / BM) *
+                          ((args.N + BN - 1) / BN) * args.split_k * args.batch;
+  int grid = static_cast<int>(tiles < g_num_sms ? tiles : g_num_sms);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (grid <= 0) return 0;
+  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, args);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
+}
+
+}  // namespace pd
+
+using namespace pd;
+
+// C ABI -----------------------------------------------------------------------------------------
+// All pointers are device pointers; `stream` is a cudaStream_t. Return value 0 = launched.
+struct PdGemmCall {
+  // problem
+  int M, N, batch;
+  int K0, K1;
+  // operands of phase 0 and (if K1 > 0) phase 1
+  const void* A0; long long lda0; long long bsa0; int a_mn0;
+  const void* B0; long long ldb0; long long bsb0; int b_mn0;
+  const void* A1; long long lda1; long long bsa1; int a_mn1;
+  const void* B1; long long ldb1; long long bsb1; int b_mn1;
+  // outputs
+  void* out0; long long ldo0; long long bso0; int out_fp32; int accumulate;
+  void* out1; long long ldo1; long long bso1;
+  // plain epilogue
+  float alpha; const float* bias; long long bias_bs; int act;
+  // mask epilogues
+  int epi;
+  const void* ci; long long ld_ci;
+  const void* H; long long ld_h;
+  const float* delta; const float* rowscale;
+  float* dci; long long ld_dci; int dci_accumulate;
+  unsigned long long seed; unsigned int rng_stream; int mask_mode;
+  // control
+  int split_k; int bn; int max_ctas;
+  int* status;
+};
+
+extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (c->M <= 0 || c->N <= 0 || c->batch <= 0 || c->K0 <= 0) return kBadArgument;
+  if (c->epi != EPI_PLAIN && (c->batch != 1 || c->accumulate || c->out_fp32)) return kBadArgument;
+  if (c->accumulate && !c->out_fp32) return kBadArgument;
+  const int bn = c->bn == 128 ? 128 : 256;
+  const int nout = (c->epi == EPI_MASK_FWD && c->out1 != nullptr) ? 2 : 1;
+
+  GemmArgs a{};
+  a.M = c->M; a.N = c->N; a.batch = c->batch;
+  a.kblocks0 = (c->K0 + BK - 1) / BK;
+  a.kblocks1 = c->K1 > 0 ? (c->K1 + BK - 1) / BK : 0;
+  a.split_k = c->split_k > 0 ? c->split_k : 1;
+  if (a.split_k > 1 && !(c->accumulate && c->epi == EPI_PLAIN && c->act == ACT_NONE &&
+                         c->bias == nullptr))
+    return kBadArgument;
+  if (a.split_k > a.kblocks0 + a.kblocks1) a.split_k = a.kblocks0 + a.kblocks1;
+  a.a_mn0 = c->a_mn0; a.b_mn0 = c->b_mn0; a.a_mn1 = c->a_mn1; a.b_mn1 = c->b_mn1;
+  a.accumulate = c->accumulate; a.out_fp32 = c->out_fp32; a.has_out1 = c->out1 != nullptr;
+  a.alpha = c->alpha; a.bias = c->bias; a.bias_bs = c->bias_bs; a.act = c->act;
+  a.ci = static_cast<const __nv_bfloat16*>(c->ci); a.ld_ci = c->ld_ci;
+  a.H = static_cast<const __nv_bfloat16*>(c->H); a.ld_h = c->ld_h;
+  a.delta = c->delta; a.rowscale = c->rowscale;
+  a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate;
+  a.seed = c->seed; a.stream = c->rng_stream; a.mask_mode = c->mask_mode;
+  a.status = c->status;
+  if (c->epi != EPI_PLAIN) {
+    if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15))
+      return kBadArgument;
+    if (c->epi == EPI_MASK_BWD && c->dci != nullptr) {
+      if (c->H == nullptr || (c->ld_h % 8) != 0 || (c->ld_dci % 4) != 0 ||
+          (reinterpret_cast<uintptr_t>(c->H) & 15) || (reinterpret_cast<uintptr_t>(c->dci) & 15))
+        return kBadArgument;
+    }
+    if (c->N % 8 != 0) return kBadArgument;
+  }
+
+  CUtensorMap ta0, tb0, ta1, tb1, to0, to1;
+  int rc;
+  OperandDesc A0{c->A0, c->lda0, c->bsa0, c->a_mn0}, B0{c->B0, c->ldb0, c->bsb0, c->b_mn0};
+  if ((rc = encode_operand(&ta0, A0, c->M, c->K0, c->batch, BM))) return 1000 + rc;
+  if ((rc = encode_operand(&tb0, B0, c->N, c->K0, c->batch, bn))) return 2000 + rc;
+  if (c->K1 > 0) {
+    OperandDesc A1{c->A1, c->lda1, c->bsa1, c->a_mn1}, B1{c->B1, c->ldb1, c->bsb1, c->b_mn1};
+    if ((rc = encode_operand(&ta1, A1, c->M, c->K1, c->batch, BM))) return 3000 + rc;
+    if ((rc = encode_operand(&tb1, B1, c->N, c->K1, c->batch, bn))) return 4000 + rc;
+  } else {
+    ta1 = ta0;
+    tb1 = tb0;
+  }
+  const int oes = c->out_fp32 ? 4 : 2;
+  if ((rc = encode_tmap(&to0, c->out0, oes, true, c->N, c->M, c->ldo0, c->batch, c->bso0,
+                        c->out_fp32 ? 32 : 64, 32)))
+    return 5000 + rc;
+  if (nout == 2) {
+    if ((rc = encode_tmap(&to1, c->out1, 2, false, c->N, c->M, c->ldo1, 1, 0, 64, 32)))
+      return 6000 + rc;
+  } else {
+    to1 = to0;
+  }
+
+#define PD_LAUNCH(BN_, EPI_, NOUT_) \
+  launch_gemm<BN_, EPI_, NOUT_>(ta0, tb0, ta1, tb1, to0, to1, a, c->max_ctas, stream)
+  if (c->epi == EPI_PLAIN) return bn == 256 ? PD_LAUNCH(256, EPI_PLAIN, 1) : PD_LAUNCH(128, EPI_PLAIN, 1);
+  if (c->epi == EPI_MASK_FWD) {
+    if (nout == 2) return bn == 256 ? PD_LAUNCH(256, EPI_MASK_FWD, 2) : PD_LAUNCH(128, EPI_MASK_FWD, 2);
+    return bn == 256 ? PD_LAUNCH(256, EPI_MASK_FWD, 1) : PD_LAUNCH(128, EPI_MASK_FWD, 1);
+  }
+  if (c->epi == EPI_MASK_BWD) return bn == 256 ? PD_LAUNCH(256, EPI_MASK_BWD, 1) : PD_LAUNCH(128, EPI_MASK_BWD, 1);
+#undef PD_LAUNCH
+  return kBadArgument;
+}
+
+extern "C" int pd_gemm_call_size() { return static_cast<int>(sizeof(PdGemmCall)); }

@@ -1,0 +1,187 @@
+"""ctypes binding of the native sm_100a kernel library (`ops/_lib/libpdb200.so`).
+
+The library is plain C ABI: device pointers and a `cudaStream_t` go in, an int comes back
+(0 = launched). Nothing here falls back to another implementation: on a machine with a GPU the
+library must load, otherwise `lib()` raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libpdb200.so"
+
+EPI_PLAIN, EPI_MASK_FWD, EPI_MASK_BWD = 0, 1, 2
+ACT_NONE, ACT_GELU, ACT_SILU, ACT_RELU = 0, 1, 2, 3
+_ACT = {None: ACT_NONE, "none": ACT_NONE, "gelu": ACT_GELU, "silu": ACT_SILU, "relu": ACT_RELU}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class PdGemmCall(C.Structure):
+    _fields_ = [
+        ("M", C.c_int), ("N", C.c_int), ("batch", C.c_int), ("K0", C.c_int), ("K1", C.c_int),
+        ("A0", C.c_void_p), ("lda0", C.c_longlong), ("bsa0", C.c_longlong), ("a_mn0", C.c_int),
+        ("B0", C.c_void_p), ("ldb0", C.c_longlong), ("bsb0", C.c_longlong), ("b_mn0", C.c_int),
+        ("A1", C.c_void_p), ("lda1", C.c_longlong), ("bsa1", C.c_longlong), ("a_mn1", C.c_int),
+        ("B1", C.c_void_p), ("ldb1", C.c_longlong), ("bsb1", C.c_longlong), ("b_mn1", C.c_int),
+        ("out0", C.c_void_p), ("ldo0", C.c_longlong), ("bso0", C.c_longlong),
+        ("out_fp32", C.c_int), ("accumulate", C.c_int),
+        ("out1", C.c_void_p), ("ldo1", C.c_longlong), ("bso1", C.c_longlong),
+        ("alpha", C.c_float), ("bias", C.c_void_p), ("bias_bs", C.c_longlong), ("act", C.c_int),
+        ("epi", C.c_int),
+        ("ci", C.c_void_p), ("ld_ci", C.c_longlong),
+        ("H", C.c_void_p), ("ld_h", C.c_longlong),
+        ("delta", C.c_void_p), ("rowscale", C.c_void_p),
+        ("dci", C.c_void_p), ("ld_dci", C.c_longlong), ("dci_accumulate", C.c_int),
+        ("seed", C.c_ulonglong), ("rng_stream", C.c_uint), ("mask_mode", C.c_int),
+        ("split_k", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int),
+        ("status", C.c_void_p),
+    ]  # fmt: skip
+
+
+@lru_cache(maxsize=1)
+def lib() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise NativeError(
+            f"{LIB_PATH} is missing: run `python -m param_decomp_b200.ops.build` (needs nvcc)"
+        )
+    handle = C.CDLL(str(LIB_PATH))
+    handle.pd_gemm.argtypes = [C.POINTER(PdGemmCall), C.c_void_p]
+    handle.pd_gemm.restype = C.c_int
+    handle.pd_gemm_call_size.restype = C.c_int
+    if handle.pd_gemm_call_size() != C.sizeof(PdGemmCall):
+        raise NativeError("PdGemmCall layout differs between native.py and gemm_sm100.cu")
+    return handle
+
+
+def available() -> bool:
+    return torch.cuda.is_available() and LIB_PATH.exists()
+
+
+def current_stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+@lru_cache(maxsize=8)
+def _status_word(device_index: int) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", device_index))
+
+
+def status_word() -> torch.Tensor:
+    """The per-device int32 the kernels report a timed-out wait in (0 = no error)."""
+    return _status_word(torch.cuda.current_device())
+
+
+def check_status() -> None:
+    """Synchronising check of the status word; raises if a bounded wait ran out."""
+    code = int(status_word().item())
+    if code != 0:
+        status_word().zero_()
+        raise NativeError(f"a device-side wait timed out (status code {code})")
+
+
+def _operand(t: torch.Tensor, mn_major: bool) -> tuple[int, int, int]:
+    """(ptr, ld, batch_stride) of a 2-D or 3-D bf16 operand whose last dim is contiguous."""
+    assert t.dtype == torch.bfloat16 and t.stride(-1) == 1, (t.dtype, t.stride())
+    bs = t.stride(0) if t.dim() == 3 else 0
+    return t.data_ptr(), t.stride(-2), bs
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    a1: torch.Tensor | None = None,
+    b1: torch.Tensor | None = None,
+    a1_mn: bool = False,
+    b1_mn: bool = False,
+    accumulate: bool = False,
+    alpha: float = 1.0,
+    bias: torch.Tensor | None = None,
+    act: str | None = None,
+    split_k: int = 1,
+    bn: int = 256,
+    epi: int = EPI_PLAIN,
+    out1: torch.Tensor | None = None,
+    ci: torch.Tensor | None = None,
+    h: torch.Tensor | None = None,
+    delta: torch.Tensor | None = None,
+    rowscale: torch.Tensor | None = None,
+    dci: torch.Tensor | None = None,
+    dci_accumulate: bool = False,
+    seed: int = 0,
+    rng_stream: int = 0,
+    mask_mode: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
+
+    `a` is `[M, K]` (`a_mn=False`) or `[K, M]` (`a_mn=True`); `b` is `[N, K]` (`b_mn=False`) or
+    `[K, N]` (`b_mn=True`); a leading batch dim is allowed on all of a/b/out for the plain epilogue.
+    """
+    call = PdGemmCall()
+    M, N = out.shape[-2], out.shape[-1]
+    K0 = a.shape[-2] if a_mn else a.shape[-1]
+    assert (b.shape[-2] if b_mn else b.shape[-1]) == K0, (a.shape, b.shape, a_mn, b_mn)
+    assert (a.shape[-1] if a_mn else a.shape[-2]) == M and (b.shape[-1] if b_mn else b.shape[-2]) == N
+    batch = out.shape[0] if out.dim() == 3 else 1
+    call.M, call.N, call.batch, call.K0 = M, N, batch, K0
+    call.A0, call.lda0, call.bsa0 = _operand(a, a_mn)
+    call.B0, call.ldb0, call.bsb0 = _operand(b, b_mn)
+    call.a_mn0, call.b_mn0 = int(a_mn), int(b_mn)
+    if a1 is not None:
+        assert b1 is not None
+        K1 = a1.shape[-2] if a1_mn else a1.shape[-1]
+        assert (b1.shape[-2] if b1_mn else b1.shape[-1]) == K1
+        call.K1 = K1
+        call.A1, call.lda1, call.bsa1 = _operand(a1, a1_mn)
+        call.B1, call.ldb1, call.bsb1 = _operand(b1, b1_mn)
+        call.a_mn1, call.b_mn1 = int(a1_mn), int(b1_mn)
+    assert out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    call.out0, call.ldo0 = out.data_ptr(), out.stride(-2)
+    call.bso0 = out.stride(0) if out.dim() == 3 else 0
+    call.out_fp32 = int(out.dtype == torch.float32)
+    call.accumulate = int(accumulate)
+    if out1 is not None:
+        assert out1.dtype == torch.bfloat16 and out1.stride(-1) == 1
+        call.out1, call.ldo1 = out1.data_ptr(), out1.stride(-2)
+    call.alpha = alpha
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.stride(-1) == 1
+        call.bias = bias.data_ptr()
+        call.bias_bs = bias.stride(0) if bias.dim() == 2 else 0
+    call.act = _ACT[act]
+    call.epi = epi
+    if ci is not None:
+        assert ci.dtype == torch.bfloat16 and ci.stride(-1) == 1
+        call.ci, call.ld_ci = ci.data_ptr(), ci.stride(-2)
+    if h is not None:
+        assert h.dtype == torch.bfloat16 and h.stride(-1) == 1
+        call.H, call.ld_h = h.data_ptr(), h.stride(-2)
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.numel() == M
+        call.delta = delta.data_ptr()
+    if rowscale is not None:
+        assert rowscale.dtype == torch.float32 and rowscale.is_contiguous() and rowscale.numel() == M
+        call.rowscale = rowscale.data_ptr()
+    if dci is not None:
+        assert dci.dtype == torch.float32 and dci.stride(-1) == 1
+        call.dci, call.ld_dci = dci.data_ptr(), dci.stride(-2)
+    call.dci_accumulate = int(dci_accumulate)
+    call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
+    call.split_k, call.bn, call.max_ctas = split_k, bn, max_ctas
+    call.status = status_word().data_ptr()
+    rc = lib().pd_gemm(C.byref(call), current_stream_ptr())
+    if rc != 0:
+        raise NativeError(f"pd_gemm refused the call (code {rc})")
+    return out
