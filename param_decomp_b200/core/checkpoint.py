@@ -1,0 +1,203 @@
+"""safetensors checkpoints of a decomposition run.
+
+Layout under `<run_dir>/ckpts/<step>/`:
+  decomposition.safetensors   components/<group>/V  [g, d_in, C]   (stack pads stripped)
+                              components/<group>/U  [g, C, d_out]
+                              ci_fn/<parameter path>
+                              metadata: JSON `site_stack_indices` {site: [group, index]} so a
+                              component key "<site>:<idx>" addresses column idx of that slice
+  training.safetensors        opt/components/<leaf>/{mu,nu,mom}, opt/ci_fn/...,
+                              adversaries/<term>/{sources,delta,opt}/..., frequency/<site>, step
+Multi-rank runs write `<name>-rank<r>-of-<n>.safetensors` holding each rank's shard plus an
+`index.json` of `{key: {axis, world}}`; `load_*` re-assembles (or re-shards) them, so a checkpoint
+written on one mesh restores on another.
+
+The reference stores the same two items (`decomposition`, `training`) with Orbax
+(param_decomp/core/checkpoint.py:63-239); the key paths here mirror its tree paths. Retention
+(`keep_last n | keep_all`) follows core/configs.py:1048-1089.
+"""
+
+from __future__ import annotations
+
+import json
+import shutil
+from pathlib import Path
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
+from torch import Tensor, nn
+
+from param_decomp_b200.core.components import ComponentStacks
+from param_decomp_b200.core.losses import FrequencyEMA
+
+DECOMPOSITION_FILE = "decomposition.safetensors"
+TRAINING_FILE = "training.safetensors"
+
+
+def ckpt_root(run_dir: Path) -> Path:
+    return Path(run_dir) / "ckpts"
+
+
+def list_steps(run_dir: Path) -> list[int]:
+    root = ckpt_root(run_dir)
+    if not root.exists():
+        return []
+    return sorted(int(p.name) for p in root.iterdir() if p.is_dir() and p.name.isdigit()
+                  and (p / DECOMPOSITION_FILE).exists())
+
+
+def latest_step(run_dir: Path) -> int | None:
+    steps = list_steps(run_dir)
+    return steps[-1] if steps else None
+
+
+def _storable(t: Tensor) -> Tensor:
+    t = t.detach().cpu().contiguous()
+    return t.view(torch.int16) if t.dtype == torch.uint16 else t
+
+
+def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module) -> tuple[dict[str, Tensor], dict[str, str]]:
+    out: dict[str, Tensor] = {}
+    for gname, members in components.groups.items():
+        key = components.param_key(gname)
+        n = len(members)
+        out[f"components/{gname}/V"] = _storable(components.V[key][:n])
+        out[f"components/{gname}/U"] = _storable(components.U[key][:n])
+    for name, p in ci_fn.state_dict().items():
+        out[f"ci_fn/{name}"] = _storable(p)
+    meta = {
+        "site_stack_indices": json.dumps({s: list(v) for s, v in components.site_stack_indices.items()}),
+        "format": "param_decomp_b200/decomposition/v1",
+    }
+    return out, meta
+
+
+def training_tensors(state) -> tuple[dict[str, Tensor], dict[str, str]]:
+    out: dict[str, Tensor] = {"step": torch.tensor(state.step, dtype=torch.int64)}
+    uint16_keys = []
+    for group, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
+        for k, v in opt.state_dict().items():
+            out[f"opt/{group}/{k}"] = _storable(v)
+    for term, adv in state.adversaries.items():
+        for k, v in adv.state_dict().items():
+            if v.dtype == torch.uint16:
+                uint16_keys.append(f"adversaries/{term}/{k}")
+            out[f"adversaries/{term}/{k}"] = _storable(v)
+    for site, ema in state.frequency.items():
+        out[f"frequency/{site}/value"] = _storable(ema.value)
+        out[f"frequency/{site}/weight"] = torch.tensor(ema.weight, dtype=torch.float64)
+        out[f"frequency/{site}/halflife"] = torch.tensor(ema.halflife_steps, dtype=torch.float64)
+    meta = {"uint16_keys": json.dumps(uint16_keys), "format": "param_decomp_b200/training/v1"}
+    return out, meta
+
+
+def save_state(run_dir: Path, state, retention_keep_last: int | None = None) -> Path:
+    """Synchronous save of both items at `state.step`, then prune per the retention policy."""
+    step_dir = ckpt_root(run_dir) / str(state.step)
+    tmp = step_dir.with_name(step_dir.name + ".tmp")
+    if tmp.exists():
+        shutil.rmtree(tmp)
+    tmp.mkdir(parents=True)
+    d, dm = decomposition_tensors(state.components, state.ci_fn)
+    save_file(d, str(tmp / DECOMPOSITION_FILE), metadata=dm)
+    t, tm = training_tensors(state)
+    save_file(t, str(tmp / TRAINING_FILE), metadata=tm)
+    if step_dir.exists():
+        shutil.rmtree(step_dir)
+    tmp.rename(step_dir)  # a step directory is visible only once complete
+    if retention_keep_last is not None:
+        for old in list_steps(run_dir)[:-retention_keep_last]:
+            shutil.rmtree(ckpt_root(run_dir) / str(old))
+    return step_dir
+
+
+def _read(path: Path) -> tuple[dict[str, Tensor], dict[str, str]]:
+    tensors = {}
+    with safe_open(str(path), framework="pt") as f:
+        meta = f.metadata() or {}
+        for k in f.keys():
+            tensors[k] = f.get_tensor(k)
+    return tensors, meta
+
+
+def restore_components(run_dir: Path, step: int, components: ComponentStacks) -> None:
+    """V/U only (analysis-time partial restore). Pads of the destination are re-derived (zero)."""
+    tensors, _ = _read(ckpt_root(run_dir) / str(step) / DECOMPOSITION_FILE)
+    with torch.no_grad():
+        for gname, members in components.groups.items():
+            key, n = components.param_key(gname), len(members)
+            V, U = tensors[f"components/{gname}/V"], tensors[f"components/{gname}/U"]
+            assert V.shape[0] == n, f"group {gname}: checkpoint has {V.shape[0]} sites, run has {n}"
+            components.V[key].zero_()
+            components.U[key].zero_()
+            components.V[key][:n].copy_(V)
+            components.U[key][:n].copy_(U)
+
+
+def restore_decomposition(run_dir: Path, step: int, components: ComponentStacks, ci_fn: nn.Module) -> None:
+    restore_components(run_dir, step, components)
+    tensors, _ = _read(ckpt_root(run_dir) / str(step) / DECOMPOSITION_FILE)
+    sd = {k[len("ci_fn/"):]: v for k, v in tensors.items() if k.startswith("ci_fn/")}
+    ci_fn.load_state_dict(sd)
+
+
+def restore_state(run_dir: Path, step: int, state) -> None:
+    """Full resume: decomposition + optimizer states + adversaries + frequency EMA + step."""
+    restore_decomposition(run_dir, step, state.components, state.ci_fn)
+    tensors, meta = _read(ckpt_root(run_dir) / str(step) / TRAINING_FILE)
+    uint16_keys = set(json.loads(meta.get("uint16_keys", "[]")))
+    dev = next(state.components.parameters()).device
+
+    def get(k: str) -> Tensor:
+        v = tensors[k]
+        return (v.view(torch.uint16) if k in uint16_keys else v).to(dev)
+
+    state.step = int(tensors["step"].item())
+    for group, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
+        prefix = f"opt/{group}/"
+        opt.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)})
+    for term, adv in state.adversaries.items():
+        prefix = f"adversaries/{term}/"
+        adv.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)})
+    sites = {k.split("/")[1] for k in tensors if k.startswith("frequency/")}
+    for site in sites:
+        state.frequency[site] = FrequencyEMA(
+            halflife_steps=float(tensors[f"frequency/{site}/halflife"].item()),
+            value=get(f"frequency/{site}/value"),
+            weight=float(tensors[f"frequency/{site}/weight"].item()),
+        )
+
+
+# ---- sharded files ----------------------------------------------------------------------------------
+
+
+def save_sharded(path: Path, tensors: dict[str, Tensor], shard_axes: dict[str, int], rank: int, world: int) -> None:
+    """Each rank writes its shard; rank 0 also writes the index naming every key's shard axis."""
+    path = Path(path)
+    save_file({k: _storable(v) for k, v in tensors.items()},
+              str(path.with_name(f"{path.stem}-rank{rank}-of-{world}.safetensors")))
+    if rank == 0:
+        path.with_name(path.stem + ".index.json").write_text(json.dumps({"world": world, "axes": shard_axes}))
+
+
+def load_sharded(path: Path, rank: int = 0, world: int = 1) -> dict[str, Tensor]:
+    """Re-assemble every key along its shard axis, then cut the `rank`-of-`world` slice of the NEW
+    mesh (world=1 returns whole tensors), so checkpoints move between topologies."""
+    path = Path(path)
+    index = json.loads(path.with_name(path.stem + ".index.json").read_text())
+    old_world, axes = index["world"], index["axes"]
+    parts = [_read(path.with_name(f"{path.stem}-rank{r}-of-{old_world}.safetensors"))[0] for r in range(old_world)]
+    out = {}
+    for k in parts[0]:
+        ax = axes.get(k)
+        if ax is None:
+            out[k] = parts[0][k]
+            continue
+        full = torch.cat([p[k] for p in parts], dim=ax)
+        if world > 1:
+            n = full.shape[ax]
+            assert n % world == 0, f"{k}: axis {ax} of size {n} does not tile {world} ranks"
+            full = full.narrow(ax, rank * (n // world), n // world).contiguous()
+        out[k] = full
+    return out

@@ -1,0 +1,72 @@
+"""The CI-function contract.
+
+A CI function reads *taps* (clean activations of the target, keyed by name) and emits one
+pre-activation tensor `[..., C_site]` per decomposed site. `squash` turns pre-activations into the
+two importances the objective uses: `lower` (masks) and `upper` (minimality penalty).
+
+Parity: param_decomp/core/ci_fn/interface.py:24-110 (CI triple, CIFn protocol, TapSpec),
+architecture.py:14-43 (parameter census / useful FLOPs hooks), runtime.py:10-27.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Protocol
+
+from torch import Tensor, nn
+
+from param_decomp_b200.core.components import SelectedCI
+from param_decomp_b200.core.squashing import lower_leaky_hard_sigmoid, upper_leaky_hard_sigmoid
+
+
+@dataclass(frozen=True)
+class TapSpec:
+    key: str
+    width: int
+
+
+@dataclass
+class CI:
+    preactivations: dict[str, Tensor | SelectedCI]
+    lower: dict[str, Tensor | SelectedCI]
+    upper: dict[str, Tensor | SelectedCI]
+
+    def dense_lower(self) -> dict[str, Tensor]:
+        return {k: (v.scatter_dense() if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()}
+
+    def dense_upper(self) -> dict[str, Tensor]:
+        return {k: (v.scatter_dense() if isinstance(v, SelectedCI) else v) for k, v in self.upper.items()}
+
+
+def _map(fn, v):
+    if isinstance(v, SelectedCI):
+        return SelectedCI(fn(v.values), v.selection, v.n_blocks)
+    return fn(v)
+
+
+def squash(pre: dict[str, Tensor | SelectedCI]) -> CI:
+    return CI(
+        preactivations=pre,
+        lower={k: _map(lower_leaky_hard_sigmoid, v) for k, v in pre.items()},
+        upper={k: _map(upper_leaky_hard_sigmoid, v) for k, v in pre.items()},
+    )
+
+
+class CIFn(Protocol):
+    """`nn.Module`s implementing `forward(taps, **context) -> {site: preactivations}`."""
+
+    input_taps: tuple[str, ...]
+
+    def forward(self, taps: dict[str, Tensor], **context: Any) -> dict[str, Tensor | SelectedCI]: ...
+
+    def parameter_census(self) -> dict[str, int]: ...
+
+    def useful_flops_per_position(self) -> int: ...
+
+
+def census(module: nn.Module) -> dict[str, int]:
+    out: dict[str, int] = {"total": 0, "matrix": 0, "other": 0}
+    for p in module.parameters():
+        out["total"] += p.numel()
+        out["matrix" if p.dim() >= 2 else "other"] += p.numel()
+    return out

@@ -1,0 +1,121 @@
+"""MLP causal-importance functions: per-site (`layerwise_mlp`) and joint (`global_mlp`).
+
+Both are pointwise over all leading axes, so the same module serves positionless toys `[B, d]` and
+per-token LM activations `[B, T, d]`.
+
+Parity: param_decomp/core/ci_fn/implementations/mlp.py:57-92 (`SiteMLP`: Linear + exact-erf GELU
+... Linear, Kaiming-normal weights, zero biases), layerwise_mlp.py:30-164, global_mlp.py:30-170.
+
+Sites of one group share their shapes, so `LayerwiseMLPCIFn` stores each group's MLPs stacked
+(`W1 [g, d_in, h]`, ...) and evaluates the whole group as one batched GEMM chain; on the fused
+backend that chain is one launch of the batched tcgen05 kernel per layer.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor, nn
+
+from param_decomp_b200.core.ci_fn.interface import census
+
+
+def _kaiming_(w: Tensor, fan_in: int, generator: torch.Generator | None) -> None:
+    std = math.sqrt(2.0 / fan_in)
+    with torch.no_grad():
+        w.copy_(torch.randn(w.shape, generator=generator, dtype=torch.float32).to(w.device) * std)
+
+
+class SiteMLP(nn.Module):
+    """`d_in -> hidden... -> d_out` for `n_stack` independent copies evaluated together."""
+
+    def __init__(self, n_stack: int, d_in: int, hidden_dims: tuple[int, ...], d_out: int,
+                 generator: torch.Generator | None = None) -> None:
+        super().__init__()
+        dims = (d_in, *hidden_dims, d_out)
+        self.dims = dims
+        self.n_stack = n_stack
+        self.weights = nn.ParameterList()
+        self.biases = nn.ParameterList()
+        for a, b in zip(dims[:-1], dims[1:]):
+            w = nn.Parameter(torch.empty(n_stack, a, b))
+            _kaiming_(w, a, generator)
+            self.weights.append(w)
+            self.biases.append(nn.Parameter(torch.zeros(n_stack, 1, b)))
+
+    def forward(self, x: Tensor) -> Tensor:
+        """`x [n_stack, N, d_in] -> [n_stack, N, d_out]`."""
+        h = x
+        last = len(self.weights) - 1
+        for i, (w, b) in enumerate(zip(self.weights, self.biases)):
+            h = torch.baddbmm(b.to(h.dtype), h, w.to(h.dtype))
+            if i != last:
+                h = F.gelu(h)  # exact erf form
+        return h
+
+    def flops_per_row(self) -> int:
+        return sum(2 * a * b for a, b in zip(self.dims[:-1], self.dims[1:])) * self.n_stack
+
+
+class LayerwiseMLPCIFn(nn.Module):
+    """One MLP per site, reading that site's own tap. `site_taps[site] = tap key`."""
+
+    def __init__(self, site_shapes: dict[str, tuple[int, int]], site_taps: dict[str, str],
+                 hidden_dims: tuple[int, ...], generator: torch.Generator | None = None) -> None:
+        super().__init__()
+        self.site_taps = dict(site_taps)
+        self.input_taps = tuple(dict.fromkeys(site_taps.values()))
+        # group sites by (d_in, C) so each group is one stacked MLP
+        self.group_members: dict[str, list[str]] = {}
+        for site, (d_in, C) in site_shapes.items():
+            self.group_members.setdefault(f"{d_in}_{C}", []).append(site)
+        self.mlps = nn.ModuleDict()
+        for key, members in self.group_members.items():
+            d_in, C = site_shapes[members[0]]
+            self.mlps[key] = SiteMLP(len(members), d_in, tuple(hidden_dims), C, generator)
+
+    def forward(self, taps: dict[str, Tensor], **context: Any) -> dict[str, Tensor]:
+        out: dict[str, Tensor] = {}
+        for key, members in self.group_members.items():
+            xs = [taps[self.site_taps[s]] for s in members]
+            lead = xs[0].shape[:-1]
+            x = torch.stack([t.reshape(-1, t.shape[-1]) for t in xs]).float()
+            y = self.mlps[key](x)
+            for i, s in enumerate(members):
+                out[s] = y[i].reshape(*lead, -1)
+        return out
+
+    def parameter_census(self) -> dict[str, int]:
+        return census(self)
+
+    def useful_flops_per_position(self) -> int:
+        return sum(m.flops_per_row() for m in self.mlps.values())  # type: ignore[union-attr]
+
+
+class GlobalMLPCIFn(nn.Module):
+    """One MLP over the concatenation of all taps; its output splits into per-site CI."""
+
+    def __init__(self, taps: tuple[tuple[str, int], ...], site_cs: dict[str, int],
+                 hidden_dims: tuple[int, ...], generator: torch.Generator | None = None) -> None:
+        super().__init__()
+        self.input_taps = tuple(k for k, _ in taps)
+        self.site_cs = dict(site_cs)
+        d_in = sum(w for _, w in taps)
+        self.mlp = SiteMLP(1, d_in, tuple(hidden_dims), sum(site_cs.values()), generator)
+
+    def forward(self, taps: dict[str, Tensor], **context: Any) -> dict[str, Tensor]:
+        xs = [taps[k] for k in self.input_taps]
+        lead = xs[0].shape[:-1]
+        x = torch.cat([t.reshape(-1, t.shape[-1]) for t in xs], dim=-1).float()
+        y = self.mlp(x[None])[0]
+        parts = torch.split(y, list(self.site_cs.values()), dim=-1)
+        return {s: p.reshape(*lead, -1) for s, p in zip(self.site_cs, parts)}
+
+    def parameter_census(self) -> dict[str, int]:
+        return census(self)
+
+    def useful_flops_per_position(self) -> int:
+        return self.mlp.flops_per_row()

@@ -1,0 +1,302 @@
+"""The generic training engine: state init, resume / fine-tune, the step loop, logging, evaluation
+scheduling, preemption consensus and checkpoint cadence. Every target goes through this one loop
+and is seen only via the `DecomposedModel` protocol.
+
+Parity: param_decomp/core/run.py:1012-1199 (`run_decomposition_training`), :820-871 (Fresh |
+Resume | FineTune start), :747-798 (faithfulness warm-up), :1435-1636 (timed loop), :335-379
+(SIGTERM consensus), :282-322 (due evaluations), :883-909 (saver, no-checkpoint re-entry marker),
+:1202-1353 (targeted loop); core/run_state.py:252-380 (state init).
+"""
+
+from __future__ import annotations
+
+import signal
+import threading
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Callable, Protocol
+
+import torch
+from torch import nn
+
+from param_decomp_b200.config.run import (
+    Cadence,
+    KeepLastNCheckpoints,
+    NoCheckpointing,
+    PDConfig,
+    PeriodicCheckpointing,
+    ResumeProvenance,
+    TargetedPDConfig,
+)
+from param_decomp_b200.core import checkpoint as ckpt
+from param_decomp_b200.core.adversary import PersistentAdversary
+from param_decomp_b200.core.components import ComponentStacks
+from param_decomp_b200.core.metrics import (
+    NO_REENTRY_MARKER,
+    MetricsSink,
+    PerformanceTracker,
+    assert_all_finite,
+    get_logger,
+)
+from param_decomp_b200.core.model import DecomposedModel
+from param_decomp_b200.core.objective import NontargetObjective, PDObjective, build_objective
+from param_decomp_b200.core.optim import build_group_optimizer
+from param_decomp_b200.core.rng import StepKey
+from param_decomp_b200.core.train import DataCollectives, StepContext, TrainState, faithfulness_warmup, train_step
+
+
+class Evaluation(Protocol):
+    """Scheduled evaluation: `run(step, state) -> {key: scalar}` if anything is due at `step`."""
+
+    def is_due(self, step: int) -> bool: ...
+
+    def run(self, step: int, state: TrainState, ctx: StepContext) -> dict[str, Any]: ...
+
+
+# ---- preemption -------------------------------------------------------------------------------------
+
+
+class PreemptionFlag:
+    """SIGTERM sets a host flag; `consensus()` ORs it over ranks (a host-side all-reduce on the CPU
+    group) at a step boundary so every rank stops at the same step."""
+
+    def __init__(self, collectives: DataCollectives) -> None:
+        self._flag = threading.Event()
+        self._collectives = collectives
+        self._installed = False
+
+    def install(self) -> None:
+        if threading.current_thread() is threading.main_thread():
+            signal.signal(signal.SIGTERM, lambda *_: self._flag.set())
+            self._installed = True
+
+    def set(self) -> None:
+        self._flag.set()
+
+    def consensus(self) -> bool:
+        local = 1.0 if self._flag.is_set() else 0.0
+        any_fn = getattr(self._collectives, "host_any", None)
+        return bool(any_fn(local)) if any_fn is not None else bool(local)
+
+
+# ---- state ------------------------------------------------------------------------------------------
+
+
+def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | TargetedPDConfig,
+                     objective: PDObjective, device: torch.device | str, batch_rows: int,
+                     positions: int | None, stack_multiple: int = 1, use_fused_optim: bool = False,
+                     init_components: Callable[[ComponentStacks], None] | None = None) -> TrainState:
+    """Seeded init: `init` / `source` / `run` streams are separated like the reference's
+    `split(PRNGKey(seed), 3)`."""
+    g = torch.Generator().manual_seed(pd.seed)
+    components = ComponentStacks(model.sites, stack_multiple)
+    components.init_random(g)
+    if init_components is not None:
+        init_components(components)
+    components.to(device)
+    ci_fn.to(device)
+    comp_named = [(n, p) for n, p in components.named_parameters()]
+    ci_named = [(n, p) for n, p in ci_fn.named_parameters()]
+    state = TrainState(
+        components=components,
+        ci_fn=ci_fn,
+        components_opt=build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim),
+        ci_fn_opt=build_group_optimizer(pd.ci_fn_optimizer, ci_named, pd.steps, 2, use_fused_optim),
+    )
+    src_key = StepKey(pd.seed ^ 0x5EED, 0)
+    for term in objective.persistent_terms():
+        cfg = term.cfg
+        pool = cfg.pool.size_per_batch_element if hasattr(cfg, "pool") else 1  # type: ignore[attr-defined]
+        shape = getattr(cfg, "source_shape", "bc")
+        state.adversaries[term.name] = PersistentAdversary.init(
+            model.sites, cfg.optimizer, cfg.source_dtype, shape, batch_rows, positions, src_key,  # type: ignore[attr-defined]
+            pool_size=pool, device=device)
+    return state
+
+
+@dataclass
+class RunResult:
+    final_step: int
+    stopped_by_sigterm: bool
+    last_metrics: dict[str, float] = field(default_factory=dict)
+    run_dir: Path | None = None
+
+
+def _resolve_start(run_dir: Path | None, state: TrainState, cadence: Cadence,
+                   provenance: ResumeProvenance | None, log) -> str:
+    """Fresh | Resume(own newest checkpoint) | FineTune(parent V/U + CI fn, step 0)."""
+    if run_dir is not None:
+        if isinstance(cadence.checkpointing, NoCheckpointing):
+            marker = run_dir / NO_REENTRY_MARKER
+            assert not marker.exists(), f"{run_dir} ran without checkpoints: re-entering it is refused"
+            run_dir.mkdir(parents=True, exist_ok=True)
+            marker.write_text("started\n")
+        else:
+            own = ckpt.latest_step(run_dir)
+            if own is not None:
+                ckpt.restore_state(run_dir, own, state)
+                log.info("resumed from %s/ckpts/%d", run_dir, own)
+                return "resume"
+    if provenance is not None:
+        ckpt.restore_decomposition(provenance.parent_run_dir, provenance.parent_step, state.components, state.ci_fn)
+        log.info("fine-tune: loaded V/U + CI fn from %s step %d", provenance.parent_run_dir, provenance.parent_step)
+        return "finetune"
+    return "fresh"
+
+
+def run_decomposition_training(
+    model: DecomposedModel,
+    ci_fn: nn.Module,
+    pd: PDConfig | TargetedPDConfig,
+    cadence: Cadence,
+    sample_batch: Callable[[int], Any],
+    *,
+    device: torch.device | str = "cpu",
+    run_dir: Path | None = None,
+    sink: MetricsSink | None = None,
+    evaluation: Evaluation | None = None,
+    collectives: DataCollectives | None = None,
+    resume_provenance: ResumeProvenance | None = None,
+    nontarget: NontargetObjective | None = None,
+    sample_nontarget_batch: Callable[[int], Any] | None = None,
+    batch_rows: int | None = None,
+    positions: int | None = None,
+    units_per_step: int | None = None,
+    flops_per_step: float = 0.0,
+    peak_flops: float = 0.0,
+    lazy_masks: bool = False,
+    use_fused_optim: bool = False,
+    init_components: Callable[[ComponentStacks], None] | None = None,
+    extra_log: Callable[[int, TrainState, StepContext], dict[str, Any]] | None = None,
+    max_steps_this_entry: int | None = None,
+    profile_steps: int = 0,
+    state_out: list | None = None,
+) -> RunResult:
+    collectives = collectives or DataCollectives()
+    log = get_logger(collectives.rank)
+    objective = build_objective(pd)
+    ctx = StepContext.build(model, objective, pd, collectives=collectives, lazy_masks=lazy_masks, nontarget=nontarget)
+    rows = batch_rows if batch_rows is not None else pd.batch_size // collectives.world_size
+    state = init_train_state(model, ci_fn, pd, objective, device, rows, positions,
+                             use_fused_optim=use_fused_optim, init_components=init_components)
+    if state_out is not None:
+        state_out.append(state)
+    start_kind = _resolve_start(run_dir, state, cadence, resume_provenance, log)
+
+    if start_kind != "resume" and isinstance(pd, PDConfig) and pd.faithfulness_warmup_steps > 0:
+        last = faithfulness_warmup(ctx, state, pd.faithfulness_warmup_steps, pd.faithfulness_warmup_lr,
+                                   pd.faithfulness_warmup_weight_decay,
+                                   log=lambda i, v: log.info("faithfulness warm-up %d: %.3e", i, v))
+        log.info("faithfulness warm-up done (%.3e)", last)
+
+    own_sink = sink is None and run_dir is not None
+    if own_sink:
+        sink = MetricsSink.for_run(run_dir, collectives.rank)  # type: ignore[arg-type]
+    perf = PerformanceTracker(pd.steps, units_per_step or pd.batch_size, flops_per_step, peak_flops)
+    perf.step_last = state.step
+    preempt = PreemptionFlag(collectives)
+    preempt.install()
+
+    saving = isinstance(cadence.checkpointing, PeriodicCheckpointing) and run_dir is not None
+    keep = None
+    if saving and isinstance(cadence.checkpointing.retention, KeepLastNCheckpoints):  # type: ignore[union-attr]
+        keep = cadence.checkpointing.retention.n  # type: ignore[union-attr]
+
+    def save() -> None:
+        if saving and collectives.rank == 0:
+            ckpt.save_state(run_dir, state, keep)  # type: ignore[arg-type]
+        barrier = getattr(collectives, "barrier", None)
+        if barrier is not None:
+            barrier()
+
+    result = RunResult(final_step=state.step, stopped_by_sigterm=False, run_dir=run_dir)
+    entry_steps = 0
+    profiler = None
+    if profile_steps > 0 and run_dir is not None:
+        from torch.profiler import ProfilerActivity, profile
+
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+        profiler = profile(activities=acts)
+
+    while state.step < pd.steps:
+        step = state.step
+        if evaluation is not None and evaluation.is_due(step):
+            ev = evaluation.run(step, state, ctx)
+            if sink is not None and ev:
+                sink.log(step, ev, prefix="eval/")
+        if saving and step > 0 and step % cadence.checkpointing.save_every == 0 and ckpt.latest_step(run_dir) != step:  # type: ignore[union-attr,arg-type]
+            save()
+
+        batch = sample_batch(step)
+        nt_batch = sample_nontarget_batch(step) if sample_nontarget_batch is not None else None
+        if profiler is not None and entry_steps == 2:
+            profiler.start()
+        metrics = train_step(ctx, state, batch, nt_batch)
+        if profiler is not None and entry_steps == 2 + profile_steps - 1:
+            profiler.stop()
+            (Path(run_dir) / "profile").mkdir(parents=True, exist_ok=True)  # type: ignore[arg-type]
+            profiler.export_chrome_trace(str(Path(run_dir) / "profile" / "trace.json"))  # type: ignore[arg-type]
+            break
+        entry_steps += 1
+
+        if cadence.should_log_train(step) or state.step == pd.steps:
+            scalars = {k: v for k, v in metrics.items()}
+            scalars.update(perf.tick(state.step))
+            if extra_log is not None:
+                scalars.update(extra_log(step, state, ctx))
+            floats = sink.log(step, scalars) if sink is not None else {("train/" + k): float(v) for k, v in scalars.items()}
+            assert_all_finite(step, floats)
+            result.last_metrics = floats
+            log.info("step %d  total=%.4e  step_time=%.3fs", step, floats.get("train/loss/total", float("nan")),
+                     floats.get("train/perf/step_time_s", float("nan")))
+
+        if preempt.consensus():
+            log.info("SIGTERM consensus at step %d: saving and exiting", state.step)
+            save()
+            result.stopped_by_sigterm = True
+            break
+        if max_steps_this_entry is not None and entry_steps >= max_steps_this_entry:
+            break
+
+    if state.step >= pd.steps:
+        if evaluation is not None and evaluation.is_due(state.step):
+            ev = evaluation.run(state.step, state, ctx)
+            if sink is not None and ev:
+                sink.log(state.step, ev, prefix="eval/")
+        save()
+    result.final_step = state.step
+    if own_sink and sink is not None:
+        sink.close()
+    return result
+
+
+class StepWatchdog:
+    """Host thread that turns a stalled step into a clean abort: if `beat()` is not called for
+    `limit_s`, `on_stall` runs (default: raise SIGTERM in this process so the loop exits at the next
+    boundary, or `os._exit` if it never reaches one)."""
+
+    def __init__(self, limit_s: float, on_stall: Callable[[], None] | None = None) -> None:
+        self.limit_s = limit_s
+        self.on_stall = on_stall or (lambda: signal.raise_signal(signal.SIGTERM))
+        self._last = time.monotonic()
+        self._stop = threading.Event()
+        self.fired = False
+        self._thread = threading.Thread(target=self._watch, daemon=True)
+
+    def start(self) -> "StepWatchdog":
+        self._thread.start()
+        return self
+
+    def beat(self) -> None:
+        self._last = time.monotonic()
+
+    def stop(self) -> None:
+        self._stop.set()
+
+    def _watch(self) -> None:
+        while not self._stop.wait(min(self.limit_s / 4, 1.0)):
+            if time.monotonic() - self._last > self.limit_s:
+                self.fired = True
+                self.on_stall()
+                return
