@@ -38,6 +38,7 @@ class SiteMLP(nn.Module):
         dims = (d_in, *hidden_dims, d_out)
         self.dims = dims
         self.n_stack = n_stack
+        self.fused = False  # set by the builder on the fused sm_100a backend
         self.weights = nn.ParameterList()
         self.biases = nn.ParameterList()
         for a, b in zip(dims[:-1], dims[1:]):
@@ -50,8 +51,13 @@ class SiteMLP(nn.Module):
         """`x [n_stack, N, d_in] -> [n_stack, N, d_out]`."""
         h = x
         last = len(self.weights) - 1
+        fused = self.fused and x.is_cuda and all(d % 8 == 0 for d in self.dims)
+        if fused:
+            from param_decomp_b200.ops.linear import bmm_bias
+
+            h = h.to(torch.bfloat16)
         for i, (w, b) in enumerate(zip(self.weights, self.biases)):
-            h = torch.baddbmm(b.to(h.dtype), h, w.to(h.dtype))
+            h = bmm_bias(h, w, b) if fused else torch.baddbmm(b.to(h.dtype), h, w.to(h.dtype))
             if i != last:
                 h = F.gelu(h)  # exact erf form
         return h
@@ -82,8 +88,9 @@ class LayerwiseMLPCIFn(nn.Module):
         for key, members in self.group_members.items():
             xs = [taps[self.site_taps[s]] for s in members]
             lead = xs[0].shape[:-1]
-            x = torch.stack([t.reshape(-1, t.shape[-1]) for t in xs]).float()
-            y = self.mlps[key](x)
+            x = torch.stack([t.reshape(-1, t.shape[-1]) for t in xs])
+            mlp = self.mlps[key]
+            y = mlp(x if mlp.fused else x.float())
             for i, s in enumerate(members):
                 out[s] = y[i].reshape(*lead, -1)
         return out
@@ -109,8 +116,8 @@ class GlobalMLPCIFn(nn.Module):
     def forward(self, taps: dict[str, Tensor], **context: Any) -> dict[str, Tensor]:
         xs = [taps[k] for k in self.input_taps]
         lead = xs[0].shape[:-1]
-        x = torch.cat([t.reshape(-1, t.shape[-1]) for t in xs], dim=-1).float()
-        y = self.mlp(x[None])[0]
+        x = torch.cat([t.reshape(-1, t.shape[-1]) for t in xs], dim=-1)
+        y = self.mlp((x if self.mlp.fused else x.float())[None])[0]
         parts = torch.split(y, list(self.site_cs.values()), dim=-1)
         return {s: p.reshape(*lead, -1) for s, p in zip(self.site_cs, parts)}
 

@@ -199,21 +199,44 @@ class ComponentStacks(nn.Module):
 @dataclass
 class ComputeWeights:
     """Per-step working copies in the compute dtype (bf16 for LMs): cast once, used by every masked
-    forward of the step. Holds the autograd link back to the fp32 masters."""
+    forward of the step.
+
+    Eager backend: `V`/`U` are autograd views of the cast masters, gradients flow back through the
+    cast. Fused backend (`direct_grads=True`): `V`/`U` carry no autograd history; the site kernels
+    accumulate fp32 weight gradients straight into `grad_V`/`grad_U`, which are views of the stacked
+    masters' `.grad` buffers."""
 
     V: dict[str, Tensor] = field(default_factory=dict)
     U: dict[str, Tensor] = field(default_factory=dict)
+    grad_V: dict[str, Tensor] = field(default_factory=dict)
+    grad_U: dict[str, Tensor] = field(default_factory=dict)
+    direct_grads: bool = False
 
     def site(self, name: str) -> tuple[Tensor, Tensor]:
         return self.V[name], self.U[name]
 
+    def detached(self) -> "ComputeWeights":
+        """Same operands, no gradient of any kind (adversary ascents, evaluation)."""
+        return ComputeWeights({k: v.detach() for k, v in self.V.items()},
+                              {k: v.detach() for k, v in self.U.items()})
 
-def prepare_compute_weights(stacks: ComponentStacks, dtype: torch.dtype) -> ComputeWeights:
-    out = ComputeWeights()
+
+def prepare_compute_weights(stacks: ComponentStacks, dtype: torch.dtype, direct_grads: bool = False) -> ComputeWeights:
+    out = ComputeWeights(direct_grads=direct_grads)
     for gname, members in stacks.groups.items():
         key = stacks.param_key(gname)
-        Vc = stacks.V[key].to(dtype)  # one cast per stack; site views slice it
-        Uc = stacks.U[key].to(dtype)
+        pV, pU = stacks.V[key], stacks.U[key]
+        if direct_grads:
+            with torch.no_grad():
+                Vc, Uc = pV.to(dtype), pU.to(dtype)
+            if pV.grad is None:
+                pV.grad = torch.zeros_like(pV)
+            if pU.grad is None:
+                pU.grad = torch.zeros_like(pU)
+        else:
+            Vc, Uc = pV.to(dtype), pU.to(dtype)  # one cast per stack; site views slice it
         for i, s in enumerate(members):
             out.V[s.name], out.U[s.name] = Vc[i], Uc[i]
+            if direct_grads:
+                out.grad_V[s.name], out.grad_U[s.name] = pV.grad[i], pU.grad[i]
     return out

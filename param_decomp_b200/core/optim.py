@@ -86,8 +86,13 @@ class GroupOptimizer:
         if grads is None:
             grads = [p.grad for p in self.params]
         live = [(n, p, g) for n, p, g in zip(self.names, self.params, grads) if g is not None]
-        norm = global_norm([g for _, _, g in live])
-        scale = clip_scale(norm, self.cfg.grad_clip_norm)
+        if self.use_fused and live and live[0][1].is_cuda:
+            from param_decomp_b200.ops import optim as fused
+
+            norm, scale = fused.grad_norm_and_scale([g for _, _, g in live], self.cfg.grad_clip_norm)
+        else:
+            norm = global_norm([g for _, _, g in live])
+            scale = clip_scale(norm, self.cfg.grad_clip_norm)
         lr = self.lr_at(step_idx)
         self.count += 1
         self.applied_learning_rate = lr

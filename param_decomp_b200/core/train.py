@@ -258,7 +258,7 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
 
 
 def _detach_weights(w: ComputeWeights) -> ComputeWeights:
-    return ComputeWeights({k: v.detach() for k, v in w.V.items()}, {k: v.detach() for k, v in w.U.items()})
+    return w.detached()
 
 
 def _detach_ci(ci_lower: dict[str, Tensor]) -> dict[str, Tensor]:
@@ -305,7 +305,13 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
 
     with torch.no_grad():
         clean = ctx.model.clean_forward(batch, capture=obj.capture_keys())
-    weights = prepare_compute_weights(state.components, ctx.model.compute_dtype)
+    direct = getattr(ctx.model, "backend", "eager_torch") == "fused_sm100"
+    for p in state.components_opt.params + state.ci_fn_opt.params:
+        if direct and p.grad is not None:
+            p.grad.zero_()
+        else:
+            p.grad = None
+    weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct)
     ci = run_ci_fn(ctx, state, clean)
     ci_lower = ci.dense_lower()
 
@@ -371,8 +377,6 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         gs = torch.autograd.grad(tgt, [all_leaves[k] for k in names], retain_graph=True, allow_unused=True)
         final_grads.append((term, {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, gs)}))
 
-    for p in state.components_opt.params + state.ci_fn_opt.params:
-        p.grad = None
     total_loss.backward()
     ctx.collectives.reduce_grads(state.components_opt.params + state.ci_fn_opt.params)
 

@@ -1,0 +1,109 @@
+"""LM evaluation operations: CE / KL under the six mask variants, CI-L0, per-position active
+counts, attention-pattern reconstruction, plus the target-agnostic metrics of `evals.core`.
+
+Parity: param_decomp/experiments/lm/eval.py:309-394 (mask variants `ci_masked`, `unmasked`,
+`stoch_masked`, `random_masked`, `rounded_masked`, `zero_masked`; CE, KL vs the target, and the
+CE-unrecovered fraction against the zero-masked baseline), experiments/lm/eval_operations.py,
+attn_patterns_eval.py, ci_position_eval.py.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable
+
+import torch
+from torch import Tensor
+
+from param_decomp_b200.config import evals as E
+from param_decomp_b200.core import masking
+from param_decomp_b200.core.components import prepare_compute_weights
+from param_decomp_b200.core.rng import StepKey
+from param_decomp_b200.core.train import StepContext, TrainState, run_ci_fn
+from param_decomp_b200.evals.core import run_eval_metrics
+
+
+@torch.no_grad()
+def ce_and_kl(ctx: StepContext, state: TrainState, batch: Any, rounding_threshold: float = 0.0) -> dict[str, float]:
+    model = ctx.model
+    clean = model.clean_forward(batch)
+    weights = prepare_compute_weights(state.components, model.compute_dtype).detached()
+    ci = run_ci_fn(ctx, state, clean).dense_lower()
+    key = StepKey(0xE7A1, 0)
+    site_index = ctx.site_index
+    variants: dict[str, masking.Masks] = {
+        "ci_masked": masking.ci_masks(ci),
+        "unmasked": masking.unmasked_no_delta(ci),
+        "stoch_masked": masking.stochastic_masks(ci, key, 0, 0, site_index=site_index, lazy=False),
+        "random_masked": masking.stochastic_masks({k: torch.zeros_like(v) for k, v in ci.items()}, key, 1, 0,
+                                                  site_index=site_index, with_delta=False, lazy=False),
+        "rounded_masked": masking.ci_masks({k: (v > rounding_threshold).to(v.dtype) for k, v in ci.items()}),
+        "zero_masked": masking.constant_masks(ci, 0.0, None),
+    }
+    out: dict[str, float] = {}
+    target_ce = float(model.ce_loss(clean, batch.tokens))
+    out["ce/target"] = target_ce
+    ce: dict[str, float] = {}
+    for name, masks in variants.items():
+        res = model.masked_forward(weights, batch, masks)
+        out[f"kl/{name}"] = float(model.recon_loss(clean, res))
+        ce[name] = float(model.ce_loss(res, batch.tokens))
+        out[f"ce/{name}"] = ce[name]
+    denom = ce["zero_masked"] - target_ce
+    for name in variants:
+        out[f"ce_unrecovered/{name}"] = (ce[name] - target_ce) / denom if abs(denom) > 1e-12 else 0.0
+    return out
+
+
+@torch.no_grad()
+def active_counts_per_position(ci: dict[str, Tensor]) -> dict[str, float]:
+    out = {}
+    for thr in (0.0, 0.01, 0.1):
+        per_pos = sum((c > thr).float().sum(-1) for c in ci.values())  # [B, T]
+        out[f"l0/per_position/gt_{thr}/mean"] = float(per_pos.mean())
+        out[f"l0/per_position/gt_{thr}/last"] = float(per_pos[:, -1].mean())
+    return out
+
+
+@torch.no_grad()
+def attention_pattern_recon(ctx: StepContext, state: TrainState, batch: Any, stochastic: bool) -> dict[str, float]:
+    from param_decomp_b200.ops.attention_kl import attention_pattern_kl
+
+    model = ctx.model
+    n_layer = model.arch.n_layer
+    keys = tuple(f"attn_scores.{i}" for i in range(n_layer))
+    clean = model.clean_forward(batch, capture=keys)
+    weights = prepare_compute_weights(state.components, model.compute_dtype).detached()
+    ci = run_ci_fn(ctx, state, clean).dense_lower()
+    masks = (masking.stochastic_masks(ci, StepKey(0xE7A2, 0), 0, 0, site_index=ctx.site_index, lazy=False)
+             if stochastic else masking.ci_masks(ci))
+    res = model.masked_forward(weights, batch, masks, capture=keys)
+    vals = [float(attention_pattern_kl(clean.captures[k], res.captures[k])) for k in keys]
+    tag = "StochasticAttnPatternsReconLoss" if stochastic else "CIMaskedAttnPatternsReconLoss"
+    out = {f"{tag}/layer_{i}": v for i, v in enumerate(vals)}
+    out[tag] = sum(vals) / len(vals)
+    return out
+
+
+class LMEvaluation:
+    def __init__(self, cfg: E.EvalConfig, sample_eval: Callable[[int], Any]) -> None:
+        self.cfg = cfg
+        self.sample = sample_eval
+
+    def is_due(self, step: int) -> bool:
+        return any(self.cfg.is_due(m, step) for m in self.cfg.metrics)
+
+    def _extra(self, metric: Any, step: int, state: TrainState, ctx: StepContext, batch: Any) -> dict[str, float]:
+        if isinstance(metric, E.CEandKLLossesConfig):
+            return ce_and_kl(ctx, state, batch, metric.rounding_threshold)
+        if isinstance(metric, E.CIActiveCountsPerPositionConfig):
+            with torch.no_grad():
+                clean = ctx.model.clean_forward(batch)
+                return active_counts_per_position(run_ci_fn(ctx, state, clean).dense_lower())
+        if isinstance(metric, E.CIMaskedAttnPatternsReconLossConfig):
+            return attention_pattern_recon(ctx, state, batch, stochastic=False)
+        if isinstance(metric, E.StochasticAttnPatternsReconLossConfig):
+            return attention_pattern_recon(ctx, state, batch, stochastic=True)
+        return {}
+
+    def run(self, step: int, state: TrainState, ctx: StepContext) -> dict[str, Any]:
+        return run_eval_metrics(self.cfg, step, state, ctx, self.sample, extra=self._extra)

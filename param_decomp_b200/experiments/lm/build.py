@@ -1,0 +1,123 @@
+"""Resolve an `LMExperimentConfig` into runtime objects: target, sites, CI function, data sources.
+
+Parity: param_decomp/experiments/lm/load_run.py:88-183 (`load_target`, `build_target`),
+experiments/lm/config.py:262-327 (C-spec -> site tree), :454-696 (CI-fn resolution),
+experiments/lm/training.py:197-301 (`_train` wiring).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any, Callable
+
+import torch
+from torch import nn
+
+from param_decomp_b200.config import experiments as X
+from param_decomp_b200.core.ci_fn.mlp import GlobalMLPCIFn, LayerwiseMLPCIFn
+from param_decomp_b200.core.components import SiteSpec
+from param_decomp_b200.data.synthetic import ZipfTokenSource
+from param_decomp_b200.models import transformer as tf
+
+
+@dataclass
+class LMRun:
+    model: Any
+    ci_fn: nn.Module
+    sample_train: Callable[[int], Any]
+    sample_eval: Callable[[int], Any]
+    arch: X.TransformerArchConfig
+    tokens_per_step: int
+    init_components: Callable | None = None
+
+
+def _dtype(name: str) -> torch.dtype:
+    return torch.bfloat16 if name == "bfloat16" else torch.float32
+
+
+def resolve_site_cs(sites: Any, arch: X.TransformerArchConfig) -> dict[str, int]:
+    """Tile the per-matrix-type `cs` over the selected layers, in canonical within-block order."""
+    layers = X.select_layers(sites.layers, arch.n_layer)
+    if isinstance(sites, X.GluTransformerCSpec):
+        assert arch.family == "glu_transformer", f"c-spec family glu_transformer != target family {arch.family}"
+        kinds = [k for k in tf.GLU_KINDS if k in sites.cs]
+    elif isinstance(sites, X.SimpleMlpCSpec):
+        assert arch.family == "simple_mlp", f"c-spec family simple_mlp != target family {arch.family}"
+        kinds = [k for k in tf.SIMPLE_KINDS if k in sites.cs]
+    else:
+        raise NotImplementedError(f"site spec {sites.kind!r} is resolved by its own target module")
+    return {tf.site_name(arch.family, i, k): sites.cs[k] for i in layers for k in kinds}
+
+
+def load_target_weights(cfg: X.LMTargetConfig, data_root: Path | None, device) -> tuple[X.TransformerArchConfig, dict]:
+    spec = cfg.spec
+    dtype = _dtype(cfg.weights_dtype)
+    if isinstance(spec, X.RandomInitTarget):
+        return spec.arch, tf.random_init_weights(spec.arch, spec.seed, dtype, device)
+    from param_decomp_b200.models import loaders
+
+    return loaders.load_from_spec(spec, data_root, dtype, device)
+
+
+def build_ci_fn(cfg: Any, model: Any, seed: int) -> nn.Module:
+    g = torch.Generator().manual_seed(seed + 1)
+    sites: tuple[SiteSpec, ...] = model.sites
+    if isinstance(cfg, X.LMLayerwiseMlpCIFnConfig):
+        return LayerwiseMLPCIFn({s.name: (s.d_in, s.C) for s in sites}, {s.name: model.tap_for_site(s.name) for s in sites},
+                                tuple(cfg.hidden_dims), g)
+    from param_decomp_b200.core.ci_fn import resolve
+
+    return resolve.build_lm_ci_fn(cfg, model, g)
+
+
+def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_root: Path | None,
+                 device: torch.device | str, rank: int = 0, world: int = 1) -> LMRun:
+    arch, weights = load_target_weights(cfg.target, data_root, device)
+    sites_cfg = cfg.decomposition.sites
+    edge = cfg.target.output_edge
+    n_chunks = edge.n_vocab_chunks if isinstance(edge, X.StreamedOutputEdgeConfig) else None
+    backend = cfg.runtime.backend if torch.device(device).type == "cuda" else "eager_torch"
+    if arch.family == "moe" or isinstance(sites_cfg, (X.MoeCSpec, X.Qwen36MoeCSpec)):
+        from param_decomp_b200.models import moe
+
+        model = moe.build_moe_model(arch, weights, sites_cfg, cfg.target, backend, rank, world)
+    else:
+        site_cs = resolve_site_cs(sites_cfg, arch)
+        model = tf.TransformerDecomposedModel(arch, weights, site_cs, backend=backend,
+                                              attention=cfg.target.attention_implementation, n_vocab_chunks=n_chunks)
+    ci_fn = build_ci_fn(cfg.decomposition.ci, model, cfg.pd.seed)
+    if backend == "fused_sm100":
+        from param_decomp_b200.core.ci_fn.mlp import SiteMLP
+
+        for m in ci_fn.modules():
+            if isinstance(m, SiteMLP):
+                m.fused = True
+
+    seq = cfg.data.seq_len
+
+    def source(ref: Any, salt: int):
+        if isinstance(ref, X.SyntheticZipfDataset):
+            return ZipfTokenSource(arch.vocab_size, seq, ref.exponent, ref.seed + salt)
+        from param_decomp_b200.data.shards import ShardServer
+
+        assert data_root is not None, "named datasets need --data-root"
+        return ShardServer.open(ref, data_root, seq, cfg.data.layout, seed=cfg.pd.seed + salt)
+
+    train_src, eval_src = source(cfg.data.train, 0), source(cfg.data.eval, 1)
+    gb = cfg.pd.batch_size
+    eb = cfg.eval.batch_size if cfg.eval is not None else gb
+    pin = torch.device(device).type == "cuda"
+
+    def sample_train(step: int):
+        return train_src.batch(step, gb, rank, world, pin=pin).to(device, non_blocking=True)
+
+    def sample_eval(i: int):
+        return eval_src.batch(i, eb, rank, world, pin=pin).to(device, non_blocking=True)
+
+    init = None
+    if getattr(sites_cfg, "initialization", "random") == "nonlinearity_aligned":
+        from param_decomp_b200.core.init_aligned import nonlinearity_aligned_init
+
+        init = lambda comps: nonlinearity_aligned_init(comps, model, cfg.pd.seed)  # noqa: E731
+    return LMRun(model, ci_fn, sample_train, sample_eval, arch, gb * seq, init)

@@ -1,0 +1,39 @@
+"""`python -m param_decomp_b200.experiments.lm.run <config.yaml> --data-root <dir>`
+
+One process per GPU (launch N ranks with `torchrun`); rank/world come from the environment.
+The process environment named in `runtime.launch_env` is exported before CUDA initialises.
+
+Parity: param_decomp/experiments/lm/run.py:12-32 and experiments/lm/training.py:197-371.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+from pathlib import Path
+
+
+def main(argv: list[str] | None = None) -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("config", type=Path)
+    ap.add_argument("--data-root", type=Path, required=True)
+    ap.add_argument("--run-id", type=str, default=None)
+    ap.add_argument("--device", type=str, default=None)
+    ap.add_argument("--max-steps", type=int, default=None, help="stop this entry after N steps")
+    args = ap.parse_args(argv)
+
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+
+    cfg = LMExperimentConfig.from_file(args.config)
+    for k, v in cfg.runtime.launch_env.rendered().items():
+        os.environ.setdefault(k, v)
+
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    res = train_lm(cfg, args.data_root, run_id=args.run_id, device=args.device, max_steps_this_entry=args.max_steps)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(f"finished at step {res.final_step}: {res.run_dir}")
+
+
+if __name__ == "__main__":
+    main()

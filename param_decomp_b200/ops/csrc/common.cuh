@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 namespace pd {
 
@@ -230,15 +231,16 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// ---- Philox4x32-10 -----------------------------------------------------------------------------
+// ---- Philox4x32-7 ------------------------------------------------------------------------------
 // Counter-based, so a mask element is a pure function of (seed, stream, row, column): the same
 // on every rank and every tiling, and recomputable in the backward pass without storing it.
 struct Philox {
   static constexpr uint32_t kM0 = 0xD2511F53u, kM1 = 0xCD9E8D57u;
   static constexpr uint32_t kW0 = 0x9E3779B9u, kW1 = 0xBB67AE85u;
+  static constexpr int kRounds = 7;  // the fewest rounds for which Philox4x32 passes BigCrush
   __host__ __device__ static inline uint4 run(uint4 c, uint2 k) {
 #pragma unroll
-    for (int i = 0; i < 10; ++i) {
+    for (int i = 0; i < kRounds; ++i) {
 #ifdef __CUDA_ARCH__
       const uint32_t hi0 = __umulhi(kM0, c.x), lo0 = kM0 * c.x;
       const uint32_t hi1 = __umulhi(kM1, c.z), lo1 = kM1 * c.z;
@@ -255,6 +257,19 @@ struct Philox {
   }
 };
 
+// (b + 0.5) / 65536 without an int->float conversion: put the 16 bits at the top of the mantissa
+// of a float in [1,2), subtract 1, add half a step. Exact in fp32.
+__host__ __device__ inline float bits16_to_unit(uint32_t b) {
+  const uint32_t f = 0x3F800000u | (b << 7);
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(f) - 1.0f + (0.5f / 65536.0f);
+#else
+  float x;
+  memcpy(&x, &f, 4);
+  return x - 1.0f + (0.5f / 65536.0f);
+#endif
+}
+
 // Eight uniforms in (0,1) with 16 random bits each for columns [8*g, 8*g+8) of `row`.
 // u = (bits + 0.5) / 65536: never 0 or 1, exactly representable in fp32.
 __host__ __device__ inline void philox_uniform8(uint64_t seed, uint32_t stream, uint32_t row,
@@ -265,8 +280,8 @@ __host__ __device__ inline void philox_uniform8(uint64_t seed, uint32_t stream, 
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    u[2 * i] = (static_cast<float>(w[i] & 0xFFFFu) + 0.5f) * (1.0f / 65536.0f);
-    u[2 * i + 1] = (static_cast<float>(w[i] >> 16) + 0.5f) * (1.0f / 65536.0f);
+    u[2 * i] = bits16_to_unit(w[i] & 0xFFFFu);
+    u[2 * i + 1] = bits16_to_unit(w[i] >> 16);
   }
 }
 

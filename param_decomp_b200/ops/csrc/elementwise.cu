@@ -1,0 +1,389 @@
+// Bandwidth-bound kernels of the step: fused AdamW with device-side global-norm clipping,
+// fp32 -> bf16 casts, RMSNorm forward/backward, rotary embedding, SwiGLU forward/backward,
+// per-row scaling, leaky-hard sigmoids. All are plain grid-stride / row-per-warp kernels with
+// 16-byte vector accesses; none of them waits on anything, so none needs a status word.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+inline int blocks_for(long long n, int per_block, int cap = 148 * 16) {
+  long long b = (n + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  return static_cast<int>(b < cap ? b : cap);
+}
+
+// ---- optimizer ------------------------------------------------------------------------------
+__global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+  float acc = 0.f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n;
+       i += stride) {
+    if (i + 3 < n) {
+      const float4 v = *reinterpret_cast<const float4*>(g + i);
+      acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    } else {
+      for (long long j = i; j < n; ++j) acc += g[j] * g[j];
+    }
+  }
+  acc = warp_sum(acc);
+  __shared__ float part[kThreads / 32];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kThreads / 32 ? part[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) atomicAdd(out, v);
+  }
+}
+
+// scale = min(max_norm / (sqrt(sumsq) + 1e-6), 1); max_norm <= 0 means no clipping.
+__global__ void clip_scale_kernel(const float* __restrict__ sumsq, float max_norm,
+                                  float* __restrict__ scale, float* __restrict__ norm_out) {
+  const float norm = sqrtf(*sumsq);
+  *norm_out = norm;
+  *scale = max_norm > 0.f ? fminf(max_norm / (norm + 1e-6f), 1.f) : 1.f;
+}
+
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v, long long n, float lr,
+                             float b1, float b2, float eps, float wd, float inv_bc1, float inv_bc2,
+                             const float* __restrict__ grad_scale) {
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n;
+       i += stride) {
+    if (i + 3 < n) {
+      float4 pp = *reinterpret_cast<float4*>(p + i);
+      const float4 gg = *reinterpret_cast<const float4*>(g + i);
+      float4 mm = *reinterpret_cast<float4*>(m + i);
+      float4 vv = *reinterpret_cast<float4*>(v + i);
+      float* pa = &pp.x; const float* ga = &gg.x; float* ma = &mm.x; float* va = &vv.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gk = ga[k] * gs;
+        ma[k] = b1 * ma[k] + (1.f - b1) * gk;
+        va[k] = b2 * va[k] + (1.f - b2) * gk * gk;
+        const float upd = (ma[k] * inv_bc1) / (sqrtf(va[k] * inv_bc2) + eps) + wd * pa[k];
+        pa[k] -= lr * upd;
+      }
+      *reinterpret_cast<float4*>(p + i) = pp;
+      *reinterpret_cast<float4*>(m + i) = mm;
+      *reinterpret_cast<float4*>(v + i) = vv;
+    } else {
+      for (long long j = i; j < n; ++j) {
+        const float gk = g[j] * gs;
+        m[j] = b1 * m[j] + (1.f - b1) * gk;
+        v[j] = b2 * v[j] + (1.f - b2) * gk * gk;
+        p[j] -= lr * ((m[j] * inv_bc1) / (sqrtf(v[j] * inv_bc2) + eps) + wd * p[j]);
+      }
+    }
+  }
+}
+
+__global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                 long long n) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n;
+       i += stride) {
+    if (i + 7 < n) {
+      const float4 a = *reinterpret_cast<const float4*>(src + i);
+      const float4 b = *reinterpret_cast<const float4*>(src + i + 4);
+      __nv_bfloat162 o[4] = {__floats2bfloat162_rn(a.x, a.y), __floats2bfloat162_rn(a.z, a.w),
+                             __floats2bfloat162_rn(b.x, b.y), __floats2bfloat162_rn(b.z, b.w)};
+      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<uint4*>(o);
+    } else {
+      for (long long j = i; j < n; ++j) dst[j] = __float2bfloat16(src[j]);
+    }
+  }
+}
+
+// ---- RMSNorm: one warp per row, bf16 in/out, fp32 statistics -----------------------------------
+// forward also stores rstd[row] for the backward.
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                   long long rows, int d, float eps) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  for (long long row = static_cast<long long>(blockIdx.x) * warps + (threadIdx.x >> 5); row < rows;
+       row += static_cast<long long>(gridDim.x) * warps) {
+    const __nv_bfloat16* xr = x + row * d;
+    float ss = 0.f;
+    for (int i = lane * 8; i < d; i += 256) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xr + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / d + eps);
+    if (lane == 0 && rstd) rstd[row] = r;
+    __nv_bfloat16* yr = y + row * d;
+    for (int i = lane * 8; i < d; i += 256) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xr + i);
+      const uint4 wq = w ? *reinterpret_cast<const uint4*>(w + i) : make_uint4(0, 0, 0, 0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wq);
+      __nv_bfloat162 o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 f = __bfloat1622float2(h[k]);
+        const float2 g = w ? __bfloat1622float2(wh[k]) : make_float2(1.f, 1.f);
+        o[k] = __floats2bfloat162_rn(f.x * r * g.x, f.y * r * g.y);
+      }
+      *reinterpret_cast<uint4*>(yr + i) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+}
+
+// dx = rstd * (g*w - xhat * mean(g*w*xhat)), xhat = x*rstd. The weight is frozen: no dw.
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ dy,
+                                   const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+                                   long long rows, int d) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  for (long long row = static_cast<long long>(blockIdx.x) * warps + (threadIdx.x >> 5); row < rows;
+       row += static_cast<long long>(gridDim.x) * warps) {
+    const __nv_bfloat16* xr = x + row * d;
+    const __nv_bfloat16* gr = dy + row * d;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane * 8; i < d; i += 256) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xr + i);
+      const uint4 gq = *reinterpret_cast<const uint4*>(gr + i);
+      const uint4 wq = w ? *reinterpret_cast<const uint4*>(w + i) : make_uint4(0, 0, 0, 0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wq);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]), g = __bfloat1622float2(gh[k]);
+        const float2 ww = w ? __bfloat1622float2(wh[k]) : make_float2(1.f, 1.f);
+        dot += g.x * ww.x * f.x * r + g.y * ww.y * f.y * r;
+      }
+    }
+    dot = warp_sum(dot) / d;
+    __nv_bfloat16* dr = dx + row * d;
+    for (int i = lane * 8; i < d; i += 256) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xr + i);
+      const uint4 gq = *reinterpret_cast<const uint4*>(gr + i);
+      const uint4 wq = w ? *reinterpret_cast<const uint4*>(w + i) : make_uint4(0, 0, 0, 0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wq);
+      __nv_bfloat162 o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]), g = __bfloat1622float2(gh[k]);
+        const float2 ww = w ? __bfloat1622float2(wh[k]) : make_float2(1.f, 1.f);
+        o[k] = __floats2bfloat162_rn(r * (g.x * ww.x - f.x * r * dot), r * (g.y * ww.y - f.y * r * dot));
+      }
+      *reinterpret_cast<uint4*>(dr + i) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+}
+
+// ---- rotary embedding (rotate-half form), in place on [rows = B*T, heads, hd] -------------------
+// cos/sin [T, hd/2] fp32; `inverse` applies the transpose rotation (the backward).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+                            const float* __restrict__ sn, long long rows, int T, int heads, int hd,
+                            int inverse) {
+  const int half = hd >> 1;
+  const long long total = rows * heads * half;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i % half);
+    const long long rh = i / half;
+    const long long row = rh / heads;
+    const int t = static_cast<int>(row % T);
+    const float c = cs[t * half + j];
+    const float s = inverse ? -sn[t * half + j] : sn[t * half + j];
+    __nv_bfloat16* p = x + rh * hd;
+    const float a = __bfloat162float(p[j]), b = __bfloat162float(p[j + half]);
+    p[j] = __float2bfloat16(a * c - b * s);
+    p[j + half] = __float2bfloat16(b * c + a * s);
+  }
+}
+
+// ---- SwiGLU ---------------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate,
+                                  const __nv_bfloat16* __restrict__ up,
+                                  __nv_bfloat16* __restrict__ out, long long n) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n;
+       i += stride) {
+    const uint4 gq = *reinterpret_cast<const uint4*>(gate + i);
+    const uint4 uq = *reinterpret_cast<const uint4*>(up + i);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uq);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(gh[k]), u = __bfloat1622float2(uh[k]);
+      o[k] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate,
+                                  const __nv_bfloat16* __restrict__ up,
+                                  const __nv_bfloat16* __restrict__ dout,
+                                  __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup,
+                                  long long n) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n;
+       i += stride) {
+    const uint4 gq = *reinterpret_cast<const uint4*>(gate + i);
+    const uint4 uq = *reinterpret_cast<const uint4*>(up + i);
+    const uint4 dq = *reinterpret_cast<const uint4*>(dout + i);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uq);
+    const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&dq);
+    __nv_bfloat162 og[4], ou[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(gh[k]), u = __bfloat1622float2(uh[k]),
+                   d = __bfloat1622float2(dh[k]);
+      const float sx = 1.f / (1.f + __expf(-g.x)), sy = 1.f / (1.f + __expf(-g.y));
+      ou[k] = __floats2bfloat162_rn(d.x * g.x * sx, d.y * g.y * sy);
+      og[k] = __floats2bfloat162_rn(d.x * u.x * sx * (1.f + g.x * (1.f - sx)),
+                                    d.y * u.y * sy * (1.f + g.y * (1.f - sy)));
+    }
+    *reinterpret_cast<uint4*>(dgate + i) = *reinterpret_cast<uint4*>(og);
+    *reinterpret_cast<uint4*>(dup + i) = *reinterpret_cast<uint4*>(ou);
+  }
+}
+
+// y[row, :] = x[row, :] * s[row]
+__global__ void rowscale_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ s,
+                                __nv_bfloat16* __restrict__ y, long long rows, int d) {
+  const long long total = rows * (d / 8);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / (d / 8);
+    const float sc = s[row];
+    const uint4 q = *reinterpret_cast<const uint4*>(x + i * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      o[k] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+    *reinterpret_cast<uint4*>(y + i * 8) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// lower (bf16, masks) and upper (fp32-accurate bf16, minimality) leaky-hard sigmoids of fp32/bf16
+// pre-activations in one pass.
+__global__ void ci_squash_kernel(const __nv_bfloat16* __restrict__ pre,
+                                 __nv_bfloat16* __restrict__ lower,
+                                 __nv_bfloat16* __restrict__ upper, long long n, float alpha) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n;
+       i += stride) {
+    const uint4 q = *reinterpret_cast<const uint4*>(pre + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    __nv_bfloat162 lo[4], hi[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      const float lx = fminf(fmaxf(f.x, 0.f), 1.f), ly = fminf(fmaxf(f.y, 0.f), 1.f);
+      lo[k] = __floats2bfloat162_rn(lx, ly);
+      hi[k] = __floats2bfloat162_rn(f.x > 1.f ? 1.f + alpha * (f.x - 1.f) : lx,
+                                    f.y > 1.f ? 1.f + alpha * (f.y - 1.f) : ly);
+    }
+    *reinterpret_cast<uint4*>(lower + i) = *reinterpret_cast<uint4*>(lo);
+    *reinterpret_cast<uint4*>(upper + i) = *reinterpret_cast<uint4*>(hi);
+  }
+}
+
+}  // namespace
+
+#define PD_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : 1)
+
+extern "C" int pd_sumsq(const float* g, long long n, float* out, void* stream) {
+  sumsq_kernel<<<blocks_for(n, kThreads * 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(g, n, out);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_clip_scale(const float* sumsq, float max_norm, float* scale, float* norm, void* stream) {
+  clip_scale_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, scale, norm);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_adamw(float* p, const float* g, float* m, float* v, long long n, float lr, float b1,
+                        float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
+                        void* stream) {
+  adamw_kernel<<<blocks_for(n, kThreads * 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      p, g, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, grad_scale);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_cast_bf16(const float* src, void* dst, long long n, void* stream) {
+  cast_bf16_kernel<<<blocks_for(n, kThreads * 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, static_cast<__nv_bfloat16*>(dst), n);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int d,
+                              float eps, void* stream) {
+  if (d % 8 != 0) return 5;
+  rmsnorm_fwd_kernel<<<blocks_for(rows, kThreads / 32), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(y), rstd, rows, d, eps);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                              long long rows, int d, void* stream) {
+  if (d % 8 != 0) return 5;
+  rmsnorm_bwd_kernel<<<blocks_for(rows, kThreads / 32), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<__nv_bfloat16*>(dx), rows, d);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rope(void* x, const float* cs, const float* sn, long long rows, int T, int heads, int hd,
+                       int inverse, void* stream) {
+  rope_kernel<<<blocks_for(rows * heads * (hd / 2), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), cs, sn, rows, T, heads, hd, inverse);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_swiglu_fwd(const void* gate, const void* up, void* out, long long n, void* stream) {
+  if (n % 8 != 0) return 5;
+  swiglu_fwd_kernel<<<blocks_for(n, kThreads * 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
+      static_cast<__nv_bfloat16*>(out), n);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup,
+                             long long n, void* stream) {
+  if (n % 8 != 0) return 5;
+  swiglu_bwd_kernel<<<blocks_for(n, kThreads * 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
+      static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dgate),
+      static_cast<__nv_bfloat16*>(dup), n);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rowscale(const void* x, const float* s, void* y, long long rows, int d, void* stream) {
+  if (d % 8 != 0) return 5;
+  rowscale_kernel<<<blocks_for(rows * (d / 8), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), s, static_cast<__nv_bfloat16*>(y), rows, d);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_ci_squash(const void* pre, void* lower, void* upper, long long n, float alpha, void* stream) {
+  if (n % 8 != 0) return 5;
+  ci_squash_kernel<<<blocks_for(n, kThreads * 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(lower),
+      static_cast<__nv_bfloat16*>(upper), n, alpha);
+  return PD_CHECK_LAUNCH();
+}

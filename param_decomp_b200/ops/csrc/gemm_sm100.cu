@@ -11,9 +11,14 @@
 // Two K-phases let one accumulator take  (xV .* coef) U  +  (d .* x) W^T  without a second pass:
 // phase 0 walks the component axis, phase 1 walks d_in, and the sum never leaves TMEM.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + single-thread MMA issuer,
-// warps 2..5 = epilogue (each owns the TMEM lane quarter warp_id % 4). Two accumulators of BN columns
-// alternate so the epilogue of tile i overlaps the main loop of tile i+1.
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + single-thread MMA issuer,
+// warps 2..9 = epilogue. A warp may only read the TMEM lane quarter warp_id % 4, so two warps share
+// each quarter and take alternate output boxes; with short K (d_in = 768) the epilogue is the
+// longer half of a tile and needs the issue slots of all four schedulers. Two accumulators of BN
+// columns alternate so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Tiles are rasterised in panels of kGroupM row blocks so that one wave of CTAs touches few
+// distinct A and B blocks (both stay in L2 while the [M,N]-sized epilogue tensors stream past).
 //
 // Epilogues:
 //   EPI_PLAIN     out0 = act(alpha * acc + bias)          bf16 or fp32, optional reduce-add (split-K
@@ -30,7 +35,9 @@ namespace pd {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kNumThreads = 192;
+constexpr int kNumEpiWarps = 8;
+constexpr int kNumThreads = 32 * (2 + kNumEpiWarps);
+constexpr int kGroupM = 16;
 constexpr int kStageBytesA = BM * BK * 2;  // 16 KiB
 constexpr int kOutBoxBytes = 32 * 128;     // one 32-row x 128-byte staging box
 
@@ -60,6 +67,7 @@ struct GemmArgs {
   int dci_accumulate;
   unsigned long long seed;
   unsigned int stream;
+  unsigned int row_offset;
   int mask_mode;
   int* status;
 };
@@ -68,7 +76,7 @@ template <int BN, int NOUT>
 struct SmemPlan {
   static constexpr int kStageBytesB = BN * BK * 2;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kOutBytes = 4 * NOUT * 2 * kOutBoxBytes;
+  static constexpr int kOutBytes = kNumEpiWarps * NOUT * kOutBoxBytes;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/;
   static constexpr int kStagesRaw = (kBudget - kOutBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
@@ -174,7 +182,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, 4);
+      mbar_init(bar_tempty + 8 * s, kNumEpiWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -195,14 +203,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  // Tile decode: m fastest so the CTAs of one wave share the B block (kept hot in L2).
+  // Tile decode: batch / split outermost, then panels of kGroupM row blocks walked column by column.
+  const long long tiles_per_mat = static_cast<long long>(num_m) * num_n;
   auto decode = [&](long long t, int& b, int& mb, int& nb, int& sp) {
-    mb = static_cast<int>(t % num_m);
-    t /= num_m;
-    nb = static_cast<int>(t % num_n);
-    t /= num_n;
-    sp = static_cast<int>(t % split);
-    b = static_cast<int>(t / split);
+    const long long outer = t / tiles_per_mat;
+    const int pid = static_cast<int>(t % tiles_per_mat);
+    sp = static_cast<int>(outer % split);
+    b = static_cast<int>(outer / split);
+    const int per_group = kGroupM * num_n;
+    const int group = pid / per_group;
+    const int first_m = group * kGroupM;
+    const int gsz = min(num_m - first_m, kGroupM);
+    const int in_group = pid % per_group;
+    mb = first_m + in_group % gsz;
+    nb = in_group / gsz;
   };
 
   if (warp == 0) {
@@ -312,23 +326,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const uint32_t my_out = smem_out + q * (NOUT * 2 * kOutBoxBytes);
+    const int ew = warp - 2;   // 0..7
+    const int q = warp & 3;    // TMEM lane quarter this warp may read
+    const int grp = ew >> 2;   // the two warps of a quarter take alternate boxes
+    const uint32_t box0 = smem_out + ew * (NOUT * kOutBoxBytes);
+    const uint32_t box1 = box0 + (NOUT - 1) * kOutBoxBytes;
     int acc = 0;
     uint32_t acc_phase = 0;
-    int buf = 0;
+    const bool out32 = (EPI == EPI_PLAIN) && args.out_fp32;
+    const int box_cols = out32 ? 32 : 64;
+    const int nboxes = BN / box_cols;
+    const bool plain_fast = (EPI == EPI_PLAIN) && args.bias == nullptr && args.act == ACT_NONE &&
+                            args.alpha == 1.0f;
     for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int b, mb, nb, sp;
       decode(t, b, mb, nb, sp);
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
-        if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
-        break;
-      }
-      tc_fence_after();
       const int row = mb * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t tmem_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-
       float delta = 0.0f, rs = 1.0f;
       if constexpr (EPI != EPI_PLAIN) {
         if (row_ok) {
@@ -336,137 +351,164 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           if (args.rowscale) rs = args.rowscale[row];
         }
       }
-
-      const bool box64 = (EPI != EPI_PLAIN) || !args.out_fp32;  // bf16 outputs use 64-col boxes
+      bool have_acc = false;
+      bool failed = false;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = nb * BN + c * 32;
+      for (int j = grp; j < nboxes; j += 2) {
+        const int col0 = nb * BN + j * box_cols;
         if (col0 >= args.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_row + c * 32, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-
-        const int half = box64 ? (c & 1) : 0;
-        const bool new_box = box64 ? (half == 0) : true;
-        if (new_box) {
-          // The boxes of `buf` were handed to TMA two steps ago: make sure they have been read.
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-        }
-        const uint32_t box0 = my_out + (0 * 2 + buf) * kOutBoxBytes;
-        const uint32_t box1 = my_out + ((NOUT - 1) * 2 + buf) * kOutBoxBytes;
-
-        if constexpr (EPI == EPI_PLAIN) {
-          const float* bias = args.bias ? args.bias + b * args.bias_bs : nullptr;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = v[i] * args.alpha;
-            if (bias && col0 + i < args.N) x += bias[col0 + i];
-            v[i] = apply_act(x, args.act);
-          }
-          if (args.out_fp32)
-            stage_fp32(box0, lane, v);
-          else
-            stage_bf16_half(box0, lane, half, v);
-        } else {
-          // ---- mask epilogues: coef[i] for this row and 32 columns ----
-          float coef[32], dmdci[32];
+        // Global operands of the mask epilogues are requested before the accumulator wait so their
+        // latency hides behind the main loop of this tile.
+        uint4 ciq[8];
+        if constexpr (EPI != EPI_PLAIN) {
           const __nv_bfloat16* ci_row = args.ci + static_cast<long long>(row) * args.ld_ci + col0;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float cf[8];
-            const bool ok = row_ok && (col0 + 8 * g < args.N);
-            if (ok) {
-              unpack8(*reinterpret_cast<const uint4*>(ci_row + 8 * g), cf);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) cf[i] = 0.0f;
-            }
-            if (args.mask_mode == 0) {
-              float u[8];
-              philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(row),
-                              static_cast<uint32_t>((col0 >> 3) + g), u);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                coef[8 * g + i] = rs * (cf[i] + (1.0f - cf[i]) * u[i] - delta);
-                dmdci[8 * g + i] = rs * (1.0f - u[i]);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                coef[8 * g + i] = rs * (cf[i] - delta);
-                dmdci[8 * g + i] = rs;
-              }
-            }
+          for (int g = 0; g < 8; ++g) {
+            if (row_ok && col0 + 8 * g < args.N)
+              ciq[g] = __ldg(reinterpret_cast<const uint4*>(ci_row + 8 * g));
+            else
+              ciq[g] = make_uint4(0u, 0u, 0u, 0u);
           }
-          if constexpr (EPI == EPI_MASK_FWD) {
-            if (NOUT == 2 && args.has_out1) stage_bf16_half(box1, lane, half, v);
+        }
+        if (!have_acc) {
+          if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+            if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          have_acc = true;
+        }
+        uint32_t r[2][32];
+        tmem_ld_32x32(tmem_row + j * box_cols, r[0]);
+        if (!out32) tmem_ld_32x32(tmem_row + j * box_cols + 32, r[1]);
+        tmem_ld_wait();
+        // The staging boxes were handed to TMA one box ago: make sure they have been read.
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= coef[i];
-            stage_bf16_half(box0, lane, half, v);
+        for (int half = 0; half < 2; ++half) {
+          if (half == 1 && out32) break;
+          const int c0 = col0 + 32 * half;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[half][i]);
+          if constexpr (EPI == EPI_PLAIN) {
+            if (!plain_fast) {
+              const float* bias = args.bias ? args.bias + b * args.bias_bs : nullptr;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float x = v[i] * args.alpha;
+                if (bias && c0 + i < args.N) x += bias[c0 + i];
+                v[i] = x;
+              }
+              if (args.act == ACT_GELU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], ACT_GELU);
+              } else if (args.act == ACT_SILU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], ACT_SILU);
+              } else if (args.act == ACT_RELU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+              }
+            }
+            if (out32)
+              stage_fp32(box0, lane, v);
+            else
+              stage_bf16_half(box0, lane, half, v);
           } else {
-            // backward: v = dA. dci gets dA * H * dm/dci; out0 = dA * coef.
-            if (args.dci != nullptr && row_ok) {
-              const __nv_bfloat16* h_row = args.H + static_cast<long long>(row) * args.ld_h + col0;
-              float* d_row = args.dci + static_cast<long long>(row) * args.ld_dci + col0;
+            float coef[32], dmdci[32];
 #pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                if (col0 + 8 * g < args.N) {
-                  float hf[8];
-                  unpack8(*reinterpret_cast<const uint4*>(h_row + 8 * g), hf);
-                  float4 o0, o1;
-                  float* dst = d_row + 8 * g;
-                  if (args.dci_accumulate) {
-                    o0 = *reinterpret_cast<float4*>(dst);
-                    o1 = *reinterpret_cast<float4*>(dst + 4);
-                  } else {
-                    o0 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    o1 = o0;
-                  }
-                  o0.x += v[8 * g + 0] * hf[0] * dmdci[8 * g + 0];
-                  o0.y += v[8 * g + 1] * hf[1] * dmdci[8 * g + 1];
-                  o0.z += v[8 * g + 2] * hf[2] * dmdci[8 * g + 2];
-                  o0.w += v[8 * g + 3] * hf[3] * dmdci[8 * g + 3];
-                  o1.x += v[8 * g + 4] * hf[4] * dmdci[8 * g + 4];
-                  o1.y += v[8 * g + 5] * hf[5] * dmdci[8 * g + 5];
-                  o1.z += v[8 * g + 6] * hf[6] * dmdci[8 * g + 6];
-                  o1.w += v[8 * g + 7] * hf[7] * dmdci[8 * g + 7];
-                  *reinterpret_cast<float4*>(dst) = o0;
-                  *reinterpret_cast<float4*>(dst + 4) = o1;
+            for (int g = 0; g < 4; ++g) {
+              float cf[8];
+              unpack8(ciq[4 * half + g], cf);
+              if (args.mask_mode == 0) {
+                float u[8];
+                philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(row) + args.row_offset,
+                                static_cast<uint32_t>((c0 >> 3) + g), u);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float om = 1.0f - u[i];
+                  coef[8 * g + i] = rs * (fmaf(cf[i], om, u[i]) - delta);  // ci + (1-ci) u - d
+                  dmdci[8 * g + i] = rs * om;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  coef[8 * g + i] = rs * (cf[i] - delta);
+                  dmdci[8 * g + i] = rs;
                 }
               }
             }
+            if constexpr (EPI == EPI_MASK_FWD) {
+              if (NOUT == 2 && args.has_out1) stage_bf16_half(box1, lane, half, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= coef[i];
-            stage_bf16_half(box0, lane, half, v);
+              for (int i = 0; i < 32; ++i) v[i] *= coef[i];
+              stage_bf16_half(box0, lane, half, v);
+            } else {
+              if (args.dci != nullptr && row_ok) {
+                const __nv_bfloat16* h_row = args.H + static_cast<long long>(row) * args.ld_h + c0;
+                float* d_row = args.dci + static_cast<long long>(row) * args.ld_dci + c0;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  if (c0 + 8 * g < args.N) {
+                    float hf[8];
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(h_row + 8 * g)), hf);
+                    float4 o0, o1;
+                    float* dst = d_row + 8 * g;
+                    if (args.dci_accumulate) {
+                      o0 = *reinterpret_cast<float4*>(dst);
+                      o1 = *reinterpret_cast<float4*>(dst + 4);
+                    } else {
+                      o0 = make_float4(0.f, 0.f, 0.f, 0.f);
+                      o1 = o0;
+                    }
+                    o0.x += v[8 * g + 0] * hf[0] * dmdci[8 * g + 0];
+                    o0.y += v[8 * g + 1] * hf[1] * dmdci[8 * g + 1];
+                    o0.z += v[8 * g + 2] * hf[2] * dmdci[8 * g + 2];
+                    o0.w += v[8 * g + 3] * hf[3] * dmdci[8 * g + 3];
+                    o1.x += v[8 * g + 4] * hf[4] * dmdci[8 * g + 4];
+                    o1.y += v[8 * g + 5] * hf[5] * dmdci[8 * g + 5];
+                    o1.z += v[8 * g + 6] * hf[6] * dmdci[8 * g + 6];
+                    o1.w += v[8 * g + 7] * hf[7] * dmdci[8 * g + 7];
+                    *reinterpret_cast<float4*>(dst) = o0;
+                    *reinterpret_cast<float4*>(dst + 4) = o1;
+                  }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= coef[i];
+              stage_bf16_half(box0, lane, half, v);
+            }
           }
         }
 
-        const bool box_done = box64 ? (half == 1 || col0 + 32 >= args.N) : true;
-        if (box_done) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int ccol = box64 ? (col0 - half * 32) : col0;
-            const int crow = mb * BM + q * 32;
-            if (crow < args.M) {
-              if (args.accumulate)
-                tma_reduce_add_3d(&tmOut0, box0, ccol, crow, b);
-              else
-                tma_store_3d(&tmOut0, box0, ccol, crow, b);
-              if constexpr (EPI == EPI_MASK_FWD && NOUT == 2) {
-                if (args.has_out1) tma_store_3d(&tmOut1, box1, ccol, crow, b);
-              }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int crow = mb * BM + q * 32;
+          if (crow < args.M) {
+            if (args.accumulate)
+              tma_reduce_add_3d(&tmOut0, box0, col0, crow, b);
+            else
+              tma_store_3d(&tmOut0, box0, col0, crow, b);
+            if constexpr (EPI == EPI_MASK_FWD && NOUT == 2) {
+              if (args.has_out1) tma_store_3d(&tmOut1, box1, col0, crow, b);
             }
-            tma_store_commit();
           }
-          buf ^= 1;
+          tma_store_commit();
         }
       }
-      // Accumulator drained: hand it back to the MMA warp.
+      if (failed) break;
+      if (!have_acc) {  // no box of this tile fell to this warp: still consume the phase
+        if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+          if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+          break;
+        }
+      }
+      // Accumulator drained by this warp: hand it back to the MMA warp.
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
@@ -569,7 +611,7 @@ struct PdGemmCall {
   const void* H; long long ld_h;
   const float* delta; const float* rowscale;
   float* dci; long long ld_dci; int dci_accumulate;
-  unsigned long long seed; unsigned int rng_stream; int mask_mode;
+  unsigned long long seed; unsigned int rng_stream; unsigned int rng_row_offset; int mask_mode;
   // control
   int split_k; int bn; int max_ctas;
   int* status;
@@ -599,7 +641,7 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.H = static_cast<const __nv_bfloat16*>(c->H); a.ld_h = c->ld_h;
   a.delta = c->delta; a.rowscale = c->rowscale;
   a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate;
-  a.seed = c->seed; a.stream = c->rng_stream; a.mask_mode = c->mask_mode;
+  a.seed = c->seed; a.stream = c->rng_stream; a.row_offset = c->rng_row_offset; a.mask_mode = c->mask_mode;
   a.status = c->status;
   if (c->epi != EPI_PLAIN) {
     if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15))

@@ -1,0 +1,133 @@
+"""Bindings + autograd wrappers of the bandwidth-bound kernels (`csrc/elementwise.cu`)."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import Tensor
+
+from param_decomp_b200.ops import native as nv
+
+_configured = False
+
+
+def _lib():
+    global _configured
+    lib = nv.lib()
+    if not _configured:
+        P, LL, I, F = C.c_void_p, C.c_longlong, C.c_int, C.c_float
+        lib.pd_sumsq.argtypes = [P, LL, P, P]
+        lib.pd_clip_scale.argtypes = [P, F, P, P, P]
+        lib.pd_adamw.argtypes = [P, P, P, P, LL, F, F, F, F, F, F, F, P, P]
+        lib.pd_cast_bf16.argtypes = [P, P, LL, P]
+        lib.pd_rmsnorm_fwd.argtypes = [P, P, P, P, LL, I, F, P]
+        lib.pd_rmsnorm_bwd.argtypes = [P, P, P, P, P, LL, I, P]
+        lib.pd_rope.argtypes = [P, P, P, LL, I, I, I, I, P]
+        lib.pd_swiglu_fwd.argtypes = [P, P, P, LL, P]
+        lib.pd_swiglu_bwd.argtypes = [P, P, P, P, P, LL, P]
+        lib.pd_rowscale.argtypes = [P, P, P, LL, I, P]
+        lib.pd_ci_squash.argtypes = [P, P, P, LL, F, P]
+        _configured = True
+    return lib
+
+
+def _check(rc: int, what: str) -> None:
+    nv.count_launch()
+    if rc != 0:
+        raise nv.NativeError(f"{what} failed to launch (code {rc})")
+
+
+def _s() -> int:
+    return nv.current_stream_ptr()
+
+
+def cast_bf16(src: Tensor, out: Tensor | None = None) -> Tensor:
+    assert src.dtype == torch.float32 and src.is_contiguous()
+    out = out if out is not None else torch.empty_like(src, dtype=torch.bfloat16)
+    _check(_lib().pd_cast_bf16(src.data_ptr(), out.data_ptr(), src.numel(), _s()), "cast_bf16")
+    return out
+
+
+def rowscale(x: Tensor, s: Tensor) -> Tensor:
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and s.dtype == torch.float32
+    y = torch.empty_like(x)
+    _check(_lib().pd_rowscale(x.data_ptr(), s.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], _s()), "rowscale")
+    return y
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, w: Tensor | None, eps: float) -> Tensor:  # type: ignore[override]
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        rows, d = x2.shape
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        _check(_lib().pd_rmsnorm_fwd(x2.data_ptr(), w.data_ptr() if w is not None else None, y.data_ptr(),
+                                     rstd.data_ptr(), rows, d, eps, _s()), "rmsnorm_fwd")
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x2, w, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(x2.shape)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dx = torch.empty_like(x2)
+        _check(_lib().pd_rmsnorm_bwd(x2.data_ptr(), w.data_ptr() if w is not None else None, dy2.data_ptr(),
+                                     rstd.data_ptr(), dx.data_ptr(), x2.shape[0], x2.shape[1], _s()), "rmsnorm_bwd")
+        return dx.view(ctx.shape), None, None
+
+
+def rms_norm(x: Tensor, w: Tensor | None, eps: float) -> Tensor:
+    return _RMSNorm.apply(x, w, eps)
+
+
+class _Rope(torch.autograd.Function):
+    """Rotary embedding on `[B, T, H, hd]` (full head_dim). Out of place; backward = inverse rotation."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, cos_half: Tensor, sin_half: Tensor) -> Tensor:  # type: ignore[override]
+        B, T, H, hd = x.shape
+        y = x.contiguous().clone()
+        _check(_lib().pd_rope(y.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr(), B * T, T, H, hd, 0, _s()), "rope")
+        ctx.save_for_backward(cos_half, sin_half)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        cos_half, sin_half = ctx.saved_tensors
+        B, T, H, hd = dy.shape
+        dx = dy.contiguous().clone()
+        _check(_lib().pd_rope(dx.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr(), B * T, T, H, hd, 1, _s()), "rope_bwd")
+        return dx, None, None
+
+
+def rope(x: Tensor, cos_half: Tensor, sin_half: Tensor) -> Tensor:
+    """`cos_half/sin_half [T, hd/2]` fp32 contiguous (positions shared by every batch row)."""
+    return _Rope.apply(x, cos_half, sin_half)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate: Tensor, up: Tensor) -> Tensor:  # type: ignore[override]
+        gate, up = gate.contiguous(), up.contiguous()
+        out = torch.empty_like(gate)
+        _check(_lib().pd_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _s()), "swiglu_fwd")
+        ctx.save_for_backward(gate, up)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout: Tensor):  # type: ignore[override]
+        gate, up = ctx.saved_tensors
+        dout = dout.contiguous()
+        dg, du = torch.empty_like(gate), torch.empty_like(up)
+        _check(_lib().pd_swiglu_bwd(gate.data_ptr(), up.data_ptr(), dout.data_ptr(), dg.data_ptr(), du.data_ptr(),
+                                    gate.numel(), _s()), "swiglu_bwd")
+        return dg, du
+
+
+def swiglu(gate: Tensor, up: Tensor) -> Tensor:
+    return _SwiGLU.apply(gate, up)

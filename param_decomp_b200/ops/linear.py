@@ -1,0 +1,90 @@
+"""Autograd wrappers that put the target's linears and the decomposed sites on the tcgen05 engine."""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from param_decomp_b200.core.components import ComputeWeights
+from param_decomp_b200.core.masking import SiteMask
+from param_decomp_b200.ops import native as nv
+from param_decomp_b200.ops.site_linear import SiteWeights, fused_site_forward
+
+
+class _FrozenLinear(torch.autograd.Function):
+    """`y = x W^T` with a frozen `W [d_out, d_in]`: the backward is `dx = dy W` (W read MN-major)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, W: Tensor) -> Tensor:  # type: ignore[override]
+        y = torch.empty(x.shape[0], W.shape[0], device=x.device, dtype=torch.bfloat16)
+        nv.gemm(x, W, y)
+        ctx.save_for_backward(W)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        (W,) = ctx.saved_tensors
+        dx = torch.empty(dy.shape[0], W.shape[1], device=dy.device, dtype=torch.bfloat16)
+        nv.gemm(dy.contiguous(), W, dx, b_mn=True)
+        return dx, None
+
+
+def linear(x: Tensor, W: Tensor) -> Tensor:
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if x2.requires_grad:
+        y = _FrozenLinear.apply(x2, W)
+    else:
+        y = torch.empty(x2.shape[0], W.shape[0], device=x.device, dtype=torch.bfloat16)
+        nv.gemm(x2, W, y)
+    return y.reshape(*lead, -1)
+
+
+def site(x: Tensor, weights: ComputeWeights, name: str, W: Tensor, sm: SiteMask) -> Tensor:
+    V, U = weights.site(name)
+    sw = SiteWeights(V, U, W, weights.grad_V.get(name), weights.grad_U.get(name))
+    return fused_site_forward(x, sw, sm, need_weight_grads=weights.direct_grads)
+
+
+class _BmmBias(torch.autograd.Function):
+    """`y[g] = x[g] W[g] + b[g]` for a stack of `g` independent linears with TRAINABLE fp32 masters.
+
+    bf16 operands on the batched tcgen05 kernel, fp32 weight/bias gradients. `x [g, N, K]` bf16,
+    `W [g, K, M]` fp32, `b [g, 1, M]` fp32 -> `[g, N, M]` bf16.
+    """
+
+    @staticmethod
+    def forward(ctx, x: Tensor, W: Tensor, b: Tensor) -> Tensor:  # type: ignore[override]
+        from param_decomp_b200.ops.elementwise import cast_bf16
+
+        Wb = cast_bf16(W.detach().contiguous())
+        g, N, K = x.shape
+        M = W.shape[-1]
+        x = x.contiguous()
+        y = torch.empty(g, N, M, device=x.device, dtype=torch.bfloat16)
+        nv.gemm(x, Wb, y, b_mn=True, bias=b.detach().reshape(g, M).contiguous())
+        ctx.save_for_backward(x, Wb)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x, Wb = ctx.saved_tensors
+        dy = dy.contiguous()
+        g, N, K = x.shape
+        M = Wb.shape[-1]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            nv.gemm(dy, Wb, dx)  # Wb [g, K, M] read as the K-major B operand of dx = dy W^T
+        dW = torch.zeros(g, K, M, device=x.device, dtype=torch.float32)
+        tiles = ((K + 127) // 128) * ((M + 255) // 256) * g
+        split = max(1, min(148 // max(tiles, 1), N // 512))
+        nv.gemm(x, dy, dW, a_mn=True, b_mn=True, accumulate=True, split_k=split)
+        db = dy.float().sum(1, keepdim=True)
+        return dx, dW, db
+
+
+def bmm_bias(x: Tensor, W: Tensor, b: Tensor) -> Tensor:
+    return _BmmBias.apply(x, W, b)

@@ -40,7 +40,7 @@ class PdGemmCall(C.Structure):
         ("H", C.c_void_p), ("ld_h", C.c_longlong),
         ("delta", C.c_void_p), ("rowscale", C.c_void_p),
         ("dci", C.c_void_p), ("ld_dci", C.c_longlong), ("dci_accumulate", C.c_int),
-        ("seed", C.c_ulonglong), ("rng_stream", C.c_uint), ("mask_mode", C.c_int),
+        ("seed", C.c_ulonglong), ("rng_stream", C.c_uint), ("rng_row_offset", C.c_uint), ("mask_mode", C.c_int),
         ("split_k", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int),
         ("status", C.c_void_p),
     ]  # fmt: skip
@@ -59,6 +59,29 @@ def lib() -> C.CDLL:
     if handle.pd_gemm_call_size() != C.sizeof(PdGemmCall):
         raise NativeError("PdGemmCall layout differs between native.py and gemm_sm100.cu")
     return handle
+
+
+_LAUNCHES = 0
+
+
+def count_launch(n: int = 1) -> None:
+    """Every launch of one of this library's kernels is counted (reported by the benchmark)."""
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def has_symbol(name: str) -> bool:
+    if not LIB_PATH.exists():
+        return False
+    try:
+        getattr(lib(), name)
+        return True
+    except AttributeError:
+        return False
 
 
 def available() -> bool:
@@ -121,6 +144,7 @@ def gemm(
     dci_accumulate: bool = False,
     seed: int = 0,
     rng_stream: int = 0,
+    row_offset: int = 0,
     mask_mode: int = 0,
     max_ctas: int = 0,
 ) -> torch.Tensor:
@@ -179,9 +203,11 @@ def gemm(
         call.dci, call.ld_dci = dci.data_ptr(), dci.stride(-2)
     call.dci_accumulate = int(dci_accumulate)
     call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
+    call.rng_row_offset = row_offset & 0xFFFFFFFF
     call.split_k, call.bn, call.max_ctas = split_k, bn, max_ctas
     call.status = status_word().data_ptr()
     rc = lib().pd_gemm(C.byref(call), current_stream_ptr())
+    count_launch()
     if rc != 0:
         raise NativeError(f"pd_gemm refused the call (code {rc})")
     return out

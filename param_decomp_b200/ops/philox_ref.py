@@ -1,4 +1,4 @@
-"""Pure-torch restatement of the device Philox4x32-10 stream (`csrc/common.cuh`).
+"""Pure-torch restatement of the device Philox4x32-7 stream (`csrc/common.cuh`).
 
 Used by tests and by the eager fallback of the mask sampler so that a mask element is the same
 function of `(seed, stream, row, column)` on CPU and in the fused GEMM epilogues.
@@ -11,6 +11,7 @@ import torch
 _M0, _M1 = 0xD2511F53, 0xCD9E8D57
 _W0, _W1 = 0x9E3779B9, 0xBB67AE85
 _MASK = 0xFFFFFFFF
+ROUNDS = 7
 
 
 def _mulhilo(a: int, b: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -25,8 +26,8 @@ def _mulhilo(a: int, b: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 
 def philox4x32(c0, c1, c2, c3, k0: int, k1: int):
-    """Ten rounds on int64 tensors holding uint32 values. Returns four such tensors."""
-    for _ in range(10):
+    """`ROUNDS` rounds on int64 tensors holding uint32 values. Returns four such tensors."""
+    for _ in range(ROUNDS):
         hi0, lo0 = _mulhilo(_M0, c0)
         hi1, lo1 = _mulhilo(_M1, c2)
         c0, c1, c2, c3 = (hi1 ^ c1 ^ k0) & _MASK, lo1, (hi0 ^ c3 ^ k1) & _MASK, lo0

@@ -1,0 +1,151 @@
+"""Fused decomposed-linear site on the tcgen05 GEMM engine (forward and backward).
+
+Contract (identical to `core.decomposed_linear.site_forward`):
+    y = ((x V) * coef) U + d_eff * (x W^T),   coef = r * (m - d),   d_eff = r * d + (1 - r)
+with `r` the routing indicator (1 = routed), `d` the delta mask, `m` the component mask which is
+either drawn in the kernel epilogue from Philox counters (`StochasticSpec`) or supplied.
+
+Launches per forward:  (1) H = x V with the mask epilogue -> A = H * coef (and H if a backward
+will need it)   (2) y = A U + (d_eff * x) W^T as ONE GEMM with two K-phases sharing the accumulator.
+Backward:  (3) dA = dy U^T with the backward mask epilogue -> dH = dA * coef, dci / dm
+(4) dx = dH V^T + (d_eff * dy) W   (two K-phases)   (5) dV += x^T dH   (6) dU += A^T dy, both
+accumulated in fp32 straight into the master gradient buffers with TMA reduce-add (split-K).
+No operand is ever transposed in memory: the kernel reads MN-major tiles directly.
+
+Weight gradients bypass autograd: `grad_V` / `grad_U` are fp32 views into the stacked masters'
+`.grad`, so several uses of a site in one step (draws, terms) accumulate in place.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from param_decomp_b200.core.masking import SiteMask
+from param_decomp_b200.ops import native as nv
+
+
+@dataclass
+class SiteWeights:
+    """bf16 operands of one site plus (optional) fp32 gradient sinks."""
+
+    V: Tensor  # [d_in, C] bf16
+    U: Tensor  # [C, d_out] bf16
+    W: Tensor | None  # [d_out, d_in] bf16 frozen
+    grad_V: Tensor | None = None  # [d_in, C] fp32, accumulated into
+    grad_U: Tensor | None = None  # [C, d_out] fp32
+
+
+def _split_k_for(M: int, N: int, K: int, sms: int = 148) -> int:
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    if tiles >= sms:
+        return 1
+    return max(1, min(sms // tiles, K // 512))
+
+
+class _FusedSite(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, ci_or_mask: Tensor | None, delta: Tensor | None, w: SiteWeights,
+                rowscale: Tensor | None, d_eff: Tensor | None, seed: int, stream: int, mask_mode: int,
+                row_offset: int, need_weight_grads: bool) -> Tensor:  # type: ignore[override]
+        N = x.shape[0]
+        C, d_out = w.U.shape
+        A = torch.empty(N, C, device=x.device, dtype=torch.bfloat16)
+        need_bwd = x.requires_grad or (ci_or_mask is not None and ci_or_mask.requires_grad) or need_weight_grads
+        need_H = need_bwd and ((ci_or_mask is not None and ci_or_mask.requires_grad)
+                               or (delta is not None and delta.requires_grad))
+        H = torch.empty_like(A) if need_H else None
+        if ci_or_mask is None:
+            # all-ones mask: coef = rowscale * (1 - delta); reuse the materialised-mask mode on a
+            # broadcast row of ones (stride 0 rows are fine for the epilogue's plain loads)
+            ones = torch.ones(1, C, device=x.device, dtype=torch.bfloat16).expand(N, C)
+            ci_arg, mode = ones, 1
+        else:
+            ci_arg, mode = ci_or_mask, mask_mode
+        nv.gemm(x, w.V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci_arg, delta=delta, rowscale=rowscale,
+                seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset)
+        y = torch.empty(N, d_out, device=x.device, dtype=torch.bfloat16)
+        if d_eff is not None:
+            xd = x * d_eff.to(torch.bfloat16)[:, None]
+            nv.gemm(A, w.U, y, b_mn=True, a1=xd, b1=w.W)
+        else:
+            nv.gemm(A, w.U, y, b_mn=True)
+        ctx.save_for_backward(x, ci_or_mask, delta, rowscale, d_eff, A, H)
+        ctx.w = w
+        ctx.rng = (seed, stream, mode, row_offset)
+        ctx.need_weight_grads = need_weight_grads
+        ctx.ci_arg_is_ones = ci_or_mask is None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x, ci_or_mask, delta, rowscale, d_eff, A, H = ctx.saved_tensors
+        w: SiteWeights = ctx.w
+        seed, stream, mode, row_offset = ctx.rng
+        N, d_in = x.shape
+        C, d_out = w.U.shape
+        dy = dy.contiguous()
+        need_dci = H is not None
+        dH = torch.empty(N, C, device=x.device, dtype=torch.bfloat16)
+        dci = torch.empty(N, C, device=x.device, dtype=torch.float32) if need_dci else None
+        if ctx.ci_arg_is_ones:
+            ci_arg = torch.ones(1, C, device=x.device, dtype=torch.bfloat16).expand(N, C)
+        else:
+            ci_arg = ci_or_mask
+        nv.gemm(dy, w.U, dH, epi=nv.EPI_MASK_BWD, ci=ci_arg, h=H, delta=delta, rowscale=rowscale, dci=dci,
+                seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(N, d_in, device=x.device, dtype=torch.bfloat16)
+            if d_eff is not None:
+                dyd = dy * d_eff.to(torch.bfloat16)[:, None]
+                nv.gemm(dH, w.V, dx, a1=dyd, b1=w.W, b1_mn=True)
+            else:
+                nv.gemm(dH, w.V, dx)
+        if ctx.need_weight_grads:
+            assert w.grad_V is not None and w.grad_U is not None
+            nv.gemm(x, dH, w.grad_V, a_mn=True, b_mn=True, accumulate=True, split_k=_split_k_for(d_in, C, N))
+            nv.gemm(A, dy, w.grad_U, a_mn=True, b_mn=True, accumulate=True, split_k=_split_k_for(C, d_out, N))
+        d_delta = None
+        if delta is not None and ctx.needs_input_grad[2]:
+            # d/d(delta) = -sum_c dA*H*r + r * <dy, x W^T>; only adversarial delta sources need it
+            xw = torch.empty(N, d_out, device=x.device, dtype=torch.bfloat16)
+            nv.gemm(x, w.W, xw)
+            r = rowscale if rowscale is not None else 1.0
+            d_delta = (dy.float() * xw.float()).sum(-1) * r
+            if dci is not None:
+                d_delta = d_delta - dci.sum(-1)  # mask_mode 1: dci holds dA*H*r
+        dci_out = dci.to(ci_or_mask.dtype) if (dci is not None and ctx.needs_input_grad[1]) else None
+        return dx, dci_out, d_delta, None, None, None, None, None, None, None, None
+
+
+def fused_site_forward(x: Tensor, w: SiteWeights, sm: SiteMask, need_weight_grads: bool) -> Tensor:
+    """`x [..., d_in]` bf16 -> `[..., d_out]` bf16. Stochastic specs stay lazy (drawn in-kernel)."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    N = x2.shape[0]
+    delta = None if sm.delta is None else sm.delta.reshape(N).float()
+    rowscale = d_eff = None
+    if sm.route is not None:
+        rowscale = sm.route.reshape(N).float()
+        d_eff = (rowscale * delta + (1 - rowscale)) if delta is not None else (1 - rowscale)
+    elif delta is not None:
+        d_eff = delta
+    if sm.stochastic is not None:
+        assert sm.ci is not None
+        mask_t, mode = sm.ci.reshape(N, -1), 0
+        seed, stream, row_offset = sm.stochastic.seed64, sm.stochastic.stream, sm.stochastic.row_offset
+    else:
+        mask_t = None if sm.mask is None else sm.mask.reshape(N, -1)
+        mode, seed, stream, row_offset = 1, 0, 0, 0
+    if mask_t is not None:
+        if mask_t.dtype != torch.bfloat16:
+            mask_t = mask_t.to(torch.bfloat16)
+        if not mask_t.is_contiguous():
+            mask_t = mask_t.contiguous()
+    y = _FusedSite.apply(x2, mask_t, delta, w, rowscale, d_eff, seed, stream, mode, row_offset, need_weight_grads)
+    return y.reshape(*lead, -1)
