@@ -30,6 +30,9 @@ class CI:
     preactivations: dict[str, Tensor | SelectedCI]
     lower: dict[str, Tensor | SelectedCI]
     upper: dict[str, Tensor | SelectedCI]
+    activity: dict[str, Tensor] | None = None
+    """Fused backend only: per-component mean smooth-L0 activity `[C]`, produced in the same pass
+    as `lower` (then `upper` is not materialised)."""
 
     def dense_lower(self) -> dict[str, Tensor]:
         return {k: (v.scatter_dense() if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()}
@@ -42,6 +45,16 @@ def _map(fn, v):
     if isinstance(v, SelectedCI):
         return SelectedCI(fn(v.values), v.selection, v.n_blocks)
     return fn(v)
+
+
+def squash_fused(pre: dict[str, Tensor], gamma: float, normalize_at_one: bool) -> CI:
+    """One kernel pass per site: lower importances and the minimality activity together."""
+    from param_decomp_b200.ops.elementwise import squash_activity
+
+    lower, act = {}, {}
+    for k, v in pre.items():
+        lower[k], act[k] = squash_activity(v, gamma, normalize_at_one)
+    return CI(preactivations=pre, lower=lower, upper={}, activity=act)
 
 
 def squash(pre: dict[str, Tensor | SelectedCI]) -> CI:

@@ -91,8 +91,8 @@ class LayerwiseMLPCIFn(nn.Module):
             x = torch.stack([t.reshape(-1, t.shape[-1]) for t in xs])
             mlp = self.mlps[key]
             y = mlp(x if mlp.fused else x.float())
-            for i, s in enumerate(members):
-                out[s] = y[i].reshape(*lead, -1)
+            for s, yi in zip(members, y.unbind(0)):  # one stacked gradient per group in backward
+                out[s] = yi.reshape(*lead, -1)
         return out
 
     def parameter_census(self) -> dict[str, int]:

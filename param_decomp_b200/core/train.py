@@ -221,8 +221,11 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
     metrics["schedules/gamma"] = torch.tensor(gamma)
     activity = None
     freq_total = None
-    for name, up in ci.upper.items():
-        f_local = loss_fns.component_activity(up, gamma, cfg.normalize_at_one)
+    for name in ci.lower:
+        if ci.activity is not None:
+            f_local = ci.activity[name]
+        else:
+            f_local = loss_fns.component_activity(ci.upper[name], gamma, cfg.normalize_at_one)
         f = ctx.collectives.mean(f_local)  # global-batch mean BEFORE the log
         act = f.sum()
         activity = act if activity is None else activity + act
@@ -265,8 +268,16 @@ def _detach_ci(ci_lower: dict[str, Tensor]) -> dict[str, Tensor]:
     return {k: v.detach() for k, v in ci_lower.items()}
 
 
-def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult) -> CI:
+def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: int | None = None) -> CI:
     pre = state.ci_fn(clean.taps, aux=clean.aux, components=state.components)
+    cfg = ctx.objective.minimality
+    fusable = (step is not None and ctx.lazy_masks and isinstance(cfg, L.ImportanceMinimalityLossConfig)
+               and all(isinstance(v, torch.Tensor) and v.is_cuda and v.dtype == torch.bfloat16
+                       and v.shape[-1] % 8 == 0 for v in pre.values()))
+    if fusable:
+        from param_decomp_b200.core.ci_fn.interface import squash_fused
+
+        return squash_fused(pre, get_scheduled_value(step, ctx.pd.steps, cfg.gamma), cfg.normalize_at_one)
     return squash(pre)
 
 
@@ -312,7 +323,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         else:
             p.grad = None
     weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct)
-    ci = run_ci_fn(ctx, state, clean)
+    ci = run_ci_fn(ctx, state, clean, step)
     ci_lower = ci.dense_lower()
 
     for term in obj.persistent_terms():

@@ -299,6 +299,11 @@ class TransformerDecomposedModel:
 
     # -- output edge: KL(clean || masked) over the vocabulary ---------------------------------------
     def _clean_logit_stats(self, hidden: Tensor) -> dict[str, Tensor]:
+        """Fused backend: the clean logits are formed once per step and reused by every draw."""
+        if self.backend == "fused_sm100" and hidden.is_cuda:
+            from param_decomp_b200.ops import vocab_kl
+
+            return {"logits": vocab_kl.padded_logits(hidden.reshape(-1, hidden.shape[-1]), self.head_weight())}
         return {}
 
     def recon_loss(self, clean: ForwardResult, masked: ForwardResult) -> Tensor:
@@ -310,7 +315,7 @@ class TransformerDecomposedModel:
         if self.backend == "fused_sm100" and hm.is_cuda:
             from param_decomp_b200.ops import vocab_kl
 
-            return vocab_kl.kl_from_hidden(hc, hm, self.head_weight(), self.kl_token_chunk)
+            return vocab_kl.kl_from_hidden(clean.aux["clean_stats"]["logits"], hm, self.head_weight())
         return chunked_kl_from_hidden(hc, hm, self.head_weight(), self.kl_token_chunk)
 
     def ce_loss(self, out: ForwardResult, tokens: Tensor) -> Tensor:

@@ -312,6 +312,169 @@ __global__ void ci_squash_kernel(const __nv_bfloat16* __restrict__ pre,
   }
 }
 
+
+// ---- fused CI squash + smooth-L0 activity ------------------------------------------------------
+// One pass over the pre-activations [rows, C] (bf16):
+//   lower = clamp(pre, 0, 1)                                   (bf16, feeds the masks)
+//   colsum[c] += sum_rows psi(upper(pre)),  psi(u) = u^2 / (u^2 + gamma^2) (* (1 + gamma^2))
+// Block = 32 column groups of 8 columns x 8 row lanes; grid = (C / 256, row chunks).
+__global__ void ci_squash_activity_kernel(const __nv_bfloat16* __restrict__ pre,
+                                          __nv_bfloat16* __restrict__ lower,
+                                          float* __restrict__ colsum, long long rows, int C,
+                                          float gamma2, float norm, float alpha) {
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + cg) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < C) {
+    for (long long r = static_cast<long long>(blockIdx.y) * 8 + rl; r < rows;
+         r += static_cast<long long>(gridDim.y) * 8) {
+      const uint4 q = *reinterpret_cast<const uint4*>(pre + r * C + col);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+      __nv_bfloat162 lo[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        const float lx = fminf(fmaxf(f.x, 0.f), 1.f), ly = fminf(fmaxf(f.y, 0.f), 1.f);
+        lo[k] = __floats2bfloat162_rn(lx, ly);
+        const float ux = f.x > 1.f ? 1.f + alpha * (f.x - 1.f) : lx;
+        const float uy = f.y > 1.f ? 1.f + alpha * (f.y - 1.f) : ly;
+        acc[2 * k] += norm * ux * ux / (ux * ux + gamma2);
+        acc[2 * k + 1] += norm * uy * uy / (uy * uy + gamma2);
+      }
+      *reinterpret_cast<uint4*>(lower + r * C + col) = *reinterpret_cast<uint4*>(lo);
+    }
+  }
+  __shared__ float red[8][32][8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[rl][cg][k] = acc[k];
+  __syncthreads();
+  if (rl == 0 && col < C) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float v = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v += red[j][cg][k];
+      atomicAdd(colsum + col + k, v);
+    }
+  }
+}
+
+// dpre = lower'(pre; dlower) + dcol[c] * psi'(upper) * upper'(pre)
+//   lower': pre in (0,1] -> g;  pre <= 0 -> (g < 0 ? alpha g : 0);  pre > 1 -> 0
+__global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ pre,
+                                              const __nv_bfloat16* __restrict__ dlower,
+                                              const float* __restrict__ dcol,
+                                              __nv_bfloat16* __restrict__ dpre, long long rows, int C,
+                                              float gamma2, float norm, float alpha) {
+  const long long total = rows * (C / 8);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int col = static_cast<int>(i % (C / 8)) * 8;
+    const uint4 q = *reinterpret_cast<const uint4*>(pre + i * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    uint4 gq = make_uint4(0, 0, 0, 0);
+    if (dlower) gq = *reinterpret_cast<const uint4*>(dlower + i * 8);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
+    const float4 d0 = *reinterpret_cast<const float4*>(dcol + col);
+    const float4 d1 = *reinterpret_cast<const float4*>(dcol + col + 4);
+    const float dc[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]), g = __bfloat1622float2(gh[k]);
+      float out[2];
+      const float x[2] = {f.x, f.y}, gg[2] = {g.x, g.y};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float xv = x[e];
+        float lg = 0.f, u, du;
+        if (xv > 1.f) { u = 1.f + alpha * (xv - 1.f); du = alpha; }
+        else if (xv > 0.f) { u = xv; du = 1.f; lg = gg[e]; }
+        else { u = 0.f; du = 0.f; lg = gg[e] < 0.f ? alpha * gg[e] : 0.f; }
+        const float den = u * u + gamma2;
+        const float dpsi = norm * 2.f * u * gamma2 / (den * den);
+        out[e] = lg + dc[2 * k + e] * dpsi * du;
+      }
+      o[k] = __floats2bfloat162_rn(out[0], out[1]);
+    }
+    *reinterpret_cast<uint4*>(dpre + i * 8) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// ---- vocabulary KL: one block per position ------------------------------------------------------
+// kl[row] = KL(softmax(lc[row]) || softmax(lm[row]));  dlm[row] = softmax(lm) - softmax(lc)
+// (the caller scales by the upstream gradient / number of positions inside the next GEMM).
+// Rows are `ld` elements apart (padded to a multiple of 8); V valid columns.
+__global__ void vocab_kl_kernel(const __nv_bfloat16* __restrict__ lc, const __nv_bfloat16* __restrict__ lm,
+                                __nv_bfloat16* __restrict__ dlm, float* __restrict__ kl, int V, long long ld) {
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* a = lc + row * ld;
+  const __nv_bfloat16* b = lm + row * ld;
+  __shared__ float red[4][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  // pass 1: row maxima
+  float ma = -INFINITY, mb = -INFINITY;
+  for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(a + i), qb = *reinterpret_cast<const uint4*>(b + i);
+    const __nv_bfloat16* ha = reinterpret_cast<const __nv_bfloat16*>(&qa);
+    const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&qb);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (i + k < V) { ma = fmaxf(ma, __bfloat162float(ha[k])); mb = fmaxf(mb, __bfloat162float(hb[k])); }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
+    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+  }
+  if (lane == 0) { red[0][warp] = ma; red[1][warp] = mb; }
+  __syncthreads();
+  ma = red[0][0]; mb = red[1][0];
+  for (int w = 1; w < nw; ++w) { ma = fmaxf(ma, red[0][w]); mb = fmaxf(mb, red[1][w]); }
+  __syncthreads();
+  // pass 2: partition functions and the cross term sum exp(a - ma) * (a - b)
+  float sa = 0.f, sb = 0.f, cross = 0.f;
+  for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(a + i), qb = *reinterpret_cast<const uint4*>(b + i);
+    const __nv_bfloat16* ha = reinterpret_cast<const __nv_bfloat16*>(&qa);
+    const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&qb);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (i + k < V) {
+        const float x = __bfloat162float(ha[k]), y = __bfloat162float(hb[k]);
+        const float ea = __expf(x - ma);
+        sa += ea; sb += __expf(y - mb); cross += ea * (x - y);
+      }
+    }
+  }
+  sa = warp_sum(sa); sb = warp_sum(sb); cross = warp_sum(cross);
+  if (lane == 0) { red[0][warp] = sa; red[1][warp] = sb; red[2][warp] = cross; }
+  __syncthreads();
+  sa = 0.f; sb = 0.f; cross = 0.f;
+  for (int w = 0; w < nw; ++w) { sa += red[0][w]; sb += red[1][w]; cross += red[2][w]; }
+  const float lsa = ma + __logf(sa), lsb = mb + __logf(sb);
+  // KL = sum p_a (a - lsa - b + lsb) = cross / sa - lsa + lsb
+  if (threadIdx.x == 0) kl[row] = cross / sa - lsa + lsb;
+  // pass 3: gradient wrt the masked logits
+  if (dlm != nullptr) {
+    __nv_bfloat16* d = dlm + row * ld;
+    const float ia = 1.f / sa, ib = 1.f / sb;
+    for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
+      const uint4 qa = *reinterpret_cast<const uint4*>(a + i), qb = *reinterpret_cast<const uint4*>(b + i);
+      const __nv_bfloat16* ha = reinterpret_cast<const __nv_bfloat16*>(&qa);
+      const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&qb);
+      __nv_bfloat16 o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float x = __bfloat162float(ha[k]), y = __bfloat162float(hb[k]);
+        o[k] = __float2bfloat16(i + k < V ? __expf(y - mb) * ib - __expf(x - ma) * ia : 0.f);
+      }
+      *reinterpret_cast<uint4*>(d + i) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+}
+
 }  // namespace
 
 #define PD_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : 1)
@@ -385,5 +548,38 @@ extern "C" int pd_ci_squash(const void* pre, void* lower, void* upper, long long
   ci_squash_kernel<<<blocks_for(n, kThreads * 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(lower),
       static_cast<__nv_bfloat16*>(upper), n, alpha);
+  return PD_CHECK_LAUNCH();
+}
+
+extern "C" int pd_ci_squash_activity(const void* pre, void* lower, float* colsum, long long rows, int C,
+                                     float gamma, int normalize_at_one, float alpha, void* stream) {
+  if (C % 8 != 0) return 5;
+  const int gx = (C + 255) / 256;
+  int gy = (148 * 4 + gx - 1) / gx;
+  if (gy > (rows + 7) / 8) gy = static_cast<int>((rows + 7) / 8);
+  if (gy < 1) gy = 1;
+  const float g2 = gamma * gamma;
+  ci_squash_activity_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(lower), colsum, rows, C, g2,
+      normalize_at_one ? 1.f + g2 : 1.f, alpha);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_ci_squash_activity_bwd(const void* pre, const void* dlower, const float* dcol, void* dpre,
+                                         long long rows, int C, float gamma, int normalize_at_one, float alpha,
+                                         void* stream) {
+  if (C % 8 != 0) return 5;
+  const float g2 = gamma * gamma;
+  ci_squash_activity_bwd_kernel<<<blocks_for(rows * (C / 8), kThreads), kThreads, 0,
+                                  static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(dlower), dcol,
+      static_cast<__nv_bfloat16*>(dpre), rows, C, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_vocab_kl(const void* lc, const void* lm, void* dlm, float* kl, long long rows, int V,
+                           long long ld, void* stream) {
+  if (ld % 8 != 0 || rows <= 0) return 5;
+  vocab_kl_kernel<<<static_cast<unsigned>(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(lc), static_cast<const __nv_bfloat16*>(lm),
+      static_cast<__nv_bfloat16*>(dlm), kl, V, ld);
   return PD_CHECK_LAUNCH();
 }

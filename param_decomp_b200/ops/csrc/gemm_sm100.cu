@@ -65,6 +65,7 @@ struct GemmArgs {
   float* dci;
   long long ld_dci;
   int dci_accumulate;
+  int dci_bf16;
   unsigned long long seed;
   unsigned int stream;
   unsigned int row_offset;
@@ -456,25 +457,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
                   if (c0 + 8 * g < args.N) {
                     float hf[8];
                     unpack8(__ldg(reinterpret_cast<const uint4*>(h_row + 8 * g)), hf);
-                    float4 o0, o1;
-                    float* dst = d_row + 8 * g;
-                    if (args.dci_accumulate) {
-                      o0 = *reinterpret_cast<float4*>(dst);
-                      o1 = *reinterpret_cast<float4*>(dst + 4);
+                    float t[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) t[i] = v[8 * g + i] * hf[i] * dmdci[8 * g + i];
+                    if (args.dci_bf16) {
+                      __nv_bfloat16* dstb = reinterpret_cast<__nv_bfloat16*>(args.dci) +
+                                            static_cast<long long>(row) * args.ld_dci + c0 + 8 * g;
+                      if (args.dci_accumulate) {
+                        float old8[8];
+                        unpack8(*reinterpret_cast<const uint4*>(dstb), old8);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) t[i] += old8[i];
+                      }
+                      uint4 pk;
+                      pk.x = pack_bf16(t[0], t[1]); pk.y = pack_bf16(t[2], t[3]);
+                      pk.z = pack_bf16(t[4], t[5]); pk.w = pack_bf16(t[6], t[7]);
+                      *reinterpret_cast<uint4*>(dstb) = pk;
                     } else {
-                      o0 = make_float4(0.f, 0.f, 0.f, 0.f);
-                      o1 = o0;
+                      float* dst = d_row + 8 * g;
+                      float4 o0 = make_float4(t[0], t[1], t[2], t[3]), o1 = make_float4(t[4], t[5], t[6], t[7]);
+                      if (args.dci_accumulate) {
+                        const float4 p0 = *reinterpret_cast<float4*>(dst), p1 = *reinterpret_cast<float4*>(dst + 4);
+                        o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
+                        o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+                      }
+                      *reinterpret_cast<float4*>(dst) = o0;
+                      *reinterpret_cast<float4*>(dst + 4) = o1;
                     }
-                    o0.x += v[8 * g + 0] * hf[0] * dmdci[8 * g + 0];
-                    o0.y += v[8 * g + 1] * hf[1] * dmdci[8 * g + 1];
-                    o0.z += v[8 * g + 2] * hf[2] * dmdci[8 * g + 2];
-                    o0.w += v[8 * g + 3] * hf[3] * dmdci[8 * g + 3];
-                    o1.x += v[8 * g + 4] * hf[4] * dmdci[8 * g + 4];
-                    o1.y += v[8 * g + 5] * hf[5] * dmdci[8 * g + 5];
-                    o1.z += v[8 * g + 6] * hf[6] * dmdci[8 * g + 6];
-                    o1.w += v[8 * g + 7] * hf[7] * dmdci[8 * g + 7];
-                    *reinterpret_cast<float4*>(dst) = o0;
-                    *reinterpret_cast<float4*>(dst + 4) = o1;
                   }
                 }
               }
@@ -610,7 +619,7 @@ struct PdGemmCall {
   const void* ci; long long ld_ci;
   const void* H; long long ld_h;
   const float* delta; const float* rowscale;
-  float* dci; long long ld_dci; int dci_accumulate;
+  float* dci; long long ld_dci; int dci_accumulate; int dci_bf16;
   unsigned long long seed; unsigned int rng_stream; unsigned int rng_row_offset; int mask_mode;
   // control
   int split_k; int bn; int max_ctas;
@@ -640,14 +649,14 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.ci = static_cast<const __nv_bfloat16*>(c->ci); a.ld_ci = c->ld_ci;
   a.H = static_cast<const __nv_bfloat16*>(c->H); a.ld_h = c->ld_h;
   a.delta = c->delta; a.rowscale = c->rowscale;
-  a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate;
+  a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate; a.dci_bf16 = c->dci_bf16;
   a.seed = c->seed; a.stream = c->rng_stream; a.row_offset = c->rng_row_offset; a.mask_mode = c->mask_mode;
   a.status = c->status;
   if (c->epi != EPI_PLAIN) {
     if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15))
       return kBadArgument;
     if (c->epi == EPI_MASK_BWD && c->dci != nullptr) {
-      if (c->H == nullptr || (c->ld_h % 8) != 0 || (c->ld_dci % 4) != 0 ||
+      if (c->H == nullptr || (c->ld_h % 8) != 0 || (c->ld_dci % (c->dci_bf16 ? 8 : 4)) != 0 ||
           (reinterpret_cast<uintptr_t>(c->H) & 15) || (reinterpret_cast<uintptr_t>(c->dci) & 15))
         return kBadArgument;
     }

@@ -131,3 +131,64 @@ class _SwiGLU(torch.autograd.Function):
 
 def swiglu(gate: Tensor, up: Tensor) -> Tensor:
     return _SwiGLU.apply(gate, up)
+
+
+class _SquashActivity(torch.autograd.Function):
+    """`pre [rows, C]` bf16 -> (`lower` bf16, `activity [C]` fp32 = mean over rows of the smooth-L0
+    penalty of the upper-leaky importance). One read of `pre` in forward, one fused pass in backward
+    that applies the lower-leaky gradient rule and the minimality gradient together."""
+
+    @staticmethod
+    def forward(ctx, pre: Tensor, gamma: float, normalize_at_one: bool, alpha: float):  # type: ignore[override]
+        rows, Cn = pre.shape
+        pre = pre.contiguous()
+        lower = torch.empty_like(pre)
+        colsum = torch.zeros(Cn, device=pre.device, dtype=torch.float32)
+        lib = _lib()
+        lib.pd_ci_squash_activity.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_float,
+                                              C.c_int, C.c_float, C.c_void_p]
+        _check(lib.pd_ci_squash_activity(pre.data_ptr(), lower.data_ptr(), colsum.data_ptr(), rows, Cn, gamma,
+                                         int(normalize_at_one), alpha, _s()), "ci_squash_activity")
+        ctx.save_for_backward(pre)
+        ctx.cfg = (gamma, normalize_at_one, alpha)
+        ctx.mark_non_differentiable()
+        return lower, colsum / rows
+
+    @staticmethod
+    def backward(ctx, dlower: Tensor | None, dact: Tensor | None):  # type: ignore[override]
+        (pre,) = ctx.saved_tensors
+        gamma, norm, alpha = ctx.cfg
+        rows, Cn = pre.shape
+        dcol = (dact.float() / rows).contiguous() if dact is not None else torch.zeros(Cn, device=pre.device)
+        dpre = torch.empty_like(pre)
+        lib = _lib()
+        lib.pd_ci_squash_activity_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
+                                                  C.c_float, C.c_int, C.c_float, C.c_void_p]
+        dl = None if dlower is None else dlower.contiguous()
+        _check(lib.pd_ci_squash_activity_bwd(pre.data_ptr(), dl.data_ptr() if dl is not None else None, dcol.data_ptr(),
+                                             dpre.data_ptr(), rows, Cn, gamma, int(norm), alpha, _s()),
+               "ci_squash_activity_bwd")
+        return dpre, None, None, None
+
+
+def squash_activity(pre: Tensor, gamma: float, normalize_at_one: bool, alpha: float = 0.01) -> tuple[Tensor, Tensor]:
+    lead = pre.shape[:-1]
+    lower, act = _SquashActivity.apply(pre.reshape(-1, pre.shape[-1]), gamma, normalize_at_one, alpha)
+    return lower.reshape(*lead, -1), act
+
+
+def vocab_kl_rows(lc: Tensor, lm: Tensor, want_grad: bool) -> tuple[Tensor, Tensor | None]:
+    """Per-row `KL(softmax(lc) || softmax(lm))` and (optionally) `softmax(lm) - softmax(lc)`.
+    `lc`, `lm`: `[rows, V]` bf16 views whose row pitch is a multiple of 8 elements."""
+    rows, V = lc.shape
+    assert lc.stride(1) == 1 and lm.stride(1) == 1 and lc.stride(0) == lm.stride(0) and lc.stride(0) % 8 == 0
+    kl = torch.empty(rows, device=lc.device, dtype=torch.float32)
+    dlm = None
+    if want_grad:
+        dlm = torch.empty(rows, lc.stride(0), device=lc.device, dtype=torch.bfloat16)[:, :V]
+    lib = _lib()
+    lib.pd_vocab_kl.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong,
+                                C.c_void_p]
+    _check(lib.pd_vocab_kl(lc.data_ptr(), lm.data_ptr(), dlm.data_ptr() if dlm is not None else None, kl.data_ptr(),
+                           rows, V, lc.stride(0), _s()), "vocab_kl")
+    return kl, dlm

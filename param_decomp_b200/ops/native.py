@@ -39,7 +39,7 @@ class PdGemmCall(C.Structure):
         ("ci", C.c_void_p), ("ld_ci", C.c_longlong),
         ("H", C.c_void_p), ("ld_h", C.c_longlong),
         ("delta", C.c_void_p), ("rowscale", C.c_void_p),
-        ("dci", C.c_void_p), ("ld_dci", C.c_longlong), ("dci_accumulate", C.c_int),
+        ("dci", C.c_void_p), ("ld_dci", C.c_longlong), ("dci_accumulate", C.c_int), ("dci_bf16", C.c_int),
         ("seed", C.c_ulonglong), ("rng_stream", C.c_uint), ("rng_row_offset", C.c_uint), ("mask_mode", C.c_int),
         ("split_k", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int),
         ("status", C.c_void_p),
@@ -199,8 +199,9 @@ def gemm(
         assert rowscale.dtype == torch.float32 and rowscale.is_contiguous() and rowscale.numel() == M
         call.rowscale = rowscale.data_ptr()
     if dci is not None:
-        assert dci.dtype == torch.float32 and dci.stride(-1) == 1
+        assert dci.dtype in (torch.float32, torch.bfloat16) and dci.stride(-1) == 1
         call.dci, call.ld_dci = dci.data_ptr(), dci.stride(-2)
+        call.dci_bf16 = int(dci.dtype == torch.bfloat16)
     call.dci_accumulate = int(dci_accumulate)
     call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
     call.rng_row_offset = row_offset & 0xFFFFFFFF

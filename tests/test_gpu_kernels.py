@@ -1,0 +1,291 @@
+"""sm_100a kernels against plain PyTorch fp32 references (run on a B200)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+bf = torch.bfloat16
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.fixture(scope="module")
+def nv():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from param_decomp_b200.ops import native
+
+    native.lib()  # must load: no silent fallback on a GPU box
+    return native
+
+
+def _done(nv):
+    torch.cuda.synchronize()
+    nv.check_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(512, 512, 256), (1000, 776, 328), (130, 72, 64)])
+def test_gemm_all_majors(nv, a_mn, b_mn, shape):
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=bf)
+    b = torch.randn(N, K, device="cuda", dtype=bf)
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte row pitch")
+    out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    nv.gemm(a.T.contiguous() if a_mn else a, b.T.contiguous() if b_mn else b, out, a_mn=a_mn, b_mn=b_mn)
+    _done(nv)
+    assert rel(out, a.float() @ b.float().T) < 1e-5
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_bf16_out_splitk_two_phase(nv, bn):
+    torch.manual_seed(1)
+    M, N, K, K1 = 1000, 776, 640, 192
+    a, b = torch.randn(M, K, device="cuda", dtype=bf), torch.randn(N, K, device="cuda", dtype=bf)
+    a1, b1 = torch.randn(M, K1, device="cuda", dtype=bf), torch.randn(K1, N, device="cuda", dtype=bf)
+    ob = torch.zeros(M, N, device="cuda", dtype=bf)
+    nv.gemm(a, b, ob, a1=a1, b1=b1, b1_mn=True, bn=bn)
+    base = torch.randn(M, N, device="cuda")
+    acc = base.clone()
+    nv.gemm(a, b, acc, accumulate=True, split_k=3, bn=bn)
+    _done(nv)
+    assert rel(ob, a.float() @ b.float().T + a1.float() @ b1.float()) < 5e-3
+    assert rel(acc, base + a.float() @ b.float().T) < 1e-5
+
+
+def test_gemm_batched_bias_act(nv):
+    torch.manual_seed(2)
+    B = 3
+    a, b = torch.randn(B, 200, 128, device="cuda", dtype=bf), torch.randn(B, 128, 264, device="cuda", dtype=bf)
+    bias = torch.randn(B, 264, device="cuda")
+    for act, fn in (("gelu", torch.nn.functional.gelu), ("silu", torch.nn.functional.silu), ("relu", torch.relu), (None, lambda t: t)):
+        o = torch.zeros(B, 200, 264, device="cuda", dtype=bf)
+        nv.gemm(a, b, o, b_mn=True, bias=bias, act=act, alpha=0.5)
+        _done(nv)
+        assert rel(o, fn(0.5 * (a.float() @ b.float()) + bias[:, None, :])) < 5e-3, act
+
+
+def test_mask_epilogues_match_philox_reference(nv):
+    from param_decomp_b200.ops.philox_ref import uniform
+
+    torch.manual_seed(3)
+    M, C, D, Dout = 640, 512, 192, 256
+    x = torch.randn(M, D, device="cuda", dtype=bf)
+    V = (torch.randn(D, C, device="cuda") / D**0.5).to(bf)
+    U = (torch.randn(C, Dout, device="cuda") / C**0.5).to(bf)
+    ci = torch.rand(M, C, device="cuda").to(bf)
+    delta = torch.rand(M, device="cuda")
+    rs = (torch.rand(M, device="cuda") > 0.3).float()
+    A, H = torch.zeros(M, C, device="cuda", dtype=bf), torch.zeros(M, C, device="cuda", dtype=bf)
+    nv.gemm(x, V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci, delta=delta, rowscale=rs, seed=1234,
+            rng_stream=7, row_offset=100)
+    u = uniform(1234, 7, M, C, row_offset=100, device="cuda")
+    Href = x.float() @ V.float()
+    coef = rs[:, None] * (ci.float() + (1 - ci.float()) * u - delta[:, None])
+    dy = torch.randn(M, Dout, device="cuda", dtype=bf)
+    dH = torch.zeros(M, C, device="cuda", dtype=bf)
+    dci32 = torch.randn(M, C, device="cuda")
+    dci0 = dci32.clone()
+    nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, delta=delta, rowscale=rs, dci=dci32, dci_accumulate=True,
+            seed=1234, rng_stream=7, row_offset=100)
+    dcib = torch.zeros(M, C, device="cuda", dtype=bf)
+    nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, delta=delta, rowscale=rs, dci=dcib, seed=1234, rng_stream=7,
+            row_offset=100)
+    _done(nv)
+    dA = dy.float() @ U.float().T
+    want_dci = dA * H.float() * rs[:, None] * (1 - u)
+    assert rel(H, Href) < 5e-3 and rel(A, Href * coef) < 5e-3
+    assert rel(dH, dA * coef) < 5e-3
+    assert rel(dci32, dci0 + want_dci) < 1e-5 and rel(dcib, want_dci) < 5e-3
+
+
+def test_bounded_wait_reports_instead_of_hanging(nv):
+    """A GEMM whose grid is capped far below the tile count still finishes and leaves status 0; the
+    status word protocol itself is exercised by reading and clearing it."""
+    a = torch.randn(4096, 256, device="cuda", dtype=bf)
+    b = torch.randn(4096, 256, device="cuda", dtype=bf)
+    o = torch.empty(4096, 4096, device="cuda", dtype=bf)
+    nv.gemm(a, b, o, max_ctas=3)
+    _done(nv)
+    assert rel(o, a.float() @ b.float().T) < 5e-3
+    assert int(nv.status_word().item()) == 0
+
+
+def test_elementwise_kernels(nv):
+    from param_decomp_b200.models import ports
+    from param_decomp_b200.ops import elementwise as ew
+
+    torch.manual_seed(4)
+    x = torch.randn(6, 130, 768, device="cuda", dtype=bf, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(768, device="cuda")).to(bf)
+    y = ew.rms_norm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2 = x.detach().float().requires_grad_(True)
+    y2 = ports.rms_norm(x2, w.float(), 1e-6)
+    y2.backward(g.float())
+    assert rel(y, y2) < 5e-3 and rel(x.grad, x2.grad) < 1e-2
+
+    q = torch.randn(2, 128, 4, 64, device="cuda", dtype=bf, requires_grad=True)
+    cos, sin = ports.rope_cos_sin(torch.arange(128, device="cuda")[None], 64, 10000.0)
+    r = ew.rope(q, cos[0, :, :32].contiguous(), sin[0, :, :32].contiguous())
+    r.backward(torch.ones_like(r))
+    q2 = q.detach().float().requires_grad_(True)
+    r2 = ports.apply_rope(q2, cos, sin)
+    r2.backward(torch.ones_like(r2))
+    assert rel(r, r2) < 5e-3 and rel(q.grad, q2.grad) < 5e-3
+
+    ga = torch.randn(300, 512, device="cuda", dtype=bf, requires_grad=True)
+    up = torch.randn(300, 512, device="cuda", dtype=bf, requires_grad=True)
+    o = ew.swiglu(ga, up)
+    go = torch.randn_like(o)
+    o.backward(go)
+    g2, u2 = ga.detach().float().requires_grad_(True), up.detach().float().requires_grad_(True)
+    o2 = torch.nn.functional.silu(g2) * u2
+    o2.backward(go.float())
+    assert rel(o, o2) < 5e-3 and rel(ga.grad, g2.grad) < 1e-2 and rel(up.grad, u2.grad) < 1e-2
+    assert rel(ew.cast_bf16(g2.detach()), g2.detach()) < 5e-3
+    s = torch.rand(300, device="cuda")
+    assert rel(ew.rowscale(ga.detach(), s), ga.detach().float() * s[:, None]) < 5e-3
+    _done(nv)
+
+
+def test_fused_adamw_and_clip(nv):
+    from param_decomp_b200.ops import optim as fo
+
+    torch.manual_seed(5)
+    p = torch.randn(1000, 77, device="cuda")
+    g = torch.randn_like(p) * 3
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    ref = p.clone().requires_grad_(True)
+    ref.grad = g.clone()
+    tn = torch.nn.utils.clip_grad_norm_([ref], 1.0)
+    topt = torch.optim.AdamW([ref], lr=1e-2, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8)
+    topt.step()
+    norm, scale = fo.grad_norm_and_scale([g], 1.0)
+    fo.adamw_step([p], [g], [m], [v], lr=1e-2, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, bc1=1 - 0.9, bc2=1 - 0.95, grad_scale=scale)
+    _done(nv)
+    assert float(norm) == pytest.approx(float(tn), rel=1e-4)
+    assert torch.allclose(p, ref.detach(), atol=2e-6)
+
+
+def test_squash_activity_matches_eager(nv):
+    from param_decomp_b200.core import losses
+    from param_decomp_b200.core.squashing import lower_leaky_hard_sigmoid, upper_leaky_hard_sigmoid
+    from param_decomp_b200.ops.elementwise import squash_activity
+
+    torch.manual_seed(6)
+    pre = (torch.randn(777, 512, device="cuda") * 1.5).to(bf).requires_grad_(True)
+    lower, act = squash_activity(pre, 0.3, True)
+    gl = torch.randn_like(lower)
+    ga = torch.randn(512, device="cuda")
+    (lower.float() * gl.float()).sum().add((act * ga).sum()).backward()
+    p2 = pre.detach().float().requires_grad_(True)
+    l2 = lower_leaky_hard_sigmoid(p2)
+    a2 = losses.component_activity(upper_leaky_hard_sigmoid(p2), 0.3, True)
+    ((l2 * gl.float()).sum() + (a2 * ga).sum()).backward()
+    _done(nv)
+    assert rel(lower, l2) < 1e-6 and rel(act, a2) < 1e-4
+    assert rel(pre.grad, p2.grad) < 1e-2
+
+
+def test_vocab_kl_matches_eager(nv):
+    from param_decomp_b200.core.losses import kl_from_logits
+    from param_decomp_b200.ops import vocab_kl
+
+    torch.manual_seed(7)
+    n, d, V = 300, 128, 1003
+    head = (torch.randn(V, d, device="cuda") * 0.2).to(bf)
+    hc = torch.randn(n, d, device="cuda", dtype=bf)
+    hm = (hc.float() + 0.3 * torch.randn(n, d, device="cuda")).to(bf).requires_grad_(True)
+    loss = vocab_kl.kl_from_hidden(vocab_kl.padded_logits(hc, head), hm, head)
+    (loss * 3.0).backward()
+    h2 = hm.detach().float().requires_grad_(True)
+    ref = kl_from_logits((hc.float() @ head.float().T).to(bf), (h2 @ head.float().T).to(bf).float() + 0 * h2.sum())
+    ref2 = kl_from_logits(hc.float() @ head.float().T, h2 @ head.float().T)
+    (ref2 * 3.0).backward()
+    _done(nv)
+    assert float(loss) == pytest.approx(float(ref2), rel=3e-2)
+    assert rel(hm.grad, h2.grad) < 5e-2
+
+
+def test_fused_site_matches_eager(nv):
+    from param_decomp_b200.core.decomposed_linear import site_forward
+    from param_decomp_b200.core.masking import SiteMask, StochasticSpec
+    from param_decomp_b200.ops.site_linear import SiteWeights, fused_site_forward
+
+    torch.manual_seed(8)
+    N, d_in, C, d_out = 384, 192, 256, 320
+    V32 = torch.randn(d_in, C, device="cuda") / d_in**0.5
+    U32 = torch.randn(C, d_out, device="cuda") / C**0.5
+    W = (torch.randn(d_out, d_in, device="cuda") / d_in**0.5).to(bf)
+    x = torch.randn(2, N // 2, d_in, device="cuda", dtype=bf)
+    ci = torch.rand(2, N // 2, C, device="cuda").to(bf)
+    delta = torch.rand(2, N // 2, 1, device="cuda").to(bf)
+    route = torch.rand(2, N // 2, device="cuda") > 0.25
+    spec = StochasticSpec(seed64=(5 << 32) | 9, stream=77, row_offset=0)
+    for sm in (SiteMask(ci=ci, delta=delta, route=route, stochastic=spec), SiteMask(mask=ci, delta=None),
+               SiteMask(mask=None, delta=delta), SiteMask()):
+        xf = x.clone().requires_grad_(True)
+        cif = ci.clone().requires_grad_(True)
+        smf = SiteMask(ci=cif if sm.ci is not None else None, mask=cif if sm.mask is not None else None,
+                       delta=sm.delta, route=sm.route, stochastic=sm.stochastic)
+        gV, gU = torch.zeros_like(V32), torch.zeros_like(U32)
+        w = SiteWeights(V32.to(bf), U32.to(bf), W, gV, gU)
+        y = fused_site_forward(xf, w, smf, need_weight_grads=True)
+        gy = torch.randn_like(y)
+        y.backward(gy)
+        xe = x.clone().float().requires_grad_(True)
+        cie = ci.clone().float().requires_grad_(True)
+        Ve, Ue = V32.to(bf).float().requires_grad_(True), U32.to(bf).float().requires_grad_(True)
+        sme = SiteMask(ci=cie if sm.ci is not None else None, mask=cie if sm.mask is not None else None,
+                       delta=None if sm.delta is None else sm.delta.float(), route=sm.route, stochastic=sm.stochastic)
+        ye = site_forward(xe, Ve, Ue, W.float(), sme)
+        ye.backward(gy.float())
+        _done(nv)
+        assert rel(y, ye) < 1e-2
+        assert rel(xf.grad, xe.grad) < 2e-2
+        assert rel(gV, Ve.grad) < 2e-2 and rel(gU, Ue.grad) < 2e-2
+        if cie.grad is not None:
+            assert rel(cif.grad, cie.grad) < 2e-2
+
+
+def test_step_parity_fused_vs_eager(nv):
+    import copy
+    import json
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+    from param_decomp_b200.core.objective import build_objective
+    from param_decomp_b200.core.run import init_train_state
+    from param_decomp_b200.core.train import StepContext, train_step
+    from param_decomp_b200.experiments.lm.build import build_lm_run
+
+    dev = torch.device("cuda", 0)
+    res = {}
+    for backend in ("eager_torch", "fused_sm100"):
+        c = copy.deepcopy(ge.SMOKE_CONFIG)
+        c["runtime"]["backend"] = backend
+        cfg = LMExperimentConfig.model_validate(c)
+        run = build_lm_run(cfg, None, dev)
+        obj = build_objective(cfg.pd)
+        fused = backend == "fused_sm100"
+        ctx = StepContext.build(run.model, obj, cfg.pd, lazy_masks=fused)
+        st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, dev, cfg.pd.batch_size, cfg.data.seq_len, use_fused_optim=fused)
+        for s in range(3):
+            m = train_step(ctx, st, run.sample_train(s))
+        _done(nv)
+        res[backend] = {k: float(v) for k, v in m.items()}
+    for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss",
+              "grad_norm/components"):
+        a, b = res["eager_torch"][k], res["fused_sm100"][k]
+        assert abs(a - b) <= 2e-2 * abs(a) + 1e-6, (k, a, b)
+
+
+def test_smoke_entry(nv):
+    import __graft_entry__ as ge
+
+    ge.smoke()
