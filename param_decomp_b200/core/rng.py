@@ -44,6 +44,13 @@ class StepKey:
 def uniform(key: StepKey, stream: int, rows: int, cols: int, row_offset: int = 0,
             device: torch.device | str = "cpu") -> Tensor:
     """`[rows, cols]` uniforms in (0,1); `cols` is padded up to a multiple of 8 internally."""
+    if torch.device(device).type == "cuda":
+        from param_decomp_b200.ops import native
+
+        if native.LIB_PATH.exists():  # same stream, one kernel instead of ~150 tiny integer ops
+            from param_decomp_b200.ops.elementwise import philox_uniform
+
+            return philox_uniform(key.seed64, stream, rows, cols, row_offset, device)
     padded = ((cols + 7) // 8) * 8
     u = philox_ref.uniform(key.seed64, stream, rows, padded, row_offset, device)
     return u[:, :cols]

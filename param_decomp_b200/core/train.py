@@ -91,6 +91,14 @@ class StepContext:
     nontarget: NontargetObjective | None = None
     relative_faithfulness: bool = True
 
+    def weights_sq_host(self) -> dict[str, float]:
+        """`||W_s||^2` as host floats (read back once, then cached)."""
+        cached = getattr(self, "_wsq_host", None)
+        if cached is None:
+            cached = {k: float(v) for k, v in self.weights_sq.items()}
+            self._wsq_host = cached
+        return cached
+
     @classmethod
     def build(cls, model: DecomposedModel, objective: PDObjective, pd, **kw: Any) -> "StepContext":
         return cls(model=model, objective=objective, pd=pd, weights_W=target_weights(model),
@@ -269,7 +277,8 @@ def _detach_ci(ci_lower: dict[str, Tensor]) -> dict[str, Tensor]:
 
 
 def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: int | None = None) -> CI:
-    pre = state.ci_fn(clean.taps, aux=clean.aux, components=state.components)
+    pre = state.ci_fn(clean.taps, aux=clean.aux, components=state.components,
+                      segment_ids=clean.aux.get("segment_ids"), positions=clean.aux.get("positions"))
     cfg = ctx.objective.minimality
     fusable = (step is not None and ctx.lazy_masks and isinstance(cfg, L.ImportanceMinimalityLossConfig)
                and all(isinstance(v, torch.Tensor) and v.is_cuda and v.dtype == torch.bfloat16
@@ -336,10 +345,16 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         total_loss = x if total_loss is None else total_loss + x
 
     if obj.faith is not None:
-        faith = loss_fns.faithfulness_loss(state.components, ctx.weights_W, ctx.weights_sq,
-                                           relative=ctx.relative_faithfulness)
+        c_f = scheduled_or_constant(obj.faith.coeff, step, total)
+        if direct and ctx.relative_faithfulness and all(not s.blocked for s in ctx.model.sites):
+            from param_decomp_b200.ops.faithfulness import fused_faithfulness
+
+            faith = fused_faithfulness(state.components, ctx.weights_W, ctx.weights_sq_host(), c_f)
+        else:
+            faith = loss_fns.faithfulness_loss(state.components, ctx.weights_W, ctx.weights_sq,
+                                               relative=ctx.relative_faithfulness)
         metrics["loss/" + obj.faith.instance_key] = faith.detach()
-        add(scheduled_or_constant(obj.faith.coeff, step, total) * faith)
+        add(c_f * faith)
     add(evaluate_minimality(ctx, state, ci, step, metrics))
     if obj.nonlinearity is not None:
         nl = obj.nonlinearity

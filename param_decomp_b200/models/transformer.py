@@ -171,6 +171,15 @@ class TransformerDecomposedModel:
     def target_weight(self, site: str) -> Tensor:
         return self.w[site + ".weight"]
 
+    def layer_of_site(self, site: str) -> int:
+        return self._site_layer_kind[site][0]
+
+    def block_tap_widths(self, layer: int) -> dict[str, int]:
+        """Every site-input vector the block computes (each physical vector once)."""
+        a = self.arch
+        return {f"attn_in.{layer}": a.d_model, f"attn_out.{layer}": a.n_head * self.head_dim,
+                f"mlp_in.{layer}": a.d_model, f"mlp_hidden.{layer}": a.d_ff}
+
     def head_weight(self) -> Tensor:
         return self.w["embed.weight"] if self.arch.tie_embeddings else self.w["lm_head.weight"]
 
@@ -288,6 +297,7 @@ class TransformerDecomposedModel:
         out = self._run(batch, None, None, capture, want_taps=True)
         # the clean side of the KL: keep what the loss needs, once per step
         out.aux["clean_stats"] = self._clean_logit_stats(out.output)
+        out.aux["segment_ids"], out.aux["positions"] = batch.segment_ids, batch.positions
         return out
 
     def masked_forward(self, weights: ComputeWeights, batch: LMBatch, masks: Masks,

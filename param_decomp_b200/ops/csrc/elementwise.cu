@@ -2,9 +2,7 @@
 // fp32 -> bf16 casts, RMSNorm forward/backward, rotary embedding, SwiGLU forward/backward,
 // per-row scaling, leaky-hard sigmoids. All are plain grid-stride / row-per-warp kernels with
 // 16-byte vector accesses; none of them waits on anything, so none needs a status word.
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
+#include "common.cuh"
 
 namespace {
 
@@ -475,6 +473,35 @@ __global__ void vocab_kl_kernel(const __nv_bfloat16* __restrict__ lc, const __nv
   }
 }
 
+
+// out[row, 8g .. 8g+7] = the Philox uniforms the GEMM epilogues draw for (seed, stream, row, g).
+__global__ void philox_uniform_kernel(float* __restrict__ out, long long rows, int groups, int cols,
+                                      unsigned long long seed, unsigned int stream, unsigned int row_offset) {
+  const long long total = rows * groups;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / groups;
+    const int g = static_cast<int>(i % groups);
+    float u[8];
+    pd::philox_uniform8(seed, stream, static_cast<uint32_t>(row) + row_offset, static_cast<uint32_t>(g), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (8 * g + k < cols) out[row * cols + 8 * g + k] = u[k];
+  }
+}
+
+// hi = bf16(x), lo = bf16(x - hi): x ~= hi + lo to ~16 mantissa bits, for split-precision products.
+__global__ void split_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ hi,
+                                  __nv_bfloat16* __restrict__ lo, long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float v = x[i];
+    const __nv_bfloat16 h = __float2bfloat16(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16(v - __bfloat162float(h));
+  }
+}
+
 }  // namespace
 
 #define PD_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : 1)
@@ -581,5 +608,18 @@ extern "C" int pd_vocab_kl(const void* lc, const void* lm, void* dlm, float* kl,
   vocab_kl_kernel<<<static_cast<unsigned>(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(lc), static_cast<const __nv_bfloat16*>(lm),
       static_cast<__nv_bfloat16*>(dlm), kl, V, ld);
+  return PD_CHECK_LAUNCH();
+}
+
+extern "C" int pd_philox_uniform(float* out, long long rows, int cols, unsigned long long seed, unsigned int stream,
+                                 unsigned int row_offset, void* stream_v) {
+  const int groups = (cols + 7) / 8;
+  philox_uniform_kernel<<<blocks_for(rows * groups, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream_v)>>>(
+      out, rows, groups, cols, seed, stream, row_offset);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_split_bf16(const float* x, void* hi, void* lo, long long n, void* stream) {
+  split_bf16_kernel<<<blocks_for(n, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, static_cast<__nv_bfloat16*>(hi), static_cast<__nv_bfloat16*>(lo), n);
   return PD_CHECK_LAUNCH();
 }

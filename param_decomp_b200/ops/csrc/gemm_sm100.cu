@@ -27,6 +27,8 @@
 //                 coef = rowscale * (m - delta),  m = ci + (1 - ci) * u,  u ~ Philox(seed, stream, row, col)
 //                 or m read from memory when mask_mode == 1
 //   EPI_MASK_BWD  acc = dA;  out0 = bf16(acc .* coef);  dci (+)= acc .* H .* rowscale .* dm/dci
+//   EPI_FAITH     out0 = bf16(R - acc) with R read from memory, and *sumsq += sum (R - acc)^2:
+//                 the faithfulness residual W - (VU)^T and its squared norm without a second pass
 //
 // Every wait is bounded (see common.cuh); on time-out the kernel stores a code to *status and returns.
 #include "common.cuh"
@@ -41,7 +43,7 @@ constexpr int kGroupM = 16;
 constexpr int kStageBytesA = BM * BK * 2;  // 16 KiB
 constexpr int kOutBoxBytes = 32 * 128;     // one 32-row x 128-byte staging box
 
-enum Epi : int { EPI_PLAIN = 0, EPI_MASK_FWD = 1, EPI_MASK_BWD = 2 };
+enum Epi : int { EPI_PLAIN = 0, EPI_MASK_FWD = 1, EPI_MASK_BWD = 2, EPI_FAITH = 3 };
 enum Act : int { ACT_NONE = 0, ACT_GELU = 1, ACT_SILU = 2, ACT_RELU = 3 };
 
 struct GemmArgs {
@@ -334,6 +336,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const uint32_t box1 = box0 + (NOUT - 1) * kOutBoxBytes;
     int acc = 0;
     uint32_t acc_phase = 0;
+    float faith_acc = 0.0f;
     const bool out32 = (EPI == EPI_PLAIN) && args.out_fp32;
     const int box_cols = out32 ? 32 : 64;
     const int nboxes = BN / box_cols;
@@ -419,6 +422,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
               stage_fp32(box0, lane, v);
             else
               stage_bf16_half(box0, lane, half, v);
+          } else if constexpr (EPI == EPI_FAITH) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float rf[8];
+              unpack8(ciq[4 * half + g], rf);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float dlt = rf[i] - v[8 * g + i];
+                v[8 * g + i] = dlt;
+                faith_acc += dlt * dlt;
+              }
+            }
+            stage_bf16_half(box0, lane, half, v);
           } else {
             float coef[32], dmdci[32];
 #pragma unroll
@@ -525,6 +541,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    if constexpr (EPI == EPI_FAITH) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) faith_acc += __shfl_xor_sync(0xffffffffu, faith_acc, o);
+      if (lane == 0 && args.dci != nullptr) atomicAdd(args.dci, faith_acc);
     }
     if (lane == 0) tma_store_wait_all<0>();
   }
@@ -652,7 +673,10 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate; a.dci_bf16 = c->dci_bf16;
   a.seed = c->seed; a.stream = c->rng_stream; a.row_offset = c->rng_row_offset; a.mask_mode = c->mask_mode;
   a.status = c->status;
-  if (c->epi != EPI_PLAIN) {
+  if (c->epi == EPI_FAITH) {
+    if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15) || c->N % 8 != 0)
+      return kBadArgument;
+  } else if (c->epi != EPI_PLAIN) {
     if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15))
       return kBadArgument;
     if (c->epi == EPI_MASK_BWD && c->dci != nullptr) {
@@ -695,6 +719,7 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
     return bn == 256 ? PD_LAUNCH(256, EPI_MASK_FWD, 1) : PD_LAUNCH(128, EPI_MASK_FWD, 1);
   }
   if (c->epi == EPI_MASK_BWD) return bn == 256 ? PD_LAUNCH(256, EPI_MASK_BWD, 1) : PD_LAUNCH(128, EPI_MASK_BWD, 1);
+  if (c->epi == EPI_FAITH) return bn == 256 ? PD_LAUNCH(256, EPI_FAITH, 1) : PD_LAUNCH(128, EPI_FAITH, 1);
 #undef PD_LAUNCH
   return kBadArgument;
 }

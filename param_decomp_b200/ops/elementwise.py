@@ -192,3 +192,22 @@ def vocab_kl_rows(lc: Tensor, lm: Tensor, want_grad: bool) -> tuple[Tensor, Tens
     _check(lib.pd_vocab_kl(lc.data_ptr(), lm.data_ptr(), dlm.data_ptr() if dlm is not None else None, kl.data_ptr(),
                            rows, V, lc.stride(0), _s()), "vocab_kl")
     return kl, dlm
+
+
+def philox_uniform(seed64: int, stream: int, rows: int, cols: int, row_offset: int, device) -> Tensor:
+    """`[rows, cols]` fp32 uniforms, bit-identical to `philox_ref.uniform` and to the GEMM epilogues."""
+    out = torch.empty(rows, cols, device=device, dtype=torch.float32)
+    lib = _lib()
+    lib.pd_philox_uniform.argtypes = [C.c_void_p, C.c_longlong, C.c_int, C.c_ulonglong, C.c_uint, C.c_uint, C.c_void_p]
+    _check(lib.pd_philox_uniform(out.data_ptr(), rows, cols, seed64 & (2**64 - 1), stream & 0xFFFFFFFF,
+                                 row_offset & 0xFFFFFFFF, _s()), "philox_uniform")
+    return out
+
+
+def split_bf16(x: Tensor) -> tuple[Tensor, Tensor]:
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    hi, lo = torch.empty_like(x, dtype=torch.bfloat16), torch.empty_like(x, dtype=torch.bfloat16)
+    lib = _lib()
+    lib.pd_split_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]
+    _check(lib.pd_split_bf16(x.data_ptr(), hi.data_ptr(), lo.data_ptr(), x.numel(), _s()), "split_bf16")
+    return hi, lo

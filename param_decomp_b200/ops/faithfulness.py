@@ -1,0 +1,56 @@
+"""Faithfulness loss and its gradients on the tcgen05 engine, never materialising fp32 `V U`.
+
+Per site:  D = W - (V U)^T  comes out of ONE GEMM whose epilogue subtracts the accumulator from `W`
+and reduces `sum D^2` on the fly; the product uses split-precision operands
+(`V = V_hi + V_lo`, `U = U_hi + U_lo` in bf16, three K-phases `U_hi V_hi + U_lo V_hi + U_hi V_lo`
+laid side by side along K), which restores ~16 mantissa bits so the loss keeps falling below the
+bf16 rounding floor. Gradients `dV = -2s (U D)^T`, `dU = -2s V^T D^T` are two more GEMMs that
+accumulate straight into the fp32 master gradients (`s = coeff / (n_sites ||W||^2)`).
+
+Parity: param_decomp/core/faithfulness.py:16-104 (target-relative mean over sites, pads contribute
+nothing), targets/transformer.py:2134-2185 (weight deltas).
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from param_decomp_b200.core.components import ComponentStacks
+from param_decomp_b200.ops import native as nv
+from param_decomp_b200.ops.elementwise import split_bf16
+
+
+def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host: dict[str, float], coeff: float,
+                       accumulate_grads: bool = True) -> Tensor:
+    """Returns the (detached) loss `mean_s ||D_s||^2 / ||W_s||^2`; adds `coeff * dLoss` to `.grad`."""
+    sites = [s for s in stacks.sites if not s.blocked]
+    assert len(sites) == len(stacks.sites), "blocked sites use the grouped faithfulness path"
+    dev = next(stacks.parameters()).device
+    sumsq = torch.zeros(len(sites), 8, device=dev, dtype=torch.float32)
+    n_sites = len(sites)
+    k = 0
+    for gname, members in stacks.groups.items():
+        key = stacks.param_key(gname)
+        pV, pU = stacks.V[key], stacks.U[key]
+        Vh, Vl = split_bf16(pV.detach())
+        Uh, Ul = split_bf16(pU.detach())
+        if accumulate_grads:
+            if pV.grad is None:
+                pV.grad = torch.zeros_like(pV)
+            if pU.grad is None:
+                pU.grad = torch.zeros_like(pU)
+        for i, s in enumerate(members):
+            Wb = W[s.name]
+            assert Wb.dtype == torch.bfloat16, "the fused faithfulness path expects a bf16 target"
+            U_cat = torch.cat([Uh[i], Ul[i], Uh[i]], dim=0)  # [3C, d_out]
+            V_cat = torch.cat([Vh[i], Vh[i], Vl[i]], dim=1)  # [d_in, 3C]
+            D = torch.empty(s.d_out, s.d_in, device=dev, dtype=torch.bfloat16)
+            nv.gemm(U_cat, V_cat, D, a_mn=True, epi=nv.EPI_FAITH, ci=Wb, dci=sumsq[k:k + 1])
+            if accumulate_grads:
+                alpha = -2.0 * coeff / (n_sites * w_sq_host[s.name])
+                nv.gemm(D, Uh[i], pV.grad[i], a_mn=True, accumulate=True, alpha=alpha)
+                nv.gemm(Vh[i], D, pU.grad[i], a_mn=True, accumulate=True, alpha=alpha)
+            k += 1
+    wsq = torch.tensor([w_sq_host[s.name] for s in sites], device=dev, dtype=torch.float32)
+    return (sumsq[:, 0] / wsq).mean()

@@ -15,7 +15,7 @@ import torch
 
 LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libpdb200.so"
 
-EPI_PLAIN, EPI_MASK_FWD, EPI_MASK_BWD = 0, 1, 2
+EPI_PLAIN, EPI_MASK_FWD, EPI_MASK_BWD, EPI_FAITH = 0, 1, 2, 3
 ACT_NONE, ACT_GELU, ACT_SILU, ACT_RELU = 0, 1, 2, 3
 _ACT = {None: ACT_NONE, "none": ACT_NONE, "gelu": ACT_GELU, "silu": ACT_SILU, "relu": ACT_RELU}
 

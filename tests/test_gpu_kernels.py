@@ -289,3 +289,44 @@ def test_smoke_entry(nv):
     import __graft_entry__ as ge
 
     ge.smoke()
+
+
+def test_fused_faithfulness_matches_fp32(nv):
+    from param_decomp_b200.core import losses
+    from param_decomp_b200.core.components import ComponentStacks, SiteSpec
+    from param_decomp_b200.ops.faithfulness import fused_faithfulness
+
+    torch.manual_seed(9)
+    sites = (SiteSpec("a", 192, 256, 320, group="g"), SiteSpec("b", 192, 256, 320, group="g"),
+             SiteSpec("c", 256, 128, 64, group="h"))
+    st = ComponentStacks(sites).to("cuda")
+    st.init_random(torch.Generator().manual_seed(0))
+    W = {s.name: (st.weight(s.name).detach() + 0.02 * torch.randn(s.d_out, s.d_in, device="cuda")).to(bf) for s in sites}
+    wsq = {k: float(v.float().pow(2).sum()) for k, v in W.items()}
+    loss = fused_faithfulness(st, W, wsq, coeff=3.0)
+    gV, gU = st.V["g"].grad.clone(), st.U["h"].grad.clone()
+    for p in st.parameters():
+        p.grad = None
+    ref = losses.faithfulness_loss(st, {k: v.float() for k, v in W.items()})
+    (3.0 * ref).backward()
+    _done(nv)
+    assert float(loss) == pytest.approx(float(ref), rel=2e-3)
+    assert rel(gV, st.V["g"].grad) < 2e-2 and rel(gU, st.U["h"].grad) < 2e-2
+    # split precision: an exact factorisation gives a residual far below the bf16 rounding floor
+    Wx = {s.name: st.weight(s.name).detach().to(bf) for s in sites}
+    for p in st.parameters():
+        p.grad = None
+    exact = fused_faithfulness(st, Wx, {k: float(v.float().pow(2).sum()) for k, v in Wx.items()}, 1.0, accumulate_grads=False)
+    ref_exact = losses.faithfulness_loss(st, {k: v.float() for k, v in Wx.items()})
+    _done(nv)
+    assert float(exact) < 4 * float(ref_exact) + 1e-7
+
+
+def test_native_philox_matches_reference(nv):
+    from param_decomp_b200.ops.elementwise import philox_uniform
+    from param_decomp_b200.ops.philox_ref import uniform
+
+    a = philox_uniform(0xABCDEF0123, 99, 37, 21, 5, "cuda")
+    b = uniform(0xABCDEF0123, 99, 37, 24, 5, "cuda")[:, :21]
+    _done(nv)
+    assert torch.equal(a, b)
