@@ -95,6 +95,8 @@ def main() -> None:
     ap.add_argument("--impl", type=str, default="ours")
     ap.add_argument("--config", type=Path, default=CONFIG)
     ap.add_argument("--batch", type=int, default=None, help="override the global batch (debugging only)")
+    ap.add_argument("--optim", type=str, default="fused_p2p", choices=["fused_p2p", "collective", "ddp"],
+                    help="N>1: fused reduce-scatter+AdamW+all-gather kernel, NCCL RS/AG, or all-reduce + replicated AdamW")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -122,8 +124,9 @@ def main() -> None:
     objective = build_objective(cfg.pd)
     ctx = StepContext.build(run.model, objective, cfg.pd, collectives=topo.collectives(), lazy_masks=True)
     rows = cfg.pd.batch_size // topo.data_world
+    shard_backend = args.optim if (world > 1 and args.optim != "ddp") else None
     state = init_train_state(run.model, run.ci_fn, cfg.pd, objective, topo.device, rows, cfg.data.seq_len,
-                             use_fused_optim=True)
+                             use_fused_optim=True, shard_group=topo.data_group, shard_backend=shard_backend)
     tokens_per_step = cfg.pd.batch_size * cfg.data.seq_len
 
     def sync() -> None:
@@ -187,7 +190,8 @@ def main() -> None:
             "config": {
                 "model": f"llama-style {arch.n_layer}L d{arch.d_model} h{arch.n_head} ff{arch.d_ff} vocab{arch.vocab_size}",
                 "global_batch": cfg.pd.batch_size, "seq_len": cfg.data.seq_len,
-                "parallelism": f"dp{world}" if world > 1 else "single",
+                "parallelism": (f"dp{world} ({'zero1 ' + args.optim if shard_backend else 'ddp all-reduce'})"
+                                if world > 1 else "single"),
                 "decomposition": "q,k,v,o,gate,up,down x 4 layers, C=4096 each; layerwise MLP CI fn (hidden 512)",
                 "losses": "faithfulness + smooth-L0 minimality + KL stochastic recon x2 samples",
                 "l2": "per-step working set (>4 GB parameters and optimizer state, >20 GB activations) "

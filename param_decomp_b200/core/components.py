@@ -221,12 +221,19 @@ class ComputeWeights:
                               {k: v.detach() for k, v in self.U.items()})
 
 
-def prepare_compute_weights(stacks: ComponentStacks, dtype: torch.dtype, direct_grads: bool = False) -> ComputeWeights:
+def prepare_compute_weights(stacks: ComponentStacks, dtype: torch.dtype, direct_grads: bool = False,
+                            working: dict[str, Tensor] | None = None) -> ComputeWeights:
+    """`working`: already-cast copies keyed `"V/<group>"` / `"U/<group>"` (the sharded optimizer's
+    all-gathered bf16 buffer); when given, no cast happens here."""
     out = ComputeWeights(direct_grads=direct_grads)
     for gname, members in stacks.groups.items():
         key = stacks.param_key(gname)
         pV, pU = stacks.V[key], stacks.U[key]
-        if direct_grads:
+        if working is not None:
+            assert direct_grads, "a pre-cast working copy carries no autograd link to the masters"
+            Vc, Uc = working["V/" + key], working["U/" + key]
+            assert pV.grad is not None and pU.grad is not None
+        elif direct_grads:
             with torch.no_grad():
                 Vc, Uc = pV.to(dtype), pU.to(dtype)
             if pV.grad is None:

@@ -86,7 +86,8 @@ class PreemptionFlag:
 def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | TargetedPDConfig,
                      objective: PDObjective, device: torch.device | str, batch_rows: int,
                      positions: int | None, stack_multiple: int = 1, use_fused_optim: bool = False,
-                     init_components: Callable[[ComponentStacks], None] | None = None) -> TrainState:
+                     init_components: Callable[[ComponentStacks], None] | None = None,
+                     shard_group: Any = None, shard_backend: str | None = None) -> TrainState:
     """Seeded init: `init` / `source` / `run` streams are separated like the reference's
     `split(PRNGKey(seed), 3)`."""
     g = torch.Generator().manual_seed(pd.seed)
@@ -98,10 +99,20 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
     ci_fn.to(device)
     comp_named = [(n, p) for n, p in components.named_parameters()]
     ci_named = [(n, p) for n, p in ci_fn.named_parameters()]
+    if shard_backend is not None:
+        from param_decomp_b200.config.run import AdamWOptimizerConfig
+        from param_decomp_b200.parallel.sharded_optim import ShardedFlatAdamW
+
+        assert isinstance(pd.components_optimizer, AdamWOptimizerConfig), "the sharded optimizer implements AdamW"
+        comp_opt = ShardedFlatAdamW(pd.components_optimizer, ["/".join(n.split(".")) for n, _ in comp_named],
+                                    [p for _, p in comp_named], pd.steps, shard_group, backend=shard_backend,
+                                    keep_lo=True)
+    else:
+        comp_opt = build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim)
     state = TrainState(
         components=components,
         ci_fn=ci_fn,
-        components_opt=build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim),
+        components_opt=comp_opt,
         ci_fn_opt=build_group_optimizer(pd.ci_fn_optimizer, ci_named, pd.steps, 2, use_fused_optim),
     )
     src_key = StepKey(pd.seed ^ 0x5EED, 0)

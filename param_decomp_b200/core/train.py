@@ -326,12 +326,20 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     with torch.no_grad():
         clean = ctx.model.clean_forward(batch, capture=obj.capture_keys())
     direct = getattr(ctx.model, "backend", "eager_torch") == "fused_sm100"
-    for p in state.components_opt.params + state.ci_fn_opt.params:
+    sharded = hasattr(state.components_opt, "working_view")  # ZeRO-style optimizer owns grads + working copy
+    if sharded:
+        state.components_opt.zero_grad()
+    for p in ([] if sharded else state.components_opt.params) + state.ci_fn_opt.params:
         if direct and p.grad is not None:
             p.grad.zero_()
         else:
             p.grad = None
-    weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct)
+    working = None
+    if sharded:
+        opt = state.components_opt
+        working = {n: opt.working_view(i) for i, n in enumerate(opt.names)}
+    weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct or sharded,
+                                      working=working)
     ci = run_ci_fn(ctx, state, clean, step)
     ci_lower = ci.dense_lower()
 
@@ -349,7 +357,15 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         if direct and ctx.relative_faithfulness and all(not s.blocked for s in ctx.model.sites):
             from param_decomp_b200.ops.faithfulness import fused_faithfulness
 
-            faith = fused_faithfulness(state.components, ctx.weights_W, ctx.weights_sq_host(), c_f)
+            hi_lo = None
+            if sharded and state.components_opt.work_lo_flat is not None:
+                opt = state.components_opt
+                hi_lo = {n: (opt.working_view(i), opt.working_lo_view(i)) for i, n in enumerate(opt.names)}
+            faith = fused_faithfulness(state.components, ctx.weights_W, ctx.weights_sq_host(), c_f, hi_lo=hi_lo,
+                                       rank=getattr(ctx.collectives, "data_rank", 0) if sharded else 0,
+                                       world=ctx.collectives.world_size if sharded else 1)
+            if sharded:
+                faith = ctx.collectives.sum_(faith)
         else:
             faith = loss_fns.faithfulness_loss(state.components, ctx.weights_W, ctx.weights_sq,
                                                relative=ctx.relative_faithfulness)
@@ -404,7 +420,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         final_grads.append((term, {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, gs)}))
 
     total_loss.backward()
-    ctx.collectives.reduce_grads(state.components_opt.params + state.ci_fn_opt.params)
+    ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params) + state.ci_fn_opt.params)
 
     info_c = state.components_opt.step(step)
     info_f = state.ci_fn_opt.step(step)

@@ -22,8 +22,14 @@ from param_decomp_b200.ops.elementwise import split_bf16
 
 
 def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host: dict[str, float], coeff: float,
-                       accumulate_grads: bool = True) -> Tensor:
-    """Returns the (detached) loss `mean_s ||D_s||^2 / ||W_s||^2`; adds `coeff * dLoss` to `.grad`."""
+                       accumulate_grads: bool = True, hi_lo: dict[str, tuple[Tensor, Tensor]] | None = None,
+                       rank: int = 0, world: int = 1) -> Tensor:
+    """Returns the (detached) loss `mean_s ||D_s||^2 / ||W_s||^2`; adds `coeff * dLoss` to `.grad`.
+
+    `hi_lo["V/<group>"] = (hi, lo)`: split-precision working copies published by the sharded
+    optimizer (then no fp32 master is read). With `world > 1` the sites are dealt round-robin to the
+    ranks: each rank does the GEMMs of its own sites only, writes their gradients scaled by `world`
+    (the gradient reduction averages over ranks), and returns its partial loss; the caller sums it."""
     sites = [s for s in stacks.sites if not s.blocked]
     assert len(sites) == len(stacks.sites), "blocked sites use the grouped faithfulness path"
     dev = next(stacks.parameters()).device
@@ -33,14 +39,20 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
     for gname, members in stacks.groups.items():
         key = stacks.param_key(gname)
         pV, pU = stacks.V[key], stacks.U[key]
-        Vh, Vl = split_bf16(pV.detach())
-        Uh, Ul = split_bf16(pU.detach())
+        if hi_lo is not None:
+            (Vh, Vl), (Uh, Ul) = hi_lo["V/" + key], hi_lo["U/" + key]
+        else:
+            Vh, Vl = split_bf16(pV.detach())
+            Uh, Ul = split_bf16(pU.detach())
         if accumulate_grads:
             if pV.grad is None:
                 pV.grad = torch.zeros_like(pV)
             if pU.grad is None:
                 pU.grad = torch.zeros_like(pU)
         for i, s in enumerate(members):
+            if k % world != rank:
+                k += 1
+                continue
             Wb = W[s.name]
             assert Wb.dtype == torch.bfloat16, "the fused faithfulness path expects a bf16 target"
             U_cat = torch.cat([Uh[i], Ul[i], Uh[i]], dim=0)  # [3C, d_out]
@@ -48,9 +60,9 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
             D = torch.empty(s.d_out, s.d_in, device=dev, dtype=torch.bfloat16)
             nv.gemm(U_cat, V_cat, D, a_mn=True, epi=nv.EPI_FAITH, ci=Wb, dci=sumsq[k:k + 1])
             if accumulate_grads:
-                alpha = -2.0 * coeff / (n_sites * w_sq_host[s.name])
+                alpha = -2.0 * coeff * world / (n_sites * w_sq_host[s.name])
                 nv.gemm(D, Uh[i], pV.grad[i], a_mn=True, accumulate=True, alpha=alpha)
                 nv.gemm(Vh[i], D, pU.grad[i], a_mn=True, accumulate=True, alpha=alpha)
             k += 1
     wsq = torch.tensor([w_sq_host[s.name] for s in sites], device=dev, dtype=torch.float32)
-    return (sumsq[:, 0] / wsq).mean()
+    return (sumsq[:, 0] / wsq).sum() / n_sites

@@ -1,0 +1,125 @@
+"""Two-GPU tests of the peer-memory kernels (skipped on a 1-GPU box). Ranks are child processes,
+one per GPU; NVLS is off and the kernels use plain peer loads/stores."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _need_two_gpus():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+
+
+def _opt_worker(rank: int, world: int, port: int, backend: str, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from param_decomp_b200.config.run import AdamWOptimizerConfig
+    from param_decomp_b200.ops import native
+    from param_decomp_b200.parallel.sharded_optim import ShardedFlatAdamW
+
+    torch.manual_seed(0)
+    params = [torch.randn(300, 257, device="cuda"), torch.randn(1000, device="cuda"), torch.randn(64, 64, device="cuda")]
+    cfg = AdamWOptimizerConfig(lr_schedule=1e-2, weight_decay=0.1, grad_clip_norm=0.5)
+    opt = ShardedFlatAdamW(cfg, ["a", "b", "c"], params, total_steps=10, group=dist.group.WORLD, backend=backend,
+                           keep_lo=True)
+    for step in range(3):
+        opt.zero_grad()
+        g = torch.Generator(device="cuda").manual_seed(100 * step + rank)
+        for p in params:
+            p.grad.add_(torch.randn(p.shape, generator=g, device="cuda"))
+        opt.step(step)
+    torch.cuda.synchronize()
+    native.check_status()
+    opt.refresh_full_fp32()
+    out[rank] = ([p.detach().cpu() for p in params], opt.working_view(0).float().cpu(),
+                 opt.working_lo_view(0).float().cpu(), opt.grad_norm())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("backend", ["collective", "fused_p2p"])
+def test_sharded_adamw_two_gpus(backend):
+    _need_two_gpus()
+    from param_decomp_b200.config.run import AdamWOptimizerConfig
+    from param_decomp_b200.core.optim import build_group_optimizer
+
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_opt_worker, args=(world, port, backend, out), nprocs=world, join=True)
+    torch.manual_seed(0)
+    ref = [torch.randn(300, 257, device="cuda"), torch.randn(1000, device="cuda"), torch.randn(64, 64, device="cuda")]
+    cfg = AdamWOptimizerConfig(lr_schedule=1e-2, weight_decay=0.1, grad_clip_norm=0.5)
+    opt = build_group_optimizer(cfg, [("a", ref[0]), ("b", ref[1]), ("c", ref[2])], total_steps=10)
+    for step in range(3):
+        gens = [torch.Generator(device="cuda").manual_seed(100 * step + r) for r in range(world)]
+        grads = [sum(torch.randn(p.shape, generator=g, device="cuda") for g in gens) / world for p in ref]
+        opt.step(step, grads)
+    for r in range(world):
+        params, hi, lo, norm = out[r]
+        for a, b in zip(params, ref):
+            assert torch.allclose(a, b.cpu(), atol=2e-6), backend
+        assert torch.allclose(hi + lo, ref[0].cpu(), atol=1e-4)  # split-precision working copy
+        assert norm == pytest.approx(float(opt.last_grad_norm_t), rel=1e-4)
+
+
+def _barrier_timeout_worker(rank: int, world: int, port: int, out):
+    """Rank 1 never signals: rank 0's bounded wait must run out, report status 4 and return, and the
+    context must stay usable afterwards. (Rank 1 is idle on the host, with no kernel in flight.)"""
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import ctypes as C
+
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from param_decomp_b200.ops import native
+    from param_decomp_b200.parallel.sharded_optim import PdPeerPtrs, _peer_table, symmetric_empty
+
+    flags, ptrs = symmetric_empty(8, torch.int32, torch.device("cuda", rank), dist.group.WORLD)
+    flags.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    lib = native.lib()
+    lib.pd_peer_barrier.argtypes = [C.POINTER(PdPeerPtrs), C.c_int, C.c_int, C.c_uint, C.c_void_p, C.c_double, C.c_void_p]
+    table = _peer_table(ptrs)
+    status = native.status_word()
+    # a barrier both ranks join: completes
+    lib.pd_peer_barrier(C.byref(table), rank, world, 1, status.data_ptr(), 1.0, native.current_stream_ptr())
+    torch.cuda.synchronize()
+    ok_first = int(status.item())
+    dist.barrier()
+    code = 0
+    if rank == 0:  # only rank 0 enters the second barrier
+        lib.pd_peer_barrier(C.byref(table), rank, world, 2, status.data_ptr(), 0.5, native.current_stream_ptr())
+        torch.cuda.synchronize()
+        code = int(status.item())
+        status.zero_()
+        # context still usable
+        assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+    dist.barrier()
+    out[rank] = (ok_first, code)
+    dist.destroy_process_group()
+
+
+def test_peer_barrier_times_out_cleanly():
+    _need_two_gpus()
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_barrier_timeout_worker, args=(world, port, out), nprocs=world, join=True)
+    assert out[0] == (0, 4) and out[1] == (0, 0)

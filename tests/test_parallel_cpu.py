@@ -89,3 +89,55 @@ def test_gloo_collectives_world4():
         assert g == pytest.approx([0.5] * 3)
         assert flag is True and rid == "p-abc"
         assert tp_rank == r % 2 and data_rank == r // 2 and off == 10 * (r // 2)
+
+
+def _sharded_worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from param_decomp_b200.config.run import AdamWOptimizerConfig
+    from param_decomp_b200.parallel.sharded_optim import ShardedFlatAdamW
+
+    torch.manual_seed(0)
+    params = [torch.randn(5, 7), torch.randn(13)]
+    cfg = AdamWOptimizerConfig(lr_schedule=1e-2, weight_decay=0.1, grad_clip_norm=0.5)
+    opt = ShardedFlatAdamW(cfg, ["a", "b"], params, total_steps=10, group=dist.group.WORLD)
+    for step in range(3):
+        opt.zero_grad()
+        g = torch.Generator().manual_seed(100 * step + rank)  # each rank has its own local gradient
+        for p in params:
+            p.grad.add_(torch.randn(p.shape, generator=g))
+        opt.step(step)
+    opt.refresh_full_fp32()
+    out[rank] = ([p.detach().clone() for p in params], opt.working_view(0).float().clone(), opt.grad_norm())
+    dist.destroy_process_group()
+
+
+def test_sharded_adamw_matches_single_process_mean_gradient():
+    from param_decomp_b200.config.run import AdamWOptimizerConfig
+    from param_decomp_b200.core.optim import build_group_optimizer
+
+    world, port = 2, _free_port()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_sharded_worker, args=(world, port, out), nprocs=world, join=True)
+    torch.manual_seed(0)
+    ref = [torch.randn(5, 7), torch.randn(13)]
+    cfg = AdamWOptimizerConfig(lr_schedule=1e-2, weight_decay=0.1, grad_clip_norm=0.5)
+    opt = build_group_optimizer(cfg, [("a", ref[0]), ("b", ref[1])], total_steps=10)
+    for step in range(3):
+        grads = []
+        for p in ref:
+            gs = []
+            for r in range(world):
+                pass
+            grads.append(None)
+        gens = [torch.Generator().manual_seed(100 * step + r) for r in range(world)]
+        grads = [sum(torch.randn(p.shape, generator=g) for g in gens) / world for p in ref]
+        opt.step(step, grads)
+    for r in range(world):
+        params, work0, norm = out[r]
+        for a, b in zip(params, ref):
+            assert torch.allclose(a, b, atol=1e-6)
+        assert torch.allclose(work0, ref[0].to(torch.bfloat16).float(), atol=1e-6)
+    assert out[0][2] == pytest.approx(float(opt.last_grad_norm_t), rel=1e-5)
