@@ -353,9 +353,16 @@ class MoeCSpec(BaseConfig):
 
     kind: Literal["moe"] = "moe"
     layers: LayerSelection
-    cs: dict[Literal["q_proj", "k_proj", "v_proj", "o_proj", "experts_gate", "experts_up", "experts_down"],
+    cs: dict[Literal["q", "k", "v", "o", "experts_gate", "experts_up", "experts_down"],
              PositiveInt] = Field(..., min_length=1)
     initialization: Initialization = "random"
+
+    @field_validator("cs", mode="before")
+    @classmethod
+    def _short_names(cls, v: object) -> object:
+        if isinstance(v, dict):
+            return {(k[:-5] if isinstance(k, str) and k.endswith("_proj") else k): c for k, c in v.items()}
+        return v
 
 
 class ResidualBoundaryTapSelection(BaseConfig):

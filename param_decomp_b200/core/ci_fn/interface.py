@@ -34,6 +34,11 @@ class CI:
     """Fused backend only: per-component mean smooth-L0 activity `[C]`, produced in the same pass
     as `lower` (then `upper` is not materialised)."""
 
+    def mask_inputs(self) -> dict[str, Tensor]:
+        """What the mask samplers consume: dense `[..., C]` for dense sites, the NARROW
+        `[..., k * C_block]` values (slot-major, in routing order) for expert-blocked sites."""
+        return {k: (v.values if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()}
+
     def dense_lower(self) -> dict[str, Tensor]:
         return {k: (v.scatter_dense() if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()}
 

@@ -66,14 +66,58 @@ class SiteMLP(nn.Module):
         return sum(2 * a * b for a, b in zip(self.dims[:-1], self.dims[1:])) * self.n_stack
 
 
+class BlockedSiteMLP(nn.Module):
+    """CI for an expert-blocked site, emitted only for each token's selected experts:
+    `hidden = gelu(x W1 + b1)` shared by all experts, then one head per expert
+    `[E, hidden, C_block]` applied to the tokens routed to it -> `SelectedCI [.., k * C_block]`."""
+
+    def __init__(self, d_in: int, hidden: int, n_blocks: int, c_block: int, generator: torch.Generator | None) -> None:
+        super().__init__()
+        self.n_blocks, self.c_block = n_blocks, c_block
+        self.w1 = nn.Parameter(torch.empty(d_in, hidden))
+        _kaiming_(self.w1, d_in, generator)
+        self.b1 = nn.Parameter(torch.zeros(hidden))
+        self.heads = nn.Parameter(torch.empty(n_blocks, hidden, c_block))
+        _kaiming_(self.heads, hidden, generator)
+        self.head_bias = nn.Parameter(torch.zeros(n_blocks, c_block))
+
+    def forward(self, x: Tensor, sel) -> "SelectedCI":
+        from param_decomp_b200.core.components import SelectedCI
+
+        lead = x.shape[:-1]
+        h = F.gelu(x.reshape(-1, x.shape[-1]).float() @ self.w1 + self.b1)  # [N, hidden]
+        idx = sel.indices.reshape(-1, sel.indices.shape[-1])  # [N, k]
+        N, k = idx.shape
+        out = h.new_zeros(N, k, self.c_block)
+        flat_e = idx.reshape(-1)
+        order = flat_e.argsort(stable=True)
+        counts = torch.bincount(flat_e, minlength=self.n_blocks).tolist()
+        start = 0
+        out_flat = out.view(N * k, self.c_block)
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            jobs = order[start:start + n]
+            out_flat[jobs] = h[jobs // k] @ self.heads[e] + self.head_bias[e]
+            start += n
+        return SelectedCI(out.reshape(*lead, k * self.c_block), sel, self.n_blocks)
+
+
 class LayerwiseMLPCIFn(nn.Module):
-    """One MLP per site, reading that site's own tap. `site_taps[site] = tap key`."""
+    """One MLP per site, reading that site's own tap. `site_taps[site] = tap key`.
+    `blocked[site] = (layer, n_blocks, C_block)` marks expert-blocked sites (narrow emission)."""
 
     def __init__(self, site_shapes: dict[str, tuple[int, int]], site_taps: dict[str, str],
-                 hidden_dims: tuple[int, ...], generator: torch.Generator | None = None) -> None:
+                 hidden_dims: tuple[int, ...], generator: torch.Generator | None = None,
+                 blocked: dict[str, tuple[int, int, int]] | None = None) -> None:
         super().__init__()
         self.site_taps = dict(site_taps)
         self.input_taps = tuple(dict.fromkeys(site_taps.values()))
+        self.blocked = dict(blocked or {})
+        self.blocked_mlps = nn.ModuleDict({
+            s.replace(".", "_"): BlockedSiteMLP(site_shapes[s][0], hidden_dims[0], nb, cb, generator)
+            for s, (_, nb, cb) in self.blocked.items()})
+        site_shapes = {s: v for s, v in site_shapes.items() if s not in self.blocked}
         # group sites by (d_in, C) so each group is one stacked MLP
         self.group_members: dict[str, list[str]] = {}
         for site, (d_in, C) in site_shapes.items():
@@ -93,6 +137,10 @@ class LayerwiseMLPCIFn(nn.Module):
             y = mlp(x if mlp.fused else x.float())
             for s, yi in zip(members, y.unbind(0)):  # one stacked gradient per group in backward
                 out[s] = yi.reshape(*lead, -1)
+        if self.blocked:
+            routing = (context.get("aux") or {}).get("routing", {})
+            for s, (layer, _, _) in self.blocked.items():
+                out[s] = self.blocked_mlps[s.replace(".", "_")](taps[self.site_taps[s]], routing[layer])
         return out
 
     def parameter_census(self) -> dict[str, int]:

@@ -137,7 +137,7 @@ def masked_recon(ctx: StepContext, weights: ComputeWeights, batch: Any, clean: F
                  metrics: dict[str, Tensor] | None = None) -> tuple[Tensor, Tensor]:
     """Returns `(e2e output loss, full term loss incl. auxiliaries)`."""
     keys = term.capture_keys() if with_aux else ()
-    out = ctx.model.masked_forward(weights, batch, masks, capture=keys)
+    out = ctx.model.masked_forward(weights, batch, masks, capture=keys, clean=clean)
     e2e = ctx.model.recon_loss(clean, out)
     full = e2e
     if with_aux and term.auxiliaries:
@@ -341,7 +341,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct or sharded,
                                       working=working)
     ci = run_ci_fn(ctx, state, clean, step)
-    ci_lower = ci.dense_lower()
+    ci_lower = ci.mask_inputs()
 
     for term in obj.persistent_terms():
         ascend_persistent(ctx, state, term, weights, batch, clean, ci_lower, key, step)

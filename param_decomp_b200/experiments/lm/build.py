@@ -54,6 +54,10 @@ def load_target_weights(cfg: X.LMTargetConfig, data_root: Path | None, device) -
     spec = cfg.spec
     dtype = _dtype(cfg.weights_dtype)
     if isinstance(spec, X.RandomInitTarget):
+        if spec.arch.family == "moe":
+            from param_decomp_b200.models.moe import random_init_moe_weights
+
+            return spec.arch, random_init_moe_weights(spec.arch, spec.seed, dtype, device)
         return spec.arch, tf.random_init_weights(spec.arch, spec.seed, dtype, device)
     from param_decomp_b200.models import loaders
 
@@ -64,8 +68,10 @@ def build_ci_fn(cfg: Any, model: Any, seed: int) -> nn.Module:
     g = torch.Generator().manual_seed(seed + 1)
     sites: tuple[SiteSpec, ...] = model.sites
     if isinstance(cfg, X.LMLayerwiseMlpCIFnConfig):
-        return LayerwiseMLPCIFn({s.name: (s.d_in, s.C) for s in sites}, {s.name: model.tap_for_site(s.name) for s in sites},
-                                tuple(cfg.hidden_dims), g)
+        blocked = {s.name: (model.layer_of_site(s.name), s.n_blocks, s.C_block) for s in sites if s.blocked}
+        shapes = {s.name: (model.arch.d_model if s.blocked else s.d_in, s.C) for s in sites}
+        return LayerwiseMLPCIFn(shapes, {s.name: model.tap_for_site(s.name) for s in sites},
+                                tuple(cfg.hidden_dims), g, blocked=blocked)
     from param_decomp_b200.core.ci_fn import resolve
 
     return resolve.build_lm_ci_fn(cfg, model, g)

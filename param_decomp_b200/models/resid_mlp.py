@@ -148,7 +148,7 @@ class ResidMLPDecomposedModel:
         return ForwardResult(output=resid @ p.W_U, taps=taps)
 
     def masked_forward(self, weights: ComputeWeights, batch: Tensor, masks: Masks,
-                       capture: tuple[str, ...] = ()) -> ForwardResult:
+                       capture: tuple[str, ...] = (), clean: ForwardResult | None = None) -> ForwardResult:
         p, act = self.params, _act(self.params.act)
         resid = batch @ p.W_E
 

@@ -145,7 +145,7 @@ class TMSDecomposedModel:
         return ForwardResult(output=out, taps=taps)
 
     def masked_forward(self, weights: ComputeWeights, batch: Tensor, masks: Masks,
-                       capture: tuple[str, ...] = ()) -> ForwardResult:
+                       capture: tuple[str, ...] = (), clean: ForwardResult | None = None) -> ForwardResult:
         h = batch
         for name, W in self._layers():
             if name in masks and name in weights.V:

@@ -44,6 +44,8 @@ ATTN_KINDS = {"q", "k", "v", "o", "q_proj", "k_proj", "v_proj", "o_proj"}
 def site_name(family: str, layer: int, kind: str) -> str:
     if family == "simple_mlp":
         return f"h.{layer}.{'attn' if kind in ATTN_KINDS else 'mlp'}.{kind}"
+    if kind.startswith(("experts_", "shared_")):
+        return f"layers.{layer}.mlp.{kind}"
     return f"layers.{layer}.{'self_attn' if kind in ATTN_KINDS else 'mlp'}.{kind}_proj"
 
 
@@ -127,7 +129,7 @@ class TransformerDecomposedModel:
     def __init__(self, arch: TransformerArchConfig, weights: dict[str, Tensor], site_cs: dict[str, int],
                  backend: str = "eager_torch", attention: str = "flash", n_vocab_chunks: int | None = None,
                  kl_token_chunk: int = 8192) -> None:
-        assert arch.family in ("glu_transformer", "simple_mlp"), arch.family
+        assert arch.family in ("glu_transformer", "simple_mlp", "moe"), arch.family
         self.arch = arch
         self.w = weights
         self.backend = backend
@@ -137,21 +139,26 @@ class TransformerDecomposedModel:
         self.compute_dtype = weights["embed.weight"].dtype
         self.head_dim = arch.head_dim or arch.d_model // arch.n_head
         self.n_kv = arch.n_kv_head or arch.n_head
-        self.kinds = SIMPLE_KINDS if arch.family == "simple_mlp" else GLU_KINDS
+        self.kinds = SIMPLE_KINDS if arch.family == "simple_mlp" else self._family_kinds()
         specs = []
         self._site_layer_kind: dict[str, tuple[int, str]] = {}
         for i in range(arch.n_layer):
             for kind in self.kinds:
                 name = site_name(arch.family, i, kind)
                 if name in site_cs:
-                    W = weights[name + ".weight"]
-                    specs.append(SiteSpec(name, W.shape[1], W.shape[0], site_cs[name], group=kind,
-                                          alignment=alignment_for(arch, kind)))
+                    specs.append(self._site_spec(name, kind, site_cs[name]))
                     self._site_layer_kind[name] = (i, kind)
         unknown = set(site_cs) - set(self._site_layer_kind)
         assert not unknown, f"unknown sites {sorted(unknown)[:4]}..."
         self.sites = tuple(specs)
         self._fused_cache: dict[str, Any] = {}
+
+    def _family_kinds(self) -> tuple[str, ...]:
+        return GLU_KINDS
+
+    def _site_spec(self, name: str, kind: str, C: int) -> SiteSpec:
+        W = self.w[name + ".weight"]
+        return SiteSpec(name, W.shape[1], W.shape[0], C, group=kind, alignment=alignment_for(self.arch, kind))
 
     # -- protocol ---------------------------------------------------------------------------------
     def batch_size(self, batch: LMBatch) -> int:
@@ -225,7 +232,7 @@ class TransformerDecomposedModel:
         return ports.swiglu(gate, up)
 
     def _block(self, i: int, resid: Tensor, cos: Tensor, sin: Tensor, batch: LMBatch, weights, masks,
-               taps: dict[str, Tensor] | None, captures: dict[str, Tensor], want: set[str]) -> Tensor:
+               taps: dict[str, Tensor] | None, captures: dict[str, Tensor], want: set[str], aux: dict) -> Tensor:
         a, fam, eps = self.arch, self.arch.family, self.arch.rms_eps
         B, T, _ = resid.shape
         names = (("q_proj", "k_proj", "v_proj", "o_proj") if fam == "simple_mlp" else ("q", "k", "v", "o"))
@@ -260,7 +267,10 @@ class TransformerDecomposedModel:
         x = self._norm(resid, self.w[f"layers.{i}.mlp_norm.weight"])
         if taps is not None:
             taps[f"mlp_in.{i}"] = x
-        if fam == "simple_mlp":
+        return resid + self._mlp(i, x, lin, taps, weights, masks, aux)
+
+    def _mlp(self, i: int, x: Tensor, lin, taps: dict[str, Tensor] | None, weights, masks, aux: dict) -> Tensor:
+        if self.arch.family == "simple_mlp":
             h = F.gelu(lin(x, "c_fc"))
             down = "down_proj"
         else:
@@ -268,10 +278,12 @@ class TransformerDecomposedModel:
             down = "down"
         if taps is not None:
             taps[f"mlp_hidden.{i}"] = h
-        return resid + lin(h, down)
+        return lin(h, down)
 
-    def _run(self, batch: LMBatch, weights, masks, capture: tuple[str, ...], want_taps: bool) -> ForwardResult:
+    def _run(self, batch: LMBatch, weights, masks, capture: tuple[str, ...], want_taps: bool,
+             aux: dict | None = None) -> ForwardResult:
         a = self.arch
+        aux = {} if aux is None else aux
         want = set(capture)
         tokens = batch.tokens
         B, T = tokens.shape
@@ -285,13 +297,13 @@ class TransformerDecomposedModel:
                 taps[f"resid.{i}"] = resid
             if f"resid.{i}" in want:
                 captures[f"resid.{i}"] = resid
-            resid = self._block(i, resid, cos, sin, batch, weights, masks, taps, captures, want)
+            resid = self._block(i, resid, cos, sin, batch, weights, masks, taps, captures, want, aux)
         if taps is not None:
             taps[f"resid.{a.n_layer}"] = resid
         if f"resid.{a.n_layer}" in want:
             captures[f"resid.{a.n_layer}"] = resid
         final = self._norm(resid, self.w["final_norm.weight"])
-        return ForwardResult(output=final, taps=taps or {}, captures=captures)
+        return ForwardResult(output=final, taps=taps or {}, captures=captures, aux=aux)
 
     def clean_forward(self, batch: LMBatch, capture: tuple[str, ...] = ()) -> ForwardResult:
         out = self._run(batch, None, None, capture, want_taps=True)
@@ -301,7 +313,7 @@ class TransformerDecomposedModel:
         return out
 
     def masked_forward(self, weights: ComputeWeights, batch: LMBatch, masks: Masks,
-                       capture: tuple[str, ...] = ()) -> ForwardResult:
+                       capture: tuple[str, ...] = (), clean: ForwardResult | None = None) -> ForwardResult:
         return self._run(batch, weights, masks, capture, want_taps=False)
 
     def logits(self, final_hidden: Tensor) -> Tensor:
