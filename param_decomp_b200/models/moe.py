@@ -156,20 +156,57 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         if self.ep is not None:
             y_jobs = self.ep.run_experts(self, i, xt, expert_of_job, token_of_job, slot_of_job, weights, masks)
         else:
-            order = expert_of_job.argsort(stable=True)
-            counts = torch.bincount(expert_of_job, minlength=a.n_experts).tolist()
-            bounds = [0]
-            for n in counts:
-                bounds.append(bounds[-1] + n)
+            order, bounds = expert_of_job, [0]
+            if not self._fused(xt):
+                order = expert_of_job.argsort(stable=True)
+                for n in torch.bincount(expert_of_job, minlength=a.n_experts).tolist():
+                    bounds.append(bounds[-1] + n)
             y_jobs = self.expert_jobs(i, xt[token_of_job], expert_of_job, order, bounds, weights, masks, token_of_job,
                                       slot_of_job)
         w = sel.weights.reshape(B * T, k, 1).to(y_jobs.dtype)
         return (y_jobs.reshape(B * T, k, d) * w).sum(1).reshape(B, T, d)
 
+    def _grouped_site(self, name: str, xs: Tensor, layout, weights, masks, token_of_job: Tensor,
+                      slot_of_job: Tensor) -> Tensor:
+        """Fused path of one blocked site on padded sorted jobs (`ops/grouped.py`)."""
+        from param_decomp_b200.ops import grouped
+
+        W = self.w[name + ".weight"]
+        if weights is None or masks is None or name not in masks or name not in weights.V:
+            return grouped.grouped_linear(xs, W, layout)
+        spec = next(s for s in self.sites if s.name == name)
+        sm = masks[name].materialize()
+        c = spec.C_block
+
+        def per_job(t: Tensor | None, width: int) -> Tensor | None:
+            if t is None:
+                return None
+            flat = t.reshape(-1, t.shape[-1]) if width else t.reshape(-1)
+            vals = flat.reshape(flat.shape[0], -1, c)[token_of_job, slot_of_job] if width else flat[token_of_job]
+            out = vals.new_zeros(layout.n_rows, *vals.shape[1:])
+            return out.index_copy(0, layout.pos, vals)
+
+        m = per_job(sm.mask, c)
+        d = per_job(None if sm.delta is None else sm.delta.reshape(-1).float(), 0)
+        r = per_job(None if sm.route is None else sm.route.reshape(-1), 0)
+        V, U = weights.site(name)
+        return grouped.grouped_site(xs, V, U, W, layout, m, d, r, weights.grad_V.get(name), weights.grad_U.get(name),
+                                    need_wgrad=weights.direct_grads)
+
     def expert_jobs(self, i: int, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int], weights,
                     masks, token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
         """gate/up/down of every job; `expert_of_job` indexes THIS rank's expert bank."""
         n = lambda kind: tf.site_name("moe", i, kind)  # noqa: E731
+        if self._fused(x_jobs):
+            from param_decomp_b200.ops.grouped import JobLayout
+
+            layout = JobLayout.build(expert_of_job, self.w[n("experts_gate") + ".weight"].shape[0])
+            xs = layout.scatter_rows(x_jobs)
+            gate = self._grouped_site(n("experts_gate"), xs, layout, weights, masks, token_of_job, slot_of_job)
+            up = self._grouped_site(n("experts_up"), xs, layout, weights, masks, token_of_job, slot_of_job)
+            h = self._swiglu(gate, up)
+            return layout.gather_rows(self._grouped_site(n("experts_down"), h, layout, weights, masks, token_of_job,
+                                                         slot_of_job))
         args = (expert_of_job, order, bounds, weights, masks, token_of_job, slot_of_job)
         gate = self._expert_site(n("experts_gate"), x_jobs, *args)
         up = self._expert_site(n("experts_up"), x_jobs, *args)
@@ -190,6 +227,18 @@ def build_moe_model(arch: TransformerArchConfig, weights: dict[str, Tensor], sit
 
     layers = select_layers(sites_cfg.layers, arch.n_layer)
     kinds = [k for k in ("q", "k", "v", "o", *EXPERT_KINDS) if k in sites_cfg.cs]
-    site_cs = {tf.site_name("moe", i, k): sites_cfg.cs[k] for i in layers for k in kinds}
+
+    def local_c(kind: str) -> int:
+        C = sites_cfg.cs[kind]
+        if ep is None or kind not in EXPERT_KINDS:
+            return C
+        assert C % arch.n_experts == 0, f"{kind}: C={C} must be a multiple of n_experts={arch.n_experts}"
+        return C // arch.n_experts * ep.e_loc  # this rank's expert blocks only
+
+    site_cs = {tf.site_name("moe", i, k): local_c(k) for i in layers for k in kinds}
+    if ep is not None:
+        from param_decomp_b200.parallel.ep import shard_expert_weights
+
+        weights = shard_expert_weights(weights, arch.n_experts, ep.rank, ep.world)
     return MoEDecomposedModel(arch, weights, site_cs, backend=backend, attention=target_cfg.attention_implementation,
                               ep=ep)

@@ -336,8 +336,8 @@ __global__ void ci_squash_activity_kernel(const __nv_bfloat16* __restrict__ pre,
         lo[k] = __floats2bfloat162_rn(lx, ly);
         const float ux = f.x > 1.f ? 1.f + alpha * (f.x - 1.f) : lx;
         const float uy = f.y > 1.f ? 1.f + alpha * (f.y - 1.f) : ly;
-        acc[2 * k] += norm * ux * ux / (ux * ux + gamma2);
-        acc[2 * k + 1] += norm * uy * uy / (uy * uy + gamma2);
+        acc[2 * k] += norm * __fdividef(ux * ux, ux * ux + gamma2);
+        acc[2 * k + 1] += norm * __fdividef(uy * uy, uy * uy + gamma2);
       }
       *reinterpret_cast<uint4*>(lower + r * C + col) = *reinterpret_cast<uint4*>(lo);
     }
@@ -390,7 +390,7 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
         else if (xv > 0.f) { u = xv; du = 1.f; lg = gg[e]; }
         else { u = 0.f; du = 0.f; lg = gg[e] < 0.f ? alpha * gg[e] : 0.f; }
         const float den = u * u + gamma2;
-        const float dpsi = norm * 2.f * u * gamma2 / (den * den);
+        const float dpsi = __fdividef(norm * 2.f * u * gamma2, den * den);
         out[e] = lg + dc[2 * k + e] * dpsi * du;
       }
       o[k] = __floats2bfloat162_rn(out[0], out[1]);

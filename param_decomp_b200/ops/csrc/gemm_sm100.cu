@@ -73,6 +73,10 @@ struct GemmArgs {
   unsigned int row_offset;
   int mask_mode;
   int* status;
+  // grouped (ragged) products: see PdGemmCall
+  const int* bgroup_of_mblock;
+  const int* kblock_range;
+  int a_bcast, b_bcast;
 };
 
 template <int BN, int NOUT>
@@ -222,6 +226,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     nb = in_group / gsz;
   };
 
+  // K-block range of a tile: a split of the whole K extent, or (ragged weight-gradient products) the
+  // batch's own range of the shared K axis; an empty range yields an all-zero output tile.
+  auto tile_krange = [&](int b, int sp, int& lo, int& hi) {
+    if (args.kblock_range) {
+      lo = args.kblock_range[2 * b];
+      hi = args.kblock_range[2 * b + 1];
+    } else {
+      lo = sp * kb_per_split;
+      hi = min(kb_total, lo + kb_per_split);
+    }
+  };
+
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -231,8 +247,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
-        const int kb_lo = sp * kb_per_split;
-        const int kb_hi = min(kb_total, kb_lo + kb_per_split);
+        int kb_lo, kb_hi;
+        tile_krange(b, sp, kb_lo, kb_hi);
+        const int bb = args.bgroup_of_mblock ? args.bgroup_of_mblock[mb] : b;
+        if (bb < 0) continue;  // padding row block of a grouped product: no tile
+        const int ab = args.a_bcast ? 0 : b;
+        const int bbatch = args.b_bcast ? 0 : bb;
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
             if (args.status) atomicCAS(args.status, 0, kTimeoutProducer);
@@ -250,18 +270,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           const uint32_t sa = smem_a + stage * kStageBytesA;
           const uint32_t sb = smem_b + stage * kStageBytesB;
           if (!a_mn) {
-            tma_load_3d(sa, ta, full, k0, mb * BM, b);
+            tma_load_3d(sa, ta, full, k0, mb * BM, ab);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i)
-              tma_load_3d(sa + i * (BK * 128), ta, full, mb * BM + 64 * i, k0, b);
+              tma_load_3d(sa + i * (BK * 128), ta, full, mb * BM + 64 * i, k0, ab);
           }
           if (!b_mn) {
-            tma_load_3d(sb, tb, full, k0, nb * BN, b);
+            tma_load_3d(sb, tb, full, k0, nb * BN, bbatch);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i)
-              tma_load_3d(sb + i * (BK * 128), tb, full, nb * BN + 64 * i, k0, b);
+              tma_load_3d(sb + i * (BK * 128), tb, full, nb * BN + 64 * i, k0, bbatch);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -281,8 +301,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
-        const int kb_lo = sp * kb_per_split;
-        const int kb_hi = min(kb_total, kb_lo + kb_per_split);
+        int kb_lo, kb_hi;
+        tile_krange(b, sp, kb_lo, kb_hi);
+        if (args.bgroup_of_mblock && args.bgroup_of_mblock[mb] < 0) continue;
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) {
           if (args.status) atomicCAS(args.status, 0, kTimeoutMma);
           break;
@@ -329,6 +350,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
   } else {
     // ------------------------------ epilogue ------------------------------
+    // Work unit = a 32-column half of an output box. Global operands of the mask epilogues
+    // (ci / W rows, and H rows in the backward) are requested one unit ahead, across box and tile
+    // boundaries, so their latency hides behind the math of the previous unit.
     const int ew = warp - 2;   // 0..7
     const int q = warp & 3;    // TMEM lane quarter this warp may read
     const int grp = ew >> 2;   // the two warps of a quarter take alternate boxes
@@ -340,11 +364,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const bool out32 = (EPI == EPI_PLAIN) && args.out_fp32;
     const int box_cols = out32 ? 32 : 64;
     const int nboxes = BN / box_cols;
+    const int halves = out32 ? 1 : 2;
     const bool plain_fast = (EPI == EPI_PLAIN) && args.bias == nullptr && args.act == ACT_NONE &&
                             args.alpha == 1.0f;
-    for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    constexpr bool kWantH = (EPI == EPI_MASK_BWD);
+    const bool want_h = kWantH && args.dci != nullptr;
+
+    auto tile_is_real = [&](long long t) {
+      if (!args.bgroup_of_mblock) return true;
+      int b2, mb2, nb2, sp2;
+      decode(t, b2, mb2, nb2, sp2);
+      return args.bgroup_of_mblock[mb2] >= 0;
+    };
+    auto next_real_tile = [&](long long t) {
+      while (t < num_tiles && !tile_is_real(t)) t += gridDim.x;
+      return t;
+    };
+    uint4 pre_ci[4], pre_h[4];
+    // Request the operands of unit (t, j, half); silently does nothing past the end.
+    auto issue_prefetch = [&](long long t, int j, int half) {
+      if constexpr (EPI != EPI_PLAIN) {
+        if (t >= num_tiles) return;
+        int b2, mb2, nb2, sp2;
+        decode(t, b2, mb2, nb2, sp2);
+        const int prow = mb2 * BM + q * 32 + lane;
+        const int pcol = nb2 * BN + j * box_cols + 32 * half;
+        const bool ok_row = prow < args.M;
+        const __nv_bfloat16* ci_row = args.ci + static_cast<long long>(prow) * args.ld_ci + pcol;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          pre_ci[g] = (ok_row && pcol + 8 * g < args.N) ? __ldg(reinterpret_cast<const uint4*>(ci_row + 8 * g))
+                                                        : make_uint4(0u, 0u, 0u, 0u);
+        if (want_h) {
+          const __nv_bfloat16* h_row = args.H + static_cast<long long>(prow) * args.ld_h + pcol;
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            pre_h[g] = (ok_row && pcol + 8 * g < args.N) ? __ldg(reinterpret_cast<const uint4*>(h_row + 8 * g))
+                                                         : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    };
+    // First unit this warp owns at or after tile t (a warp may own no column of a narrow tail tile).
+    auto first_unit_from = [&](long long t, long long& t_out, int& j_out) {
+      t = next_real_tile(t);
+      while (t < num_tiles) {
+        int b2, mb2, nb2, sp2;
+        decode(t, b2, mb2, nb2, sp2);
+        if (nb2 * BN + grp * box_cols < args.N) break;
+        t = next_real_tile(t + gridDim.x);
+      }
+      t_out = t;
+      j_out = grp;
+    };
+    {
+      long long tp;
+      int jp;
+      first_unit_from(blockIdx.x, tp, jp);
+      issue_prefetch(tp, jp, 0);
+    }
+
+    for (long long t = next_real_tile(blockIdx.x); t < num_tiles; t = next_real_tile(t + gridDim.x)) {
       int b, mb, nb, sp;
       decode(t, b, mb, nb, sp);
+      int kb_lo_e, kb_hi_e;
+      tile_krange(b, sp, kb_lo_e, kb_hi_e);
+      const bool empty_k = kb_hi_e <= kb_lo_e;
       const int row = mb * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t tmem_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -358,46 +442,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       bool have_acc = false;
       bool failed = false;
 #pragma unroll 1
-      for (int j = grp; j < nboxes; j += 2) {
+      for (int j = grp; j < nboxes && !failed; j += 2) {
         const int col0 = nb * BN + j * box_cols;
         if (col0 >= args.N) break;  // uniform across the warp
-        // Global operands of the mask epilogues are requested before the accumulator wait so their
-        // latency hides behind the main loop of this tile.
-        uint4 ciq[8];
-        if constexpr (EPI != EPI_PLAIN) {
-          const __nv_bfloat16* ci_row = args.ci + static_cast<long long>(row) * args.ld_ci + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (row_ok && col0 + 8 * g < args.N)
-              ciq[g] = __ldg(reinterpret_cast<const uint4*>(ci_row + 8 * g));
-            else
-              ciq[g] = make_uint4(0u, 0u, 0u, 0u);
-          }
-        }
-        if (!have_acc) {
-          if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
-            if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
-            failed = true;
-            break;
-          }
-          tc_fence_after();
-          have_acc = true;
-        }
-        uint32_t r[2][32];
-        tmem_ld_32x32(tmem_row + j * box_cols, r[0]);
-        if (!out32) tmem_ld_32x32(tmem_row + j * box_cols + 32, r[1]);
-        tmem_ld_wait();
-        // The staging boxes were handed to TMA one box ago: make sure they have been read.
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
-
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if (half == 1 && out32) break;
+#pragma unroll 1
+        for (int half = 0; half < halves; ++half) {
           const int c0 = col0 + 32 * half;
+          if (c0 >= args.N) break;
+          uint4 ciq[4], hq[4];
+          if constexpr (EPI != EPI_PLAIN) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) ciq[g] = pre_ci[g];
+            if constexpr (kWantH) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) hq[g] = pre_h[g];
+            }
+            // the unit after this one: other half, next box of this tile, or first unit of a later tile
+            if (half + 1 < halves && c0 + 32 < args.N) {
+              issue_prefetch(t, j, half + 1);
+            } else if (j + 2 < nboxes && nb * BN + (j + 2) * box_cols < args.N) {
+              issue_prefetch(t, j + 2, 0);
+            } else {
+              long long tn;
+              int jn;
+              first_unit_from(t + gridDim.x, tn, jn);
+              issue_prefetch(tn, jn, 0);
+            }
+          }
+          if (!have_acc) {
+            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+              if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+              failed = true;
+              break;
+            }
+            tc_fence_after();
+            have_acc = true;
+          }
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_row + j * box_cols + 32 * half, r);
+          tmem_ld_wait();
+          if (half == 0) {
+            // The staging boxes were handed to TMA one box ago: make sure they have been read.
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+          }
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[half][i]);
+          for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.0f : __uint_as_float(r[i]);
+
           if constexpr (EPI == EPI_PLAIN) {
             if (!plain_fast) {
               const float* bias = args.bias ? args.bias + b * args.bias_bs : nullptr;
@@ -426,7 +518,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               float rf[8];
-              unpack8(ciq[4 * half + g], rf);
+              unpack8(ciq[g], rf);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float dlt = rf[i] - v[8 * g + i];
@@ -436,11 +528,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             }
             stage_bf16_half(box0, lane, half, v);
           } else {
-            float coef[32], dmdci[32];
+            if constexpr (EPI == EPI_MASK_FWD) {
+              if (NOUT == 2 && args.has_out1) stage_bf16_half(box1, lane, half, v);
+            }
+            // eight columns at a time: mask, its derivative, products; nothing wider stays live
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              float cf[8];
-              unpack8(ciq[4 * half + g], cf);
+              float cf[8], coef[8], dmdci[8];
+              unpack8(ciq[g], cf);
               if (args.mask_mode == 0) {
                 float u[8];
                 philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(row) + args.row_offset,
@@ -448,67 +543,55 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   const float om = 1.0f - u[i];
-                  coef[8 * g + i] = rs * (fmaf(cf[i], om, u[i]) - delta);  // ci + (1-ci) u - d
-                  dmdci[8 * g + i] = rs * om;
+                  coef[i] = rs * (fmaf(cf[i], om, u[i]) - delta);  // ci + (1-ci) u - d
+                  dmdci[i] = rs * om;
                 }
               } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                  coef[8 * g + i] = rs * (cf[i] - delta);
-                  dmdci[8 * g + i] = rs;
+                  coef[i] = rs * (cf[i] - delta);
+                  dmdci[i] = rs;
                 }
               }
-            }
-            if constexpr (EPI == EPI_MASK_FWD) {
-              if (NOUT == 2 && args.has_out1) stage_bf16_half(box1, lane, half, v);
+              if constexpr (EPI == EPI_MASK_BWD) {
+                if (want_h && row_ok && c0 + 8 * g < args.N) {
+                  float hf[8], tt[8];
+                  unpack8(hq[g], hf);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= coef[i];
-              stage_bf16_half(box0, lane, half, v);
-            } else {
-              if (args.dci != nullptr && row_ok) {
-                const __nv_bfloat16* h_row = args.H + static_cast<long long>(row) * args.ld_h + c0;
-                float* d_row = args.dci + static_cast<long long>(row) * args.ld_dci + c0;
+                  for (int i = 0; i < 8; ++i) tt[i] = v[8 * g + i] * hf[i] * dmdci[i];
+                  if (args.dci_bf16) {
+                    __nv_bfloat16* dstb = reinterpret_cast<__nv_bfloat16*>(args.dci) +
+                                          static_cast<long long>(row) * args.ld_dci + c0 + 8 * g;
+                    if (args.dci_accumulate) {
+                      float old8[8];
+                      unpack8(*reinterpret_cast<const uint4*>(dstb), old8);
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                  if (c0 + 8 * g < args.N) {
-                    float hf[8];
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(h_row + 8 * g)), hf);
-                    float t[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) t[i] = v[8 * g + i] * hf[i] * dmdci[8 * g + i];
-                    if (args.dci_bf16) {
-                      __nv_bfloat16* dstb = reinterpret_cast<__nv_bfloat16*>(args.dci) +
-                                            static_cast<long long>(row) * args.ld_dci + c0 + 8 * g;
-                      if (args.dci_accumulate) {
-                        float old8[8];
-                        unpack8(*reinterpret_cast<const uint4*>(dstb), old8);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) t[i] += old8[i];
-                      }
-                      uint4 pk;
-                      pk.x = pack_bf16(t[0], t[1]); pk.y = pack_bf16(t[2], t[3]);
-                      pk.z = pack_bf16(t[4], t[5]); pk.w = pack_bf16(t[6], t[7]);
-                      *reinterpret_cast<uint4*>(dstb) = pk;
-                    } else {
-                      float* dst = d_row + 8 * g;
-                      float4 o0 = make_float4(t[0], t[1], t[2], t[3]), o1 = make_float4(t[4], t[5], t[6], t[7]);
-                      if (args.dci_accumulate) {
-                        const float4 p0 = *reinterpret_cast<float4*>(dst), p1 = *reinterpret_cast<float4*>(dst + 4);
-                        o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
-                        o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
-                      }
-                      *reinterpret_cast<float4*>(dst) = o0;
-                      *reinterpret_cast<float4*>(dst + 4) = o1;
+                      for (int i = 0; i < 8; ++i) tt[i] += old8[i];
                     }
+                    uint4 pk;
+                    pk.x = pack_bf16(tt[0], tt[1]); pk.y = pack_bf16(tt[2], tt[3]);
+                    pk.z = pack_bf16(tt[4], tt[5]); pk.w = pack_bf16(tt[6], tt[7]);
+                    *reinterpret_cast<uint4*>(dstb) = pk;
+                  } else {
+                    float* dst = args.dci + static_cast<long long>(row) * args.ld_dci + c0 + 8 * g;
+                    float4 o0 = make_float4(tt[0], tt[1], tt[2], tt[3]), o1 = make_float4(tt[4], tt[5], tt[6], tt[7]);
+                    if (args.dci_accumulate) {
+                      const float4 p0 = *reinterpret_cast<float4*>(dst), p1 = *reinterpret_cast<float4*>(dst + 4);
+                      o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
+                      o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+                    }
+                    *reinterpret_cast<float4*>(dst) = o0;
+                    *reinterpret_cast<float4*>(dst + 4) = o1;
                   }
                 }
               }
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= coef[i];
-              stage_bf16_half(box0, lane, half, v);
+              for (int i = 0; i < 8; ++i) v[8 * g + i] *= coef[i];
             }
+            stage_bf16_half(box0, lane, half, v);
           }
         }
+        if (failed) break;
 
         fence_proxy_async_smem();
         __syncwarp();
@@ -527,7 +610,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         }
       }
       if (failed) break;
-      if (!have_acc) {  // no box of this tile fell to this warp: still consume the phase
+      if (!have_acc) {  // no column of this tile fell to this warp: still consume the phase
         if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
           if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
           break;
@@ -645,6 +728,12 @@ struct PdGemmCall {
   // control
   int split_k; int bn; int max_ctas;
   int* status;
+  // Grouped products. bgroup_of_mblock[mb] (device, one int per 128-row block of the output):
+  // batch index of the B operand for that row block (A and out are one ragged [rows, *] matrix whose
+  // rows are sorted by group and padded to 128 per group); -1 = padding block, skipped.
+  // kblock_range[2*b], [2*b+1] (device): 64-wide K-block range of batch b on a K axis shared by all
+  // batches (ragged weight gradients: A/B are broadcast, a_bcast/b_bcast = 1).
+  const int* bgroup_of_mblock; const int* kblock_range; int a_bcast; int b_bcast; int b_groups;
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -673,6 +762,8 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate; a.dci_bf16 = c->dci_bf16;
   a.seed = c->seed; a.stream = c->rng_stream; a.row_offset = c->rng_row_offset; a.mask_mode = c->mask_mode;
   a.status = c->status;
+  a.bgroup_of_mblock = c->bgroup_of_mblock; a.kblock_range = c->kblock_range;
+  a.a_bcast = c->a_bcast; a.b_bcast = c->b_bcast;
   if (c->epi == EPI_FAITH) {
     if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15) || c->N % 8 != 0)
       return kBadArgument;
@@ -690,12 +781,14 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   CUtensorMap ta0, tb0, ta1, tb1, to0, to1;
   int rc;
   OperandDesc A0{c->A0, c->lda0, c->bsa0, c->a_mn0}, B0{c->B0, c->ldb0, c->bsb0, c->b_mn0};
-  if ((rc = encode_operand(&ta0, A0, c->M, c->K0, c->batch, BM))) return 1000 + rc;
-  if ((rc = encode_operand(&tb0, B0, c->N, c->K0, c->batch, bn))) return 2000 + rc;
+  const int a_batch = c->a_bcast ? 1 : c->batch;
+  const int b_batch = c->b_bcast ? 1 : (c->bgroup_of_mblock ? c->b_groups : c->batch);
+  if ((rc = encode_operand(&ta0, A0, c->M, c->K0, a_batch, BM))) return 1000 + rc;
+  if ((rc = encode_operand(&tb0, B0, c->N, c->K0, b_batch, bn))) return 2000 + rc;
   if (c->K1 > 0) {
     OperandDesc A1{c->A1, c->lda1, c->bsa1, c->a_mn1}, B1{c->B1, c->ldb1, c->bsb1, c->b_mn1};
-    if ((rc = encode_operand(&ta1, A1, c->M, c->K1, c->batch, BM))) return 3000 + rc;
-    if ((rc = encode_operand(&tb1, B1, c->N, c->K1, c->batch, bn))) return 4000 + rc;
+    if ((rc = encode_operand(&ta1, A1, c->M, c->K1, a_batch, BM))) return 3000 + rc;
+    if ((rc = encode_operand(&tb1, B1, c->N, c->K1, b_batch, bn))) return 4000 + rc;
   } else {
     ta1 = ta0;
     tb1 = tb0;

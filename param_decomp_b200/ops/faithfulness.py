@@ -35,6 +35,7 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
     dev = next(stacks.parameters()).device
     sumsq = torch.zeros(len(sites), 8, device=dev, dtype=torch.float32)
     n_sites = len(sites)
+    row_of = {s.name: i for i, s in enumerate(sites)}  # sumsq rows follow `sites`, not the group walk
     k = 0
     for gname, members in stacks.groups.items():
         key = stacks.param_key(gname)
@@ -58,7 +59,8 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
             U_cat = torch.cat([Uh[i], Ul[i], Uh[i]], dim=0)  # [3C, d_out]
             V_cat = torch.cat([Vh[i], Vh[i], Vl[i]], dim=1)  # [d_in, 3C]
             D = torch.empty(s.d_out, s.d_in, device=dev, dtype=torch.bfloat16)
-            nv.gemm(U_cat, V_cat, D, a_mn=True, epi=nv.EPI_FAITH, ci=Wb, dci=sumsq[k:k + 1])
+            r = row_of[s.name]
+            nv.gemm(U_cat, V_cat, D, a_mn=True, epi=nv.EPI_FAITH, ci=Wb, dci=sumsq[r:r + 1])
             if accumulate_grads:
                 alpha = -2.0 * coeff * world / (n_sites * w_sq_host[s.name])
                 nv.gemm(D, Uh[i], pV.grad[i], a_mn=True, accumulate=True, alpha=alpha)

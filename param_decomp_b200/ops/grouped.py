@@ -1,0 +1,142 @@
+"""Grouped (per-expert) decomposed sites on the tcgen05 engine.
+
+Jobs (token, slot) are sorted by expert and each expert's run is padded to a multiple of 128 rows,
+so every 128-row block of the job matrix belongs to exactly one expert. The GEMM kernel then takes a
+per-row-block map to pick the expert's weight matrix (forward and input gradients), and per-expert
+K ranges over the shared job axis for the weight gradients (`dW[e] = sum_{j in e} lhs_j^T dout_j`);
+experts with no jobs produce all-zero gradients without touching the tensor core.
+
+This replaces the reference's ragged-dot kernels: tokamax `ragged_dot` for forward / dlhs and the
+Pallas-Triton transposed grouped matmul for the weight gradient
+(param_decomp/routed/experts.py:209-323), with the mask epilogues of the dense site kernel fused in.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from param_decomp_b200.ops import native as nv
+
+PAD = 128
+
+
+@dataclass
+class JobLayout:
+    """Sorted-and-padded job order. `pos[j]` = row of job `j` in the padded matrix."""
+
+    pos: Tensor  # [J] int64
+    n_rows: int  # padded row count (multiple of 128)
+    bgroup: Tensor  # [n_rows / 128] int32: expert of each row block, -1 for unused tail blocks
+    krange: Tensor  # [E, 2] int32: 64-row K-block range of each expert
+    counts: Tensor  # [E] int64
+
+    @classmethod
+    def build(cls, expert_of_job: Tensor, n_experts: int) -> "JobLayout":
+        J = expert_of_job.numel()
+        counts = torch.bincount(expert_of_job, minlength=n_experts)
+        padded = (counts + PAD - 1) // PAD * PAD
+        starts = torch.cumsum(padded, 0) - padded
+        order = expert_of_job.argsort(stable=True)
+        sorted_e = expert_of_job[order]
+        first = torch.cumsum(counts, 0) - counts
+        rank_in_group = torch.arange(J, device=expert_of_job.device) - first[sorted_e]
+        pos = torch.empty(J, dtype=torch.int64, device=expert_of_job.device)
+        pos[order] = starts[sorted_e] + rank_in_group
+        # static upper bound on rows so shapes do not depend on the routing (no host sync)
+        n_rows = (J + n_experts * (PAD - 1) + PAD - 1) // PAD * PAD
+        blocks = torch.arange(n_rows // PAD, device=pos.device) * PAD
+        ends = starts + padded
+        owner = torch.searchsorted(ends, blocks, right=True)
+        valid = (owner < n_experts) & (blocks < ends[-1])
+        bgroup = torch.where(valid, owner, torch.full_like(owner, -1)).to(torch.int32)
+        krange = torch.stack([starts // 64, (starts + padded) // 64], dim=1).to(torch.int32).contiguous()
+        return cls(pos, n_rows, bgroup, krange, counts)
+
+    def scatter_rows(self, x_jobs: Tensor) -> Tensor:
+        out = x_jobs.new_zeros(self.n_rows, x_jobs.shape[-1])
+        out.index_copy_(0, self.pos, x_jobs)
+        return out
+
+    def gather_rows(self, padded: Tensor) -> Tensor:
+        return padded[self.pos]
+
+
+class _GroupedSite(torch.autograd.Function):
+    """Blocked site on padded sorted jobs. `x [R, d_in]`, `V [E, d_in, c]`, `U [E, c, d_out]`,
+    `W [E, d_out, d_in]`, `mask [R, c]` (materialised, may require grad), `delta/d_eff/rowscale [R]`."""
+
+    @staticmethod
+    def forward(ctx, x, mask, delta, V, U, W, gV, gU, layout: JobLayout, rowscale, d_eff, need_wgrad: bool):  # type: ignore[override]
+        R = x.shape[0]
+        E, _, c = V.shape
+        d_out = U.shape[-1]
+        A = torch.empty(R, c, device=x.device, dtype=torch.bfloat16)
+        need_H = mask is not None and mask.requires_grad
+        H = torch.empty_like(A) if need_H else None
+        ci = mask if mask is not None else torch.ones(1, c, device=x.device, dtype=torch.bfloat16).expand(R, c)
+        nv.gemm(x, V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci, delta=delta, rowscale=rowscale, mask_mode=1,
+                bgroup_of_mblock=layout.bgroup)
+        y = torch.empty(R, d_out, device=x.device, dtype=torch.bfloat16)
+        if d_eff is not None:
+            xd = x * d_eff.to(torch.bfloat16)[:, None]
+            nv.gemm(A, U, y, b_mn=True, a1=xd, b1=W, bgroup_of_mblock=layout.bgroup)
+        else:
+            nv.gemm(A, U, y, b_mn=True, bgroup_of_mblock=layout.bgroup)
+        ctx.save_for_backward(x, mask, delta, rowscale, d_eff, A, H, V, U, W)
+        ctx.layout, ctx.sinks, ctx.need_wgrad = layout, (gV, gU), need_wgrad
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x, mask, delta, rowscale, d_eff, A, H, V, U, W = ctx.saved_tensors
+        layout: JobLayout = ctx.layout
+        gV, gU = ctx.sinks
+        R, d_in = x.shape
+        E, _, c = V.shape
+        dy = dy.contiguous()
+        dH = torch.empty(R, c, device=x.device, dtype=torch.bfloat16)
+        dm = torch.empty(R, c, device=x.device, dtype=torch.bfloat16) if H is not None else None
+        ci = mask if mask is not None else torch.ones(1, c, device=x.device, dtype=torch.bfloat16).expand(R, c)
+        nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, delta=delta, rowscale=rowscale, dci=dm, mask_mode=1,
+                bgroup_of_mblock=layout.bgroup)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(R, d_in, device=x.device, dtype=torch.bfloat16)
+            if d_eff is not None:
+                dyd = dy * d_eff.to(torch.bfloat16)[:, None]
+                nv.gemm(dH, V, dx, a1=dyd, b1=W, b1_mn=True, bgroup_of_mblock=layout.bgroup)
+            else:
+                nv.gemm(dH, V, dx, bgroup_of_mblock=layout.bgroup)
+        if ctx.need_wgrad:
+            # dV[e] += x_e^T dH_e ; dU[e] += A_e^T dy_e  (ragged K ranges over the job axis)
+            nv.gemm(x, dH, gV, a_mn=True, b_mn=True, accumulate=True, kblock_range=layout.krange, a_bcast=True,
+                    b_bcast=True)
+            nv.gemm(A, dy, gU, a_mn=True, b_mn=True, accumulate=True, kblock_range=layout.krange, a_bcast=True,
+                    b_bcast=True)
+        dmask = dm if (dm is not None and ctx.needs_input_grad[1]) else None
+        return dx, dmask, None, None, None, None, None, None, None, None, None, None
+
+
+def grouped_site(x: Tensor, V: Tensor, U: Tensor, W: Tensor | None, layout: JobLayout, mask: Tensor | None,
+                 delta: Tensor | None, route: Tensor | None, grad_V: Tensor | None, grad_U: Tensor | None,
+                 need_wgrad: bool) -> Tensor:
+    """All arguments already in padded sorted-job order (`layout.scatter_rows`)."""
+    rowscale = d_eff = None
+    if route is not None:
+        rowscale = route.float()
+        d_eff = (rowscale * delta + (1 - rowscale)) if delta is not None else (1 - rowscale)
+    elif delta is not None:
+        d_eff = delta
+    if mask is not None and mask.dtype != torch.bfloat16:
+        mask = mask.to(torch.bfloat16)
+    return _GroupedSite.apply(x.contiguous(), mask, delta, V, U, W, grad_V, grad_U, layout, rowscale, d_eff, need_wgrad)
+
+
+def grouped_linear(x: Tensor, W: Tensor, layout: JobLayout) -> Tensor:
+    """Frozen expert bank `y_j = x_j W[e(j)]^T` (clean forward)."""
+    y = torch.empty(x.shape[0], W.shape[1], device=x.device, dtype=torch.bfloat16)
+    nv.gemm(x.contiguous(), W, y, bgroup_of_mblock=layout.bgroup)
+    return y

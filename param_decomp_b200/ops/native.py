@@ -43,6 +43,8 @@ class PdGemmCall(C.Structure):
         ("seed", C.c_ulonglong), ("rng_stream", C.c_uint), ("rng_row_offset", C.c_uint), ("mask_mode", C.c_int),
         ("split_k", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int),
         ("status", C.c_void_p),
+        ("bgroup_of_mblock", C.c_void_p), ("kblock_range", C.c_void_p), ("a_bcast", C.c_int), ("b_bcast", C.c_int),
+        ("b_groups", C.c_int),
     ]  # fmt: skip
 
 
@@ -147,6 +149,10 @@ def gemm(
     row_offset: int = 0,
     mask_mode: int = 0,
     max_ctas: int = 0,
+    bgroup_of_mblock: torch.Tensor | None = None,
+    kblock_range: torch.Tensor | None = None,
+    a_bcast: bool = False,
+    b_bcast: bool = False,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -207,6 +213,17 @@ def gemm(
     call.rng_row_offset = row_offset & 0xFFFFFFFF
     call.split_k, call.bn, call.max_ctas = split_k, bn, max_ctas
     call.status = status_word().data_ptr()
+    if bgroup_of_mblock is not None:
+        assert bgroup_of_mblock.dtype == torch.int32 and bgroup_of_mblock.numel() == (M + 127) // 128
+        call.bgroup_of_mblock = bgroup_of_mblock.data_ptr()
+        call.b_groups = b.shape[0]
+        call.bsb0 = b.stride(0)
+        if b1 is not None:
+            call.bsb1 = b1.stride(0)
+    if kblock_range is not None:
+        assert kblock_range.dtype == torch.int32 and kblock_range.numel() == 2 * batch
+        call.kblock_range = kblock_range.data_ptr()
+    call.a_bcast, call.b_bcast = int(a_bcast), int(b_bcast)
     rc = lib().pd_gemm(C.byref(call), current_stream_ptr())
     count_launch()
     if rc != 0:

@@ -39,10 +39,19 @@ class SiteWeights:
 
 
 def _split_k_for(M: int, N: int, K: int, sms: int = 148) -> int:
+    """Split count for a weight-gradient GEMM (`K` = tokens): few output tiles leave SMs idle and
+    an unlucky tile count wastes most of its last wave, so take the split (<= 8, >= 2048 tokens per
+    split) whose tile count fills its waves best."""
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
-    if tiles >= sms:
-        return 1
-    return max(1, min(sms // tiles, K // 512))
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        if s > 1 and K // s < 2048:
+            break
+        waves = tiles * s / sms
+        eff = waves / -(-tiles * s // sms)
+        if eff > best_eff + 0.03:
+            best, best_eff = s, eff
+    return best
 
 
 class _FusedSite(torch.autograd.Function):

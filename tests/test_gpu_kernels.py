@@ -301,7 +301,7 @@ def test_fused_faithfulness_matches_fp32(nv):
              SiteSpec("c", 256, 128, 64, group="h"))
     st = ComponentStacks(sites).to("cuda")
     st.init_random(torch.Generator().manual_seed(0))
-    W = {s.name: (st.weight(s.name).detach() + 0.02 * torch.randn(s.d_out, s.d_in, device="cuda")).to(bf) for s in sites}
+    W = {s.name: (st.weight(s.name).detach() + 0.02 * torch.randn(s.d_out, s.d_in, device="cuda")).to(bf).contiguous() for s in sites}
     wsq = {k: float(v.float().pow(2).sum()) for k, v in W.items()}
     loss = fused_faithfulness(st, W, wsq, coeff=3.0)
     gV, gU = st.V["g"].grad.clone(), st.U["h"].grad.clone()
@@ -313,7 +313,7 @@ def test_fused_faithfulness_matches_fp32(nv):
     assert float(loss) == pytest.approx(float(ref), rel=2e-3)
     assert rel(gV, st.V["g"].grad) < 2e-2 and rel(gU, st.U["h"].grad) < 2e-2
     # split precision: an exact factorisation gives a residual far below the bf16 rounding floor
-    Wx = {s.name: st.weight(s.name).detach().to(bf) for s in sites}
+    Wx = {s.name: st.weight(s.name).detach().to(bf).contiguous() for s in sites}
     for p in st.parameters():
         p.grad = None
     exact = fused_faithfulness(st, Wx, {k: float(v.float().pow(2).sum()) for k, v in Wx.items()}, 1.0, accumulate_grads=False)
@@ -330,3 +330,42 @@ def test_native_philox_matches_reference(nv):
     b = uniform(0xABCDEF0123, 99, 37, 24, 5, "cuda")[:, :21]
     _done(nv)
     assert torch.equal(a, b)
+
+
+def test_grouped_site_matches_per_expert_eager(nv):
+    """Ragged groups incl. empty experts: forward, input/mask gradients and per-expert weight gradients."""
+    from param_decomp_b200.core.decomposed_linear import site_forward
+    from param_decomp_b200.core.masking import SiteMask
+    from param_decomp_b200.ops.grouped import JobLayout, grouped_site
+
+    torch.manual_seed(11)
+    E, d_in, c, d_out, J = 5, 128, 64, 192, 700
+    expert = torch.randint(0, E - 1, (J,), device="cuda")  # expert E-1 stays empty
+    expert[:3] = 0
+    V32 = torch.randn(E, d_in, c, device="cuda") / d_in**0.5
+    U32 = torch.randn(E, c, d_out, device="cuda") / c**0.5
+    W = (torch.randn(E, d_out, d_in, device="cuda") / d_in**0.5).to(bf)
+    x = torch.randn(J, d_in, device="cuda", dtype=bf)
+    m = torch.rand(J, c, device="cuda").to(bf)
+    d = torch.rand(J, device="cuda")
+    layout = JobLayout.build(expert, E)
+    assert layout.n_rows % 128 == 0 and int(layout.counts[E - 1]) == 0
+    xf, mf = x.clone().requires_grad_(True), m.clone().requires_grad_(True)
+    gV, gU = torch.zeros_like(V32), torch.zeros_like(U32)
+    ys = grouped_site(layout.scatter_rows(xf), V32.to(bf), U32.to(bf), W, layout, layout.scatter_rows(mf),
+                      layout.scatter_rows(d[:, None])[:, 0], None, gV, gU, need_wgrad=True)
+    y = layout.gather_rows(ys)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xe, me = x.float().requires_grad_(True), m.float().requires_grad_(True)
+    Ve, Ue = V32.to(bf).float().requires_grad_(True), U32.to(bf).float().requires_grad_(True)
+    ye = torch.zeros(J, d_out, device="cuda")
+    for e in range(E):
+        rows = (expert == e).nonzero()[:, 0]
+        if rows.numel():
+            ye[rows] = site_forward(xe[rows], Ve[e], Ue[e], W[e].float(), SiteMask(mask=me[rows], delta=d[rows, None]))
+    ye.backward(gy.float())
+    _done(nv)
+    assert rel(y, ye) < 1e-2 and rel(xf.grad, xe.grad) < 2e-2 and rel(mf.grad, me.grad) < 2e-2
+    assert rel(gV, Ve.grad) < 2e-2 and rel(gU, Ue.grad) < 2e-2
+    assert float(gV[E - 1].abs().max()) == 0.0  # the empty expert's gradient is exactly zero
