@@ -502,6 +502,41 @@ __global__ void split_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __
   }
 }
 
+
+// out[c] += sum over rows of x[row, c] (bf16 in, fp32 out). Same tiling as the activity kernel.
+__global__ void colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long long rows,
+                                   int C) {
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + cg) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < C) {
+    for (long long r = static_cast<long long>(blockIdx.y) * 8 + rl; r < rows;
+         r += static_cast<long long>(gridDim.y) * 8) {
+      const uint4 q = *reinterpret_cast<const uint4*>(x + r * C + col);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+  }
+  __shared__ float red[8][32][8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[rl][cg][k] = acc[k];
+  __syncthreads();
+  if (rl == 0 && col < C) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float v = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v += red[j][cg][k];
+      atomicAdd(out + col + k, v);
+    }
+  }
+}
+
 }  // namespace
 
 #define PD_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : 1)
@@ -621,5 +656,16 @@ extern "C" int pd_philox_uniform(float* out, long long rows, int cols, unsigned 
 extern "C" int pd_split_bf16(const float* x, void* hi, void* lo, long long n, void* stream) {
   split_bf16_kernel<<<blocks_for(n, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       x, static_cast<__nv_bfloat16*>(hi), static_cast<__nv_bfloat16*>(lo), n);
+  return PD_CHECK_LAUNCH();
+}
+
+extern "C" int pd_colsum_bf16(const void* x, float* out, long long rows, int C, void* stream) {
+  if (C % 8 != 0) return 5;
+  const int gx = (C + 255) / 256;
+  int gy = (148 * 4 + gx - 1) / gx;
+  if (gy > (rows + 7) / 8) gy = static_cast<int>((rows + 7) / 8);
+  if (gy < 1) gy = 1;
+  colsum_bf16_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), out, rows, C);
   return PD_CHECK_LAUNCH();
 }

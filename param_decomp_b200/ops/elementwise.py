@@ -211,3 +211,17 @@ def split_bf16(x: Tensor) -> tuple[Tensor, Tensor]:
     lib.pd_split_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]
     _check(lib.pd_split_bf16(x.data_ptr(), hi.data_ptr(), lo.data_ptr(), x.numel(), _s()), "split_bf16")
     return hi, lo
+
+
+def colsum_bf16(x: Tensor) -> Tensor:
+    """Column sums of a `[..., rows, C]` bf16 tensor in fp32: `[..., C]` (one read, no fp32 copy)."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    lead = x.shape[:-2]
+    rows, Cn = x.shape[-2], x.shape[-1]
+    flat = x.reshape(-1, rows, Cn)
+    out = torch.zeros(flat.shape[0], Cn, device=x.device, dtype=torch.float32)
+    lib = _lib()
+    lib.pd_colsum_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p]
+    for i in range(flat.shape[0]):
+        _check(lib.pd_colsum_bf16(flat[i].data_ptr(), out[i].data_ptr(), rows, Cn, _s()), "colsum_bf16")
+    return out.reshape(*lead, Cn)

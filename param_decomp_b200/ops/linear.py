@@ -82,7 +82,9 @@ class _BmmBias(torch.autograd.Function):
         tiles = ((K + 127) // 128) * ((M + 255) // 256) * g
         split = max(1, min(148 // max(tiles, 1), N // 512))
         nv.gemm(x, dy, dW, a_mn=True, b_mn=True, accumulate=True, split_k=split)
-        db = dy.float().sum(1, keepdim=True)
+        from param_decomp_b200.ops.elementwise import colsum_bf16
+
+        db = colsum_bf16(dy).unsqueeze(1) if M % 8 == 0 else dy.float().sum(1, keepdim=True)
         return dx, dW, db
 
 

@@ -131,3 +131,40 @@ def test_resid_mlp_runs(tmp_path):
     raw["decomposition"]["sites"]["sites"] = [{"name": "layers.0.mlp_in", "C": 12}, {"name": "layers.0.mlp_out", "C": 12}]
     res = run_resid_mlp(ResidMLPExperimentConfig.model_validate(raw), tmp_path, run_id="p-000000dd")
     assert res.final_step == 6
+
+
+def test_pretrain_cache_roundtrip_feeds_decomposition(tmp_path):
+    """Pretrain a tiny LlamaSimpleMLP, then load it as a `pretrained` target by run path."""
+    import torch
+
+    from param_decomp_b200.config.experiments import PretrainedTarget
+    from param_decomp_b200.models import loaders
+    from param_decomp_b200.pretrain.train import PretrainConfig, pretrain
+
+    cfg = PretrainConfig.model_validate({
+        "run_name": "t", "global_batch": 4, "num_iterations": 4, "warmup_iters": 1, "learning_rate": 1e-3,
+        "log_every": 2, "val_every": 2, "save_every": 2, "dtype": "float32",
+        "model": {"vocab_size": 64, "n_layer": 2, "n_head": 2, "n_embd": 32, "n_intermediate": 64, "n_ctx": 16}})
+    entry = pretrain(cfg, tmp_path, run_id="t-0000abcd", project="spd")
+    assert (entry / "model_config.yaml").exists() and len(list(entry.glob("model_step_*.safetensors"))) == 2
+    spec = PretrainedTarget(model_class="LlamaSimpleMLP", run_path="goodfire/spd/runs/t-0000abcd")
+    arch, weights = loaders.load_from_spec(spec, tmp_path, torch.float32, "cpu")
+    assert arch.family == "simple_mlp" and arch.n_layer == 2 and "h.0.attn.q_proj.weight" in weights
+
+
+def test_nonlinearity_aligned_init_is_rank_one_slices_of_w():
+    import torch
+
+    from param_decomp_b200.config.experiments import TransformerArchConfig
+    from param_decomp_b200.core.components import ComponentStacks
+    from param_decomp_b200.core.init_aligned import nonlinearity_aligned_init
+    from param_decomp_b200.models import transformer as tf
+
+    arch = TransformerArchConfig(family="simple_mlp", n_layer=1, d_model=16, n_head=2, d_ff=32, vocab_size=20)
+    w = tf.random_init_weights(arch, 0, torch.float32)
+    name = tf.site_name("simple_mlp", 0, "c_fc")
+    m = tf.TransformerDecomposedModel(arch, w, {name: 32})
+    st = ComponentStacks(m.sites)
+    nonlinearity_aligned_init(st, m, 0)
+    # C == d_ff and every neuron covered once: the components sum to W exactly
+    assert torch.allclose(st.weight(name), w[name + ".weight"], atol=1e-5)

@@ -369,3 +369,23 @@ def test_grouped_site_matches_per_expert_eager(nv):
     assert rel(y, ye) < 1e-2 and rel(xf.grad, xe.grad) < 2e-2 and rel(mf.grad, me.grad) < 2e-2
     assert rel(gV, Ve.grad) < 2e-2 and rel(gU, Ue.grad) < 2e-2
     assert float(gV[E - 1].abs().max()) == 0.0  # the empty expert's gradient is exactly zero
+
+
+def test_colsum_and_bmm_bias_grads(nv):
+    from param_decomp_b200.ops.elementwise import colsum_bf16
+    from param_decomp_b200.ops.linear import bmm_bias
+
+    torch.manual_seed(12)
+    x = torch.randn(3, 500, 256, device="cuda", dtype=bf)
+    assert rel(colsum_bf16(x), x.float().sum(1)) < 1e-5
+    W = (torch.randn(3, 256, 128, device="cuda") / 16).requires_grad_(True)
+    b = torch.randn(3, 1, 128, device="cuda").requires_grad_(True)
+    xin = x.clone().requires_grad_(True)
+    y = bmm_bias(xin, W, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2, W2, b2 = x.float().requires_grad_(True), W.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    y2 = torch.baddbmm(b2, x2, W2)
+    y2.backward(gy.float())
+    _done(nv)
+    assert rel(y, y2) < 1e-2 and rel(xin.grad, x2.grad) < 2e-2 and rel(W.grad, W2.grad) < 2e-2 and rel(b.grad, b2.grad) < 1e-2
