@@ -334,6 +334,13 @@ inline int encode_tmap(CUtensorMap* tm, const void* base, int elem_size, bool is
   CUresult r = fn(tm, dt, rank, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // The driver call needs a context current on THIS host thread (e.g. a fresh autograd worker);
+    // a no-op runtime call binds the device's primary context, then the encode is retried once.
+    cudaFree(nullptr);
+    r = fn(tm, dt, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? 0 : 200 + static_cast<int>(r);
 }
 

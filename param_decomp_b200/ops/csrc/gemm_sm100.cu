@@ -38,7 +38,13 @@ namespace pd {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kNumEpiWarps = 8;
-constexpr int kNumThreads = 32 * (2 + kNumEpiWarps);
+constexpr int kGatherWarp = 2 + kNumEpiWarps;  // pulls peers' A rows for all-gather -> GEMM
+constexpr int kNumThreads = 32 * (3 + kNumEpiWarps);
+constexpr int kMaxPeers = 8;
+
+struct PeerMaps {
+  CUtensorMap m[kMaxPeers];
+};
 constexpr int kGroupM = 16;
 constexpr int kStageBytesA = BM * BK * 2;  // 16 KiB
 constexpr int kOutBoxBytes = 32 * 128;     // one 32-row x 128-byte staging box
@@ -77,6 +83,19 @@ struct GemmArgs {
   const int* bgroup_of_mblock;
   const int* kblock_range;
   int a_bcast, b_bcast;
+  // GEMM -> reduce-scatter: output row block goes to its owner's fp32 buffer by TMA reduce-add
+  int rs_world;          // 0/1 = off
+  int rs_rows;           // rows per owner (multiple of 128)
+  // all-gather -> GEMM: A (phase 0) rows are sharded by rank; remote row blocks are pulled into the
+  // local full-size A buffer by the gather warp, each block once per GPU, and released by a flag
+  int ag_world, ag_rank; // ag_world 0/1 = off
+  int ag_rows;           // rows per rank (multiple of 128)
+  const void* ag_src[kMaxPeers];  // each rank's shard [ag_rows, K0] bf16, row pitch ag_ld elements
+  void* ag_dst;          // local full buffer [M, K0] (the A0 operand), same row pitch
+  long long ag_ld;
+  int ag_k;              // K0 in elements
+  unsigned int* ag_flags;  // [num_m] local flags, block is ready when flag == ag_seq
+  unsigned int ag_seq;
 };
 
 template <int BN, int NOUT>
@@ -148,7 +167,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
             const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
             const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
-            const GemmArgs args) {
+            const __grid_constant__ PeerMaps peerOut, const GemmArgs args) {
   using Plan = SmemPlan<BN, NOUT>;
   constexpr int kStages = Plan::kStages;
   constexpr int kStageBytesB = Plan::kStageBytesB;
@@ -224,6 +243,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const int in_group = pid % per_group;
     mb = first_m + in_group % gsz;
     nb = in_group / gsz;
+    if (args.ag_world > 1) {  // start with the row blocks this rank already holds
+      const int per_rank = args.ag_rows / BM;
+      mb = (mb + args.ag_rank * per_rank) % num_m;
+    }
   };
 
   // K-block range of a tile: a split of the whole K extent, or (ragged weight-gradient products) the
@@ -253,6 +276,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         if (bb < 0) continue;  // padding row block of a grouped product: no tile
         const int ab = args.a_bcast ? 0 : b;
         const int bbatch = args.b_bcast ? 0 : bb;
+        if (args.ag_world > 1 && mb * BM / args.ag_rows != args.ag_rank) {
+          // remote row block: wait (bounded) until the gather warp of some CTA has landed it locally
+          const unsigned long long t0 = globaltimer_ns();
+          bool ready = true;
+          while (true) {
+            unsigned int f;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(args.ag_flags + mb) : "memory");
+            if (f == args.ag_seq) break;
+            if (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs) {
+              *abort_flag = 1;
+              if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
+              ready = false;
+              break;
+            }
+          }
+          if (!ready) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes -> TMA reads
+        }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
             if (args.status) atomicCAS(args.status, 0, kTimeoutProducer);
@@ -346,6 +390,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           acc = 0;
           acc_phase ^= 1;
         }
+      }
+    }
+  } else if (warp == kGatherWarp) {
+    // ------------------------------ all-gather of remote A row blocks ------------------------------
+    if (args.ag_world > 1) {
+      const int per_rank = args.ag_rows / BM;
+      const int n_remote = num_m - per_rank;
+      const int vec_per_row = args.ag_k / 8;  // 16-byte vectors per row
+      // remote blocks in consumption order (the raster starts right after the local range)
+      for (int i = blockIdx.x; i < n_remote; i += gridDim.x) {
+        const int mb = ((args.ag_rank + 1) * per_rank + i) % num_m;
+        const int owner = mb / per_rank;
+        const int row0 = (mb - owner * per_rank) * BM;
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(args.ag_src[owner]) +
+                                                          static_cast<long long>(row0) * args.ag_ld);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.ag_dst) +
+                                              static_cast<long long>(mb) * BM * args.ag_ld);
+        const int rows = min(BM, args.M - mb * BM);
+        const long long pitch = args.ag_ld / 8;
+        for (int idx = lane; idx < rows * vec_per_row; idx += 32) {
+          const int r = idx / vec_per_row, c = idx - r * vec_per_row;
+          dst[r * pitch + c] = src[r * pitch + c];
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(args.ag_flags + mb), "r"(args.ag_seq) : "memory");
       }
     }
   } else {
@@ -598,7 +669,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         if (lane == 0) {
           const int crow = mb * BM + q * 32;
           if (crow < args.M) {
-            if (args.accumulate)
+            if (args.rs_world > 1) {
+              const int owner = crow / args.rs_rows;
+              tma_reduce_add_3d(&peerOut.m[owner], box0, col0, crow - owner * args.rs_rows, b);
+            } else if (args.accumulate)
               tma_reduce_add_3d(&tmOut0, box0, col0, crow, b);
             else
               tma_store_3d(&tmOut0, box0, col0, crow, b);
@@ -673,7 +747,7 @@ static int encode_operand(CUtensorMap* tm, const OperandDesc& op, int mn_extent,
 template <int BN, int EPI, int NOUT>
 static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
                        const CUtensorMap& b1, const CUtensorMap& o0, const CUtensorMap& o1,
-                       const GemmArgs& args, int max_ctas, cudaStream_t stream) {
+                       const PeerMaps& peers, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
   using Plan = SmemPlan<BN, NOUT>;
   auto kern = gemm_kernel<BN, EPI, NOUT>;
   static bool configured = false;
@@ -693,7 +767,8 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
   int grid = static_cast<int>(tiles < g_num_sms ? tiles : g_num_sms);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
-  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, args);
+  if (args.ag_world > 1 && grid < g_num_sms && tiles > grid) return kBadArgument;  // gather needs the full persistent grid
+  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, peers, args);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
@@ -734,6 +809,10 @@ struct PdGemmCall {
   // kblock_range[2*b], [2*b+1] (device): 64-wide K-block range of batch b on a K axis shared by all
   // batches (ragged weight gradients: A/B are broadcast, a_bcast/b_bcast = 1).
   const int* bgroup_of_mblock; const int* kblock_range; int a_bcast; int b_bcast; int b_groups;
+  // GEMM -> reduce-scatter over peer memory: rs_out[r] = rank r's fp32 [rs_rows, N] buffer (pitch ldo0)
+  int rs_world; int rs_rows; void* rs_out[8];
+  // all-gather -> GEMM: ag_src[r] = rank r's A shard [ag_rows, K0]; A0 is the local full buffer
+  int ag_world; int ag_rank; int ag_rows; const void* ag_src[8]; unsigned int* ag_flags; unsigned int ag_seq;
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -764,6 +843,20 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.status = c->status;
   a.bgroup_of_mblock = c->bgroup_of_mblock; a.kblock_range = c->kblock_range;
   a.a_bcast = c->a_bcast; a.b_bcast = c->b_bcast;
+  a.rs_world = c->rs_world; a.rs_rows = c->rs_rows;
+  a.ag_world = c->ag_world; a.ag_rank = c->ag_rank; a.ag_rows = c->ag_rows;
+  a.ag_dst = const_cast<void*>(c->A0); a.ag_ld = c->lda0; a.ag_k = c->K0; a.ag_flags = c->ag_flags; a.ag_seq = c->ag_seq;
+  for (int r = 0; r < kMaxPeers; ++r) a.ag_src[r] = c->ag_src[r];
+  if (c->rs_world > 1) {
+    if (c->rs_world > kMaxPeers || !c->out_fp32 || c->epi != EPI_PLAIN || c->batch != 1 || (c->rs_rows % BM) != 0 ||
+        c->rs_rows * c->rs_world < c->M)
+      return kBadArgument;
+  }
+  if (c->ag_world > 1) {
+    if (c->ag_world > kMaxPeers || c->a_mn0 || c->batch != 1 || (c->ag_rows % BM) != 0 || (c->K0 % 8) != 0 ||
+        c->ag_rows * c->ag_world != c->M || c->ag_flags == nullptr || a.split_k != 1)
+      return kBadArgument;
+  }
   if (c->epi == EPI_FAITH) {
     if (c->ci == nullptr || (c->ld_ci % 8) != 0 || (reinterpret_cast<uintptr_t>(c->ci) & 15) || c->N % 8 != 0)
       return kBadArgument;
@@ -779,6 +872,7 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   }
 
   CUtensorMap ta0, tb0, ta1, tb1, to0, to1;
+  PeerMaps peers;
   int rc;
   OperandDesc A0{c->A0, c->lda0, c->bsa0, c->a_mn0}, B0{c->B0, c->ldb0, c->bsb0, c->b_mn0};
   const int a_batch = c->a_bcast ? 1 : c->batch;
@@ -804,8 +898,14 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
     to1 = to0;
   }
 
+  for (int r = 0; r < kMaxPeers; ++r) peers.m[r] = to0;
+  if (c->rs_world > 1) {
+    for (int r = 0; r < c->rs_world; ++r)
+      if ((rc = encode_tmap(&peers.m[r], c->rs_out[r], 4, true, c->N, c->rs_rows, c->ldo0, 1, 0, 32, 32)))
+        return 7000 + rc;
+  }
 #define PD_LAUNCH(BN_, EPI_, NOUT_) \
-  launch_gemm<BN_, EPI_, NOUT_>(ta0, tb0, ta1, tb1, to0, to1, a, c->max_ctas, stream)
+  launch_gemm<BN_, EPI_, NOUT_>(ta0, tb0, ta1, tb1, to0, to1, peers, a, c->max_ctas, stream)
   if (c->epi == EPI_PLAIN) return bn == 256 ? PD_LAUNCH(256, EPI_PLAIN, 1) : PD_LAUNCH(128, EPI_PLAIN, 1);
   if (c->epi == EPI_MASK_FWD) {
     if (nout == 2) return bn == 256 ? PD_LAUNCH(256, EPI_MASK_FWD, 2) : PD_LAUNCH(128, EPI_MASK_FWD, 2);

@@ -45,6 +45,9 @@ class PdGemmCall(C.Structure):
         ("status", C.c_void_p),
         ("bgroup_of_mblock", C.c_void_p), ("kblock_range", C.c_void_p), ("a_bcast", C.c_int), ("b_bcast", C.c_int),
         ("b_groups", C.c_int),
+        ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
+        ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
+        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint),
     ]  # fmt: skip
 
 
@@ -153,6 +156,8 @@ def gemm(
     kblock_range: torch.Tensor | None = None,
     a_bcast: bool = False,
     b_bcast: bool = False,
+    rs: tuple[list[int], int] | None = None,
+    ag: tuple[list[int], int, int, torch.Tensor, int] | None = None,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -224,6 +229,18 @@ def gemm(
         assert kblock_range.dtype == torch.int32 and kblock_range.numel() == 2 * batch
         call.kblock_range = kblock_range.data_ptr()
     call.a_bcast, call.b_bcast = int(a_bcast), int(b_bcast)
+    if rs is not None:  # (peer pointers of every rank's fp32 [rows_per_rank, N] buffer, rows_per_rank)
+        ptrs, rows = rs
+        call.rs_world, call.rs_rows = len(ptrs), rows
+        for i, ptr in enumerate(ptrs):
+            call.rs_out[i] = ptr
+    if ag is not None:  # (peer pointers of every rank's A shard, my rank, rows per rank, flags, sequence number)
+        ptrs, rank, rows, flags, seq = ag
+        assert flags.dtype == torch.int32 and flags.numel() >= (M + 127) // 128
+        call.ag_world, call.ag_rank, call.ag_rows = len(ptrs), rank, rows
+        for i, ptr in enumerate(ptrs):
+            call.ag_src[i] = ptr
+        call.ag_flags, call.ag_seq = flags.data_ptr(), seq & 0xFFFFFFFF
     rc = lib().pd_gemm(C.byref(call), current_stream_ptr())
     count_launch()
     if rc != 0:

@@ -123,3 +123,53 @@ def test_peer_barrier_times_out_cleanly():
     out = mp.Manager().dict()
     mp.spawn(_barrier_timeout_worker, args=(world, port, out), nprocs=world, join=True)
     assert out[0] == (0, 4) and out[1] == (0, 0)
+
+
+def _tp_worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from param_decomp_b200.ops import native
+    from param_decomp_b200.parallel import tp
+
+    bf = torch.bfloat16
+    M, K, N = 1024, 512, 384
+    ws = tp.TPWorkspace(dist.group.WORLD, max_rows=M, max_cols=max(K, N), device=torch.device("cuda", rank))
+    g = torch.Generator(device="cuda").manual_seed(1234)  # same full operands on every rank
+    a_full = torch.randn(M, K, generator=g, device="cuda").to(bf)
+    b_full = (torch.randn(N, K, generator=g, device="cuda") / K**0.5).to(bf)
+    res = {}
+    # GEMM -> reduce-scatter: each rank contracts its K slice
+    ks = slice(rank * K // world, (rank + 1) * K // world)
+    for rep in range(2):  # twice: sequence numbers and buffer reuse
+        y = tp.gemm_reduce_scatter(ws, a_full[:, ks].contiguous(), b_full[:, ks].contiguous())
+        torch.cuda.synchronize()
+        want = (a_full.float() @ b_full.float().T)[rank * M // world:(rank + 1) * M // world]
+        res[f"rs{rep}"] = float((y - want).norm() / want.norm())
+    y2 = tp.gemm_reduce_scatter_nccl(dist.group.WORLD, a_full[:, ks].contiguous(), b_full[:, ks].contiguous())
+    res["rs_vs_nccl"] = float((y - y2).norm() / y2.norm())
+    # all-gather -> GEMM: each rank holds a row slice of A
+    rows = M // world
+    for rep in range(2):
+        o = torch.zeros(M, N, device="cuda", dtype=bf)
+        tp.allgather_gemm(ws, a_full[rank * rows:(rank + 1) * rows].contiguous(), b_full, o)
+        torch.cuda.synchronize()
+        want = a_full.float() @ b_full.float().T
+        res[f"ag{rep}"] = float((o.float() - want).norm() / want.norm())
+    native.check_status()
+    out[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_tp_gemms_two_gpus():
+    _need_two_gpus()
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_tp_worker, args=(world, port, out), nprocs=world, join=True)
+    for r in range(world):
+        for k, v in out[r].items():
+            assert v < (1e-5 if k.startswith("rs") and "nccl" not in k else 1e-2), (r, k, v)
