@@ -38,8 +38,9 @@ namespace pd {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kNumEpiWarps = 8;
-constexpr int kGatherWarp = 2 + kNumEpiWarps;  // pulls peers' A rows for all-gather -> GEMM
-constexpr int kNumThreads = 32 * (3 + kNumEpiWarps);
+constexpr int kNumThreads = 32 * (2 + kNumEpiWarps);
+constexpr int kGatherChunk = 16384;  // bytes per bulk copy of the all-gather CTAs
+constexpr int kGatherSlotsMax = 12;
 constexpr int kMaxPeers = 8;
 
 struct PeerMaps {
@@ -96,6 +97,7 @@ struct GemmArgs {
   int ag_k;              // K0 in elements
   unsigned int* ag_flags;  // [num_m] local flags, block is ready when flag == ag_seq
   unsigned int ag_seq;
+  int ag_gather_ctas;    // trailing CTAs of the grid that only move peers' rows (no tiles)
 };
 
 template <int BN, int NOUT>
@@ -107,6 +109,7 @@ struct SmemPlan {
   static constexpr int kStagesRaw = (kBudget - kOutBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kTotal = kStages * kStageBytes + kOutBytes + 256 + 1024;
+  static_assert(16 * kStages + 40 + 8 * kGatherSlotsMax <= 256, "barrier area");
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -200,6 +203,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   const int split = args.split_k;
   const int kb_per_split = (kb_total + split - 1) / split;
   const long long num_tiles = static_cast<long long>(num_m) * num_n * split * args.batch;
+  // All-gather mode: the last `ag_gather_ctas` CTAs own no tiles; they stream peers' row blocks
+  // into the local A buffer while the others compute.
+  const int n_gather = args.ag_world > 1 ? args.ag_gather_ctas : 0;
+  const int n_compute = static_cast<int>(gridDim.x) - n_gather;
+  const bool is_gather_cta = static_cast<int>(blockIdx.x) >= n_compute;
+  const long long tile0 = is_gather_cta ? num_tiles : static_cast<long long>(blockIdx.x);
+  const long long tstride = n_compute;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -263,11 +273,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && is_gather_cta) {
+      // Bulk-copy ring: peer global -> shared (mbarrier) -> local global (bulk group). The pipeline
+      // stages are unused in this CTA and serve as the ring; loads run kSlots-2 chunks ahead.
+      constexpr int kSlots = (kStages * Plan::kStageBytes / kGatherChunk) < kGatherSlotsMax
+                                 ? (kStages * Plan::kStageBytes / kGatherChunk) : kGatherSlotsMax;
+      constexpr int kLag = kSlots - 2;
+      const uint32_t bar_g = tmem_slot + 8;
+      for (int s2 = 0; s2 < kSlots; ++s2) mbar_init(bar_g + 8 * s2, 1);
+      mbar_fence_init();
+      const int per_rank = args.ag_rows / BM;
+      const int n_remote = num_m - per_rank;
+      const int gidx = static_cast<int>(blockIdx.x) - n_compute;
+      const long long block_bytes = static_cast<long long>(BM) * args.ag_k * 2;
+      const int chunks = static_cast<int>((block_bytes + kGatherChunk - 1) / kGatherChunk);
+      const int my_blocks = n_remote > gidx ? (n_remote - gidx + n_gather - 1) / n_gather : 0;
+      const long long total = static_cast<long long>(my_blocks) * chunks;
+      auto locate = [&](long long q, const char*& src, char*& dst, uint32_t& bytes, int& mb, bool& last) {
+        const int blk = static_cast<int>(q / chunks), ch = static_cast<int>(q % chunks);
+        const int i = gidx + blk * n_gather;  // remote blocks in the order the raster consumes them
+        mb = ((args.ag_rank + 1) * per_rank + i) % num_m;
+        const int owner = mb / per_rank;
+        const long long off = static_cast<long long>(ch) * kGatherChunk;
+        src = static_cast<const char*>(args.ag_src[owner]) +
+              static_cast<long long>(mb - owner * per_rank) * block_bytes + off;
+        dst = static_cast<char*>(args.ag_dst) + static_cast<long long>(mb) * block_bytes + off;
+        bytes = static_cast<uint32_t>(block_bytes - off < kGatherChunk ? block_bytes - off : kGatherChunk);
+        last = ch == chunks - 1;
+      };
+      bool ok = true;
+      for (long long it = 0; it < total + kLag && ok; ++it) {
+        if (it < total) {
+          const char* src; char* dst; uint32_t bytes; int mb; bool last;
+          locate(it, src, dst, bytes, mb, last);
+          const int slot = static_cast<int>(it % kSlots);
+          // the store that last read this slot was committed kSlots - kLag - 1 = 1 group ago
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          mbar_expect_tx(bar_g + 8 * slot, bytes);
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+              ::"r"(smem_a + slot * kGatherChunk), "l"(src), "r"(bytes), "r"(bar_g + 8 * slot) : "memory");
+        }
+        const long long j = it - kLag;
+        if (j >= 0) {
+          const char* src; char* dst; uint32_t bytes; int mb; bool last;
+          locate(j, src, dst, bytes, mb, last);
+          const int slot = static_cast<int>(j % kSlots);
+          if (!mbar_wait(bar_g + 8 * slot, static_cast<uint32_t>((j / kSlots) & 1), abort_flag)) {
+            if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
+            ok = false;
+            break;
+          }
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dst), "r"(smem_a + slot * kGatherChunk), "r"(bytes) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          if (last) {  // the whole row block has landed: publish it to the producers of every CTA
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(args.ag_flags + mb), "r"(args.ag_seq) : "memory");
+          }
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (long long t = tile0; t < num_tiles && ok; t += tstride) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
         int kb_lo, kb_hi;
@@ -342,7 +415,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (long long t = tile0; t < num_tiles && ok; t += tstride) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
         int kb_lo, kb_hi;
@@ -392,33 +465,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         }
       }
     }
-  } else if (warp == kGatherWarp) {
-    // ------------------------------ all-gather of remote A row blocks ------------------------------
-    if (args.ag_world > 1) {
-      const int per_rank = args.ag_rows / BM;
-      const int n_remote = num_m - per_rank;
-      const int vec_per_row = args.ag_k / 8;  // 16-byte vectors per row
-      // remote blocks in consumption order (the raster starts right after the local range)
-      for (int i = blockIdx.x; i < n_remote; i += gridDim.x) {
-        const int mb = ((args.ag_rank + 1) * per_rank + i) % num_m;
-        const int owner = mb / per_rank;
-        const int row0 = (mb - owner * per_rank) * BM;
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(args.ag_src[owner]) +
-                                                          static_cast<long long>(row0) * args.ag_ld);
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.ag_dst) +
-                                              static_cast<long long>(mb) * BM * args.ag_ld);
-        const int rows = min(BM, args.M - mb * BM);
-        const long long pitch = args.ag_ld / 8;
-        for (int idx = lane; idx < rows * vec_per_row; idx += 32) {
-          const int r = idx / vec_per_row, c = idx - r * vec_per_row;
-          dst[r * pitch + c] = src[r * pitch + c];
-        }
-        __threadfence();
-        __syncwarp();
-        if (lane == 0)
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(args.ag_flags + mb), "r"(args.ag_seq) : "memory");
-      }
-    }
   } else {
     // ------------------------------ epilogue ------------------------------
     // Work unit = a 32-column half of an output box. Global operands of the mask epilogues
@@ -448,7 +494,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       return args.bgroup_of_mblock[mb2] >= 0;
     };
     auto next_real_tile = [&](long long t) {
-      while (t < num_tiles && !tile_is_real(t)) t += gridDim.x;
+      while (t < num_tiles && !tile_is_real(t)) t += tstride;
       return t;
     };
     uint4 pre_ci[4], pre_h[4];
@@ -482,7 +528,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         int b2, mb2, nb2, sp2;
         decode(t, b2, mb2, nb2, sp2);
         if (nb2 * BN + grp * box_cols < args.N) break;
-        t = next_real_tile(t + gridDim.x);
+        t = next_real_tile(t + tstride);
       }
       t_out = t;
       j_out = grp;
@@ -490,11 +536,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     {
       long long tp;
       int jp;
-      first_unit_from(blockIdx.x, tp, jp);
+      first_unit_from(tile0, tp, jp);
       issue_prefetch(tp, jp, 0);
     }
 
-    for (long long t = next_real_tile(blockIdx.x); t < num_tiles; t = next_real_tile(t + gridDim.x)) {
+    for (long long t = next_real_tile(tile0); t < num_tiles; t = next_real_tile(t + tstride)) {
       int b, mb, nb, sp;
       decode(t, b, mb, nb, sp);
       int kb_lo_e, kb_hi_e;
@@ -536,7 +582,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             } else {
               long long tn;
               int jn;
-              first_unit_from(t + gridDim.x, tn, jn);
+              first_unit_from(t + tstride, tn, jn);
               issue_prefetch(tn, jn, 0);
             }
           }
@@ -767,8 +813,16 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
   int grid = static_cast<int>(tiles < g_num_sms ? tiles : g_num_sms);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
-  if (args.ag_world > 1 && grid < g_num_sms && tiles > grid) return kBadArgument;  // gather needs the full persistent grid
-  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, peers, args);
+  GemmArgs launch_args = args;
+  if (args.ag_world > 1) {
+    // every CTA must be resident (producers wait on blocks that gather CTAs deliver): one per SM
+    if (max_ctas > 0 && max_ctas < g_num_sms) return kBadArgument;
+    grid = g_num_sms;
+    int g = args.ag_gather_ctas > 0 ? args.ag_gather_ctas : 16;
+    if (g > grid / 2) g = grid / 2;
+    launch_args.ag_gather_ctas = g;
+  }
+  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, peers, launch_args);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
@@ -847,6 +901,7 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.ag_world = c->ag_world; a.ag_rank = c->ag_rank; a.ag_rows = c->ag_rows;
   a.ag_dst = const_cast<void*>(c->A0); a.ag_ld = c->lda0; a.ag_k = c->K0; a.ag_flags = c->ag_flags; a.ag_seq = c->ag_seq;
   for (int r = 0; r < kMaxPeers; ++r) a.ag_src[r] = c->ag_src[r];
+  a.ag_gather_ctas = 0;
   if (c->rs_world > 1) {
     if (c->rs_world > kMaxPeers || !c->out_fp32 || c->epi != EPI_PLAIN || c->batch != 1 || (c->rs_rows % BM) != 0 ||
         c->rs_rows * c->rs_world < c->M)
@@ -854,7 +909,7 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   }
   if (c->ag_world > 1) {
     if (c->ag_world > kMaxPeers || c->a_mn0 || c->batch != 1 || (c->ag_rows % BM) != 0 || (c->K0 % 8) != 0 ||
-        c->ag_rows * c->ag_world != c->M || c->ag_flags == nullptr || a.split_k != 1)
+        c->ag_rows * c->ag_world != c->M || c->ag_flags == nullptr || a.split_k != 1 || c->lda0 != c->K0)
       return kBadArgument;
   }
   if (c->epi == EPI_FAITH) {
