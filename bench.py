@@ -97,6 +97,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=None, help="override the global batch (debugging only)")
     ap.add_argument("--optim", type=str, default="fused_p2p", choices=["fused_p2p", "collective", "ddp"],
                     help="N>1: fused reduce-scatter+AdamW+all-gather kernel, NCCL RS/AG, or all-reduce + replicated AdamW")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -166,10 +168,15 @@ def main() -> None:
     if topo.rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profile_range:
+        torch.cuda.profiler.start()
     e0.record()
     for b in dev_batches:
         train_step(ctx, state, b)
     e1.record()
+    if args.profile_range:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     sync()
     clocks = sampler.stop() if topo.rank == 0 else {}
     launches = native.launch_count() - launches0

@@ -50,7 +50,12 @@ def cast_bf16(src: Tensor, out: Tensor | None = None) -> Tensor:
 
 
 def rowscale(x: Tensor, s: Tensor) -> Tensor:
-    assert x.dtype == torch.bfloat16 and x.is_contiguous() and s.dtype == torch.float32
+    """`y[r, :] = x[r, :] * s[r]` (bf16 rows, fp32 scales), one vectorised pass."""
+    assert x.dtype == torch.bfloat16 and s.dtype == torch.float32
+    x = x if x.is_contiguous() else x.contiguous()
+    s = s if s.is_contiguous() else s.contiguous()
+    if x.shape[1] % 8 != 0 or x.data_ptr() % 16 != 0:
+        return (x.float() * s[:, None]).to(torch.bfloat16)
     y = torch.empty_like(x)
     _check(_lib().pd_rowscale(x.data_ptr(), s.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], _s()), "rowscale")
     return y

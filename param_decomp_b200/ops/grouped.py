@@ -18,6 +18,7 @@ from dataclasses import dataclass
 import torch
 from torch import Tensor
 
+from param_decomp_b200.ops import elementwise as ew
 from param_decomp_b200.ops import native as nv
 
 PAD = 128
@@ -81,7 +82,7 @@ class _GroupedSite(torch.autograd.Function):
                 bgroup_of_mblock=layout.bgroup)
         y = torch.empty(R, d_out, device=x.device, dtype=torch.bfloat16)
         if d_eff is not None:
-            xd = x * d_eff.to(torch.bfloat16)[:, None]
+            xd = ew.rowscale(x, d_eff)
             nv.gemm(A, U, y, b_mn=True, a1=xd, b1=W, bgroup_of_mblock=layout.bgroup)
         else:
             nv.gemm(A, U, y, b_mn=True, bgroup_of_mblock=layout.bgroup)
@@ -106,7 +107,7 @@ class _GroupedSite(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = torch.empty(R, d_in, device=x.device, dtype=torch.bfloat16)
             if d_eff is not None:
-                dyd = dy * d_eff.to(torch.bfloat16)[:, None]
+                dyd = ew.rowscale(dy, d_eff)
                 nv.gemm(dH, V, dx, a1=dyd, b1=W, b1_mn=True, bgroup_of_mblock=layout.bgroup)
             else:
                 nv.gemm(dH, V, dx, bgroup_of_mblock=layout.bgroup)

@@ -24,6 +24,7 @@ import torch
 from torch import Tensor
 
 from param_decomp_b200.core.masking import SiteMask
+from param_decomp_b200.ops import elementwise as ew
 from param_decomp_b200.ops import native as nv
 
 
@@ -77,7 +78,7 @@ class _FusedSite(torch.autograd.Function):
                 seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset)
         y = torch.empty(N, d_out, device=x.device, dtype=torch.bfloat16)
         if d_eff is not None:
-            xd = x * d_eff.to(torch.bfloat16)[:, None]
+            xd = ew.rowscale(x, d_eff)
             nv.gemm(A, w.U, y, b_mn=True, a1=xd, b1=w.W)
         else:
             nv.gemm(A, w.U, y, b_mn=True)
@@ -111,7 +112,7 @@ class _FusedSite(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = torch.empty(N, d_in, device=x.device, dtype=torch.bfloat16)
             if d_eff is not None:
-                dyd = dy * d_eff.to(torch.bfloat16)[:, None]
+                dyd = ew.rowscale(dy, d_eff)
                 nv.gemm(dH, w.V, dx, a1=dyd, b1=w.W, b1_mn=True)
             else:
                 nv.gemm(dH, w.V, dx)
