@@ -125,7 +125,7 @@ def sdpa(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, segment_ids: Tens
     from param_decomp_b200.ops import attention as attn_ops
 
     if attn_ops.supported(q, k, v, segment_ids):
-        return attn_ops.flash_attention(q, k, v, causal)
+        return attn_ops.flash_attention(q, k, v, causal, segment_ids)
     mask = attention_mask(q.shape[1], False, segment_ids, q.device) if segment_ids is not None else None
     if mask is not None and causal:
         mask = mask & torch.ones(q.shape[1], q.shape[1], dtype=torch.bool, device=q.device).tril()

@@ -389,3 +389,33 @@ def test_colsum_and_bmm_bias_grads(nv):
     y2.backward(gy.float())
     _done(nv)
     assert rel(y, y2) < 1e-2 and rel(xin.grad, x2.grad) < 2e-2 and rel(W.grad, W2.grad) < 2e-2 and rel(b.grad, b2.grad) < 1e-2
+
+
+@pytest.mark.parametrize("hd,H,Hkv,causal,seg", [(64, 4, 4, True, False), (64, 4, 2, True, True), (128, 2, 1, True, False),
+                                                  (64, 2, 2, False, False), (128, 2, 2, False, True)])
+def test_flash_attention_matches_fp32_reference(nv, hd, H, Hkv, causal, seg):
+    from param_decomp_b200.models import ports
+    from param_decomp_b200.ops import attention as attn
+
+    torch.manual_seed(0)
+    B, T = 2, 384
+    q = torch.randn(B, T, H, hd, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    k = torch.randn(B, T, Hkv, hd, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(B, T, Hkv, hd, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    seg_ids = None
+    if seg:
+        cuts = torch.tensor([[0, 100, 250], [0, 129, 300]], device="cuda")
+        pos = torch.arange(T, device="cuda")
+        seg_ids = (pos[None, :, None] >= cuts[:, None, :]).sum(-1).to(torch.int32)
+    assert attn.supported(q, k, v, seg_ids)
+    out = attn.flash_attention(q, k, v, causal, seg_ids)
+    g = torch.randn_like(out)
+    out.backward(g)
+    got = [out.detach().float(), q.grad.float(), k.grad.float(), v.grad.float()]
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = ports.sdpa_reference(q2, k2, v2, causal, seg_ids)
+    ref.backward(g.float())
+    want = [ref.detach(), q2.grad, k2.grad, v2.grad]
+    nv.check_status()
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        assert rel(a, b) < 2e-2, (name, rel(a, b))
