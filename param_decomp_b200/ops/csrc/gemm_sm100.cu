@@ -98,6 +98,7 @@ struct GemmArgs {
   unsigned int* ag_flags;  // [num_m] local flags, block is ready when flag == ag_seq
   unsigned int ag_seq;
   int ag_gather_ctas;    // trailing CTAs of the grid that only move peers' rows (no tiles)
+  int ag_mode;           // 0: A row blocks (activations sharded by rows); 1: B K-slabs (weights sharded by K rows)
 };
 
 template <int BN, int NOUT>
@@ -253,7 +254,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const int in_group = pid % per_group;
     mb = first_m + in_group % gsz;
     nb = in_group / gsz;
-    if (args.ag_world > 1) {  // start with the row blocks this rank already holds
+    if (args.ag_world > 1 && args.ag_mode == 0) {  // start with the row blocks this rank already holds
       const int per_rank = args.ag_rows / BM;
       mb = (mb + args.ag_rank * per_rank) % num_m;
     }
@@ -282,57 +283,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       const uint32_t bar_g = tmem_slot + 8;
       for (int s2 = 0; s2 < kSlots; ++s2) mbar_init(bar_g + 8 * s2, 1);
       mbar_fence_init();
-      const int per_rank = args.ag_rows / BM;
-      const int n_remote = num_m - per_rank;
+      // a block = 128 rows of A (mode 0) or one 64-row K slab of B (mode 1); both are contiguous
+      const int blk_rows = args.ag_mode == 0 ? BM : BK;
+      const int n_blocks = args.ag_mode == 0 ? num_m : args.kblocks0;
+      const int per_rank = args.ag_rows / blk_rows;
+      const int n_remote = n_blocks - per_rank;
       const int gidx = static_cast<int>(blockIdx.x) - n_compute;
-      const long long block_bytes = static_cast<long long>(BM) * args.ag_k * 2;
+      const long long block_bytes = static_cast<long long>(blk_rows) * args.ag_k * 2;
       const int chunks = static_cast<int>((block_bytes + kGatherChunk - 1) / kGatherChunk);
       const int my_blocks = n_remote > gidx ? (n_remote - gidx + n_gather - 1) / n_gather : 0;
-      const long long total = static_cast<long long>(my_blocks) * chunks;
-      auto locate = [&](long long q, const char*& src, char*& dst, uint32_t& bytes, int& mb, bool& last) {
-        const int blk = static_cast<int>(q / chunks), ch = static_cast<int>(q % chunks);
-        const int i = gidx + blk * n_gather;  // remote blocks in the order the raster consumes them
-        mb = ((args.ag_rank + 1) * per_rank + i) % num_m;
-        const int owner = mb / per_rank;
-        const long long off = static_cast<long long>(ch) * kGatherChunk;
-        src = static_cast<const char*>(args.ag_src[owner]) +
-              static_cast<long long>(mb - owner * per_rank) * block_bytes + off;
-        dst = static_cast<char*>(args.ag_dst) + static_cast<long long>(mb) * block_bytes + off;
-        bytes = static_cast<uint32_t>(block_bytes - off < kGatherChunk ? block_bytes - off : kGatherChunk);
-        last = ch == chunks - 1;
+      // One cursor for the loads and one for the stores: (block, chunk) advance by increments only,
+      // the block's addresses are resolved once per block (no division per chunk in this thread).
+      struct Cursor {
+        int blk, ch, mb, slot;
+        uint32_t parity;
+        const char* src;
+        char* dst;
       };
+      auto open_block = [&](Cursor& c) {
+        int i = gidx + c.blk * n_gather;  // remote blocks in the order the raster consumes them
+        int mb = (args.ag_rank + 1) * per_rank + i;
+        while (mb >= n_blocks) mb -= n_blocks;
+        int owner = 0, first = 0;
+        while (first + per_rank <= mb) { first += per_rank; ++owner; }
+        c.mb = mb;
+        c.src = static_cast<const char*>(args.ag_src[owner]) + static_cast<long long>(mb - first) * block_bytes;
+        c.dst = static_cast<char*>(args.ag_dst) + static_cast<long long>(mb) * block_bytes;
+      };
+      auto advance = [&](Cursor& c) {
+        if (++c.slot == kSlots) { c.slot = 0; c.parity ^= 1u; }
+        if (++c.ch == chunks) { c.ch = 0; ++c.blk; if (c.blk < my_blocks) open_block(c); }
+      };
+      Cursor ld{0, 0, 0, 0, 0u, nullptr, nullptr}, st{0, 0, 0, 0, 0u, nullptr, nullptr};
+      if (my_blocks > 0) { open_block(ld); open_block(st); }
+      const int total = my_blocks * chunks;
       bool ok = true;
-      for (long long it = 0; it < total + kLag && ok; ++it) {
+      for (int it = 0; it < total + kLag && ok; ++it) {
         if (it < total) {
-          const char* src; char* dst; uint32_t bytes; int mb; bool last;
-          locate(it, src, dst, bytes, mb, last);
-          const int slot = static_cast<int>(it % kSlots);
+          const long long off = static_cast<long long>(ld.ch) * kGatherChunk;
+          const uint32_t bytes = static_cast<uint32_t>(block_bytes - off < kGatherChunk ? block_bytes - off : kGatherChunk);
           // the store that last read this slot was committed kSlots - kLag - 1 = 1 group ago
           asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          mbar_expect_tx(bar_g + 8 * slot, bytes);
+          mbar_expect_tx(bar_g + 8 * ld.slot, bytes);
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-              ::"r"(smem_a + slot * kGatherChunk), "l"(src), "r"(bytes), "r"(bar_g + 8 * slot) : "memory");
+              ::"r"(smem_a + ld.slot * kGatherChunk), "l"(ld.src + off), "r"(bytes), "r"(bar_g + 8 * ld.slot) : "memory");
+          advance(ld);
         }
-        const long long j = it - kLag;
-        if (j >= 0) {
-          const char* src; char* dst; uint32_t bytes; int mb; bool last;
-          locate(j, src, dst, bytes, mb, last);
-          const int slot = static_cast<int>(j % kSlots);
-          if (!mbar_wait(bar_g + 8 * slot, static_cast<uint32_t>((j / kSlots) & 1), abort_flag)) {
+        if (it >= kLag) {
+          const long long off = static_cast<long long>(st.ch) * kGatherChunk;
+          const uint32_t bytes = static_cast<uint32_t>(block_bytes - off < kGatherChunk ? block_bytes - off : kGatherChunk);
+          if (!mbar_wait(bar_g + 8 * st.slot, st.parity, abort_flag)) {
             if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
             ok = false;
             break;
           }
           asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                       ::"l"(dst), "r"(smem_a + slot * kGatherChunk), "r"(bytes) : "memory");
+                       ::"l"(st.dst + off), "r"(smem_a + st.slot * kGatherChunk), "r"(bytes) : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          if (last) {  // the whole row block has landed: publish it to the producers of every CTA
+          if (st.ch == chunks - 1) {  // the whole block has landed: publish it to the producers of every CTA
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async;" ::: "memory");
             __threadfence();
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(args.ag_flags + mb), "r"(args.ag_seq) : "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(args.ag_flags + st.mb), "r"(args.ag_seq) : "memory");
           }
+          advance(st);
         }
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -340,6 +355,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      unsigned long long landed = 0ull;  // mode 1: K slabs (< 64) already seen complete
+      auto wait_block = [&](int idx) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (true) {
+          unsigned int f;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(args.ag_flags + idx) : "memory");
+          if (f == args.ag_seq) break;
+          if (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
+            return false;
+          }
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // bulk-copy writes -> TMA reads
+        return true;
+      };
+      const bool ag_b = args.ag_world > 1 && args.ag_mode == 1;
+      const int ag_per_rank = args.ag_world > 1 ? args.ag_rows / (ag_b ? BK : BM) : 1;
+      const int ag_lo = args.ag_rank * ag_per_rank, ag_hi = ag_lo + ag_per_rank;  // this rank's own blocks
       for (long long t = tile0; t < num_tiles && ok; t += tstride) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
@@ -349,28 +383,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         if (bb < 0) continue;  // padding row block of a grouped product: no tile
         const int ab = args.a_bcast ? 0 : b;
         const int bbatch = args.b_bcast ? 0 : bb;
-        if (args.ag_world > 1 && mb * BM / args.ag_rows != args.ag_rank) {
-          // remote row block: wait (bounded) until the gather warp of some CTA has landed it locally
-          const unsigned long long t0 = globaltimer_ns();
-          bool ready = true;
-          while (true) {
-            unsigned int f;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(args.ag_flags + mb) : "memory");
-            if (f == args.ag_seq) break;
-            if (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs) {
-              *abort_flag = 1;
-              if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
-              ready = false;
-              break;
-            }
-          }
-          if (!ready) {
+        if (args.ag_world > 1 && args.ag_mode == 0 && (mb < ag_lo || mb >= ag_hi)) {
+          // remote row block: wait (bounded) until a gather CTA has landed it locally
+          if (!wait_block(mb)) {
             ok = false;
             break;
           }
-          asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes -> TMA reads
         }
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        for (int kbi = kb_lo; kbi < kb_hi; ++kbi) {
+          int kb = kbi;
+          if (ag_b) {  // this rank's own K slabs first, then the peers' in the order they arrive
+            kb = kbi + ag_lo;
+            if (kb >= args.kblocks0) kb -= args.kblocks0;
+            if ((kb < ag_lo || kb >= ag_hi) && !(kb < 64 && ((landed >> kb) & 1ull))) {
+              if (!wait_block(kb)) {
+                ok = false;
+                break;
+              }
+              if (kb < 64) landed |= 1ull << kb;
+            }
+          }
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
             if (args.status) atomicCAS(args.status, 0, kTimeoutProducer);
             ok = false;
@@ -818,7 +850,7 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
     // every CTA must be resident (producers wait on blocks that gather CTAs deliver): one per SM
     if (max_ctas > 0 && max_ctas < g_num_sms) return kBadArgument;
     grid = g_num_sms;
-    int g = args.ag_gather_ctas > 0 ? args.ag_gather_ctas : 16;
+    int g = args.ag_gather_ctas > 0 ? args.ag_gather_ctas : (args.ag_mode == 1 ? 8 : 16);
     if (g > grid / 2) g = grid / 2;
     launch_args.ag_gather_ctas = g;
   }
@@ -867,6 +899,8 @@ struct PdGemmCall {
   int rs_world; int rs_rows; void* rs_out[8];
   // all-gather -> GEMM: ag_src[r] = rank r's A shard [ag_rows, K0]; A0 is the local full buffer
   int ag_world; int ag_rank; int ag_rows; const void* ag_src[8]; unsigned int* ag_flags; unsigned int ag_seq;
+  // ag_mode 1: ag_src[r] = rank r's K slab [ag_rows, N] of the MN-major B operand; B0 is the local full buffer
+  int ag_mode; int ag_gather_ctas;
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -901,15 +935,24 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.ag_world = c->ag_world; a.ag_rank = c->ag_rank; a.ag_rows = c->ag_rows;
   a.ag_dst = const_cast<void*>(c->A0); a.ag_ld = c->lda0; a.ag_k = c->K0; a.ag_flags = c->ag_flags; a.ag_seq = c->ag_seq;
   for (int r = 0; r < kMaxPeers; ++r) a.ag_src[r] = c->ag_src[r];
-  a.ag_gather_ctas = 0;
+  a.ag_gather_ctas = c->ag_gather_ctas;
+  a.ag_mode = c->ag_mode;
+  if (c->ag_world > 1 && c->ag_mode == 1) {
+    a.ag_dst = const_cast<void*>(c->B0); a.ag_ld = c->ldb0; a.ag_k = c->N;
+  }
   if (c->rs_world > 1) {
     if (c->rs_world > kMaxPeers || !c->out_fp32 || c->epi != EPI_PLAIN || c->batch != 1 || (c->rs_rows % BM) != 0 ||
         c->rs_rows * c->rs_world < c->M)
       return kBadArgument;
   }
-  if (c->ag_world > 1) {
+  if (c->ag_world > 1 && c->ag_mode == 0) {
     if (c->ag_world > kMaxPeers || c->a_mn0 || c->batch != 1 || (c->ag_rows % BM) != 0 || (c->K0 % 8) != 0 ||
         c->ag_rows * c->ag_world != c->M || c->ag_flags == nullptr || a.split_k != 1 || c->lda0 != c->K0)
+      return kBadArgument;
+  } else if (c->ag_world > 1) {
+    if (c->ag_world > kMaxPeers || c->ag_mode != 1 || !c->b_mn0 || c->batch != 1 || c->K1 != 0 ||
+        (c->ag_rows % BK) != 0 || (c->N % 8) != 0 || c->ag_rows * c->ag_world != c->K0 || c->ag_flags == nullptr ||
+        a.split_k != 1 || c->ldb0 != c->N || c->bgroup_of_mblock != nullptr || c->kblock_range != nullptr)
       return kBadArgument;
   }
   if (c->epi == EPI_FAITH) {

@@ -47,7 +47,7 @@ class PdGemmCall(C.Structure):
         ("b_groups", C.c_int),
         ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
-        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint),
+        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int),
     ]  # fmt: skip
 
 
@@ -158,6 +158,8 @@ def gemm(
     b_bcast: bool = False,
     rs: tuple[list[int], int] | None = None,
     ag: tuple[list[int], int, int, torch.Tensor, int] | None = None,
+    ag_b: tuple[list[int], int, int, torch.Tensor, int] | None = None,
+    ag_gather_ctas: int = 0,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -241,6 +243,14 @@ def gemm(
         for i, ptr in enumerate(ptrs):
             call.ag_src[i] = ptr
         call.ag_flags, call.ag_seq = flags.data_ptr(), seq & 0xFFFFFFFF
+    if ag_b is not None:  # the same for K slabs of the MN-major B operand (rows per rank = K rows)
+        ptrs, rank, rows, flags, seq = ag_b
+        assert ag is None and flags.dtype == torch.int32 and flags.numel() >= (K0 + 63) // 64
+        call.ag_world, call.ag_rank, call.ag_rows, call.ag_mode = len(ptrs), rank, rows, 1
+        for i, ptr in enumerate(ptrs):
+            call.ag_src[i] = ptr
+        call.ag_flags, call.ag_seq = flags.data_ptr(), seq & 0xFFFFFFFF
+    call.ag_gather_ctas = ag_gather_ctas
     rc = lib().pd_gemm(C.byref(call), current_stream_ptr())
     count_launch()
     if rc != 0:

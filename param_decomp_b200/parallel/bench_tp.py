@@ -66,10 +66,28 @@ def main() -> None:
         "allgather_gemm fused": lambda: tp.allgather_gemm(ws, x, v, out, b_mn=True),
         "allgather_gemm nccl": lambda: tp.allgather_gemm_nccl(dist.group.WORLD, x, v, out, b_mn=True),
     }
+    xs = torch.randn(M, d, device=dev).to(bf)
+    v_loc = (torch.randn(d // world, Cc, device=dev) / d**0.5).to(bf)
+    ci = torch.rand(M, Cc, device=dev).to(bf)
+    mask_kw = dict(epi=native.EPI_MASK_FWD, ci=ci, seed=1, rng_stream=1)
+    cases["allgather_weight_gemm fused (mask epilogue)"] = lambda: tp.allgather_weight_gemm(ws, xs, v_loc, out, **mask_kw)
+    cases["allgather_weight_gemm fused, shard already published"] = lambda: tp.allgather_weight_gemm(
+        ws, xs, v_loc, out, publish=False, **mask_kw)
+    cases["allgather_weight_gemm fused, 16 gather CTAs"] = lambda: tp.allgather_weight_gemm(
+        ws, xs, v_loc, out, publish=False, ag_gather_ctas=16, **mask_kw)
+    v_all = (torch.randn(d, Cc, device=dev) / d**0.5).to(bf)
+    cases["masked x V with a resident weight (no collective)"] = lambda: native.gemm(xs, v_all, out, b_mn=True, **mask_kw)
+    cases["allgather_weight_gemm nccl (mask epilogue)"] = lambda: tp.allgather_weight_gemm_nccl(
+        dist.group.WORLD, xs, v_loc, out, **mask_kw)
     for name, fn in cases.items():
         ms = _time(fn, args.iters, flush)
         flops = 2.0 * M * (Cc // world) * d if "reduce" in name else 2.0 * M * d * Cc
-        link_bytes = (M * d * 4 * (world - 1) / world) if "reduce" in name else (M // world * d * 2 * (world - 1))
+        if "reduce" in name:
+            link_bytes = M * d * 4 * (world - 1) / world
+        elif "weight" in name:
+            link_bytes = d // world * Cc * 2 * (world - 1)
+        else:
+            link_bytes = M // world * d * 2 * (world - 1)
         if rank == 0:
             print(json.dumps({"case": name, "world": world, "ms": ms, "tflops_per_gpu": flops / ms / 1e9,
                               "nvlink_gb_per_s_per_gpu": link_bytes / ms / 1e6, "M": M, "C": Cc, "d": d}))

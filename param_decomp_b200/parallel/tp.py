@@ -10,7 +10,12 @@
     per GPU - and releases it with a flag; the TMA producer waits (bounded) on the flag of the block it
     is about to load, and tiles are rasterised so the local blocks are consumed first while remote
     ones stream in. tcgen05 is fed by local, non-multicast TMA only.
-Both have NCCL twins (`*_nccl`) that serve as oracle and as the measured baseline.
+  * `allgather_weight_gemm`: `Y = X W_full` where the weight (`V [d_in, C]`, row-sharded over the
+    fsdp ranks) lives 1/W per GPU. A few CTAs bulk-copy the peers' 64-row K slabs into the local
+    full-size buffer; the TMA producer walks K starting at this rank's own slab and waits (bounded)
+    on a slab's flag only the first time it needs it. Any epilogue works, so this is how the masked
+    `x V` product consumes component shards without a separate all-gather.
+All have NCCL twins (`*_nccl`) that serve as oracle and as the measured baseline.
 
 Reference behaviour covered: the tp all-reduce / reduce-scatter of row-linear outputs and of the
 `(...)@U` contraction over `C / tp`, and the all-gather of sequence-parallel activations
@@ -53,7 +58,8 @@ class TPWorkspace:
         self.flags, self.flag_ptrs = symmetric_empty(8, torch.int32, self.device, self.group)
         self.flags.zero_()
         self.ag_full = torch.empty(self.max_rows * self.max_cols, device=self.device, dtype=torch.bfloat16)
-        self.ag_flags = torch.zeros((self.max_rows + 127) // 128, device=self.device, dtype=torch.int32)
+        self.ag_flags = torch.zeros(max((self.max_rows + 127) // 128, 64), device=self.device, dtype=torch.int32)
+        self.w_buf = self.w_ptrs = self.w_full = None
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
 
@@ -115,6 +121,34 @@ def allgather_gemm(ws: TPWorkspace, a_local: Tensor, b: Tensor, out: Tensor, *, 
     ws._ag_seq += 1
     nv.gemm(full, b, out, b_mn=b_mn, ag=(ws.ag_ptrs, ws.rank, rows, ws.ag_flags, ws._ag_seq), **kw)
     ws.barrier()  # nobody overwrites its shard while a peer may still be reading it
+    return out
+
+
+def allgather_weight_gemm(ws: TPWorkspace, x: Tensor, w_local: Tensor, out: Tensor, publish: bool = True, **kw) -> Tensor:
+    """`x [M, K]`, `w_local [K / W, N]` bf16 (this rank's K rows of the MN-major weight);
+    `out = x @ all_gather(w_local)`; keyword arguments select the epilogue (e.g. the mask epilogue).
+    `publish=False` re-uses the shard already sitting in the symmetric buffer (same weights, next draw)."""
+    kr, N = w_local.shape
+    K = kr * ws.world
+    assert kr % 64 == 0 and N % 8 == 0 and x.shape[1] == K
+    if ws.w_buf is None or ws.w_buf.numel() < kr * N:
+        ws.w_buf, ws.w_ptrs = symmetric_empty(kr * N, torch.bfloat16, ws.device, ws.group)
+        ws.w_full = torch.empty(K * N, device=ws.device, dtype=torch.bfloat16)
+    full = ws.w_full[: K * N].view(K, N)
+    if publish:
+        ws.w_buf[: kr * N].view(kr, N).copy_(w_local)
+        full[ws.rank * kr:(ws.rank + 1) * kr].copy_(w_local)
+        ws.barrier()
+    ws._ag_seq += 1
+    nv.gemm(x, full, out, b_mn=True, ag_b=(ws.w_ptrs, ws.rank, kr, ws.ag_flags, ws._ag_seq), **kw)
+    return out
+
+
+def allgather_weight_gemm_nccl(group, x: Tensor, w_local: Tensor, out: Tensor, **kw) -> Tensor:
+    world = dist.get_world_size(group)
+    full = torch.empty(w_local.shape[0] * world, w_local.shape[1], device=x.device, dtype=w_local.dtype)
+    dist.all_gather_into_tensor(full, w_local.contiguous(), group=group)
+    nv.gemm(x, full, out, b_mn=True, **kw)
     return out
 
 

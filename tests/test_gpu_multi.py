@@ -159,6 +159,20 @@ def _tp_worker(rank: int, world: int, port: int, out):
         torch.cuda.synchronize()
         want = a_full.float() @ b_full.float().T
         res[f"ag{rep}"] = float((o.float() - want).norm() / want.norm())
+    # all-gather of a K-sharded weight inside the masked `x V` product (mask epilogue intact)
+    Cc = 512
+    v_full = (torch.randn(K, Cc, generator=g, device="cuda") / K**0.5).to(bf)
+    ci = torch.rand(M, Cc, generator=g, device="cuda").to(bf)
+    kr = K // world
+    for rep in range(2):
+        A1 = torch.zeros(M, Cc, device="cuda", dtype=bf)
+        tp.allgather_weight_gemm(ws, a_full, v_full[rank * kr:(rank + 1) * kr].contiguous(), A1, publish=rep == 0,
+                                 epi=native.EPI_MASK_FWD, ci=ci, seed=7, rng_stream=3)
+        A2 = torch.zeros(M, Cc, device="cuda", dtype=bf)
+        native.gemm(a_full, v_full, A2, b_mn=True, epi=native.EPI_MASK_FWD, ci=ci, seed=7, rng_stream=3)
+        torch.cuda.synchronize()
+        res[f"agw{rep}"] = float((A1.float() - A2.float()).norm() / A2.float().norm())
+    ws.barrier()
     native.check_status()
     out[rank] = res
     dist.barrier()
@@ -172,4 +186,6 @@ def test_fused_tp_gemms_two_gpus():
     mp.spawn(_tp_worker, args=(world, port, out), nprocs=world, join=True)
     for r in range(world):
         for k, v in out[r].items():
-            assert v < (1e-5 if k.startswith("rs") and "nccl" not in k else 1e-2), (r, k, v)
+            # the K-sharded weight product starts its K walk at the local slab: same sum, other order
+            tol = 1e-5 if (k.startswith("rs") and "nccl" not in k) else (3e-3 if k.startswith("agw") else 1e-2)
+            assert v < tol, (r, k, v, dict(out[r]))
