@@ -190,8 +190,82 @@ __global__ void __launch_bounds__(kThreads) rs_adamw_ag_kernel(RsAdamwArgs a) {
 
 }  // namespace
 
+
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel dispatch / combine: rows travel to their owner by direct peer stores.
+//   row j of `src` (optionally row `gather[j]`: the router's permutation is applied on the fly)
+//   goes to rank dest_rank[j], row dest_row[j] of that rank's receive buffer (16-byte vectors over
+//   NVLink). Up to two payloads with the same routing move in one launch (activations and their
+//   mask rows). After its rows are stored and fenced, each block takes a ticket; the last block of
+//   the grid signals every peer and waits (bounded) for every peer's signal, so when the kernel
+//   completes the receive buffers of THIS rank are complete too. No block waits on another block,
+//   so the launch needs no co-residency.
+// Replaces the all-to-all-free "EP by activation slicing" of the reference
+// (param_decomp/routed/experts.py:28-40,864-885) on the all-to-all path.
+// ---------------------------------------------------------------------------------------------
 struct PdPeerPtrs {
   void* ptr[kMaxRanks];
+};
+
+struct ScatterArgs {
+  const uint4* src[2];
+  int vecs[2];             // 16-byte vectors per row of each payload (0 = payload unused)
+  PeerTable dst[2];        // per-rank receive buffers of each payload
+  const long long* gather; // [n] source row of job j, or null for j
+  const int* dest_rank;    // [n]
+  const long long* dest_row;  // [n]
+  long long n;
+  PeerTable flags;
+  int rank, world;
+  unsigned int seq;
+  unsigned int* ticket;    // local counter, zero between launches
+  int* status;
+  unsigned long long limit_ns;
+};
+
+__global__ void __launch_bounds__(256) ep_scatter_rows_kernel(ScatterArgs a) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long j = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); j < a.n;
+       j += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const long long srow = a.gather ? a.gather[j] : j;
+    const int r = a.dest_rank[j];
+    const long long drow = a.dest_row[j];
+    if (r < 0 || r >= a.world) continue;  // job not sent anywhere
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      const int vecs = a.vecs[p];
+      if (vecs == 0) continue;
+      const uint4* s = a.src[p] + srow * vecs;
+      uint4* d = static_cast<uint4*>(a.dst[p].ptr[r]) + drow * vecs;
+      for (int v = lane; v < vecs; v += 32) d[v] = s[v];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(a.ticket, 1u);
+    if (t == gridDim.x - 1) {  // every block of this rank has stored and fenced its rows
+      *a.ticket = 0u;
+      peer_barrier(a.flags, a.rank, a.world, a.seq, a.status, a.limit_ns);
+    }
+  }
+}
+
+struct PdEpScatterCall {
+  const void* src[2];
+  int row_bytes[2];
+  PdPeerPtrs dst[2];
+  const long long* gather;
+  const int* dest_rank;
+  const long long* dest_row;
+  long long n;
+  PdPeerPtrs flags;
+  int rank, world;
+  unsigned int seq;
+  unsigned int* ticket;
+  int* status;
+  double limit_s;
 };
 
 extern "C" int pd_peer_barrier(const PdPeerPtrs* flags, int rank, int world, unsigned int seq, int* status,
@@ -241,4 +315,24 @@ extern "C" int pd_rs_adamw_ag(const PdRsAdamwCall* c, void* stream) {
   cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(rs_adamw_ag_kernel), dim3(blocks),
                                               dim3(kThreads), params, 0, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : 100 + static_cast<int>(e);
+}
+
+extern "C" int pd_ep_scatter_rows(const PdEpScatterCall* c, void* stream) {
+  if (c->world < 1 || c->world > kMaxRanks || c->n < 0 || c->ticket == nullptr) return pd::kBadArgument;
+  ScatterArgs a;
+  for (int p = 0; p < 2; ++p) {
+    if (c->row_bytes[p] % 16 != 0 || (reinterpret_cast<uintptr_t>(c->src[p]) & 15)) return pd::kBadArgument;
+    a.src[p] = static_cast<const uint4*>(c->src[p]);
+    a.vecs[p] = c->src[p] ? c->row_bytes[p] / 16 : 0;
+    for (int r = 0; r < kMaxRanks; ++r) a.dst[p].ptr[r] = c->dst[p].ptr[r];
+  }
+  for (int r = 0; r < kMaxRanks; ++r) a.flags.ptr[r] = c->flags.ptr[r];
+  a.gather = c->gather; a.dest_rank = c->dest_rank; a.dest_row = c->dest_row; a.n = c->n;
+  a.rank = c->rank; a.world = c->world; a.seq = c->seq; a.ticket = c->ticket; a.status = c->status;
+  a.limit_ns = static_cast<unsigned long long>(c->limit_s * 1e9);
+  long long blocks = (c->n + 7) / 8;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  ep_scatter_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

@@ -189,3 +189,69 @@ def test_fused_tp_gemms_two_gpus():
             # the K-sharded weight product starts its K walk at the local slab: same sum, other order
             tol = 1e-5 if (k.startswith("rs") and "nccl" not in k) else (3e-3 if k.startswith("agw") else 1e-2)
             assert v < tol, (r, k, v, dict(out[r]))
+
+
+def _ep_worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from param_decomp_b200.config.experiments import MoeCSpec, TransformerArchConfig
+    from param_decomp_b200.core import masking
+    from param_decomp_b200.core.components import ComponentStacks, prepare_compute_weights
+    from param_decomp_b200.core.rng import StepKey
+    from param_decomp_b200.models import moe
+    from param_decomp_b200.models.transformer import LMBatch
+    from param_decomp_b200.ops import native
+    from param_decomp_b200.parallel.ep import ExpertParallel
+
+    arch = TransformerArchConfig(family="moe", n_layer=2, d_model=64, n_head=2, d_ff=32, vocab_size=50, n_experts=6,
+                                 experts_per_token=2)
+    c = 8
+    sites = MoeCSpec(layers={"kind": "all"}, cs={k: 6 * c for k in ("experts_gate", "experts_up", "experts_down")})
+
+    class Target:
+        attention_implementation = "xla"
+
+    dev = torch.device("cuda", rank)
+    B, T = 4, 16
+    g = torch.Generator().manual_seed(9)
+    tokens = torch.randint(0, 50, (B, T), generator=g)[rank * 2:(rank + 1) * 2].to(dev)
+    res = {}
+    for transport in ("collective", "p2p"):
+        ep = ExpertParallel(dist.group.WORLD, arch.n_experts, mode="all_to_all", transport=transport)
+        weights = {k: v.to(dev) for k, v in moe.random_init_moe_weights(arch, 0, torch.float32).items()}
+        model = moe.build_moe_model(arch, weights, sites, Target, "eager_torch", ep=ep)
+        stacks = ComponentStacks(model.sites)
+        stacks.init_random(torch.Generator().manual_seed(5 + rank))
+        stacks.to(dev)
+        gen = torch.Generator().manual_seed(3)
+        ci = {s.name: torch.rand(2, T, 2 * c, generator=gen).to(dev) for s in model.sites}
+        batch = LMBatch(tokens)
+        clean = model.clean_forward(batch)
+        masks = masking.stochastic_masks(ci, StepKey(1, 2), 0, 0, site_index={s.name: i for i, s in enumerate(model.sites)},
+                                         row_offset=rank * 2 * T, lazy=False)
+        w = prepare_compute_weights(stacks, torch.float32)
+        y = model.masked_forward(w, batch, masks, clean=clean).output
+        y.pow(2).sum().backward()
+        torch.cuda.synchronize()
+        res[transport] = (y.detach().cpu(), {k: v.grad.detach().cpu().clone() for k, v in stacks.V.items()})
+    native.check_status()
+    out[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ep_p2p_matches_collective_two_gpus():
+    _need_two_gpus()
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_ep_worker, args=(world, port, out), nprocs=world, join=True)
+    for r in range(world):
+        ya, ga = out[r]["collective"]
+        yb, gb = out[r]["p2p"]
+        assert torch.equal(ya, yb)
+        for k in ga:
+            assert torch.allclose(ga[k], gb[k], atol=1e-6), k
