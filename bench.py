@@ -195,12 +195,15 @@ def main() -> None:
             "vs_baseline": None, "dtype": "bf16", "impl": "ours",
             "data": "synthetic Zipf(1.1) token ids, seeded random-init target weights",
             "config": {
-                "model": f"llama-style {arch.n_layer}L d{arch.d_model} h{arch.n_head} ff{arch.d_ff} vocab{arch.vocab_size}",
+                "model": (f"{arch.family} {arch.n_layer}L d{arch.d_model} h{arch.n_head} ff{arch.d_ff} vocab{arch.vocab_size}"
+                          + (f" experts{arch.n_experts} top{arch.experts_per_token}" if arch.family == "moe" else "")),
+                "config_file": str(args.config.relative_to(ROOT)) if args.config.is_relative_to(ROOT) else str(args.config),
                 "global_batch": cfg.pd.batch_size, "seq_len": cfg.data.seq_len,
                 "parallelism": (f"dp{world} ({'zero1 ' + args.optim if shard_backend else 'ddp all-reduce'})"
                                 if world > 1 else "single"),
-                "decomposition": "q,k,v,o,gate,up,down x 4 layers, C=4096 each; layerwise MLP CI fn (hidden 512)",
-                "losses": "faithfulness + smooth-L0 minimality + KL stochastic recon x2 samples",
+                "decomposition": (", ".join(f"{k}:{v}" for k, v in cfg.decomposition.sites.cs.items())
+                                  + f" components per matrix x {arch.n_layer} layers; CI fn {cfg.decomposition.ci.type}"),
+                "losses": ", ".join(type(m).__name__ for m in cfg.pd.loss_metrics),
                 "l2": "per-step working set (>4 GB parameters and optimizer state, >20 GB activations) "
                       "exceeds the 126 MB L2; no explicit flush between steps",
             },

@@ -69,6 +69,11 @@ def lib() -> C.CDLL:
 _LAUNCHES = 0
 
 
+@lru_cache(maxsize=1)
+def _pd_gemm():
+    return lib().pd_gemm
+
+
 def count_launch(n: int = 1) -> None:
     """Every launch of one of this library's kernels is counted (reported by the benchmark)."""
     global _LAUNCHES
@@ -94,7 +99,8 @@ def available() -> bool:
 
 
 def current_stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the current CUDA stream (the C accessor: this runs once per kernel launch)."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 @lru_cache(maxsize=8)
@@ -104,7 +110,12 @@ def _status_word(device_index: int) -> torch.Tensor:
 
 def status_word() -> torch.Tensor:
     """The per-device int32 the kernels report a timed-out wait in (0 = no error)."""
-    return _status_word(torch.cuda.current_device())
+    return _status_word(torch._C._cuda_getDevice())
+
+
+@lru_cache(maxsize=8)
+def _status_ptr(device_index: int) -> int:
+    return _status_word(device_index).data_ptr()
 
 
 def check_status() -> None:
@@ -219,7 +230,7 @@ def gemm(
     call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
     call.rng_row_offset = row_offset & 0xFFFFFFFF
     call.split_k, call.bn, call.max_ctas = split_k, bn, max_ctas
-    call.status = status_word().data_ptr()
+    call.status = _status_ptr(torch._C._cuda_getDevice())
     if bgroup_of_mblock is not None:
         assert bgroup_of_mblock.dtype == torch.int32 and bgroup_of_mblock.numel() == (M + 127) // 128
         call.bgroup_of_mblock = bgroup_of_mblock.data_ptr()
@@ -251,8 +262,9 @@ def gemm(
             call.ag_src[i] = ptr
         call.ag_flags, call.ag_seq = flags.data_ptr(), seq & 0xFFFFFFFF
     call.ag_gather_ctas = ag_gather_ctas
-    rc = lib().pd_gemm(C.byref(call), current_stream_ptr())
-    count_launch()
+    rc = _pd_gemm()(C.byref(call), current_stream_ptr())
+    global _LAUNCHES
+    _LAUNCHES += 1
     if rc != 0:
         raise NativeError(f"pd_gemm refused the call (code {rc})")
     return out
