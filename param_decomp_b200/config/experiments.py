@@ -200,7 +200,7 @@ class TransformerArchConfig(BaseConfig):
     """Inline architecture of a decoder-only LM (addition: the reference always derives this from a
     checkpoint). Covers Llama / Qwen3 / LlamaSimpleMLP shapes and the plain top-k MoE."""
 
-    family: Literal["glu_transformer", "simple_mlp", "moe"] = "glu_transformer"
+    family: Literal["glu_transformer", "simple_mlp", "moe", "qwen35_moe"] = "glu_transformer"
     n_layer: PositiveInt
     d_model: PositiveInt
     n_head: PositiveInt
@@ -217,13 +217,33 @@ class TransformerArchConfig(BaseConfig):
     n_experts: PositiveInt | None = None
     experts_per_token: PositiveInt | None = None
     norm_topk_prob: bool = True
+    # qwen35_moe only (hybrid decoder: gated-DeltaNet layers, every `interval`-th layer gated full
+    # attention, top-k MoE + shared expert in every layer; `d_ff` = per-expert hidden width)
+    full_attention_interval: PositiveInt | None = None
+    partial_rotary_factor: PositiveFloat = 1.0
+    linear_num_key_heads: PositiveInt | None = None
+    linear_key_head_dim: PositiveInt | None = None
+    linear_num_value_heads: PositiveInt | None = None
+    linear_value_head_dim: PositiveInt | None = None
+    linear_conv_kernel_dim: PositiveInt = 4
+    shared_expert_intermediate: PositiveInt | None = None
+    delta_rule_kernel: Literal["sequential", "chunkwise", "cuda"] = "chunkwise"
 
     @model_validator(mode="after")
     def _check(self) -> Self:
         kv = self.n_kv_head or self.n_head
         assert self.n_head % kv == 0, "n_head must be a multiple of n_kv_head"
-        if self.family == "moe":
+        if self.family in ("moe", "qwen35_moe"):
             assert self.n_experts and self.experts_per_token, "moe needs n_experts and experts_per_token"
+        if self.family == "qwen35_moe":
+            iv = self.full_attention_interval
+            assert iv and iv >= 2 and self.n_layer % iv == 0, "n_layer must be a multiple of full_attention_interval >= 2"
+            for f in ("linear_num_key_heads", "linear_key_head_dim", "linear_num_value_heads", "linear_value_head_dim",
+                      "shared_expert_intermediate", "head_dim"):
+                assert getattr(self, f), f"qwen35_moe needs {f}"
+            assert self.linear_num_value_heads % self.linear_num_key_heads == 0
+            rot = self.head_dim * self.partial_rotary_factor
+            assert rot == int(rot) and int(rot) % 2 == 0, "rotary width must be an even integer"
         return self
 
 

@@ -54,6 +54,10 @@ def load_target_weights(cfg: X.LMTargetConfig, data_root: Path | None, device) -
     spec = cfg.spec
     dtype = _dtype(cfg.weights_dtype)
     if isinstance(spec, X.RandomInitTarget):
+        if spec.arch.family == "qwen35_moe":
+            from param_decomp_b200.models.qwen35 import random_init_qwen35_weights
+
+            return spec.arch, random_init_qwen35_weights(spec.arch, spec.seed, dtype, device)
         if spec.arch.family == "moe":
             from param_decomp_b200.models.moe import random_init_moe_weights
 
@@ -84,7 +88,11 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
     edge = cfg.target.output_edge
     n_chunks = edge.n_vocab_chunks if isinstance(edge, X.StreamedOutputEdgeConfig) else None
     backend = cfg.runtime.backend if torch.device(device).type == "cuda" else "eager_torch"
-    if arch.family == "moe" or isinstance(sites_cfg, (X.MoeCSpec, X.Qwen36MoeCSpec)):
+    if arch.family == "qwen35_moe":
+        from param_decomp_b200.models import qwen35
+
+        model = qwen35.build_qwen35_model(arch, weights, sites_cfg, cfg.target, backend)
+    elif arch.family == "moe" or isinstance(sites_cfg, (X.MoeCSpec, X.Qwen36MoeCSpec)):
         from param_decomp_b200.models import moe
 
         model = moe.build_moe_model(arch, weights, sites_cfg, cfg.target, backend, rank, world)

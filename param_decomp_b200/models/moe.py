@@ -105,6 +105,9 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         a = self.arch
         return {f"attn_in.{layer}": a.d_model, f"attn_out.{layer}": a.n_head * self.head_dim, f"mlp_in.{layer}": a.d_model}
 
+    def expert_site_names(self, layer: int) -> list[str]:
+        return [tf.site_name("moe", layer, k) for k in EXPERT_KINDS]
+
     # -- expert bank --------------------------------------------------------------------------------
     def _expert_site(self, name: str, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int],
                      weights: ComputeWeights | None, masks: Masks | None, token_of_job: Tensor,

@@ -150,3 +150,124 @@ def causal_depthwise_conv1d_silu(x: Tensor, weight: Tensor, bias: Tensor | None 
     xp = F.pad(x.transpose(1, 2).float(), (K - 1, 0))
     y = F.conv1d(xp, weight.float().unsqueeze(1), bias.float() if bias is not None else None, groups=D)
     return F.silu(y).transpose(1, 2).to(x.dtype)
+
+
+# ---- Qwen3.5 (gated DeltaNet) pieces ------------------------------------------------------------
+# Parity: param_decomp/target_ports/qwen3_5_moe.py:33-74 (norms, l2norm, conv), :89-158 (sequential
+# rule), :187-293 (chunkwise WY form), :296-312 (partial RoPE).
+
+GATED_DELTA_CHUNK = 64
+
+
+def l2norm(x: Tensor, eps: float = 1e-6) -> Tensor:
+    """Unit-normalise the last axis; eps joins the SUM of squares inside the rsqrt."""
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def apply_partial_rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    """RoPE on the first `cos.shape[-1]` dims of each head, pass-through on the rest.
+    `x [B, T, H, hd]`, `cos/sin [B|1, T, r]`."""
+    r = cos.shape[-1]
+    rot, rest = x[..., :r], x[..., r:]
+    c, s = cos.unsqueeze(2), sin.unsqueeze(2)
+    out = (rot.float() * c + rotate_half(rot.float()) * s).to(x.dtype)
+    return torch.cat([out, rest], dim=-1)
+
+
+def _delta_rule_sequential(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor) -> Tensor:
+    """Per-token recurrence (the oracle). fp32 `[B, T, H, *]` inputs, q already scaled."""
+    B, T, H, dk = q.shape
+    dv = v.shape[-1]
+    S = q.new_zeros(B, H, dk, dv)
+    outs = []
+    for t in range(T):
+        S = S * torch.exp(g[:, t])[..., None, None]
+        mem = torch.einsum("bhkv,bhk->bhv", S, k[:, t])
+        delta = (v[:, t] - mem) * beta[:, t][..., None]
+        S = S + torch.einsum("bhk,bhv->bhkv", k[:, t], delta)
+        outs.append(torch.einsum("bhkv,bhk->bhv", S, q[:, t]))
+    return torch.stack(outs, dim=1)
+
+
+def _solve_unit_lower(a_strict: Tensor, rhs: Tensor, block: int = 8) -> Tensor:
+    """`(I + A) x = rhs`, `A` strictly lower triangular: block forward substitution with small
+    diagonal blocks inverted by the (exact, nilpotent) Neumann series. Substitution keeps every
+    partial result a prefix of the bounded solution, unlike a full log-depth inverse."""
+    c = a_strict.shape[-1]
+    block = min(block, c)
+    assert c % block == 0
+    eye = torch.eye(block, dtype=a_strict.dtype, device=a_strict.device)
+    xs: list[Tensor] = []
+    for i in range(c // block):
+        sl = slice(i * block, (i + 1) * block)
+        acc = rhs[..., sl, :]
+        for j, xj in enumerate(xs):
+            acc = acc - a_strict[..., sl, j * block:(j + 1) * block] @ xj
+        d = a_strict[..., sl, sl]
+        inv, term = eye - d, -d
+        for _ in range(block - 2):  # (I + D)^-1 = sum_j (-D)^j, D^block = 0
+            term = term @ (-d)
+            inv = inv + term
+        xs.append(inv @ acc)
+    return torch.cat(xs, dim=-2)
+
+
+def _delta_rule_chunkwise(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, chunk: int) -> Tensor:
+    """The same recurrence in WY form: one sequential step per `chunk` tokens."""
+    B, T, H, dk = q.shape
+    dv = v.shape[-1]
+    n = -(-T // chunk)
+    pad = n * chunk - T
+    if pad:
+        q, k, v = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (q, k, v))
+        g, beta = (F.pad(x, (0, 0, 0, pad)) for x in (g, beta))
+
+    def ch(x: Tensor) -> Tensor:  # [B, n*c, H, ...] -> [n, B, H, c, ...]
+        p = x.reshape(B, n, chunk, H, *x.shape[3:])
+        return p.permute(1, 0, 3, 2, *range(4, p.dim()))
+
+    q, k, v, g, beta = map(ch, (q, k, v, g, beta))
+    gc = g.cumsum(-1)
+    idx = torch.arange(chunk, device=q.device)
+    lower = idx[:, None] >= idx[None, :]
+    diff = gc[..., :, None] - gc[..., None, :]
+    decay = torch.where(lower, torch.exp(torch.where(lower, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
+    kb = k * beta[..., None]
+    a = (kb @ k.transpose(-1, -2) * decay).tril(-1)
+    rhs = torch.cat([v * beta[..., None], kb * torch.exp(gc)[..., None]], dim=-1)
+    solved = _solve_unit_lower(a, rhs)
+    w, u = solved[..., :dv], solved[..., dv:]
+    q_dec = q * torch.exp(gc)[..., None]
+    local = q @ k.transpose(-1, -2) * decay
+    g_last = gc[..., -1]
+    k_dec = k * torch.exp(g_last[..., None] - gc)[..., None]
+    S = q.new_zeros(B, H, dk, dv)
+    outs = []
+    for i in range(n):
+        delta = w[i] - u[i] @ S
+        outs.append(q_dec[i] @ S + local[i] @ delta)
+        S = S * torch.exp(g_last[i])[..., None, None] + k_dec[i].transpose(-1, -2) @ delta
+    out = torch.stack(outs, dim=0)  # [n, B, H, c, dv]
+    return out.permute(1, 0, 3, 2, 4).reshape(B, n * chunk, H, dv)[:, :T]
+
+
+def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, kernel: str = "chunkwise") -> Tensor:
+    """`S_t = exp(g_t) S_{t-1};  S_t += k_t (x) beta_t (v_t - S_t^T k_t);  o_t = S_t^T q_t / sqrt(dk)`.
+    `q, k [B, T, H, dk]` (already repeated to the value-head count), `v [B, T, H, dv]`, `g, beta [B, T, H]`.
+    q and k are l2-normalised in the input dtype, the recurrence runs in fp32. `kernel`:
+    `sequential` (oracle), `chunkwise` (WY form), `cuda` (the sm_100a kernel; falls back off-GPU)."""
+    in_dtype = q.dtype
+    q, k = l2norm(q), l2norm(k)
+    q = q.float() * q.shape[-1] ** -0.5
+    k, v, g, beta = k.float(), v.float(), g.float(), beta.float()
+    if kernel == "cuda" and q.is_cuda:
+        from param_decomp_b200.ops import delta_rule
+
+        if delta_rule.supported(q, v):
+            return delta_rule.gated_delta_rule(q, k, v, g, beta).to(in_dtype)
+        kernel = "chunkwise"
+    if kernel == "sequential":
+        out = _delta_rule_sequential(q, k, v, g, beta)
+    else:
+        out = _delta_rule_chunkwise(q, k, v, g, beta, GATED_DELTA_CHUNK)
+    return out.to(in_dtype)

@@ -202,7 +202,7 @@ class ExpertParallel:
         x_recv = ship(xt[token_of_job])
         e_recv = _AllToAll.apply((expert_of_job % self.e_loc)[order], send_l, recv_l, self.group)
         # per-job mask payload of the three expert sites
-        names = [f"layers.{layer}.mlp.experts_{k}" for k in ("gate", "up", "down")]
+        names = model.expert_site_names(layer)
         job_masks: dict[str, SiteMask] = {}
         if masks is not None:
             for name in names:
@@ -270,7 +270,7 @@ class ExpertParallel:
             return out[:, :cols]
 
         x_recv = ship(xt, token_of_job)  # the router's gather is applied by the kernel
-        names = [f"layers.{layer}.mlp.experts_{k}" for k in ("gate", "up", "down")]
+        names = model.expert_site_names(layer)
         job_masks: dict[str, SiteMask] = {}
         if masks is not None:
             for name in names:
@@ -313,7 +313,7 @@ class ExpertParallel:
             if masks is not None:
                 sub_masks = {}
                 for name, sm in masks.items():
-                    if ".experts_" not in name or f"layers.{layer}." not in name:
+                    if name not in model.expert_site_names(layer):
                         continue
                     sm = sm.materialize()
                     c = next(s for s in model.sites if s.name == name).C_block
