@@ -419,3 +419,45 @@ def test_flash_attention_matches_fp32_reference(nv, hd, H, Hkv, causal, seg):
     nv.check_status()
     for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
         assert rel(a, b) < 2e-2, (name, rel(a, b))
+
+
+@pytest.mark.parametrize("dk,dv,T", [(64, 64, 200), (128, 128, 130), (32, 32, 64)])
+def test_gated_delta_rule_kernel(nv, dk, dv, T):
+    from param_decomp_b200.models import ports
+    from param_decomp_b200.ops import delta_rule
+
+    torch.manual_seed(0)
+    B, H = 2, 3
+    q = ports.l2norm(torch.randn(B, T, H, dk, device="cuda")) * dk**-0.5
+    k = ports.l2norm(torch.randn(B, T, H, dk, device="cuda"))
+    v = torch.randn(B, T, H, dv, device="cuda")
+    g = -torch.rand(B, T, H, device="cuda") * 1.5
+    beta = torch.rand(B, T, H, device="cuda")
+    ins = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta)]
+    assert delta_rule.supported(ins[0], ins[2])
+    out = delta_rule.gated_delta_rule(*ins)
+    go = torch.randn_like(out)
+    out.backward(go)
+    ref_ins = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta)]
+    ref = ports._delta_rule_sequential(*ref_ins)
+    ref.backward(go)
+    assert rel(out, ref) < 1e-4
+    for name, a, b in zip("q k v g beta".split(), ins, ref_ins):
+        assert rel(a.grad, b.grad) < 2e-3, (name, rel(a.grad, b.grad))
+
+
+def test_causal_conv1d_silu_kernel(nv):
+    from param_decomp_b200.models import ports
+    from param_decomp_b200.ops import delta_rule
+
+    torch.manual_seed(0)
+    B, T, D, K = 2, 70, 96, 4
+    x = torch.randn(B, T, D, device="cuda").to(bf).requires_grad_(True)
+    w = (torch.randn(D, K, device="cuda") * 0.5).to(bf).requires_grad_(True)
+    y = delta_rule.causal_conv1d_silu(x, w)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2, w2 = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    y2 = ports.causal_depthwise_conv1d_silu(x2, w2)
+    y2.backward(gy.float())
+    assert rel(y, y2) < 1e-2 and rel(x.grad, x2.grad) < 1e-2 and rel(w.grad, w2.grad) < 1e-2
