@@ -251,8 +251,9 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
         v = lin(x, "attn_v").view(B, T, kv, hd)
         q, k = ports.apply_partial_rope(q, cos, sin), ports.apply_partial_rope(k, cos, sin)
         if f"attn_scores.{i}" in want:
-            captures[f"attn_scores.{i}"] = ports.attention_scores(q, k).masked_fill(
-                ~ports.attention_mask(T, True, batch.segment_ids, q.device), float("-inf"))
+            from param_decomp_b200.ops.attention_kl import capture_scores
+
+            captures[f"attn_scores.{i}"] = capture_scores(q, k, True, batch.segment_ids, self._fused(q))
         out = ports.sdpa(q.contiguous(), k.contiguous(), v.contiguous(), True, batch.segment_ids, self.attention_impl)
         return (out.float() * torch.sigmoid(gate.float())).to(x.dtype).reshape(B, T, a.n_head * hd)
 

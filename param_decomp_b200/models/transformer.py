@@ -256,8 +256,9 @@ class TransformerDecomposedModel:
         shared = batch.positions is None
         q, k = self._rope(q, cos, sin, shared), self._rope(k, cos, sin, shared)
         if f"attn_scores.{i}" in want:
-            captures[f"attn_scores.{i}"] = ports.attention_scores(q, k).masked_fill(
-                ~ports.attention_mask(T, True, batch.segment_ids, q.device), float("-inf"))
+            from param_decomp_b200.ops.attention_kl import capture_scores
+
+            captures[f"attn_scores.{i}"] = capture_scores(q, k, True, batch.segment_ids, self._fused(q))
         att = ports.sdpa(q, k, v, True, batch.segment_ids, self.attention_impl).reshape(B, T, a.n_head * self.head_dim)
         if taps is not None:
             taps[f"attn_out.{i}"] = att

@@ -461,3 +461,31 @@ def test_causal_conv1d_silu_kernel(nv):
     y2 = ports.causal_depthwise_conv1d_silu(x2, w2)
     y2.backward(gy.float())
     assert rel(y, y2) < 1e-2 and rel(x.grad, x2.grad) < 1e-2 and rel(w.grad, w2.grad) < 1e-2
+
+
+@pytest.mark.parametrize("hd,H,Hkv,seg", [(64, 4, 2, False), (128, 2, 2, True)])
+def test_streamed_attention_pattern_kl(nv, hd, H, Hkv, seg):
+    from param_decomp_b200.models import ports
+    from param_decomp_b200.ops import attention_kl as akl
+
+    torch.manual_seed(0)
+    B, T = 2, 256
+    mk = lambda h: (torch.randn(B, T, h, hd, device="cuda") * 0.7).to(bf)  # noqa: E731
+    qc, kc = mk(H), mk(Hkv)
+    qm = (qc.float() + 0.3 * torch.randn_like(qc.float())).to(bf).requires_grad_(True)
+    km = (kc.float() + 0.3 * torch.randn_like(kc.float())).to(bf).requires_grad_(True)
+    seg_ids = None
+    if seg:
+        seg_ids = (torch.arange(T, device="cuda")[None, :] >= torch.tensor([[90], [200]], device="cuda")).to(torch.int32)
+    assert akl.streamed_supported(qm, km)
+    loss = akl.attention_pattern_kl_streamed(qc, kc, qm, km, True, seg_ids)
+    loss.backward()
+    q2, k2 = qm.detach().float().requires_grad_(True), km.detach().float().requires_grad_(True)
+    mask = ports.attention_mask(T, True, seg_ids, "cuda")
+    sc = ports.attention_scores(qc.float(), kc.float()).masked_fill(~mask, float("-inf"))
+    sm = ports.attention_scores(q2, k2).masked_fill(~mask, float("-inf"))
+    ref = akl.attention_pattern_kl(sc, sm)
+    ref.backward()
+    nv.check_status()
+    assert abs(float(loss) - float(ref)) < 2e-3 * max(1.0, abs(float(ref))), (float(loss), float(ref))
+    assert rel(qm.grad, q2.grad) < 3e-2 and rel(km.grad, k2.grad) < 3e-2, (rel(qm.grad, q2.grad), rel(km.grad, k2.grad))
