@@ -85,9 +85,12 @@ def attention_pattern_recon(ctx: StepContext, state: TrainState, batch: Any, sto
 
 
 class LMEvaluation:
-    def __init__(self, cfg: E.EvalConfig, sample_eval: Callable[[int], Any]) -> None:
+    def __init__(self, cfg: E.EvalConfig, sample_eval: Callable[[int], Any], run_dir: Any = None,
+                 arithmetic_grid: Any = None) -> None:
         self.cfg = cfg
         self.sample = sample_eval
+        self.run_dir = run_dir
+        self.arithmetic_grid = arithmetic_grid  # evals.lm_ops.ArithmeticPromptGrid (needs the target's tokenizer)
 
     def is_due(self, step: int) -> bool:
         return any(self.cfg.is_due(m, step) for m in self.cfg.metrics)
@@ -103,6 +106,16 @@ class LMEvaluation:
             return attention_pattern_recon(ctx, state, batch, stochastic=False)
         if isinstance(metric, E.StochasticAttnPatternsReconLossConfig):
             return attention_pattern_recon(ctx, state, batch, stochastic=True)
+        from param_decomp_b200.evals import lm_ops
+
+        if isinstance(metric, E.RouterDivergenceConfig):
+            return lm_ops.router_divergence(ctx, state, batch, tuple(s.kind for s in metric.strategies))
+        if isinstance(metric, E.WellTemperednessConfig):
+            extra = metric.model_extra or {}
+            return lm_ops.well_temperedness(ctx, state, batch, int(extra.get("n_locations", 4)),
+                                            int(extra.get("n_components", 16)), run_dir=self.run_dir)
+        if isinstance(metric, E.ArithmeticCIGridConfig) and self.arithmetic_grid is not None:
+            return lm_ops.arithmetic_ci_grid(ctx, state, self.arithmetic_grid, metric.top_k, run_dir=self.run_dir)
         return {}
 
     def run(self, step: int, state: TrainState, ctx: StepContext) -> dict[str, Any]:

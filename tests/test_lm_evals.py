@@ -1,0 +1,56 @@
+"""Slow-tier LM evaluation operations on tiny CPU models."""
+import math
+
+import numpy as np
+import torch
+
+from param_decomp_b200.core.objective import build_objective
+from param_decomp_b200.core.run import init_train_state
+from param_decomp_b200.core.train import StepContext
+from param_decomp_b200.evals import lm_ops
+from param_decomp_b200.experiments.lm.build import build_lm_run
+from param_decomp_b200.utils import figures
+from tests.test_qwen35 import _config
+from param_decomp_b200.models import qwen35
+
+
+def _setup():
+    cs = {k: (12 if k.startswith("experts_") else 8) for k in qwen35.KIND_ORDER}
+    cfg = _config(cs)
+    run = build_lm_run(cfg, None, "cpu")
+    obj = build_objective(cfg.pd)
+    ctx = StepContext.build(run.model, obj, cfg.pd, lazy_masks=False)
+    state = init_train_state(run.model, run.ci_fn, cfg.pd, obj, torch.device("cpu"), 4, 24)
+    return run, ctx, state
+
+
+def test_router_divergence_and_well_temperedness(tmp_path):
+    run, ctx, state = _setup()
+    batch = run.sample_eval(0)
+    rd = lm_ops.router_divergence(ctx, state, batch, ("ci_masked", "stochastic"))
+    assert "RouterDivergence/ci_masked/kl" in rd and all(math.isfinite(v) for v in rd.values())
+    assert all(0.0 <= v <= 1.0 for k, v in rd.items() if "topk_kept" in k)
+    wt = lm_ops.well_temperedness(ctx, state, batch, n_locations=2, n_components=6, run_dir=tmp_path)
+    assert 0.0 <= wt["WellTemperedness/all"] <= 1.0
+    assert (tmp_path / "figures" / "well_temperedness_pre_vs_damage.png").exists()
+
+
+def test_ordering_score():
+    pre = torch.tensor([0.1, 0.5, 0.9, 1.5])
+    assert lm_ops.fraction_well_ordered_pairs(pre, pre * 2) == 1.0
+    assert lm_ops.fraction_well_ordered_pairs(pre, -pre) == 0.0
+    assert lm_ops.fraction_well_ordered_pairs(pre, torch.zeros(4)) == 0.5
+
+
+def test_arithmetic_grid_and_figures(tmp_path):
+    run, ctx, state = _setup()
+    enc = lambda s: [ord(c) % 97 for c in s]  # noqa: E731  one token per character
+    grid = lm_ops.build_arithmetic_prompt_grid(enc, [1, 2, 3], [4, 5], "add")
+    assert grid.tokens.shape == (6, 4) and grid.answers == [5, 6, 6, 7, 7, 8]
+    out = lm_ops.arithmetic_ci_grid(ctx, state, grid, top_k=4, run_dir=tmp_path)
+    assert any(k.endswith("n_alive") for k in out)
+    assert len(list((tmp_path / "figures").glob("arithmetic_ci_*.png"))) == len(run.model.sites)
+    pm, perm = lm_ops.permute_to_identity(torch.eye(4)[:, [2, 0, 3, 1]])
+    assert torch.equal(pm, torch.eye(4)) and sorted(perm.tolist()) == [0, 1, 2, 3]
+    png = figures.heatmap(np.arange(12.0).reshape(3, 4))
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and png[-8:-4] == b"IEND"
