@@ -183,6 +183,8 @@ def run_decomposition_training(
     max_steps_this_entry: int | None = None,
     profile_steps: int = 0,
     state_out: list | None = None,
+    shard_group: Any = None,
+    shard_backend: str | None = None,
 ) -> RunResult:
     collectives = collectives or DataCollectives()
     log = get_logger(collectives.rank)
@@ -190,7 +192,8 @@ def run_decomposition_training(
     ctx = StepContext.build(model, objective, pd, collectives=collectives, lazy_masks=lazy_masks, nontarget=nontarget)
     rows = batch_rows if batch_rows is not None else pd.batch_size // collectives.world_size
     state = init_train_state(model, ci_fn, pd, objective, device, rows, positions,
-                             use_fused_optim=use_fused_optim, init_components=init_components)
+                             use_fused_optim=use_fused_optim, init_components=init_components,
+                             shard_group=shard_group, shard_backend=shard_backend)
     if state_out is not None:
         state_out.append(state)
     start_kind = _resolve_start(run_dir, state, cadence, resume_provenance, log)

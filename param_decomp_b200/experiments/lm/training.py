@@ -10,10 +10,24 @@ from pathlib import Path
 
 import torch
 
-from param_decomp_b200.config.experiments import LMExperimentConfig
+from param_decomp_b200.config.experiments import LMExperimentConfig, LMTargetedExperimentConfig
 from param_decomp_b200.core.metrics import MetricsSink, device_peak_flops, get_logger, mint_run_id, pin_launch_config, run_dir_for
 from param_decomp_b200.core.run import RunResult, run_decomposition_training
 from param_decomp_b200.experiments.lm.build import build_lm_run
+
+
+def optimizer_sharding(cfg: LMExperimentConfig | LMTargetedExperimentConfig, topo) -> tuple[object, str | None]:
+    """Which optimizer layout a placement asks for on this topology: `ddp` keeps replicated masters
+    and all-reduces gradients; every sharded preset (`owner`, `zero1`, the resident family) runs the
+    ZeRO-style flat-sharded AdamW - the fused reduce-scatter + AdamW + all-gather kernel over NVLink
+    peer memory on GPUs, the collective (gloo / NCCL) form elsewhere."""
+    if topo.data_world <= 1:
+        return None, None
+    name = cfg.runtime.sharding if isinstance(cfg.runtime.sharding, str) else "owner"
+    if name == "ddp":
+        return None, None
+    backend = "fused_p2p" if topo.device.type == "cuda" and getattr(cfg.runtime, "backend", "") == "fused_sm100" else "collective"
+    return topo.data_group, backend
 
 
 def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None = None, device: str | None = None,
@@ -24,6 +38,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     log = get_logger(topo.rank)
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world)
     collectives = topo.collectives()
+    shard_group, shard_backend = optimizer_sharding(cfg, topo)
 
     run_dir, sink = None, None
     if data_root is not None:
@@ -37,7 +52,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     from param_decomp_b200.evals.lm import LMEvaluation
     from param_decomp_b200.utils.flops import decomposition_step_flops
 
-    evaluation = LMEvaluation(cfg.eval, run.sample_eval) if cfg.eval is not None else None
+    evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir) if cfg.eval is not None else None
     fused = getattr(run.model, "backend", "") == "fused_sm100"
     flops = decomposition_step_flops(run.model, run.ci_fn, cfg.pd, cfg.data.seq_len)
     try:
@@ -48,7 +63,63 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             units_per_step=run.tokens_per_step, flops_per_step=flops / topo.world, peak_flops=device_peak_flops(),
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
             max_steps_this_entry=max_steps_this_entry, state_out=state_out,
-            profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0)
+            profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
+            shard_group=shard_group, shard_backend=shard_backend)
+    finally:
+        if sink is not None:
+            sink.close()
+        topo.shutdown()
+
+
+def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, run_id: str | None = None,
+                      device: str | None = None, max_steps_this_entry: int | None = None,
+                      state_out: list | None = None, encode=None) -> RunResult:
+    """Targeted decomposition (tPD): every step sees a TARGET batch drawn from the prompt pool (full
+    reconstruction vocabulary, no faithfulness) and a broad NONTARGET batch from the corpus
+    (`nontarget:` losses, delta pinned on, no adversaries). Parity:
+    param_decomp/experiments/lm/training_targeted.py, targeted_data.py, core/run.py:1202-1353."""
+    from param_decomp_b200.core.objective import build_nontarget_objective, build_objective
+    from param_decomp_b200.experiments.lm.targeted_data import PromptPool
+    from param_decomp_b200.parallel import topology
+
+    topo = topology.initialize(cfg.runtime.mesh, device)
+    log = get_logger(topo.rank)
+    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world)
+    pool = PromptPool.build(cfg.prompts, run.arch.vocab_size, data_root, cfg.pd.seed, encode=encode)
+    n_target_terms = len(build_objective(cfg.pd).recon)
+    nontarget = build_nontarget_objective(cfg.nontarget, first_index=n_target_terms)
+    nt_rows = cfg.nontarget.batch_size
+
+    def sample_target(step: int):
+        return pool.batch(step, cfg.pd.batch_size, topo.data_rank, topo.data_world).to(topo.device)
+
+    def sample_nontarget(step: int):
+        full = run.sample_train(step)  # the corpus stream, cut to the non-target batch size
+        rows = max(1, nt_rows // topo.data_world)
+        cut = lambda t: None if t is None else t[:rows]  # noqa: E731
+        return type(full)(tokens=full.tokens[:rows], segment_ids=cut(full.segment_ids), positions=cut(full.positions))
+
+    run_dir, sink = None, None
+    if data_root is not None:
+        run_id = topo.broadcast_object(run_id or mint_run_id())
+        run_dir = run_dir_for(data_root, run_id)
+        if topo.rank == 0:
+            pin_launch_config(run_dir, cfg.to_yaml())
+        sink = MetricsSink.for_run(run_dir, topo.rank, cfg.wandb, cfg.run_name, cfg.model_dump(mode="json"))
+        log.info("run dir %s", run_dir)
+    from param_decomp_b200.evals.lm import LMEvaluation
+
+    evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir) if cfg.eval is not None else None
+    fused = getattr(run.model, "backend", "") == "fused_sm100"
+    try:
+        return run_decomposition_training(
+            run.model, run.ci_fn, cfg.pd, cfg.cadence, sample_target, device=topo.device, run_dir=run_dir, sink=sink,
+            evaluation=evaluation, collectives=topo.collectives(), nontarget=nontarget,
+            sample_nontarget_batch=sample_nontarget, batch_rows=max(cfg.pd.batch_size, nt_rows) // topo.data_world,
+            positions=max(pool.seq_len, cfg.data.seq_len), units_per_step=(cfg.pd.batch_size * pool.seq_len
+                                                                          + nt_rows * cfg.data.seq_len),
+            lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
+            max_steps_this_entry=max_steps_this_entry, state_out=state_out)
     finally:
         if sink is not None:
             sink.close()
