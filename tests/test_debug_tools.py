@@ -1,0 +1,44 @@
+"""Census, memory ledger and the deviceless fit check."""
+import torch
+import torch.distributed as dist
+
+from param_decomp_b200.config.experiments import LMExperimentConfig
+from param_decomp_b200.core.debug import fit_check, memory_ledger
+from param_decomp_b200.core.debug.census import census
+
+
+def test_fit_check_orders_configs():
+    cfg = LMExperimentConfig.from_file("param_decomp_b200/experiments/configs/lm_llama4l_c4096.yaml")
+    one, eight = fit_check.estimate(cfg, 1), fit_check.estimate(cfg, 8)
+    assert one.fits and eight.total_gib < one.total_gib
+    assert not fit_check.estimate(cfg, 1, pool_gib=10.0).fits
+    moe = LMExperimentConfig.from_file("param_decomp_b200/experiments/configs/lm_moe4l_e42.yaml")
+    assert not fit_check.estimate(moe, 1).fits and fit_check.estimate(moe, 8).fits
+    assert "TOTAL" in str(one)
+
+
+def test_memory_ledger_roundtrip(tmp_path):
+    led = memory_ledger.Ledger(top_n=3)
+    keep = torch.zeros(1000, 100)
+    led.mark("after_alloc")
+    led.mark("end")
+    led.save(tmp_path / "a.json")
+    other = memory_ledger.Ledger.load(tmp_path / "a.json")
+    assert [m.name for m in other.marks] == ["after_alloc", "end"]
+    assert memory_ledger.diff(led, other) == [("after_alloc", 0), ("end", 0)]
+    assert "peak" in led.report() and keep.numel() == 100000
+
+
+def test_census_counts_collectives(monkeypatch):
+    calls = []
+    monkeypatch.setattr(dist, "all_reduce", lambda t, *a, **k: calls.append(t.numel()))
+    with census() as c:
+        dist.all_reduce(torch.zeros(10))
+        dist.all_reduce(torch.zeros(6))
+    assert c.collectives["all_reduce"] == 2 and c.collective_bytes["all_reduce"] == 64 and calls == [10, 6]
+    c.assert_collectives({"all_reduce"})
+    try:
+        c.assert_collectives({"reduce_scatter_tensor"})
+        raise RuntimeError("should have refused")
+    except AssertionError:
+        pass
