@@ -81,25 +81,42 @@ class BlockedSiteMLP(nn.Module):
         _kaiming_(self.heads, hidden, generator)
         self.head_bias = nn.Parameter(torch.zeros(n_blocks, c_block))
 
+    fused = False  # set by the builder on the fused sm_100a backend
+
     def forward(self, x: Tensor, sel) -> "SelectedCI":
         from param_decomp_b200.core.components import SelectedCI
 
         lead = x.shape[:-1]
-        h = F.gelu(x.reshape(-1, x.shape[-1]).float() @ self.w1 + self.b1)  # [N, hidden]
         idx = sel.indices.reshape(-1, sel.indices.shape[-1])  # [N, k]
         N, k = idx.shape
-        out = h.new_zeros(N, k, self.c_block)
         flat_e = idx.reshape(-1)
+        x2 = x.reshape(-1, x.shape[-1])
+        hidden = self.w1.shape[1]
+        if (self.fused and x.is_cuda and x2.shape[1] % 8 == 0 and hidden % 64 == 0 and self.c_block % 8 == 0):
+            # one batched GEMM for the shared trunk, then the per-expert heads as a grouped GEMM over
+            # (token, slot) jobs sorted by expert: no Python loop over experts, no host sync
+            from param_decomp_b200.ops.grouped import JobLayout, grouped_linear_trainable
+            from param_decomp_b200.ops.linear import bmm_bias
+
+            h = F.gelu(bmm_bias(x2.to(torch.bfloat16).unsqueeze(0), self.w1.unsqueeze(0), self.b1.view(1, 1, -1))[0])
+            layout = JobLayout.build(flat_e, self.n_blocks)
+            token_of_job = torch.arange(N, device=x.device).repeat_interleave(k)
+            hj = layout.scatter_rows(h[token_of_job])
+            out = layout.gather_rows(grouped_linear_trainable(hj, self.heads, self.head_bias, layout))
+            return SelectedCI(out.reshape(*lead, k * self.c_block), sel, self.n_blocks)
+        h = F.gelu(x2.float() @ self.w1 + self.b1)  # [N, hidden]
         order = flat_e.argsort(stable=True)
         counts = torch.bincount(flat_e, minlength=self.n_blocks).tolist()
-        start = 0
-        out_flat = out.view(N * k, self.c_block)
+        pieces, start = [], 0
         for e, n in enumerate(counts):
             if n == 0:
                 continue
             jobs = order[start:start + n]
-            out_flat[jobs] = h[jobs // k] @ self.heads[e] + self.head_bias[e]
+            pieces.append(h[jobs // k] @ self.heads[e] + self.head_bias[e])
             start += n
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=order.device)
+        out = torch.cat(pieces)[inv]  # back to job order without in-place slice writes
         return SelectedCI(out.reshape(*lead, k * self.c_block), sel, self.n_blocks)
 
 

@@ -102,10 +102,10 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
                                               attention=cfg.target.attention_implementation, n_vocab_chunks=n_chunks)
     ci_fn = build_ci_fn(cfg.decomposition.ci, model, cfg.pd.seed)
     if backend == "fused_sm100":
-        from param_decomp_b200.core.ci_fn.mlp import SiteMLP
+        from param_decomp_b200.core.ci_fn.mlp import BlockedSiteMLP, SiteMLP
 
         for m in ci_fn.modules():
-            if isinstance(m, SiteMLP):
+            if isinstance(m, (SiteMLP, BlockedSiteMLP)):
                 m.fused = True
 
     seq = cfg.data.seq_len

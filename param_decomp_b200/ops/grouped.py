@@ -141,3 +141,51 @@ def grouped_linear(x: Tensor, W: Tensor, layout: JobLayout) -> Tensor:
     y = torch.empty(x.shape[0], W.shape[1], device=x.device, dtype=torch.bfloat16)
     nv.gemm(x.contiguous(), W, y, bgroup_of_mblock=layout.bgroup)
     return y
+
+
+class _GroupedLinearTrainable(torch.autograd.Function):
+    """`y_j = x_j W[e(j)] + b[e(j)]` on padded sorted jobs with gradients for `x`, `W [E, K, N]`
+    (fp32 master, read through a bf16 copy) and `b [E, N]`."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, W: Tensor, b: Tensor | None, layout: JobLayout) -> Tensor:  # type: ignore[override]
+        from param_decomp_b200.ops.elementwise import cast_bf16
+
+        Wb = cast_bf16(W.detach().contiguous()) if W.dtype != torch.bfloat16 else W.detach().contiguous()
+        R, _ = x.shape
+        N = W.shape[-1]
+        x = x.contiguous()
+        y = torch.empty(R, N, device=x.device, dtype=torch.bfloat16)
+        nv.gemm(x, Wb, y, b_mn=True, bgroup_of_mblock=layout.bgroup)
+        if b is not None:
+            # rows of padding blocks carry expert -1: they are never read back, any bias row will do
+            row_e = layout.bgroup.clamp_min(0).long().repeat_interleave(PAD)
+            y = y + b.detach().to(torch.bfloat16)[row_e]
+        ctx.save_for_backward(x, Wb)
+        ctx.layout, ctx.has_bias, ctx.w_dtype = layout, b is not None, W.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x, Wb = ctx.saved_tensors
+        layout: JobLayout = ctx.layout
+        dy = dy.contiguous()
+        E, K, N = Wb.shape
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            nv.gemm(dy, Wb, dx, bgroup_of_mblock=layout.bgroup)  # W_e [K, N] as the K-major B of dx = dy W_e^T
+        dW = torch.zeros(E, K, N, device=x.device, dtype=torch.float32)
+        nv.gemm(x, dy, dW, a_mn=True, b_mn=True, accumulate=True, kblock_range=layout.krange, a_bcast=True, b_bcast=True)
+        db = None
+        if ctx.has_bias:
+            row_e = layout.bgroup.long().repeat_interleave(PAD)
+            valid = row_e >= 0
+            db = torch.zeros(E, N, device=x.device, dtype=torch.float32)
+            db.index_add_(0, row_e.clamp_min(0), dy.float() * valid[:, None])
+        return dx, dW.to(ctx.w_dtype), db, None
+
+
+def grouped_linear_trainable(x: Tensor, W: Tensor, b: Tensor | None, layout: JobLayout) -> Tensor:
+    """Per-expert trainable linear on padded sorted job rows (`layout.scatter_rows`)."""
+    return _GroupedLinearTrainable.apply(x, W, b, layout)

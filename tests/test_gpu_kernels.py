@@ -489,3 +489,34 @@ def test_streamed_attention_pattern_kl(nv, hd, H, Hkv, seg):
     nv.check_status()
     assert abs(float(loss) - float(ref)) < 2e-3 * max(1.0, abs(float(ref))), (float(loss), float(ref))
     assert rel(qm.grad, q2.grad) < 3e-2 and rel(km.grad, k2.grad) < 3e-2, (rel(qm.grad, q2.grad), rel(km.grad, k2.grad))
+
+
+def test_blocked_ci_mlp_fused_matches_eager(nv):
+    from param_decomp_b200.core.ci_fn.mlp import BlockedSiteMLP
+    from param_decomp_b200.core.components import BlockSelection
+
+    torch.manual_seed(0)
+    N, d, hidden, E, c, k = 700, 64, 128, 6, 32, 2
+    g = torch.Generator().manual_seed(1)
+    mlp_a = BlockedSiteMLP(d, hidden, E, c, g).cuda()
+    mlp_b = BlockedSiteMLP(d, hidden, E, c, g).cuda()
+    mlp_b.load_state_dict(mlp_a.state_dict())
+    with torch.no_grad():
+        for m in (mlp_a, mlp_b):
+            m.head_bias.normal_(generator=None)
+        mlp_b.head_bias.copy_(mlp_a.head_bias)
+    mlp_a.fused = True
+    x = torch.randn(1, N, d, device="cuda").to(bf)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(N)]).view(1, N, k)
+    idx[0, :, 0].clamp_(max=E - 2)  # leave the last expert nearly empty
+    sel = BlockSelection(idx, torch.full((1, N, k), 0.5, device="cuda"))
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, yb = mlp_a(xa, sel).values, mlp_b(xb, sel).values
+    go = torch.randn_like(yb)
+    ya.backward(go.to(ya.dtype))
+    yb.backward(go)
+    nv.check_status()
+    assert rel(ya, yb) < 2e-2
+    assert rel(xa.grad, xb.grad) < 3e-2
+    for (n, pa), (_, pb) in zip(mlp_a.named_parameters(), mlp_b.named_parameters()):
+        assert rel(pa.grad, pb.grad) < 3e-2, (n, rel(pa.grad, pb.grad))
