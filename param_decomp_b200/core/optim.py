@@ -49,13 +49,46 @@ def newton_schulz(G: Tensor, steps: int = 5, dtype: torch.dtype = torch.bfloat16
     if transposed:
         X = X.transpose(-1, -2)
     X = X / (X.float().norm(dim=(-2, -1), keepdim=True) + eps).to(dtype)
-    for _ in range(steps):
-        A = X @ X.transpose(-1, -2)
-        B = b * A + c * (A @ A)
-        X = a * X + B @ X
+    if _native_ns_ok(X):
+        X = _newton_schulz_native(X, steps)
+    else:
+        for _ in range(steps):
+            A = X @ X.transpose(-1, -2)
+            B = b * A + c * (A @ A)
+            X = a * X + B @ X
     if transposed:
         X = X.transpose(-1, -2)
     return X.to(G.dtype)
+
+
+def _native_ns_ok(X: Tensor) -> bool:
+    if not (X.is_cuda and X.dtype == torch.bfloat16 and X.dim() in (2, 3)):
+        return False
+    from param_decomp_b200.ops import native as nv
+
+    return nv.available() and X.shape[-1] % 8 == 0 and X.shape[-2] % 8 == 0
+
+
+def _newton_schulz_native(X: Tensor, steps: int) -> Tensor:
+    """The quintic iteration on the batched tcgen05 GEMM: `A = X X^T` and `A A` are K-major products
+    (A is symmetric, so it is its own transposed operand), `B X` reads X as the MN-major operand; the
+    polynomial's scalings ride in the epilogue's alpha, the two axpys are single elementwise passes."""
+    from param_decomp_b200.ops import native as nv
+
+    a, b, c = NS_COEFFS
+    squeeze = X.dim() == 2
+    X = (X.unsqueeze(0) if squeeze else X).contiguous()
+    g, m, n = X.shape
+    A = torch.empty(g, m, m, device=X.device, dtype=torch.bfloat16)
+    AA = torch.empty_like(A)
+    BX = torch.empty_like(X)
+    for _ in range(steps):
+        nv.gemm(X, X, A)                        # A = X X^T
+        nv.gemm(A, A, AA, alpha=c)              # c A A   (A^T = A)
+        Bm = torch.add(AA, A, alpha=b)          # B = b A + c A A
+        nv.gemm(Bm, X, BX, b_mn=True)           # B X
+        X = torch.add(BX, X, alpha=a)           # a X + B X
+    return X[0] if squeeze else X
 
 
 @dataclass

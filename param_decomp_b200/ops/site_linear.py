@@ -41,12 +41,12 @@ class SiteWeights:
 
 def _split_k_for(M: int, N: int, K: int, sms: int = 148) -> int:
     """Split count for a weight-gradient GEMM (`K` = tokens): few output tiles leave SMs idle and
-    an unlucky tile count wastes most of its last wave, so take the split (<= 8, >= 2048 tokens per
+    an unlucky tile count wastes most of its last wave, so take the split (<= 8, >= 1024 tokens per
     split) whose tile count fills its waves best."""
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     best, best_eff = 1, 0.0
     for s in range(1, 9):
-        if s > 1 and K // s < 2048:
+        if s > 1 and K // s < 1024:
             break
         waves = tiles * s / sms
         eff = waves / -(-tiles * s // sms)

@@ -520,3 +520,22 @@ def test_blocked_ci_mlp_fused_matches_eager(nv):
     assert rel(xa.grad, xb.grad) < 3e-2
     for (n, pa), (_, pb) in zip(mlp_a.named_parameters(), mlp_b.named_parameters()):
         assert rel(pa.grad, pb.grad) < 3e-2, (n, rel(pa.grad, pb.grad))
+
+
+def test_newton_schulz_on_native_gemm(nv):
+    from param_decomp_b200.core import optim
+
+    torch.manual_seed(0)
+    G = torch.randn(3, 128, 320, device="cuda")
+    got = optim.newton_schulz(G, 5)
+    X = G.to(bf)
+    X = X / (X.float().norm(dim=(-2, -1), keepdim=True) + 1e-8).to(bf)
+    a, b, c = optim.NS_COEFFS
+    for _ in range(5):
+        A = X @ X.transpose(-1, -2)
+        X = a * X + (b * A + c * (A @ A)) @ X
+    assert rel(got, X.float()) < 3e-2
+    s = torch.linalg.svdvals(got[0].float())
+    assert float(s.max()) < 1.3 and float(s.min()) > 0.4  # singular values pushed towards one
+    tall = optim.newton_schulz(torch.randn(256, 64, device="cuda"), 5)
+    assert tall.shape == (256, 64)
