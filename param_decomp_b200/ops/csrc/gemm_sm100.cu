@@ -101,9 +101,9 @@ struct GemmArgs {
   int ag_mode;           // 0: A row blocks (activations sharded by rows); 1: B K-slabs (weights sharded by K rows)
 };
 
-template <int BN, int NOUT>
+template <int BN, int NOUT, int CG = 1>
 struct SmemPlan {
-  static constexpr int kStageBytesB = BN * BK * 2;
+  static constexpr int kStageBytesB = BN * BK * 2 / CG;  // a CTA pair splits the B tile
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
   static constexpr int kOutBytes = kNumEpiWarps * NOUT * kOutBoxBytes;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/;
@@ -166,16 +166,19 @@ __device__ __forceinline__ void stage_fp32(uint32_t box, int lane, const float (
   }
 }
 
-template <int BN, int EPI, int NOUT>
+template <int BN, int EPI, int NOUT, int CG>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
             const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
             const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
             const __grid_constant__ PeerMaps peerOut, const GemmArgs args) {
-  using Plan = SmemPlan<BN, NOUT>;
+  using Plan = SmemPlan<BN, NOUT, CG>;
   constexpr int kStages = Plan::kStages;
   constexpr int kStageBytesB = Plan::kStageBytesB;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two as tcgen05.alloc requires
+  // CG == 2: two CTAs of a cluster share a 256-row tile; rank 0 issues the MMAs for both.
+  const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -203,14 +206,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   const int kb_total = args.kblocks0 + args.kblocks1;
   const int split = args.split_k;
   const int kb_per_split = (kb_total + split - 1) / split;
-  const long long num_tiles = static_cast<long long>(num_m) * num_n * split * args.batch;
+  const int num_m_t = (num_m + CG - 1) / CG;  // row tiles of 128 * CG rows
+  const long long num_tiles = static_cast<long long>(num_m_t) * num_n * split * args.batch;
   // All-gather mode: the last `ag_gather_ctas` CTAs own no tiles; they stream peers' row blocks
   // into the local A buffer while the others compute.
   const int n_gather = args.ag_world > 1 ? args.ag_gather_ctas : 0;
   const int n_compute = static_cast<int>(gridDim.x) - n_gather;
   const bool is_gather_cta = static_cast<int>(blockIdx.x) >= n_compute;
-  const long long tile0 = is_gather_cta ? num_tiles : static_cast<long long>(blockIdx.x);
-  const long long tstride = n_compute;
+  const long long tile0 = is_gather_cta ? num_tiles : static_cast<long long>(blockIdx.x) / CG;
+  const long long tstride = n_compute / CG;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -219,7 +223,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, kNumEpiWarps);
+      mbar_init(bar_tempty + 8 * s, kNumEpiWarps * CG);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -232,16 +236,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_pair(tmem_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   // Tile decode: batch / split outermost, then panels of kGroupM row blocks walked column by column.
-  const long long tiles_per_mat = static_cast<long long>(num_m) * num_n;
+  const long long tiles_per_mat = static_cast<long long>(num_m_t) * num_n;
   auto decode = [&](long long t, int& b, int& mb, int& nb, int& sp) {
     const long long outer = t / tiles_per_mat;
     const int pid = static_cast<int>(t % tiles_per_mat);
@@ -250,9 +260,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const int per_group = kGroupM * num_n;
     const int group = pid / per_group;
     const int first_m = group * kGroupM;
-    const int gsz = min(num_m - first_m, kGroupM);
+    const int gsz = min(num_m_t - first_m, kGroupM);
     const int in_group = pid % per_group;
-    mb = first_m + in_group % gsz;
+    mb = (first_m + in_group % gsz) * CG + static_cast<int>(cta_rank);
     nb = in_group / gsz;
     if (args.ag_world > 1 && args.ag_mode == 0) {  // start with the row blocks this rank already holds
       const int per_rank = args.ag_rows / BM;
@@ -415,22 +425,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           const int a_mn = p1 ? args.a_mn1 : args.a_mn0;
           const int b_mn = p1 ? args.b_mn1 : args.b_mn0;
           const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, kStageBytesA + kStageBytesB);
+          // pair: the leader's barrier collects the bytes of both CTAs' copies
+          if (leader) mbar_expect_tx(full, (kStageBytesA + kStageBytesB) * CG);
           const uint32_t sa = smem_a + stage * kStageBytesA;
           const uint32_t sb = smem_b + stage * kStageBytesB;
+          auto load = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2) {
+            if constexpr (CG == 2)
+              tma_load_3d_pair(dst, tm, full, c0, c1, c2);
+            else
+              tma_load_3d(dst, tm, full, c0, c1, c2);
+          };
           if (!a_mn) {
-            tma_load_3d(sa, ta, full, k0, mb * BM, ab);
+            load(sa, ta, k0, mb * BM, ab);
           } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i)
-              tma_load_3d(sa + i * (BK * 128), ta, full, mb * BM + 64 * i, k0, ab);
+            for (int i = 0; i < BM / 64; ++i) load(sa + i * (BK * 128), ta, mb * BM + 64 * i, k0, ab);
           }
+          const int n0 = nb * BN + static_cast<int>(cta_rank) * (BN / CG);  // this CTA's share of the B tile
           if (!b_mn) {
-            tma_load_3d(sb, tb, full, k0, nb * BN, bbatch);
+            load(sb, tb, k0, n0, bbatch);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              tma_load_3d(sb + i * (BK * 128), tb, full, nb * BN + 64 * i, k0, bbatch);
+            for (int i = 0; i < BN / 64 / CG; ++i) load(sb + i * (BK * 128), tb, n0 + 64 * i, k0, bbatch);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -441,7 +457,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -469,7 +485,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           const bool p1 = kb >= args.kblocks0;
           const int a_mn = p1 ? args.a_mn1 : args.a_mn0;
           const int b_mn = p1 ? args.b_mn1 : args.b_mn0;
-          const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn, b_mn);
+          const uint32_t idesc = make_idesc_bf16(BM * CG, BN, a_mn, b_mn);
           const uint32_t sa = smem_a + stage * kStageBytesA;
           const uint32_t sb = smem_b + stage * kStageBytesB;
           const uint64_t adesc = make_smem_desc(sa, a_mn ? BK * 128 : 16, 1024);
@@ -480,17 +496,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           const uint64_t b_step = b_mn ? (2048 >> 4) : (32 >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            umma_bf16(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc,
-                      (kb > kb_lo || k > 0) ? 1u : 0u);
+            if constexpr (CG == 2)
+              umma_bf16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
+            else
+              umma_bf16(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
-          umma_commit(bar_empty + 8 * stage);
+          if constexpr (CG == 2)
+            umma_commit_pair(bar_empty + 8 * stage);
+          else
+            umma_commit(bar_empty + 8 * stage);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(bar_tfull + 8 * acc);
+        if constexpr (CG == 2)
+          umma_commit_pair(bar_tfull + 8 * acc);
+        else
+          umma_commit(bar_tfull + 8 * acc);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -771,7 +795,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       // Accumulator drained by this warp: hand it back to the MMA warp.
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (lane == 0) {
+        if (CG == 2 && !leader)
+          mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));  // the MMA issuer lives in the leader
+        else
+          mbar_arrive(bar_tempty + 8 * acc);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -794,9 +823,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   }
   tc_fence_before();
   __syncthreads();
+  // pair: neither CTA may retire while its partner can still signal its barriers or read its smem
+  if constexpr (CG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (CG == 2)
+      tmem_dealloc_pair(tmem_base, kTmemCols);
+    else
+      tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -811,6 +845,7 @@ struct OperandDesc {
 };
 
 static int g_num_sms = 0;
+static bool g_pair_default = true;  // pd_gemm_set_pair_default(0) turns automatic pairing off
 
 static int encode_operand(CUtensorMap* tm, const OperandDesc& op, int mn_extent, int k_extent,
                           int batch, int box_rows_k_major) {
@@ -822,12 +857,12 @@ static int encode_operand(CUtensorMap* tm, const OperandDesc& op, int mn_extent,
                      BK);
 }
 
-template <int BN, int EPI, int NOUT>
+template <int BN, int EPI, int NOUT, int CG>
 static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
                        const CUtensorMap& b1, const CUtensorMap& o0, const CUtensorMap& o1,
                        const PeerMaps& peers, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
-  using Plan = SmemPlan<BN, NOUT>;
-  auto kern = gemm_kernel<BN, EPI, NOUT>;
+  using Plan = SmemPlan<BN, NOUT, CG>;
+  auto kern = gemm_kernel<BN, EPI, NOUT, CG>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -840,10 +875,11 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const long long tiles = static_cast<long long>((args.M + BM - 1) / BM) *
-                          ((args.N + BN - 1) / BN) * args.split_k * args.batch;
+  const long long tiles = static_cast<long long>((args.M + BM * CG - 1) / (BM * CG)) *
+                          ((args.N + BN - 1) / BN) * args.split_k * args.batch * CG;
   int grid = static_cast<int>(tiles < g_num_sms ? tiles : g_num_sms);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  grid -= grid % CG;
   if (grid <= 0) return 0;
   GemmArgs launch_args = args;
   if (args.ag_world > 1) {
@@ -853,6 +889,22 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
     int g = args.ag_gather_ctas > 0 ? args.ag_gather_ctas : (args.ag_mode == 1 ? 8 : 16);
     if (g > grid / 2) g = grid / 2;
     launch_args.ag_gather_ctas = g;
+  }
+  if constexpr (CG == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = Plan::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, o0, o1, peers, launch_args);
+    return le == cudaSuccess ? 0 : 400 + static_cast<int>(le);
   }
   kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, peers, launch_args);
   cudaError_t e = cudaGetLastError();
@@ -901,6 +953,7 @@ struct PdGemmCall {
   int ag_world; int ag_rank; int ag_rows; const void* ag_src[8]; unsigned int* ag_flags; unsigned int ag_seq;
   // ag_mode 1: ag_src[r] = rank r's K slab [ag_rows, N] of the MN-major B operand; B0 is the local full buffer
   int ag_mode; int ag_gather_ctas;
+  int cta_group;  // 0 = automatic, 1 = single CTA tiles, 2 = CTA pairs where the call allows them
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -975,12 +1028,21 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   OperandDesc A0{c->A0, c->lda0, c->bsa0, c->a_mn0}, B0{c->B0, c->ldb0, c->bsb0, c->b_mn0};
   const int a_batch = c->a_bcast ? 1 : c->batch;
   const int b_batch = c->b_bcast ? 1 : (c->bgroup_of_mblock ? c->b_groups : c->batch);
+  // CTA pairs (one MMA over two CTAs, each staging half of B): dense, ungrouped products whose row
+  // count fills at least one 256-row tile; `cta_group` = 1 / 2 forces the choice, 0 = automatic.
+  const bool pair_ok = bn == 256 && c->bgroup_of_mblock == nullptr && c->ag_world <= 1 && c->rs_world <= 1 &&
+                       c->M >= 2 * BM && (c->max_ctas == 0 || c->max_ctas >= 2);
+  // Measured on the flagship shapes: pairs win 5-23% whenever an operand is MN-major (several TMA boxes
+  // per stage); with both operands K-major the single-CTA tiles are as fast or faster.
+  const bool pair = pair_ok && c->cta_group != 1 &&
+                    (c->cta_group == 2 || (g_pair_default && (c->a_mn0 || c->b_mn0)));
+  const int b_box = pair ? bn / 2 : bn;
   if ((rc = encode_operand(&ta0, A0, c->M, c->K0, a_batch, BM))) return 1000 + rc;
-  if ((rc = encode_operand(&tb0, B0, c->N, c->K0, b_batch, bn))) return 2000 + rc;
+  if ((rc = encode_operand(&tb0, B0, c->N, c->K0, b_batch, b_box))) return 2000 + rc;
   if (c->K1 > 0) {
     OperandDesc A1{c->A1, c->lda1, c->bsa1, c->a_mn1}, B1{c->B1, c->ldb1, c->bsb1, c->b_mn1};
     if ((rc = encode_operand(&ta1, A1, c->M, c->K1, a_batch, BM))) return 3000 + rc;
-    if ((rc = encode_operand(&tb1, B1, c->N, c->K1, b_batch, bn))) return 4000 + rc;
+    if ((rc = encode_operand(&tb1, B1, c->N, c->K1, b_batch, b_box))) return 4000 + rc;
   } else {
     ta1 = ta0;
     tb1 = tb0;
@@ -1003,7 +1065,15 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
         return 7000 + rc;
   }
 #define PD_LAUNCH(BN_, EPI_, NOUT_) \
-  launch_gemm<BN_, EPI_, NOUT_>(ta0, tb0, ta1, tb1, to0, to1, peers, a, c->max_ctas, stream)
+  launch_gemm<BN_, EPI_, NOUT_, 1>(ta0, tb0, ta1, tb1, to0, to1, peers, a, c->max_ctas, stream)
+#define PD_LAUNCH2(EPI_, NOUT_) \
+  launch_gemm<256, EPI_, NOUT_, 2>(ta0, tb0, ta1, tb1, to0, to1, peers, a, c->max_ctas, stream)
+  if (pair) {
+    if (c->epi == EPI_PLAIN) return PD_LAUNCH2(EPI_PLAIN, 1);
+    if (c->epi == EPI_MASK_FWD) return nout == 2 ? PD_LAUNCH2(EPI_MASK_FWD, 2) : PD_LAUNCH2(EPI_MASK_FWD, 1);
+    if (c->epi == EPI_MASK_BWD) return PD_LAUNCH2(EPI_MASK_BWD, 1);
+    if (c->epi == EPI_FAITH) return PD_LAUNCH2(EPI_FAITH, 1);
+  }
   if (c->epi == EPI_PLAIN) return bn == 256 ? PD_LAUNCH(256, EPI_PLAIN, 1) : PD_LAUNCH(128, EPI_PLAIN, 1);
   if (c->epi == EPI_MASK_FWD) {
     if (nout == 2) return bn == 256 ? PD_LAUNCH(256, EPI_MASK_FWD, 2) : PD_LAUNCH(128, EPI_MASK_FWD, 2);
@@ -1011,8 +1081,11 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   }
   if (c->epi == EPI_MASK_BWD) return bn == 256 ? PD_LAUNCH(256, EPI_MASK_BWD, 1) : PD_LAUNCH(128, EPI_MASK_BWD, 1);
   if (c->epi == EPI_FAITH) return bn == 256 ? PD_LAUNCH(256, EPI_FAITH, 1) : PD_LAUNCH(128, EPI_FAITH, 1);
+#undef PD_LAUNCH2
 #undef PD_LAUNCH
   return kBadArgument;
 }
+
+extern "C" void pd_gemm_set_pair_default(int on) { g_pair_default = on != 0; }
 
 extern "C" int pd_gemm_call_size() { return static_cast<int>(sizeof(PdGemmCall)); }

@@ -47,7 +47,7 @@ class PdGemmCall(C.Structure):
         ("b_groups", C.c_int),
         ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
-        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int),
+        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int),
     ]  # fmt: skip
 
 
@@ -171,6 +171,7 @@ def gemm(
     ag: tuple[list[int], int, int, torch.Tensor, int] | None = None,
     ag_b: tuple[list[int], int, int, torch.Tensor, int] | None = None,
     ag_gather_ctas: int = 0,
+    cta_group: int = 0,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -262,6 +263,7 @@ def gemm(
             call.ag_src[i] = ptr
         call.ag_flags, call.ag_seq = flags.data_ptr(), seq & 0xFFFFFFFF
     call.ag_gather_ctas = ag_gather_ctas
+    call.cta_group = cta_group
     rc = _pd_gemm()(C.byref(call), current_stream_ptr())
     global _LAUNCHES
     _LAUNCHES += 1

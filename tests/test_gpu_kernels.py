@@ -539,3 +539,37 @@ def test_newton_schulz_on_native_gemm(nv):
     assert float(s.max()) < 1.3 and float(s.min()) > 0.4  # singular values pushed towards one
     tall = optim.newton_schulz(torch.randn(256, 64, device="cuda"), 5)
     assert tall.shape == (256, 64)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (384, 320, 192), (1024, 768, 4096)])
+def test_cta_pair_gemm_matches_single_cta(nv, M, N, K):
+    """`cta_group::2` tiles (one MMA over two CTAs) against the single-CTA kernel, all operand majors,
+    an odd row-block count (the peer CTA's rows fall outside the matrix) and ragged N."""
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").to(bf)
+    b = (torch.randn(N, K, device="cuda") / K**0.5).to(bf)
+    at, bt = a.t().contiguous(), b.t().contiguous()
+    for a_mn, b_mn in ((False, False), (False, True), (True, False), (True, True)):
+        outs = []
+        for cg in (1, 2):
+            o = torch.zeros(M, N, device="cuda", dtype=bf)
+            nv.gemm(at if a_mn else a, bt if b_mn else b, o, a_mn=a_mn, b_mn=b_mn, cta_group=cg)
+            outs.append(o)
+        torch.cuda.synchronize()
+        nv.check_status()
+        assert torch.equal(outs[0], outs[1]), (a_mn, b_mn, rel(outs[1], outs[0]))
+        assert rel(outs[1], a.float() @ b.float().t()) < 1e-2
+    # mask epilogue (forward, two outputs) and the split-K fp32 reduce path
+    ci = torch.rand(M, N, device="cuda").to(bf)
+    delta = torch.rand(M, device="cuda")
+    res = []
+    for cg in (1, 2):
+        A_, H_ = torch.zeros(M, N, device="cuda", dtype=bf), torch.zeros(M, N, device="cuda", dtype=bf)
+        nv.gemm(a, b, A_, epi=nv.EPI_MASK_FWD, out1=H_, ci=ci, delta=delta, seed=5, rng_stream=2, cta_group=cg)
+        g32 = torch.zeros(M, N, device="cuda")
+        nv.gemm(a, b, g32, accumulate=True, split_k=2 if K >= 256 else 1, cta_group=cg)
+        res.append((A_, H_, g32))
+    torch.cuda.synchronize()
+    nv.check_status()
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert rel(res[1][2], res[0][2]) < 1e-5
