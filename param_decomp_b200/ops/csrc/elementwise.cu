@@ -216,6 +216,39 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
+// eight rotation pairs per thread (16-byte loads of the low and the high half); needs hd % 16 == 0
+__global__ void rope_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+                                const float* __restrict__ sn, long long rows, int T, int heads, int hd,
+                                int inverse) {
+  const int half = hd >> 1, groups = half >> 3;
+  const long long total = rows * heads * groups;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(i % groups);
+    const long long rh = i / groups;
+    const int t = static_cast<int>((rh / heads) % T);
+    __nv_bfloat16* p = x + rh * hd + 8 * g;
+    const uint4 lo = *reinterpret_cast<const uint4*>(p), hi = *reinterpret_cast<const uint4*>(p + half);
+    const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+    const float4* c4 = reinterpret_cast<const float4*>(cs + static_cast<long long>(t) * half + 8 * g);
+    const float4* s4 = reinterpret_cast<const float4*>(sn + static_cast<long long>(t) * half + 8 * g);
+    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    const float c[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+    const float sv[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+    __nv_bfloat162 ol[4], oh[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = __bfloat1622float2(l2[k]), b = __bfloat1622float2(h2[k]);
+      const float s0 = inverse ? -sv[2 * k] : sv[2 * k], s1 = inverse ? -sv[2 * k + 1] : sv[2 * k + 1];
+      ol[k] = __floats2bfloat162_rn(a.x * c[2 * k] - b.x * s0, a.y * c[2 * k + 1] - b.y * s1);
+      oh[k] = __floats2bfloat162_rn(b.x * c[2 * k] + a.x * s0, b.y * c[2 * k + 1] + a.y * s1);
+    }
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<uint4*>(ol);
+    *reinterpret_cast<uint4*>(p + half) = *reinterpret_cast<uint4*>(oh);
+  }
+}
+
 // ---- SwiGLU ---------------------------------------------------------------------------------
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate,
                                   const __nv_bfloat16* __restrict__ up,
@@ -579,6 +612,12 @@ extern "C" int pd_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
 }
 extern "C" int pd_rope(void* x, const float* cs, const float* sn, long long rows, int T, int heads, int hd,
                        int inverse, void* stream) {
+  if (hd % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(cs) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(sn) & 15) == 0) {
+    rope_vec_kernel<<<blocks_for(rows * heads * (hd / 16), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(x), cs, sn, rows, T, heads, hd, inverse);
+    return PD_CHECK_LAUNCH();
+  }
   rope_kernel<<<blocks_for(rows * heads * (hd / 2), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(x), cs, sn, rows, T, heads, hd, inverse);
   return PD_CHECK_LAUNCH();
@@ -640,7 +679,9 @@ extern "C" int pd_ci_squash_activity_bwd(const void* pre, const void* dlower, co
 extern "C" int pd_vocab_kl(const void* lc, const void* lm, void* dlm, float* kl, long long rows, int V,
                            long long ld, void* stream) {
   if (ld % 8 != 0 || rows <= 0) return 5;
-  vocab_kl_kernel<<<static_cast<unsigned>(rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  // 512 threads per row: four rows in flight per SM keep the rows being re-read (passes 2 and 3)
+  // within L2 while different rows' load-bound and exp-bound passes still overlap on the SM
+  vocab_kl_kernel<<<static_cast<unsigned>(rows), 512, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(lc), static_cast<const __nv_bfloat16*>(lm),
       static_cast<__nv_bfloat16*>(dlm), kl, V, ld);
   return PD_CHECK_LAUNCH();

@@ -9,7 +9,9 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 os.environ.setdefault("WANDB_MODE", "disabled")
 
-REFERENCE_CONFIGS = Path("/root/reference/param_decomp/param_decomp/experiments")
+# the upstream tree, when it is mounted next to this repository (or named by PD_REFERENCE_ROOT)
+_REF_ROOT = Path(os.environ.get("PD_REFERENCE_ROOT", ROOT.parent / "reference"))
+REFERENCE_CONFIGS = _REF_ROOT / "param_decomp" / "param_decomp" / "experiments"
 
 
 def pytest_configure(config):
