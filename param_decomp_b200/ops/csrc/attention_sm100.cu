@@ -53,8 +53,9 @@ struct FwdPlan {
   static constexpr int kQBytes = kTile * HD * 2;
   static constexpr int kKVBytes = kTile * HD * 2;
   static constexpr int kPBytes = kTile * kTile * 2;
-  static constexpr int kStages = 2;
-  static constexpr int kTotal = kQBytes + 2 * kStages * kKVBytes + kPBytes + 1024 /*align*/ + 1024 /*barriers, seg ids*/;
+  static constexpr int kStages = 2;                 // K ring
+  static constexpr int kVStages = HD == 64 ? 1 : 2;  // one V buffer keeps a CTA under half an SM's shared memory
+  static constexpr int kTotal = kQBytes + (kStages + kVStages) * kKVBytes + kPBytes + 1024 /*align*/ + 1024 /*barriers, seg ids*/;
   static constexpr uint32_t kTmemCols = 256;  // S: 128 columns, O: HD columns at column 128
 };
 
@@ -68,13 +69,14 @@ __global__ void __launch_bounds__(kFwdThreads, HD == 64 ? 2 : 1) attn_fwd_kernel
                                                                 const AttnArgs args) {
   using Plan = FwdPlan<HD>;
   constexpr int kStages = Plan::kStages;
+  constexpr int kVStages = Plan::kVStages;
   constexpr int kKB = HD / 64;  // 64-wide K blocks of the head dimension
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sm_q = base;
   const uint32_t sm_k = sm_q + Plan::kQBytes;
   const uint32_t sm_v = sm_k + kStages * Plan::kKVBytes;
-  const uint32_t sm_p = sm_v + kStages * Plan::kKVBytes;
+  const uint32_t sm_p = sm_v + kVStages * Plan::kKVBytes;
   const uint32_t sm_bar = sm_p + Plan::kPBytes;
   // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, p_full, o_full
   const uint32_t bar_q = sm_bar;
@@ -137,13 +139,15 @@ __global__ void __launch_bounds__(kFwdThreads, HD == 64 ? 2 : 1) attn_fwd_kernel
         for (int c = 0; c < kKB; ++c)
           tma_load_3d(sm_k + st * Plan::kKVBytes + c * (kTile * 128), &tmK, bar_kf + 8 * st, hk * HD + 64 * c,
                       j * kTile, b);
-        if (!mbar_wait(bar_ve + 8 * st, ph ^ 1, abort_flag)) {
+        const int vs = j % kVStages;
+        const uint32_t vph = static_cast<uint32_t>((j / kVStages) & 1);
+        if (!mbar_wait(bar_ve + 8 * vs, vph ^ 1, abort_flag)) {
           atomicCAS(args.status, 0, kTimeoutProducer);
           break;
         }
-        mbar_expect_tx(bar_vf + 8 * st, Plan::kKVBytes);
+        mbar_expect_tx(bar_vf + 8 * vs, Plan::kKVBytes);
         for (int c = 0; c < kKB; ++c)
-          tma_load_3d(sm_v + st * Plan::kKVBytes + c * (kTile * 128), &tmV, bar_vf + 8 * st, hk * HD + 64 * c,
+          tma_load_3d(sm_v + vs * Plan::kKVBytes + c * (kTile * 128), &tmV, bar_vf + 8 * vs, hk * HD + 64 * c,
                       j * kTile, b);
       }
     }
@@ -175,9 +179,10 @@ __global__ void __launch_bounds__(kFwdThreads, HD == 64 ? 2 : 1) attn_fwd_kernel
         if (!mbar_wait(bar_p, static_cast<uint32_t>(j & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(bar_vf + 8 * st, static_cast<uint32_t>((j / kStages) & 1), abort_flag)) { ok = false; break; }
+        const int vs = j % kVStages;
+        if (!mbar_wait(bar_vf + 8 * vs, static_cast<uint32_t>((j / kVStages) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t vd = make_smem_desc(sm_v + st * Plan::kKVBytes, kTile * 128, 1024);
+        const uint64_t vd = make_smem_desc(sm_v + vs * Plan::kKVBytes, kTile * 128, 1024);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {  // two 64-wide blocks of the key index
           const uint64_t pd_ = make_smem_desc(sm_p + c * (kTile * 128), 16, 1024);
@@ -185,7 +190,7 @@ __global__ void __launch_bounds__(kFwdThreads, HD == 64 ? 2 : 1) attn_fwd_kernel
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem_o, pd_ + k * 2, vd + (c * 4 + k) * (2048 >> 4), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(bar_ve + 8 * st);
+        umma_commit(bar_ve + 8 * vs);
         umma_commit(bar_o);
       }
       if (!ok) atomicCAS(args.status, 0, kTimeoutMma);
