@@ -78,6 +78,8 @@ def dense_moe_oracle(x: Tensor, sel: BlockSelection, Wg: Tensor, Wu: Tensor, Wd:
 
 
 class MoEDecomposedModel(tf.TransformerDecomposedModel):
+    use_row_map = True  # fused backend: mask inputs stay in token order (False = materialise per-job rows)
+
     def __init__(self, arch: TransformerArchConfig, weights: dict[str, Tensor], site_cs: dict[str, int],
                  backend: str = "eager_torch", attention: str = "flash", ep: Any = None, **kw: Any) -> None:
         assert arch.family == "moe"
@@ -178,8 +180,29 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         if weights is None or masks is None or name not in masks or name not in weights.V:
             return grouped.grouped_linear(xs, W, layout)
         spec = next(s for s in self.sites if s.name == name)
-        sm = masks[name].materialize()
         c = spec.C_block
+        sm0 = masks[name]
+        V, U = weights.site(name)
+        J = token_of_job.numel()
+        src = sm0.ci if sm0.stochastic is not None else sm0.mask
+        if self.use_row_map and src is not None and self.ep is None and src.shape[-1] % c == 0 and c % 8 == 0:
+            # mask inputs stay in token order; the kernels map job rows to them and draw the mask themselves
+            from param_decomp_b200.ops import grouped as G
+
+            kk = src.shape[-1] // c
+            n_tok = src.numel() // src.shape[-1]
+            if J == n_tok * kk:
+                ci2 = src.reshape(n_tok, kk * c)
+                ci2 = ci2 if ci2.dtype == torch.bfloat16 else ci2.to(torch.bfloat16)
+                ci2 = ci2 if ci2.is_contiguous() else ci2.contiguous()
+                st = sm0.stochastic
+                mode, seed, stream, off = (0, st.seed64, st.stream, st.row_offset) if st is not None else (1, 0, 0, 0)
+                d = None if sm0.delta is None else sm0.delta.reshape(n_tok).float().contiguous()
+                r = None if sm0.route is None else sm0.route.reshape(n_tok)
+                return G.grouped_site_mapped(xs, V, U, W, layout, ci2, mode, seed, stream, off, d, r, kk,
+                                             weights.grad_V.get(name), weights.grad_U.get(name),
+                                             need_wgrad=weights.direct_grads)
+        sm = sm0.materialize()
 
         def per_job(t: Tensor | None, width: int) -> Tensor | None:
             if t is None:
@@ -192,7 +215,6 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         m = per_job(sm.mask, c)
         d = per_job(None if sm.delta is None else sm.delta.reshape(-1).float(), 0)
         r = per_job(None if sm.route is None else sm.route.reshape(-1), 0)
-        V, U = weights.site(name)
         return grouped.grouped_site(xs, V, U, W, layout, m, d, r, weights.grad_V.get(name), weights.grad_U.get(name),
                                     need_wgrad=weights.direct_grads)
 

@@ -99,6 +99,10 @@ struct GemmArgs {
   unsigned int ag_seq;
   int ag_gather_ctas;    // trailing CTAs of the grid that only move peers' rows (no tiles)
   int ag_mode;           // 0: A row blocks (activations sharded by rows); 1: B K-slabs (weights sharded by K rows)
+  // Mask epilogues on job rows (routed experts): row r of the product reads its CI / mask values, its
+  // delta and row scale, draws its uniforms and writes its CI gradient at the SOURCE position
+  // rowmap[r] = {source row, first source column, -, -}; source row -1 marks a padding row.
+  const int4* rowmap;
 };
 
 template <int BN, int NOUT, int CG = 1>
@@ -562,8 +566,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         decode(t, b2, mb2, nb2, sp2);
         const int prow = mb2 * BM + q * 32 + lane;
         const int pcol = nb2 * BN + j * box_cols + 32 * half;
-        const bool ok_row = prow < args.M;
-        const __nv_bfloat16* ci_row = args.ci + static_cast<long long>(prow) * args.ld_ci + pcol;
+        bool ok_row = prow < args.M;
+        long long src = prow;
+        int colb = 0;
+        if (args.rowmap != nullptr && ok_row) {
+          const int4 pm = __ldg(args.rowmap + prow);
+          src = pm.x;
+          colb = pm.y;
+          ok_row = pm.x >= 0;
+        }
+        const __nv_bfloat16* ci_row = args.ci + src * args.ld_ci + colb + pcol;
 #pragma unroll
         for (int g = 0; g < 4; ++g)
           pre_ci[g] = (ok_row && pcol + 8 * g < args.N) ? __ldg(reinterpret_cast<const uint4*>(ci_row + 8 * g))
@@ -603,13 +615,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       tile_krange(b, sp, kb_lo_e, kb_hi_e);
       const bool empty_k = kb_hi_e <= kb_lo_e;
       const int row = mb * BM + q * 32 + lane;
-      const bool row_ok = row < args.M;
+      bool row_ok = row < args.M;
+      long long src_row = row;  // where this row's mask inputs live (differs from `row` on job rows)
+      int src_col = 0;
       const uint32_t tmem_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       float delta = 0.0f, rs = 1.0f;
       if constexpr (EPI != EPI_PLAIN) {
+        if (args.rowmap != nullptr && row_ok) {
+          const int4 rm = __ldg(args.rowmap + row);
+          src_row = rm.x;
+          src_col = rm.y;
+          row_ok = rm.x >= 0;
+        }
         if (row_ok) {
-          if (args.delta) delta = args.delta[row];
-          if (args.rowscale) rs = args.rowscale[row];
+          if (args.delta) delta = args.delta[src_row];
+          if (args.rowscale) rs = args.rowscale[src_row];
         }
       }
       bool have_acc = false;
@@ -711,8 +731,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
               unpack8(ciq[g], cf);
               if (args.mask_mode == 0) {
                 float u[8];
-                philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(row) + args.row_offset,
-                                static_cast<uint32_t>((c0 >> 3) + g), u);
+                philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(src_row) + args.row_offset,
+                                static_cast<uint32_t>(((src_col + c0) >> 3) + g), u);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   const float om = 1.0f - u[i];
@@ -734,7 +754,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
                   for (int i = 0; i < 8; ++i) tt[i] = v[8 * g + i] * hf[i] * dmdci[i];
                   if (args.dci_bf16) {
                     __nv_bfloat16* dstb = reinterpret_cast<__nv_bfloat16*>(args.dci) +
-                                          static_cast<long long>(row) * args.ld_dci + c0 + 8 * g;
+                                          src_row * args.ld_dci + src_col + c0 + 8 * g;
                     if (args.dci_accumulate) {
                       float old8[8];
                       unpack8(*reinterpret_cast<const uint4*>(dstb), old8);
@@ -746,7 +766,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
                     pk.z = pack_bf16(tt[4], tt[5]); pk.w = pack_bf16(tt[6], tt[7]);
                     *reinterpret_cast<uint4*>(dstb) = pk;
                   } else {
-                    float* dst = args.dci + static_cast<long long>(row) * args.ld_dci + c0 + 8 * g;
+                    float* dst = args.dci + src_row * args.ld_dci + src_col + c0 + 8 * g;
                     float4 o0 = make_float4(tt[0], tt[1], tt[2], tt[3]), o1 = make_float4(tt[4], tt[5], tt[6], tt[7]);
                     if (args.dci_accumulate) {
                       const float4 p0 = *reinterpret_cast<float4*>(dst), p1 = *reinterpret_cast<float4*>(dst + 4);
@@ -954,6 +974,7 @@ struct PdGemmCall {
   // ag_mode 1: ag_src[r] = rank r's K slab [ag_rows, N] of the MN-major B operand; B0 is the local full buffer
   int ag_mode; int ag_gather_ctas;
   int cta_group;  // 0 = automatic, 1 = single CTA tiles, 2 = CTA pairs where the call allows them
+  const void* rowmap;  // [M] int4 {source row, first source column, 0, 0} for the mask epilogues, or null
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -990,6 +1011,7 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   for (int r = 0; r < kMaxPeers; ++r) a.ag_src[r] = c->ag_src[r];
   a.ag_gather_ctas = c->ag_gather_ctas;
   a.ag_mode = c->ag_mode;
+  a.rowmap = static_cast<const int4*>(c->rowmap);
   if (c->ag_world > 1 && c->ag_mode == 1) {
     a.ag_dst = const_cast<void*>(c->B0); a.ag_ld = c->ldb0; a.ag_k = c->N;
   }

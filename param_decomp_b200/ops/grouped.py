@@ -56,6 +56,22 @@ class JobLayout:
         krange = torch.stack([starts // 64, (starts + padded) // 64], dim=1).to(torch.int32).contiguous()
         return cls(pos, n_rows, bgroup, krange, counts)
 
+    def rowmap(self, k: int, c: int) -> Tensor:
+        """`[n_rows, 4]` int32 for the mask epilogues on job rows: padded row -> (token, first column of
+        its slot in the narrow `[tokens, k * c]` layout); jobs are token-major, slot-minor. Padding
+        rows carry token -1."""
+        key = (k, c)
+        cache = self.__dict__.setdefault("_rowmaps", {})
+        if key not in cache:
+            J = self.pos.numel()
+            j = torch.arange(J, device=self.pos.device)
+            rm = torch.zeros(self.n_rows, 4, dtype=torch.int32, device=self.pos.device)
+            rm[:, 0] = -1
+            rm[self.pos, 0] = (j // k).to(torch.int32)
+            rm[self.pos, 1] = ((j % k) * c).to(torch.int32)
+            cache[key] = rm
+        return cache[key]
+
     def scatter_rows(self, x_jobs: Tensor) -> Tensor:
         out = x_jobs.new_zeros(self.n_rows, x_jobs.shape[-1])
         out.index_copy_(0, self.pos, x_jobs)
@@ -189,3 +205,79 @@ class _GroupedLinearTrainable(torch.autograd.Function):
 def grouped_linear_trainable(x: Tensor, W: Tensor, b: Tensor | None, layout: JobLayout) -> Tensor:
     """Per-expert trainable linear on padded sorted job rows (`layout.scatter_rows`)."""
     return _GroupedLinearTrainable.apply(x, W, b, layout)
+
+
+class _GroupedSiteMapped(torch.autograd.Function):
+    """Blocked site whose mask inputs stay in their source layout: `ci [N, k c]` (narrow CI or a
+    materialised mask), `delta`, `rowscale [N]`; the kernels reach them through `rowmap`, draw the
+    stochastic mask in the epilogue (`mode 0`) and write the CI gradient back in the narrow layout."""
+
+    @staticmethod
+    def forward(ctx, x, ci, delta, V, U, W, gV, gU, layout: JobLayout, rowscale, d_eff_rows, need_wgrad: bool,
+                rowmap: Tensor, mode: int, seed: int, stream: int, row_offset: int):  # type: ignore[override]
+        R = x.shape[0]
+        E, _, c = V.shape
+        d_out = U.shape[-1]
+        A = torch.empty(R, c, device=x.device, dtype=torch.bfloat16)
+        need_H = ci.requires_grad
+        H = torch.empty_like(A) if need_H else None
+        rng = dict(seed=seed, rng_stream=stream, row_offset=row_offset, mask_mode=mode, rowmap=rowmap)
+        nv.gemm(x, V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci, delta=delta, rowscale=rowscale,
+                bgroup_of_mblock=layout.bgroup, **rng)
+        y = torch.empty(R, d_out, device=x.device, dtype=torch.bfloat16)
+        if d_eff_rows is not None:
+            xd = ew.rowscale(x, d_eff_rows)
+            nv.gemm(A, U, y, b_mn=True, a1=xd, b1=W, bgroup_of_mblock=layout.bgroup)
+        else:
+            nv.gemm(A, U, y, b_mn=True, bgroup_of_mblock=layout.bgroup)
+        ctx.save_for_backward(x, ci, delta, rowscale, d_eff_rows, A, H, V, U, W, rowmap)
+        ctx.layout, ctx.sinks, ctx.need_wgrad, ctx.rng = layout, (gV, gU), need_wgrad, (mode, seed, stream, row_offset)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x, ci, delta, rowscale, d_eff_rows, A, H, V, U, W, rowmap = ctx.saved_tensors
+        layout: JobLayout = ctx.layout
+        gV, gU = ctx.sinks
+        mode, seed, stream, row_offset = ctx.rng
+        R, d_in = x.shape
+        c = V.shape[-1]
+        dy = dy.contiguous()
+        dH = torch.empty(R, c, device=x.device, dtype=torch.bfloat16)
+        dci = torch.zeros_like(ci) if H is not None else None
+        nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, delta=delta, rowscale=rowscale, dci=dci,
+                bgroup_of_mblock=layout.bgroup, seed=seed, rng_stream=stream, row_offset=row_offset, mask_mode=mode,
+                rowmap=rowmap)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(R, d_in, device=x.device, dtype=torch.bfloat16)
+            if d_eff_rows is not None:
+                nv.gemm(dH, V, dx, a1=ew.rowscale(dy, d_eff_rows), b1=W, b1_mn=True, bgroup_of_mblock=layout.bgroup)
+            else:
+                nv.gemm(dH, V, dx, bgroup_of_mblock=layout.bgroup)
+        if ctx.need_wgrad:
+            nv.gemm(x, dH, gV, a_mn=True, b_mn=True, accumulate=True, kblock_range=layout.krange, a_bcast=True,
+                    b_bcast=True)
+            nv.gemm(A, dy, gU, a_mn=True, b_mn=True, accumulate=True, kblock_range=layout.krange, a_bcast=True,
+                    b_bcast=True)
+        return (dx, dci if ctx.needs_input_grad[1] else None) + (None,) * 15
+
+
+def grouped_site_mapped(x: Tensor, V: Tensor, U: Tensor, W: Tensor, layout: JobLayout, ci: Tensor, mode: int,
+                        seed: int, stream: int, row_offset: int, delta: Tensor | None, route: Tensor | None, k: int,
+                        grad_V: Tensor | None, grad_U: Tensor | None, need_wgrad: bool) -> Tensor:
+    """`x` padded job rows; `ci [N, k c]` bf16 in token order; `delta`, `route [N]` per token."""
+    c = V.shape[-1]
+    rowmap = layout.rowmap(k, c)
+    rowscale = d_tok = None
+    if route is not None:
+        rowscale = route.float().contiguous()
+        d_tok = (rowscale * delta + (1 - rowscale)) if delta is not None else (1 - rowscale)
+    elif delta is not None:
+        d_tok = delta
+    d_rows = None
+    if d_tok is not None:
+        tok = rowmap[:, 0].long()
+        d_rows = torch.where(tok >= 0, d_tok[tok.clamp_min(0)], torch.zeros((), device=x.device)).contiguous()
+    return _GroupedSiteMapped.apply(x.contiguous(), ci, delta, V, U, W, grad_V, grad_U, layout, rowscale, d_rows,
+                                    need_wgrad, rowmap, mode, seed, stream, row_offset)

@@ -47,7 +47,7 @@ class PdGemmCall(C.Structure):
         ("b_groups", C.c_int),
         ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
-        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int),
+        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int), ("rowmap", C.c_void_p),
     ]  # fmt: skip
 
 
@@ -172,6 +172,7 @@ def gemm(
     ag_b: tuple[list[int], int, int, torch.Tensor, int] | None = None,
     ag_gather_ctas: int = 0,
     cta_group: int = 0,
+    rowmap: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -218,10 +219,10 @@ def gemm(
         assert h.dtype == torch.bfloat16 and h.stride(-1) == 1
         call.H, call.ld_h = h.data_ptr(), h.stride(-2)
     if delta is not None:
-        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.numel() == M
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and (delta.numel() == M or rowmap is not None)
         call.delta = delta.data_ptr()
     if rowscale is not None:
-        assert rowscale.dtype == torch.float32 and rowscale.is_contiguous() and rowscale.numel() == M
+        assert rowscale.dtype == torch.float32 and rowscale.is_contiguous() and (rowscale.numel() == M or rowmap is not None)
         call.rowscale = rowscale.data_ptr()
     if dci is not None:
         assert dci.dtype in (torch.float32, torch.bfloat16) and dci.stride(-1) == 1
@@ -264,6 +265,9 @@ def gemm(
         call.ag_flags, call.ag_seq = flags.data_ptr(), seq & 0xFFFFFFFF
     call.ag_gather_ctas = ag_gather_ctas
     call.cta_group = cta_group
+    if rowmap is not None:
+        assert rowmap.dtype == torch.int32 and rowmap.shape == (M, 4) and rowmap.is_contiguous()
+        call.rowmap = rowmap.data_ptr()
     rc = _pd_gemm()(C.byref(call), current_stream_ptr())
     global _LAUNCHES
     _LAUNCHES += 1

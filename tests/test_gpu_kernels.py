@@ -573,3 +573,62 @@ def test_cta_pair_gemm_matches_single_cta(nv, M, N, K):
     nv.check_status()
     assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
     assert rel(res[1][2], res[0][2]) < 1e-5
+
+
+def test_moe_fused_lazy_masks_match_eager(nv):
+    """The expert bank on the fused path (masks drawn in the grouped-GEMM epilogue through the row map)
+    against the eager bank in fp32 with materialised masks from the same Philox stream: outputs, CI
+    gradients (narrow layout) and component gradients."""
+    from param_decomp_b200.config.experiments import MoeCSpec, TransformerArchConfig
+    from param_decomp_b200.core import masking
+    from param_decomp_b200.core.components import ComponentStacks, prepare_compute_weights
+    from param_decomp_b200.core.rng import StepKey
+    from param_decomp_b200.models import moe
+
+    arch = TransformerArchConfig(family="moe", n_layer=1, d_model=64, n_head=2, d_ff=128, vocab_size=80, n_experts=4,
+                                 experts_per_token=2)
+    c, k, N = 32, 2, 200
+    sites = MoeCSpec(layers={"kind": "all"}, cs={kk: 4 * c for kk in ("experts_gate", "experts_up", "experts_down")})
+
+    class Target:
+        attention_implementation = "xla"
+
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(3)
+    x_tok = torch.randn(N, 64, generator=g).cuda()
+    idx = torch.stack([torch.randperm(4, generator=g)[:k] for _ in range(N)]).cuda()
+    token_of_job = torch.arange(N, device="cuda").repeat_interleave(k)
+    slot_of_job = torch.arange(k, device="cuda").repeat(N)
+    expert_of_job = idx.reshape(-1)
+    G = torch.randn(N * k, 64, generator=g).cuda()
+    ci0 = {kk: torch.rand(1, N, k * c, generator=g).cuda().to(bf) for kk in ("gate", "up", "down")}
+    res = {}
+    for backend in ("eager_torch", "fused_sm100"):
+        fused = backend == "fused_sm100"
+        dt = bf if fused else torch.float32
+        w = {kk: (v.float() * 20).to(dt).cuda() for kk, v in moe.random_init_moe_weights(arch, 0, torch.float32).items()}
+        model = moe.build_moe_model(arch, w, sites, Target, backend)
+        stacks = ComponentStacks(model.sites)
+        stacks.init_random(torch.Generator().manual_seed(5))
+        stacks.cuda()
+        ci = {s.name: ci0[s.name.split("_")[-1]].to(dt).requires_grad_(True) for s in model.sites}
+        masks = masking.stochastic_masks(ci, StepKey(1, 2), 0, 0, site_index={s.name: i for i, s in enumerate(model.sites)},
+                                         lazy=fused)
+        cw = prepare_compute_weights(stacks, dt, direct_grads=fused)
+        order, bounds = expert_of_job, [0]
+        if not fused:
+            order = expert_of_job.argsort(stable=True)
+            for n in torch.bincount(expert_of_job, minlength=4).tolist():
+                bounds.append(bounds[-1] + n)
+        y = model.expert_jobs(0, x_tok.to(dt)[token_of_job], expert_of_job, order, bounds, cw, masks, token_of_job, slot_of_job)
+        (y.float() * G).sum().backward()
+        torch.cuda.synchronize()
+        res[backend] = (y.detach().float(), {kk: v.grad.float() for kk, v in ci.items()},
+                        {kk: p.grad.float().clone() for kk, p in stacks.V.items() if p.grad is not None})
+    nv.check_status()
+    a, b = res["fused_sm100"], res["eager_torch"]
+    assert rel(a[0], b[0]) < 3e-2, rel(a[0], b[0])
+    for kk in b[1]:
+        assert rel(a[1][kk], b[1][kk]) < 5e-2, (kk, rel(a[1][kk], b[1][kk]))
+    for kk in b[2]:
+        assert rel(a[2][kk], b[2][kk]) < 5e-2, (kk, rel(a[2][kk], b[2][kk]))
