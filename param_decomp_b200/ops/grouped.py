@@ -195,10 +195,12 @@ class _GroupedLinearTrainable(torch.autograd.Function):
         nv.gemm(x, dy, dW, a_mn=True, b_mn=True, accumulate=True, kblock_range=layout.krange, a_bcast=True, b_bcast=True)
         db = None
         if ctx.has_bias:
-            row_e = layout.bgroup.long().repeat_interleave(PAD)
-            valid = row_e >= 0
+            # every 128-row block belongs to one expert: reduce inside blocks first, then add the few
+            # hundred block sums into their experts (a row-wise index_add would serialise on E rows)
+            blocks = dy.float().view(-1, PAD, N).sum(1)
+            be = layout.bgroup.long()
             db = torch.zeros(E, N, device=x.device, dtype=torch.float32)
-            db.index_add_(0, row_e.clamp_min(0), dy.float() * valid[:, None])
+            db.index_add_(0, be.clamp_min(0), blocks * (be >= 0)[:, None])
         return dx, dW.to(ctx.w_dtype), db, None
 
 
