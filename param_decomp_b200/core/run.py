@@ -257,6 +257,9 @@ def run_decomposition_training(
         if cadence.should_log_train(step) or state.step == pd.steps:
             scalars = {k: v for k, v in metrics.items()}
             scalars.update(perf.tick(state.step))
+            from param_decomp_b200.core.gauge import uv_norm_ratio_metrics
+
+            scalars.update(uv_norm_ratio_metrics(state.components))  # drift of the V/U scale symmetry
             if extra_log is not None:
                 scalars.update(extra_log(step, state, ctx))
             floats = sink.log(step, scalars) if sink is not None else {("train/" + k): float(v) for k, v in scalars.items()}
