@@ -259,6 +259,8 @@ def run_decomposition_training(
             scalars.update(perf.tick(state.step))
             from param_decomp_b200.core.gauge import uv_norm_ratio_metrics
 
+            if hasattr(state.components_opt, "refresh_full_fp32"):
+                state.components_opt.refresh_full_fp32()  # sharded masters: gather the shards before reading
             scalars.update(uv_norm_ratio_metrics(state.components))  # drift of the V/U scale symmetry
             if extra_log is not None:
                 scalars.update(extra_log(step, state, ctx))
