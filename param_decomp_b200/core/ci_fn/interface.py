@@ -52,13 +52,17 @@ def _map(fn, v):
     return fn(v)
 
 
-def squash_fused(pre: dict[str, Tensor], gamma: float, normalize_at_one: bool) -> CI:
+def squash_fused(pre: dict[str, Tensor | SelectedCI], gamma: float, normalize_at_one: bool) -> CI:
     """One kernel pass per site: lower importances and the minimality activity together."""
-    from param_decomp_b200.ops.elementwise import squash_activity
+    from param_decomp_b200.ops.elementwise import squash_activity, squash_activity_selected
 
     lower, act = {}, {}
     for k, v in pre.items():
-        lower[k], act[k] = squash_activity(v, gamma, normalize_at_one)
+        if isinstance(v, SelectedCI):
+            low, act[k] = squash_activity_selected(v.values, v.selection.indices, v.n_blocks, gamma, normalize_at_one)
+            lower[k] = SelectedCI(low, v.selection, v.n_blocks)
+        else:
+            lower[k], act[k] = squash_activity(v, gamma, normalize_at_one)
     return CI(preactivations=pre, lower=lower, upper={}, activity=act)
 
 

@@ -276,13 +276,19 @@ def _detach_ci(ci_lower: dict[str, Tensor]) -> dict[str, Tensor]:
     return {k: v.detach() for k, v in ci_lower.items()}
 
 
+def _fusable_pre(v) -> bool:
+    if isinstance(v, SelectedCI):
+        t = v.values
+        return t.is_cuda and t.dtype == torch.bfloat16 and v.C_block % 8 == 0
+    return isinstance(v, torch.Tensor) and v.is_cuda and v.dtype == torch.bfloat16 and v.shape[-1] % 8 == 0
+
+
 def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: int | None = None) -> CI:
     pre = state.ci_fn(clean.taps, aux=clean.aux, components=state.components,
                       segment_ids=clean.aux.get("segment_ids"), positions=clean.aux.get("positions"))
     cfg = ctx.objective.minimality
     fusable = (step is not None and ctx.lazy_masks and isinstance(cfg, L.ImportanceMinimalityLossConfig)
-               and all(isinstance(v, torch.Tensor) and v.is_cuda and v.dtype == torch.bfloat16
-                       and v.shape[-1] % 8 == 0 for v in pre.values()))
+               and all(_fusable_pre(v) for v in pre.values()))
     if fusable:
         from param_decomp_b200.core.ci_fn.interface import squash_fused
 
@@ -354,8 +360,10 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
 
     if obj.faith is not None:
         c_f = scheduled_or_constant(obj.faith.coeff, step, total)
-        if direct and ctx.relative_faithfulness and all(not s.blocked for s in ctx.model.sites):
-            from param_decomp_b200.ops.faithfulness import fused_faithfulness
+        from param_decomp_b200.ops import faithfulness as fused_faith
+
+        if direct and ctx.relative_faithfulness and fused_faith.blocked_supported(state.components):
+            fused_faithfulness = fused_faith.fused_faithfulness
 
             hi_lo = None
             if sharded and state.components_opt.work_lo_flat is not None:

@@ -38,6 +38,7 @@ from param_decomp_b200.core.decomposed_linear import site_forward
 from param_decomp_b200.core.masking import Masks, SiteMask
 from param_decomp_b200.core.model import ForwardResult
 from param_decomp_b200.models import transformer as tf
+from param_decomp_b200.ops.grouped import repeat_rows
 
 EXPERT_KINDS = ("experts_gate", "experts_up", "experts_down")
 
@@ -166,8 +167,8 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
                 order = expert_of_job.argsort(stable=True)
                 for n in torch.bincount(expert_of_job, minlength=a.n_experts).tolist():
                     bounds.append(bounds[-1] + n)
-            y_jobs = self.expert_jobs(i, xt[token_of_job], expert_of_job, order, bounds, weights, masks, token_of_job,
-                                      slot_of_job)
+            y_jobs = self.expert_jobs(i, repeat_rows(xt, k), expert_of_job, order, bounds, weights, masks, token_of_job,
+                                      slot_of_job, routing_indices=sel.indices)
         w = sel.weights.reshape(B * T, k, 1).to(y_jobs.dtype)
         return (y_jobs.reshape(B * T, k, d) * w).sum(1).reshape(B, T, d)
 
@@ -219,13 +220,15 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
                                     need_wgrad=weights.direct_grads)
 
     def expert_jobs(self, i: int, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int], weights,
-                    masks, token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
-        """gate/up/down of every job; `expert_of_job` indexes THIS rank's expert bank."""
+                    masks, token_of_job: Tensor, slot_of_job: Tensor, routing_indices: Tensor | None = None) -> Tensor:
+        """gate/up/down of every job; `expert_of_job` indexes THIS rank's expert bank. `routing_indices`:
+        the pinned `[.., k]` selection tensor the jobs were flattened from (keys the cached job layout)."""
         n = lambda kind: tf.site_name("moe", i, kind)  # noqa: E731
         if self._fused(x_jobs):
             from param_decomp_b200.ops.grouped import JobLayout
 
-            layout = JobLayout.build(expert_of_job, self.w[n("experts_gate") + ".weight"].shape[0])
+            n_e = self.w[n("experts_gate") + ".weight"].shape[0]
+            layout = JobLayout.cached(routing_indices, n_e) if routing_indices is not None else JobLayout.build(expert_of_job, n_e)
             xs = layout.scatter_rows(x_jobs)
             gate = self._grouped_site(n("experts_gate"), xs, layout, weights, masks, token_of_job, slot_of_job)
             up = self._grouped_site(n("experts_up"), xs, layout, weights, masks, token_of_job, slot_of_job)

@@ -36,6 +36,7 @@ from param_decomp_b200.core.components import BlockSelection, SiteSpec
 from param_decomp_b200.formats.nonlinearity import KVHeads, Neurons, NonlinearityAlignment, QueryHeads
 from param_decomp_b200.models import moe, ports
 from param_decomp_b200.models import transformer as tf
+from param_decomp_b200.ops.grouped import repeat_rows
 
 KIND_ORDER = ("gdn_q", "gdn_k", "gdn_v", "gdn_z", "gdn_b", "gdn_a", "gdn_out", "attn_q", "attn_k", "attn_v", "attn_o",
               "experts_gate", "experts_up", "experts_down", "shared_gate", "shared_up", "shared_down")
@@ -315,8 +316,8 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
                 order = expert_of_job.argsort(stable=True)
                 for n in torch.bincount(expert_of_job, minlength=a.n_experts).tolist():
                     bounds.append(bounds[-1] + n)
-            y_jobs = self.expert_jobs(i, xt[token_of_job], expert_of_job, order, bounds, weights, masks, token_of_job,
-                                      slot_of_job)
+            y_jobs = self.expert_jobs(i, repeat_rows(xt, k), expert_of_job, order, bounds, weights, masks, token_of_job,
+                                      slot_of_job, routing_indices=(pinned[i].indices if pinned is not None else sel.indices))
         routed = (y_jobs.reshape(B * T, k, d) * sel_w.reshape(B * T, k, 1).to(y_jobs.dtype)).sum(1).reshape(B, T, d)
         h = self._swiglu(lin(x, "shared_gate"), lin(x, "shared_up"))
         if taps is not None:
@@ -326,12 +327,13 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
         return routed + (sg * shared.float()).to(x.dtype)
 
     def expert_jobs(self, i: int, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int], weights,
-                    masks, token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
+                    masks, token_of_job: Tensor, slot_of_job: Tensor, routing_indices: Tensor | None = None) -> Tensor:
         n = lambda kind: site_name(i, kind)  # noqa: E731
         if self._fused(x_jobs):
             from param_decomp_b200.ops.grouped import JobLayout
 
-            layout = JobLayout.build(expert_of_job, self.w[n("experts_gate") + ".weight"].shape[0])
+            n_e = self.w[n("experts_gate") + ".weight"].shape[0]
+            layout = JobLayout.cached(routing_indices, n_e) if routing_indices is not None else JobLayout.build(expert_of_job, n_e)
             xs = layout.scatter_rows(x_jobs)
             gate = self._grouped_site(n("experts_gate"), xs, layout, weights, masks, token_of_job, slot_of_job)
             up = self._grouped_site(n("experts_up"), xs, layout, weights, masks, token_of_job, slot_of_job)

@@ -432,6 +432,105 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
   }
 }
 
+// ---- the same pair for narrow CI of an expert-blocked site ---------------------------------------
+// `pre [tokens, k * c]` holds one c-wide slot per selected expert of each token. The rows of the
+// padded sorted job layout map to (token, slot) through `rowmap`, and every 128-row block belongs
+// to one expert (`bgroup`), so a block sums its rows in registers and issues one atomic per column
+// into `colsum [n_experts * c]`. `lower` is written back in token order.
+__global__ void ci_squash_activity_jobs_kernel(const __nv_bfloat16* __restrict__ pre,
+                                               __nv_bfloat16* __restrict__ lower,
+                                               float* __restrict__ colsum,
+                                               const int4* __restrict__ rowmap,
+                                               const int* __restrict__ bgroup, int c, long long pitch,
+                                               float gamma2, float norm, float alpha) {
+  const int e = bgroup[blockIdx.y];
+  if (e < 0) return;
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + cg) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < c) {
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int4 rm = rowmap[static_cast<long long>(blockIdx.y) * 128 + rl + 8 * i];
+      if (rm.x < 0) continue;
+      const long long at = static_cast<long long>(rm.x) * pitch + rm.y + col;
+      const uint4 q = *reinterpret_cast<const uint4*>(pre + at);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+      __nv_bfloat162 lo[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        const float lx = fminf(fmaxf(f.x, 0.f), 1.f), ly = fminf(fmaxf(f.y, 0.f), 1.f);
+        lo[k] = __floats2bfloat162_rn(lx, ly);
+        const float ux = f.x > 1.f ? 1.f + alpha * (f.x - 1.f) : lx;
+        const float uy = f.y > 1.f ? 1.f + alpha * (f.y - 1.f) : ly;
+        acc[2 * k] += norm * __fdividef(ux * ux, ux * ux + gamma2);
+        acc[2 * k + 1] += norm * __fdividef(uy * uy, uy * uy + gamma2);
+      }
+      *reinterpret_cast<uint4*>(lower + at) = *reinterpret_cast<uint4*>(lo);
+    }
+  }
+  __shared__ float red[8][32][8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[rl][cg][k] = acc[k];
+  __syncthreads();
+  if (rl == 0 && col < c) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float v = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v += red[j][cg][k];
+      atomicAdd(colsum + static_cast<long long>(e) * c + col + k, v);
+    }
+  }
+}
+
+// Backward in token order: the expert of a slot comes from `experts [tokens, k]`.
+__global__ void ci_squash_activity_jobs_bwd_kernel(const __nv_bfloat16* __restrict__ pre,
+                                                   const __nv_bfloat16* __restrict__ dlower,
+                                                   const float* __restrict__ dcol,
+                                                   const long long* __restrict__ experts,
+                                                   __nv_bfloat16* __restrict__ dpre, long long tokens,
+                                                   int k_sel, int c, float gamma2, float norm,
+                                                   float alpha) {
+  const int groups = c / 8;
+  const long long total = tokens * k_sel * groups;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long job = i / groups;
+    const int col = static_cast<int>(i - job * groups) * 8;
+    const long long e = experts[job];
+    const uint4 q = *reinterpret_cast<const uint4*>(pre + i * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    uint4 gq = make_uint4(0, 0, 0, 0);
+    if (dlower) gq = *reinterpret_cast<const uint4*>(dlower + i * 8);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
+    const float4 d0 = *reinterpret_cast<const float4*>(dcol + e * c + col);
+    const float4 d1 = *reinterpret_cast<const float4*>(dcol + e * c + col + 4);
+    const float dc[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]), g = __bfloat1622float2(gh[k]);
+      float out[2];
+      const float x[2] = {f.x, f.y}, gg[2] = {g.x, g.y};
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const float xv = x[t];
+        float lg = 0.f, u, du;
+        if (xv > 1.f) { u = 1.f + alpha * (xv - 1.f); du = alpha; }
+        else if (xv > 0.f) { u = xv; du = 1.f; lg = gg[t]; }
+        else { u = 0.f; du = 0.f; lg = gg[t] < 0.f ? alpha * gg[t] : 0.f; }
+        const float den = u * u + gamma2;
+        const float dpsi = __fdividef(norm * 2.f * u * gamma2, den * den);
+        out[t] = lg + dc[2 * k + t] * dpsi * du;
+      }
+      o[k] = __floats2bfloat162_rn(out[0], out[1]);
+    }
+    *reinterpret_cast<uint4*>(dpre + i * 8) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
 // ---- vocabulary KL: one block per position ------------------------------------------------------
 // kl[row] = KL(softmax(lc[row]) || softmax(lm[row]));  dlm[row] = softmax(lm) - softmax(lc)
 // (the caller scales by the upstream gradient / number of positions inside the next GEMM).
@@ -674,6 +773,29 @@ extern "C" int pd_ci_squash_activity_bwd(const void* pre, const void* dlower, co
                                   static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(dlower), dcol,
       static_cast<__nv_bfloat16*>(dpre), rows, C, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_ci_squash_activity_jobs(const void* pre, void* lower, float* colsum, const void* rowmap,
+                                          const int* bgroup, long long n_rows, int c, long long pitch,
+                                          float gamma, int normalize_at_one, float alpha, void* stream) {
+  if (c % 8 != 0 || pitch % 8 != 0 || n_rows % 128 != 0 || n_rows <= 0) return 5;
+  const float g2 = gamma * gamma;
+  ci_squash_activity_jobs_kernel<<<dim3((c + 255) / 256, static_cast<unsigned>(n_rows / 128)), 256, 0,
+                                   static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(lower), colsum,
+      static_cast<const int4*>(rowmap), bgroup, c, pitch, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_ci_squash_activity_jobs_bwd(const void* pre, const void* dlower, const float* dcol,
+                                              const long long* experts, void* dpre, long long tokens, int k_sel,
+                                              int c, float gamma, int normalize_at_one, float alpha,
+                                              void* stream) {
+  if (c % 8 != 0 || tokens <= 0) return 5;
+  const float g2 = gamma * gamma;
+  ci_squash_activity_jobs_bwd_kernel<<<blocks_for(tokens * k_sel * (c / 8), kThreads), kThreads, 0,
+                                       static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(dlower), dcol, experts,
+      static_cast<__nv_bfloat16*>(dpre), tokens, k_sel, c, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_vocab_kl(const void* lc, const void* lm, void* dlm, float* kl, long long rows, int V,

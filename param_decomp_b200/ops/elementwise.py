@@ -182,6 +182,68 @@ def squash_activity(pre: Tensor, gamma: float, normalize_at_one: bool, alpha: fl
     return lower.reshape(*lead, -1), act
 
 
+class _SquashActivityJobs(torch.autograd.Function):
+    """Narrow CI of an expert-blocked site: `pre [tokens, k * c]` bf16 with the selected experts
+    `experts [tokens, k]` -> (`lower` bf16 in the same layout, `activity [n_blocks * c]` fp32 = the
+    per-component sum of the smooth-L0 penalty over the tokens that selected its expert, divided by
+    the number of tokens). The forward walks the padded sorted job layout so every thread block sums
+    one expert's rows; the backward is pointwise in token order."""
+
+    @staticmethod
+    def forward(ctx, pre: Tensor, experts: Tensor, layout, n_blocks: int, gamma: float,  # type: ignore[override]
+                normalize_at_one: bool, alpha: float):
+        tokens, kc = pre.shape
+        k = experts.shape[-1]
+        c = kc // k
+        pre = pre.contiguous()
+        experts = experts.reshape(tokens, k).contiguous()
+        lower = torch.empty_like(pre)
+        colsum = torch.zeros(n_blocks * c, device=pre.device, dtype=torch.float32)
+        rowmap = layout.rowmap(k, c)
+        lib = _lib()
+        lib.pd_ci_squash_activity_jobs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                   C.c_longlong, C.c_int, C.c_longlong, C.c_float, C.c_int,
+                                                   C.c_float, C.c_void_p]
+        _check(lib.pd_ci_squash_activity_jobs(pre.data_ptr(), lower.data_ptr(), colsum.data_ptr(), rowmap.data_ptr(),
+                                              layout.bgroup.data_ptr(), layout.n_rows, c, kc, gamma,
+                                              int(normalize_at_one), alpha, _s()), "ci_squash_activity_jobs")
+        ctx.save_for_backward(pre, experts)
+        ctx.cfg = (gamma, normalize_at_one, alpha, k, c)
+        ctx.n_blocks = n_blocks
+        return lower, colsum / tokens
+
+    @staticmethod
+    def backward(ctx, dlower: Tensor | None, dact: Tensor | None):  # type: ignore[override]
+        pre, experts = ctx.saved_tensors
+        gamma, norm, alpha, k, c = ctx.cfg
+        tokens = pre.shape[0]
+        dcol = (dact.float() / tokens).contiguous() if dact is not None else torch.zeros(
+            ctx.n_blocks * c, device=pre.device)
+        dpre = torch.empty_like(pre)
+        lib = _lib()
+        lib.pd_ci_squash_activity_jobs_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                       C.c_longlong, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float,
+                                                       C.c_void_p]
+        dl = None if dlower is None else dlower.contiguous()
+        _check(lib.pd_ci_squash_activity_jobs_bwd(pre.data_ptr(), dl.data_ptr() if dl is not None else None,
+                                                  dcol.data_ptr(), experts.data_ptr(), dpre.data_ptr(), tokens, k, c,
+                                                  gamma, int(norm), alpha, _s()), "ci_squash_activity_jobs_bwd")
+        return dpre, None, None, None, None, None, None
+
+
+def squash_activity_selected(values: Tensor, experts: Tensor, n_blocks: int, gamma: float, normalize_at_one: bool,
+                             alpha: float = 0.01) -> tuple[Tensor, Tensor]:
+    """`values [..., k * c]`, `experts [..., k]` (the pinned selection tensor, which also keys the cached
+    job layout) -> (`lower` like `values`, `activity [n_blocks * c]`)."""
+    from param_decomp_b200.ops.grouped import JobLayout
+
+    layout = JobLayout.cached(experts, n_blocks)
+    lead = values.shape[:-1]
+    lower, act = _SquashActivityJobs.apply(values.reshape(-1, values.shape[-1]), experts, layout, n_blocks, gamma,
+                                           normalize_at_one, alpha)
+    return lower.reshape(*lead, -1), act
+
+
 def vocab_kl_rows(lc: Tensor, lm: Tensor, want_grad: bool) -> tuple[Tensor, Tensor | None]:
     """Per-row `KL(softmax(lc) || softmax(lm))` and (optionally) `softmax(lm) - softmax(lc)`.
     `lc`, `lm`: `[rows, V]` bf16 views whose row pitch is a multiple of 8 elements."""

@@ -30,8 +30,7 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
     optimizer (then no fp32 master is read). With `world > 1` the sites are dealt round-robin to the
     ranks: each rank does the GEMMs of its own sites only, writes their gradients scaled by `world`
     (the gradient reduction averages over ranks), and returns its partial loss; the caller sums it."""
-    sites = [s for s in stacks.sites if not s.blocked]
-    assert len(sites) == len(stacks.sites), "blocked sites use the grouped faithfulness path"
+    sites = list(stacks.sites)
     dev = next(stacks.parameters()).device
     sumsq = torch.zeros(len(sites), 8, device=dev, dtype=torch.float32)
     n_sites = len(sites)
@@ -56,6 +55,12 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
                 continue
             Wb = W[s.name]
             assert Wb.dtype == torch.bfloat16, "the fused faithfulness path expects a bf16 target"
+            if s.blocked:
+                _blocked_site(s, Vh[i], Vl[i], Uh[i], Ul[i], Wb, sumsq[row_of[s.name]:row_of[s.name] + 1],
+                              pV.grad[i] if accumulate_grads else None, pU.grad[i] if accumulate_grads else None,
+                              -2.0 * coeff * world / (n_sites * w_sq_host[s.name]))
+                k += 1
+                continue
             U_cat = torch.cat([Uh[i], Ul[i], Uh[i]], dim=0)  # [3C, d_out]
             V_cat = torch.cat([Vh[i], Vh[i], Vl[i]], dim=1)  # [d_in, 3C]
             D = torch.empty(s.d_out, s.d_in, device=dev, dtype=torch.bfloat16)
@@ -68,3 +73,26 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
             k += 1
     wsq = torch.tensor([w_sq_host[s.name] for s in sites], device=dev, dtype=torch.float32)
     return (sumsq[:, 0] / wsq).sum() / n_sites
+
+
+def blocked_supported(stacks: ComponentStacks) -> bool:
+    """Blocked sites run as one grouped product over the `[E * d_out, d_in]` view of the expert bank:
+    a 128-row tile must not straddle two experts."""
+    return all(not s.blocked or (s.d_out % 128 == 0 and s.d_in % 8 == 0 and s.C_block % 8 == 0) for s in stacks.sites)
+
+
+def _blocked_site(s, Vh: Tensor, Vl: Tensor, Uh: Tensor, Ul: Tensor, Wb: Tensor, sumsq: Tensor, gV: Tensor | None,
+                  gU: Tensor | None, alpha: float) -> None:
+    """`V [E, d_in, c]`, `U [E, c, d_out]`, `W [E, d_out, d_in]`: the residual of all experts in one
+    launch (each 128-row tile of the stacked rows picks its expert's `V`), then two batched products
+    for the gradients."""
+    E, d_out, d_in = Wb.shape
+    A = torch.cat([Uh, Ul, Uh], dim=1).transpose(1, 2).reshape(E * d_out, -1)  # rows (e, o), K = 3c
+    V_cat = torch.cat([Vh, Vh, Vl], dim=2)  # [E, d_in, 3c]
+    D = torch.empty(E, d_out, d_in, device=Wb.device, dtype=torch.bfloat16)
+    owner = torch.arange(E, device=Wb.device, dtype=torch.int32).repeat_interleave(d_out // 128)
+    nv.gemm(A, V_cat, D.view(E * d_out, d_in), epi=nv.EPI_FAITH, ci=Wb.reshape(E * d_out, d_in), dci=sumsq,
+            bgroup_of_mblock=owner)
+    if gV is not None:
+        nv.gemm(D, Uh, gV, a_mn=True, accumulate=True, alpha=alpha)  # dV[e] = alpha D_e^T U_e^T
+        nv.gemm(Vh, D, gU, a_mn=True, accumulate=True, alpha=alpha)  # dU[e] = alpha V_e^T D_e^T

@@ -13,6 +13,7 @@ Pallas-Triton transposed grouped matmul for the weight gradient
 
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
 
 import torch
@@ -22,6 +23,7 @@ from param_decomp_b200.ops import elementwise as ew
 from param_decomp_b200.ops import native as nv
 
 PAD = 128
+_LAYOUTS: dict[tuple[int, int], tuple[weakref.ref, "JobLayout"]] = {}
 
 
 @dataclass
@@ -35,9 +37,26 @@ class JobLayout:
     counts: Tensor  # [E] int64
 
     @classmethod
+    def cached(cls, indices: Tensor, n_experts: int) -> "JobLayout":
+        """The layout of the jobs `indices.reshape(-1)` (token-major, slot-minor), built once per
+        routing decision: the clean pass, every masked pass and the CI function of a layer all see the
+        same pinned `indices` tensor, so they share one sort."""
+        key = (id(indices), n_experts)
+        hit = _LAYOUTS.get(key)
+        if hit is not None and hit[0]() is indices:
+            return hit[1]
+        for k in [k for k, (ref, _) in _LAYOUTS.items() if ref() is None]:
+            del _LAYOUTS[k]
+        layout = cls.build(indices.reshape(-1), n_experts)
+        _LAYOUTS[key] = (weakref.ref(indices), layout)
+        return layout
+
+    @classmethod
     def build(cls, expert_of_job: Tensor, n_experts: int) -> "JobLayout":
         J = expert_of_job.numel()
-        counts = torch.bincount(expert_of_job, minlength=n_experts)
+        # (a scatter-add, not bincount: bincount sizes its output from the data and synchronises)
+        counts = torch.zeros(n_experts, dtype=torch.int64, device=expert_of_job.device).scatter_add_(
+            0, expert_of_job, torch.ones_like(expert_of_job))
         padded = (counts + PAD - 1) // PAD * PAD
         starts = torch.cumsum(padded, 0) - padded
         order = expert_of_job.argsort(stable=True)
@@ -73,12 +92,47 @@ class JobLayout:
         return cache[key]
 
     def scatter_rows(self, x_jobs: Tensor) -> Tensor:
-        out = x_jobs.new_zeros(self.n_rows, x_jobs.shape[-1])
-        out.index_copy_(0, self.pos, x_jobs)
-        return out
+        """Job order -> padded sorted rows (zeros in the padding)."""
+        return _ScatterRows.apply(x_jobs, self.pos, self.n_rows)
 
     def gather_rows(self, padded: Tensor) -> Tensor:
-        return padded[self.pos]
+        """Padded sorted rows -> job order."""
+        return _GatherRows.apply(padded, self.pos, self.n_rows)
+
+
+class _ScatterRows(torch.autograd.Function):
+    """`pos` is injective, so the adjoint of the row scatter is a plain row gather (the generic
+    indexing backward would sort the indices to accumulate duplicates that cannot occur)."""
+
+    @staticmethod
+    def forward(ctx, x_jobs: Tensor, pos: Tensor, n_rows: int) -> Tensor:  # type: ignore[override]
+        ctx.pos = pos
+        out = x_jobs.new_zeros(n_rows, x_jobs.shape[-1])
+        out.index_copy_(0, pos, x_jobs)
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        return g.index_select(0, ctx.pos), None, None
+
+
+class _GatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, padded: Tensor, pos: Tensor, n_rows: int) -> Tensor:  # type: ignore[override]
+        ctx.pos, ctx.n_rows = pos, n_rows
+        return padded.index_select(0, pos)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        out = g.new_zeros(ctx.n_rows, g.shape[-1])
+        out.index_copy_(0, ctx.pos, g)
+        return out, None, None
+
+
+def repeat_rows(x: Tensor, k: int) -> Tensor:
+    """`x [N, d] -> [N * k, d]`, row `n` repeated `k` times in place (token-major jobs); the adjoint
+    is a sum over the `k` copies rather than an index accumulation."""
+    return x.unsqueeze(1).expand(x.shape[0], k, x.shape[1]).reshape(x.shape[0] * k, x.shape[1])
 
 
 class _GroupedSite(torch.autograd.Function):

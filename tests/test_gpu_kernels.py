@@ -192,6 +192,41 @@ def test_squash_activity_matches_eager(nv):
     assert rel(pre.grad, p2.grad) < 1e-2
 
 
+def test_squash_activity_selected_matches_eager(nv):
+    """Narrow CI of an expert-blocked site: the job-layout kernel against the eager squash plus the
+    scatter-by-expert activity, values and gradients; also the injective row scatter / gather."""
+    from param_decomp_b200.core import losses
+    from param_decomp_b200.core.components import BlockSelection, SelectedCI
+    from param_decomp_b200.core.squashing import lower_leaky_hard_sigmoid, upper_leaky_hard_sigmoid
+    from param_decomp_b200.ops.elementwise import squash_activity_selected
+    from param_decomp_b200.ops.grouped import JobLayout, repeat_rows
+
+    torch.manual_seed(16)
+    N, E, k, c = 333, 10, 3, 40
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(N)])
+    sel = BlockSelection(idx, torch.rand(N, k, device="cuda"))
+    pre = (torch.randn(N, k * c, device="cuda") * 1.5).to(bf).requires_grad_(True)
+    lower, act = squash_activity_selected(pre, idx, E, 0.3, True)
+    gl, ga = torch.randn_like(lower), torch.randn(E * c, device="cuda")
+    (lower.float() * gl.float()).sum().add((act * ga).sum()).backward()
+    p2 = pre.detach().float().requires_grad_(True)
+    l2 = lower_leaky_hard_sigmoid(p2)
+    a2 = losses.component_activity(SelectedCI(upper_leaky_hard_sigmoid(p2), sel, E), 0.3, True)
+    ((l2 * gl.float()).sum() + (a2 * ga).sum()).backward()
+    _done(nv)
+    assert rel(lower, l2) < 1e-6 and rel(act, a2) < 1e-4
+    assert rel(pre.grad, p2.grad) < 1e-2
+
+    layout = JobLayout.cached(idx, E)
+    assert JobLayout.cached(idx, E) is layout
+    x = torch.randn(N, 24, device="cuda", requires_grad=True)
+    y = layout.gather_rows(layout.scatter_rows(repeat_rows(x, k)) * 2.0)
+    gy = torch.randn_like(y)
+    (y * gy).sum().backward()
+    assert torch.equal(y.detach(), (x.detach() * 2.0).repeat_interleave(k, 0))
+    assert rel(x.grad, 2.0 * gy.reshape(N, k, -1).sum(1)) < 1e-6
+
+
 def test_vocab_kl_matches_eager(nv):
     from param_decomp_b200.core.losses import kl_from_logits
     from param_decomp_b200.ops import vocab_kl
@@ -320,6 +355,34 @@ def test_fused_faithfulness_matches_fp32(nv):
     ref_exact = losses.faithfulness_loss(st, {k: v.float() for k, v in Wx.items()})
     _done(nv)
     assert float(exact) < 4 * float(ref_exact) + 1e-7
+
+
+def test_fused_faithfulness_blocked_sites(nv):
+    """Expert-blocked sites: one grouped residual product over the stacked expert rows plus batched
+    gradient products, against the fp32 eager loss."""
+    from param_decomp_b200.core import losses
+    from param_decomp_b200.core.components import ComponentStacks, SiteSpec
+    from param_decomp_b200.ops.faithfulness import blocked_supported, fused_faithfulness
+
+    torch.manual_seed(19)
+    E = 5
+    sites = (SiteSpec("up", 192, 256, E * 64, group="gu", n_blocks=E), SiteSpec("gate", 192, 256, E * 64, group="gu", n_blocks=E),
+             SiteSpec("down", 256, 128, E * 64, group="dn", n_blocks=E), SiteSpec("q", 192, 192, 320, group="q"))
+    st = ComponentStacks(sites).to("cuda")
+    st.init_random(torch.Generator().manual_seed(0))
+    assert blocked_supported(st)
+    W = {s.name: (st.weight(s.name).detach() + 0.02 * torch.randn_like(st.weight(s.name))).to(bf).contiguous() for s in sites}
+    wsq = {k: float(v.float().pow(2).sum()) for k, v in W.items()}
+    loss = fused_faithfulness(st, W, wsq, coeff=2.0)
+    got = {n: p.grad.clone() for n, p in st.named_parameters()}
+    for p in st.parameters():
+        p.grad = None
+    ref = losses.faithfulness_loss(st, {k: v.float() for k, v in W.items()})
+    (2.0 * ref).backward()
+    _done(nv)
+    assert float(loss) == pytest.approx(float(ref), rel=2e-3)
+    for n, p in st.named_parameters():
+        assert rel(got[n], p.grad) < 2e-2, n
 
 
 def test_native_philox_matches_reference(nv):
