@@ -95,12 +95,12 @@ class BlockedSiteMLP(nn.Module):
         if (self.fused and x.is_cuda and x2.shape[1] % 8 == 0 and hidden % 64 == 0 and self.c_block % 8 == 0):
             # one batched GEMM for the shared trunk, then the per-expert heads as a grouped GEMM over
             # (token, slot) jobs sorted by expert: no Python loop over experts, no host sync
-            from param_decomp_b200.ops.grouped import JobLayout, grouped_linear_trainable, repeat_rows
+            from param_decomp_b200.ops.grouped import JobLayout, grouped_linear_trainable
             from param_decomp_b200.ops.linear import bmm_bias
 
             h = F.gelu(bmm_bias(x2.to(torch.bfloat16).unsqueeze(0), self.w1.unsqueeze(0), self.b1.view(1, 1, -1))[0])
             layout = JobLayout.cached(sel.indices, self.n_blocks)
-            hj = layout.scatter_rows(repeat_rows(h, k))
+            hj = layout.expand_tokens(h, k)
             out = layout.gather_rows(grouped_linear_trainable(hj, self.heads, self.head_bias, layout))
             return SelectedCI(out.reshape(*lead, k * self.c_block), sel, self.n_blocks)
         h = F.gelu(x2.float() @ self.w1 + self.b1)  # [N, hidden]

@@ -159,6 +159,9 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         token_of_job = torch.arange(B * T, device=x.device).repeat_interleave(k)
         slot_of_job = torch.arange(k, device=x.device).repeat(B * T)
         expert_of_job = idx.reshape(-1)
+        if self.ep is None and self._fused(xt):
+            return self.expert_tokens(i, xt, sel.indices, sel.weights, weights, masks, token_of_job,
+                                      slot_of_job).reshape(B, T, d)
         if self.ep is not None:
             y_jobs = self.ep.run_experts(self, i, xt, expert_of_job, token_of_job, slot_of_job, weights, masks)
         else:
@@ -218,6 +221,22 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         r = per_job(None if sm.route is None else sm.route.reshape(-1), 0)
         return grouped.grouped_site(xs, V, U, W, layout, m, d, r, weights.grad_V.get(name), weights.grad_U.get(name),
                                     need_wgrad=weights.direct_grads)
+
+    def expert_tokens(self, i: int, xt: Tensor, indices: Tensor, route_w: Tensor, weights, masks,
+                      token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
+        """Fused single-rank path: tokens `[N, d]` fan out to padded sorted job rows, run gate / up / down on
+        the grouped kernels and come back as the routing-weighted sum per token."""
+        from param_decomp_b200.ops.grouped import JobLayout
+
+        n = lambda kind: tf.site_name("moe", i, kind)  # noqa: E731
+        k = indices.shape[-1]
+        layout = JobLayout.cached(indices, self.w[n("experts_gate") + ".weight"].shape[0])
+        xs = layout.expand_tokens(xt, k)
+        gate = self._grouped_site(n("experts_gate"), xs, layout, weights, masks, token_of_job, slot_of_job)
+        up = self._grouped_site(n("experts_up"), xs, layout, weights, masks, token_of_job, slot_of_job)
+        down = self._grouped_site(n("experts_down"), self._swiglu(gate, up), layout, weights, masks, token_of_job,
+                                  slot_of_job)
+        return layout.combine(down, route_w.reshape(-1, k))
 
     def expert_jobs(self, i: int, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int], weights,
                     masks, token_of_job: Tensor, slot_of_job: Tensor, routing_indices: Tensor | None = None) -> Tensor:

@@ -319,6 +319,71 @@ __global__ void rowscale_kernel(const __nv_bfloat16* __restrict__ x, const float
   }
 }
 
+// ---- routed rows: tokens <-> padded sorted job rows -----------------------------------------------
+// `rowmap[r] = (token, slot, -, -)` of padded row r (token -1 on padding rows); `pos[token * k + slot]`
+// is the inverse. Both directions move whole rows in 16-byte pieces; no row is written twice, so
+// neither direction needs atomics or a cleared destination.
+//
+// out[r, :] = w[src] * x[src, :],  src = token * rep + slot * use_slot;  zero rows on padding.
+__global__ void rows_expand_kernel(const __nv_bfloat16* __restrict__ x, const int4* __restrict__ rowmap,
+                                   const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                   long long n_rows, int d, int k_sel, int rep, int use_slot) {
+  const int segs = d / 8;
+  const long long total = n_rows * segs;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / segs;
+    const int seg = static_cast<int>(i - r * segs);
+    const int4 rm = __ldg(rowmap + r);
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (rm.x >= 0) {
+      const long long src = static_cast<long long>(rm.x) * rep + (use_slot ? rm.y : 0);
+      q = *reinterpret_cast<const uint4*>(x + src * d + seg * 8);
+      if (w != nullptr) {
+        const float sc = w[static_cast<long long>(rm.x) * k_sel + rm.y];
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          h[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = q;
+  }
+}
+
+// y[n, :] = sum_s w[n, s] * padded[pos[n * k + s], :]   (fp32 accumulation)
+__global__ void rows_combine_kernel(const __nv_bfloat16* __restrict__ padded, const long long* __restrict__ pos,
+                                    const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                    long long tokens, int d, int k_sel) {
+  const int segs = d / 8;
+  const long long total = tokens * segs;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long n = i / segs;
+    const int seg = static_cast<int>(i - n * segs);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int s = 0; s < k_sel; ++s) {
+      const long long r = __ldg(pos + n * k_sel + s);
+      const float sc = w != nullptr ? __ldg(w + n * k_sel + s) : 1.0f;
+      const uint4 q = *reinterpret_cast<const uint4*>(padded + r * d + seg * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] = fmaf(f.x, sc, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(f.y, sc, acc[2 * j + 1]);
+      }
+    }
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(y + i * 8) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
 // lower (bf16, masks) and upper (fp32-accurate bf16, minimality) leaky-hard sigmoids of fp32/bf16
 // pre-activations in one pass.
 __global__ void ci_squash_kernel(const __nv_bfloat16* __restrict__ pre,
@@ -741,6 +806,21 @@ extern "C" int pd_rowscale(const void* x, const float* s, void* y, long long row
   if (d % 8 != 0) return 5;
   rowscale_kernel<<<blocks_for(rows * (d / 8), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), s, static_cast<__nv_bfloat16*>(y), rows, d);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rows_expand(const void* x, const void* rowmap, const float* w, void* out, long long n_rows,
+                              int d, int k_sel, int rep, int use_slot, void* stream) {
+  if (d % 8 != 0 || n_rows <= 0) return 5;
+  rows_expand_kernel<<<blocks_for(n_rows * (d / 8), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const int4*>(rowmap), w,
+      static_cast<__nv_bfloat16*>(out), n_rows, d, k_sel, rep, use_slot);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rows_combine(const void* padded, const long long* pos, const float* w, void* y,
+                               long long tokens, int d, int k_sel, void* stream) {
+  if (d % 8 != 0 || tokens <= 0) return 5;
+  rows_combine_kernel<<<blocks_for(tokens * (d / 8), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(padded), pos, w, static_cast<__nv_bfloat16*>(y), tokens, d, k_sel);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_ci_squash(const void* pre, void* lower, void* upper, long long n, float alpha, void* stream) {

@@ -61,6 +61,32 @@ def rowscale(x: Tensor, s: Tensor) -> Tensor:
     return y
 
 
+def rows_expand(x: Tensor, rowmap: Tensor, w: Tensor | None, n_rows: int, k: int, rep: int, use_slot: bool) -> Tensor:
+    """`out[r] = w[token, slot] * x[token * rep + slot * use_slot]` for the `(token, slot)` that `rowmap`
+    gives padded row `r`; zero rows where the map holds token -1. bf16 rows, fp32 weights."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and rowmap.dtype == torch.int32 and rowmap.shape[1] == 4
+    out = torch.empty(n_rows, x.shape[1], device=x.device, dtype=torch.bfloat16)
+    lib = _lib()
+    lib.pd_rows_expand.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int,
+                                   C.c_int, C.c_int, C.c_void_p]
+    _check(lib.pd_rows_expand(x.data_ptr(), rowmap.data_ptr(), w.data_ptr() if w is not None else None, out.data_ptr(),
+                              n_rows, x.shape[1], k, rep, int(use_slot), _s()), "rows_expand")
+    return out
+
+
+def rows_combine(padded: Tensor, pos: Tensor, w: Tensor | None, tokens: int, k: int) -> Tensor:
+    """`y[n] = sum_s w[n, s] * padded[pos[n * k + s]]` (fp32 accumulation, bf16 rows)."""
+    assert padded.dtype == torch.bfloat16 and padded.is_contiguous() and pos.dtype == torch.int64
+    assert pos.numel() == tokens * k
+    y = torch.empty(tokens, padded.shape[1], device=padded.device, dtype=torch.bfloat16)
+    lib = _lib()
+    lib.pd_rows_combine.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int,
+                                    C.c_void_p]
+    _check(lib.pd_rows_combine(padded.data_ptr(), pos.data_ptr(), w.data_ptr() if w is not None else None,
+                               y.data_ptr(), tokens, padded.shape[1], k, _s()), "rows_combine")
+    return y
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, w: Tensor | None, eps: float) -> Tensor:  # type: ignore[override]

@@ -91,13 +91,76 @@ class JobLayout:
             cache[key] = rm
         return cache[key]
 
+    def expand_tokens(self, x: Tensor, k: int) -> Tensor:
+        """`x [N, d]` -> padded sorted job rows `[n_rows, d]`, token `n` feeding its `k` jobs."""
+        if _fast_rows(x):
+            return _TokensToRows.apply(x, self, k)
+        return self.scatter_rows(repeat_rows(x, k))
+
+    def combine(self, padded: Tensor, route_w: Tensor) -> Tensor:
+        """`y[n] = sum_s route_w[n, s] * padded[row of job (n, s)]`: job rows back to tokens with the
+        routing weights applied. `route_w [N, k]`."""
+        N, k = route_w.shape
+        if _fast_rows(padded):
+            return _RowsToTokens.apply(padded, route_w.float().contiguous(), self)
+        y = self.gather_rows(padded).reshape(N, k, -1)
+        return (y * route_w.reshape(N, k, 1).to(y.dtype)).sum(1)
+
     def scatter_rows(self, x_jobs: Tensor) -> Tensor:
         """Job order -> padded sorted rows (zeros in the padding)."""
-        return _ScatterRows.apply(x_jobs, self.pos, self.n_rows)
+        return _ScatterRows.apply(x_jobs, self.pos, self.n_rows, self)
 
     def gather_rows(self, padded: Tensor) -> Tensor:
         """Padded sorted rows -> job order."""
-        return _GatherRows.apply(padded, self.pos, self.n_rows)
+        return _GatherRows.apply(padded, self.pos, self.n_rows, self)
+
+
+def _fast_rows(t: Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape[1] % 8 == 0
+
+
+class _TokensToRows(torch.autograd.Function):
+    """One pass each way: rows are copied in 16-byte pieces through the row map (forward) and summed
+    over a token's `k` jobs through its inverse (backward); nothing is cleared or accumulated."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, layout: "JobLayout", k: int) -> Tensor:  # type: ignore[override]
+        ctx.layout, ctx.k, ctx.n = layout, k, x.shape[0]
+        return ew.rows_expand(x.contiguous(), layout.rowmap(k, 1), None, layout.n_rows, k, rep=1, use_slot=False)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        return ew.rows_combine(g.contiguous(), ctx.layout.pos, None, ctx.n, ctx.k), None, None
+
+
+class _RowsToTokens(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, padded: Tensor, route_w: Tensor, layout: "JobLayout") -> Tensor:  # type: ignore[override]
+        ctx.layout = layout
+        padded = padded.contiguous()
+        ctx.save_for_backward(route_w, padded if ctx.needs_input_grad[1] else None)
+        N, k = route_w.shape
+        return ew.rows_combine(padded, layout.pos, route_w, N, k)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        route_w, padded = ctx.saved_tensors
+        layout, (N, k) = ctx.layout, route_w.shape
+        g = g.contiguous()
+        d_padded = ew.rows_expand(g, layout.rowmap(k, 1), route_w, layout.n_rows, k, rep=1, use_slot=False)
+        d_w = None
+        if padded is not None:  # routing weights recomputed from the live activations
+            d_w = (padded.index_select(0, layout.pos).reshape(N, k, -1).float() * g.float()[:, None, :]).sum(-1)
+        return d_padded, d_w, None
+
+
+def _place_rows(x_jobs: Tensor, pos: Tensor, n_rows: int, layout: "JobLayout") -> Tensor:
+    """Job-order rows to their padded positions, zeros elsewhere."""
+    if _fast_rows(x_jobs):
+        return ew.rows_expand(x_jobs.contiguous(), layout.rowmap(1, 1), None, n_rows, 1, rep=1, use_slot=False)
+    out = x_jobs.new_zeros(n_rows, x_jobs.shape[-1])
+    out.index_copy_(0, pos, x_jobs)
+    return out
 
 
 class _ScatterRows(torch.autograd.Function):
@@ -105,28 +168,24 @@ class _ScatterRows(torch.autograd.Function):
     indexing backward would sort the indices to accumulate duplicates that cannot occur)."""
 
     @staticmethod
-    def forward(ctx, x_jobs: Tensor, pos: Tensor, n_rows: int) -> Tensor:  # type: ignore[override]
+    def forward(ctx, x_jobs: Tensor, pos: Tensor, n_rows: int, layout: "JobLayout") -> Tensor:  # type: ignore[override]
         ctx.pos = pos
-        out = x_jobs.new_zeros(n_rows, x_jobs.shape[-1])
-        out.index_copy_(0, pos, x_jobs)
-        return out
+        return _place_rows(x_jobs, pos, n_rows, layout)
 
     @staticmethod
     def backward(ctx, g: Tensor):  # type: ignore[override]
-        return g.index_select(0, ctx.pos), None, None
+        return g.index_select(0, ctx.pos), None, None, None
 
 
 class _GatherRows(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, padded: Tensor, pos: Tensor, n_rows: int) -> Tensor:  # type: ignore[override]
-        ctx.pos, ctx.n_rows = pos, n_rows
+    def forward(ctx, padded: Tensor, pos: Tensor, n_rows: int, layout: "JobLayout") -> Tensor:  # type: ignore[override]
+        ctx.pos, ctx.n_rows, ctx.layout = pos, n_rows, layout
         return padded.index_select(0, pos)
 
     @staticmethod
     def backward(ctx, g: Tensor):  # type: ignore[override]
-        out = g.new_zeros(ctx.n_rows, g.shape[-1])
-        out.index_copy_(0, ctx.pos, g)
-        return out, None, None
+        return _place_rows(g, ctx.pos, ctx.n_rows, ctx.layout), None, None, None
 
 
 def repeat_rows(x: Tensor, k: int) -> Tensor:

@@ -226,6 +226,23 @@ def test_squash_activity_selected_matches_eager(nv):
     assert torch.equal(y.detach(), (x.detach() * 2.0).repeat_interleave(k, 0))
     assert rel(x.grad, 2.0 * gy.reshape(N, k, -1).sum(1)) < 1e-6
 
+    # the row kernels: token fan-out and routing-weighted combine against the indexing forms
+    xb = torch.randn(N, 72, device="cuda").to(bf).requires_grad_(True)
+    rw = torch.rand(N, k, device="cuda", requires_grad=True)
+    scale = torch.randn(layout.n_rows, 1, device="cuda").to(bf)
+    out = layout.combine(layout.expand_tokens(xb, k) * scale, rw)
+    go = torch.randn_like(out)
+    (out.float() * go.float()).sum().backward()
+    x2, w2 = xb.detach().float().requires_grad_(True), rw.detach().clone().requires_grad_(True)
+    rows = torch.zeros(layout.n_rows, 72, device="cuda").index_copy(0, layout.pos, x2.repeat_interleave(k, 0))
+    ref = ((rows * scale.float())[layout.pos].reshape(N, k, -1) * w2[..., None]).sum(1)
+    (ref * go.float()).sum().backward()
+    _done(nv)
+    assert rel(out, ref) < 5e-3 and rel(xb.grad, x2.grad) < 1e-2 and rel(rw.grad, w2.grad) < 1e-2
+    jobs = torch.randn(N * k, 40, device="cuda").to(bf)
+    assert torch.equal(layout.scatter_rows(jobs)[layout.pos], jobs)
+    assert float(layout.scatter_rows(jobs).float().abs().sum()) == pytest.approx(float(jobs.float().abs().sum()), rel=1e-5)
+
 
 def test_vocab_kl_matches_eager(nv):
     from param_decomp_b200.core.losses import kl_from_logits
