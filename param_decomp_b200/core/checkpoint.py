@@ -57,13 +57,20 @@ def _storable(t: Tensor) -> Tensor:
     return t.view(torch.int16) if t.dtype == torch.uint16 else t
 
 
-def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module) -> tuple[dict[str, Tensor], dict[str, str]]:
+def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module,
+                          expert_shard=None) -> tuple[dict[str, Tensor], dict[str, str]]:
+    """`expert_shard` (`parallel.expert_shard.ExpertSharding`): blocked groups hold this rank's experts
+    only; they are gathered over the expert group (a collective every rank of it must enter) so the
+    file always has the global `[sites, E, ...]` stacks."""
     out: dict[str, Tensor] = {}
     for gname, members in components.groups.items():
         key = components.param_key(gname)
         n = len(members)
-        out[f"components/{gname}/V"] = _storable(components.V[key][:n])
-        out[f"components/{gname}/U"] = _storable(components.U[key][:n])
+        V, U = components.V[key][:n].detach(), components.U[key][:n].detach()
+        if expert_shard is not None and key in expert_shard.blocked_keys:
+            V, U = expert_shard.gather(V), expert_shard.gather(U)
+        out[f"components/{gname}/V"] = _storable(V)
+        out[f"components/{gname}/U"] = _storable(U)
     for name, p in ci_fn.state_dict().items():
         out[f"ci_fn/{name}"] = _storable(p)
     meta = {
@@ -73,11 +80,13 @@ def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module) -> tupl
     return out, meta
 
 
-def training_tensors(state) -> tuple[dict[str, Tensor], dict[str, str]]:
+def training_tensors(state, expert_shard=None) -> tuple[dict[str, Tensor], dict[str, str]]:
     out: dict[str, Tensor] = {"step": torch.tensor(state.step, dtype=torch.int64)}
     uint16_keys = []
     for group, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
-        for k, v in opt.state_dict().items():
+        for k, v in sorted(opt.state_dict().items()):  # sorted: the gathers below must line up across ranks
+            if expert_shard is not None and group == "components" and v.dim() >= 2 and expert_shard.is_split(k):
+                v = expert_shard.gather(v)
             out[f"opt/{group}/{k}"] = _storable(v)
     for term, adv in state.adversaries.items():
         for k, v in adv.state_dict().items():
@@ -92,16 +101,29 @@ def training_tensors(state) -> tuple[dict[str, Tensor], dict[str, str]]:
     return out, meta
 
 
-def save_state(run_dir: Path, state, retention_keep_last: int | None = None) -> Path:
-    """Synchronous save of both items at `state.step`, then prune per the retention policy."""
+def save_state(run_dir: Path, state, retention_keep_last: int | None = None, expert_shard=None,
+               write: bool = True) -> Path:
+    """Synchronous save of both items at `state.step`, then prune per the retention policy. With
+    `expert_shard` every rank of the expert group calls this (the tensors are gathered collectively)
+    and only the one with `write=True` touches the file system."""
     step_dir = ckpt_root(run_dir) / str(state.step)
+    if expert_shard is not None:
+        d, dm = decomposition_tensors(state.components, state.ci_fn, expert_shard)
+        t, tm = training_tensors(state, expert_shard)
+        if not write:
+            return step_dir
+        return _write_step(run_dir, step_dir, d, dm, t, tm, retention_keep_last)
+    d, dm = decomposition_tensors(state.components, state.ci_fn)
+    t, tm = training_tensors(state)
+    return _write_step(run_dir, step_dir, d, dm, t, tm, retention_keep_last)
+
+
+def _write_step(run_dir: Path, step_dir: Path, d, dm, t, tm, retention_keep_last: int | None) -> Path:
     tmp = step_dir.with_name(step_dir.name + ".tmp")
     if tmp.exists():
         shutil.rmtree(tmp)
     tmp.mkdir(parents=True)
-    d, dm = decomposition_tensors(state.components, state.ci_fn)
     save_file(d, str(tmp / DECOMPOSITION_FILE), metadata=dm)
-    t, tm = training_tensors(state)
     save_file(t, str(tmp / TRAINING_FILE), metadata=tm)
     if step_dir.exists():
         shutil.rmtree(step_dir)
@@ -121,13 +143,16 @@ def _read(path: Path) -> tuple[dict[str, Tensor], dict[str, str]]:
     return tensors, meta
 
 
-def restore_components(run_dir: Path, step: int, components: ComponentStacks) -> None:
-    """V/U only (analysis-time partial restore). Pads of the destination are re-derived (zero)."""
+def restore_components(run_dir: Path, step: int, components: ComponentStacks, expert_shard=None) -> None:
+    """V/U only (analysis-time partial restore). Pads of the destination are re-derived (zero). With
+    `expert_shard` the file's global blocked stacks are cut to this rank's experts."""
     tensors, _ = _read(ckpt_root(run_dir) / str(step) / DECOMPOSITION_FILE)
     with torch.no_grad():
         for gname, members in components.groups.items():
             key, n = components.param_key(gname), len(members)
             V, U = tensors[f"components/{gname}/V"], tensors[f"components/{gname}/U"]
+            if expert_shard is not None and key in expert_shard.blocked_keys:
+                V, U = expert_shard.local_slice(V), expert_shard.local_slice(U)
             assert V.shape[0] == n, f"group {gname}: checkpoint has {V.shape[0]} sites, run has {n}"
             components.V[key].zero_()
             components.U[key].zero_()
@@ -135,8 +160,9 @@ def restore_components(run_dir: Path, step: int, components: ComponentStacks) ->
             components.U[key][:n].copy_(U)
 
 
-def restore_decomposition(run_dir: Path, step: int, components: ComponentStacks, ci_fn: nn.Module) -> None:
-    restore_components(run_dir, step, components)
+def restore_decomposition(run_dir: Path, step: int, components: ComponentStacks, ci_fn: nn.Module,
+                          expert_shard=None) -> None:
+    restore_components(run_dir, step, components, expert_shard)
     tensors, _ = _read(ckpt_root(run_dir) / str(step) / DECOMPOSITION_FILE)
     sd = {k[len("ci_fn/"):]: v for k, v in tensors.items() if k.startswith("ci_fn/")}
     ci_fn.load_state_dict(sd)
@@ -144,13 +170,17 @@ def restore_decomposition(run_dir: Path, step: int, components: ComponentStacks,
 
 def restore_state(run_dir: Path, step: int, state) -> None:
     """Full resume: decomposition + optimizer states + adversaries + frequency EMA + step."""
-    restore_decomposition(run_dir, step, state.components, state.ci_fn)
+    expert_shard = getattr(state, "expert_shard", None)
+    restore_decomposition(run_dir, step, state.components, state.ci_fn, expert_shard)
     tensors, meta = _read(ckpt_root(run_dir) / str(step) / TRAINING_FILE)
     uint16_keys = set(json.loads(meta.get("uint16_keys", "[]")))
     dev = next(state.components.parameters()).device
 
     def get(k: str) -> Tensor:
         v = tensors[k]
+        if (expert_shard is not None and k.startswith("opt/components/") and v.dim() >= 2
+                and expert_shard.is_split(k[len("opt/components/"):])):
+            v = expert_shard.local_slice(v)
         return (v.view(torch.uint16) if k in uint16_keys else v).to(dev)
 
     state.step = int(tensors["step"].item())

@@ -25,9 +25,14 @@ from param_decomp_b200.core.ci_fn.transformer import (
 )
 
 
+def _sites(model):
+    """Site specs with GLOBAL block counts (a model split by expert parallelism lists only its own blocks in `sites`)."""
+    return getattr(model, "global_sites", model.sites)
+
+
 def _site_layers(model: Any) -> dict[int, list]:
     by_layer: dict[int, list] = {}
-    for s in model.sites:
+    for s in _sites(model):
         by_layer.setdefault(model.layer_of_site(s.name), []).append(s)
     return dict(sorted(by_layer.items()))
 
@@ -63,18 +68,18 @@ def _attention(cfg: Any) -> dict:
 def build_lm_ci_fn(cfg: Any, model: Any, g: torch.Generator) -> nn.Module:
     by_layer = _site_layers(model)
     layers = list(by_layer)
-    site_taps = {s.name: model.tap_for_site(s.name) for s in model.sites}
+    site_taps = {s.name: model.tap_for_site(s.name) for s in _sites(model)}
     if isinstance(cfg, X.LMGlobalMlpCIFnConfig):
         widths = tap_widths_for(model, layers, cfg.input_tap)
-        return GlobalMLPCIFn(tuple(widths.items()), {s.name: s.C for s in model.sites}, tuple(cfg.hidden_dims), g)
+        return GlobalMLPCIFn(tuple(widths.items()), {s.name: s.C for s in _sites(model)}, tuple(cfg.hidden_dims), g)
     if isinstance(cfg, X.GlobalTransformerCIFnConfig):
         widths = tap_widths_for(model, layers, cfg.input_tap)
         cond = None
         if cfg.component_conditioning is not None:
             cond = {"output_scale_init": cfg.component_conditioning.output_scale_init}
-            for s in model.sites:  # conditioning also reads each site's own input
+            for s in _sites(model):  # conditioning also reads each site's own input
                 widths.setdefault(site_taps[s.name], s.d_in)
-        return GlobalTransformerCIFn(widths, {s.name: s.C for s in model.sites}, site_taps, cfg.d_model, cfg.n_blocks,
+        return GlobalTransformerCIFn(widths, {s.name: s.C for s in _sites(model)}, site_taps, cfg.d_model, cfg.n_blocks,
                                      _attention(cfg.attention), {"kind": cfg.ffn.kind, "hidden": cfg.ffn.hidden},
                                      final_norm=cfg.final_norm == X.FinalNormalization.RMS,
                                      learned_norm_scale=cfg.learned_norm_scale, conditioning=cond, g=g)

@@ -134,6 +134,13 @@ def faithfulness_loss(stacks: ComponentStacks, target_weights: dict[str, Tensor]
     return torch.stack(terms).mean()
 
 
+def faithfulness_terms(stacks: ComponentStacks, target_weights: dict[str, Tensor],
+                       weight_sq_norms: dict[str, Tensor]) -> Tensor:
+    """`[n_sites]`: `||Delta_s||_F^2 / ||W_s||_F^2` per site, in `stacks.sites` order."""
+    return torch.stack([weight_delta(target_weights[s.name], *stacks.site(s.name)).pow(2).sum() / weight_sq_norms[s.name]
+                        for s in stacks.sites])
+
+
 # ---- nonlinearity locality -----------------------------------------------------------------------
 
 

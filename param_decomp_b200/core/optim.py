@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
+from typing import Any
 
 import torch
 from torch import Tensor
@@ -105,6 +106,7 @@ class GroupOptimizer:
     applied_learning_rate: float = 0.0
     last_grad_norm: float = 0.0
     use_fused: bool = False
+    norm_fn: Any = None  # (names, grads) -> global L2 norm, for leaves that are split over a process group
 
     def lr_at(self, step: int) -> float:
         return get_scheduled_value(min(step, self.total_steps), self.total_steps, self.cfg.lr_schedule)
@@ -119,7 +121,10 @@ class GroupOptimizer:
         if grads is None:
             grads = [p.grad for p in self.params]
         live = [(n, p, g) for n, p, g in zip(self.names, self.params, grads) if g is not None]
-        if self.use_fused and live and live[0][1].is_cuda:
+        if self.norm_fn is not None and live:
+            norm = self.norm_fn([n for n, _, _ in live], [g for _, _, g in live])
+            scale = clip_scale(norm, self.cfg.grad_clip_norm)
+        elif self.use_fused and live and live[0][1].is_cuda:
             from param_decomp_b200.ops import optim as fused
 
             norm, scale = fused.grad_norm_and_scale([g for _, _, g in live], self.cfg.grad_clip_norm)

@@ -87,12 +87,17 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
                      objective: PDObjective, device: torch.device | str, batch_rows: int,
                      positions: int | None, stack_multiple: int = 1, use_fused_optim: bool = False,
                      init_components: Callable[[ComponentStacks], None] | None = None,
-                     shard_group: Any = None, shard_backend: str | None = None) -> TrainState:
+                     shard_group: Any = None, shard_backend: str | None = None,
+                     expert_shard: Any = None) -> TrainState:
     """Seeded init: `init` / `source` / `run` streams are separated like the reference's
     `split(PRNGKey(seed), 3)`."""
     g = torch.Generator().manual_seed(pd.seed)
     components = ComponentStacks(model.sites, stack_multiple)
-    components.init_random(g)
+    if expert_shard is not None:
+        assert shard_backend is None, "expert-split component stacks use the replicated-optimizer layout"
+        expert_shard.init_components(components, g)  # the single-process draw, this rank's expert blocks kept
+    else:
+        components.init_random(g)
     if init_components is not None:
         init_components(components)
     components.to(device)
@@ -109,19 +114,22 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
                                     keep_lo=True)
     else:
         comp_opt = build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim)
+    if expert_shard is not None:
+        comp_opt.norm_fn = expert_shard.grad_norm
     state = TrainState(
         components=components,
         ci_fn=ci_fn,
         components_opt=comp_opt,
         ci_fn_opt=build_group_optimizer(pd.ci_fn_optimizer, ci_named, pd.steps, 2, use_fused_optim),
     )
+    state.expert_shard = expert_shard  # type: ignore[attr-defined]
     src_key = StepKey(pd.seed ^ 0x5EED, 0)
     for term in objective.persistent_terms():
         cfg = term.cfg
         pool = cfg.pool.size_per_batch_element if hasattr(cfg, "pool") else 1  # type: ignore[attr-defined]
         shape = getattr(cfg, "source_shape", "bc")
         state.adversaries[term.name] = PersistentAdversary.init(
-            model.sites, cfg.optimizer, cfg.source_dtype, shape, batch_rows, positions, src_key,  # type: ignore[attr-defined]
+            getattr(model, "global_sites", model.sites), cfg.optimizer, cfg.source_dtype, shape, batch_rows, positions, src_key,  # type: ignore[attr-defined]
             pool_size=pool, device=device)
     return state
 
@@ -150,7 +158,8 @@ def _resolve_start(run_dir: Path | None, state: TrainState, cadence: Cadence,
                 log.info("resumed from %s/ckpts/%d", run_dir, own)
                 return "resume"
     if provenance is not None:
-        ckpt.restore_decomposition(provenance.parent_run_dir, provenance.parent_step, state.components, state.ci_fn)
+        ckpt.restore_decomposition(provenance.parent_run_dir, provenance.parent_step, state.components, state.ci_fn,
+                                   getattr(state, "expert_shard", None))
         log.info("fine-tune: loaded V/U + CI fn from %s step %d", provenance.parent_run_dir, provenance.parent_step)
         return "finetune"
     return "fresh"
@@ -189,11 +198,17 @@ def run_decomposition_training(
     collectives = collectives or DataCollectives()
     log = get_logger(collectives.rank)
     objective = build_objective(pd)
-    ctx = StepContext.build(model, objective, pd, collectives=collectives, lazy_masks=lazy_masks, nontarget=nontarget)
+    expert_shard = None
+    if getattr(model, "ep", None) is not None:
+        from param_decomp_b200.parallel.expert_shard import ExpertSharding
+
+        expert_shard = ExpertSharding.for_model(model)
+    ctx = StepContext.build(model, objective, pd, collectives=collectives, lazy_masks=lazy_masks, nontarget=nontarget,
+                            expert_shard=expert_shard)
     rows = batch_rows if batch_rows is not None else pd.batch_size // collectives.world_size
     state = init_train_state(model, ci_fn, pd, objective, device, rows, positions,
                              use_fused_optim=use_fused_optim, init_components=init_components,
-                             shard_group=shard_group, shard_backend=shard_backend)
+                             shard_group=shard_group, shard_backend=shard_backend, expert_shard=expert_shard)
     if state_out is not None:
         state_out.append(state)
     start_kind = _resolve_start(run_dir, state, cadence, resume_provenance, log)
@@ -218,7 +233,11 @@ def run_decomposition_training(
         keep = cadence.checkpointing.retention.n  # type: ignore[union-attr]
 
     def save() -> None:
-        if saving and collectives.rank == 0:
+        if saving and expert_shard is not None:
+            # the ranks of one expert group (the first data shard's) assemble the global stacks; rank 0 writes
+            if getattr(collectives, "data_rank", 0) == 0:
+                ckpt.save_state(run_dir, state, keep, expert_shard=expert_shard, write=collectives.rank == 0)  # type: ignore[arg-type]
+        elif saving and collectives.rank == 0:
             ckpt.save_state(run_dir, state, keep)  # type: ignore[arg-type]
         barrier = getattr(collectives, "barrier", None)
         if barrier is not None:

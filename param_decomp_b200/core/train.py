@@ -64,6 +64,10 @@ class DataCollectives:
     def sum_(self, t: Tensor) -> Tensor:
         return t
 
+    def reduce_grads_everywhere(self, params: list[Tensor]) -> None:
+        """Average `.grad` over EVERY rank of the job (leaves replicated over the non-batch axes too)."""
+        self.reduce_grads(params)
+
 
 @dataclass
 class TrainState:
@@ -90,6 +94,7 @@ class StepContext:
     lazy_masks: bool = False  # fused backend draws stochastic masks in-kernel
     nontarget: NontargetObjective | None = None
     relative_faithfulness: bool = True
+    expert_shard: Any = None  # parallel.expert_shard.ExpertSharding when expert blocks are split over ranks
 
     def weights_sq_host(self) -> dict[str, float]:
         """`||W_s||^2` as host floats (read back once, then cached)."""
@@ -101,8 +106,13 @@ class StepContext:
 
     @classmethod
     def build(cls, model: DecomposedModel, objective: PDObjective, pd, **kw: Any) -> "StepContext":
-        return cls(model=model, objective=objective, pd=pd, weights_W=target_weights(model),
-                   weights_sq=target_weight_sq_norms(model),
+        wsq = target_weight_sq_norms(model)
+        shard = kw.get("expert_shard")
+        if shard is not None:  # a split expert bank is normalised by the norm of the WHOLE bank
+            for s in model.sites:
+                if s.blocked:
+                    wsq[s.name] = shard.sum_over_group(wsq[s.name].clone())
+        return cls(model=model, objective=objective, pd=pd, weights_W=target_weights(model), weights_sq=wsq,
                    site_index={s.name: i for i, s in enumerate(model.sites)}, **kw)
 
 
@@ -362,7 +372,19 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         c_f = scheduled_or_constant(obj.faith.coeff, step, total)
         from param_decomp_b200.ops import faithfulness as fused_faith
 
-        if direct and ctx.relative_faithfulness and fused_faith.blocked_supported(state.components):
+        shard = ctx.expert_shard
+        if shard is not None:
+            # each rank holds some experts' blocks: its loss (and gradients) cover those, the logged value is
+            # the sum over the expert group of the split sites' terms plus the replicated sites' terms
+            assert ctx.relative_faithfulness, "expert-split runs use the target-relative faithfulness"
+            terms = loss_fns.faithfulness_terms(state.components, ctx.weights_W, ctx.weights_sq)
+            split = torch.tensor([s.blocked for s in state.components.sites], device=terms.device)
+            faith = terms.mean()
+            whole = (terms.detach() * ~split).sum() + shard.sum_over_group((terms.detach() * split).sum())
+            metrics["loss/" + obj.faith.instance_key] = whole / len(state.components.sites)
+            unseen = c_f * (whole / len(state.components.sites) - faith.detach())  # other ranks' experts
+            add(c_f * faith)
+        elif direct and ctx.relative_faithfulness and fused_faith.blocked_supported(state.components):
             fused_faithfulness = fused_faith.fused_faithfulness
 
             hi_lo = None
@@ -377,8 +399,9 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         else:
             faith = loss_fns.faithfulness_loss(state.components, ctx.weights_W, ctx.weights_sq,
                                                relative=ctx.relative_faithfulness)
-        metrics["loss/" + obj.faith.instance_key] = faith.detach()
-        add(c_f * faith)
+        if shard is None:
+            metrics["loss/" + obj.faith.instance_key] = faith.detach()
+            add(c_f * faith)
     add(evaluate_minimality(ctx, state, ci, step, metrics))
     if obj.nonlinearity is not None:
         nl = obj.nonlinearity
@@ -418,7 +441,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         add(_nontarget_pass(ctx, state, weights, nontarget_batch, key, step, metrics))
 
     assert total_loss is not None
-    metrics["loss/total"] = total_loss.detach()
+    metrics["loss/total"] = total_loss.detach() + (unseen if ctx.expert_shard is not None and obj.faith is not None else 0)
 
     # source gradients first (they need the graph), then the parameter backward
     final_grads = []
@@ -428,7 +451,15 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         final_grads.append((term, {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, gs)}))
 
     total_loss.backward()
-    ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params) + state.ci_fn_opt.params)
+    if ctx.expert_shard is not None:
+        assert not sharded, "expert-split component stacks use the replicated-optimizer layout"
+        opt = state.components_opt
+        split = [p for n, p in zip(opt.names, opt.params) if ctx.expert_shard.is_split(n)]
+        whole = [p for n, p in zip(opt.names, opt.params) if not ctx.expert_shard.is_split(n)]
+        ctx.collectives.reduce_grads(split)
+        ctx.collectives.reduce_grads_everywhere(whole + state.ci_fn_opt.params)
+    else:
+        ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params) + state.ci_fn_opt.params)
 
     info_c = state.components_opt.step(step)
     info_f = state.ci_fn_opt.step(step)

@@ -30,6 +30,7 @@ class LMRun:
     arch: X.TransformerArchConfig
     tokens_per_step: int
     init_components: Callable | None = None
+    ep: Any = None  # parallel.ep.ExpertParallel when the experts are split over the mesh's tp axis
 
 
 def _dtype(name: str) -> torch.dtype:
@@ -70,7 +71,7 @@ def load_target_weights(cfg: X.LMTargetConfig, data_root: Path | None, device) -
 
 def build_ci_fn(cfg: Any, model: Any, seed: int) -> nn.Module:
     g = torch.Generator().manual_seed(seed + 1)
-    sites: tuple[SiteSpec, ...] = model.sites
+    sites: tuple[SiteSpec, ...] = getattr(model, "global_sites", model.sites)
     if isinstance(cfg, X.LMLayerwiseMlpCIFnConfig):
         blocked = {s.name: (model.layer_of_site(s.name), s.n_blocks, s.C_block) for s in sites if s.blocked}
         shapes = {s.name: (model.arch.d_model if s.blocked else s.d_in, s.C) for s in sites}
@@ -82,8 +83,16 @@ def build_ci_fn(cfg: Any, model: Any, seed: int) -> nn.Module:
 
 
 def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_root: Path | None,
-                 device: torch.device | str, rank: int = 0, world: int = 1) -> LMRun:
+                 device: torch.device | str, rank: int = 0, world: int = 1, expert_group: Any = None) -> LMRun:
+    """`rank`/`world` index the batch axes (data shards). `expert_group`: the process group of the mesh's
+    `tp` axis; on a mixture-of-experts target its ranks split the experts (and their component blocks)
+    and see the same tokens (param_decomp/routed/experts.py:28-40)."""
     arch, weights = load_target_weights(cfg.target, data_root, device)
+    ep = None
+    if expert_group is not None and arch.family in ("moe", "qwen35_moe"):
+        from param_decomp_b200.parallel.ep import ExpertParallel
+
+        ep = ExpertParallel(expert_group, arch.n_experts, mode="allreduce")
     sites_cfg = cfg.decomposition.sites
     edge = cfg.target.output_edge
     n_chunks = edge.n_vocab_chunks if isinstance(edge, X.StreamedOutputEdgeConfig) else None
@@ -91,11 +100,11 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
     if arch.family == "qwen35_moe":
         from param_decomp_b200.models import qwen35
 
-        model = qwen35.build_qwen35_model(arch, weights, sites_cfg, cfg.target, backend)
+        model = qwen35.build_qwen35_model(arch, weights, sites_cfg, cfg.target, backend, ep=ep)
     elif arch.family == "moe" or isinstance(sites_cfg, (X.MoeCSpec, X.Qwen36MoeCSpec)):
         from param_decomp_b200.models import moe
 
-        model = moe.build_moe_model(arch, weights, sites_cfg, cfg.target, backend, rank, world)
+        model = moe.build_moe_model(arch, weights, sites_cfg, cfg.target, backend, rank, world, ep=ep)
     else:
         site_cs = resolve_site_cs(sites_cfg, arch)
         model = tf.TransformerDecomposedModel(arch, weights, site_cs, backend=backend,
@@ -134,4 +143,4 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
         from param_decomp_b200.core.init_aligned import nonlinearity_aligned_init
 
         init = lambda comps: nonlinearity_aligned_init(comps, model, cfg.pd.seed)  # noqa: E731
-    return LMRun(model, ci_fn, sample_train, sample_eval, arch, gb * seq, init)
+    return LMRun(model, ci_fn, sample_train, sample_eval, arch, gb * seq, init, ep)

@@ -30,15 +30,23 @@ def optimizer_sharding(cfg: LMExperimentConfig | LMTargetedExperimentConfig, top
     return topo.data_group, backend
 
 
+def expert_group_of(topo):
+    """The mesh's `tp` axis is the expert-shard axis of a mixture-of-experts target
+    (param_decomp/core/placement.py:1040-1048: blocked sites place `expert -> tp`)."""
+    return topo.groups.get("tp") if topo.tp_world > 1 else None
+
+
 def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None = None, device: str | None = None,
              max_steps_this_entry: int | None = None, state_out: list | None = None) -> RunResult:
     from param_decomp_b200.parallel import topology
 
     topo = topology.initialize(cfg.runtime.mesh, device)
     log = get_logger(topo.rank)
-    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world)
+    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
     collectives = topo.collectives()
     shard_group, shard_backend = optimizer_sharding(cfg, topo)
+    if run.ep is not None:  # expert blocks differ per tp rank: replicated-optimizer layout over the batch axes
+        shard_group, shard_backend = None, None
 
     run_dir, sink = None, None
     if data_root is not None:
@@ -84,7 +92,7 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
 
     topo = topology.initialize(cfg.runtime.mesh, device)
     log = get_logger(topo.rank)
-    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world)
+    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
     pool = PromptPool.build(cfg.prompts, run.arch.vocab_size, data_root, cfg.pd.seed, encode=encode)
     n_target_terms = len(build_objective(cfg.pd).recon)
     nontarget = build_nontarget_objective(cfg.nontarget, first_index=n_target_terms)

@@ -111,6 +111,17 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
     def expert_site_names(self, layer: int) -> list[str]:
         return [tf.site_name("moe", layer, k) for k in EXPERT_KINDS]
 
+    @property
+    def global_sites(self) -> tuple[SiteSpec, ...]:
+        """The sites as the CI function, masks and adversaries see them. Under expert parallelism
+        `sites` describes this rank's component blocks (its own experts, dummies included) while the
+        importances of a token cover whichever of ALL experts it selected."""
+        if self.ep is None:
+            return self.sites
+        E = self.ep.n_experts
+        return tuple(s if not s.blocked else SiteSpec(s.name, s.d_in, s.d_out, s.C_block * E, group=s.group, n_blocks=E,
+                                                      alignment=s.alignment) for s in self.sites)
+
     # -- expert bank --------------------------------------------------------------------------------
     def _expert_site(self, name: str, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int],
                      weights: ComputeWeights | None, masks: Masks | None, token_of_job: Tensor,

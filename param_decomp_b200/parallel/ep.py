@@ -77,6 +77,37 @@ class _AllToAll(torch.autograd.Function):
         return out, None, None, None
 
 
+class _CopyToGroup(torch.autograd.Function):
+    """Identity whose adjoint sums over the group: for a replicated tensor that every rank feeds to
+    its own (different) experts, so the partial gradients add up to the full one on every rank."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromGroup(torch.autograd.Function):
+    """Sum over the group whose adjoint is the identity: the summed output feeds a computation that is
+    replicated on every rank, so each rank's partial receives the (identical) full gradient."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        out = x.contiguous().clone()
+        dist.all_reduce(out, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        return g, None
+
+
 class P2PRows:
     """Symmetric receive buffers + flags of one expert group for `pd_ep_scatter_rows`.
 
@@ -302,29 +333,38 @@ class ExpertParallel:
         return model.expert_jobs(layer, x_jobs, e_local, order, bounds, weights, masks, ar, torch.zeros_like(ar))
 
     def _allreduce(self, model, layer, xt, expert_of_job, token_of_job, slot_of_job, weights, masks) -> Tensor:
-        import torch.distributed.nn.functional as dfn
-
+        """Tokens are replicated over the group; this rank runs the jobs of its own experts and the
+        partial outputs are summed. Gradients are exact on every rank: inputs shared by the ranks
+        (activations, mask inputs) pass through `_CopyToGroup`, the sum through `_ReduceFromGroup`, so
+        replicated parameters upstream see the full gradient and local expert blocks see their own."""
         lo = self.rank * self.e_loc
         mine = (expert_of_job >= lo) & (expert_of_job < lo + self.e_loc)
         idx = mine.nonzero()[:, 0]
+        share = lambda t: _CopyToGroup.apply(t, self.group) if t.requires_grad else t  # noqa: E731
+        xt = share(xt)
         y = xt.new_zeros(expert_of_job.numel(), xt.shape[-1])
+        keep_alive = xt.sum() * 0  # every rank must reach the same backward collectives, jobs or not
+        sub_masks = None
+        if masks is not None:
+            sub_masks = {}
+            for name in model.expert_site_names(layer):
+                if name not in masks:
+                    continue
+                sm = masks[name].materialize()
+                c = next(s for s in model.sites if s.name == name).C_block
+                m = d = None
+                if sm.mask is not None:
+                    flat = share(sm.mask.reshape(-1, sm.mask.shape[-1]))
+                    keep_alive = keep_alive + flat.sum() * 0
+                    m = flat.reshape(flat.shape[0], -1, c)[token_of_job[idx], slot_of_job[idx]]
+                if sm.delta is not None:
+                    dl = share(sm.delta.reshape(-1, 1))
+                    keep_alive = keep_alive + dl.sum() * 0
+                    d = dl[token_of_job[idx]]
+                r = None if sm.route is None else sm.route.reshape(-1)[token_of_job[idx]]
+                sub_masks[name] = SiteMask(mask=m, delta=d, route=r)
         if idx.numel():
-            sub_masks = None
-            if masks is not None:
-                sub_masks = {}
-                for name, sm in masks.items():
-                    if name not in model.expert_site_names(layer):
-                        continue
-                    sm = sm.materialize()
-                    c = next(s for s in model.sites if s.name == name).C_block
-                    m = None
-                    if sm.mask is not None:
-                        flat = sm.mask.reshape(-1, sm.mask.shape[-1])
-                        m = flat.reshape(flat.shape[0], -1, c)[token_of_job[idx], slot_of_job[idx]]
-                    d = None if sm.delta is None else sm.delta.reshape(-1, 1)[token_of_job[idx]]
-                    r = None if sm.route is None else sm.route.reshape(-1)[token_of_job[idx]]
-                    sub_masks[name] = SiteMask(mask=m, delta=d, route=r)
             ar = torch.arange(idx.numel(), device=xt.device)
             y_local = self._local(model, layer, xt[token_of_job[idx]], expert_of_job[idx] - lo, weights, sub_masks, ar)
             y = y.index_copy(0, idx, y_local.to(y.dtype))
-        return dfn.all_reduce(y, group=self.group)
+        return _ReduceFromGroup.apply(y + keep_alive.to(y.dtype), self.group)

@@ -78,10 +78,16 @@ class DistCollectives(DataCollectives):
     def row_offset(self, local_rows: int) -> int:
         return self.data_rank * local_rows
 
-    def reduce_grads(self, params: list[Tensor]) -> None:
-        """Average gradients over the data group in few large flat buckets (NVSwitch makes the cost
-        launch-bound, not link-bound, so buckets are sized for latency: 256 MiB)."""
-        if self.world_size == 1:
+    def reduce_grads_everywhere(self, params: list[Tensor]) -> None:
+        self.reduce_grads(params, group=None, world=self.topo.world)
+
+    def reduce_grads(self, params: list[Tensor], group: Any = "data", world: int | None = None) -> None:
+        """Average gradients over the data group (or, `group=None`, the whole job) in few large flat
+        buckets (NVSwitch makes the cost launch-bound, not link-bound, so buckets are sized for
+        latency: 256 MiB)."""
+        group = self.topo.data_group if group == "data" else group
+        world = self.world_size if world is None else world
+        if world == 1:
             return
         grads = [p.grad for p in params if p.grad is not None]
         bucket, size, limit = [], 0, 64 * 1024 * 1024  # elements
@@ -90,8 +96,8 @@ class DistCollectives(DataCollectives):
             if not bucket:
                 return
             flat = torch.cat([g.reshape(-1) for g in bucket]) if len(bucket) > 1 else bucket[0].reshape(-1)
-            dist.all_reduce(flat, group=self.topo.data_group)
-            flat.div_(self.world_size)
+            dist.all_reduce(flat, group=group)
+            flat.div_(world)
             if len(bucket) > 1:
                 off = 0
                 for g in bucket:
@@ -100,8 +106,8 @@ class DistCollectives(DataCollectives):
             bucket, size = [], 0
         for g in grads:
             if g.numel() >= limit:
-                dist.all_reduce(g, group=self.topo.data_group)
-                g.div_(self.world_size)
+                dist.all_reduce(g, group=group)
+                g.div_(world)
                 continue
             bucket.append(g)
             size += g.numel()
