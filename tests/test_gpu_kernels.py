@@ -337,6 +337,47 @@ def test_step_parity_fused_vs_eager(nv):
         assert abs(a - b) <= 2e-2 * abs(a) + 1e-6, (k, a, b)
 
 
+def test_qwen35_hybrid_step_fused_vs_eager(nv):
+    """The hybrid target (gated delta rule + gated attention + routed experts with a shared expert) through
+    three engine steps: the fused backend (delta-rule, conv, flash-attention and grouped kernels) against the
+    eager backend on the same bf16 weights."""
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+    from param_decomp_b200.core.objective import build_objective
+    from param_decomp_b200.core.run import init_train_state
+    from param_decomp_b200.core.train import StepContext, train_step
+    from param_decomp_b200.experiments.lm.build import build_lm_run
+    from param_decomp_b200.models import qwen35
+
+    arch = dict(family="qwen35_moe", n_layer=2, d_model=64, n_head=4, n_kv_head=2, head_dim=64, d_ff=64, vocab_size=512,
+                max_seq_len=64, n_experts=4, experts_per_token=2, full_attention_interval=2, partial_rotary_factor=0.5,
+                linear_num_key_heads=2, linear_key_head_dim=64, linear_num_value_heads=4, linear_value_head_dim=64,
+                linear_conv_kernel_dim=4, shared_expert_intermediate=64)
+    raw = LMExperimentConfig.from_file("param_decomp_b200/experiments/configs/lm_moe4l_e42.yaml").model_dump(mode="json")
+    raw["target"]["spec"]["arch"] = arch
+    raw["decomposition"]["sites"] = {"kind": "qwen36_moe", "layers": {"kind": "all"},
+                                     "cs": {k: (128 if k.startswith("experts_") else 64) for k in qwen35.KIND_ORDER}}
+    raw["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [64]}
+    raw["data"]["seq_len"] = 64
+    raw["pd"]["batch_size"] = 4
+    dev = torch.device("cuda", 0)
+    res = {}
+    for backend in ("eager_torch", "fused_sm100"):
+        raw["runtime"]["backend"] = backend
+        cfg = LMExperimentConfig.model_validate(raw)
+        run = build_lm_run(cfg, None, dev)
+        obj = build_objective(cfg.pd)
+        fused = backend == "fused_sm100"
+        ctx = StepContext.build(run.model, obj, cfg.pd, lazy_masks=fused)
+        st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, dev, cfg.pd.batch_size, cfg.data.seq_len, use_fused_optim=fused)
+        for s in range(3):
+            m = train_step(ctx, st, run.sample_train(s))
+        _done(nv)
+        res[backend] = {k: float(v) for k, v in m.items()}
+    for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss"):
+        a, b = res["eager_torch"][k], res["fused_sm100"][k]
+        assert abs(a - b) <= 5e-2 * abs(a) + 1e-6, (k, a, b)
+
+
 def test_smoke_entry(nv):
     import __graft_entry__ as ge
 

@@ -255,3 +255,56 @@ def test_ep_p2p_matches_collective_two_gpus():
         assert torch.equal(ya, yb)
         for k in ga:
             assert torch.allclose(ga[k], gb[k], atol=1e-6), k
+
+
+def _moe_engine_cfg(tp: int):
+    import copy
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"]["backend"] = "fused_sm100"
+    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
+    c["runtime"]["sharding"] = "ddp"
+    c["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 64, "n_head": 2, "d_ff": 128,
+                                   "vocab_size": 512, "n_experts": 4, "experts_per_token": 2}
+    c["decomposition"]["sites"] = {"kind": "moe", "layers": {"kind": "all"},
+                                   "cs": {"q": 64, "experts_gate": 128, "experts_up": 128, "experts_down": 128}}
+    c["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [64]}
+    c["data"]["seq_len"] = 64
+    c["pd"]["batch_size"] = 4
+    c["pd"]["steps"] = 3
+    c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "none"}}
+    c["eval"] = None
+    return LMExperimentConfig.model_validate(c)
+
+
+def _ep_engine_worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from param_decomp_b200.experiments.lm.training import train_lm
+    from param_decomp_b200.ops import native
+
+    states: list = []
+    res = train_lm(_moe_engine_cfg(world), None, device="cuda", state_out=states)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert states[0].expert_shard is not None
+    out[rank] = dict(res.last_metrics)
+
+
+def test_expert_split_engine_two_gpus():
+    """The engine with the experts split over two GPUs (fused backend, grouped kernels on each rank's own
+    experts) against the same run on one GPU."""
+    _need_two_gpus()
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_ep_engine_worker, args=(world, port, out), nprocs=world, join=True)
+    ref = train_lm(_moe_engine_cfg(1), None, device="cuda").last_metrics
+    for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss"):
+        for r in range(world):
+            got, want = out[r]["train/" + k], ref["train/" + k]
+            assert abs(got - want) <= 3e-2 * abs(want) + 1e-6, (k, r, got, want)
