@@ -1,5 +1,6 @@
-"""Frozen-target weight sources: HuggingFace safetensors snapshots (Llama-3.1, Qwen3) and the
-in-house pretrain cache (LlamaSimpleMLP / LlamaSimple / GPT2Simple checkpoints).
+"""Frozen-target weight sources: HuggingFace safetensors snapshots (Llama-3.1, Qwen3, the Qwen3.5 /
+Qwen3-Next hybrid mixture-of-experts family) and the in-house pretrain cache (LlamaSimpleMLP /
+LlamaSimple / GPT2Simple checkpoints, hybrid mixture-of-experts checkpoints).
 
 All loaders return `(TransformerArchConfig, {internal key: tensor})` with the key grammar of
 `models/transformer.py` (`embed.weight`, `layers.{i}.attn_norm.weight`, site weights named by the
@@ -94,9 +95,13 @@ def remap_hf_llama(raw: dict[str, Tensor], arch: TransformerArchConfig) -> dict[
 
 def load_hf_snapshot(snapshot_dir: Path, dtype: torch.dtype, device) -> tuple[TransformerArchConfig, dict[str, Tensor]]:
     cfg = json.loads((Path(snapshot_dir) / "config.json").read_text())
-    arch = arch_from_hf_config(cfg)
     files = sorted(Path(snapshot_dir).glob("*.safetensors"))
     assert files, f"no safetensors files in {snapshot_dir}"
+    text = cfg.get("text_config", cfg)
+    if "linear_num_value_heads" in text:  # hybrid DeltaNet mixture-of-experts family
+        arch = qwen35_arch_from_hf_config(cfg)
+        return arch, remap_hf_qwen35(read_safetensors(files, dtype, device), arch)
+    arch = arch_from_hf_config(cfg)
     return arch, remap_hf_llama(read_safetensors(files, dtype, device), arch)
 
 
@@ -143,6 +148,119 @@ def save_simple_mlp_cache(entry: Path, arch: TransformerArchConfig, weights: dic
     save_file({k: v.detach().cpu().contiguous() for k, v in raw.items()}, str(entry / f"model_step_{step}.safetensors"))
 
 
+# ---- Qwen3.5-style hybrid (gated DeltaNet + gated attention + routed experts) ------------------------
+
+
+def qwen35_arch_from_hf_config(cfg: dict[str, Any]) -> TransformerArchConfig:
+    """`config.json` of a Qwen3.5 / Qwen3-Next style mixture-of-experts model (the text tower's fields
+    sit under `text_config` in the multimodal layout)."""
+    c = cfg.get("text_config", cfg)
+    rope = c.get("rope_parameters") or c.get("rope_scaling") or {}
+    interval = c.get("full_attention_interval", 4)
+    if c.get("layer_types"):  # the explicit per-layer list wins; it must be the periodic pattern
+        kinds = list(c["layer_types"])
+        interval = kinds.index("full_attention") + 1
+        assert kinds == [("full_attention" if (i + 1) % interval == 0 else "linear_attention") for i in range(len(kinds))], \
+            f"layer_types {kinds} is not one full-attention layer every {interval}"
+    return TransformerArchConfig(
+        family="qwen35_moe", n_layer=c["num_hidden_layers"], d_model=c["hidden_size"], n_head=c["num_attention_heads"],
+        n_kv_head=c.get("num_key_value_heads"), head_dim=c.get("head_dim") or c["hidden_size"] // c["num_attention_heads"],
+        d_ff=c["moe_intermediate_size"], vocab_size=c["vocab_size"], max_seq_len=c.get("max_position_embeddings", 4096),
+        rope_theta=float(rope.get("rope_theta", c.get("rope_theta", 10000.0))), rms_eps=c.get("rms_norm_eps", 1e-6),
+        n_experts=c["num_experts"], experts_per_token=c["num_experts_per_tok"],
+        norm_topk_prob=c.get("norm_topk_prob", True), full_attention_interval=interval,
+        partial_rotary_factor=float(rope.get("partial_rotary_factor", c.get("partial_rotary_factor", 0.25))),
+        linear_num_key_heads=c["linear_num_key_heads"], linear_key_head_dim=c["linear_key_head_dim"],
+        linear_num_value_heads=c["linear_num_value_heads"], linear_value_head_dim=c["linear_value_head_dim"],
+        linear_conv_kernel_dim=c.get("linear_conv_kernel_dim", 4),
+        shared_expert_intermediate=c["shared_expert_intermediate_size"],
+        tie_embeddings=c.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False)))
+
+
+def remap_hf_qwen35(raw: dict[str, Tensor], arch: TransformerArchConfig) -> dict[str, Tensor]:
+    """HF keys -> the key grammar of `models/qwen35.py`.
+
+    Accepts both text-tower prefixes (`model.language_model.` and `model.`), the fused expert banks
+    (`mlp.experts.gate_up_proj [E, 2 ff, d]`, `mlp.experts.down_proj [E, d, ff]`) as well as one matrix
+    per expert (`mlp.experts.{e}.gate_proj.weight`), and the fused DeltaNet input projection
+    (`in_proj_qkv`, rows `[q | k | v]`, the depthwise `conv1d` over the same channel order) next to the
+    Qwen3-Next form (`in_proj_qkvz` / `in_proj_ba`, grouped per key head). The gated-attention query
+    projection keeps its per-head `[q | gate]` row order, which is the order the model reads."""
+    from param_decomp_b200.models import qwen35 as Q
+
+    root = "model.language_model." if any(k.startswith("model.language_model.") for k in raw) else "model."
+    a = arch
+    kd, vd = a.linear_num_key_heads * a.linear_key_head_dim, a.linear_num_value_heads * a.linear_value_head_dim
+    out = {"embed.weight": raw[root + "embed_tokens.weight"], "final_norm.weight": raw[root + "norm.weight"]}
+    out["lm_head.weight"] = raw["lm_head.weight"] if "lm_head.weight" in raw else raw[root + "embed_tokens.weight"]
+    for i in range(a.n_layer):
+        p = f"{root}layers.{i}."
+        out[f"layers.{i}.attn_norm.weight"] = raw[p + "input_layernorm.weight"]
+        out[f"layers.{i}.mlp_norm.weight"] = raw[p + "post_attention_layernorm.weight"]
+        if Q.is_full_attention(a, i):
+            for kind, hf in (("attn_q", "q_proj"), ("attn_k", "k_proj"), ("attn_v", "v_proj"), ("attn_o", "o_proj")):
+                out[Q.site_name(i, kind) + ".weight"] = raw[p + f"self_attn.{hf}.weight"]
+            out[f"layers.{i}.self_attn.q_norm.weight"] = raw[p + "self_attn.q_norm.weight"]
+            out[f"layers.{i}.self_attn.k_norm.weight"] = raw[p + "self_attn.k_norm.weight"]
+        else:
+            la = p + "linear_attn."
+            if la + "in_proj_qkv.weight" in raw:
+                qkv = raw[la + "in_proj_qkv.weight"]
+                q, k, v = qkv[:kd], qkv[kd:2 * kd], qkv[2 * kd:]
+                z, b, al = raw[la + "in_proj_z.weight"], raw[la + "in_proj_b.weight"], raw[la + "in_proj_a.weight"]
+            else:  # Qwen3-Next: rows grouped per key head as [q | k | v-heads | z-heads] and [b-heads | a-heads]
+                Hk, dk, dv = a.linear_num_key_heads, a.linear_key_head_dim, a.linear_value_head_dim
+                rep = a.linear_num_value_heads // Hk
+                g = raw[la + "in_proj_qkvz.weight"].reshape(Hk, 2 * dk + 2 * rep * dv, -1)
+                q, k = g[:, :dk].reshape(kd, -1), g[:, dk:2 * dk].reshape(kd, -1)
+                v, z = g[:, 2 * dk:2 * dk + rep * dv].reshape(vd, -1), g[:, 2 * dk + rep * dv:].reshape(vd, -1)
+                ba = raw[la + "in_proj_ba.weight"].reshape(Hk, 2 * rep, -1)
+                b, al = ba[:, :rep].reshape(Hk * rep, -1), ba[:, rep:].reshape(Hk * rep, -1)
+            for kind, w in (("gdn_q", q), ("gdn_k", k), ("gdn_v", v), ("gdn_z", z), ("gdn_b", b), ("gdn_a", al)):
+                out[Q.site_name(i, kind) + ".weight"] = w.contiguous()
+            out[Q.site_name(i, "gdn_out") + ".weight"] = raw[la + "out_proj.weight"]
+            conv = raw[la + "conv1d.weight"].reshape(2 * kd + vd, -1)  # [channels, 1, K] -> [channels, K]
+            out[f"layers.{i}.linear_attn.conv_q.weight"] = conv[:kd].contiguous()
+            out[f"layers.{i}.linear_attn.conv_k.weight"] = conv[kd:2 * kd].contiguous()
+            out[f"layers.{i}.linear_attn.conv_v.weight"] = conv[2 * kd:].contiguous()
+            for leaf in ("A_log", "dt_bias", "norm.weight"):
+                out[f"layers.{i}.linear_attn.{leaf}"] = raw[la + leaf]
+        m = p + "mlp."
+        out[f"layers.{i}.mlp.router.weight"] = raw[m + "gate.weight"]
+        if m + "experts.gate_up_proj" in raw:
+            gu = raw[m + "experts.gate_up_proj"]
+            gate, up, down = gu[:, :a.d_ff], gu[:, a.d_ff:], raw[m + "experts.down_proj"]
+        else:
+            per = lambda nm: torch.stack([raw[f"{m}experts.{e}.{nm}.weight"] for e in range(a.n_experts)])  # noqa: E731
+            gate, up, down = per("gate_proj"), per("up_proj"), per("down_proj")
+        for kind, w in (("experts_gate", gate), ("experts_up", up), ("experts_down", down)):
+            out[Q.site_name(i, kind) + ".weight"] = w.contiguous()
+        for kind, hf in (("shared_gate", "gate_proj"), ("shared_up", "up_proj"), ("shared_down", "down_proj")):
+            out[Q.site_name(i, kind) + ".weight"] = raw[m + f"shared_expert.{hf}.weight"]
+        out[f"layers.{i}.mlp.shared_expert_gate.weight"] = raw[m + "shared_expert_gate.weight"].reshape(1, -1)
+    return out
+
+
+def load_qwen35_cache(entry: Path, dtype: torch.dtype, device) -> tuple[TransformerArchConfig, dict[str, Tensor]]:
+    """Pretrain-cache entry of a hybrid model: `model_config.yaml` holds either the architecture in this
+    package's field names (`model: {family: qwen35_moe, ...}`) or an HF-style config; the newest
+    `model_step_<N>.safetensors` holds HF-style keys or this package's own keys."""
+    mc = yaml.safe_load((entry / "model_config.yaml").read_text())
+    m = mc.get("model", mc)
+    arch = TransformerArchConfig.model_validate(m) if "family" in m else qwen35_arch_from_hf_config(m)
+    raw = read_safetensors([latest_checkpoint(entry)], dtype, device)
+    return arch, (raw if "embed.weight" in raw else remap_hf_qwen35(raw, arch))
+
+
+def save_qwen35_cache(entry: Path, arch: TransformerArchConfig, weights: dict[str, Tensor], step: int) -> None:
+    """Write a pretrain-cache entry in this package's own key grammar (pretrainer, tests)."""
+    from safetensors.torch import save_file
+
+    entry.mkdir(parents=True, exist_ok=True)
+    (entry / "model_config.yaml").write_text(yaml.dump({"model": arch.model_dump(mode="json")}))
+    save_file({k: v.detach().cpu().contiguous() for k, v in weights.items()}, str(entry / f"model_step_{step}.safetensors"))
+
+
 def load_from_spec(spec: Any, data_root: Path | None, dtype: torch.dtype, device) -> tuple[TransformerArchConfig, dict]:
     if isinstance(spec, PretrainedTarget):
         assert data_root is not None, "pretrained targets resolve under --data-root"
@@ -153,5 +271,6 @@ def load_from_spec(spec: Any, data_root: Path | None, dtype: torch.dtype, device
         assert snap.exists(), f"{snap} missing: HF snapshots must be staged offline under <data_root>/hf_snapshots/"
         return load_hf_snapshot(snap, dtype, device)
     if isinstance(spec, PretrainedQwen35MoeTarget):
-        raise NotImplementedError("the Qwen3.5 hybrid (DeltaNet) checkpoint layout is loaded by models/qwen35.py")
+        assert data_root is not None, "pretrained targets resolve under --data-root"
+        return load_qwen35_cache(pretrain_cache_dir(data_root, spec.run_path), dtype, device)
     raise TypeError(type(spec).__name__)
