@@ -68,7 +68,7 @@ def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module,
         n = len(members)
         V, U = components.V[key][:n].detach(), components.U[key][:n].detach()
         if expert_shard is not None and key in expert_shard.blocked_keys:
-            V, U = expert_shard.gather(V), expert_shard.gather(U)
+            V, U = expert_shard.gather(V, "V"), expert_shard.gather(U, "U")
         out[f"components/{gname}/V"] = _storable(V)
         out[f"components/{gname}/U"] = _storable(U)
     for name, p in ci_fn.state_dict().items():
@@ -86,7 +86,7 @@ def training_tensors(state, expert_shard=None) -> tuple[dict[str, Tensor], dict[
     for group, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
         for k, v in sorted(opt.state_dict().items()):  # sorted: the gathers below must line up across ranks
             if expert_shard is not None and group == "components" and v.dim() >= 2 and expert_shard.is_split(k):
-                v = expert_shard.gather(v)
+                v = expert_shard.gather(v, k)
             out[f"opt/{group}/{k}"] = _storable(v)
     for term, adv in state.adversaries.items():
         for k, v in adv.state_dict().items():
@@ -152,7 +152,7 @@ def restore_components(run_dir: Path, step: int, components: ComponentStacks, ex
             key, n = components.param_key(gname), len(members)
             V, U = tensors[f"components/{gname}/V"], tensors[f"components/{gname}/U"]
             if expert_shard is not None and key in expert_shard.blocked_keys:
-                V, U = expert_shard.local_slice(V), expert_shard.local_slice(U)
+                V, U = expert_shard.local_slice(V, "V"), expert_shard.local_slice(U, "U")
             assert V.shape[0] == n, f"group {gname}: checkpoint has {V.shape[0]} sites, run has {n}"
             components.V[key].zero_()
             components.U[key].zero_()
@@ -180,7 +180,7 @@ def restore_state(run_dir: Path, step: int, state) -> None:
         v = tensors[k]
         if (expert_shard is not None and k.startswith("opt/components/") and v.dim() >= 2
                 and expert_shard.is_split(k[len("opt/components/"):])):
-            v = expert_shard.local_slice(v)
+            v = expert_shard.local_slice(v, k[len("opt/components/"):])
         return (v.view(torch.uint16) if k in uint16_keys else v).to(dev)
 
     state.step = int(tensors["step"].item())

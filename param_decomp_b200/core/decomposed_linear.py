@@ -18,6 +18,39 @@ from torch import Tensor
 from param_decomp_b200.core.masking import SiteMask
 
 
+def site_forward_split(x: Tensor, V: Tensor, U: Tensor, W: Tensor | None, sm: SiteMask, group,
+                       bias: Tensor | None = None) -> Tensor:
+    """The same contract with the component axis split over `group`: `V [d_in, C / W]`, `U [C / W, d_out]`
+    are this rank's columns / rows, `sm` is the whole site's mask (replicated). Each rank contracts over
+    its own components; the partial outputs are summed over the group and the target term, which does not
+    depend on the components, is added once (param_decomp/core/decomposed_linear.py:142-175)."""
+    from param_decomp_b200.parallel.group_ops import ReduceFromGroup, copy_to_group
+
+    sm = sm.column_shard(group).materialize()
+    h = copy_to_group(x, group) @ V.to(x.dtype)
+    coef = sm.mask
+    if sm.delta is not None:
+        d = copy_to_group(sm.delta, group)  # its gradient through the component path is partial per rank
+        coef = (coef - d) if coef is not None else (1.0 - d)
+    if coef is not None:
+        h = h * coef.to(h.dtype)
+    out = ReduceFromGroup.apply(h @ U.to(x.dtype), group)
+    return _target_term(out, x, W, sm, bias)
+
+
+def _target_term(out: Tensor, x: Tensor, W: Tensor | None, sm: SiteMask, bias: Tensor | None) -> Tensor:
+    if sm.delta is not None or sm.route is not None:
+        assert W is not None, "delta masks and partial routing need the frozen weight"
+        xw = F.linear(x, W.to(x.dtype))
+        if sm.delta is not None:
+            out = out + sm.delta.to(out.dtype) * xw
+        if sm.route is not None:
+            out = torch.where(sm.route.unsqueeze(-1), out, xw)
+    if bias is not None:
+        out = out + bias.to(out.dtype)
+    return out
+
+
 def site_forward(x: Tensor, V: Tensor, U: Tensor, W: Tensor | None, sm: SiteMask,
                  bias: Tensor | None = None) -> Tensor:
     """`x [..., d_in]`, `V [d_in, C]`, `U [C, d_out]`, `W [d_out, d_in]` (needed iff delta/route)."""

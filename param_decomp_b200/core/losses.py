@@ -135,10 +135,22 @@ def faithfulness_loss(stacks: ComponentStacks, target_weights: dict[str, Tensor]
 
 
 def faithfulness_terms(stacks: ComponentStacks, target_weights: dict[str, Tensor],
-                       weight_sq_norms: dict[str, Tensor]) -> Tensor:
-    """`[n_sites]`: `||Delta_s||_F^2 / ||W_s||_F^2` per site, in `stacks.sites` order."""
-    return torch.stack([weight_delta(target_weights[s.name], *stacks.site(s.name)).pow(2).sum() / weight_sq_norms[s.name]
-                        for s in stacks.sites])
+                       weight_sq_norms: dict[str, Tensor], component_group=None) -> Tensor:
+    """`[n_sites]`: `||Delta_s||_F^2 / ||W_s||_F^2` per site, in `stacks.sites` order. With
+    `component_group` every rank holds a slice of each site's components: the products `V_r U_r` are
+    summed over the group (each rank then sees the whole residual and the exact gradient of its slice)."""
+    terms = []
+    for s in stacks.sites:
+        V, U = stacks.site(s.name)
+        W = target_weights[s.name]
+        if component_group is not None:
+            from param_decomp_b200.parallel.group_ops import ReduceFromGroup
+
+            delta = W.float() - ReduceFromGroup.apply(V.float() @ U.float(), component_group).transpose(-1, -2)
+        else:
+            delta = weight_delta(W, V, U)
+        terms.append(delta.pow(2).sum() / weight_sq_norms[s.name])
+    return torch.stack(terms)
 
 
 # ---- nonlinearity locality -----------------------------------------------------------------------

@@ -38,6 +38,7 @@ class StochasticSpec:
     seed64: int
     stream: int
     row_offset: int = 0
+    col_offset: int = 0  # global index of `ci`'s first column when `ci` is a column slice of the site (multiple of 8)
 
 
 @dataclass(frozen=True)
@@ -55,9 +56,27 @@ class SiteMask:
         assert self.ci is not None
         lead, C = self.ci.shape[:-1], self.ci.shape[-1]
         key = StepKey(self.stochastic.seed64 >> 32, self.stochastic.seed64 & 0xFFFFFFFF)
-        u = rng.uniform_like_rows(key, self.stochastic.stream, tuple(lead), C,
-                                  self.stochastic.row_offset, self.ci.device).to(self.ci.dtype)
+        c0 = self.stochastic.col_offset
+        u = rng.uniform_like_rows(key, self.stochastic.stream, tuple(lead), c0 + C,
+                                  self.stochastic.row_offset, self.ci.device)[..., c0:].to(self.ci.dtype)
         return replace(self, mask=self.ci + (1 - self.ci) * u, stochastic=None)
+
+    def column_shard(self, group) -> "SiteMask":
+        """This rank's equal column slice of a mask that is replicated over `group` (components split
+        over tensor-parallel ranks): `ci` / `mask` are sliced with a gradient that re-assembles the full
+        tensor on every rank, a lazy draw keeps its place in the counter space, `delta` / `route` are
+        per-position and stay whole."""
+        import torch.distributed as dist
+
+        from param_decomp_b200.parallel.group_ops import slice_columns
+
+        cut = lambda t: None if t is None else slice_columns(t, group)  # noqa: E731
+        st = self.stochastic
+        if st is not None:
+            assert self.ci is not None
+            width = self.ci.shape[-1] // dist.get_world_size(group)
+            st = replace(st, col_offset=st.col_offset + dist.get_rank(group) * width)
+        return replace(self, ci=cut(self.ci), mask=cut(self.mask), stochastic=st)
 
 
 Masks = dict[str, SiteMask]

@@ -199,7 +199,7 @@ def run_decomposition_training(
     log = get_logger(collectives.rank)
     objective = build_objective(pd)
     expert_shard = None
-    if getattr(model, "ep", None) is not None:
+    if getattr(model, "ep", None) is not None or getattr(model, "component_group", None) is not None:
         from param_decomp_b200.parallel.expert_shard import ExpertSharding
 
         expert_shard = ExpertSharding.for_model(model)

@@ -377,8 +377,10 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
             # each rank holds some experts' blocks: its loss (and gradients) cover those, the logged value is
             # the sum over the expert group of the split sites' terms plus the replicated sites' terms
             assert ctx.relative_faithfulness, "expert-split runs use the target-relative faithfulness"
-            terms = loss_fns.faithfulness_terms(state.components, ctx.weights_W, ctx.weights_sq)
-            split = torch.tensor([s.blocked for s in state.components.sites], device=terms.device)
+            by_c = shard.by_component
+            terms = loss_fns.faithfulness_terms(state.components, ctx.weights_W, ctx.weights_sq,
+                                                component_group=shard.group if by_c else None)
+            split = torch.tensor([s.blocked and not by_c for s in state.components.sites], device=terms.device)
             faith = terms.mean()
             whole = (terms.detach() * ~split).sum() + shard.sum_over_group((terms.detach() * split).sum())
             metrics["loss/" + obj.faith.instance_key] = whole / len(state.components.sites)
@@ -487,7 +489,7 @@ def fresh_pgd_sources(ctx: StepContext, term: ReconTerm, weights: ComputeWeights
     lead = _lead_of(ci_lower)
     positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None
     device = next(iter(ci_lower.values())).device
-    leaves = adv_mod.fresh_sources(ctx.model.sites, cfg.init, cfg.source_shape, lead[0], positions, key,  # type: ignore[attr-defined]
+    leaves = adv_mod.fresh_sources(getattr(ctx.model, "global_sites", ctx.model.sites), cfg.init, cfg.source_shape, lead[0], positions, key,  # type: ignore[attr-defined]
                                    term.index, device)
     w_d, ci_d = _detach_weights(weights), _detach_ci(ci_lower)
     for _ in range(cfg.n_steps):  # type: ignore[attr-defined]
@@ -560,8 +562,13 @@ def faithfulness_warmup(ctx: StepContext, state: TrainState, steps: int, lr: flo
     last = float("nan")
     for i in range(steps):
         opt.zero_grad(set_to_none=True)
-        loss = loss_fns.faithfulness_loss(state.components, ctx.weights_W, ctx.weights_sq,
-                                          relative=ctx.relative_faithfulness)
+        shard = ctx.expert_shard
+        if shard is not None:  # split stacks: per-site terms with this rank's experts / the group-wide product
+            loss = loss_fns.faithfulness_terms(state.components, ctx.weights_W, ctx.weights_sq,
+                                               component_group=shard.group if shard.by_component else None).mean()
+        else:
+            loss = loss_fns.faithfulness_loss(state.components, ctx.weights_W, ctx.weights_sq,
+                                              relative=ctx.relative_faithfulness)
         loss.backward()
         opt.step()
         if log is not None and (i % 50 == 0 or i == steps - 1):

@@ -62,7 +62,7 @@ def fresh_pgd_recon(ctx: StepContext, state: TrainState, batch: Any, step_size: 
     lead = tuple(next(iter(ci_lower.values())).shape[:-1])
     positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None
     device = next(iter(ci_lower.values())).device
-    leaves = adv_mod.fresh_sources(ctx.model.sites, "random", "c", lead[0], positions, key, 15, device)
+    leaves = adv_mod.fresh_sources(getattr(ctx.model, "global_sites", ctx.model.sites), "random", "c", lead[0], positions, key, 15, device)
     term = ReconTerm(name="eval_pgd", index=15, strategy="fresh_pgd", cfg=None)  # type: ignore[arg-type]
     out: dict[int, float] = {}
     done = 0

@@ -85,8 +85,9 @@ def build_ci_fn(cfg: Any, model: Any, seed: int) -> nn.Module:
 def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_root: Path | None,
                  device: torch.device | str, rank: int = 0, world: int = 1, expert_group: Any = None) -> LMRun:
     """`rank`/`world` index the batch axes (data shards). `expert_group`: the process group of the mesh's
-    `tp` axis; on a mixture-of-experts target its ranks split the experts (and their component blocks)
-    and see the same tokens (param_decomp/routed/experts.py:28-40)."""
+    `tp` axis, whose ranks see the same tokens; on a mixture-of-experts target they split the experts (and
+    their component blocks, param_decomp/routed/experts.py:28-40), on a dense target every site's component
+    axis (param_decomp/core/placement.py:1040-1048)."""
     arch, weights = load_target_weights(cfg.target, data_root, device)
     ep = None
     if expert_group is not None and arch.family in ("moe", "qwen35_moe"):
@@ -109,6 +110,8 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
         site_cs = resolve_site_cs(sites_cfg, arch)
         model = tf.TransformerDecomposedModel(arch, weights, site_cs, backend=backend,
                                               attention=cfg.target.attention_implementation, n_vocab_chunks=n_chunks)
+    if expert_group is not None and ep is None:
+        model.split_components(expert_group)  # dense target: the tp axis divides every site's component axis
     ci_fn = build_ci_fn(cfg.decomposition.ci, model, cfg.pd.seed)
     if backend == "fused_sm100":
         from param_decomp_b200.core.ci_fn.mlp import BlockedSiteMLP, SiteMLP

@@ -45,8 +45,8 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
     collectives = topo.collectives()
     shard_group, shard_backend = optimizer_sharding(cfg, topo)
-    if run.ep is not None:  # expert blocks differ per tp rank: replicated-optimizer layout over the batch axes
-        shard_group, shard_backend = None, None
+    if run.ep is not None or getattr(run.model, "component_group", None) is not None:
+        shard_group, shard_backend = None, None  # split stacks differ per tp rank: replicated-optimizer layout
 
     run_dir, sink = None, None
     if data_root is not None:

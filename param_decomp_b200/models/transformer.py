@@ -30,7 +30,7 @@ from torch import Tensor
 
 from param_decomp_b200.config.experiments import TransformerArchConfig
 from param_decomp_b200.core.components import ComputeWeights, SiteSpec
-from param_decomp_b200.core.decomposed_linear import site_forward
+from param_decomp_b200.core.decomposed_linear import site_forward, site_forward_split
 from param_decomp_b200.core.masking import Masks
 from param_decomp_b200.core.model import ForwardResult
 from param_decomp_b200.formats.nonlinearity import KVHeads, Neurons, NonlinearityAlignment, QueryHeads
@@ -194,16 +194,40 @@ class TransformerDecomposedModel:
     def _linear(self, x: Tensor, name: str, weights: ComputeWeights | None, masks: Masks | None) -> Tensor:
         W = self.w[name + ".weight"]
         decomposed = weights is not None and masks is not None and name in masks and name in weights.V
+        split = getattr(self, "component_group", None) if decomposed else None
         if self.backend == "fused_sm100" and x.is_cuda:
             from param_decomp_b200.ops import linear as fused
 
+            if decomposed and split is not None:
+                return fused.site_split(x, weights, name, W, masks[name], split)  # type: ignore[index]
             if decomposed:
                 return fused.site(x, weights, name, W, masks[name])  # type: ignore[index]
             return fused.linear(x, W)
         if decomposed:
             V, U = weights.site(name)  # type: ignore[union-attr]
+            if split is not None:
+                return site_forward_split(x, V, U, W, masks[name], split)  # type: ignore[index]
             return site_forward(x, V, U, W, masks[name])  # type: ignore[index]
         return F.linear(x, W)
+
+    def split_components(self, group: Any) -> None:
+        """Split every site's component axis over the ranks of `group` (the mesh's `tp` axis): from here on
+        `sites` describes this rank's `C / W` components and `global_sites` the whole sites, which is what
+        the CI function, the masks and the adversaries see (param_decomp/core/placement.py:1040-1048)."""
+        import torch.distributed as dist
+
+        world = dist.get_world_size(group)
+        assert all(not s.blocked for s in self.sites), "blocked sites split by expert, not by component"
+        for s in self.sites:
+            assert s.C % (8 * world) == 0, f"{s.name}: C={s.C} must be a multiple of 8 x {world} ranks"
+        self._global_sites = self.sites
+        self.sites = tuple(SiteSpec(s.name, s.d_in, s.d_out, s.C // world, group=s.group, alignment=s.alignment)
+                           for s in self.sites)
+        self.component_group = group
+
+    @property
+    def global_sites(self) -> tuple[SiteSpec, ...]:
+        return getattr(self, "_global_sites", self.sites)
 
     # the three bandwidth-bound ops of a block: hand-written kernels on the fused backend
     def _fused(self, x: Tensor) -> bool:

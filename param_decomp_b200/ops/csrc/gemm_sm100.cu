@@ -103,6 +103,9 @@ struct GemmArgs {
   // delta and row scale, draws its uniforms and writes its CI gradient at the SOURCE position
   // rowmap[r] = {source row, first source column, -, -}; source row -1 marks a padding row.
   const int4* rowmap;
+  // First global column of this product's mask columns in the Philox counter space (a rank that holds a
+  // column slice of a site draws the same uniforms the whole site would); multiple of 8.
+  unsigned int philox_col0;
 };
 
 template <int BN, int NOUT, int CG = 1>
@@ -732,7 +735,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
               if (args.mask_mode == 0) {
                 float u[8];
                 philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(src_row) + args.row_offset,
-                                static_cast<uint32_t>(((src_col + c0) >> 3) + g), u);
+                                static_cast<uint32_t>(((src_col + c0) >> 3) + g) + (args.philox_col0 >> 3), u);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   const float om = 1.0f - u[i];
@@ -975,6 +978,7 @@ struct PdGemmCall {
   int ag_mode; int ag_gather_ctas;
   int cta_group;  // 0 = automatic, 1 = single CTA tiles, 2 = CTA pairs where the call allows them
   const void* rowmap;  // [M] int4 {source row, first source column, 0, 0} for the mask epilogues, or null
+  unsigned int philox_col0;  // global index of mask column 0 in the Philox counter space (multiple of 8)
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -1012,6 +1016,8 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.ag_gather_ctas = c->ag_gather_ctas;
   a.ag_mode = c->ag_mode;
   a.rowmap = static_cast<const int4*>(c->rowmap);
+  a.philox_col0 = c->philox_col0;
+  if (c->philox_col0 % 8 != 0) return kBadArgument;
   if (c->ag_world > 1 && c->ag_mode == 1) {
     a.ag_dst = const_cast<void*>(c->B0); a.ag_ld = c->ldb0; a.ag_k = c->N;
   }

@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+from dataclasses import replace
+
 import torch
 from torch import Tensor
 
@@ -46,6 +48,24 @@ def site(x: Tensor, weights: ComputeWeights, name: str, W: Tensor, sm: SiteMask)
     V, U = weights.site(name)
     sw = SiteWeights(V, U, W, weights.grad_V.get(name), weights.grad_U.get(name))
     return fused_site_forward(x, sw, sm, need_weight_grads=weights.direct_grads)
+
+
+def site_split(x: Tensor, weights: ComputeWeights, name: str, W: Tensor, sm: SiteMask, group) -> Tensor:
+    """The site with its component axis split over `group` (this rank holds `V[:, C/W]`, `U[C/W, :]`): the
+    rank's columns of the replicated mask, the fused kernels on the local slice, partial outputs summed
+    over the group; the first rank carries the target term."""
+    import torch.distributed as dist
+
+    from param_decomp_b200.parallel.group_ops import ReduceFromGroup, copy_to_group
+
+    V, U = weights.site(name)
+    sw = SiteWeights(V, U, W, weights.grad_V.get(name), weights.grad_U.get(name))
+    sm = sm.column_shard(group)
+    if sm.delta is not None and sm.delta.requires_grad:
+        sm = replace(sm, delta=copy_to_group(sm.delta, group))
+    part = fused_site_forward(copy_to_group(x, group), sw, sm, need_weight_grads=weights.direct_grads,
+                              target_term=dist.get_rank(group) == 0)
+    return ReduceFromGroup.apply(part, group)
 
 
 class _BmmBias(torch.autograd.Function):

@@ -47,7 +47,7 @@ class PdGemmCall(C.Structure):
         ("b_groups", C.c_int),
         ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
-        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int), ("rowmap", C.c_void_p),
+        ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int), ("rowmap", C.c_void_p), ("philox_col0", C.c_uint),
     ]  # fmt: skip
 
 
@@ -173,6 +173,7 @@ def gemm(
     ag_gather_ctas: int = 0,
     cta_group: int = 0,
     rowmap: torch.Tensor | None = None,
+    philox_col0: int = 0,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -231,6 +232,7 @@ def gemm(
     call.dci_accumulate = int(dci_accumulate)
     call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
     call.rng_row_offset = row_offset & 0xFFFFFFFF
+    call.philox_col0 = philox_col0
     call.split_k, call.bn, call.max_ctas = split_k, bn, max_ctas
     call.status = _status_ptr(torch._C._cuda_getDevice())
     if bgroup_of_mblock is not None:

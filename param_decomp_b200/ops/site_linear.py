@@ -59,7 +59,13 @@ class _FusedSite(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, ci_or_mask: Tensor | None, delta: Tensor | None, w: SiteWeights,
                 rowscale: Tensor | None, d_eff: Tensor | None, seed: int, stream: int, mask_mode: int,
-                row_offset: int, need_weight_grads: bool) -> Tensor:  # type: ignore[override]
+                row_offset: int, need_weight_grads: bool, col_offset: int = 0,
+                target_term: bool = True) -> Tensor:  # type: ignore[override]
+        """`col_offset`: place of mask column 0 in the site's Philox counter space (a rank holding a column
+        slice of the components draws the uniforms the whole site would). `target_term=False`: the
+        `d_eff * x W^T` part is left to another rank of a component-split site."""
+        if not target_term:
+            d_eff = None
         N = x.shape[0]
         C, d_out = w.U.shape
         A = torch.empty(N, C, device=x.device, dtype=torch.bfloat16)
@@ -75,7 +81,7 @@ class _FusedSite(torch.autograd.Function):
         else:
             ci_arg, mode = ci_or_mask, mask_mode
         nv.gemm(x, w.V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci_arg, delta=delta, rowscale=rowscale,
-                seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset)
+                seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset, philox_col0=col_offset)
         y = torch.empty(N, d_out, device=x.device, dtype=torch.bfloat16)
         if d_eff is not None:
             xd = ew.rowscale(x, d_eff)
@@ -84,7 +90,8 @@ class _FusedSite(torch.autograd.Function):
             nv.gemm(A, w.U, y, b_mn=True)
         ctx.save_for_backward(x, ci_or_mask, delta, rowscale, d_eff, A, H)
         ctx.w = w
-        ctx.rng = (seed, stream, mode, row_offset)
+        ctx.rng = (seed, stream, mode, row_offset, col_offset)
+        ctx.target_term = target_term
         ctx.need_weight_grads = need_weight_grads
         ctx.ci_arg_is_ones = ci_or_mask is None
         return y
@@ -93,7 +100,7 @@ class _FusedSite(torch.autograd.Function):
     def backward(ctx, dy: Tensor):  # type: ignore[override]
         x, ci_or_mask, delta, rowscale, d_eff, A, H = ctx.saved_tensors
         w: SiteWeights = ctx.w
-        seed, stream, mode, row_offset = ctx.rng
+        seed, stream, mode, row_offset, col_offset = ctx.rng
         N, d_in = x.shape
         C, d_out = w.U.shape
         dy = dy.contiguous()
@@ -107,7 +114,7 @@ class _FusedSite(torch.autograd.Function):
         else:
             ci_arg = ci_or_mask
         nv.gemm(dy, w.U, dH, epi=nv.EPI_MASK_BWD, ci=ci_arg, h=H, delta=delta, rowscale=rowscale, dci=dci,
-                seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset)
+                seed=seed, rng_stream=stream, mask_mode=mode, row_offset=row_offset, philox_col0=col_offset)
         dx = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty(N, d_in, device=x.device, dtype=torch.bfloat16)
@@ -123,19 +130,22 @@ class _FusedSite(torch.autograd.Function):
         d_delta = None
         if delta is not None and ctx.needs_input_grad[2]:
             # d/d(delta) = -sum_c dA*H*r + r * <dy, x W^T>; only adversarial delta sources need it
-            xw = torch.empty(N, d_out, device=x.device, dtype=torch.bfloat16)
-            nv.gemm(x, w.W, xw)
-            r = rowscale if rowscale is not None else 1.0
-            d_delta = (dy.float() * xw.float()).sum(-1) * r
+            d_delta = torch.zeros(N, device=x.device, dtype=torch.float32)
+            if ctx.target_term:
+                xw = torch.empty(N, d_out, device=x.device, dtype=torch.bfloat16)
+                nv.gemm(x, w.W, xw)
+                r = rowscale if rowscale is not None else 1.0
+                d_delta = (dy.float() * xw.float()).sum(-1) * r
             if dci is not None:
                 d_delta = d_delta - dci.float().sum(-1)  # mask_mode 1: dci holds dA*H*r
         dci_out = None
         if dci is not None and ctx.needs_input_grad[1]:
             dci_out = dci if dci.dtype == ci_or_mask.dtype else dci.to(ci_or_mask.dtype)
-        return dx, dci_out, d_delta, None, None, None, None, None, None, None, None
+        return dx, dci_out, d_delta, None, None, None, None, None, None, None, None, None, None
 
 
-def fused_site_forward(x: Tensor, w: SiteWeights, sm: SiteMask, need_weight_grads: bool) -> Tensor:
+def fused_site_forward(x: Tensor, w: SiteWeights, sm: SiteMask, need_weight_grads: bool,
+                       target_term: bool = True) -> Tensor:
     """`x [..., d_in]` bf16 -> `[..., d_out]` bf16. Stochastic specs stay lazy (drawn in-kernel)."""
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -149,10 +159,12 @@ def fused_site_forward(x: Tensor, w: SiteWeights, sm: SiteMask, need_weight_grad
         d_eff = (rowscale * delta + (1 - rowscale)) if delta is not None else (1 - rowscale)
     elif delta is not None:
         d_eff = delta
+    col_offset = 0
     if sm.stochastic is not None:
         assert sm.ci is not None
         mask_t, mode = sm.ci.reshape(N, -1), 0
         seed, stream, row_offset = sm.stochastic.seed64, sm.stochastic.stream, sm.stochastic.row_offset
+        col_offset = sm.stochastic.col_offset
     else:
         mask_t = None if sm.mask is None else sm.mask.reshape(N, -1)
         mode, seed, stream, row_offset = 1, 0, 0, 0
@@ -161,5 +173,6 @@ def fused_site_forward(x: Tensor, w: SiteWeights, sm: SiteMask, need_weight_grad
             mask_t = mask_t.to(torch.bfloat16)
         if not mask_t.is_contiguous():
             mask_t = mask_t.contiguous()
-    y = _FusedSite.apply(x2, mask_t, delta, w, rowscale, d_eff, seed, stream, mode, row_offset, need_weight_grads)
+    y = _FusedSite.apply(x2, mask_t, delta, w, rowscale, d_eff, seed, stream, mode, row_offset, need_weight_grads,
+                         col_offset, target_term)
     return y.reshape(*lead, -1)

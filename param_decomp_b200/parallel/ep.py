@@ -77,35 +77,8 @@ class _AllToAll(torch.autograd.Function):
         return out, None, None, None
 
 
-class _CopyToGroup(torch.autograd.Function):
-    """Identity whose adjoint sums over the group: for a replicated tensor that every rank feeds to
-    its own (different) experts, so the partial gradients add up to the full one on every rank."""
-
-    @staticmethod
-    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
-        ctx.group = group
-        return x.view_as(x)
-
-    @staticmethod
-    def backward(ctx, g: Tensor):  # type: ignore[override]
-        g = g.contiguous().clone()
-        dist.all_reduce(g, group=ctx.group)
-        return g, None
-
-
-class _ReduceFromGroup(torch.autograd.Function):
-    """Sum over the group whose adjoint is the identity: the summed output feeds a computation that is
-    replicated on every rank, so each rank's partial receives the (identical) full gradient."""
-
-    @staticmethod
-    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
-        out = x.contiguous().clone()
-        dist.all_reduce(out, group=group)
-        return out
-
-    @staticmethod
-    def backward(ctx, g: Tensor):  # type: ignore[override]
-        return g, None
+from param_decomp_b200.parallel.group_ops import CopyToGroup as _CopyToGroup  # noqa: E402
+from param_decomp_b200.parallel.group_ops import ReduceFromGroup as _ReduceFromGroup  # noqa: E402
 
 
 class P2PRows:

@@ -1,4 +1,5 @@
-"""Engine-side bookkeeping for component stacks whose expert blocks are split over a process group.
+"""Engine-side bookkeeping for component stacks that are split over the mesh's tp axis: by expert
+(mixture-of-experts targets) or along the component axis `C` (dense targets, `V[:, C/W]`, `U[C/W, :]`).
 
 The MoE targets under expert parallelism (`parallel/ep.py`) keep, per rank, the component blocks of
 that rank's experts only: a blocked group's stacks are `V [sites, E_loc, d_in, c]`,
@@ -31,9 +32,10 @@ from param_decomp_b200.core.components import ComponentStacks, SiteSpec
 
 @dataclass
 class ExpertSharding:
-    group: Any  # the expert (tp-axis) process group
-    n_experts: int  # true expert count E (before padding to a multiple of the group)
-    blocked_keys: frozenset[str]  # parameter keys (`ComponentStacks.param_key`) of blocked groups
+    group: Any  # the process group of the mesh's tp axis
+    n_experts: int  # true expert count E (before padding to a multiple of the group); 0 in component mode
+    blocked_keys: frozenset[str]  # parameter keys (`ComponentStacks.param_key`) of the split groups
+    by_component: bool = False  # True: dense stacks split along C (`V[..., C/W]`, `U[..., C/W, :]`)
 
     def __post_init__(self) -> None:
         self.world = dist.get_world_size(self.group)
@@ -45,10 +47,22 @@ class ExpertSharding:
     @classmethod
     def for_model(cls, model: Any) -> "ExpertSharding | None":
         ep = getattr(model, "ep", None)
-        if ep is None:
-            return None
-        keys = frozenset(ComponentStacks.param_key(s.group) for s in model.sites if s.blocked)
-        return cls(ep.group, ep.n_experts, keys)
+        if ep is not None:
+            keys = frozenset(ComponentStacks.param_key(s.group) for s in model.sites if s.blocked)
+            return cls(ep.group, ep.n_experts, keys)
+        group = getattr(model, "component_group", None)
+        if group is not None:
+            keys = frozenset(ComponentStacks.param_key(s.group) for s in model.sites)
+            return cls(group, 0, keys, by_component=True)
+        return None
+
+    def _axis(self, leaf_name: str) -> int:
+        """Which axis of a split leaf is divided: the expert axis, or (component mode) `C` - the last axis of
+        a `V`-shaped leaf, the one before last of a `U`-shaped leaf."""
+        if not self.by_component:
+            return 1
+        parts = leaf_name.replace(".", "/").split("/")
+        return -1 if "V" in parts else -2
 
     # ---- which leaves are split ----------------------------------------------------------------
     def is_split(self, leaf_name: str) -> bool:
@@ -58,20 +72,31 @@ class ExpertSharding:
         return any(ComponentStacks.param_key(p) in self.blocked_keys for p in parts)
 
     # ---- global <-> local ------------------------------------------------------------------------
-    def local_slice(self, t_global: Tensor) -> Tensor:
-        """`[sites, E, ...] -> [sites, E_loc, ...]`: this rank's experts, zero dummies at the tail."""
+    def local_slice(self, t_global: Tensor, leaf_name: str = "") -> Tensor:
+        """`[sites, E, ...] -> [sites, E_loc, ...]`: this rank's experts, zero dummies at the tail (component
+        mode: this rank's equal slice of the `C` axis)."""
+        if self.by_component:
+            ax = self._axis(leaf_name)
+            width = t_global.shape[ax] // self.world
+            return t_global.narrow(ax, self.rank * width, width).contiguous()
         out = t_global.new_zeros(t_global.shape[0], self.e_loc, *t_global.shape[2:])
         if self.n_real:
             out[:, :self.n_real] = t_global[:, self.lo:self.lo + self.n_real]
         return out
 
-    def gather(self, t_local: Tensor) -> Tensor:
-        """`[sites, E_loc, ...]` on every rank of the group `-> [sites, E, ...]` (collective)."""
+    def gather(self, t_local: Tensor, leaf_name: str = "") -> Tensor:
+        """`[sites, E_loc, ...]` on every rank of the group `-> [sites, E, ...]` (collective); component
+        mode: the slices of the `C` axis side by side."""
         parts = [torch.empty_like(t_local) for _ in range(self.world)]
         dist.all_gather(parts, t_local.contiguous(), group=self.group)
+        if self.by_component:
+            return torch.cat(parts, dim=self._axis(leaf_name)).contiguous()
         return torch.cat(parts, dim=1)[:, :self.n_experts].contiguous()
 
     def global_sites(self, sites: tuple[SiteSpec, ...]) -> tuple[SiteSpec, ...]:
+        if self.by_component:
+            return tuple(SiteSpec(s.name, s.d_in, s.d_out, s.C * self.world, group=s.group, alignment=s.alignment)
+                         for s in sites)
         return tuple(s if not s.blocked else SiteSpec(s.name, s.d_in, s.d_out, s.C_block * self.n_experts, group=s.group,
                                                       n_blocks=self.n_experts, alignment=s.alignment) for s in sites)
 
@@ -83,10 +108,10 @@ class ExpertSharding:
         full.init_random(generator)
         for gname in local.groups:
             key = local.param_key(gname)
-            for mine, theirs in ((local.V[key], full.V[key]), (local.U[key], full.U[key])):
+            for leaf, mine, theirs in (("V", local.V[key], full.V[key]), ("U", local.U[key], full.U[key])):
                 n = theirs.shape[0]
                 if key in self.blocked_keys:
-                    mine[:n].copy_(self.local_slice(theirs))
+                    mine[:n].copy_(self.local_slice(theirs, leaf))
                 else:
                     mine[:n].copy_(theirs)
 

@@ -1,0 +1,74 @@
+"""Autograd pieces for computations split over a process group whose ranks all see the same batch
+(tensor / expert parallelism): the conjugate identity / all-reduce pair and a column slice of a
+replicated tensor. With them every rank holds exact gradients - full ones for replicated leaves,
+its own for split leaves - so the data-parallel reduction needs no special cases.
+
+Parity: the reshard points GSPMD inserts around `param_decomp/core/decomposed_linear.py:142-175`
+(contraction over `C / tp` -> all-reduce of the site output) and `param_decomp/routed/experts.py:864-885`.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+
+class CopyToGroup(torch.autograd.Function):
+    """Identity whose adjoint sums over the group: for a replicated tensor that every rank feeds to
+    its own (different) part of the weights, so the partial gradients add up to the full one."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class ReduceFromGroup(torch.autograd.Function):
+    """Sum over the group whose adjoint is the identity: the summed output feeds a computation that is
+    replicated on every rank, so each rank's partial receives the (identical) full gradient."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        out = x.contiguous().clone()
+        dist.all_reduce(out, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        return g, None
+
+
+class SliceColumns(torch.autograd.Function):
+    """`x[..., lo:hi]` of a replicated tensor, rank `r` of the group taking the `r`-th equal slice. Each
+    rank's gradient lives on its own columns only, so the adjoint is an all-gather along the last axis
+    (every rank ends with the full gradient) rather than an all-reduce of mostly-zero tensors."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        width = x.shape[-1] // world
+        assert width * world == x.shape[-1], f"{x.shape[-1]} columns do not tile {world} ranks"
+        ctx.group, ctx.world = group, world
+        return x[..., rank * width:(rank + 1) * width]
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        g = g.contiguous()
+        parts = [torch.empty_like(g) for _ in range(ctx.world)]
+        dist.all_gather(parts, g, group=ctx.group)
+        return torch.cat(parts, dim=-1), None
+
+
+def copy_to_group(x: Tensor, group) -> Tensor:
+    return CopyToGroup.apply(x, group) if x.requires_grad else x
+
+
+def slice_columns(x: Tensor, group) -> Tensor:
+    return SliceColumns.apply(x, group)

@@ -1,0 +1,109 @@
+"""Component-split (tensor-parallel) training through the engine on CPU (gloo, 2 ranks on the mesh's tp
+axis): every site's component axis is divided over the ranks; the run follows the single-process run
+step for step and writes the same checkpoint files."""
+import copy
+import os
+import socket
+import tempfile
+from pathlib import Path
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+import __graft_entry__ as ge
+from param_decomp_b200.config.experiments import LMExperimentConfig
+from param_decomp_b200.core.checkpoint import DECOMPOSITION_FILE, TRAINING_FILE
+
+STEPS = 4
+SPLIT_ID, SINGLE_ID = "p-0000cccc", "p-0000dddd"
+
+
+def _cfg(tp: int, losses: str) -> LMExperimentConfig:
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"]["backend"] = "eager_torch"
+    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
+    c["runtime"]["sharding"] = "ddp"
+    c["target"]["weights_dtype"] = "float32"
+    c["target"]["attention_implementation"] = "xla"
+    c["target"]["spec"]["arch"] = {"family": "glu_transformer", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 48,
+                                   "vocab_size": 100}
+    c["decomposition"]["sites"] = {"kind": "glu_transformer", "layers": {"kind": "all"},
+                                   "cs": {"q": 32, "o": 16, "gate": 48, "down": 32}}
+    c["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [16]}
+    c["data"]["seq_len"] = 8
+    c["pd"]["batch_size"] = 4
+    c["pd"]["steps"] = STEPS
+    if losses == "pgd":  # a persistent adversary: sources live on the whole sites, their gradients re-assemble
+        c["pd"]["loss_metrics"] = [
+            {"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 1.0},
+            {"type": "PersistentPGDReconLoss", "coeff": 1.0, "source_shape": "bc", "n_warmup_steps": 1,
+             "optimizer": {"type": "adam", "lr_schedule": 0.05}},
+            {"type": "FaithfulnessLoss", "coeff": 10.0},
+        ]
+    c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "periodic", "save_every": 2, "retention": {"kind": "keep_all"}}}
+    c["eval"] = None
+    return LMExperimentConfig.model_validate(c)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _train(cfg, root: Path, run_id: str):
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    states: list = []
+    res = train_lm(cfg, root, run_id=run_id, device="cpu", state_out=states)
+    return res, states[0]
+
+
+def _worker(rank: int, world: int, port: int, root: str, losses: str, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    res, state = _train(_cfg(world, losses), Path(root), SPLIT_ID)
+    assert state.expert_shard is not None and state.expert_shard.by_component
+    out[rank] = (dict(res.last_metrics), {n: p.detach().clone() for n, p in state.components.named_parameters()},
+                 {n: p.detach().clone() for n, p in state.ci_fn.named_parameters()})
+
+
+@pytest.mark.parametrize("losses", ["stochastic", "pgd"])
+def test_component_split_engine_matches_single_process(losses):
+    from safetensors import safe_open
+
+    with tempfile.TemporaryDirectory() as root:
+        world, port = 2, _free_port()
+        out = mp.Manager().dict()
+        mp.spawn(_worker, args=(world, port, root, losses, out), nprocs=world, join=True)
+        res, ref = _train(_cfg(1, losses), Path(root), SINGLE_ID)
+        keys = [k for k in res.last_metrics if k.startswith("train/loss/") or k.startswith("train/grad_norm/")]
+        assert len(keys) >= 4
+        for k in keys:
+            for r in range(world):
+                got, want = out[r][0][k], res.last_metrics[k]
+                assert abs(got - want) <= 3e-4 * abs(want) + 1e-7, (k, r, got, want)
+        ref_params = dict(ref.components.named_parameters())
+        for r in range(world):
+            _, local, ci_params = out[r]
+            for name, p in local.items():
+                g = ref_params[name].detach()
+                ax = -1 if name.startswith("V") else -2
+                w = g.shape[ax] // world
+                assert torch.allclose(p, g.narrow(ax, r * w, w), atol=3e-6), name
+            for name, p in ref.ci_fn.named_parameters():
+                assert torch.allclose(ci_params[name], p.detach(), atol=3e-6), name
+        for item in (DECOMPOSITION_FILE, TRAINING_FILE):
+            split_f = [p for p in sorted(Path(root).rglob(item)) if SPLIT_ID in str(p)][-1]
+            single_f = Path(str(split_f).replace(SPLIT_ID, SINGLE_ID))
+            with safe_open(str(split_f), framework="pt") as fs, safe_open(str(single_f), framework="pt") as f1:
+                assert set(fs.keys()) == set(f1.keys())
+                for k in fs.keys():
+                    assert fs.get_tensor(k).shape == f1.get_tensor(k).shape, k
+                    a, b = fs.get_tensor(k).float(), f1.get_tensor(k).float()
+                    if k.startswith("adversaries/") or k.startswith("opt/"):
+                        # sign-like Adam steps amplify rounding noise where a gradient is ~0: compare in the mean
+                        assert float((a - b).abs().mean()) <= 1e-3 * (float(b.abs().mean()) + 1e-3), k
+                    else:
+                        assert torch.allclose(a, b, atol=3e-6), k
