@@ -102,6 +102,32 @@ def test_mask_epilogues_match_philox_reference(nv):
     assert rel(dci32, dci0 + want_dci) < 1e-5 and rel(dcib, want_dci) < 5e-3
 
 
+def test_mask_epilogue_column_slice_draws_the_sites_uniforms(nv):
+    """A product over a column slice of a site (tensor-parallel components) with `philox_col0` set to the
+    slice's first column reproduces the corresponding columns of the whole-site product, forward and
+    mask gradient, reading `ci` through a strided view."""
+    torch.manual_seed(21)
+    M, C, D, Dout, lo = 384, 512, 128, 192, 256
+    x = torch.randn(M, D, device="cuda", dtype=bf)
+    V = (torch.randn(D, C, device="cuda") / D**0.5).to(bf)
+    U = (torch.randn(C, Dout, device="cuda") / C**0.5).to(bf)
+    ci = torch.rand(M, C, device="cuda").to(bf)
+    dy = torch.randn(M, Dout, device="cuda", dtype=bf)
+    rng = dict(seed=77, rng_stream=5, row_offset=9)
+    A, H = torch.empty(M, C, device="cuda", dtype=bf), torch.empty(M, C, device="cuda", dtype=bf)
+    nv.gemm(x, V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci, **rng)
+    dH, dci = torch.empty(M, C, device="cuda", dtype=bf), torch.empty(M, C, device="cuda", dtype=bf)
+    nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, dci=dci, **rng)
+    Vs, Us = V[:, lo:].contiguous(), U[lo:].contiguous()
+    As, Hs = torch.empty(M, C - lo, device="cuda", dtype=bf), torch.empty(M, C - lo, device="cuda", dtype=bf)
+    nv.gemm(x, Vs, As, b_mn=True, epi=nv.EPI_MASK_FWD, out1=Hs, ci=ci[:, lo:], philox_col0=lo, **rng)
+    dHs, dcis = torch.empty(M, C - lo, device="cuda", dtype=bf), torch.empty(M, C - lo, device="cuda", dtype=bf)
+    nv.gemm(dy, Us, dHs, epi=nv.EPI_MASK_BWD, ci=ci[:, lo:], h=Hs, dci=dcis, philox_col0=lo, **rng)
+    _done(nv)
+    assert torch.equal(As, A[:, lo:]) and torch.equal(Hs, H[:, lo:])
+    assert torch.equal(dHs, dH[:, lo:]) and torch.equal(dcis, dci[:, lo:])
+
+
 def test_bounded_wait_reports_instead_of_hanging(nv):
     """A GEMM whose grid is capped far below the tile count still finishes and leaves status 0; the
     status word protocol itself is exercised by reading and clearing it."""

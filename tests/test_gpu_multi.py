@@ -308,3 +308,49 @@ def test_expert_split_engine_two_gpus():
         for r in range(world):
             got, want = out[r]["train/" + k], ref["train/" + k]
             assert abs(got - want) <= 3e-2 * abs(want) + 1e-6, (k, r, got, want)
+
+
+def _dense_engine_cfg(tp: int):
+    import copy
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"]["backend"] = "fused_sm100"
+    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
+    c["runtime"]["sharding"] = "ddp"
+    c["pd"]["steps"] = 3
+    c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "none"}}
+    c["eval"] = None
+    return LMExperimentConfig.model_validate(c)
+
+
+def _tp_engine_worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from param_decomp_b200.experiments.lm.training import train_lm
+    from param_decomp_b200.ops import native
+
+    states: list = []
+    res = train_lm(_dense_engine_cfg(world), None, device="cuda", state_out=states)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert states[0].expert_shard is not None and states[0].expert_shard.by_component
+    out[rank] = dict(res.last_metrics)
+
+
+def test_component_split_engine_two_gpus():
+    """The engine with every site's component axis split over two GPUs (fused backend: the mask kernels draw
+    their slice of the site's uniforms, partial site outputs are summed over the pair) against one GPU."""
+    _need_two_gpus()
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_tp_engine_worker, args=(world, port, out), nprocs=world, join=True)
+    ref = train_lm(_dense_engine_cfg(1), None, device="cuda").last_metrics
+    for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss"):
+        for r in range(world):
+            got, want = out[r]["train/" + k], ref["train/" + k]
+            assert abs(got - want) <= 3e-2 * abs(want) + 1e-6, (k, r, got, want)
