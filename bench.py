@@ -99,6 +99,12 @@ def main() -> None:
                     help="N>1: fused reduce-scatter+AdamW+all-gather kernel, NCCL RS/AG, or all-reduce + replicated AdamW")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
+    ap.add_argument("--tp", type=int, default=1,
+                    help="size of the mesh's tp axis (ranks of one tp group see the same tokens and split the experts "
+                         "of a mixture-of-experts target or every site's component axis of a dense one)")
+    ap.add_argument("--kernel-table", type=Path, default=None,
+                    help="after the timed steps, run one more step under the torch profiler and write the kernels "
+                         "ranked by device time to this file (never part of a reported number)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -121,14 +127,23 @@ def main() -> None:
     cfg = LMExperimentConfig.from_file(args.config)
     pd = cfg.pd if args.batch is None else cfg.pd.model_copy(update={"batch_size": args.batch})
     cfg = cfg.model_copy(update={"pd": pd})
-    topo = topology.initialize(HsdpMeshShape(replicate=1, fsdp=world, tp=1), "cuda")
-    run = build_lm_run(cfg, None, topo.device, topo.data_rank, topo.data_world)
+    assert world % args.tp == 0, f"--tp {args.tp} does not divide {world} GPUs"
+    topo = topology.initialize(HsdpMeshShape(replicate=1, fsdp=world // args.tp, tp=args.tp), "cuda")
+    run = build_lm_run(cfg, None, topo.device, topo.data_rank, topo.data_world,
+                       expert_group=topo.groups.get("tp") if args.tp > 1 else None)
     objective = build_objective(cfg.pd)
-    ctx = StepContext.build(run.model, objective, cfg.pd, collectives=topo.collectives(), lazy_masks=True)
+    expert_shard = None
+    if args.tp > 1:
+        from param_decomp_b200.parallel.expert_shard import ExpertSharding
+
+        expert_shard = ExpertSharding.for_model(run.model)
+    ctx = StepContext.build(run.model, objective, cfg.pd, collectives=topo.collectives(), lazy_masks=True,
+                            expert_shard=expert_shard)
     rows = cfg.pd.batch_size // topo.data_world
-    shard_backend = args.optim if (world > 1 and args.optim != "ddp") else None
+    shard_backend = args.optim if (topo.data_world > 1 and args.optim != "ddp" and args.tp == 1) else None
     state = init_train_state(run.model, run.ci_fn, cfg.pd, objective, topo.device, rows, cfg.data.seq_len,
-                             use_fused_optim=True, shard_group=topo.data_group, shard_backend=shard_backend)
+                             use_fused_optim=True, shard_group=topo.data_group, shard_backend=shard_backend,
+                             expert_shard=expert_shard)
     tokens_per_step = cfg.pd.batch_size * cfg.data.seq_len
 
     def sync() -> None:
@@ -181,6 +196,17 @@ def main() -> None:
     clocks = sampler.stop() if topo.rank == 0 else {}
     launches = native.launch_count() - launches0
     native.check_status()
+    if args.kernel_table is not None:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            train_step(ctx, state, dev_batches[0])
+            torch.cuda.synchronize()
+        if topo.rank == 0:
+            args.kernel_table.parent.mkdir(parents=True, exist_ok=True)
+            args.kernel_table.write_text(prof.key_averages().table(sort_by="self_cuda_time_total", row_limit=40,
+                                                                    max_name_column_width=90))
+        sync()
     ms = torch.tensor([e0.elapsed_time(e1)], device=topo.device)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -199,7 +225,8 @@ def main() -> None:
                           + (f" experts{arch.n_experts} top{arch.experts_per_token}" if arch.family == "moe" else "")),
                 "config_file": str(args.config.relative_to(ROOT)) if args.config.is_relative_to(ROOT) else str(args.config),
                 "global_batch": cfg.pd.batch_size, "seq_len": cfg.data.seq_len,
-                "parallelism": (f"dp{world} ({'zero1 ' + args.optim if shard_backend else 'ddp all-reduce'})"
+                "parallelism": ((f"dp{topo.data_world}" + (f" x tp{args.tp}" if args.tp > 1 else "")
+                                 + f" ({'zero1 ' + args.optim if shard_backend else 'ddp all-reduce'})")
                                 if world > 1 else "single"),
                 "decomposition": (", ".join(f"{k}:{v}" for k, v in cfg.decomposition.sites.cs.items())
                                   + f" components per matrix x {arch.n_layer} layers; CI fn {cfg.decomposition.ci.type}"),
