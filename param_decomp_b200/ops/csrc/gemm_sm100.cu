@@ -1058,7 +1058,10 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   const int b_batch = c->b_bcast ? 1 : (c->bgroup_of_mblock ? c->b_groups : c->batch);
   // CTA pairs (one MMA over two CTAs, each staging half of B): dense, ungrouped products whose row
   // count fills at least one 256-row tile; `cta_group` = 1 / 2 forces the choice, 0 = automatic.
-  const bool pair_ok = bn == 256 && c->bgroup_of_mblock == nullptr && c->ag_world <= 1 && c->rs_world <= 1 &&
+  // A grouped product may pair only on request (`cta_group` = 2): the caller then guarantees that row groups
+  // start on 256-row boundaries, so both CTAs of a pair read the same group's B.
+  const bool grouped_pair = c->bgroup_of_mblock == nullptr || (c->cta_group == 2 && c->M % (2 * BM) == 0);
+  const bool pair_ok = bn == 256 && grouped_pair && c->ag_world <= 1 && c->rs_world <= 1 &&
                        c->M >= 2 * BM && (c->max_ctas == 0 || c->max_ctas >= 2);
   // Measured on the flagship shapes: pairs win 5-23% whenever an operand is MN-major (several TMA boxes
   // per stage); with both operands K-major the single-CTA tiles are as fast or faster, except the
