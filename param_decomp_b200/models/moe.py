@@ -173,6 +173,9 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         if self.ep is None and self._fused(xt):
             return self.expert_tokens(i, xt, sel.indices, sel.weights, weights, masks, token_of_job,
                                       slot_of_job).reshape(B, T, d)
+        if self.ep is not None and self.ep.fast_allreduce(self, xt):
+            return self.ep.run_tokens_allreduce(self, i, xt, sel.indices, sel.weights, weights, masks, token_of_job,
+                                                slot_of_job).reshape(B, T, d)
         if self.ep is not None:
             y_jobs = self.ep.run_experts(self, i, xt, expert_of_job, token_of_job, slot_of_job, weights, masks)
         else:
@@ -200,7 +203,8 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         V, U = weights.site(name)
         J = token_of_job.numel()
         src = sm0.ci if sm0.stochastic is not None else sm0.mask
-        if self.use_row_map and src is not None and self.ep is None and src.shape[-1] % c == 0 and c % 8 == 0:
+        local_ok = self.ep is None or getattr(layout, "foreign", False)
+        if self.use_row_map and src is not None and local_ok and src.shape[-1] % c == 0 and c % 8 == 0:
             # mask inputs stay in token order; the kernels map job rows to them and draw the mask themselves
             from param_decomp_b200.ops import grouped as G
 
@@ -234,14 +238,15 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
                                     need_wgrad=weights.direct_grads)
 
     def expert_tokens(self, i: int, xt: Tensor, indices: Tensor, route_w: Tensor, weights, masks,
-                      token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
+                      token_of_job: Tensor, slot_of_job: Tensor, layout=None) -> Tensor:
         """Fused single-rank path: tokens `[N, d]` fan out to padded sorted job rows, run gate / up / down on
         the grouped kernels and come back as the routing-weighted sum per token."""
         from param_decomp_b200.ops.grouped import JobLayout
 
         n = lambda kind: tf.site_name("moe", i, kind)  # noqa: E731
         k = indices.shape[-1]
-        layout = JobLayout.cached(indices, self.w[n("experts_gate") + ".weight"].shape[0])
+        if layout is None:  # (an expert group passes the layout of its own experts' jobs)
+            layout = JobLayout.cached(indices, self.w[n("experts_gate") + ".weight"].shape[0])
         xs = layout.expand_tokens(xt, k)
         gate = self._grouped_site(n("experts_gate"), xs, layout, weights, masks, token_of_job, slot_of_job)
         up = self._grouped_site(n("experts_up"), xs, layout, weights, masks, token_of_job, slot_of_job)

@@ -311,6 +311,9 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
         if self.ep is None and self._fused(xt):
             routed = self.expert_tokens(i, xt, pinned[i].indices if pinned is not None else sel.indices, sel_w, weights,
                                         masks, token_of_job, slot_of_job).reshape(B, T, d)
+        elif self.ep is not None and self.ep.fast_allreduce(self, xt):
+            routed = self.ep.run_tokens_allreduce(self, i, xt, pinned[i].indices if pinned is not None else sel.indices,
+                                                  sel_w, weights, masks, token_of_job, slot_of_job).reshape(B, T, d)
         elif self.ep is not None:
             y_jobs = self.ep.run_experts(self, i, xt, expert_of_job, token_of_job, slot_of_job, weights, masks)
         else:
@@ -321,7 +324,7 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
                     bounds.append(bounds[-1] + n)
             y_jobs = self.expert_jobs(i, repeat_rows(xt, k), expert_of_job, order, bounds, weights, masks, token_of_job,
                                       slot_of_job, routing_indices=(pinned[i].indices if pinned is not None else sel.indices))
-        if not (self.ep is None and self._fused(xt)):
+        if not self._fused(xt) or (self.ep is not None and not self.ep.fast_allreduce(self, xt)):
             routed = (y_jobs.reshape(B * T, k, d) * sel_w.reshape(B * T, k, 1).to(y_jobs.dtype)).sum(1).reshape(B, T, d)
         h = self._swiglu(lin(x, "shared_gate"), lin(x, "shared_up"))
         if taps is not None:
@@ -331,14 +334,15 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
         return routed + (sg * shared.float()).to(x.dtype)
 
     def expert_tokens(self, i: int, xt: Tensor, indices: Tensor, route_w: Tensor, weights, masks,
-                      token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
+                      token_of_job: Tensor, slot_of_job: Tensor, layout=None) -> Tensor:
         """Fused single-rank path: tokens `[N, d]` fan out to padded sorted job rows, run gate / up / down on
         the grouped kernels and come back as the routing-weighted sum per token."""
         from param_decomp_b200.ops.grouped import JobLayout
 
         n = lambda kind: site_name(i, kind)  # noqa: E731
         k = indices.shape[-1]
-        layout = JobLayout.cached(indices, self.w[n("experts_gate") + ".weight"].shape[0])
+        if layout is None:  # (an expert group passes the layout of its own experts' jobs)
+            layout = JobLayout.cached(indices, self.w[n("experts_gate") + ".weight"].shape[0])
         xs = layout.expand_tokens(xt, k)
         gate = self._grouped_site(n("experts_gate"), xs, layout, weights, masks, token_of_job, slot_of_job)
         up = self._grouped_site(n("experts_up"), xs, layout, weights, masks, token_of_job, slot_of_job)

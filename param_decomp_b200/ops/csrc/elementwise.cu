@@ -354,9 +354,10 @@ __global__ void rows_expand_kernel(const __nv_bfloat16* __restrict__ x, const in
 }
 
 // y[n, :] = sum_s w[n, s] * padded[pos[n * k + s], :]   (fp32 accumulation)
+// With `bgroup` (owner of every 128-row block, -1 = rows no product wrote) jobs in unowned blocks are left out.
 __global__ void rows_combine_kernel(const __nv_bfloat16* __restrict__ padded, const long long* __restrict__ pos,
-                                    const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
-                                    long long tokens, int d, int k_sel) {
+                                    const float* __restrict__ w, const int* __restrict__ bgroup,
+                                    __nv_bfloat16* __restrict__ y, long long tokens, int d, int k_sel) {
   const int segs = d / 8;
   const long long total = tokens * segs;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -367,6 +368,7 @@ __global__ void rows_combine_kernel(const __nv_bfloat16* __restrict__ padded, co
 #pragma unroll 4
     for (int s = 0; s < k_sel; ++s) {
       const long long r = __ldg(pos + n * k_sel + s);
+      if (bgroup != nullptr && __ldg(bgroup + (r >> 7)) < 0) continue;
       const float sc = w != nullptr ? __ldg(w + n * k_sel + s) : 1.0f;
       const uint4 q = *reinterpret_cast<const uint4*>(padded + r * d + seg * 8);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
@@ -816,11 +818,11 @@ extern "C" int pd_rows_expand(const void* x, const void* rowmap, const float* w,
       static_cast<__nv_bfloat16*>(out), n_rows, d, k_sel, rep, use_slot);
   return PD_CHECK_LAUNCH();
 }
-extern "C" int pd_rows_combine(const void* padded, const long long* pos, const float* w, void* y,
-                               long long tokens, int d, int k_sel, void* stream) {
+extern "C" int pd_rows_combine(const void* padded, const long long* pos, const float* w, const int* bgroup,
+                               void* y, long long tokens, int d, int k_sel, void* stream) {
   if (d % 8 != 0 || tokens <= 0) return 5;
   rows_combine_kernel<<<blocks_for(tokens * (d / 8), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(padded), pos, w, static_cast<__nv_bfloat16*>(y), tokens, d, k_sel);
+      static_cast<const __nv_bfloat16*>(padded), pos, w, bgroup, static_cast<__nv_bfloat16*>(y), tokens, d, k_sel);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_ci_squash(const void* pre, void* lower, void* upper, long long n, float alpha, void* stream) {

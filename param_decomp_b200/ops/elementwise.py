@@ -74,16 +74,19 @@ def rows_expand(x: Tensor, rowmap: Tensor, w: Tensor | None, n_rows: int, k: int
     return out
 
 
-def rows_combine(padded: Tensor, pos: Tensor, w: Tensor | None, tokens: int, k: int) -> Tensor:
-    """`y[n] = sum_s w[n, s] * padded[pos[n * k + s]]` (fp32 accumulation, bf16 rows)."""
+def rows_combine(padded: Tensor, pos: Tensor, w: Tensor | None, tokens: int, k: int,
+                 bgroup: Tensor | None = None) -> Tensor:
+    """`y[n] = sum_s w[n, s] * padded[pos[n * k + s]]` (fp32 accumulation, bf16 rows). `bgroup` (int32, one
+    entry per 128 rows): jobs whose row block has owner -1 are skipped (rows this rank never computed)."""
     assert padded.dtype == torch.bfloat16 and padded.is_contiguous() and pos.dtype == torch.int64
     assert pos.numel() == tokens * k
     y = torch.empty(tokens, padded.shape[1], device=padded.device, dtype=torch.bfloat16)
     lib = _lib()
-    lib.pd_rows_combine.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int,
-                                    C.c_void_p]
+    lib.pd_rows_combine.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
+                                    C.c_int, C.c_void_p]
     _check(lib.pd_rows_combine(padded.data_ptr(), pos.data_ptr(), w.data_ptr() if w is not None else None,
-                               y.data_ptr(), tokens, padded.shape[1], k, _s()), "rows_combine")
+                               bgroup.data_ptr() if bgroup is not None else None, y.data_ptr(), tokens,
+                               padded.shape[1], k, _s()), "rows_combine")
     return y
 
 

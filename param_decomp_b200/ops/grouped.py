@@ -59,6 +59,29 @@ class JobLayout:
         return layout
 
     @classmethod
+    def cached_local(cls, indices: Tensor, lo: int, n_local: int) -> "JobLayout":
+        """The layout one rank of an expert group uses when every rank sees all tokens: the jobs of its own
+        experts `[lo, lo + n_local)` form groups `0 .. n_local - 1`, all other jobs are parked in a last group
+        whose row blocks carry owner -1, so the grouped products skip them and `combine` leaves them out."""
+        key = (id(indices), -(lo * 65536 + n_local) - 1)
+        hit = _LAYOUTS.get(key)
+        if hit is not None and hit[0]() is indices:
+            return hit[1]
+        e = indices.reshape(-1)
+        mine = (e >= lo) & (e < lo + n_local)
+        layout = cls.build(torch.where(mine, e - lo, torch.full_like(e, n_local)), n_local + 1)
+        layout.bgroup = torch.where(layout.bgroup == n_local, torch.full_like(layout.bgroup, -1), layout.bgroup)
+        layout.krange = layout.krange[:n_local].contiguous()
+        layout.foreign = True
+        _LAYOUTS[key] = (weakref.ref(indices), layout)
+        return layout
+
+    @property
+    def skip(self) -> Tensor | None:
+        """Row-block owners for the combine kernels when some rows are never computed."""
+        return self.bgroup if getattr(self, "foreign", False) else None
+
+    @classmethod
     def build(cls, expert_of_job: Tensor, n_experts: int) -> "JobLayout":
         J = expert_of_job.numel()
         # (a scatter-add, not bincount: bincount sizes its output from the data and synchronises)
@@ -137,7 +160,7 @@ class _TokensToRows(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g: Tensor):  # type: ignore[override]
-        return ew.rows_combine(g.contiguous(), ctx.layout.pos, None, ctx.n, ctx.k), None, None
+        return ew.rows_combine(g.contiguous(), ctx.layout.pos, None, ctx.n, ctx.k, ctx.layout.skip), None, None
 
 
 class _RowsToTokens(torch.autograd.Function):
@@ -147,7 +170,7 @@ class _RowsToTokens(torch.autograd.Function):
         padded = padded.contiguous()
         ctx.save_for_backward(route_w, padded if ctx.needs_input_grad[1] else None)
         N, k = route_w.shape
-        return ew.rows_combine(padded, layout.pos, route_w, N, k)
+        return ew.rows_combine(padded, layout.pos, route_w, N, k, layout.skip)
 
     @staticmethod
     def backward(ctx, g: Tensor):  # type: ignore[override]
@@ -158,6 +181,9 @@ class _RowsToTokens(torch.autograd.Function):
         d_w = None
         if padded is not None:  # routing weights recomputed from the live activations
             d_w = (padded.index_select(0, layout.pos).reshape(N, k, -1).float() * g.float()[:, None, :]).sum(-1)
+            if layout.skip is not None:  # rows of jobs this rank never computed hold no data
+                owned = layout.skip[(layout.pos >> 7)].reshape(N, k) >= 0
+                d_w = torch.where(owned, d_w, torch.zeros((), device=d_w.device))
         return d_padded, d_w, None
 
 

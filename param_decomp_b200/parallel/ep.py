@@ -232,6 +232,35 @@ class ExpertParallel:
         inv[order] = torch.arange(J, device=order.device)
         return y_sorted[inv]
 
+    def fast_allreduce(self, model, xt: Tensor) -> bool:
+        """Whether `run_tokens_allreduce` applies: all-reduce mode on the fused backend with mask inputs
+        read through the row map."""
+        return self.mode == "allreduce" and model._fused(xt) and getattr(model, "use_row_map", False)
+
+    def run_tokens_allreduce(self, model, layer: int, xt: Tensor, indices: Tensor, route_w: Tensor, weights, masks,
+                             token_of_job: Tensor, slot_of_job: Tensor) -> Tensor:
+        """All-reduce mode on the grouped kernels, tokens in and tokens out. The job layout parks every other
+        rank's jobs in row blocks without an owner, so the grouped products touch this rank's experts only and
+        the routing-weighted combine leaves the rest out; the mask inputs stay in token order (read through the
+        row map). No host synchronisation: shapes do not depend on the routing."""
+        from dataclasses import replace
+
+        from param_decomp_b200.ops.grouped import JobLayout
+        from param_decomp_b200.parallel.group_ops import copy_to_group
+
+        layout = JobLayout.cached_local(indices, self.rank * self.e_loc, self.e_loc)
+        shared = dict(masks) if masks is not None else None
+        if shared is not None:
+            for name in model.expert_site_names(layer):
+                sm = shared.get(name)
+                if sm is None:
+                    continue
+                cut = lambda t: None if t is None else copy_to_group(t, self.group)  # noqa: E731
+                shared[name] = replace(sm, ci=cut(sm.ci), mask=cut(sm.mask), delta=cut(sm.delta))
+        y = model.expert_tokens(layer, copy_to_group(xt, self.group), indices, copy_to_group(route_w, self.group),
+                                weights, shared, token_of_job, slot_of_job, layout=layout)
+        return _ReduceFromGroup.apply(y, self.group)
+
     def _all_to_all_p2p(self, model, layer: int, xt: Tensor, expert_of_job: Tensor, token_of_job: Tensor,
                         slot_of_job: Tensor, weights, masks) -> Tensor:
         """Same result as the collective transport; rows move by `pd_ep_scatter_rows`."""
