@@ -464,18 +464,19 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
                                               const float* __restrict__ dcol,
                                               __nv_bfloat16* __restrict__ dpre, long long rows, int C,
                                               float gamma2, float norm, float alpha) {
-  const long long total = rows * (C / 8);
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int col = static_cast<int>(i % (C / 8)) * 8;
-    const uint4 q = *reinterpret_cast<const uint4*>(pre + i * 8);
+  // Same tiling as the forward: a thread owns 8 columns (its dcol values stay in registers) and walks
+  // rows with the grid's row stride, two rows in flight per iteration.
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + cg) * 8;
+  if (col >= C) return;
+  const float4 d0 = *reinterpret_cast<const float4*>(dcol + col);
+  const float4 d1 = *reinterpret_cast<const float4*>(dcol + col + 4);
+  const float dc[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+  const float k2 = norm * 2.f * gamma2;
+  const long long stride = static_cast<long long>(gridDim.y) * 8;
+  auto one = [&](long long r, const uint4 q, const uint4 gq) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-    uint4 gq = make_uint4(0, 0, 0, 0);
-    if (dlower) gq = *reinterpret_cast<const uint4*>(dlower + i * 8);
     const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
-    const float4 d0 = *reinterpret_cast<const float4*>(dcol + col);
-    const float4 d1 = *reinterpret_cast<const float4*>(dcol + col + 4);
-    const float dc[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
     __nv_bfloat162 o[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -490,12 +491,27 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
         else if (xv > 0.f) { u = xv; du = 1.f; lg = gg[e]; }
         else { u = 0.f; du = 0.f; lg = gg[e] < 0.f ? alpha * gg[e] : 0.f; }
         const float den = u * u + gamma2;
-        const float dpsi = __fdividef(norm * 2.f * u * gamma2, den * den);
+        const float dpsi = __fdividef(k2 * u, den * den);
         out[e] = lg + dc[2 * k + e] * dpsi * du;
       }
       o[k] = __floats2bfloat162_rn(out[0], out[1]);
     }
-    *reinterpret_cast<uint4*>(dpre + i * 8) = *reinterpret_cast<uint4*>(o);
+    *reinterpret_cast<uint4*>(dpre + r * C + col) = *reinterpret_cast<uint4*>(o);
+  };
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  long long r = static_cast<long long>(blockIdx.y) * 8 + rl;
+  for (; r + stride < rows; r += 2 * stride) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(pre + r * C + col);
+    const uint4 qb = *reinterpret_cast<const uint4*>(pre + (r + stride) * C + col);
+    const uint4 ga = dlower ? *reinterpret_cast<const uint4*>(dlower + r * C + col) : zero;
+    const uint4 gb = dlower ? *reinterpret_cast<const uint4*>(dlower + (r + stride) * C + col) : zero;
+    one(r, qa, ga);
+    one(r + stride, qb, gb);
+  }
+  if (r < rows) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(pre + r * C + col);
+    const uint4 ga = dlower ? *reinterpret_cast<const uint4*>(dlower + r * C + col) : zero;
+    one(r, qa, ga);
   }
 }
 
@@ -701,6 +717,37 @@ __global__ void split_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __
   }
 }
 
+// Split-precision operands of the faithfulness product, written straight in the layouts the product reads
+// (three K-phases side by side): x [g, rows, cols] fp32 ->
+//   along_cols = 1: out [g, rows, 3 cols] = [hi | hi | lo] per row   (V: K runs along the columns)
+//   along_cols = 0: out [g, 3 rows, cols] = [hi ; lo ; hi]           (U: K runs along the rows)
+__global__ void split3_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long g,
+                                   long long rows, long long cols, int along_cols) {
+  const long long quads = cols / 4, per = rows * quads, total = g * per;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long b = i / per, rem = i - b * per, r = rem / quads, c = (rem - r * quads) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(x + (b * rows + r) * cols + c);
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+    const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+    const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - f0.x, v.y - f0.y);
+    const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - f1.x, v.w - f1.y);
+    uint2 hi, lo;
+    hi.x = *reinterpret_cast<const uint32_t*>(&h0); hi.y = *reinterpret_cast<const uint32_t*>(&h1);
+    lo.x = *reinterpret_cast<const uint32_t*>(&l0); lo.y = *reinterpret_cast<const uint32_t*>(&l1);
+    if (along_cols) {
+      __nv_bfloat16* o = out + (b * rows + r) * 3 * cols + c;
+      *reinterpret_cast<uint2*>(o) = hi;
+      *reinterpret_cast<uint2*>(o + cols) = hi;
+      *reinterpret_cast<uint2*>(o + 2 * cols) = lo;
+    } else {
+      __nv_bfloat16* o = out + (b * 3 * rows + r) * cols + c;
+      *reinterpret_cast<uint2*>(o) = hi;
+      *reinterpret_cast<uint2*>(o + rows * cols) = lo;
+      *reinterpret_cast<uint2*>(o + 2 * rows * cols) = hi;
+    }
+  }
+}
 
 // out[c] += sum over rows of x[row, c] (bf16 in, fp32 out). Same tiling as the activity kernel.
 __global__ void colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long long rows,
@@ -851,8 +898,11 @@ extern "C" int pd_ci_squash_activity_bwd(const void* pre, const void* dlower, co
                                          void* stream) {
   if (C % 8 != 0) return 5;
   const float g2 = gamma * gamma;
-  ci_squash_activity_bwd_kernel<<<blocks_for(rows * (C / 8), kThreads), kThreads, 0,
-                                  static_cast<cudaStream_t>(stream)>>>(
+  const int gx = (C + 255) / 256;
+  long long gy = (148 * 8 + gx - 1) / gx;
+  if (gy > (rows + 7) / 8) gy = (rows + 7) / 8;
+  if (gy < 1) gy = 1;
+  ci_squash_activity_bwd_kernel<<<dim3(gx, static_cast<unsigned>(gy)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(dlower), dcol,
       static_cast<__nv_bfloat16*>(dpre), rows, C, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
   return PD_CHECK_LAUNCH();
@@ -901,6 +951,14 @@ extern "C" int pd_philox_uniform(float* out, long long rows, int cols, unsigned 
 extern "C" int pd_split_bf16(const float* x, void* hi, void* lo, long long n, void* stream) {
   split_bf16_kernel<<<blocks_for(n, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       x, static_cast<__nv_bfloat16*>(hi), static_cast<__nv_bfloat16*>(lo), n);
+  return PD_CHECK_LAUNCH();
+}
+
+extern "C" int pd_split3_bf16(const float* x, void* out, long long g, long long rows, long long cols,
+                              int along_cols, void* stream) {
+  if (cols % 4 != 0 || g <= 0 || rows <= 0) return 5;
+  split3_bf16_kernel<<<blocks_for(g * rows * (cols / 4), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, static_cast<__nv_bfloat16*>(out), g, rows, cols, along_cols);
   return PD_CHECK_LAUNCH();
 }
 

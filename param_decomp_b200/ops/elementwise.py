@@ -309,6 +309,18 @@ def split_bf16(x: Tensor) -> tuple[Tensor, Tensor]:
     return hi, lo
 
 
+def split3_bf16(x: Tensor, along_cols: bool) -> Tensor:
+    """Split-precision copy of `x [g, rows, cols]` fp32 (`x = hi + lo` in bf16) laid out as three K-phases:
+    `[g, rows, 3 cols] = [hi | hi | lo]` (`along_cols`) or `[g, 3 rows, cols] = [hi ; lo ; hi]`."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 3 and x.shape[2] % 4 == 0
+    g, rows, cols = x.shape
+    out = torch.empty((g, rows, 3 * cols) if along_cols else (g, 3 * rows, cols), device=x.device, dtype=torch.bfloat16)
+    lib = _lib()
+    lib.pd_split3_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int, C.c_void_p]
+    _check(lib.pd_split3_bf16(x.data_ptr(), out.data_ptr(), g, rows, cols, int(along_cols), _s()), "split3_bf16")
+    return out
+
+
 def colsum_bf16(x: Tensor) -> Tensor:
     """Column sums of a `[..., rows, C]` bf16 tensor in fp32: `[..., C]` (one read, no fp32 copy)."""
     assert x.dtype == torch.bfloat16 and x.is_contiguous()

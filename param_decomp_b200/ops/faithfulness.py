@@ -18,7 +18,7 @@ from torch import Tensor
 
 from param_decomp_b200.core.components import ComponentStacks
 from param_decomp_b200.ops import native as nv
-from param_decomp_b200.ops.elementwise import split_bf16
+from param_decomp_b200.ops.elementwise import split3_bf16, split_bf16
 
 
 def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host: dict[str, float], coeff: float,
@@ -39,8 +39,14 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
     for gname, members in stacks.groups.items():
         key = stacks.param_key(gname)
         pV, pU = stacks.V[key], stacks.U[key]
+        V3 = U3 = None
         if hi_lo is not None:
             (Vh, Vl), (Uh, Ul) = hi_lo["V/" + key], hi_lo["U/" + key]
+        elif pV.dim() == 3 and pV.shape[-1] % 8 == 0 and pU.shape[-1] % 8 == 0:
+            # dense stacks: one pass writes the three K-phases side by side; hi parts are views of them
+            C_ = pV.shape[-1]
+            V3, U3 = split3_bf16(pV.detach(), along_cols=True), split3_bf16(pU.detach(), along_cols=False)
+            Vh, Vl, Uh, Ul = V3[..., :C_], V3[..., 2 * C_:], U3[:, :C_], U3[:, C_:2 * C_]
         else:
             Vh, Vl = split_bf16(pV.detach())
             Uh, Ul = split_bf16(pU.detach())
@@ -61,8 +67,11 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
                               -2.0 * coeff * world / (n_sites * w_sq_host[s.name]))
                 k += 1
                 continue
-            U_cat = torch.cat([Uh[i], Ul[i], Uh[i]], dim=0)  # [3C, d_out]
-            V_cat = torch.cat([Vh[i], Vh[i], Vl[i]], dim=1)  # [d_in, 3C]
+            if V3 is not None:
+                U_cat, V_cat = U3[i], V3[i]
+            else:
+                U_cat = torch.cat([Uh[i], Ul[i], Uh[i]], dim=0)  # [3C, d_out]
+                V_cat = torch.cat([Vh[i], Vh[i], Vl[i]], dim=1)  # [d_in, 3C]
             D = torch.empty(s.d_out, s.d_in, device=dev, dtype=torch.bfloat16)
             r = row_of[s.name]
             nv.gemm(U_cat, V_cat, D, a_mn=True, epi=nv.EPI_FAITH, ci=Wb, dci=sumsq[r:r + 1])
