@@ -194,6 +194,8 @@ def run_decomposition_training(
     state_out: list | None = None,
     shard_group: Any = None,
     shard_backend: str | None = None,
+    remat_recon_forwards: bool = False,
+    remat_ci_fn: bool = False,
 ) -> RunResult:
     collectives = collectives or DataCollectives()
     log = get_logger(collectives.rank)
@@ -204,7 +206,8 @@ def run_decomposition_training(
 
         expert_shard = ExpertSharding.for_model(model)
     ctx = StepContext.build(model, objective, pd, collectives=collectives, lazy_masks=lazy_masks, nontarget=nontarget,
-                            expert_shard=expert_shard)
+                            expert_shard=expert_shard, remat_recon_forwards=remat_recon_forwards,
+                            remat_ci_fn=remat_ci_fn)
     rows = batch_rows if batch_rows is not None else pd.batch_size // collectives.world_size
     state = init_train_state(model, ci_fn, pd, objective, device, rows, positions,
                              use_fused_optim=use_fused_optim, init_components=init_components,

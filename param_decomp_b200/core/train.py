@@ -95,6 +95,10 @@ class StepContext:
     nontarget: NontargetObjective | None = None
     relative_faithfulness: bool = True
     expert_shard: Any = None  # parallel.expert_shard.ExpertSharding when expert blocks are split over ranks
+    # activation recompute (param_decomp/targets/transformer.py:1910-1918, experiments/lm/runtime.py:340-360):
+    # a masked forward / the CI function keeps only its inputs and is run again during the backward pass
+    remat_recon_forwards: bool = False
+    remat_ci_fn: bool = False
 
     def weights_sq_host(self) -> dict[str, float]:
         """`||W_s||^2` as host floats (read back once, then cached)."""
@@ -294,8 +298,16 @@ def _fusable_pre(v) -> bool:
 
 
 def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: int | None = None) -> CI:
-    pre = state.ci_fn(clean.taps, aux=clean.aux, components=state.components,
-                      segment_ids=clean.aux.get("segment_ids"), positions=clean.aux.get("positions"))
+    def ci_forward():
+        return state.ci_fn(clean.taps, aux=clean.aux, components=state.components,
+                           segment_ids=clean.aux.get("segment_ids"), positions=clean.aux.get("positions"))
+
+    if ctx.remat_ci_fn and torch.is_grad_enabled():
+        from torch.utils.checkpoint import checkpoint
+
+        pre = checkpoint(ci_forward, use_reentrant=False)
+    else:
+        pre = ci_forward()
     cfg = ctx.objective.minimality
     fusable = (step is not None and ctx.lazy_masks and isinstance(cfg, L.ImportanceMinimalityLossConfig)
                and all(_fusable_pre(v) for v in pre.values()))
@@ -427,7 +439,17 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         vals_e2e, vals_full = [], []
         for draw in range(term.n_samples):
             masks = build_masks(ctx, term, ci_lower, key, draw, leaves, state, step)
-            e2e, full = masked_recon(ctx, weights, batch, clean, masks, term, step, with_aux=True, metrics=metrics)
+            if ctx.remat_recon_forwards and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+
+                # masks are counter-based (same draw on the second run); the closure's tensors are tracked by
+                # the checkpoint's saved-tensor hooks, so nothing of the forward stays alive until backward
+                aux_metrics: dict[str, Tensor] = {}
+                e2e, full = checkpoint(lambda m=masks, am=aux_metrics: masked_recon(
+                    ctx, weights, batch, clean, m, term, step, with_aux=True, metrics=am), use_reentrant=False)
+                metrics.update({k: v.detach() for k, v in aux_metrics.items()})
+            else:
+                e2e, full = masked_recon(ctx, weights, batch, clean, masks, term, step, with_aux=True, metrics=metrics)
             vals_e2e.append(e2e)
             vals_full.append(full)
         e2e_mean = torch.stack(vals_e2e).mean()

@@ -72,7 +72,8 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
             max_steps_this_entry=max_steps_this_entry, state_out=state_out,
             profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
-            shard_group=shard_group, shard_backend=shard_backend)
+            shard_group=shard_group, shard_backend=shard_backend,
+            remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn)
     finally:
         if sink is not None:
             sink.close()
@@ -123,6 +124,7 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
         return run_decomposition_training(
             run.model, run.ci_fn, cfg.pd, cfg.cadence, sample_target, device=topo.device, run_dir=run_dir, sink=sink,
             evaluation=evaluation, collectives=topo.collectives(), nontarget=nontarget,
+            remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn,
             sample_nontarget_batch=sample_nontarget, batch_rows=max(cfg.pd.batch_size, nt_rows) // topo.data_world,
             positions=max(pool.seq_len, cfg.data.seq_len), units_per_step=(cfg.pd.batch_size * pool.seq_len
                                                                           + nt_rows * cfg.data.seq_len),

@@ -168,3 +168,42 @@ def test_nonlinearity_aligned_init_is_rank_one_slices_of_w():
     nonlinearity_aligned_init(st, m, 0)
     # C == d_ff and every neuron covered once: the components sum to W exactly
     assert torch.allclose(st.weight(name), w[name + ".weight"], atol=1e-5)
+
+
+def test_activation_recompute_changes_nothing_but_memory():
+    """`runtime.remat_recon_forwards` / `remat_ci_fn`: every masked forward and the CI function are run again
+    in the backward pass instead of keeping their activations; losses and gradients are the same."""
+    import copy
+
+    import torch
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+    from param_decomp_b200.core.objective import build_objective
+    from param_decomp_b200.core.run import init_train_state
+    from param_decomp_b200.core.train import StepContext, train_step
+    from param_decomp_b200.experiments.lm.build import build_lm_run
+
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"]["backend"] = "eager_torch"
+    c["target"]["weights_dtype"] = "float32"
+    c["target"]["attention_implementation"] = "xla"
+    c["target"]["spec"]["arch"] = {"family": "glu_transformer", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 48,
+                                   "vocab_size": 100}
+    c["decomposition"]["sites"]["cs"] = {"q": 16, "o": 16, "gate": 24, "down": 16}
+    c["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [16]}
+    c["data"]["seq_len"] = 8
+    cfg = LMExperimentConfig.model_validate(c)
+    out = {}
+    for remat in (False, True):
+        run = build_lm_run(cfg, None, "cpu")
+        obj = build_objective(cfg.pd)
+        ctx = StepContext.build(run.model, obj, cfg.pd, remat_recon_forwards=remat, remat_ci_fn=remat)
+        st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, "cpu", cfg.pd.batch_size, cfg.data.seq_len)
+        m = train_step(ctx, st, run.sample_train(0))
+        out[remat] = ({k: float(v) for k, v in m.items() if k.startswith("loss/") or k.startswith("grad_norm/")},
+                      [p.detach().clone() for p in st.components.parameters()],
+                      [p.detach().clone() for p in st.ci_fn.parameters()])
+    assert out[False][0] == pytest.approx(out[True][0], rel=1e-6)
+    for a, b in zip(out[False][1] + out[False][2], out[True][1] + out[True][2]):
+        assert torch.allclose(a, b, atol=1e-7)
