@@ -30,6 +30,15 @@ def optimizer_sharding(cfg: LMExperimentConfig | LMTargetedExperimentConfig, top
     return topo.data_group, backend
 
 
+def check_runtime_supported(cfg) -> None:
+    """Refuse, rather than silently ignore, runtime options this engine does not act on."""
+    if cfg.runtime.sequence_sharding != "replicate":
+        raise NotImplementedError(
+            "runtime.sequence_sharding=sequence_parallel (position-sharded residual stream between sublayers, "
+            "param_decomp/core/placement.py:273-287) is not implemented: the tp axis sums site / expert outputs "
+            "with an all-reduce and keeps the residual stream whole on every rank")
+
+
 def expert_group_of(topo):
     """The mesh's `tp` axis is the expert-shard axis of a mixture-of-experts target
     (param_decomp/core/placement.py:1040-1048: blocked sites place `expert -> tp`)."""
@@ -40,6 +49,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
              max_steps_this_entry: int | None = None, state_out: list | None = None) -> RunResult:
     from param_decomp_b200.parallel import topology
 
+    check_runtime_supported(cfg)
     topo = topology.initialize(cfg.runtime.mesh, device)
     log = get_logger(topo.rank)
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
@@ -91,6 +101,7 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
     from param_decomp_b200.experiments.lm.targeted_data import PromptPool
     from param_decomp_b200.parallel import topology
 
+    check_runtime_supported(cfg)
     topo = topology.initialize(cfg.runtime.mesh, device)
     log = get_logger(topo.rank)
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
