@@ -102,6 +102,9 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=1,
                     help="size of the mesh's tp axis (ranks of one tp group see the same tokens and split the experts "
                          "of a mixture-of-experts target or every site's component axis of a dense one)")
+    ap.add_argument("--expert-dispatch", type=str, default="allreduce", choices=["allreduce", "all_to_all"],
+                    help="with --tp on a mixture-of-experts target: tokens replicated over the tp group and partial "
+                         "outputs summed, or the batch sharded over it too and jobs stored into their expert's owner")
     ap.add_argument("--kernel-table", type=Path, default=None,
                     help="after the timed steps, run one more step under the torch profiler and write the kernels "
                          "ranked by device time to this file (never part of a reported number)")
@@ -128,9 +131,10 @@ def main() -> None:
     pd = cfg.pd if args.batch is None else cfg.pd.model_copy(update={"batch_size": args.batch})
     cfg = cfg.model_copy(update={"pd": pd})
     assert world % args.tp == 0, f"--tp {args.tp} does not divide {world} GPUs"
-    topo = topology.initialize(HsdpMeshShape(replicate=1, fsdp=world // args.tp, tp=args.tp), "cuda")
+    topo = topology.initialize(HsdpMeshShape(replicate=1, fsdp=world // args.tp, tp=args.tp), "cuda",
+                               batch_over_tp=args.expert_dispatch == "all_to_all")
     run = build_lm_run(cfg, None, topo.device, topo.data_rank, topo.data_world,
-                       expert_group=topo.groups.get("tp") if args.tp > 1 else None)
+                       expert_group=topo.groups.get("tp") if args.tp > 1 else None, expert_mode=args.expert_dispatch)
     objective = build_objective(cfg.pd)
     expert_shard = None
     if args.tp > 1:
@@ -225,7 +229,7 @@ def main() -> None:
                           + (f" experts{arch.n_experts} top{arch.experts_per_token}" if arch.family == "moe" else "")),
                 "config_file": str(args.config.relative_to(ROOT)) if args.config.is_relative_to(ROOT) else str(args.config),
                 "global_batch": cfg.pd.batch_size, "seq_len": cfg.data.seq_len,
-                "parallelism": ((f"dp{topo.data_world}" + (f" x tp{args.tp}" if args.tp > 1 else "")
+                "parallelism": ((f"dp{topo.data_world}" + (f" x tp{args.tp}" + (f" {args.expert_dispatch}" if run.ep is not None else "") if args.tp > 1 else "")
                                  + f" ({'zero1 ' + args.optim if shard_backend else 'ddp all-reduce'})")
                                 if world > 1 else "single"),
                 "decomposition": (", ".join(f"{k}:{v}" for k, v in cfg.decomposition.sites.cs.items())

@@ -238,7 +238,7 @@ def run_decomposition_training(
     def save() -> None:
         if saving and expert_shard is not None:
             # the ranks of one expert group (the first data shard's) assemble the global stacks; rank 0 writes
-            if getattr(collectives, "data_rank", 0) == 0:
+            if collectives.in_first_tp_group:
                 ckpt.save_state(run_dir, state, keep, expert_shard=expert_shard, write=collectives.rank == 0)  # type: ignore[arg-type]
         elif saving and collectives.rank == 0:
             ckpt.save_state(run_dir, state, keep)  # type: ignore[arg-type]

@@ -68,6 +68,13 @@ class DataCollectives:
         """Average `.grad` over EVERY rank of the job (leaves replicated over the non-batch axes too)."""
         self.reduce_grads(params)
 
+    def reduce_split_grads(self, params: list[Tensor]) -> None:
+        """Average `.grad` of leaves that are split over the tp axis (see the distributed implementation)."""
+        self.reduce_grads(params)
+
+    in_first_tp_group: bool = True
+    split_grad_scale: float = 1.0  # see `DistCollectives.split_grad_scale`
+
 
 @dataclass
 class TrainState:
@@ -397,6 +404,10 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
             whole = (terms.detach() * ~split).sum() + shard.sum_over_group((terms.detach() * split).sum())
             metrics["loss/" + obj.faith.instance_key] = whole / len(state.components.sites)
             unseen = c_f * (whole / len(state.components.sites) - faith.detach())  # other ranks' experts
+            k = ctx.collectives.split_grad_scale
+            if k != 1.0:  # batch-independent term on split leaves: cancel the batch-shard division of their gradients
+                faith_g = (terms * torch.where(split, k, 1.0)).mean()
+                faith = faith.detach() + (faith_g - faith_g.detach())
             add(c_f * faith)
         elif direct and ctx.relative_faithfulness and fused_faith.blocked_supported(state.components):
             fused_faithfulness = fused_faith.fused_faithfulness
@@ -480,7 +491,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         opt = state.components_opt
         split = [p for n, p in zip(opt.names, opt.params) if ctx.expert_shard.is_split(n)]
         whole = [p for n, p in zip(opt.names, opt.params) if not ctx.expert_shard.is_split(n)]
-        ctx.collectives.reduce_grads(split)
+        ctx.collectives.reduce_split_grads(split)
         ctx.collectives.reduce_grads_everywhere(whole + state.ci_fn_opt.params)
     else:
         ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params) + state.ci_fn_opt.params)

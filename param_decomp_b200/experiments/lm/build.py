@@ -83,7 +83,8 @@ def build_ci_fn(cfg: Any, model: Any, seed: int) -> nn.Module:
 
 
 def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_root: Path | None,
-                 device: torch.device | str, rank: int = 0, world: int = 1, expert_group: Any = None) -> LMRun:
+                 device: torch.device | str, rank: int = 0, world: int = 1, expert_group: Any = None,
+                 expert_mode: str = "allreduce") -> LMRun:
     """`rank`/`world` index the batch axes (data shards). `expert_group`: the process group of the mesh's
     `tp` axis, whose ranks see the same tokens; on a mixture-of-experts target they split the experts (and
     their component blocks, param_decomp/routed/experts.py:28-40), on a dense target every site's component
@@ -93,7 +94,11 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
     if expert_group is not None and arch.family in ("moe", "qwen35_moe"):
         from param_decomp_b200.parallel.ep import ExpertParallel
 
-        ep = ExpertParallel(expert_group, arch.n_experts, mode="allreduce")
+        on_gpu = torch.device(device).type == "cuda" and cfg.runtime.backend == "fused_sm100"
+        # `all_to_all`: the batch is sharded over the group too and jobs travel to their expert's owner (by
+        # direct peer stores on GPUs); `allreduce`: the reference's scheme, tokens replicated over the group
+        ep = ExpertParallel(expert_group, arch.n_experts, mode=expert_mode,
+                            transport="p2p" if (expert_mode == "all_to_all" and on_gpu) else "collective")
     sites_cfg = cfg.decomposition.sites
     edge = cfg.target.output_edge
     n_chunks = edge.n_vocab_chunks if isinstance(edge, X.StreamedOutputEdgeConfig) else None
@@ -111,6 +116,7 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
         model = tf.TransformerDecomposedModel(arch, weights, site_cs, backend=backend,
                                               attention=cfg.target.attention_implementation, n_vocab_chunks=n_chunks)
     if expert_group is not None and ep is None:
+        assert expert_mode != "all_to_all", "all_to_all dispatch applies to mixture-of-experts targets"
         model.split_components(expert_group)  # dense target: the tp axis divides every site's component axis
     ci_fn = build_ci_fn(cfg.decomposition.ci, model, cfg.pd.seed)
     if backend == "fused_sm100":

@@ -39,6 +39,12 @@ def check_runtime_supported(cfg) -> None:
             "with an all-reduce and keeps the residual stream whole on every rank")
 
 
+def expert_mode_of(cfg) -> str:
+    """`target.expert_implementation: all_to_all` selects token dispatch to the experts' owners (the batch is then
+    sharded over the tp axis as well); every other value keeps the reference's activation slicing."""
+    return "all_to_all" if getattr(cfg.target, "expert_implementation", "") == "all_to_all" else "allreduce"
+
+
 def expert_group_of(topo):
     """The mesh's `tp` axis is the expert-shard axis of a mixture-of-experts target
     (param_decomp/core/placement.py:1040-1048: blocked sites place `expert -> tp`)."""
@@ -50,9 +56,11 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     from param_decomp_b200.parallel import topology
 
     check_runtime_supported(cfg)
-    topo = topology.initialize(cfg.runtime.mesh, device)
+    mode = expert_mode_of(cfg)
+    topo = topology.initialize(cfg.runtime.mesh, device, batch_over_tp=mode == "all_to_all")
     log = get_logger(topo.rank)
-    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
+    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
+                       expert_mode=mode)
     collectives = topo.collectives()
     shard_group, shard_backend = optimizer_sharding(cfg, topo)
     if run.ep is not None or getattr(run.model, "component_group", None) is not None:
@@ -102,9 +110,11 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
     from param_decomp_b200.parallel import topology
 
     check_runtime_supported(cfg)
-    topo = topology.initialize(cfg.runtime.mesh, device)
+    mode = expert_mode_of(cfg)
+    topo = topology.initialize(cfg.runtime.mesh, device, batch_over_tp=mode == "all_to_all")
     log = get_logger(topo.rank)
-    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo))
+    run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
+                       expert_mode=mode)
     pool = PromptPool.build(cfg.prompts, run.arch.vocab_size, data_root, cfg.pd.seed, encode=encode)
     n_target_terms = len(build_objective(cfg.pd).recon)
     nontarget = build_nontarget_objective(cfg.nontarget, first_index=n_target_terms)

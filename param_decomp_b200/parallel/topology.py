@@ -87,7 +87,7 @@ class DistCollectives(DataCollectives):
         latency: 256 MiB)."""
         group = self.topo.data_group if group == "data" else group
         world = self.world_size if world is None else world
-        if world == 1:
+        if world == 1 or self.topo.world == 1:
             return
         grads = [p.grad for p in params if p.grad is not None]
         bucket, size, limit = [], 0, 64 * 1024 * 1024  # elements
@@ -115,6 +115,27 @@ class DistCollectives(DataCollectives):
                 flush()
         flush()
 
+    @property
+    def in_first_tp_group(self) -> bool:
+        """Ranks `0 .. tp-1` (tp is the fastest axis): the one tp group that assembles split stacks for a save."""
+        return self.topo.rank < self.topo.tp_world
+
+    @property
+    def split_grad_scale(self) -> float:
+        """Factor for batch-independent loss terms on split leaves: `reduce_split_grads` divides by the number of
+        batch shards, of which only `1 / tp` contributed such a term to a given part."""
+        return float(self.topo.tp_world) if self.topo.batch_over_tp else 1.0
+
+    def reduce_split_grads(self, params: list[Tensor]) -> None:
+        """Gradients of leaves that are split over the tp axis (each rank holds its own part). When the batch
+        is replicated over tp they average over the batch axes like everything else. When the batch is also
+        sharded over tp (all-to-all expert dispatch) a part's gradient already holds the sum over its tp group's
+        tokens: sum over the ranks holding the same part, divide by the number of batch shards (all ranks)."""
+        if self.topo.batch_over_tp:
+            self.reduce_grads(params, group=self.topo.replica_group, world=self.topo.world)
+        else:
+            self.reduce_grads(params)
+
     def host_any(self, flag: float) -> bool:
         if self.topo.world == 1:
             return bool(flag)
@@ -139,6 +160,8 @@ class Topology:
     data_group: Any = None
     cpu_group: Any = None
     owns_process_group: bool = False
+    batch_over_tp: bool = False  # True: the batch is sharded over the tp axis as well (all-to-all expert dispatch)
+    replica_group: Any = None  # ranks sharing this rank's tp coordinate (they hold the same split parts)
 
     @property
     def tp_world(self) -> int:
@@ -150,11 +173,11 @@ class Topology:
 
     @property
     def data_world(self) -> int:
-        return self.world // self.tp_world
+        return self.world if self.batch_over_tp else self.world // self.tp_world
 
     @property
     def data_rank(self) -> int:
-        return self.rank // self.tp_world
+        return self.rank if self.batch_over_tp else self.rank // self.tp_world
 
     def axis_size(self, name: str) -> int:
         return dict(self.axes).get(name, 1)
@@ -176,7 +199,7 @@ class Topology:
 
 
 def initialize(shape: HsdpMeshShape | ResidentMeshShape | None, device: str | None = None,
-               timeout_s: float = 600.0) -> Topology:
+               timeout_s: float = 600.0, batch_over_tp: bool = False) -> Topology:
     """Join the job named by `RANK/WORLD_SIZE/LOCAL_RANK/MASTER_*` (single process if unset) and
     build one process group per mesh axis plus the data (batch-axes) group and a gloo group."""
     env_world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -229,4 +252,8 @@ def initialize(shape: HsdpMeshShape | ResidentMeshShape | None, device: str | No
         g = dist.new_group(ranks=list(members))
         if rank in members:
             topo.data_group = g
+    topo.replica_group = topo.data_group
+    if batch_over_tp and topo.tp_world > 1:
+        topo.batch_over_tp = True
+        topo.data_group = dist.new_group(ranks=list(range(env_world)))  # every rank takes its own batch rows
     return topo

@@ -7,6 +7,7 @@ import socket
 import tempfile
 from pathlib import Path
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -19,7 +20,7 @@ STEPS = 4
 SPLIT_ID, SINGLE_ID = "p-0000aaaa", "p-0000bbbb"
 
 
-def _cfg(tp: int) -> LMExperimentConfig:
+def _cfg(tp: int, mode: str = "allreduce") -> LMExperimentConfig:
     c = copy.deepcopy(ge.SMOKE_CONFIG)
     c["runtime"]["backend"] = "eager_torch"
     c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
@@ -36,6 +37,8 @@ def _cfg(tp: int) -> LMExperimentConfig:
     c["pd"]["steps"] = STEPS
     c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "periodic", "save_every": 2, "retention": {"kind": "keep_all"}}}
     c["eval"] = None
+    if mode == "all_to_all":
+        c["target"]["expert_implementation"] = "all_to_all"
     return LMExperimentConfig.model_validate(c)
 
 
@@ -53,11 +56,11 @@ def _train(cfg, root: Path, run_id: str, max_steps=None):
     return res, states[0]
 
 
-def _worker(rank: int, world: int, port: int, root: str, out):
+def _worker(rank: int, world: int, port: int, root: str, mode: str, out):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
     torch.manual_seed(0)
-    res, state = _train(_cfg(world), Path(root), SPLIT_ID)
+    res, state = _train(_cfg(world, mode), Path(root), SPLIT_ID)
     shard = state.expert_shard
     assert shard is not None and shard.world == world
     local = {n: p.detach().clone() for n, p in state.components.named_parameters()}
@@ -66,21 +69,26 @@ def _worker(rank: int, world: int, port: int, root: str, out):
     assert not dist.is_initialized()  # train_lm tears its own process group down
 
 
-def test_expert_split_engine_matches_single_process():
+@pytest.mark.parametrize("mode", ["allreduce", "all_to_all"])
+def test_expert_split_engine_matches_single_process(mode):
+    """`allreduce`: tokens replicated over the pair; `all_to_all`: each rank takes half of the batch and jobs
+    travel to their expert's owner (`target.expert_implementation: all_to_all`)."""
     from safetensors import safe_open
 
     with tempfile.TemporaryDirectory() as root:
         world, port = 2, _free_port()
         out = mp.Manager().dict()
-        mp.spawn(_worker, args=(world, port, root, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, root, mode, out), nprocs=world, join=True)
 
         res, ref = _train(_cfg(1), Path(root), SINGLE_ID)
         ref_params = dict(ref.components.named_parameters())
         for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss",
                   "grad_norm/components", "grad_norm/ci_fn"):
-            for r in range(world):
-                got, want = out[r][0]["train/" + k], res.last_metrics["train/" + k]
-                assert abs(got - want) <= 2e-4 * abs(want) + 1e-7, (k, r, got, want)
+            got = sum(out[r][0]["train/" + k] for r in range(world)) / world  # (per-rank batch shards under all_to_all)
+            want = res.last_metrics["train/" + k]
+            assert abs(got - want) <= 2e-4 * abs(want) + 1e-7, (k, got, want)
+            if mode == "allreduce":
+                assert abs(out[0][0]["train/" + k] - out[1][0]["train/" + k]) <= 1e-5 * abs(want) + 1e-8
         for r in range(world):
             _, local, lo, n_real, ci_params = out[r]
             for name, p in local.items():
