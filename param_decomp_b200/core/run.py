@@ -160,6 +160,8 @@ def _resolve_start(run_dir: Path | None, state: TrainState, cadence: Cadence,
     if provenance is not None:
         ckpt.restore_decomposition(provenance.parent_run_dir, provenance.parent_step, state.components, state.ci_fn,
                                    getattr(state, "expert_shard", None))
+        if hasattr(state.components_opt, "sync_from_parameters"):
+            state.components_opt.sync_from_parameters()
         log.info("fine-tune: loaded V/U + CI fn from %s step %d", provenance.parent_run_dir, provenance.parent_step)
         return "finetune"
     return "fresh"
@@ -220,6 +222,8 @@ def run_decomposition_training(
         last = faithfulness_warmup(ctx, state, pd.faithfulness_warmup_steps, pd.faithfulness_warmup_lr,
                                    pd.faithfulness_warmup_weight_decay,
                                    log=lambda i, v: log.info("faithfulness warm-up %d: %.3e", i, v))
+        if hasattr(state.components_opt, "sync_from_parameters"):
+            state.components_opt.sync_from_parameters()  # the warm-up stepped the parameters' own storage
         log.info("faithfulness warm-up done (%.3e)", last)
 
     own_sink = sink is None and run_dir is not None
@@ -235,7 +239,18 @@ def run_decomposition_training(
     if saving and isinstance(cadence.checkpointing.retention, KeepLastNCheckpoints):  # type: ignore[union-attr]
         keep = cadence.checkpointing.retention.n  # type: ignore[union-attr]
 
+    def sync_masters(for_save: bool) -> None:
+        """A sharded optimizer keeps each rank's slice of the masters: before anything reads the parameters
+        (evaluation, checkpoint) gather them - and, for a save, the moments - on every rank."""
+        opt = state.components_opt
+        if for_save and hasattr(opt, "gather_state"):
+            opt.gather_state()
+        elif hasattr(opt, "refresh_full_fp32"):
+            opt.refresh_full_fp32()
+
     def save() -> None:
+        if saving:
+            sync_masters(for_save=True)
         if saving and expert_shard is not None:
             # the ranks of one expert group (the first data shard's) assemble the global stacks; rank 0 writes
             if collectives.in_first_tp_group:
@@ -258,6 +273,7 @@ def run_decomposition_training(
     while state.step < pd.steps:
         step = state.step
         if evaluation is not None and evaluation.is_due(step):
+            sync_masters(for_save=False)
             ev = evaluation.run(step, state, ctx)
             if sink is not None and ev:
                 sink.log(step, ev, prefix="eval/")
@@ -302,6 +318,7 @@ def run_decomposition_training(
 
     if state.step >= pd.steps:
         if evaluation is not None and evaluation.is_due(state.step):
+            sync_masters(for_save=False)
             ev = evaluation.run(state.step, state, ctx)
             if sink is not None and ev:
                 sink.log(state.step, ev, prefix="eval/")

@@ -233,13 +233,53 @@ class ShardedFlatAdamW:
         else:
             self.full_fp32.copy_(self.master)
 
+    def _gather_flat(self, shard: Tensor) -> Tensor:
+        if self.world == 1:
+            return shard.clone()
+        full = torch.empty(self.n, device=shard.device, dtype=shard.dtype)
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        return full
+
+    def gather_state(self) -> None:
+        """Collective (every rank of the group): assemble the moments of all shards so that `state_dict` -
+        which only the writing rank calls - can return them per parameter. Masters are gathered into the
+        parameters' own storage at the same time."""
+        self.refresh_full_fp32()
+        self._gathered = (self._gather_flat(self.mu), self._gather_flat(self.nu))
+
     def state_dict(self) -> dict[str, Tensor]:
-        return {"master": self.master, "mu": self.mu, "nu": self.nu,
-                "count": torch.tensor(self.count, dtype=torch.int64)}
+        """Per-parameter moments under the replicated optimizer's key grammar (`V.<key>/mu`, `.../nu`), so a
+        checkpoint does not depend on how many ranks shared the optimizer state."""
+        if self.world > 1:
+            assert getattr(self, "_gathered", None) is not None, "call gather_state() on every rank before saving"
+            mu, nu = self._gathered
+            self._gathered = None
+        else:
+            mu, nu = self.mu, self.nu
+        out: dict[str, Tensor] = {"count": torch.tensor(self.count, dtype=torch.int64)}
+        for n, p, o in zip(self.names, self.params, self.offsets):
+            key = n.replace("/", ".", 1)
+            out[key + "/mu"] = mu[o:o + p.numel()].view_as(p).clone()
+            out[key + "/nu"] = nu[o:o + p.numel()].view_as(p).clone()
+        return out
 
     def load_state_dict(self, sd: dict[str, Tensor]) -> None:
-        self.master.copy_(sd["master"])
-        self.mu.copy_(sd["mu"])
-        self.nu.copy_(sd["nu"])
+        """Moments from the per-parameter entries; masters and working copies from the parameters' storage
+        (restored before this call)."""
         self.count = int(sd["count"].item())
-        self.work_flat[self.shard_off:self.shard_off + self.shard_len].copy_(self.master)
+        sl = slice(self.shard_off, self.shard_off + self.shard_len)
+        for suffix, dst in (("mu", self.mu), ("nu", self.nu)):
+            full = torch.zeros(self.n, device=dst.device, dtype=torch.float32)
+            for n, p, o in zip(self.names, self.params, self.offsets):
+                v = sd.get(n.replace("/", ".", 1) + "/" + suffix)
+                if v is not None:
+                    full[o:o + p.numel()].copy_(v.reshape(-1))
+            dst.copy_(full[sl])
+        self.sync_from_parameters()
+
+    def sync_from_parameters(self) -> None:
+        """Adopt the values currently in the parameters' storage (after a restore or an in-place edit)."""
+        self.master.copy_(self.full_fp32[self.shard_off:self.shard_off + self.shard_len])
+        self.work_flat.copy_(self.full_fp32)
+        if self.work_lo_flat is not None:
+            self.work_lo_flat.copy_(self.full_fp32 - self.work_flat.float())
