@@ -504,7 +504,12 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     metrics["schedules/lr_ci_fn"] = torch.tensor(info_f["lr"])
 
     if isinstance(ctx.pd, TargetedPDConfig) and ctx.pd.ci_scaled_weight_decay is not None:
+        opt = state.components_opt
+        if hasattr(opt, "refresh_full_fp32"):  # sharded masters: edit the gathered values, then re-adopt them
+            opt.refresh_full_fp32()
         _ci_scaled_weight_decay(ctx, state, ci, info_c["lr"], ctx.pd.ci_scaled_weight_decay)
+        if hasattr(opt, "sync_from_parameters"):
+            opt.sync_from_parameters()
 
     final_key = StepKey(ctx.pd.seed ^ 0x51C, step)
     for term, grads in final_grads:
