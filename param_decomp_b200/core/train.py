@@ -316,7 +316,9 @@ def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: i
     else:
         pre = ci_forward()
     cfg = ctx.objective.minimality
+    needs_upper = isinstance(ctx.pd, TargetedPDConfig) and ctx.pd.ci_scaled_weight_decay is not None
     fusable = (step is not None and ctx.lazy_masks and isinstance(cfg, L.ImportanceMinimalityLossConfig)
+               and not needs_upper  # (the fused pass emits lower importances + activity, no upper tensor)
                and all(_fusable_pre(v) for v in pre.values()))
     if fusable:
         from param_decomp_b200.core.ci_fn.interface import squash_fused
