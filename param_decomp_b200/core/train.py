@@ -372,10 +372,14 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         else:
             p.grad = None
     working = None
-    if sharded:
+    if sharded and direct:
         opt = state.components_opt
         working = {n: opt.working_view(i) for i, n in enumerate(opt.names)}
-    weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct or sharded,
+    elif sharded:
+        # eager backend: weight gradients come from autograd, so the forward reads the (gathered) fp32 masters
+        # themselves; their `.grad` are views of the optimizer's flat gradient buffer and accumulate in place
+        state.components_opt.refresh_full_fp32()
+    weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct,
                                       working=working)
     ci = run_ci_fn(ctx, state, clean, step)
     ci_lower = ci.mask_inputs()

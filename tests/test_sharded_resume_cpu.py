@@ -80,6 +80,13 @@ def test_sharded_optimizer_resume_and_layout_independent_checkpoint():
             assert s1 == s2 == STEPS
             for a, b in zip(full, resumed):
                 assert torch.allclose(a, b, atol=1e-6)
+        # the two-rank sharded run follows the single-process run with the replicated optimizer
+        from param_decomp_b200.experiments.lm.training import train_lm
+
+        single: list = []
+        train_lm(_cfg(1), Path(root), run_id="p-00001111", device="cpu", state_out=single)
+        for a, b in zip(out[0][0], single[0].components.parameters()):
+            assert torch.allclose(a, b.detach(), atol=2e-5), float((a - b).abs().max())
         # one process, replicated optimizer, reads the 2-rank checkpoint
         cfg = _cfg(1)
         run = build_lm_run(cfg, None, "cpu")
