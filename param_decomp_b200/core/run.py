@@ -94,7 +94,8 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
     g = torch.Generator().manual_seed(pd.seed)
     components = ComponentStacks(model.sites, stack_multiple)
     if expert_shard is not None:
-        assert shard_backend is None, "expert-split component stacks use the replicated-optimizer layout"
+        assert shard_backend is None or expert_shard.by_component, \
+            "expert-split component stacks use the replicated-optimizer layout"
         expert_shard.init_components(components, g)  # the single-process draw, this rank's expert blocks kept
     else:
         components.init_random(g)
@@ -111,10 +112,10 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
         assert isinstance(pd.components_optimizer, AdamWOptimizerConfig), "the sharded optimizer implements AdamW"
         comp_opt = ShardedFlatAdamW(pd.components_optimizer, ["/".join(n.split(".")) for n, _ in comp_named],
                                     [p for _, p in comp_named], pd.steps, shard_group, backend=shard_backend,
-                                    keep_lo=True)
+                                    keep_lo=True, norm_group=expert_shard.group if expert_shard is not None else None)
     else:
         comp_opt = build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim)
-    if expert_shard is not None:
+    if expert_shard is not None and shard_backend is None:
         comp_opt.norm_fn = expert_shard.grad_norm
     state = TrainState(
         components=components,

@@ -403,6 +403,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
             # the sum over the expert group of the split sites' terms plus the replicated sites' terms
             assert ctx.relative_faithfulness, "expert-split runs use the target-relative faithfulness"
             by_c = shard.by_component
+            if sharded and direct:
+                state.components_opt.refresh_full_fp32()  # the terms below read the fp32 masters
             terms = loss_fns.faithfulness_terms(state.components, ctx.weights_W, ctx.weights_sq,
                                                 component_group=shard.group if by_c else None)
             split = torch.tensor([s.blocked and not by_c for s in state.components.sites], device=terms.device)
@@ -492,8 +494,10 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         final_grads.append((term, {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, gs)}))
 
     total_loss.backward()
-    if ctx.expert_shard is not None:
-        assert not sharded, "expert-split component stacks use the replicated-optimizer layout"
+    if ctx.expert_shard is not None and sharded:
+        assert ctx.expert_shard.by_component, "expert-split component stacks use the replicated-optimizer layout"
+        ctx.collectives.reduce_grads_everywhere(state.ci_fn_opt.params)  # component grads: inside the optimizer step
+    elif ctx.expert_shard is not None:
         opt = state.components_opt
         split = [p for n, p in zip(opt.names, opt.params) if ctx.expert_shard.is_split(n)]
         whole = [p for n, p in zip(opt.names, opt.params) if not ctx.expert_shard.is_split(n)]

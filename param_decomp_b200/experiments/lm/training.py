@@ -63,8 +63,10 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
                        expert_mode=mode)
     collectives = topo.collectives()
     shard_group, shard_backend = optimizer_sharding(cfg, topo)
-    if run.ep is not None or getattr(run.model, "component_group", None) is not None:
-        shard_group, shard_backend = None, None  # split stacks differ per tp rank: replicated-optimizer layout
+    if run.ep is not None:
+        shard_group, shard_backend = None, None  # expert blocks differ per tp rank: replicated-optimizer layout
+    elif getattr(run.model, "component_group", None) is not None and shard_backend is not None:
+        shard_backend = "collective"  # component slices: sharded over the batch axes, clip norm summed over tp
 
     run_dir, sink = None, None
     if data_root is not None:

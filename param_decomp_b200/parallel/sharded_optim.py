@@ -83,6 +83,7 @@ class ShardedFlatAdamW:
     backend: str = "collective"  # "fused_p2p" | "collective"
     wait_limit_s: float = 2.0
     keep_lo: bool = False  # also publish bf16(p - bf16(p)): split-precision operands for faithfulness
+    norm_group: object | None = None  # leaves are slices of stacks split over this group: its ranks' squares add up
     count: int = 0
     applied_learning_rate: float = 0.0
     last_grad_norm_t: Tensor | None = None
@@ -90,6 +91,8 @@ class ShardedFlatAdamW:
     state: dict[str, Tensor] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
+        assert self.norm_group is None or self.backend == "collective", \
+            "the fused kernel computes the clip norm among its own peers; split stacks use the collective form"
         self.world = dist.get_world_size(self.group) if self.group is not None else 1
         self.rank = dist.get_rank(self.group) if self.group is not None else 0
         dev = self.params[0].device
@@ -208,6 +211,8 @@ class ShardedFlatAdamW:
         sumsq = shard.pow(2).sum()
         if self.world > 1:
             dist.all_reduce(sumsq, group=self.group)
+        if self.norm_group is not None:
+            dist.all_reduce(sumsq, group=self.norm_group)
         norm = sumsq.sqrt() / self.world
         scale = torch.clamp(max_norm / (norm + 1e-6), max=1.0) if max_norm > 0 else torch.ones_like(norm)
         g = shard * (scale / self.world)

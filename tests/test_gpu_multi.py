@@ -313,7 +313,7 @@ def test_expert_split_engine_two_gpus(mode):
         assert abs(got - want) <= 3e-2 * abs(want) + 1e-6, (k, got, want)
 
 
-def _dense_engine_cfg(tp: int):
+def _dense_engine_cfg(tp: int, fsdp: int = 1):
     import copy
 
     import __graft_entry__ as ge
@@ -321,22 +321,22 @@ def _dense_engine_cfg(tp: int):
 
     c = copy.deepcopy(ge.SMOKE_CONFIG)
     c["runtime"]["backend"] = "fused_sm100"
-    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
-    c["runtime"]["sharding"] = "ddp"
+    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": fsdp, "tp": tp}
+    c["runtime"]["sharding"] = "owner" if fsdp > 1 else "ddp"
     c["pd"]["steps"] = 3
     c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "none"}}
     c["eval"] = None
     return LMExperimentConfig.model_validate(c)
 
 
-def _tp_engine_worker(rank: int, world: int, port: int, out):
+def _tp_engine_worker(rank: int, world: int, port: int, fsdp: int, out):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     from param_decomp_b200.experiments.lm.training import train_lm
     from param_decomp_b200.ops import native
 
     states: list = []
-    res = train_lm(_dense_engine_cfg(world), None, device="cuda", state_out=states)
+    res = train_lm(_dense_engine_cfg(world // fsdp, fsdp), None, device="cuda", state_out=states)
     torch.cuda.synchronize()
     native.check_status()
     assert states[0].expert_shard is not None and states[0].expert_shard.by_component
@@ -351,9 +351,25 @@ def test_component_split_engine_two_gpus():
 
     world, port = 2, _free_port()
     out = mp.Manager().dict()
-    mp.spawn(_tp_engine_worker, args=(world, port, out), nprocs=world, join=True)
+    mp.spawn(_tp_engine_worker, args=(world, port, 1, out), nprocs=world, join=True)
     ref = train_lm(_dense_engine_cfg(1), None, device="cuda").last_metrics
     for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss"):
         for r in range(world):
             got, want = out[r]["train/" + k], ref["train/" + k]
             assert abs(got - want) <= 3e-2 * abs(want) + 1e-6, (k, r, got, want)
+
+
+def test_component_split_with_sharded_optimizer_four_gpus():
+    """A 2 x 2 mesh on the fused backend: the batch over two data shards with the sharded AdamW (collective form),
+    every site's components over two tp ranks; against one GPU."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    world, port = 4, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_tp_engine_worker, args=(world, port, 2, out), nprocs=world, join=True)
+    ref = train_lm(_dense_engine_cfg(1), None, device="cuda").last_metrics
+    for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss"):
+        got, want = sum(out[r]["train/" + k] for r in range(world)) / world, ref["train/" + k]
+        assert abs(got - want) <= 3e-2 * abs(want) + 1e-6, (k, got, want)

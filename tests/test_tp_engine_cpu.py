@@ -19,11 +19,11 @@ STEPS = 4
 SPLIT_ID, SINGLE_ID = "p-0000cccc", "p-0000dddd"
 
 
-def _cfg(tp: int, losses: str) -> LMExperimentConfig:
+def _cfg(tp: int, losses: str, fsdp: int = 1) -> LMExperimentConfig:
     c = copy.deepcopy(ge.SMOKE_CONFIG)
     c["runtime"]["backend"] = "eager_torch"
-    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
-    c["runtime"]["sharding"] = "ddp"
+    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": fsdp, "tp": tp}
+    c["runtime"]["sharding"] = "owner" if fsdp > 1 else "ddp"  # fsdp > 1: ZeRO-style sharded AdamW over the batch axes
     c["target"]["weights_dtype"] = "float32"
     c["target"]["attention_implementation"] = "xla"
     c["target"]["spec"]["arch"] = {"family": "glu_transformer", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 48,
@@ -60,38 +60,45 @@ def _train(cfg, root: Path, run_id: str):
     return res, states[0]
 
 
-def _worker(rank: int, world: int, port: int, root: str, losses: str, out):
+def _worker(rank: int, world: int, port: int, root: str, losses: str, fsdp: int, out):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
-    res, state = _train(_cfg(world, losses), Path(root), SPLIT_ID)
+    res, state = _train(_cfg(world // fsdp, losses, fsdp), Path(root), SPLIT_ID)
     assert state.expert_shard is not None and state.expert_shard.by_component
+    if hasattr(state.components_opt, "gather_state"):
+        assert fsdp > 1
+    else:
+        assert fsdp == 1
     out[rank] = (dict(res.last_metrics), {n: p.detach().clone() for n, p in state.components.named_parameters()},
                  {n: p.detach().clone() for n, p in state.ci_fn.named_parameters()})
 
 
-@pytest.mark.parametrize("losses", ["stochastic", "pgd"])
-def test_component_split_engine_matches_single_process(losses):
+@pytest.mark.parametrize("losses,fsdp", [("stochastic", 1), ("pgd", 1), ("stochastic", 2)])
+def test_component_split_engine_matches_single_process(losses, fsdp):
+    """`fsdp = 2`: a 2 x 2 mesh - the batch over two data shards with the sharded optimizer, the components over
+    two tp ranks."""
     from safetensors import safe_open
 
     with tempfile.TemporaryDirectory() as root:
-        world, port = 2, _free_port()
+        tp = 2
+        world, port = tp * fsdp, _free_port()
         out = mp.Manager().dict()
-        mp.spawn(_worker, args=(world, port, root, losses, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, root, losses, fsdp, out), nprocs=world, join=True)
         res, ref = _train(_cfg(1, losses), Path(root), SINGLE_ID)
         keys = [k for k in res.last_metrics if k.startswith("train/loss/") or k.startswith("train/grad_norm/")]
         assert len(keys) >= 4
         for k in keys:
-            for r in range(world):
-                got, want = out[r][0][k], res.last_metrics[k]
-                assert abs(got - want) <= 3e-4 * abs(want) + 1e-7, (k, r, got, want)
+            got = sum(out[r][0][k] for r in range(world)) / world  # (data shards see their own rows)
+            want = res.last_metrics[k]
+            assert abs(got - want) <= 3e-4 * abs(want) + 1e-7, (k, got, want)
         ref_params = dict(ref.components.named_parameters())
         for r in range(world):
             _, local, ci_params = out[r]
             for name, p in local.items():
                 g = ref_params[name].detach()
                 ax = -1 if name.startswith("V") else -2
-                w = g.shape[ax] // world
-                assert torch.allclose(p, g.narrow(ax, r * w, w), atol=3e-6), name
+                w = g.shape[ax] // tp
+                assert torch.allclose(p, g.narrow(ax, (r % tp) * w, w), atol=3e-6), name
             for name, p in ref.ci_fn.named_parameters():
                 assert torch.allclose(ci_params[name], p.detach(), atol=3e-6), name
         for item in (DECOMPOSITION_FILE, TRAINING_FILE):
