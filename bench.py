@@ -145,6 +145,8 @@ def main() -> None:
                             expert_shard=expert_shard)
     rows = cfg.pd.batch_size // topo.data_world
     shard_backend = args.optim if (topo.data_world > 1 and args.optim != "ddp" and args.tp == 1) else None
+    if args.tp > 1 and topo.data_world > 1 and args.optim != "ddp" and run.ep is None:
+        shard_backend = "collective"  # component slices: sharded AdamW over the batch axes, clip norm summed over tp
     state = init_train_state(run.model, run.ci_fn, cfg.pd, objective, topo.device, rows, cfg.data.seq_len,
                              use_fused_optim=True, shard_group=topo.data_group, shard_backend=shard_backend,
                              expert_shard=expert_shard)

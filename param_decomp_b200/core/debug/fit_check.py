@@ -42,7 +42,11 @@ def estimate(cfg: Any, n_gpus: int = 1, pool_gib: float = 170.0) -> FitReport:
     assert arch is not None, "the fit check needs an inline architecture (random_init target) or a resolved one"
     G = 2.0**30
     seq = cfg.data.seq_len
-    rows = cfg.pd.batch_size // n_gpus * seq
+    # the mesh's tp axis holds ranks that see the same rows and split the components (dense sites: along C,
+    # expert sites: by expert); the batch is divided over the remaining ranks
+    tp = min(getattr(cfg.runtime.mesh, "tp", 1), n_gpus)
+    data_shards = max(1, n_gpus // tp)
+    rows = cfg.pd.batch_size // data_shards * seq
     wbytes = 2 if cfg.target.weights_dtype == "bfloat16" else 4
     d, L, V = arch.d_model, arch.n_layer, arch.vocab_size
     hd = arch.head_dim or d // arch.n_head
@@ -67,10 +71,12 @@ def estimate(cfg: Any, n_gpus: int = 1, pool_gib: float = 170.0) -> FitReport:
     per_layer_target = sum(a * b * (E if n.startswith("experts_") else 1) for n, (a, b) in dims.items()
                            if n in ("q", "k", "v", "o") or n in cs)
     target_params += L * per_layer_target
-    comp_params = sum((din + dout) * C for din, dout, C, _ in sites)
+    comp_params = sum((din + dout) * C for din, dout, C, _ in sites) / tp
     ci_hidden = getattr(cfg.decomposition.ci, "hidden_dims", (0,))[0] if hasattr(cfg.decomposition.ci, "hidden_dims") else 0
     ci_params = sum(din * ci_hidden + ci_hidden * C for din, _, C, _ in sites)
-    shard = n_gpus if (isinstance(cfg.runtime.sharding, str) and cfg.runtime.sharding != "ddp") else 1
+    expert_split = tp > 1 and E > 1  # expert-split stacks keep the replicated optimizer over the batch axes
+    shard = data_shards if (isinstance(cfg.runtime.sharding, str) and cfg.runtime.sharding != "ddp"
+                            and not expert_split) else 1
     persistent = {
         "target weights": target_params * wbytes / G,
         "component masters + AdamW m, v (fp32)": comp_params * 12 / shard / G,
@@ -81,7 +87,7 @@ def estimate(cfg: Any, n_gpus: int = 1, pool_gib: float = 170.0) -> FitReport:
     n_draws = sum(getattr(t, "n_samples", 1) for t in build_objective(cfg.pd).recon)
     # per draw and site the fused path keeps x, A (and H when the CI needs a gradient), per job row
     # (blocked sites additionally keep the per-job mask rows, the padded job copies and the job outputs)
-    act = sum(rows * mult * ((din + 2 * C) * 2 if mult == 1.0 else (2 * din + 5 * (C // E) + 2 * dout) * 2 * 1.25)
+    act = sum(rows * mult * ((din + 2 * C / tp) * 2 if mult == 1.0 else (2 * din + 5 * (C // E) + 2 * dout) * 2 * 1.25 / tp)
               for din, dout, C, mult in sites)
     ci_act = sum(rows * ((C if mult == 1.0 else C // E * k) * 2 * 3 + ci_hidden * 2) for _, _, C, mult in sites)
     resid = rows * d * 2 * L * 6
