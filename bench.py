@@ -138,9 +138,9 @@ def main() -> None:
     objective = build_objective(cfg.pd)
     expert_shard = None
     if args.tp > 1:
-        from param_decomp_b200.parallel.expert_shard import ExpertSharding
+        from param_decomp_b200.parallel.expert_shard import StackSharding
 
-        expert_shard = ExpertSharding.for_model(run.model)
+        expert_shard = StackSharding.for_model(run.model)
     ctx = StepContext.build(run.model, objective, cfg.pd, collectives=topo.collectives(), lazy_masks=True,
                             expert_shard=expert_shard)
     rows = cfg.pd.batch_size // topo.data_world

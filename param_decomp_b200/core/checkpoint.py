@@ -59,7 +59,7 @@ def _storable(t: Tensor) -> Tensor:
 
 def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module,
                           expert_shard=None) -> tuple[dict[str, Tensor], dict[str, str]]:
-    """`expert_shard` (`parallel.expert_shard.ExpertSharding`): blocked groups hold this rank's experts
+    """`expert_shard` (`parallel.expert_shard.StackSharding`): blocked groups hold this rank's experts
     only; they are gathered over the expert group (a collective every rank of it must enter) so the
     file always has the global `[sites, E, ...]` stacks."""
     out: dict[str, Tensor] = {}

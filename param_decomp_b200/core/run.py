@@ -205,9 +205,9 @@ def run_decomposition_training(
     objective = build_objective(pd)
     expert_shard = None
     if getattr(model, "ep", None) is not None or getattr(model, "component_group", None) is not None:
-        from param_decomp_b200.parallel.expert_shard import ExpertSharding
+        from param_decomp_b200.parallel.expert_shard import StackSharding
 
-        expert_shard = ExpertSharding.for_model(model)
+        expert_shard = StackSharding.for_model(model)
     ctx = StepContext.build(model, objective, pd, collectives=collectives, lazy_masks=lazy_masks, nontarget=nontarget,
                             expert_shard=expert_shard, remat_recon_forwards=remat_recon_forwards,
                             remat_ci_fn=remat_ci_fn)

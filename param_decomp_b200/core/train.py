@@ -101,7 +101,7 @@ class StepContext:
     lazy_masks: bool = False  # fused backend draws stochastic masks in-kernel
     nontarget: NontargetObjective | None = None
     relative_faithfulness: bool = True
-    expert_shard: Any = None  # parallel.expert_shard.ExpertSharding when expert blocks are split over ranks
+    expert_shard: Any = None  # parallel.expert_shard.StackSharding when expert blocks are split over ranks
     # activation recompute (param_decomp/targets/transformer.py:1910-1918, experiments/lm/runtime.py:340-360):
     # a masked forward / the CI function keeps only its inputs and is run again during the backward pass
     remat_recon_forwards: bool = False

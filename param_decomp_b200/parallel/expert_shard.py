@@ -31,7 +31,9 @@ from param_decomp_b200.core.components import ComponentStacks, SiteSpec
 
 
 @dataclass
-class ExpertSharding:
+class StackSharding:
+    """Which component stacks are split over the tp group, and how (by expert, or along `C`)."""
+
     group: Any  # the process group of the mesh's tp axis
     n_experts: int  # true expert count E (before padding to a multiple of the group); 0 in component mode
     blocked_keys: frozenset[str]  # parameter keys (`ComponentStacks.param_key`) of the split groups
@@ -45,7 +47,7 @@ class ExpertSharding:
         self.n_real = max(0, min(self.n_experts, self.lo + self.e_loc) - self.lo)  # non-dummy local experts
 
     @classmethod
-    def for_model(cls, model: Any) -> "ExpertSharding | None":
+    def for_model(cls, model: Any) -> "StackSharding | None":
         ep = getattr(model, "ep", None)
         if ep is not None:
             keys = frozenset(ComponentStacks.param_key(s.group) for s in model.sites if s.blocked)
