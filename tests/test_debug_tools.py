@@ -14,6 +14,13 @@ def test_fit_check_orders_configs():
     assert not fit_check.estimate(cfg, 1, pool_gib=10.0).fits
     moe = LMExperimentConfig.from_file("param_decomp_b200/experiments/configs/lm_moe4l_e42.yaml")
     assert not fit_check.estimate(moe, 1).fits and fit_check.estimate(moe, 8).fits
+    # the 8B-shaped config: its fsdp 4 x tp 2 mesh (components split over tp, optimizer state over the batch shards)
+    # fits eight 180 GB parts; the same eight GPUs as pure data parallel (tp = 1) would not
+    big = LMExperimentConfig.from_file("param_decomp_b200/experiments/configs/lm_llama8b_mlp_c8192.yaml")
+    assert big.runtime.mesh.tp == 2 and fit_check.estimate(big, 8).fits
+    flat = big.model_copy(update={"runtime": big.runtime.model_copy(update={"mesh": big.runtime.mesh.model_copy(
+        update={"fsdp": 8, "tp": 1})})})
+    assert not fit_check.estimate(flat, 8).fits
     assert "TOTAL" in str(one)
 
 
