@@ -171,8 +171,8 @@ def fused_site_forward(x: Tensor, w: SiteWeights, sm: SiteMask, need_weight_grad
     if mask_t is not None:
         if mask_t.dtype != torch.bfloat16:
             mask_t = mask_t.to(torch.bfloat16)
-        if not mask_t.is_contiguous():
-            mask_t = mask_t.contiguous()
+        if mask_t.stride(-1) != 1 or mask_t.stride(0) % 8 != 0 or mask_t.data_ptr() % 16 != 0:
+            mask_t = mask_t.contiguous()  # (a column slice of a wider tensor is read in place through its row pitch)
     y = _FusedSite.apply(x2, mask_t, delta, w, rowscale, d_eff, seed, stream, mode, row_offset, need_weight_grads,
                          col_offset, target_term)
     return y.reshape(*lead, -1)

@@ -36,6 +36,12 @@ class ReduceFromGroup(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        # the partial is a fresh product nobody else reads: reduce it in place (no producer here keeps its own
+        # output for backward) instead of copying a [tokens, d_out] tensor per site
+        if x.is_contiguous() and not x.is_leaf:
+            ctx.mark_dirty(x)
+            dist.all_reduce(x, group=group)
+            return x
         out = x.contiguous().clone()
         dist.all_reduce(out, group=group)
         return out
