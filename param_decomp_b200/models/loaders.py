@@ -101,6 +101,9 @@ def load_hf_snapshot(snapshot_dir: Path, dtype: torch.dtype, device) -> tuple[Tr
     if "linear_num_value_heads" in text:  # hybrid DeltaNet mixture-of-experts family
         arch = qwen35_arch_from_hf_config(cfg)
         return arch, remap_hf_qwen35(read_safetensors(files, dtype, device), arch)
+    if "moe_intermediate_size" in cfg and ("num_experts" in cfg or "num_local_experts" in cfg):  # plain top-k MoE
+        arch = moe_arch_from_hf_config(cfg)
+        return arch, remap_hf_qwen3_moe(read_safetensors(files, dtype, device), arch)
     arch = arch_from_hf_config(cfg)
     return arch, remap_hf_llama(read_safetensors(files, dtype, device), arch)
 
@@ -148,6 +151,47 @@ def save_simple_mlp_cache(entry: Path, arch: TransformerArchConfig, weights: dic
     save_file({k: v.detach().cpu().contiguous() for k, v in raw.items()}, str(entry / f"model_step_{step}.safetensors"))
 
 
+# ---- plain top-k mixture of experts (Qwen3-MoE style: softmax router, SwiGLU experts, no shared expert) ----
+
+
+def moe_arch_from_hf_config(cfg: dict[str, Any]) -> TransformerArchConfig:
+    return TransformerArchConfig(
+        family="moe", n_layer=cfg["num_hidden_layers"], d_model=cfg["hidden_size"], n_head=cfg["num_attention_heads"],
+        n_kv_head=cfg.get("num_key_value_heads"), head_dim=cfg.get("head_dim"), d_ff=cfg["moe_intermediate_size"],
+        vocab_size=cfg["vocab_size"], max_seq_len=cfg.get("max_position_embeddings", 2048),
+        rope_theta=float((cfg.get("rope_parameters") or {}).get("rope_theta", cfg.get("rope_theta", 10000.0))),
+        rms_eps=cfg.get("rms_norm_eps", 1e-6), qk_norm=True, tie_embeddings=cfg.get("tie_word_embeddings", False),
+        n_experts=cfg.get("num_experts", cfg.get("num_local_experts")), experts_per_token=cfg["num_experts_per_tok"],
+        norm_topk_prob=cfg.get("norm_topk_prob", False))
+
+
+def remap_hf_qwen3_moe(raw: dict[str, Tensor], arch: TransformerArchConfig) -> dict[str, Tensor]:
+    """HF Qwen3-MoE keys -> the key grammar of `models/moe.py`; expert banks fused (`mlp.experts.gate_up_proj`,
+    `mlp.experts.down_proj`) or one matrix per expert (`mlp.experts.{e}.gate_proj.weight`)."""
+    out = {"embed.weight": raw["model.embed_tokens.weight"], "final_norm.weight": raw["model.norm.weight"]}
+    if "lm_head.weight" in raw and not arch.tie_embeddings:
+        out["lm_head.weight"] = raw["lm_head.weight"]
+    for i in range(arch.n_layer):
+        p = f"model.layers.{i}."
+        out[f"layers.{i}.attn_norm.weight"] = raw[p + "input_layernorm.weight"]
+        out[f"layers.{i}.mlp_norm.weight"] = raw[p + "post_attention_layernorm.weight"]
+        for k in ("q", "k", "v", "o"):
+            out[tf.weight_key("moe", i, k)] = raw[p + f"self_attn.{k}_proj.weight"]
+        out[f"layers.{i}.q_norm.weight"] = raw[p + "self_attn.q_norm.weight"]
+        out[f"layers.{i}.k_norm.weight"] = raw[p + "self_attn.k_norm.weight"]
+        m = p + "mlp."
+        out[f"layers.{i}.mlp.router.weight"] = raw[m + "gate.weight"]
+        if m + "experts.gate_up_proj" in raw:
+            gu = raw[m + "experts.gate_up_proj"]
+            gate, up, down = gu[:, :arch.d_ff], gu[:, arch.d_ff:], raw[m + "experts.down_proj"]
+        else:
+            per = lambda nm: torch.stack([raw[f"{m}experts.{e}.{nm}.weight"] for e in range(arch.n_experts)])  # noqa: E731
+            gate, up, down = per("gate_proj"), per("up_proj"), per("down_proj")
+        for kind, w in (("experts_gate", gate), ("experts_up", up), ("experts_down", down)):
+            out[tf.weight_key("moe", i, kind)] = w.contiguous()
+    return out
+
+
 # ---- Qwen3.5-style hybrid (gated DeltaNet + gated attention + routed experts) ------------------------
 
 
@@ -167,7 +211,7 @@ def qwen35_arch_from_hf_config(cfg: dict[str, Any]) -> TransformerArchConfig:
         n_kv_head=c.get("num_key_value_heads"), head_dim=c.get("head_dim") or c["hidden_size"] // c["num_attention_heads"],
         d_ff=c["moe_intermediate_size"], vocab_size=c["vocab_size"], max_seq_len=c.get("max_position_embeddings", 4096),
         rope_theta=float(rope.get("rope_theta", c.get("rope_theta", 10000.0))), rms_eps=c.get("rms_norm_eps", 1e-6),
-        n_experts=c["num_experts"], experts_per_token=c["num_experts_per_tok"],
+        n_experts=c.get("num_experts", c.get("num_local_experts")), experts_per_token=c["num_experts_per_tok"],
         norm_topk_prob=c.get("norm_topk_prob", True), full_attention_interval=interval,
         partial_rotary_factor=float(rope.get("partial_rotary_factor", c.get("partial_rotary_factor", 0.25))),
         linear_num_key_heads=c["linear_num_key_heads"], linear_key_head_dim=c["linear_key_head_dim"],
