@@ -28,11 +28,14 @@ from param_decomp_b200.config.run import WandbConfig
 from param_decomp_b200.core.metrics import MetricsSink, get_logger
 from param_decomp_b200.formats.base import BaseConfig
 from param_decomp_b200.models import transformer as tf
-from param_decomp_b200.models.loaders import save_simple_mlp_cache
+from param_decomp_b200.models.loaders import save_qwen35_cache, save_simple_mlp_cache
 
 
 class PretrainModelConfig(BaseConfig):
-    model_type: Literal["LlamaSimpleMLP", "LlamaSimple", "GPT2Simple"] = "LlamaSimpleMLP"
+    model_type: Literal["LlamaSimpleMLP", "LlamaSimple", "GPT2Simple", "Qwen35Moe"] = "LlamaSimpleMLP"
+    hybrid: TransformerArchConfig | None = None
+    """`Qwen35Moe` only: the full hybrid architecture (gated DeltaNet / gated attention / routed + shared experts);
+    the flat fields above must agree with it where they overlap."""
     block_size: PositiveInt | None = None
     vocab_size: PositiveInt
     n_layer: PositiveInt
@@ -45,6 +48,11 @@ class PretrainModelConfig(BaseConfig):
     rms_norm_eps: PositiveFloat = 1e-6
 
     def arch(self) -> TransformerArchConfig:
+        if self.model_type == "Qwen35Moe":
+            assert self.hybrid is not None and self.hybrid.family == "qwen35_moe", "Qwen35Moe needs `model.hybrid`"
+            h = self.hybrid
+            assert (h.n_layer, h.d_model, h.vocab_size) == (self.n_layer, self.n_embd, self.vocab_size)
+            return h
         family = "simple_mlp" if self.model_type in ("LlamaSimpleMLP", "GPT2Simple") else "glu_transformer"
         return TransformerArchConfig(family=family, n_layer=self.n_layer, d_model=self.n_embd, n_head=self.n_head,
                                      n_kv_head=self.n_key_value_heads, d_ff=self.n_intermediate,
@@ -93,8 +101,14 @@ def pretrain(cfg: PretrainConfig, data_root: Path, run_id: str = "t-00000000", p
     log = get_logger()
     arch = cfg.model.arch()
     dtype = torch.bfloat16 if (cfg.dtype == "bfloat16" and device != "cpu") else torch.float32
-    weights = {k: v.float().to(device).requires_grad_(True)
-               for k, v in tf.random_init_weights(arch, cfg.seed, torch.float32, device).items()}
+    hybrid = arch.family == "qwen35_moe"
+    if hybrid:
+        from param_decomp_b200.models import qwen35
+
+        init = qwen35.random_init_qwen35_weights(arch, cfg.seed, torch.float32, device)
+    else:
+        init = tf.random_init_weights(arch, cfg.seed, torch.float32, device)
+    weights = {k: v.float().to(device).requires_grad_(True) for k, v in init.items()}
     seq = cfg.model.n_ctx
 
     def source(ref: Any, salt: int):
@@ -111,8 +125,9 @@ def pretrain(cfg: PretrainConfig, data_root: Path, run_id: str = "t-00000000", p
     sink = MetricsSink.for_run(entry, 0)
 
     def loss_on(batch) -> torch.Tensor:
-        model = tf.TransformerDecomposedModel(arch, {k: v.to(dtype) for k, v in weights.items()}, {}, backend="eager_torch",
-                                              attention="xla" if device == "cpu" else cfg.attention_implementation)
+        cls = qwen35.Qwen35DecomposedModel if hybrid else tf.TransformerDecomposedModel
+        model = cls(arch, {k: v.to(dtype) for k, v in weights.items()}, {}, backend="eager_torch",
+                    attention="xla" if device == "cpu" else cfg.attention_implementation)
         toks = batch.tokens.to(device)
         out = model._run(tf.LMBatch(toks[:, :-1], None if batch.segment_ids is None else batch.segment_ids[:, :-1].to(device)),
                          None, None, (), want_taps=False)
@@ -137,8 +152,11 @@ def pretrain(cfg: PretrainConfig, data_root: Path, run_id: str = "t-00000000", p
                 val = sum(float(loss_on(val_src.batch(i, cfg.global_batch))) for i in range(min(cfg.val_steps, 2))) / min(cfg.val_steps, 2)
             sink.log(it, {"val_loss": val}, prefix="pretrain/")
         if (it + 1) % cfg.save_every == 0 or it == n_iter - 1:
-            save_simple_mlp_cache(entry, arch, {k: v.detach().to(torch.bfloat16 if cfg.dtype == "bfloat16" else torch.float32)
-                                                for k, v in weights.items()}, it + 1)
+            snap = {k: v.detach().to(torch.bfloat16 if cfg.dtype == "bfloat16" else torch.float32) for k, v in weights.items()}
+            if hybrid:
+                save_qwen35_cache(entry, arch, snap, it + 1)
+            else:
+                save_simple_mlp_cache(entry, arch, snap, it + 1)
     sink.close()
     return entry
 

@@ -1,4 +1,6 @@
 """Qwen3.5-style hybrid target: delta-rule forms agree, the model steps through the engine."""
+import math
+
 import torch
 
 from param_decomp_b200.config.experiments import LMExperimentConfig
@@ -72,3 +74,34 @@ def test_hybrid_model_trains_on_cpu():
     a = run.model.clean_forward(batch)
     b = run.model.clean_forward(batch)
     assert torch.equal(a.output, b.output) and set(a.aux["routing"]) == {0, 1, 2, 3}
+
+
+def test_pretrained_hybrid_target_roundtrip(tmp_path):
+    """Pretrain a tiny hybrid model for a few iterations, then decompose it as a `pretrained_qwen35_moe` target
+    resolved by run path through the pretrain cache."""
+    from param_decomp_b200.pretrain.train import PretrainConfig, pretrain
+
+    pcfg = PretrainConfig.model_validate({
+        "run_name": "t", "global_batch": 4, "num_iterations": 3, "warmup_iters": 1, "learning_rate": 1e-3,
+        "log_every": 1, "val_every": 3, "save_every": 3, "dtype": "float32",
+        "model": {"model_type": "Qwen35Moe", "vocab_size": 101, "n_layer": 4, "n_head": 4, "n_embd": 32,
+                  "n_intermediate": 16, "n_ctx": 24, "hybrid": ARCH}})
+    entry = pretrain(pcfg, tmp_path, run_id="t-0000beef", project="spd")
+    assert (entry / "model_config.yaml").exists() and len(list(entry.glob("model_step_*.safetensors"))) == 1
+    import json
+
+    lines = [json.loads(x) for x in (entry / "metrics.jsonl").read_text().splitlines()]
+    losses = [r["pretrain/loss"] for r in lines if "pretrain/loss" in r]
+    assert len(losses) == 3 and all(math.isfinite(v) for v in losses)
+
+    cfg = _config({"gdn_q": 8, "attn_o": 8, "experts_down": 12, "shared_up": 8})
+    raw = cfg.model_dump(mode="json")
+    raw["target"]["spec"] = {"kind": "pretrained_qwen35_moe", "run_path": "goodfire/spd/runs/t-0000beef"}
+    cfg = LMExperimentConfig.model_validate(raw)
+    run = build_lm_run(cfg, tmp_path, "cpu")
+    assert run.arch.family == "qwen35_moe" and run.arch.n_experts == 6
+    obj = build_objective(cfg.pd)
+    ctx = StepContext.build(run.model, obj, cfg.pd)
+    st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, "cpu", cfg.pd.batch_size, cfg.data.seq_len)
+    m = train_step(ctx, st, run.sample_train(0))
+    assert math.isfinite(float(m["loss/total"]))
