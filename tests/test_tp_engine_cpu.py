@@ -43,6 +43,10 @@ def _cfg(tp: int, losses: str, fsdp: int = 1) -> LMExperimentConfig:
         ]
     c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "periodic", "save_every": 2, "retention": {"kind": "keep_all"}}}
     c["eval"] = None
+    if losses == "stochastic" and fsdp == 1:  # evaluations run on the split stacks too
+        c["eval"] = {"batch_size": 4, "n_steps": 1, "every": 2, "slow_every": 4,
+                     "metrics": [{"type": "CI_L0", "groups": None},
+                                 {"type": "PGDReconLoss", "init": "random", "source_shape": "c", "n_steps": 2, "step_size": 0.1}]}
     return LMExperimentConfig.model_validate(c)
 
 
@@ -101,6 +105,18 @@ def test_component_split_engine_matches_single_process(losses, fsdp):
                 assert torch.allclose(p, g.narrow(ax, (r % tp) * w, w), atol=3e-6), name
             for name, p in ref.ci_fn.named_parameters():
                 assert torch.allclose(ci_params[name], p.detach(), atol=3e-6), name
+        if losses == "stochastic" and fsdp == 1:
+            import json
+
+            def last_eval(run_id):
+                path = next(p for p in Path(root).rglob("metrics.jsonl") if run_id in str(p))
+                rows = [json.loads(x) for x in path.read_text().splitlines()]
+                return [{k: v for k, v in r.items() if k.startswith("eval/")} for r in rows if any(k.startswith("eval/") for k in r)][-1]
+
+            a, b = last_eval(SPLIT_ID), last_eval(SINGLE_ID)
+            assert set(a) == set(b) and any(k.startswith("eval/l0/") for k in a) and "eval/PGDReconLoss_2step" in a
+            for k in a:
+                assert abs(a[k] - b[k]) <= 1e-3 * abs(b[k]) + 1e-6, (k, a[k], b[k])
         for item in (DECOMPOSITION_FILE, TRAINING_FILE):
             split_f = [p for p in sorted(Path(root).rglob(item)) if SPLIT_ID in str(p)][-1]
             single_f = Path(str(split_f).replace(SPLIT_ID, SINGLE_ID))
