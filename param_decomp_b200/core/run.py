@@ -275,7 +275,7 @@ def run_decomposition_training(
         step = state.step
         if evaluation is not None and evaluation.is_due(step):
             sync_masters(for_save=False)
-            ev = evaluation.run(step, state, ctx)
+            ev = collectives.average_scalars(evaluation.run(step, state, ctx))
             if sink is not None and ev:
                 sink.log(step, ev, prefix="eval/")
         if saving and step > 0 and step % cadence.checkpointing.save_every == 0 and ckpt.latest_step(run_dir) != step:  # type: ignore[union-attr,arg-type]
@@ -320,7 +320,7 @@ def run_decomposition_training(
     if state.step >= pd.steps:
         if evaluation is not None and evaluation.is_due(state.step):
             sync_masters(for_save=False)
-            ev = evaluation.run(state.step, state, ctx)
+            ev = collectives.average_scalars(evaluation.run(state.step, state, ctx))
             if sink is not None and ev:
                 sink.log(state.step, ev, prefix="eval/")
         save()

@@ -73,6 +73,10 @@ class DataCollectives:
         self.reduce_grads(params)
 
     in_first_tp_group: bool = True
+
+    def average_scalars(self, values: dict) -> dict:
+        """Mean over ranks of the scalar entries of an evaluation result (every rank evaluated its own rows)."""
+        return values
     split_grad_scale: float = 1.0  # see `DistCollectives.split_grad_scale`
 
 

@@ -115,6 +115,21 @@ class DistCollectives(DataCollectives):
                 flush()
         flush()
 
+    def average_scalars(self, values: dict) -> dict:
+        """Evaluation metrics are computed by every rank on its own rows of the evaluation batch: average the
+        scalar entries over the job on the host group (same keys on every rank; other entries pass through)."""
+        if self.topo.world == 1:
+            return values
+        keys = sorted(k for k, v in values.items()
+                      if isinstance(v, (int, float)) or (isinstance(v, Tensor) and v.numel() == 1))
+        if not keys:
+            return values
+        t = torch.tensor([float(values[k]) for k in keys], dtype=torch.float64)
+        dist.all_reduce(t, group=self.topo.cpu_group)
+        out = dict(values)
+        out.update({k: float(x) / self.topo.world for k, x in zip(keys, t)})
+        return out
+
     @property
     def in_first_tp_group(self) -> bool:
         """Ranks `0 .. tp-1` (tp is the fastest axis): the one tp group that assembles split stacks for a save."""
