@@ -303,6 +303,7 @@ def run_decomposition_training(
             scalars.update(uv_norm_ratio_metrics(state.components))  # drift of the V/U scale symmetry
             if extra_log is not None:
                 scalars.update(extra_log(step, state, ctx))
+            scalars = collectives.average_scalars(scalars)  # per-batch losses: the global-batch mean, as the reference logs
             floats = sink.log(step, scalars) if sink is not None else {("train/" + k): float(v) for k, v in scalars.items()}
             assert_all_finite(step, floats)
             result.last_metrics = floats
