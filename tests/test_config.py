@@ -74,3 +74,22 @@ def test_component_key():
 def test_flatten_typed_lists():
     out = flatten_typed_lists({"pd": {"loss_metrics": [{"type": "FaithfulnessLoss", "coeff": 2.0}], "seed": 1}})
     assert out["pd.loss_metrics.Faith.coeff"] == 2.0 and "loss_metrics" not in out["pd"]
+
+
+def test_sequence_parallel_is_refused_not_ignored():
+    """`runtime.sequence_sharding: sequence_parallel` parses (schema parity) and the LM roots refuse it at start-up."""
+    import copy
+
+    import pytest
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+    from param_decomp_b200.experiments.lm.training import check_runtime_supported
+
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"]["sequence_sharding"] = "sequence_parallel"
+    cfg = LMExperimentConfig.model_validate(c)
+    with pytest.raises(NotImplementedError):
+        check_runtime_supported(cfg)
+    c["runtime"]["sequence_sharding"] = "replicate"
+    check_runtime_supported(LMExperimentConfig.model_validate(c))
