@@ -42,9 +42,9 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, root: str, out):
+def _worker(rank: int, world: int, ports: tuple, root: str, out):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port))
+                      MASTER_PORT=str(ports[0]))
     from param_decomp_b200.experiments.lm.training import train_lm
 
     def run(run_id, max_steps=None):
@@ -56,9 +56,9 @@ def _worker(rank: int, world: int, port: int, root: str, out):
         return st
 
     full = run(FULL_ID)
-    os.environ["MASTER_PORT"] = str(port + 1)
+    os.environ["MASTER_PORT"] = str(ports[1])
     run(PART_ID, max_steps=4)  # saved at the top of step 3, stops after step 4 (steps 3.. are redone on re-entry)
-    os.environ["MASTER_PORT"] = str(port + 2)
+    os.environ["MASTER_PORT"] = str(ports[2])
     resumed = run(PART_ID)
     assert hasattr(full.components_opt, "gather_state"), "the config must select the sharded optimizer"
     out[rank] = ([p.detach().clone() for p in full.components.parameters()],
@@ -72,9 +72,9 @@ def test_sharded_optimizer_resume_and_layout_independent_checkpoint():
     from param_decomp_b200.experiments.lm.build import build_lm_run
 
     with tempfile.TemporaryDirectory() as root:
-        world, port = 2, _free_port()
+        world, ports = 2, (_free_port(), _free_port(), _free_port())  # one rendezvous per training entry
         out = mp.Manager().dict()
-        mp.spawn(_worker, args=(world, port, root, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, ports, root, out), nprocs=world, join=True)
         for r in range(world):
             full, resumed, s1, s2 = out[r]
             assert s1 == s2 == STEPS
