@@ -36,10 +36,15 @@ def _cfg(world: int) -> LMExperimentConfig:
     return LMExperimentConfig.model_validate(c)
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+def _free_ports(n: int) -> tuple:
+    socks = [socket.socket() for _ in range(n)]
+    try:
+        for s in socks:
+            s.bind(("127.0.0.1", 0))
+        return tuple(s.getsockname()[1] for s in socks)  # distinct: all bound at the same time
+    finally:
+        for s in socks:
+            s.close()
 
 
 def _worker(rank: int, world: int, ports: tuple, root: str, out):
@@ -72,7 +77,7 @@ def test_sharded_optimizer_resume_and_layout_independent_checkpoint():
     from param_decomp_b200.experiments.lm.build import build_lm_run
 
     with tempfile.TemporaryDirectory() as root:
-        world, ports = 2, (_free_port(), _free_port(), _free_port())  # one rendezvous per training entry
+        world, ports = 2, _free_ports(3)  # one rendezvous per training entry
         out = mp.Manager().dict()
         mp.spawn(_worker, args=(world, ports, root, out), nprocs=world, join=True)
         for r in range(world):
