@@ -130,3 +130,34 @@ def test_component_split_engine_matches_single_process(losses, fsdp):
                         assert float((a - b).abs().mean()) <= 1e-3 * (float(b.abs().mean()) + 1e-3), k
                     else:
                         assert torch.allclose(a, b, atol=3e-6), k
+
+
+def _resume_worker(rank: int, world: int, ports: tuple, root: str, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(ports[0]))
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    def run(run_id, max_steps=None):
+        states: list = []
+        train_lm(_cfg(world, "pgd"), Path(root), run_id=run_id, device="cpu", max_steps_this_entry=max_steps, state_out=states)
+        return states[0]
+
+    full = run("p-0000aaa1")
+    os.environ["MASTER_PORT"] = str(ports[1])
+    run("p-0000aaa2", max_steps=3)  # checkpoint at step 2, stopped after step 3
+    os.environ["MASTER_PORT"] = str(ports[2])
+    resumed = run("p-0000aaa2")
+    same = all(torch.allclose(a, b, atol=1e-6) for a, b in zip(list(full.components.parameters()) + list(full.ci_fn.parameters()),
+                                                                list(resumed.components.parameters()) + list(resumed.ci_fn.parameters())))
+    out[rank] = (same, full.step, resumed.step)
+
+
+def test_component_split_run_resumes_from_its_global_checkpoint():
+    """A tp-split run (persistent adversary included) interrupted after its checkpoint reaches the same
+    parameters as the uninterrupted one: the global-layout file is cut back to each rank's slice."""
+    from test_sharded_resume_cpu import _free_ports
+
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        mp.spawn(_resume_worker, args=(2, _free_ports(3), root, out), nprocs=2, join=True)
+        assert all(v == (True, STEPS, STEPS) for v in out.values()), dict(out)
