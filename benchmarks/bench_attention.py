@@ -1,12 +1,17 @@
 """Times the tcgen05 flash-attention kernels against torch's fused SDPA (library kernels).
 
-    python -m param_decomp_b200.ops.bench_attention [--batch 64 --seq 512 --heads 12 --kv-heads 12 --hd 64]
+    python benchmarks/bench_attention.py [--batch 64 --seq 512 --heads 12 --kv-heads 12 --hd 64]
 
 Causal self-attention, bf16, forward and forward+backward; CUDA-event device time with an L2-sized
 buffer rewritten between launches. One JSON line per implementation.
 """
 
 from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))  # the repository root (run as a script)
 
 import argparse
 import json

@@ -1,7 +1,7 @@
 """Micro-benchmark of the tcgen05 GEMM engine on the decomposed-site products of the flagship LM.
 
-    python -m param_decomp_b200.ops.bench_gemm                         # table over the three site shapes
-    python -m param_decomp_b200.ops.bench_gemm --case mask_fwd --rows 16384 --iters 1   # one small case (profiling)
+    python benchmarks/bench_gemm.py                         # table over the three site shapes
+    python benchmarks/bench_gemm.py --case mask_fwd --rows 16384 --iters 1   # one small case (profiling)
 
 Cases: `mask_fwd` (`A = (xV) * (m - d)` with the mask drawn in the epilogue, also emits `H = xV`),
 `site_out` (`y = A U + (d x) W^T`, two K phases on one accumulator), `mask_bwd` (`dH` and the mask
@@ -11,6 +11,11 @@ fraction printed is against the `bf16_tflops` burst figure of a cuBLAS GEMM pass
 """
 
 from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))  # the repository root (run as a script)
 
 import argparse
 import json

@@ -1,6 +1,6 @@
 """Times the memory-bound kernels of the routed-expert path at the 42-expert config's sizes.
 
-    python -m param_decomp_b200.ops.bench_moe_rows [--tokens 8192 --k 8 --experts 42 --d 512 --c 512]
+    python benchmarks/bench_moe_rows.py [--tokens 8192 --k 8 --experts 42 --d 512 --c 512]
 
 Token fan-out to padded job rows, routing-weighted combine, and the narrow CI squash + per-expert
 activity (forward and backward); CUDA-event device time with an L2-sized buffer rewritten between
@@ -9,6 +9,11 @@ copy bandwidth (`MEASURED_PEAKS.json` beside the repository root when present, e
 """
 
 from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))  # the repository root (run as a script)
 
 import argparse
 import json

@@ -1,7 +1,7 @@
 """Times the fused tensor-parallel GEMMs against their NCCL twins on the ranks of one node.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port P -m param_decomp_b200.parallel.bench_tp [--rows 32768] [--iters 20]
+        --master-port P benchmarks/bench_tp.py [--rows 32768] [--iters 20]
 
 Shapes are the flagship LM's row-parallel contraction (`A [rows, C/tp] @ U [C/tp, d_out]`, reduce-
 scattered over rows) and its sequence-parallel entry (`all_gather(x [rows/tp, d]) @ V [d, C]`).
@@ -9,6 +9,11 @@ Device-timed with CUDA events, max over ranks; rank 0 prints one JSON line per c
 """
 
 from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))  # the repository root (run as a script)
 
 import argparse
 import json

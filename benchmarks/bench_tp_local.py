@@ -1,6 +1,6 @@
 """The fused compute + collective GEMMs on ONE GPU, every "peer" buffer being local memory.
 
-    python -m param_decomp_b200.parallel.bench_tp_local [--case rs|ag_rows|ag_weight] [--rows 16384] [--iters 10]
+    python benchmarks/bench_tp_loca.pyl.py [--case rs|ag_rows|ag_weight] [--rows 16384] [--iters 10]
 
 A kernel that waits on another rank never shares a GPU with it as a separate launch, so the multi-rank
 paths are measured under `torchrun` (`bench_tp.py`) and profiled here: one process, one kernel, the
@@ -10,6 +10,11 @@ and the instruction / memory counters are the kernel's own.
 """
 
 from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))  # the repository root (run as a script)
 
 import argparse
 import json

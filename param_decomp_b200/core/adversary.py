@@ -86,19 +86,25 @@ class PersistentAdversary:
     state: dict[str, Tensor] = field(default_factory=dict)  # "<site>/mu", "<site>/nu", "<site>/vel", + "d:<site>/..."
     n_updates: int = 0
     pool_size: int = 1
+    batch_shared: bool = False  # shape `c`: one source for the whole batch, identical on every batch shard
 
     @classmethod
     def init(cls, sites: tuple[SiteSpec, ...], optimizer, source_dtype: str, shape: str, batch: int,
              positions: int | None, key: StepKey, pool_size: int = 1,
-             device: torch.device | str = "cpu") -> "PersistentAdversary":
-        adv = cls(optimizer=optimizer, source_dtype=source_dtype, pool_size=pool_size)
+             device: torch.device | str = "cpu", data_rank: int = 0) -> "PersistentAdversary":
+        """`batch` is this rank's share of the global batch and `data_rank` its place among the batch shards:
+        per-row sources are drawn at their GLOBAL row, so ranks start from different rows of one stream and
+        the job's sources do not depend on the device count; batch-shared (`c`) sources are the same draw
+        on every rank."""
+        adv = cls(optimizer=optimizer, source_dtype=source_dtype, pool_size=pool_size, batch_shared=shape == "c")
         lead = source_lead_shape(shape, batch * pool_size, positions)
         for i, s in enumerate(sites):
             rows = 1
             for n in lead:
                 rows *= n
-            u = rng.uniform(key, StepKey.stream(rng.PURPOSE_SOURCE_INIT, 0, 0, i), rows, s.C, 0, device)
-            ud = rng.uniform(key, StepKey.stream(rng.PURPOSE_SOURCE_INIT, 1, 0, i), rows, 1, 0, device)
+            off = 0 if adv.batch_shared else data_rank * rows
+            u = rng.uniform(key, StepKey.stream(rng.PURPOSE_SOURCE_INIT, 0, 0, i), rows, s.C, off, device)
+            ud = rng.uniform(key, StepKey.stream(rng.PURPOSE_SOURCE_INIT, 1, 0, i), rows, 1, off, device)
             adv.sources[s.name] = encode_sources(u.reshape(*lead, s.C), source_dtype)
             adv.delta[s.name] = encode_sources(ud.reshape(*lead, 1), source_dtype)
         return adv
@@ -160,21 +166,46 @@ class PersistentAdversary:
             stream = StepKey.stream(rng.PURPOSE_ROUND, 0, 0, zlib.crc32(k.encode()) % (1 << 20))
             store[name] = encode_sources(new.clamp_(0, 1), self.source_dtype, key, stream)
 
-    def state_dict(self) -> dict[str, Tensor]:
+    def _local_state(self) -> dict[str, Tensor]:
         out = {f"sources/{k}": v for k, v in self.sources.items()}
         out.update({f"delta/{k}": v for k, v in self.delta.items()})
         out.update({f"opt/{k}": v for k, v in self.state.items()})
+        return out
+
+    def gather_state(self, gather_rows) -> None:
+        """Collective over the batch shards (every rank calls it before a save): per-row sources and their
+        optimizer state are assembled into the global-batch layout with `gather_rows(t) -> cat over ranks on
+        dim 0`; batch-shared sources are identical on every rank and stay as they are."""
+        if self.batch_shared:
+            return
+        self._gathered = {k: gather_rows(v) for k, v in sorted(self._local_state().items())}
+
+    def state_dict(self) -> dict[str, Tensor]:
+        out = getattr(self, "_gathered", None) or self._local_state()
+        self._gathered = None
+        out = dict(out)
         out["n_updates"] = torch.tensor(self.n_updates, dtype=torch.int64)
         return out
 
-    def load_state_dict(self, sd: dict[str, Tensor]) -> None:
+    def load_state_dict(self, sd: dict[str, Tensor], data_rank: int = 0, data_world: int = 1) -> None:
+        """Entries written in the global-batch layout are cut to this rank's rows (`data_rank` of
+        `data_world` batch shards); a checkpoint of a different device count restores the same way."""
+        def local(leaf: str, v: Tensor) -> Tensor:
+            base = leaf.split("/")[0]
+            ref = self.delta.get(base[2:]) if base.startswith("d:") else self.sources.get(base)
+            if ref is None or v.dim() == 0 or ref.shape[0] == v.shape[0]:
+                return v
+            assert v.shape[0] == ref.shape[0] * data_world, \
+                f"{leaf}: checkpoint has {v.shape[0]} rows, this run {ref.shape[0]} x {data_world} batch shards"
+            return v[data_rank * ref.shape[0]:(data_rank + 1) * ref.shape[0]].contiguous()
+
         for k, v in sd.items():
             if k.startswith("sources/"):
-                self.sources[k[8:]] = v
+                self.sources[k[8:]] = local(k[8:], v)
             elif k.startswith("delta/"):
-                self.delta[k[6:]] = v
+                self.delta[k[6:]] = local("d:" + k[6:], v)
             elif k.startswith("opt/"):
-                self.state[k[4:]] = v
+                self.state[k[4:]] = local(k[4:], v)
             elif k == "n_updates":
                 self.n_updates = int(v.item())
 

@@ -168,8 +168,9 @@ def restore_decomposition(run_dir: Path, step: int, components: ComponentStacks,
     ci_fn.load_state_dict(sd)
 
 
-def restore_state(run_dir: Path, step: int, state) -> None:
-    """Full resume: decomposition + optimizer states + adversaries + frequency EMA + step."""
+def restore_state(run_dir: Path, step: int, state, data_rank: int = 0, data_world: int = 1) -> None:
+    """Full resume: decomposition + optimizer states + adversaries + frequency EMA + step. Per-row adversary
+    sources are stored for the global batch; each of `data_world` batch shards keeps its own rows."""
     expert_shard = getattr(state, "expert_shard", None)
     restore_decomposition(run_dir, step, state.components, state.ci_fn, expert_shard)
     tensors, meta = _read(ckpt_root(run_dir) / str(step) / TRAINING_FILE)
@@ -189,7 +190,7 @@ def restore_state(run_dir: Path, step: int, state) -> None:
         opt.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)})
     for term, adv in state.adversaries.items():
         prefix = f"adversaries/{term}/"
-        adv.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)})
+        adv.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)}, data_rank, data_world)
     sites = {k.split("/")[1] for k in tensors if k.startswith("frequency/")}
     for site in sites:
         state.frequency[site] = FrequencyEMA(

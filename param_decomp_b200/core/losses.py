@@ -98,13 +98,19 @@ class FrequencyEMA:
 
 
 def lp_importance_minimality(ci_upper: dict[str, Tensor], p: float, eps: float, beta: float,
-                             world_size: int = 1) -> Tensor:
-    """Per site: `sum_c [mean_c + beta * mean_c * log2(1 + sum_c * world_size)]` of `(ci+eps)^p`."""
+                             world_size: int = 1, mean_over_ranks=None) -> Tensor:
+    """Per site: `sum_c [mean_c + beta * mean_c * log2(1 + sum_c)]` of `(ci+eps)^p`, with `mean_c` / `sum_c`
+    taken over the GLOBAL batch: `mean_over_ranks` is the differentiable mean over the batch shards (each
+    holds the same number of rows), applied before the logarithm - a per-shard estimate inside the log is
+    biased (Jensen) and would make a data-parallel run differ from the single-process one."""
     total = None
     for c in ci_upper.values():
         vals = (c.float() + eps).pow(p).reshape(-1, c.shape[-1])
-        mean_c, sum_c = vals.mean(0), vals.sum(0)
-        site = (mean_c + beta * mean_c * torch.log2(1 + sum_c * world_size)).sum()
+        mean_c = vals.mean(0)
+        if mean_over_ranks is not None and world_size > 1:
+            mean_c = mean_over_ranks(mean_c)
+        sum_c = mean_c * (vals.shape[0] * world_size)
+        site = (mean_c + beta * mean_c * torch.log2(1 + sum_c)).sum()
         total = site if total is None else total + site
     assert total is not None
     return total

@@ -175,9 +175,12 @@ class GroupOptimizer:
                 fallback.append((n, p, g))
                 continue
             g = g.float() * scale.to(g.device)
+            # optax `scale_by_muon(nesterov=True)`: an EMA momentum and a bias-corrected Nesterov mix of it
+            # with the current gradient (param_decomp/core/muon_stacked.py scale_by_stacked_muon)
+            t, b = self.count, cfg.beta
             mom = self._get(n + "/mom", p)
-            mom.mul_(cfg.beta).add_(g)
-            nesterov = g + cfg.beta * mom
+            mom.mul_(b).add_(g, alpha=1 - b)
+            nesterov = (b / (1 - b ** (t + 1))) * mom + ((1 - b) / (1 - b**t)) * g
             O = newton_schulz(nesterov, cfg.ns_steps, ns_dtype)
             fan_out, fan_in = p.shape[-1], p.shape[-2]
             if cfg.consistent_rms is not None:
@@ -188,7 +191,20 @@ class GroupOptimizer:
                 p.mul_(1 - lr * cfg.weight_decay)
             p.add_(O.float(), alpha=-lr * s)
         if fallback:
-            self._adamw(fallback, scale, lr, 0.9, 0.999, cfg.weight_decay)
+            self._nadam(fallback, scale, lr, 0.9, 0.999)
+
+    def _nadam(self, live, scale: Tensor, lr: float, b1: float, b2: float) -> None:
+        """Muon's rule for leaves that are not matrices: `optax.adamw(b1=0.9, b2=0.999, eps=1e-8,
+        weight_decay=0, nesterov=True)` at the Muon learning rate (param_decomp/core/muon_stacked.py
+        `stacked_muon`, the "adam" partition)."""
+        t = self.count
+        for n, p, g in live:
+            g = g.float() * scale.to(g.device)
+            mu, nu = self._get(n + "/mu", p), self._get(n + "/nu", p)
+            mu.mul_(b1).add_(g, alpha=1 - b1)
+            nu.mul_(b2).addcmul_(g, g, value=1 - b2)
+            mu_hat = (b1 / (1 - b1 ** (t + 1))) * mu + ((1 - b1) / (1 - b1**t)) * g
+            p.add_(mu_hat / ((nu / (1 - b2**t)).sqrt() + 1e-8), alpha=-lr)
 
     # -- checkpoint ----------------------------------------------------------------------------
     def state_dict(self) -> dict[str, Tensor]:

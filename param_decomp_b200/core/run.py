@@ -88,7 +88,7 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
                      positions: int | None, stack_multiple: int = 1, use_fused_optim: bool = False,
                      init_components: Callable[[ComponentStacks], None] | None = None,
                      shard_group: Any = None, shard_backend: str | None = None,
-                     expert_shard: Any = None) -> TrainState:
+                     expert_shard: Any = None, data_rank: int = 0, peer_wait_limit_s: float = 30.0) -> TrainState:
     """Seeded init: `init` / `source` / `run` streams are separated like the reference's
     `split(PRNGKey(seed), 3)`."""
     g = torch.Generator().manual_seed(pd.seed)
@@ -112,7 +112,8 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
         assert isinstance(pd.components_optimizer, AdamWOptimizerConfig), "the sharded optimizer implements AdamW"
         comp_opt = ShardedFlatAdamW(pd.components_optimizer, ["/".join(n.split(".")) for n, _ in comp_named],
                                     [p for _, p in comp_named], pd.steps, shard_group, backend=shard_backend,
-                                    keep_lo=True, norm_group=expert_shard.group if expert_shard is not None else None)
+                                    keep_lo=True, norm_group=expert_shard.group if expert_shard is not None else None,
+                                    wait_limit_s=peer_wait_limit_s)
     else:
         comp_opt = build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim)
     if expert_shard is not None and shard_backend is None:
@@ -131,7 +132,7 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
         shape = getattr(cfg, "source_shape", "bc")
         state.adversaries[term.name] = PersistentAdversary.init(
             getattr(model, "global_sites", model.sites), cfg.optimizer, cfg.source_dtype, shape, batch_rows, positions, src_key,  # type: ignore[attr-defined]
-            pool_size=pool, device=device)
+            pool_size=pool, device=device, data_rank=data_rank)
     return state
 
 
@@ -144,18 +145,27 @@ class RunResult:
 
 
 def _resolve_start(run_dir: Path | None, state: TrainState, cadence: Cadence,
-                   provenance: ResumeProvenance | None, log) -> str:
+                   provenance: ResumeProvenance | None, log, data_rank: int = 0, data_world: int = 1,
+                   collectives: DataCollectives | None = None) -> str:
     """Fresh | Resume(own newest checkpoint) | FineTune(parent V/U + CI fn, step 0)."""
     if run_dir is not None:
         if isinstance(cadence.checkpointing, NoCheckpointing):
+            # one rank owns the marker; every rank learns its verdict (they share the run directory)
             marker = run_dir / NO_REENTRY_MARKER
-            assert not marker.exists(), f"{run_dir} ran without checkpoints: re-entering it is refused"
-            run_dir.mkdir(parents=True, exist_ok=True)
-            marker.write_text("started\n")
+            refused = False
+            if collectives is None or collectives.rank == 0:
+                refused = marker.exists()
+                if not refused:
+                    run_dir.mkdir(parents=True, exist_ok=True)
+                    marker.write_text("started\n")
+            any_fn = getattr(collectives, "host_any", None)
+            if any_fn is not None:
+                refused = bool(any_fn(float(refused)))
+            assert not refused, f"{run_dir} ran without checkpoints: re-entering it is refused"
         else:
             own = ckpt.latest_step(run_dir)
             if own is not None:
-                ckpt.restore_state(run_dir, own, state)
+                ckpt.restore_state(run_dir, own, state, data_rank, data_world)
                 log.info("resumed from %s/ckpts/%d", run_dir, own)
                 return "resume"
     if provenance is not None:
@@ -197,6 +207,7 @@ def run_decomposition_training(
     state_out: list | None = None,
     shard_group: Any = None,
     shard_backend: str | None = None,
+    peer_wait_limit_s: float = 30.0,
     remat_recon_forwards: bool = False,
     remat_ci_fn: bool = False,
 ) -> RunResult:
@@ -214,10 +225,12 @@ def run_decomposition_training(
     rows = batch_rows if batch_rows is not None else pd.batch_size // collectives.world_size
     state = init_train_state(model, ci_fn, pd, objective, device, rows, positions,
                              use_fused_optim=use_fused_optim, init_components=init_components,
-                             shard_group=shard_group, shard_backend=shard_backend, expert_shard=expert_shard)
+                             shard_group=shard_group, shard_backend=shard_backend, expert_shard=expert_shard,
+                             data_rank=getattr(collectives, "data_rank", 0), peer_wait_limit_s=peer_wait_limit_s)
     if state_out is not None:
         state_out.append(state)
-    start_kind = _resolve_start(run_dir, state, cadence, resume_provenance, log)
+    start_kind = _resolve_start(run_dir, state, cadence, resume_provenance, log,
+                                getattr(collectives, "data_rank", 0), collectives.world_size, collectives)
 
     if start_kind != "resume" and isinstance(pd, PDConfig) and pd.faithfulness_warmup_steps > 0:
         last = faithfulness_warmup(ctx, state, pd.faithfulness_warmup_steps, pd.faithfulness_warmup_lr,
@@ -240,6 +253,27 @@ def run_decomposition_training(
     if saving and isinstance(cadence.checkpointing.retention, KeepLastNCheckpoints):  # type: ignore[union-attr]
         keep = cadence.checkpointing.retention.n  # type: ignore[union-attr]
 
+    def check_device_status(where: str) -> None:
+        """The native kernels report a wait that ran out (a late or dead peer) in a per-device status word and
+        then run to completion on whatever data they had, so the parameters can no longer be trusted. Read the
+        word at points where the host waits for the device anyway and stop every rank together, before anything
+        is logged as healthy or written to a checkpoint."""
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            return
+        from param_decomp_b200.ops import native
+
+        if not native.LIB_PATH.exists():
+            return
+        code = int(native.status_word().item())
+        any_fn = getattr(collectives, "host_any", None)
+        bad = bool(any_fn(float(code != 0))) if any_fn is not None else code != 0
+        if bad:
+            native.status_word().zero_()
+            raise native.NativeError(
+                f"{where} (step {state.step}): a device-side wait timed out on this or another rank "
+                f"(local status code {code}); the step's results are not valid, stopping without a checkpoint")
+
     def sync_masters(for_save: bool) -> None:
         """A sharded optimizer keeps each rank's slice of the masters: before anything reads the parameters
         (evaluation, checkpoint) gather them - and, for a save, the moments - on every rank."""
@@ -250,8 +284,11 @@ def run_decomposition_training(
             opt.refresh_full_fp32()
 
     def save() -> None:
+        check_device_status("before a checkpoint")
         if saving:
             sync_masters(for_save=True)
+            for adv in state.adversaries.values():  # per-row sources: every batch shard contributes its rows
+                adv.gather_state(collectives.gather_rows)
         if saving and expert_shard is not None:
             # the ranks of one expert group (the first data shard's) assemble the global stacks; rank 0 writes
             if collectives.in_first_tp_group:
@@ -274,6 +311,7 @@ def run_decomposition_training(
     while state.step < pd.steps:
         step = state.step
         if evaluation is not None and evaluation.is_due(step):
+            check_device_status("before an evaluation")
             sync_masters(for_save=False)
             ev = collectives.average_scalars(evaluation.run(step, state, ctx))
             if sink is not None and ev:
@@ -294,6 +332,7 @@ def run_decomposition_training(
         entry_steps += 1
 
         if cadence.should_log_train(step) or state.step == pd.steps:
+            check_device_status("at a log step")
             scalars = {k: v for k, v in metrics.items()}
             scalars.update(perf.tick(state.step))
             from param_decomp_b200.core.gauge import uv_norm_ratio_metrics

@@ -43,6 +43,25 @@ from param_decomp_b200.core.optim import GroupOptimizer
 from param_decomp_b200.core.rng import StepKey
 
 
+class phase:
+    """NVTX range around one phase of the step (`clean`, `ci_fn`, `adversary`, `losses`, `draws`, `backward`,
+    `optimizer`), so that timelines and captures are attributable; free when no CUDA device is in use
+    (the reference labels the same phases with `jax.named_scope`, param_decomp/core/train.py:1247)."""
+
+    enabled = torch.cuda.is_available()
+
+    def __init__(self, name: str) -> None:
+        self.name = name
+
+    def __enter__(self) -> None:
+        if phase.enabled:
+            torch.cuda.nvtx.range_push("pd/" + self.name)
+
+    def __exit__(self, *exc) -> None:
+        if phase.enabled:
+            torch.cuda.nvtx.range_pop()
+
+
 class DataCollectives:
     """What the step needs from the data-parallel group. The default is a single process; the
     `parallel` package supplies the NCCL / gloo implementation."""
@@ -62,6 +81,10 @@ class DataCollectives:
         """Average `.grad` over data-parallel ranks (no-op for one process)."""
 
     def sum_(self, t: Tensor) -> Tensor:
+        return t
+
+    def gather_rows(self, t: Tensor) -> Tensor:
+        """Concatenation over the batch shards on dim 0 (global-batch layout of a per-row tensor)."""
         return t
 
     def reduce_grads_everywhere(self, params: list[Tensor]) -> None:
@@ -246,7 +269,8 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
     coeff = coeff_override if coeff_override is not None else scheduled_or_constant(cfg.coeff, step, total)
     if isinstance(cfg, L.LpImportanceMinimalityLossConfig):
         p = loss_fns.anneal_linear(cfg.p_start, cfg.p_end, run_fraction(step, total))
-        val = loss_fns.lp_importance_minimality(ci.dense_upper(), p, cfg.eps, cfg.beta, ctx.collectives.world_size)
+        val = loss_fns.lp_importance_minimality(ci.dense_upper(), p, cfg.eps, cfg.beta, ctx.collectives.world_size,
+                                                mean_over_ranks=ctx.collectives.mean)
         metrics["loss/" + cfg.instance_key] = val.detach()
         metrics["schedules/p"] = torch.tensor(p)
         return coeff * val
@@ -331,6 +355,28 @@ def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: i
     return squash(pre)
 
 
+def reduce_source_grads(ctx: StepContext, grads: dict[str, Tensor], batch_shared: bool) -> dict[str, Tensor]:
+    """Gradients of adversary sources under data parallelism, as the global-batch loss defines them
+    (param_decomp/core/init_placed.py:197-235, core/train.py:790-807, core/recon_eval.py:142-257). A source
+    shared over the batch (shape `c`, the evaluation probes) takes the MEAN over the batch shards of the
+    ranks' gradients - one packed all-reduce for all leaves - so every rank ascends the same source. A per-row
+    source (`bc` / `bsc`, every training adversary) belongs to one rank, whose local-mean loss over-weights
+    it by the number of shards."""
+    W = ctx.collectives.world_size
+    if W == 1:
+        return grads
+    if not batch_shared:
+        return {k: g / W for k, g in grads.items()}
+    names = list(grads)
+    flat = ctx.collectives.sum_(torch.cat([grads[k].reshape(-1).float() for k in names])) / W
+    out, off = {}, 0
+    for k in names:
+        n = grads[k].numel()
+        out[k] = flat[off:off + n].view_as(grads[k]).to(grads[k].dtype)
+        off += n
+    return out
+
+
 def ascend_persistent(ctx: StepContext, state: TrainState, term: ReconTerm, weights: ComputeWeights, batch: Any,
                       clean: ForwardResult, ci_lower: dict[str, Tensor], key: StepKey, step: int) -> None:
     adv = state.adversaries[term.name]
@@ -352,8 +398,7 @@ def ascend_persistent(ctx: StepContext, state: TrainState, term: ReconTerm, weig
         names = list(all_leaves)
         grads = torch.autograd.grad(target, [all_leaves[k] for k in names], allow_unused=True)
         gdict = {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, grads)}
-        # sources are per batch row, so their gradients are rank-local: nothing to reduce
-        adv.ascend(gdict, lr, key)
+        adv.ascend(reduce_source_grads(ctx, gdict, adv.batch_shared), lr, key)
 
 
 def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch: Any | None = None) -> dict[str, float]:
@@ -364,7 +409,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     obj = ctx.objective
     metrics: dict[str, Tensor] = {}
 
-    with torch.no_grad():
+    with torch.no_grad(), phase("clean"):
         clean = ctx.model.clean_forward(batch, capture=obj.capture_keys())
     direct = getattr(ctx.model, "backend", "eager_torch") == "fused_sm100"
     sharded = hasattr(state.components_opt, "working_view")  # ZeRO-style optimizer owns grads + working copy
@@ -385,11 +430,13 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         state.components_opt.refresh_full_fp32()
     weights = prepare_compute_weights(state.components, ctx.model.compute_dtype, direct_grads=direct,
                                       working=working)
-    ci = run_ci_fn(ctx, state, clean, step)
-    ci_lower = ci.mask_inputs()
+    with phase("ci_fn"):
+        ci = run_ci_fn(ctx, state, clean, step)
+        ci_lower = ci.mask_inputs()
 
-    for term in obj.persistent_terms():
-        ascend_persistent(ctx, state, term, weights, batch, clean, ci_lower, key, step)
+    with phase("adversary"):
+        for term in obj.persistent_terms():
+            ascend_persistent(ctx, state, term, weights, batch, clean, ci_lower, key, step)
 
     total_loss = None
 
@@ -397,6 +444,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         nonlocal total_loss
         total_loss = x if total_loss is None else total_loss + x
 
+    losses_range = phase("losses")
+    losses_range.__enter__()
     if obj.faith is not None:
         c_f = scheduled_or_constant(obj.faith.coeff, step, total)
         from param_decomp_b200.ops import faithfulness as fused_faith
@@ -447,6 +496,9 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         metrics["loss/" + nl.instance_key] = val.detach()
         add(scheduled_or_constant(nl.coeff, step, total) * val)
 
+    losses_range.__exit__()
+    draws_range = phase("draws")
+    draws_range.__enter__()
     source_grad_requests: list[tuple[ReconTerm, dict[str, Tensor], Tensor]] = []
     B = ctx.model.batch_size(batch)
     for term in obj.recon:
@@ -483,6 +535,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
             tgt = full_mean if term.cfg.adversary_objective == "term" else e2e_mean  # type: ignore[attr-defined]
             source_grad_requests.append((term, all_leaves, tgt))  # type: ignore[arg-type]
 
+    draws_range.__exit__()
     if ctx.nontarget is not None:
         assert nontarget_batch is not None
         add(_nontarget_pass(ctx, state, weights, nontarget_batch, key, step, metrics))
@@ -495,9 +548,12 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     for term, all_leaves, tgt in source_grad_requests:
         names = list(all_leaves)
         gs = torch.autograd.grad(tgt, [all_leaves[k] for k in names], retain_graph=True, allow_unused=True)
-        final_grads.append((term, {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, gs)}))
+        final_grads.append((term, reduce_source_grads(
+            ctx, {k: (g if g is not None else torch.zeros_like(all_leaves[k])) for k, g in zip(names, gs)},
+            state.adversaries[term.name].batch_shared)))
 
-    total_loss.backward()
+    with phase("backward"):
+        total_loss.backward()
     if ctx.expert_shard is not None and sharded:
         assert ctx.expert_shard.by_component, "expert-split component stacks use the replicated-optimizer layout"
         ctx.collectives.reduce_grads_everywhere(state.ci_fn_opt.params)  # component grads: inside the optimizer step
@@ -510,8 +566,9 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     else:
         ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params) + state.ci_fn_opt.params)
 
-    info_c = state.components_opt.step(step)
-    info_f = state.ci_fn_opt.step(step)
+    with phase("optimizer"):
+        info_c = state.components_opt.step(step)
+        info_f = state.ci_fn_opt.step(step)
     metrics["grad_norm/components"] = state.components_opt.last_grad_norm_t.detach()
     metrics["grad_norm/ci_fn"] = state.ci_fn_opt.last_grad_norm_t.detach()
     metrics["schedules/lr_components"] = torch.tensor(info_c["lr"])
@@ -549,8 +606,9 @@ def fresh_pgd_sources(ctx: StepContext, term: ReconTerm, weights: ComputeWeights
         e2e, _ = masked_recon(ctx, w_d, batch, clean, masks, term, step, with_aux=False)
         names = list(leaves)
         gs = torch.autograd.grad(e2e, [leaves[k] for k in names], allow_unused=True)
-        adv_mod.sign_ascent_(leaves, {k: (g if g is not None else torch.zeros_like(leaves[k])) for k, g in zip(names, gs)},
-                             cfg.step_size)  # type: ignore[attr-defined]
+        adv_mod.sign_ascent_(leaves, reduce_source_grads(
+            ctx, {k: (g if g is not None else torch.zeros_like(leaves[k])) for k, g in zip(names, gs)},
+            cfg.source_shape == "c"), cfg.step_size)  # type: ignore[attr-defined]
     return {k: v.detach() for k, v in leaves.items()}
 
 
@@ -610,7 +668,26 @@ def faithfulness_warmup(ctx: StepContext, state: TrainState, steps: int, lr: flo
     if steps == 0:
         return float("nan")
     params = list(state.components.parameters())
+    # A sharded optimizer (and the fused backend's direct weight gradients) keep every `.grad` as a view of
+    # their own flat buffer. The warm-up must not replace those views: park them, run on private gradients,
+    # and put the (zeroed) views back afterwards.
+    parked = [p.grad for p in params]
+    for p in params:
+        p.grad = None
     opt = torch.optim.AdamW(params, lr=lr, weight_decay=weight_decay, betas=(0.9, 0.999), eps=1e-8)
+    last = float("nan")
+    try:
+        last = _faithfulness_warmup_loop(ctx, state, opt, steps, log)
+    finally:
+        for p, g in zip(params, parked):
+            p.grad = g
+            if g is not None:
+                g.zero_()
+    return last
+
+
+def _faithfulness_warmup_loop(ctx: StepContext, state: TrainState, opt: torch.optim.Optimizer, steps: int,
+                              log: Callable[[int, float], None] | None) -> float:
     last = float("nan")
     for i in range(steps):
         opt.zero_grad(set_to_none=True)

@@ -20,7 +20,7 @@ from param_decomp_b200.core import masking
 from param_decomp_b200.core.components import prepare_compute_weights
 from param_decomp_b200.core.objective import ReconTerm
 from param_decomp_b200.core.rng import StepKey
-from param_decomp_b200.core.train import StepContext, TrainState, masked_recon, run_ci_fn
+from param_decomp_b200.core.train import StepContext, TrainState, masked_recon, reduce_source_grads, run_ci_fn
 
 
 @torch.no_grad()
@@ -73,8 +73,8 @@ def fresh_pgd_recon(ctx: StepContext, state: TrainState, batch: Any, step_size: 
             loss = ctx.model.recon_loss(clean, ctx.model.masked_forward(weights, batch, masks))
             names = list(leaves)
             gs = torch.autograd.grad(loss, [leaves[k] for k in names], allow_unused=True)
-            adv_mod.sign_ascent_(leaves, {k: (g if g is not None else torch.zeros_like(leaves[k]))
-                                          for k, g in zip(names, gs)}, step_size)
+            adv_mod.sign_ascent_(leaves, reduce_source_grads(ctx, {
+                k: (g if g is not None else torch.zeros_like(leaves[k])) for k, g in zip(names, gs)}, True), step_size)
         done = target
         with torch.no_grad():
             src, dlt = adv_mod.PersistentAdversary.split(leaves)

@@ -84,7 +84,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     fused = getattr(run.model, "backend", "") == "fused_sm100"
     flops = decomposition_step_flops(run.model, run.ci_fn, cfg.pd, cfg.data.seq_len)
     try:
-        return run_decomposition_training(
+        result = run_decomposition_training(
             run.model, run.ci_fn, cfg.pd, cfg.cadence, run.sample_train, device=topo.device, run_dir=run_dir,
             sink=sink, evaluation=evaluation, collectives=collectives, resume_provenance=cfg.resume_provenance,
             batch_rows=cfg.pd.batch_size // topo.data_world, positions=cfg.data.seq_len,
@@ -92,12 +92,17 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
             max_steps_this_entry=max_steps_this_entry, state_out=state_out,
             profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
-            shard_group=shard_group, shard_backend=shard_backend,
+            shard_group=shard_group, shard_backend=shard_backend, peer_wait_limit_s=cfg.runtime.peer_wait_limit_s,
             remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn)
-    finally:
+    except BaseException:
         if sink is not None:
             sink.close()
-        topo.shutdown()
+        topo.shutdown(failed=True)
+        raise
+    if sink is not None:
+        sink.close()
+    topo.shutdown()
+    return result
 
 
 def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, run_id: str | None = None,
@@ -144,7 +149,7 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
     evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir) if cfg.eval is not None else None
     fused = getattr(run.model, "backend", "") == "fused_sm100"
     try:
-        return run_decomposition_training(
+        result = run_decomposition_training(
             run.model, run.ci_fn, cfg.pd, cfg.cadence, sample_target, device=topo.device, run_dir=run_dir, sink=sink,
             evaluation=evaluation, collectives=topo.collectives(), nontarget=nontarget,
             remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn,
@@ -153,7 +158,12 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
                                                                           + nt_rows * cfg.data.seq_len),
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
             max_steps_this_entry=max_steps_this_entry, state_out=state_out)
-    finally:
+    except BaseException:
         if sink is not None:
             sink.close()
-        topo.shutdown()
+        topo.shutdown(failed=True)
+        raise
+    if sink is not None:
+        sink.close()
+    topo.shutdown()
+    return result

@@ -44,7 +44,8 @@ enum PdNoAllocStatus {
 //
 // The first call on each device resolves the array's device address (one
 // cudaGetSymbolAddress with that device current) and caches it. Make that first call outside any
-// stream capture.
+// stream capture. The cache is guarded by a mutex, so host threads may make their first calls
+// concurrently; that guards the address only, not the array's contents (see above).
 //
 // Returns a PdNoAllocStatus; pd_noalloc_strerror turns it into text. Sizes beyond
 // PD_NOALLOC_CLIP_MAX_ELEMS are refused with PD_NOALLOC_TOO_LARGE and nothing is launched.

@@ -6,6 +6,8 @@
 // is read that this call did not write.
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "noalloc.h"
 
 namespace {
@@ -18,6 +20,7 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) float g_clip_scratch[PD_NOALLOC_CLIP_SCRATCH_SLOTS];
 
 float* g_scratch_addr[kMaxDevices] = {};  // resolved once per device
+std::mutex g_scratch_mutex;               // two host threads may make the first call on a device together
 
 __global__ void partial_sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ slots) {
   float acc = 0.f;
@@ -58,6 +61,7 @@ __global__ void finish_clip_kernel(const float* __restrict__ slots, int n_slots,
 int resolve_scratch(float** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PD_NOALLOC_SETUP_FAILED;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);  // (locking a std::mutex allocates nothing)
   if (g_scratch_addr[dev] == nullptr) {
     float* ptr = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_clip_scratch) != cudaSuccess || ptr == nullptr)

@@ -81,7 +81,7 @@ class ShardedFlatAdamW:
     total_steps: int
     group: object | None  # data-parallel process group (None = single process)
     backend: str = "collective"  # "fused_p2p" | "collective"
-    wait_limit_s: float = 2.0
+    wait_limit_s: float = 30.0  # a peer may be late by a checkpoint write or an evaluation, not by a dead process
     keep_lo: bool = False  # also publish bf16(p - bf16(p)): split-precision operands for faithfulness
     norm_group: object | None = None  # leaves are slices of stacks split over this group: its ranks' squares add up
     count: int = 0
@@ -129,14 +129,22 @@ class ShardedFlatAdamW:
         self.nu = torch.zeros_like(self.master)
         self.norm_out = torch.zeros(1, device=dev, dtype=torch.float32)
         self.full_fp32 = full  # kept so `.data` of every parameter stays a valid fp32 view
-        for p, o in zip(self.params, self.offsets):
-            p.data = self.full_fp32[o:o + p.numel()].view_as(p)
-            p.grad = self.grad_flat[o:o + p.numel()].view_as(p)
+        self._attach_views()
         if self.group is not None and self.backend == "fused_p2p":
             torch.cuda.synchronize()
             dist.barrier(group=self.group)
 
     # -- views ---------------------------------------------------------------------------------
+    def _attach_views(self) -> None:
+        """Point every parameter's storage and `.grad` at its slice of the flat buffers."""
+        for p, o in zip(self.params, self.offsets):
+            p.data = self.full_fp32[o:o + p.numel()].view_as(p)
+            p.grad = self.grad_flat[o:o + p.numel()].view_as(p)
+
+    def _grads_attached(self) -> bool:
+        base = self.grad_flat.data_ptr()
+        return all(p.grad is not None and p.grad.data_ptr() == base + 4 * o for p, o in zip(self.params, self.offsets))
+
     def working_lo_view(self, index: int) -> Tensor:
         assert self.work_lo_flat is not None
         p, o = self.params[index], self.offsets[index]
@@ -159,6 +167,8 @@ class ShardedFlatAdamW:
     # -- the step ------------------------------------------------------------------------------
     @torch.no_grad()
     def step(self, step_idx: int) -> dict[str, float]:
+        assert self._grads_attached(), \
+            "a parameter's .grad no longer aliases the flat gradient buffer (something replaced it; gradients would be lost)"
         lr = self.lr_at(step_idx)
         self.count += 1
         self.applied_learning_rate = lr
@@ -284,6 +294,9 @@ class ShardedFlatAdamW:
 
     def sync_from_parameters(self) -> None:
         """Adopt the values currently in the parameters' storage (after a restore or an in-place edit)."""
+        if not self._grads_attached():  # an outside optimizer replaced the views: adopt values, re-home gradients
+            self._attach_views()
+            self.grad_flat.zero_()
         self.master.copy_(self.full_fp32[self.shard_off:self.shard_off + self.shard_len])
         self.work_flat.copy_(self.full_fp32)
         if self.work_lo_flat is not None:

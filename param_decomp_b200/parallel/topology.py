@@ -78,6 +78,18 @@ class DistCollectives(DataCollectives):
     def row_offset(self, local_rows: int) -> int:
         return self.data_rank * local_rows
 
+    def gather_rows(self, t: Tensor) -> Tensor:
+        if self.world_size == 1:
+            return t
+        src = t.contiguous()
+        as_int = src.dtype == torch.uint16  # no collective for uint16: move the bits
+        if as_int:
+            src = src.view(torch.int16)
+        parts = [torch.empty_like(src) for _ in range(self.world_size)]
+        dist.all_gather(parts, src, group=self.topo.data_group)
+        full = torch.cat(parts, dim=0)
+        return full.view(torch.uint16) if as_int else full
+
     def reduce_grads_everywhere(self, params: list[Tensor]) -> None:
         self.reduce_grads(params, group=None, world=self.topo.world)
 
@@ -207,9 +219,12 @@ class Topology:
         dist.broadcast_object_list(box, src=0, group=self.cpu_group)
         return box[0]
 
-    def shutdown(self) -> None:
+    def shutdown(self, failed: bool = False) -> None:
+        """Leave the job. A rank that is unwinding from an exception (`failed`) does not wait for the others
+        at a barrier they may never reach - their next collective ends with an error instead."""
         if self.owns_process_group and dist.is_initialized():
-            dist.barrier(group=self.cpu_group)
+            if not failed:
+                dist.barrier(group=self.cpu_group)
             dist.destroy_process_group()
 
 

@@ -2,13 +2,11 @@ import copy
 
 import pytest
 import torch
-import yaml
 
 from param_decomp_b200.config.experiments import LMExperimentConfig
 from param_decomp_b200.core.ci_fn.transformer import CIAttention, ComponentConditioning
 from param_decomp_b200.experiments.lm.build import build_lm_run
 
-BASE = yaml.safe_load(open("_work/lm_tiny.yaml")) if False else None
 
 
 def tiny(ci: dict, family="glu_transformer", cs=None) -> LMExperimentConfig:

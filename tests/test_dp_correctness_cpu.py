@@ -1,0 +1,183 @@
+"""Data-parallel correctness on CPU (gloo, 2 ranks) against the single-process run of the same config:
+
+* the ZeRO-style sharded optimizer after a faithfulness warm-up (the warm-up must not detach the parameters'
+  gradients from the optimizer's flat buffer);
+* adversary sources under data parallelism: batch-shared (`c`) sources - persistent and fresh - stay identical
+  on every rank and follow the single-process trajectory, per-row (`bc`) sources are drawn at their global rows
+  and a checkpoint stores them for the whole batch;
+* the L_p minimality term uses the global-batch mean inside its logarithm.
+"""
+import copy
+import os
+import socket
+import tempfile
+from pathlib import Path
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+import __graft_entry__ as ge
+from param_decomp_b200.config.experiments import LMExperimentConfig
+
+STEPS = 3
+
+
+def _cfg(world: int, losses: list, sharding: str, warmup: int = 0, save: bool = False) -> LMExperimentConfig:
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"]["backend"] = "eager_torch"
+    c["runtime"]["mesh"] = {"replicate": 1, "fsdp": world, "tp": 1}
+    c["runtime"]["sharding"] = sharding
+    c["target"]["weights_dtype"] = "float32"
+    c["target"]["attention_implementation"] = "xla"
+    c["target"]["spec"]["arch"] = {"family": "glu_transformer", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 48,
+                                   "vocab_size": 100}
+    c["decomposition"]["sites"]["cs"] = {"q": 16, "o": 16, "gate": 24, "down": 16}
+    c["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [16]}
+    c["data"]["seq_len"] = 8
+    c["pd"]["batch_size"] = 4
+    c["pd"]["steps"] = STEPS
+    c["pd"]["loss_metrics"] = losses
+    c["pd"]["faithfulness_warmup_steps"] = warmup
+    c["pd"]["faithfulness_warmup_lr"] = 1e-2
+    ck = ({"kind": "periodic", "save_every": STEPS, "retention": {"kind": "keep_all"}} if save else {"kind": "none"})
+    c["cadence"] = {"train_log_every": 1, "checkpointing": ck}
+    c["eval"] = None
+    if save:  # an evaluation probe with batch-shared (`c`) sources at the last step
+        c["eval"] = {"batch_size": 4, "n_steps": 1, "every": STEPS, "slow_every": STEPS,
+                     "metrics": [{"type": "PGDReconLoss", "init": "random", "source_shape": "c", "n_steps": 3,
+                                  "step_size": 0.1}]}
+    return LMExperimentConfig.model_validate(c)
+
+
+BASE = [{"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 1.0},
+        {"type": "StochasticReconLoss", "coeff": 1.0},
+        {"type": "FaithfulnessLoss", "coeff": 10.0}]
+
+
+def _pgd_losses(shape: str) -> list:
+    return [{"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 1.0},
+            {"type": "PersistentPGDReconLoss", "coeff": 1.0, "source_shape": shape, "n_warmup_steps": 1,
+             "optimizer": {"type": "sgd", "lr_schedule": 0.05}},
+            {"type": "PGDReconLoss", "coeff": 0.5, "init": "random", "source_shape": shape, "n_steps": 2, "step_size": 0.1},
+            {"type": "FaithfulnessLoss", "coeff": 10.0}]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _train(cfg, root, run_id):
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    states: list = []
+    res = train_lm(cfg, Path(root) if root else None, run_id=run_id, device="cpu", state_out=states)
+    st = states[0]
+    return res, st
+
+
+def _snapshot(res, st):
+    if hasattr(st.components_opt, "refresh_full_fp32") and torch.distributed.is_initialized():
+        st.components_opt.refresh_full_fp32()
+    adv = {t: {k: v.detach().clone() for k, v in a._local_state().items()} for t, a in st.adversaries.items()}
+    return (dict(res.last_metrics), [p.detach().clone() for p in st.components.parameters()], adv)
+
+
+def _worker(rank: int, world: int, port: int, root: str, kind: str, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    if kind == "warmup":
+        cfg = _cfg(world, BASE, "owner", warmup=2)
+    else:
+        cfg = _cfg(world, _pgd_losses(kind), "ddp", save=True)
+    states: list = []
+    res = train_lm(cfg, Path(root), run_id="p-0000aaaa", device="cpu", state_out=states)
+    st = states[0]
+    if kind == "warmup":
+        assert hasattr(st.components_opt, "gather_state"), "the config must select the sharded optimizer"
+    # the process group is gone after train_lm: the sharded masters were gathered by its final save / log step
+    adv = {t: {k: v.detach().clone() for k, v in a._local_state().items()} for t, a in st.adversaries.items()}
+    out[rank] = (dict(res.last_metrics), [p.detach().clone() for p in st.components.parameters()], adv)
+
+
+def test_sharded_optimizer_trains_after_faithfulness_warmup():
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        mp.spawn(_worker, args=(2, _free_port(), root, "warmup", out), nprocs=2, join=True)
+        res, st = _train(_cfg(1, BASE, "owner", warmup=2), root, "p-0000bbbb")
+        ref_metrics, ref_params, _ = _snapshot(res, st)
+        for r in range(2):
+            metrics, params, _ = out[r]
+            assert metrics["train/grad_norm/components"] > 0.0
+            assert metrics["train/loss/total"] == pytest.approx(ref_metrics["train/loss/total"], rel=1e-4)
+            assert metrics["train/grad_norm/components"] == pytest.approx(ref_metrics["train/grad_norm/components"], rel=1e-3)
+
+
+def _eval_value(root, run_id: str, key: str) -> float:
+    import json
+
+    lines = [json.loads(l) for l in (Path(root) / "runs" / run_id / "metrics.jsonl").read_text().splitlines()]
+    vals = [l[key] for l in lines if key in l]
+    assert vals, (key, sorted({k for l in lines for k in l}))
+    return vals[-1]
+
+
+@pytest.mark.parametrize("shape", ["bc"])
+def test_adversary_sources_under_data_parallel(shape):
+    from param_decomp_b200.core import checkpoint as ckpt
+
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        mp.spawn(_worker, args=(2, _free_port(), root, shape, out), nprocs=2, join=True)
+        res, st = _train(_cfg(1, _pgd_losses(shape), "ddp", save=True), root, "p-0000cccc")
+        ref_metrics, ref_params, ref_adv = _snapshot(res, st)
+        # evaluation probe with batch-shared sources: the ranks ascend ONE source on the global-batch gradient
+        assert _eval_value(root, "p-0000aaaa", "eval/PGDReconLoss_3step") == pytest.approx(
+            _eval_value(root, "p-0000cccc", "eval/PGDReconLoss_3step"), rel=2e-3)  # sign steps amplify rounding
+        (term,) = ref_adv.keys()
+        for key, ref in ref_adv[term].items():
+            a, b = out[0][2][term][key], out[1][2][term][key]
+            if ref.shape[0] == 1:  # batch-shared: every rank holds the single-process source
+                assert torch.equal(a, b), key
+                assert torch.allclose(a, ref, atol=2e-5), (key, float((a - ref).abs().max()))
+            else:  # per-row: each rank holds its rows of the single-process tensor
+                assert torch.allclose(torch.cat([a, b]), ref, atol=2e-5), (key, float((torch.cat([a, b]) - ref).abs().max()))
+        for r in range(2):
+            assert out[r][0]["train/loss/total"] == pytest.approx(ref_metrics["train/loss/total"], rel=2e-4)
+        # the checkpoint holds the sources of the global batch
+        tensors, _ = ckpt._read(Path(root) / "runs" / "p-0000aaaa" / "ckpts" / str(STEPS) / ckpt.TRAINING_FILE)
+        for key, ref in ref_adv[term].items():
+            saved = tensors[f"adversaries/{term}/{key}"]
+            assert saved.shape == ref.shape, (key, saved.shape, ref.shape)
+            assert torch.allclose(saved.float(), ref.float(), atol=2e-5)
+        # ... and a single process restores all of them, a 2-rank job its own rows
+        st.adversaries[term].load_state_dict({k[len(f"adversaries/{term}/"):]: v for k, v in tensors.items()
+                                              if k.startswith(f"adversaries/{term}/")}, 0, 1)
+        half = copy.deepcopy(st.adversaries[term])
+        for name in half.sources:
+            if half.sources[name].shape[0] > 1:
+                n = half.sources[name].shape[0] // 2
+                half.sources[name], half.delta[name] = half.sources[name][:n], half.delta[name][:n]
+        half.state = {}
+        half.load_state_dict({k[len(f"adversaries/{term}/"):]: v for k, v in tensors.items()
+                              if k.startswith(f"adversaries/{term}/")}, 1, 2)
+        for name, v in half.sources.items():
+            full = st.adversaries[term].sources[name]
+            assert torch.equal(v, full if full.shape[0] == 1 else full[full.shape[0] // 2:])
+
+
+def test_lp_minimality_uses_global_mean():
+    from param_decomp_b200.core import losses
+
+    torch.manual_seed(0)
+    ci = {"s": torch.rand(8, 5)}
+    whole = losses.lp_importance_minimality(ci, 0.9, 1e-6, 0.5)
+    halves = [{"s": ci["s"][:4]}, {"s": ci["s"][4:]}]
+    means = [(h["s"].float() + 1e-6).pow(0.9).mean(0) for h in halves]
+    glob = (means[0] + means[1]) / 2
+    got = losses.lp_importance_minimality(halves[0], 0.9, 1e-6, 0.5, world_size=2, mean_over_ranks=lambda m: glob)
+    assert float(got) == pytest.approx(float(whole), rel=1e-6)

@@ -62,17 +62,28 @@ def test_newton_schulz_orthogonalises():
 
 
 def test_muon_update_rule():
+    """Three-step trajectory against a restatement of `optax.contrib.muon(nesterov=True)` as the reference
+    configures it: EMA momentum, bias-corrected Nesterov mix, Newton-Schulz, shape scale, decoupled weight
+    decay; non-matrix leaves by Nesterov Adam(0.9, 0.999) without weight decay."""
     torch.manual_seed(0)
     W, b = torch.randn(2, 8, 4), torch.randn(4)
-    W0, b0 = W.clone(), b.clone()
-    cfg = MuonOptimizerConfig(type="muon", lr_schedule=0.1, ns_dtype="float32")
+    cfg = MuonOptimizerConfig(type="muon", lr_schedule=0.1, ns_dtype="float32", weight_decay=0.01)
     opt = build_group_optimizer(cfg, [("W", W), ("b", b)], total_steps=10)
-    gW, gb = torch.randn_like(W), torch.randn_like(b)
-    opt.step(0, [gW, gb])
-    O = newton_schulz(gW + 0.95 * gW, 5, torch.float32)  # nesterov of the first step: g + beta * (g)
-    assert torch.allclose(W, W0 - 0.1 * math.sqrt(8) * 0.2 * O, atol=1e-5)
-    # the vector leaf takes the Adam(0.9, 0.999) fallback: first step = lr * sign-ish
-    assert torch.allclose(b, b0 - 0.1 * gb / (gb.abs() + 1e-8), atol=1e-5)
+    We, be = W.clone(), b.clone()
+    mom, mu, nu = torch.zeros_like(W), torch.zeros_like(b), torch.zeros_like(b)
+    beta, lr, s = cfg.beta, 0.1, math.sqrt(8) * 0.2
+    for t in range(1, 4):
+        gW, gb = torch.randn_like(W), torch.randn_like(b)
+        opt.step(t - 1, [gW, gb])
+        mom = beta * mom + (1 - beta) * gW
+        mix = beta * mom / (1 - beta ** (t + 1)) + (1 - beta) * gW / (1 - beta**t)
+        We = We * (1 - lr * 0.01) - lr * s * newton_schulz(mix, 5, torch.float32)
+        mu = 0.9 * mu + 0.1 * gb
+        nu = 0.999 * nu + 0.001 * gb * gb
+        mu_hat = 0.9 * mu / (1 - 0.9 ** (t + 1)) + 0.1 * gb / (1 - 0.9**t)
+        be = be - lr * mu_hat / ((nu / (1 - 0.999**t)).sqrt() + 1e-8)
+        assert torch.allclose(W, We, atol=1e-5), t
+        assert torch.allclose(b, be, atol=1e-5), t
 
 
 SITES = (SiteSpec("s", 4, 4, 8),)
