@@ -105,6 +105,8 @@ def main() -> None:
     ap.add_argument("--expert-dispatch", type=str, default="allreduce", choices=["allreduce", "all_to_all"],
                     help="with --tp on a mixture-of-experts target: tokens replicated over the tp group and partial "
                          "outputs summed, or the batch sharded over it too and jobs stored into their expert's owner")
+    ap.add_argument("--no-record", action="store_true",
+                    help="issue every step launch by launch from Python instead of replaying the recorded CUDA graph")
     ap.add_argument("--kernel-table", type=Path, default=None,
                     help="after the timed steps, run one more step under the torch profiler and write the kernels "
                          "ranked by device time to this file (never part of a reported number)")
@@ -157,9 +159,14 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up (also allocates gradient buffers and the caching allocator's pools)
-    for s in range(args.warmup):
-        train_step(ctx, state, run.sample_train(s))
+    # The public step API: eager for its first steps, then recorded as a CUDA graph and replayed.
+    # Warm-up = W eager steps (they allocate gradient buffers and size the allocator's pools) plus, when the
+    # step is recorded, the recording call and one replay - all untimed.
+    from param_decomp_b200.core.recorded_step import RecordedTrainStep
+
+    step_fn = RecordedTrainStep(ctx, state, enabled=not args.no_record, eager_steps=args.warmup)
+    for s in range(args.warmup + (2 if step_fn.eligible else 0)):
+        step_fn(run.sample_train(s))
     native.check_status()
 
     # ---- end to end: pinned host tokens -> device, step, loss back to the host, every step ----
@@ -172,7 +179,7 @@ def main() -> None:
     sync()
     t0 = time.perf_counter()
     for hb in host_batches:
-        m = train_step(ctx, state, hb.to(topo.device, non_blocking=True))
+        m = step_fn(hb.to(topo.device, non_blocking=True))  # pinned host tokens -> device, every step
         loss_host = float(m["loss/total"])  # device -> host read of the step's result
     sync()
     e2e_s = time.perf_counter() - t0
@@ -193,7 +200,7 @@ def main() -> None:
         torch.cuda.profiler.start()
     e0.record()
     for b in dev_batches:
-        train_step(ctx, state, b)
+        step_fn(b)
     e1.record()
     if args.profile_range:
         torch.cuda.synchronize()
@@ -206,7 +213,7 @@ def main() -> None:
         from torch.profiler import ProfilerActivity, profile
 
         with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
-            train_step(ctx, state, dev_batches[0])
+            step_fn(dev_batches[0])
             torch.cuda.synchronize()
         if topo.rank == 0:
             args.kernel_table.parent.mkdir(parents=True, exist_ok=True)
@@ -237,6 +244,8 @@ def main() -> None:
                 "decomposition": (", ".join(f"{k}:{v}" for k, v in cfg.decomposition.sites.cs.items())
                                   + f" components per matrix x {arch.n_layer} layers; CI fn {cfg.decomposition.ci.type}"),
                 "losses": ", ".join(type(m).__name__ for m in cfg.pd.loss_metrics),
+                "step_issue": ("one CUDA graph per step (recorded after the eager warm-up)" if step_fn.graph is not None
+                               else f"launch by launch ({step_fn.reason})"),
                 "l2": "per-step working set (>4 GB parameters and optimizer state, >20 GB activations) "
                       "exceeds the 126 MB L2; no explicit flush between steps",
             },

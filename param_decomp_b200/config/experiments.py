@@ -614,6 +614,10 @@ class RuntimeConfig(BaseConfig):
     backend: Literal["eager_torch", "fused_sm100"] = "fused_sm100"
     """Addition. `fused_sm100`: the hand-written sm_100a kernels (GPU only, fails loudly without
     them). `eager_torch`: plain PyTorch ops, the CPU oracle and the correctness reference."""
+    step_recording: Literal["cuda_graph", "off"] = "cuda_graph"
+    """Addition. `cuda_graph`: on the fused backend the train step is recorded into a CUDA graph after a few
+    eager steps and replayed (per-step scalars live in a device table); runs whose step keeps per-step state
+    on the host (persistent adversaries, frequency EMA, Muon, ...) stay eager and say so in the log."""
     peer_wait_limit_s: float = 30.0
     """Addition. How long a kernel that exchanges data with peer GPUs waits for a peer before it gives up and
     reports through the device status word (the engine then stops every rank before the next log line,

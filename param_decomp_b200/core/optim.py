@@ -107,6 +107,8 @@ class GroupOptimizer:
     last_grad_norm: float = 0.0
     use_fused: bool = False
     norm_fn: Any = None  # (names, grads) -> global L2 norm, for leaves that are split over a process group
+    scalars: Any = None  # ops.step_scalars.StepScalars: learning rate and bias corrections live in device memory
+    label: str = "group"
 
     def lr_at(self, step: int) -> float:
         return get_scheduled_value(min(step, self.total_steps), self.total_steps, self.cfg.lr_schedule)
@@ -127,12 +129,14 @@ class GroupOptimizer:
         elif self.use_fused and live and live[0][1].is_cuda:
             from param_decomp_b200.ops import optim as fused
 
-            norm, scale = fused.grad_norm_and_scale([g for _, _, g in live], self.cfg.grad_clip_norm)
+            norm, scale = fused.grad_norm_and_scale_multi([p for _, p, _ in live], [g for _, _, g in live],
+                                                          self.cfg.grad_clip_norm)
         else:
             norm = global_norm([g for _, _, g in live])
             scale = clip_scale(norm, self.cfg.grad_clip_norm)
         lr = self.lr_at(step_idx)
         self.count += 1
+        self._step_idx = step_idx
         self.applied_learning_rate = lr
         self.last_grad_norm_t = norm
         if isinstance(self.cfg, AdamWOptimizerConfig):
@@ -144,16 +148,27 @@ class GroupOptimizer:
     def grad_norm(self) -> float:
         return float(self.last_grad_norm_t)
 
+    def advance_replayed(self) -> None:
+        """Host bookkeeping of a step whose launches ran from a recording (no Python ran for it)."""
+        self.count += 1
+        self._step_idx = getattr(self, "_step_idx", -1) + 1
+        self.applied_learning_rate = self.lr_at(self._step_idx)
+
     def _adamw(self, live, scale: Tensor, lr: float, b1: float, b2: float, wd: float) -> None:
         t = self.count
         bc1, bc2 = 1 - b1**t, 1 - b2**t
         if self.use_fused and live and live[0][1].is_cuda:
             from param_decomp_b200.ops import optim as fused
 
-            fused.adamw_step([p for _, p, _ in live], [g for _, _, g in live],
-                             [self._get(n + "/mu", p) for n, p, _ in live],
-                             [self._get(n + "/nu", p) for n, p, _ in live],
-                             lr=lr, b1=b1, b2=b2, eps=1e-8, wd=wd, bc1=bc1, bc2=bc2, grad_scale=scale)
+            hyper = None
+            if self.scalars is not None:
+                off = t - self._step_idx  # updates so far minus steps so far (constant within a run entry)
+                hyper = self.scalars.f32_block(f"opt/{self.label}/hyper", 3, lambda s: (
+                    self.lr_at(s), 1.0 / (1 - b1 ** (s + off)), 1.0 / (1 - b2 ** (s + off))))
+            fused.adamw_step_multi([p for _, p, _ in live], [g for _, _, g in live],
+                                   [self._get(n + "/mu", p) for n, p, _ in live],
+                                   [self._get(n + "/nu", p) for n, p, _ in live],
+                                   lr=lr, b1=b1, b2=b2, eps=1e-8, wd=wd, bc1=bc1, bc2=bc2, grad_scale=scale, hyper=hyper)
             return
         for n, p, g in live:
             g = g.float() * scale.to(g.device)

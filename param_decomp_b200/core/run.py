@@ -208,6 +208,7 @@ def run_decomposition_training(
     shard_group: Any = None,
     shard_backend: str | None = None,
     peer_wait_limit_s: float = 30.0,
+    record_step: bool = False,
     remat_recon_forwards: bool = False,
     remat_ci_fn: bool = False,
 ) -> RunResult:
@@ -299,6 +300,12 @@ def run_decomposition_training(
         if barrier is not None:
             barrier()
 
+    from param_decomp_b200.core.recorded_step import RecordedTrainStep
+
+    stepper = RecordedTrainStep(ctx, state, enabled=record_step)
+    if record_step:
+        log.info("train step: %s", "recorded as a CUDA graph after 3 eager steps" if stepper.eligible
+                 else f"eager ({stepper.reason})")
     result = RunResult(final_step=state.step, stopped_by_sigterm=False, run_dir=run_dir)
     entry_steps = 0
     profiler = None
@@ -323,7 +330,7 @@ def run_decomposition_training(
         nt_batch = sample_nontarget_batch(step) if sample_nontarget_batch is not None else None
         if profiler is not None and entry_steps == 2:
             profiler.start()
-        metrics = train_step(ctx, state, batch, nt_batch)
+        metrics = stepper(batch, nt_batch)
         if profiler is not None and entry_steps == 2 + profile_steps - 1:
             profiler.stop()
             (Path(run_dir) / "profile").mkdir(parents=True, exist_ok=True)  # type: ignore[arg-type]

@@ -133,6 +133,21 @@ class StepContext:
     # a masked forward / the CI function keeps only its inputs and is run again during the backward pass
     remat_recon_forwards: bool = False
     remat_ci_fn: bool = False
+    # `ops.step_scalars.StepScalars`: when set, everything the host computes per step (Philox seed word,
+    # scheduled coefficients, learning rates and bias corrections) is read by the kernels from a device
+    # table instead of being passed by value, so the step's launches can be recorded once and replayed
+    scalars: Any = None
+
+    def sched(self, name: str, value: Any, step: int):
+        """A scheduled quantity at `step`: a python float, or - for a real schedule while the step keeps its
+        scalars in device memory - the 0-d device tensor that holds it. Bare floats never change and stay
+        python numbers."""
+        from param_decomp_b200.config.schedule import ScheduleConfig
+
+        total = self.pd.steps
+        if self.scalars is None or not isinstance(value, ScheduleConfig):
+            return scheduled_or_constant(value, step, total)
+        return self.scalars.f32("sched/" + name, lambda s: get_scheduled_value(min(s, total), total, value))
 
     def weights_sq_host(self) -> dict[str, float]:
         """`||W_s||^2` as host floats (read back once, then cached)."""
@@ -175,7 +190,7 @@ def _aux_loss(term: ReconTerm, clean: ForwardResult, masked: ForwardResult, step
         mean = torch.stack(vals).mean()
         if metrics is not None:
             metrics[f"loss/{term.name}/{aux.name}"] = mean.detach()
-        c = scheduled_or_constant(aux.coeff, step, total)
+        c = scheduled_or_constant(aux.coeff, step, total)  # (terms with auxiliaries are not recorded)
         total_aux = c * mean if total_aux is None else total_aux + c * mean
     return total_aux
 
@@ -266,7 +281,7 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
                         coeff_override: float | None = None, update_ema: bool = True) -> Tensor:
     cfg = ctx.objective.minimality
     total = ctx.pd.steps
-    coeff = coeff_override if coeff_override is not None else scheduled_or_constant(cfg.coeff, step, total)
+    coeff = coeff_override if coeff_override is not None else ctx.sched("minimality", cfg.coeff, step)
     if isinstance(cfg, L.LpImportanceMinimalityLossConfig):
         p = loss_fns.anneal_linear(cfg.p_start, cfg.p_end, run_fraction(step, total))
         val = loss_fns.lp_importance_minimality(ci.dense_upper(), p, cfg.eps, cfg.beta, ctx.collectives.world_size,
@@ -274,8 +289,8 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
         metrics["loss/" + cfg.instance_key] = val.detach()
         metrics["schedules/p"] = torch.tensor(p)
         return coeff * val
-    gamma = get_scheduled_value(step, total, cfg.gamma)
-    metrics["schedules/gamma"] = torch.tensor(gamma)
+    gamma = ctx.sched("gamma", cfg.gamma, step)
+    metrics["schedules/gamma"] = gamma if isinstance(gamma, Tensor) else torch.tensor(gamma)
     activity = None
     freq_total = None
     for name in ci.lower:
@@ -308,13 +323,24 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
     metrics["loss/" + cfg.instance_key] = activity.detach()
     out = coeff * activity
     if freq_total is not None:
-        fc = scheduled_or_constant(cfg.frequency.coeff, step, total)  # type: ignore[union-attr]
+        fc = ctx.sched("frequency", cfg.frequency.coeff, step)  # type: ignore[union-attr]
         metrics["loss/FrequencyMinimalityLoss"] = freq_total.detach()
         out = out + fc * freq_total
     return out
 
 
 # ---- the step -------------------------------------------------------------------------------------
+
+
+def _lr_metric(ctx: StepContext, opt, lr: float) -> Tensor:
+    """The applied learning rate for the log: read from the device table when the step keeps its scalars there
+    (a replayed recording then still reports the current value)."""
+    if ctx.scalars is not None:
+        name = f"opt/{getattr(opt, 'label', '')}/hyper"
+        if name in ctx.scalars._entries:
+            e = ctx.scalars._entries[name]
+            return ctx.scalars.words[e.slot:e.slot + 1].view(torch.float32).reshape(())
+    return torch.tensor(lr)
 
 
 def _detach_weights(w: ComputeWeights) -> ComputeWeights:
@@ -351,7 +377,7 @@ def run_ci_fn(ctx: StepContext, state: TrainState, clean: ForwardResult, step: i
     if fusable:
         from param_decomp_b200.core.ci_fn.interface import squash_fused
 
-        return squash_fused(pre, get_scheduled_value(step, ctx.pd.steps, cfg.gamma), cfg.normalize_at_one)
+        return squash_fused(pre, ctx.sched("gamma", cfg.gamma, step), cfg.normalize_at_one)
     return squash(pre)
 
 
@@ -408,6 +434,13 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     key = StepKey(ctx.pd.seed, step)
     obj = ctx.objective
     metrics: dict[str, Tensor] = {}
+    if ctx.scalars is not None:
+        from param_decomp_b200.ops import native
+
+        if ctx.scalars.step != step:  # (a recorded step's table is refreshed by whoever replays it)
+            ctx.scalars.begin(step)
+        seed_word = ctx.scalars.u64("philox_seed", lambda s: StepKey(ctx.pd.seed, s).seed64)
+        native.set_step_seed(key.seed64, seed_word.data_ptr())
 
     with torch.no_grad(), phase("clean"):
         clean = ctx.model.clean_forward(batch, capture=obj.capture_keys())
@@ -447,7 +480,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     losses_range = phase("losses")
     losses_range.__enter__()
     if obj.faith is not None:
-        c_f = scheduled_or_constant(obj.faith.coeff, step, total)
+        c_f = ctx.sched("faithfulness", obj.faith.coeff, step)
         from param_decomp_b200.ops import faithfulness as fused_faith
 
         shard = ctx.expert_shard
@@ -530,7 +563,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         e2e_mean = torch.stack(vals_e2e).mean()
         full_mean = torch.stack(vals_full).mean()
         metrics["loss/" + term.name] = e2e_mean.detach()
-        add(term.coeff(step, total) * full_mean)
+        add(ctx.sched("term/" + term.name, term.cfg.coeff, step) * full_mean)
         if term.is_persistent:
             tgt = full_mean if term.cfg.adversary_objective == "term" else e2e_mean  # type: ignore[attr-defined]
             source_grad_requests.append((term, all_leaves, tgt))  # type: ignore[arg-type]
@@ -571,8 +604,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         info_f = state.ci_fn_opt.step(step)
     metrics["grad_norm/components"] = state.components_opt.last_grad_norm_t.detach()
     metrics["grad_norm/ci_fn"] = state.ci_fn_opt.last_grad_norm_t.detach()
-    metrics["schedules/lr_components"] = torch.tensor(info_c["lr"])
-    metrics["schedules/lr_ci_fn"] = torch.tensor(info_f["lr"])
+    metrics["schedules/lr_components"] = _lr_metric(ctx, state.components_opt, info_c["lr"])
+    metrics["schedules/lr_ci_fn"] = _lr_metric(ctx, state.ci_fn_opt, info_f["lr"])
 
     if isinstance(ctx.pd, TargetedPDConfig) and ctx.pd.ci_scaled_weight_decay is not None:
         opt = state.components_opt
@@ -587,6 +620,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         lr = get_scheduled_value(step, total, term.cfg.optimizer.lr_schedule)  # type: ignore[attr-defined]
         state.adversaries[term.name].ascend(grads, lr, final_key)
 
+    if ctx.scalars is not None:
+        native.set_step_seed(None)
     state.step += 1
     return metrics  # type: ignore[return-value]
 

@@ -93,6 +93,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             max_steps_this_entry=max_steps_this_entry, state_out=state_out,
             profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
             shard_group=shard_group, shard_backend=shard_backend, peer_wait_limit_s=cfg.runtime.peer_wait_limit_s,
+            record_step=fused and cfg.runtime.step_recording == "cuda_graph",
             remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn)
     except BaseException:
         if sink is not None:

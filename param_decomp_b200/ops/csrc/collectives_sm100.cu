@@ -83,10 +83,20 @@ struct RsAdamwArgs {
   float* norm_out;   // local fp32: the global gradient norm (for logging)
   int* status;
   unsigned long long limit_ns;
+  // Recorded launches (CUDA graphs): when set, {lr, 1/bc1, 1/bc2} and the first of the three sequence
+  // numbers are read from device memory at run time, so one recording serves every step.
+  const float* hyper_dev;
+  const unsigned int* seq_dev;
 };
 
 __global__ void __launch_bounds__(kThreads) rs_adamw_ag_kernel(RsAdamwArgs a) {
   cg::grid_group grid = cg::this_grid();
+  if (a.hyper_dev != nullptr) {
+    a.lr = a.hyper_dev[0];
+    a.inv_bc1 = a.hyper_dev[1];
+    a.inv_bc2 = a.hyper_dev[2];
+  }
+  if (a.seq_dev != nullptr) a.seq = *a.seq_dev;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   float* my_norm = static_cast<float*>(a.norms.ptr[a.rank]);
@@ -288,6 +298,8 @@ struct PdRsAdamwCall {
   float* norm_out;
   int* status;
   double limit_s;
+  const float* hyper_dev;         // {lr, 1/bc1, 1/bc2} in device memory, or null to use the fields above
+  const unsigned int* seq_dev;    // first sequence number in device memory, or null to use `seq`
 };
 
 extern "C" int pd_rs_adamw_ag(const PdRsAdamwCall* c, void* stream) {
@@ -305,6 +317,7 @@ extern "C" int pd_rs_adamw_ag(const PdRsAdamwCall* c, void* stream) {
   a.inv_bc1 = 1.f / c->bc1; a.inv_bc2 = 1.f / c->bc2; a.max_norm = c->max_norm;
   a.norm_out = c->norm_out; a.status = c->status;
   a.limit_ns = static_cast<unsigned long long>(c->limit_s * 1e9);
+  a.hyper_dev = c->hyper_dev; a.seq_dev = c->seq_dev;
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

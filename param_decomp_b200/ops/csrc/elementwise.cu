@@ -419,7 +419,12 @@ __global__ void ci_squash_kernel(const __nv_bfloat16* __restrict__ pre,
 __global__ void ci_squash_activity_kernel(const __nv_bfloat16* __restrict__ pre,
                                           __nv_bfloat16* __restrict__ lower,
                                           float* __restrict__ colsum, long long rows, int C,
-                                          float gamma2, float norm, float alpha) {
+                                          float gamma2, float norm, float alpha, const float* __restrict__ gamma_dev, int normalize) {
+  if (gamma_dev != nullptr) {  // the schedule's current value lives in device memory (recorded launches)
+    const float gm = *gamma_dev;
+    gamma2 = gm * gm;
+    norm = normalize ? 1.f + gamma2 : 1.f;
+  }
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int col = (blockIdx.x * 32 + cg) * 8;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -463,7 +468,12 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
                                               const __nv_bfloat16* __restrict__ dlower,
                                               const float* __restrict__ dcol,
                                               __nv_bfloat16* __restrict__ dpre, long long rows, int C,
-                                              float gamma2, float norm, float alpha) {
+                                              float gamma2, float norm, float alpha, const float* __restrict__ gamma_dev, int normalize) {
+  if (gamma_dev != nullptr) {  // the schedule's current value lives in device memory (recorded launches)
+    const float gm = *gamma_dev;
+    gamma2 = gm * gm;
+    norm = normalize ? 1.f + gamma2 : 1.f;
+  }
   // Same tiling as the forward: a thread owns 8 columns (its dcol values stay in registers) and walks
   // rows with the grid's row stride, two rows in flight per iteration.
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
@@ -525,7 +535,12 @@ __global__ void ci_squash_activity_jobs_kernel(const __nv_bfloat16* __restrict__
                                                float* __restrict__ colsum,
                                                const int4* __restrict__ rowmap,
                                                const int* __restrict__ bgroup, int c, long long pitch,
-                                               float gamma2, float norm, float alpha) {
+                                               float gamma2, float norm, float alpha, const float* __restrict__ gamma_dev, int normalize) {
+  if (gamma_dev != nullptr) {  // the schedule's current value lives in device memory (recorded launches)
+    const float gm = *gamma_dev;
+    gamma2 = gm * gm;
+    norm = normalize ? 1.f + gamma2 : 1.f;
+  }
   const int e = bgroup[blockIdx.y];
   if (e < 0) return;
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
@@ -575,7 +590,12 @@ __global__ void ci_squash_activity_jobs_bwd_kernel(const __nv_bfloat16* __restri
                                                    const long long* __restrict__ experts,
                                                    __nv_bfloat16* __restrict__ dpre, long long tokens,
                                                    int k_sel, int c, float gamma2, float norm,
-                                                   float alpha) {
+                                                   float alpha, const float* __restrict__ gamma_dev, int normalize) {
+  if (gamma_dev != nullptr) {  // the schedule's current value lives in device memory (recorded launches)
+    const float gm = *gamma_dev;
+    gamma2 = gm * gm;
+    norm = normalize ? 1.f + gamma2 : 1.f;
+  }
   const int groups = c / 8;
   const long long total = tokens * k_sel * groups;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -691,7 +711,9 @@ __global__ void vocab_kl_kernel(const __nv_bfloat16* __restrict__ lc, const __nv
 
 // out[row, 8g .. 8g+7] = the Philox uniforms the GEMM epilogues draw for (seed, stream, row, g).
 __global__ void philox_uniform_kernel(float* __restrict__ out, long long rows, int groups, int cols,
-                                      unsigned long long seed, unsigned int stream, unsigned int row_offset) {
+                                      unsigned long long seed, unsigned int stream, unsigned int row_offset,
+                                      const unsigned long long* __restrict__ seed_dev) {
+  if (seed_dev != nullptr) seed = *seed_dev;
   const long long total = rows * groups;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -702,6 +724,76 @@ __global__ void philox_uniform_kernel(float* __restrict__ out, long long rows, i
 #pragma unroll
     for (int k = 0; k < 8; ++k)
       if (8 * g + k < cols) out[row * cols + 8 * g + k] = u[k];
+  }
+}
+
+struct TensorRef {
+  float* p;
+  const float* g;
+  float* m;
+  float* v;
+  long long n;
+};
+
+__global__ void sumsq_multi_kernel(const TensorRef* __restrict__ refs, float* __restrict__ out) {
+  const TensorRef t = refs[blockIdx.y];
+  float acc = 0.f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < t.n; i += stride) {
+    if (i + 3 < t.n) {
+      const float4 v = *reinterpret_cast<const float4*>(t.g + i);
+      acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    } else {
+      for (long long j = i; j < t.n; ++j) acc += t.g[j] * t.g[j];
+    }
+  }
+  acc = warp_sum(acc);
+  __shared__ float part[kThreads / 32];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kThreads / 32 ? part[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0 && v != 0.f) atomicAdd(out, v);
+  }
+}
+
+__global__ void adamw_multi_kernel(const TensorRef* __restrict__ refs, float lr, float b1, float b2, float eps,
+                                   float wd, float inv_bc1, float inv_bc2, const float* __restrict__ hyper,
+                                   const float* __restrict__ grad_scale) {
+  const TensorRef t = refs[blockIdx.y];
+  if (hyper != nullptr) {
+    lr = hyper[0];
+    inv_bc1 = hyper[1];
+    inv_bc2 = hyper[2];
+  }
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < t.n; i += stride) {
+    if (i + 3 < t.n) {
+      float4 pp = *reinterpret_cast<float4*>(t.p + i);
+      const float4 gg = *reinterpret_cast<const float4*>(t.g + i);
+      float4 mm = *reinterpret_cast<float4*>(t.m + i);
+      float4 vv = *reinterpret_cast<float4*>(t.v + i);
+      float* pa = &pp.x; const float* ga = &gg.x; float* ma = &mm.x; float* va = &vv.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gk = ga[k] * gs;
+        ma[k] = b1 * ma[k] + (1.f - b1) * gk;
+        va[k] = b2 * va[k] + (1.f - b2) * gk * gk;
+        pa[k] -= lr * ((ma[k] * inv_bc1) / (sqrtf(va[k] * inv_bc2) + eps) + wd * pa[k]);
+      }
+      *reinterpret_cast<float4*>(t.p + i) = pp;
+      *reinterpret_cast<float4*>(t.m + i) = mm;
+      *reinterpret_cast<float4*>(t.v + i) = vv;
+    } else {
+      for (long long j = i; j < t.n; ++j) {
+        const float gk = t.g[j] * gs;
+        t.m[j] = b1 * t.m[j] + (1.f - b1) * gk;
+        t.v[j] = b2 * t.v[j] + (1.f - b2) * gk * gk;
+        t.p[j] -= lr * ((t.m[j] * inv_bc1) / (sqrtf(t.v[j] * inv_bc2) + eps) + wd * t.p[j]);
+      }
+    }
   }
 }
 
@@ -802,6 +894,23 @@ extern "C" int pd_adamw(float* p, const float* g, float* m, float* v, long long 
       p, g, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, grad_scale);
   return PD_CHECK_LAUNCH();
 }
+// Multi-tensor forms: one launch covers every leaf of an optimizer group. `refs` is a device array
+// of {p, g, m, v, n}; blockIdx.y picks the leaf, blockIdx.x strides over it. `hyper` (device, may be
+// null) holds {lr, 1 / bias_correction1, 1 / bias_correction2}: a recorded launch (CUDA graph) then
+// follows the schedule without being re-recorded.
+extern "C" int pd_sumsq_multi(const void* refs, int count, float* out, void* stream) {
+  if (count <= 0) return 0;
+  sumsq_multi_kernel<<<dim3(96, count), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const TensorRef*>(refs), out);
+  return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_adamw_multi(const void* refs, int count, float lr, float b1, float b2, float eps, float wd,
+                              float bc1, float bc2, const float* hyper, const float* grad_scale, void* stream) {
+  if (count <= 0) return 0;
+  adamw_multi_kernel<<<dim3(96, count), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const TensorRef*>(refs), lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, hyper, grad_scale);
+  return PD_CHECK_LAUNCH();
+}
 extern "C" int pd_cast_bf16(const float* src, void* dst, long long n, void* stream) {
   cast_bf16_kernel<<<blocks_for(n, kThreads * 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       src, static_cast<__nv_bfloat16*>(dst), n);
@@ -881,7 +990,8 @@ extern "C" int pd_ci_squash(const void* pre, void* lower, void* upper, long long
 }
 
 extern "C" int pd_ci_squash_activity(const void* pre, void* lower, float* colsum, long long rows, int C,
-                                     float gamma, int normalize_at_one, float alpha, void* stream) {
+                                     float gamma, int normalize_at_one, float alpha, const float* gamma_dev,
+                                     void* stream) {
   if (C % 8 != 0) return 5;
   const int gx = (C + 255) / 256;
   int gy = (148 * 4 + gx - 1) / gx;
@@ -890,12 +1000,12 @@ extern "C" int pd_ci_squash_activity(const void* pre, void* lower, float* colsum
   const float g2 = gamma * gamma;
   ci_squash_activity_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(lower), colsum, rows, C, g2,
-      normalize_at_one ? 1.f + g2 : 1.f, alpha);
+      normalize_at_one ? 1.f + g2 : 1.f, alpha, gamma_dev, normalize_at_one);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_ci_squash_activity_bwd(const void* pre, const void* dlower, const float* dcol, void* dpre,
                                          long long rows, int C, float gamma, int normalize_at_one, float alpha,
-                                         void* stream) {
+                                         const float* gamma_dev, void* stream) {
   if (C % 8 != 0) return 5;
   const float g2 = gamma * gamma;
   const int gx = (C + 255) / 256;
@@ -904,30 +1014,34 @@ extern "C" int pd_ci_squash_activity_bwd(const void* pre, const void* dlower, co
   if (gy < 1) gy = 1;
   ci_squash_activity_bwd_kernel<<<dim3(gx, static_cast<unsigned>(gy)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(dlower), dcol,
-      static_cast<__nv_bfloat16*>(dpre), rows, C, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
+      static_cast<__nv_bfloat16*>(dpre), rows, C, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha, gamma_dev,
+      normalize_at_one);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_ci_squash_activity_jobs(const void* pre, void* lower, float* colsum, const void* rowmap,
                                           const int* bgroup, long long n_rows, int c, long long pitch,
-                                          float gamma, int normalize_at_one, float alpha, void* stream) {
+                                          float gamma, int normalize_at_one, float alpha, const float* gamma_dev,
+                                          void* stream) {
   if (c % 8 != 0 || pitch % 8 != 0 || n_rows % 128 != 0 || n_rows <= 0) return 5;
   const float g2 = gamma * gamma;
   ci_squash_activity_jobs_kernel<<<dim3((c + 255) / 256, static_cast<unsigned>(n_rows / 128)), 256, 0,
                                    static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(lower), colsum,
-      static_cast<const int4*>(rowmap), bgroup, c, pitch, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
+      static_cast<const int4*>(rowmap), bgroup, c, pitch, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha, gamma_dev,
+      normalize_at_one);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_ci_squash_activity_jobs_bwd(const void* pre, const void* dlower, const float* dcol,
                                               const long long* experts, void* dpre, long long tokens, int k_sel,
                                               int c, float gamma, int normalize_at_one, float alpha,
-                                              void* stream) {
+                                              const float* gamma_dev, void* stream) {
   if (c % 8 != 0 || tokens <= 0) return 5;
   const float g2 = gamma * gamma;
   ci_squash_activity_jobs_bwd_kernel<<<blocks_for(tokens * k_sel * (c / 8), kThreads), kThreads, 0,
                                        static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(dlower), dcol, experts,
-      static_cast<__nv_bfloat16*>(dpre), tokens, k_sel, c, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha);
+      static_cast<__nv_bfloat16*>(dpre), tokens, k_sel, c, g2, normalize_at_one ? 1.f + g2 : 1.f, alpha, gamma_dev,
+      normalize_at_one);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_vocab_kl(const void* lc, const void* lm, void* dlm, float* kl, long long rows, int V,
@@ -942,10 +1056,10 @@ extern "C" int pd_vocab_kl(const void* lc, const void* lm, void* dlm, float* kl,
 }
 
 extern "C" int pd_philox_uniform(float* out, long long rows, int cols, unsigned long long seed, unsigned int stream,
-                                 unsigned int row_offset, void* stream_v) {
+                                 unsigned int row_offset, const unsigned long long* seed_dev, void* stream_v) {
   const int groups = (cols + 7) / 8;
   philox_uniform_kernel<<<blocks_for(rows * groups, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream_v)>>>(
-      out, rows, groups, cols, seed, stream, row_offset);
+      out, rows, groups, cols, seed, stream, row_offset, seed_dev);
   return PD_CHECK_LAUNCH();
 }
 extern "C" int pd_split_bf16(const float* x, void* hi, void* lo, long long n, void* stream) {

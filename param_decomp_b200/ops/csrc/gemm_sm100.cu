@@ -62,6 +62,7 @@ struct GemmArgs {
   int out_fp32;
   int has_out1;
   float alpha;
+  const float* alpha_dev;  // when set, the plain epilogue scales by alpha * *alpha_dev (a scheduled coefficient in device memory)
   const float* bias;
   long long bias_bs;
   int act;
@@ -76,6 +77,9 @@ struct GemmArgs {
   int dci_accumulate;
   int dci_bf16;
   unsigned long long seed;
+  // When set, the Philox seed is read from device memory at run time instead of `seed`: a launch recorded
+  // once (CUDA graph) then draws a fresh mask stream every replay after the host rewrites that word.
+  const unsigned long long* seed_dev;
   unsigned int stream;
   unsigned int row_offset;
   int mask_mode;
@@ -546,9 +550,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const int nboxes = BN / box_cols;
     const int halves = out32 ? 1 : 2;
     const bool plain_fast = (EPI == EPI_PLAIN) && args.bias == nullptr && args.act == ACT_NONE &&
-                            args.alpha == 1.0f;
+                            args.alpha == 1.0f && args.alpha_dev == nullptr;
+    const float alpha_eff = (EPI == EPI_PLAIN && args.alpha_dev != nullptr) ? args.alpha * *args.alpha_dev : args.alpha;
     constexpr bool kWantH = (EPI == EPI_MASK_BWD);
     const bool want_h = kWantH && args.dci != nullptr;
+    unsigned long long philox_seed = args.seed;
+    if constexpr (EPI == EPI_MASK_FWD || EPI == EPI_MASK_BWD) {
+      if (args.seed_dev != nullptr) philox_seed = *args.seed_dev;
+    }
 
     auto tile_is_real = [&](long long t) {
       if (!args.bgroup_of_mblock) return true;
@@ -691,7 +700,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
               const float* bias = args.bias ? args.bias + b * args.bias_bs : nullptr;
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                float x = v[i] * args.alpha;
+                float x = v[i] * alpha_eff;
                 if (bias && c0 + i < args.N) x += bias[c0 + i];
                 v[i] = x;
               }
@@ -734,7 +743,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
               unpack8(ciq[g], cf);
               if (args.mask_mode == 0) {
                 float u[8];
-                philox_uniform8(args.seed, args.stream, static_cast<uint32_t>(src_row) + args.row_offset,
+                philox_uniform8(philox_seed, args.stream, static_cast<uint32_t>(src_row) + args.row_offset,
                                 static_cast<uint32_t>(((src_col + c0) >> 3) + g) + (args.philox_col0 >> 3), u);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -979,6 +988,8 @@ struct PdGemmCall {
   int cta_group;  // 0 = automatic, 1 = single CTA tiles, 2 = CTA pairs where the call allows them
   const void* rowmap;  // [M] int4 {source row, first source column, 0, 0} for the mask epilogues, or null
   unsigned int philox_col0;  // global index of mask column 0 in the Philox counter space (multiple of 8)
+  const unsigned long long* seed_dev;  // when set, overrides `seed` with the value in device memory at run time
+  const float* alpha_dev;              // when set, the plain epilogue's scale is alpha * *alpha_dev
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -1000,12 +1011,12 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   if (a.split_k > a.kblocks0 + a.kblocks1) a.split_k = a.kblocks0 + a.kblocks1;
   a.a_mn0 = c->a_mn0; a.b_mn0 = c->b_mn0; a.a_mn1 = c->a_mn1; a.b_mn1 = c->b_mn1;
   a.accumulate = c->accumulate; a.out_fp32 = c->out_fp32; a.has_out1 = c->out1 != nullptr;
-  a.alpha = c->alpha; a.bias = c->bias; a.bias_bs = c->bias_bs; a.act = c->act;
+  a.alpha = c->alpha; a.alpha_dev = c->alpha_dev; a.bias = c->bias; a.bias_bs = c->bias_bs; a.act = c->act;
   a.ci = static_cast<const __nv_bfloat16*>(c->ci); a.ld_ci = c->ld_ci;
   a.H = static_cast<const __nv_bfloat16*>(c->H); a.ld_h = c->ld_h;
   a.delta = c->delta; a.rowscale = c->rowscale;
   a.dci = c->dci; a.ld_dci = c->ld_dci; a.dci_accumulate = c->dci_accumulate; a.dci_bf16 = c->dci_bf16;
-  a.seed = c->seed; a.stream = c->rng_stream; a.row_offset = c->rng_row_offset; a.mask_mode = c->mask_mode;
+  a.seed = c->seed; a.seed_dev = c->seed_dev; a.stream = c->rng_stream; a.row_offset = c->rng_row_offset; a.mask_mode = c->mask_mode;
   a.status = c->status;
   a.bgroup_of_mblock = c->bgroup_of_mblock; a.kblock_range = c->kblock_range;
   a.a_bcast = c->a_bcast; a.b_bcast = c->b_bcast;

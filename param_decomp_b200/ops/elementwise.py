@@ -42,6 +42,15 @@ def _s() -> int:
     return nv.current_stream_ptr()
 
 
+def _scalar_arg(x) -> tuple[float, int | None]:
+    """A scalar kernel argument given as a python number or as a 0-d fp32 device tensor (a slot of the
+    step-scalar table): `(by-value placeholder, device address or None)`."""
+    if isinstance(x, Tensor):
+        assert x.dtype == torch.float32 and x.is_cuda and x.numel() == 1
+        return 0.0, x.data_ptr()
+    return float(x), None
+
+
 def cast_bf16(src: Tensor, out: Tensor | None = None) -> Tensor:
     assert src.dtype == torch.float32 and src.is_contiguous()
     out = out if out is not None else torch.empty_like(src, dtype=torch.bfloat16)
@@ -173,16 +182,18 @@ class _SquashActivity(torch.autograd.Function):
     that applies the lower-leaky gradient rule and the minimality gradient together."""
 
     @staticmethod
-    def forward(ctx, pre: Tensor, gamma: float, normalize_at_one: bool, alpha: float):  # type: ignore[override]
+    def forward(ctx, pre: Tensor, gamma, normalize_at_one: bool, alpha: float):  # type: ignore[override]
+        """`gamma`: a float, or a 0-d fp32 device tensor (the schedule's slot in the step-scalar table)."""
         rows, Cn = pre.shape
         pre = pre.contiguous()
         lower = torch.empty_like(pre)
         colsum = torch.zeros(Cn, device=pre.device, dtype=torch.float32)
         lib = _lib()
         lib.pd_ci_squash_activity.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_float,
-                                              C.c_int, C.c_float, C.c_void_p]
-        _check(lib.pd_ci_squash_activity(pre.data_ptr(), lower.data_ptr(), colsum.data_ptr(), rows, Cn, gamma,
-                                         int(normalize_at_one), alpha, _s()), "ci_squash_activity")
+                                              C.c_int, C.c_float, C.c_void_p, C.c_void_p]
+        g_val, g_ptr = _scalar_arg(gamma)
+        _check(lib.pd_ci_squash_activity(pre.data_ptr(), lower.data_ptr(), colsum.data_ptr(), rows, Cn, g_val,
+                                         int(normalize_at_one), alpha, g_ptr, _s()), "ci_squash_activity")
         ctx.save_for_backward(pre)
         ctx.cfg = (gamma, normalize_at_one, alpha)
         ctx.mark_non_differentiable()
@@ -197,10 +208,11 @@ class _SquashActivity(torch.autograd.Function):
         dpre = torch.empty_like(pre)
         lib = _lib()
         lib.pd_ci_squash_activity_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
-                                                  C.c_float, C.c_int, C.c_float, C.c_void_p]
+                                                  C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
         dl = None if dlower is None else dlower.contiguous()
+        g_val, g_ptr = _scalar_arg(gamma)
         _check(lib.pd_ci_squash_activity_bwd(pre.data_ptr(), dl.data_ptr() if dl is not None else None, dcol.data_ptr(),
-                                             dpre.data_ptr(), rows, Cn, gamma, int(norm), alpha, _s()),
+                                             dpre.data_ptr(), rows, Cn, g_val, int(norm), alpha, g_ptr, _s()),
                "ci_squash_activity_bwd")
         return dpre, None, None, None
 
@@ -232,10 +244,11 @@ class _SquashActivityJobs(torch.autograd.Function):
         lib = _lib()
         lib.pd_ci_squash_activity_jobs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                    C.c_longlong, C.c_int, C.c_longlong, C.c_float, C.c_int,
-                                                   C.c_float, C.c_void_p]
+                                                   C.c_float, C.c_void_p, C.c_void_p]
+        g_val, g_ptr = _scalar_arg(gamma)
         _check(lib.pd_ci_squash_activity_jobs(pre.data_ptr(), lower.data_ptr(), colsum.data_ptr(), rowmap.data_ptr(),
-                                              layout.bgroup.data_ptr(), layout.n_rows, c, kc, gamma,
-                                              int(normalize_at_one), alpha, _s()), "ci_squash_activity_jobs")
+                                              layout.bgroup.data_ptr(), layout.n_rows, c, kc, g_val,
+                                              int(normalize_at_one), alpha, g_ptr, _s()), "ci_squash_activity_jobs")
         ctx.save_for_backward(pre, experts)
         ctx.cfg = (gamma, normalize_at_one, alpha, k, c)
         ctx.n_blocks = n_blocks
@@ -252,11 +265,12 @@ class _SquashActivityJobs(torch.autograd.Function):
         lib = _lib()
         lib.pd_ci_squash_activity_jobs_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                        C.c_longlong, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float,
-                                                       C.c_void_p]
+                                                       C.c_void_p, C.c_void_p]
         dl = None if dlower is None else dlower.contiguous()
+        g_val, g_ptr = _scalar_arg(gamma)
         _check(lib.pd_ci_squash_activity_jobs_bwd(pre.data_ptr(), dl.data_ptr() if dl is not None else None,
                                                   dcol.data_ptr(), experts.data_ptr(), dpre.data_ptr(), tokens, k, c,
-                                                  gamma, int(norm), alpha, _s()), "ci_squash_activity_jobs_bwd")
+                                                  g_val, int(norm), alpha, g_ptr, _s()), "ci_squash_activity_jobs_bwd")
         return dpre, None, None, None, None, None, None
 
 
@@ -294,9 +308,10 @@ def philox_uniform(seed64: int, stream: int, rows: int, cols: int, row_offset: i
     """`[rows, cols]` fp32 uniforms, bit-identical to `philox_ref.uniform` and to the GEMM epilogues."""
     out = torch.empty(rows, cols, device=device, dtype=torch.float32)
     lib = _lib()
-    lib.pd_philox_uniform.argtypes = [C.c_void_p, C.c_longlong, C.c_int, C.c_ulonglong, C.c_uint, C.c_uint, C.c_void_p]
+    lib.pd_philox_uniform.argtypes = [C.c_void_p, C.c_longlong, C.c_int, C.c_ulonglong, C.c_uint, C.c_uint, C.c_void_p,
+                                      C.c_void_p]
     _check(lib.pd_philox_uniform(out.data_ptr(), rows, cols, seed64 & (2**64 - 1), stream & 0xFFFFFFFF,
-                                 row_offset & 0xFFFFFFFF, _s()), "philox_uniform")
+                                 row_offset & 0xFFFFFFFF, nv.step_seed_ptr(seed64) or None, _s()), "philox_uniform")
     return out
 
 

@@ -21,10 +21,26 @@ from param_decomp_b200.ops import native as nv
 from param_decomp_b200.ops.elementwise import split3_bf16, split_bf16
 
 
-def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host: dict[str, float], coeff: float,
+_WSQ: dict[tuple, Tensor] = {}
+
+
+def _wsq_tensor(sites, w_sq_host: dict[str, float], dev) -> Tensor:
+    """`||W_s||^2` per site on the device, uploaded once (the target is frozen)."""
+    key = (str(dev), tuple((s.name, w_sq_host[s.name]) for s in sites))
+    t = _WSQ.get(key)
+    if t is None:
+        if len(_WSQ) > 16:
+            _WSQ.clear()
+        t = _WSQ[key] = torch.tensor([w_sq_host[s.name] for s in sites], device=dev, dtype=torch.float32)
+    return t
+
+
+def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host: dict[str, float], coeff,
                        accumulate_grads: bool = True, hi_lo: dict[str, tuple[Tensor, Tensor]] | None = None,
                        rank: int = 0, world: int = 1) -> Tensor:
     """Returns the (detached) loss `mean_s ||D_s||^2 / ||W_s||^2`; adds `coeff * dLoss` to `.grad`.
+    `coeff` is a float, or a 0-d fp32 device tensor (a scheduled coefficient kept in device memory), which
+    the gradient GEMMs then read at run time.
 
     `hi_lo["V/<group>"] = (hi, lo)`: split-precision working copies published by the sharded
     optimizer (then no fp32 master is read). With `world > 1` the sites are dealt round-robin to the
@@ -32,6 +48,8 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
     (the gradient reduction averages over ranks), and returns its partial loss; the caller sums it."""
     sites = list(stacks.sites)
     dev = next(stacks.parameters()).device
+    coeff_dev = coeff if isinstance(coeff, Tensor) else None
+    coeff = 1.0 if coeff_dev is not None else coeff
     sumsq = torch.zeros(len(sites), 8, device=dev, dtype=torch.float32)
     n_sites = len(sites)
     row_of = {s.name: i for i, s in enumerate(sites)}  # sumsq rows follow `sites`, not the group walk
@@ -64,7 +82,7 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
             if s.blocked:
                 _blocked_site(s, Vh[i], Vl[i], Uh[i], Ul[i], Wb, sumsq[row_of[s.name]:row_of[s.name] + 1],
                               pV.grad[i] if accumulate_grads else None, pU.grad[i] if accumulate_grads else None,
-                              -2.0 * coeff * world / (n_sites * w_sq_host[s.name]))
+                              -2.0 * coeff * world / (n_sites * w_sq_host[s.name]), coeff_dev)
                 k += 1
                 continue
             if V3 is not None:
@@ -77,11 +95,10 @@ def fused_faithfulness(stacks: ComponentStacks, W: dict[str, Tensor], w_sq_host:
             nv.gemm(U_cat, V_cat, D, a_mn=True, epi=nv.EPI_FAITH, ci=Wb, dci=sumsq[r:r + 1])
             if accumulate_grads:
                 alpha = -2.0 * coeff * world / (n_sites * w_sq_host[s.name])
-                nv.gemm(D, Uh[i], pV.grad[i], a_mn=True, accumulate=True, alpha=alpha)
-                nv.gemm(Vh[i], D, pU.grad[i], a_mn=True, accumulate=True, alpha=alpha)
+                nv.gemm(D, Uh[i], pV.grad[i], a_mn=True, accumulate=True, alpha=alpha, alpha_dev=coeff_dev)
+                nv.gemm(Vh[i], D, pU.grad[i], a_mn=True, accumulate=True, alpha=alpha, alpha_dev=coeff_dev)
             k += 1
-    wsq = torch.tensor([w_sq_host[s.name] for s in sites], device=dev, dtype=torch.float32)
-    return (sumsq[:, 0] / wsq).sum() / n_sites
+    return (sumsq[:, 0] / _wsq_tensor(sites, w_sq_host, dev)).sum() / n_sites
 
 
 def blocked_supported(stacks: ComponentStacks) -> bool:
@@ -91,7 +108,7 @@ def blocked_supported(stacks: ComponentStacks) -> bool:
 
 
 def _blocked_site(s, Vh: Tensor, Vl: Tensor, Uh: Tensor, Ul: Tensor, Wb: Tensor, sumsq: Tensor, gV: Tensor | None,
-                  gU: Tensor | None, alpha: float) -> None:
+                  gU: Tensor | None, alpha: float, alpha_dev: Tensor | None = None) -> None:
     """`V [E, d_in, c]`, `U [E, c, d_out]`, `W [E, d_out, d_in]`: the residual of all experts in one
     launch (each 128-row tile of the stacked rows picks its expert's `V`), then two batched products
     for the gradients."""
@@ -103,5 +120,5 @@ def _blocked_site(s, Vh: Tensor, Vl: Tensor, Uh: Tensor, Ul: Tensor, Wb: Tensor,
     nv.gemm(A, V_cat, D.view(E * d_out, d_in), epi=nv.EPI_FAITH, ci=Wb.reshape(E * d_out, d_in), dci=sumsq,
             bgroup_of_mblock=owner)
     if gV is not None:
-        nv.gemm(D, Uh, gV, a_mn=True, accumulate=True, alpha=alpha)  # dV[e] = alpha D_e^T U_e^T
-        nv.gemm(Vh, D, gU, a_mn=True, accumulate=True, alpha=alpha)  # dU[e] = alpha V_e^T D_e^T
+        nv.gemm(D, Uh, gV, a_mn=True, accumulate=True, alpha=alpha, alpha_dev=alpha_dev)  # dV[e] = alpha D_e^T U_e^T
+        nv.gemm(Vh, D, gU, a_mn=True, accumulate=True, alpha=alpha, alpha_dev=alpha_dev)  # dU[e] = alpha V_e^T D_e^T

@@ -48,6 +48,7 @@ class PdGemmCall(C.Structure):
         ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
         ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int), ("rowmap", C.c_void_p), ("philox_col0", C.c_uint),
+        ("seed_dev", C.c_void_p), ("alpha_dev", C.c_void_p),
     ]  # fmt: skip
 
 
@@ -126,6 +127,23 @@ def check_status() -> None:
         raise NativeError(f"a device-side wait timed out (status code {code})")
 
 
+_STEP_SEED: tuple[int, int] | None = None  # (seed64 of the running step, device address of the word holding it)
+
+
+def set_step_seed(seed64: int | None, device_ptr: int = 0) -> None:
+    """While set, a kernel asked to draw from `seed64` reads the seed from `device_ptr` at run time instead
+    of taking it by value: the train step's seed word lives in the step-scalar table
+    (`ops/step_scalars.py`), so a recorded step draws new masks on every replay. Calls with any other
+    seed are unaffected."""
+    global _STEP_SEED
+    _STEP_SEED = None if seed64 is None else (seed64 & (2**64 - 1), device_ptr)
+
+
+def step_seed_ptr(seed64: int) -> int:
+    st = _STEP_SEED
+    return st[1] if (st is not None and st[0] == (seed64 & (2**64 - 1))) else 0
+
+
 def _operand(t: torch.Tensor, mn_major: bool) -> tuple[int, int, int]:
     """(ptr, ld, batch_stride) of a 2-D or 3-D bf16 operand whose last dim is contiguous."""
     assert t.dtype == torch.bfloat16 and t.stride(-1) == 1, (t.dtype, t.stride())
@@ -174,6 +192,8 @@ def gemm(
     cta_group: int = 0,
     rowmap: torch.Tensor | None = None,
     philox_col0: int = 0,
+    seed_dev: int = 0,
+    alpha_dev: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -233,6 +253,11 @@ def gemm(
     call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
     call.rng_row_offset = row_offset & 0xFFFFFFFF
     call.philox_col0 = philox_col0
+    # device address of the step's Philox seed word (0: the seed is taken by value)
+    call.seed_dev = seed_dev or (step_seed_ptr(seed) if epi in (EPI_MASK_FWD, EPI_MASK_BWD) and mask_mode == 0 else 0)
+    if alpha_dev is not None:
+        assert alpha_dev.dtype == torch.float32 and alpha_dev.is_cuda and epi == EPI_PLAIN
+        call.alpha_dev = alpha_dev.data_ptr()
     call.split_k, call.bn, call.max_ctas = split_k, bn, max_ctas
     call.status = _status_ptr(torch._C._cuda_getDevice())
     if bgroup_of_mblock is not None:

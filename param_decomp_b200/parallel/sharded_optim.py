@@ -52,6 +52,7 @@ class PdRsAdamwCall(C.Structure):
         ("lr", C.c_float), ("b1", C.c_float), ("b2", C.c_float), ("eps", C.c_float), ("wd", C.c_float),
         ("bc1", C.c_float), ("bc2", C.c_float), ("max_norm", C.c_float),
         ("norm_out", C.c_void_p), ("status", C.c_void_p), ("limit_s", C.c_double),
+        ("hyper_dev", C.c_void_p), ("seq_dev", C.c_void_p),
     ]  # fmt: skip
 
 
@@ -87,6 +88,8 @@ class ShardedFlatAdamW:
     count: int = 0
     applied_learning_rate: float = 0.0
     last_grad_norm_t: Tensor | None = None
+    scalars: object | None = None  # ops.step_scalars.StepScalars: lr, bias corrections and barrier sequence in device memory
+    label: str = "components"
     _seq: int = 1
     state: dict[str, Tensor] = field(default_factory=dict)
 
@@ -171,6 +174,7 @@ class ShardedFlatAdamW:
             "a parameter's .grad no longer aliases the flat gradient buffer (something replaced it; gradients would be lost)"
         lr = self.lr_at(step_idx)
         self.count += 1
+        self._step_idx = step_idx
         self.applied_learning_rate = lr
         b1, b2 = self.cfg.betas
         bc1, bc2 = 1 - b1**self.count, 1 - b2**self.count
@@ -194,6 +198,11 @@ class ShardedFlatAdamW:
         call.p, call.m, call.v = self.master.data_ptr(), self.mu.data_ptr(), self.nu.data_ptr()
         call.shard_off, call.shard_len = self.shard_off, self.shard_len
         call.rank, call.world, call.seq = self.rank, self.world, self._seq
+        if self.scalars is not None:
+            off, seq0, s0 = self.count - self._step_idx, self._seq, self._step_idx
+            call.hyper_dev = self.scalars.f32_block(f"opt/{self.label}/hyper", 3, lambda s: (
+                self.lr_at(s), 1.0 / (1 - b1 ** (s + off)), 1.0 / (1 - b2 ** (s + off)))).data_ptr()
+            call.seq_dev = self.scalars.u32(f"opt/{self.label}/seq", lambda s: seq0 + 3 * (s - s0)).data_ptr()
         self._seq += 3
         call.lr, call.b1, call.b2, call.eps, call.wd = lr, b1, b2, 1e-8, self.cfg.weight_decay
         call.bc1, call.bc2, call.max_norm = bc1, bc2, max_norm
@@ -228,8 +237,15 @@ class ShardedFlatAdamW:
         g = shard * (scale / self.world)
         self.mu.mul_(b1).add_(g, alpha=1 - b1)
         self.nu.mul_(b2).addcmul_(g, g, value=1 - b2)
-        upd = (self.mu / bc1) / ((self.nu / bc2).sqrt() + 1e-8) + self.cfg.weight_decay * self.master
-        self.master.add_(upd, alpha=-lr)
+        if self.scalars is not None:  # lr and bias corrections read from device memory (recordable)
+            off = self.count - self._step_idx
+            h = self.scalars.f32_block(f"opt/{self.label}/hyper", 3, lambda s: (
+                self.lr_at(s), 1.0 / (1 - b1 ** (s + off)), 1.0 / (1 - b2 ** (s + off))))
+            upd = (self.mu * h[1]) / ((self.nu * h[2]).sqrt() + 1e-8) + self.cfg.weight_decay * self.master
+            self.master.sub_(upd * h[0])
+        else:
+            upd = (self.mu / bc1) / ((self.nu / bc2).sqrt() + 1e-8) + self.cfg.weight_decay * self.master
+            self.master.add_(upd, alpha=-lr)
         self.norm_out.copy_(norm.reshape(1))
         mine = self.master.to(torch.bfloat16)
         parts = [(self.work_flat, mine)]
@@ -240,6 +256,14 @@ class ShardedFlatAdamW:
                 dist.all_gather_into_tensor(dst, src, group=self.group)
             else:
                 dst.copy_(src)
+
+    def advance_replayed(self) -> None:
+        """Host bookkeeping of a step whose launches ran from a recording (no Python ran for it)."""
+        self.count += 1
+        self._step_idx += 1
+        self._seq += 3
+        self.applied_learning_rate = self.lr_at(self._step_idx)
+        self._full_stale = True
 
     def refresh_full_fp32(self) -> None:
         """All-gather the fp32 masters into the parameters' own storage (checkpoint / eval time)."""
