@@ -107,6 +107,8 @@ def main() -> None:
                          "outputs summed, or the batch sharded over it too and jobs stored into their expert's owner")
     ap.add_argument("--no-record", action="store_true",
                     help="issue every step launch by launch from Python instead of replaying the recorded CUDA graph")
+    ap.add_argument("--no-lanes", action="store_true",
+                    help="keep the whole step on one CUDA stream (no side-by-side draws / q,k,v / gate,up)")
     ap.add_argument("--kernel-table", type=Path, default=None,
                     help="after the timed steps, run one more step under the torch profiler and write the kernels "
                          "ranked by device time to this file (never part of a reported number)")
@@ -164,7 +166,8 @@ def main() -> None:
     # step is recorded, the recording call and one replay - all untimed.
     from param_decomp_b200.core.recorded_step import RecordedTrainStep
 
-    step_fn = RecordedTrainStep(ctx, state, enabled=not args.no_record, eager_steps=args.warmup)
+    step_fn = RecordedTrainStep(ctx, state, enabled=not args.no_record, eager_steps=args.warmup,
+                                concurrent=not args.no_lanes)
     for s in range(args.warmup + (2 if step_fn.eligible else 0)):
         step_fn(run.sample_train(s))
     native.check_status()

@@ -73,7 +73,8 @@ class RecordedTrainStep:
     and create the gradient buffers), recorded at the next call, replayed afterwards. Metrics are device tensors
     owned by the recording: read them (`float(...)`) before the next call."""
 
-    def __init__(self, ctx: StepContext, state: TrainState, enabled: bool = True, eager_steps: int = 3) -> None:
+    def __init__(self, ctx: StepContext, state: TrainState, enabled: bool = True, eager_steps: int = 3,
+                 concurrent: bool = True) -> None:
         self.ctx, self.state = ctx, state
         self.eager_steps = eager_steps
         self.reason = None if enabled else "recording is switched off"
@@ -92,6 +93,12 @@ class RecordedTrainStep:
                 ctx.scalars = StepScalars(dev)
             for label, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
                 opt.scalars, opt.label = ctx.scalars, label
+            if concurrent and ctx.lanes is None:
+                from param_decomp_b200.ops.lanes import Lanes
+
+                ctx.lanes = Lanes()
+                if hasattr(ctx.model, "_block"):
+                    ctx.model.lanes = ctx.lanes  # q / k / v and gate / up of a block fork too
 
     @property
     def eligible(self) -> bool:

@@ -133,6 +133,7 @@ class StepContext:
     # a masked forward / the CI function keeps only its inputs and is run again during the backward pass
     remat_recon_forwards: bool = False
     remat_ci_fn: bool = False
+    lanes: Any = None  # `ops.lanes.Lanes`: the mask draws of a term run side by side on CUDA side streams
     # `ops.step_scalars.StepScalars`: when set, everything the host computes per step (Philox seed word,
     # scheduled coefficients, learning rates and bias corrections) is read by the kernels from a device
     # table instead of being passed by value, so the step's launches can be recorded once and replayed
@@ -545,7 +546,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         elif term.strategy == "fresh_pgd":
             leaves = fresh_pgd_sources(ctx, term, weights, batch, clean, ci_lower, key, step)
         vals_e2e, vals_full = [], []
-        for draw in range(term.n_samples):
+
+        def one_draw(draw: int, term=term, leaves=leaves):
             masks = build_masks(ctx, term, ci_lower, key, draw, leaves, state, step)
             if ctx.remat_recon_forwards and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
@@ -553,11 +555,17 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
                 # masks are counter-based (same draw on the second run); the closure's tensors are tracked by
                 # the checkpoint's saved-tensor hooks, so nothing of the forward stays alive until backward
                 aux_metrics: dict[str, Tensor] = {}
-                e2e, full = checkpoint(lambda m=masks, am=aux_metrics: masked_recon(
+                pair = checkpoint(lambda m=masks, am=aux_metrics: masked_recon(
                     ctx, weights, batch, clean, m, term, step, with_aux=True, metrics=am), use_reentrant=False)
                 metrics.update({k: v.detach() for k, v in aux_metrics.items()})
-            else:
-                e2e, full = masked_recon(ctx, weights, batch, clean, masks, term, step, with_aux=True, metrics=metrics)
+                return pair
+            return masked_recon(ctx, weights, batch, clean, masks, term, step, with_aux=True, metrics=metrics)
+
+        if ctx.lanes is not None and term.n_samples > 1:  # the draws are independent: side by side on the device
+            pairs = ctx.lanes.run([lambda d=d: one_draw(d) for d in range(term.n_samples)])
+        else:
+            pairs = [one_draw(d) for d in range(term.n_samples)]
+        for e2e, full in pairs:
             vals_e2e.append(e2e)
             vals_full.append(full)
         e2e_mean = torch.stack(vals_e2e).mean()
@@ -587,6 +595,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
 
     with phase("backward"):
         total_loss.backward()
+        if ctx.lanes is not None:
+            ctx.lanes.join_all()  # direct weight-gradient kernels on side streams precede the optimizer
     if ctx.expert_shard is not None and sharded:
         assert ctx.expert_shard.by_component, "expert-split component stacks use the replicated-optimizer layout"
         ctx.collectives.reduce_grads_everywhere(state.ci_fn_opt.params)  # component grads: inside the optimizer step

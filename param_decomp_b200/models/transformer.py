@@ -271,9 +271,14 @@ class TransformerDecomposedModel:
         x = self._norm(resid, self.w[f"layers.{i}.attn_norm.weight"])
         if taps is not None:
             taps[f"attn_in.{i}"] = x
-        q = lin(x, names[0]).view(B, T, a.n_head, self.head_dim)
-        k = lin(x, names[1]).view(B, T, self.n_kv, self.head_dim)
-        v = lin(x, names[2]).view(B, T, self.n_kv, self.head_dim)
+        lanes = getattr(self, "lanes", None)
+        if lanes is not None and x.is_cuda:  # independent products of one input: side by side on the device
+            q, k, v = lanes.run([lambda: lin(x, names[0]), lambda: lin(x, names[1]), lambda: lin(x, names[2])])
+        else:
+            q, k, v = lin(x, names[0]), lin(x, names[1]), lin(x, names[2])
+        q = q.view(B, T, a.n_head, self.head_dim)
+        k = k.view(B, T, self.n_kv, self.head_dim)
+        v = v.view(B, T, self.n_kv, self.head_dim)
         if a.qk_norm:
             q = ports.rms_norm(q, self.w[f"layers.{i}.q_norm.weight"], eps)
             k = ports.rms_norm(k, self.w[f"layers.{i}.k_norm.weight"], eps)
@@ -299,7 +304,12 @@ class TransformerDecomposedModel:
             h = F.gelu(lin(x, "c_fc"))
             down = "down_proj"
         else:
-            h = self._swiglu(lin(x, "gate"), lin(x, "up"))
+            lanes = getattr(self, "lanes", None)
+            if lanes is not None and x.is_cuda:
+                g, u = lanes.run([lambda: lin(x, "gate"), lambda: lin(x, "up")])
+            else:
+                g, u = lin(x, "gate"), lin(x, "up")
+            h = self._swiglu(g, u)
             down = "down"
         if taps is not None:
             taps[f"mlp_hidden.{i}"] = h
