@@ -107,6 +107,8 @@ def main() -> None:
                          "outputs summed, or the batch sharded over it too and jobs stored into their expert's owner")
     ap.add_argument("--no-record", action="store_true",
                     help="issue every step launch by launch from Python instead of replaying the recorded CUDA graph")
+    ap.add_argument("--trace", action="store_true",
+                    help="print a time-stamped line per warm-up step / recording / replay on every rank (diagnostics)")
     ap.add_argument("--no-lanes", action="store_true",
                     help="keep the whole step on one CUDA stream (no side-by-side draws / q,k,v / gate,up)")
     ap.add_argument("--kernel-table", type=Path, default=None,
@@ -153,7 +155,7 @@ def main() -> None:
         shard_backend = "collective"  # component slices: sharded AdamW over the batch axes, clip norm summed over tp
     state = init_train_state(run.model, run.ci_fn, cfg.pd, objective, topo.device, rows, cfg.data.seq_len,
                              use_fused_optim=True, shard_group=topo.data_group, shard_backend=shard_backend,
-                             expert_shard=expert_shard)
+                             expert_shard=expert_shard, peer_wait_limit_s=5.0)
     tokens_per_step = cfg.pd.batch_size * cfg.data.seq_len
 
     def sync() -> None:
@@ -168,8 +170,18 @@ def main() -> None:
 
     step_fn = RecordedTrainStep(ctx, state, enabled=not args.no_record, eager_steps=args.warmup,
                                 concurrent=not args.no_lanes)
+    t_start = time.perf_counter()
+
+    def trace(what: str) -> None:
+        if args.trace:
+            torch.cuda.synchronize()
+            print(f"[rank {topo.rank} +{time.perf_counter() - t_start:7.2f}s] {what} "
+                  f"(status word {int(native.status_word().item())})", file=sys.stderr, flush=True)
+
+    trace(f"start: step issue = {'recorded' if step_fn.eligible else step_fn.reason}")
     for s in range(args.warmup + (2 if step_fn.eligible else 0)):
         step_fn(run.sample_train(s))
+        trace(f"warm-up call {s} done, graph {'yes' if step_fn.graph is not None else 'no'}")
     native.check_status()
 
     # ---- end to end: pinned host tokens -> device, step, loss back to the host, every step ----
@@ -179,7 +191,9 @@ def main() -> None:
     host_batches = [src.batch(1000 + i, cfg.pd.batch_size, topo.data_rank, topo.data_world, pin=True)
                     for i in range(args.steps)]
     h2d = host_batches[0].tokens.numel() * host_batches[0].tokens.element_size()
+    trace("before the first barrier")
     sync()
+    trace("end-to-end loop starts")
     t0 = time.perf_counter()
     for hb in host_batches:
         m = step_fn(hb.to(topo.device, non_blocking=True))  # pinned host tokens -> device, every step
@@ -257,6 +271,7 @@ def main() -> None:
                     "d2h_bytes_per_step": 4, "last_loss": loss_host},
             "gpu_launches": launches,
         }))
+    step_fn.release()  # the recorded graph holds NCCL work: it must go before the process group does
     topo.shutdown()
 
 

@@ -104,6 +104,16 @@ class RecordedTrainStep:
     def eligible(self) -> bool:
         return self.reason is None
 
+    def release(self) -> None:
+        """Destroy the recording. Must happen before the process group is torn down: a communicator whose
+        collectives are part of a live CUDA graph does not finish its destruction (the process would hang
+        at exit)."""
+        if self.graph is not None:
+            torch.cuda.synchronize()
+            self.graph.reset()
+            self.graph = None
+            self._metrics = {k: v.detach().clone() for k, v in self._metrics.items()}
+
     def __call__(self, batch: Any, nontarget_batch: Any = None) -> dict[str, Tensor]:
         if not self.eligible:
             return train_step(self.ctx, self.state, batch, nontarget_batch)

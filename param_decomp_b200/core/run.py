@@ -315,62 +315,65 @@ def run_decomposition_training(
         acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
         profiler = profile(activities=acts)
 
-    while state.step < pd.steps:
-        step = state.step
-        if evaluation is not None and evaluation.is_due(step):
-            check_device_status("before an evaluation")
-            sync_masters(for_save=False)
-            ev = collectives.average_scalars(evaluation.run(step, state, ctx))
-            if sink is not None and ev:
-                sink.log(step, ev, prefix="eval/")
-        if saving and step > 0 and step % cadence.checkpointing.save_every == 0 and ckpt.latest_step(run_dir) != step:  # type: ignore[union-attr,arg-type]
+    try:
+        while state.step < pd.steps:
+            step = state.step
+            if evaluation is not None and evaluation.is_due(step):
+                check_device_status("before an evaluation")
+                sync_masters(for_save=False)
+                ev = collectives.average_scalars(evaluation.run(step, state, ctx))
+                if sink is not None and ev:
+                    sink.log(step, ev, prefix="eval/")
+            if saving and step > 0 and step % cadence.checkpointing.save_every == 0 and ckpt.latest_step(run_dir) != step:  # type: ignore[union-attr,arg-type]
+                save()
+
+            batch = sample_batch(step)
+            nt_batch = sample_nontarget_batch(step) if sample_nontarget_batch is not None else None
+            if profiler is not None and entry_steps == 2:
+                profiler.start()
+            metrics = stepper(batch, nt_batch)
+            if profiler is not None and entry_steps == 2 + profile_steps - 1:
+                profiler.stop()
+                (Path(run_dir) / "profile").mkdir(parents=True, exist_ok=True)  # type: ignore[arg-type]
+                profiler.export_chrome_trace(str(Path(run_dir) / "profile" / "trace.json"))  # type: ignore[arg-type]
+                break
+            entry_steps += 1
+
+            if cadence.should_log_train(step) or state.step == pd.steps:
+                check_device_status("at a log step")
+                scalars = {k: v for k, v in metrics.items()}
+                scalars.update(perf.tick(state.step))
+                from param_decomp_b200.core.gauge import uv_norm_ratio_metrics
+
+                if hasattr(state.components_opt, "refresh_full_fp32"):
+                    state.components_opt.refresh_full_fp32()  # sharded masters: gather the shards before reading
+                scalars.update(uv_norm_ratio_metrics(state.components))  # drift of the V/U scale symmetry
+                if extra_log is not None:
+                    scalars.update(extra_log(step, state, ctx))
+                scalars = collectives.average_scalars(scalars)  # per-batch losses: the global-batch mean, as the reference logs
+                floats = sink.log(step, scalars) if sink is not None else {("train/" + k): float(v) for k, v in scalars.items()}
+                assert_all_finite(step, floats)
+                result.last_metrics = floats
+                log.info("step %d  total=%.4e  step_time=%.3fs", step, floats.get("train/loss/total", float("nan")),
+                         floats.get("train/perf/step_time_s", float("nan")))
+
+            if preempt.consensus():
+                log.info("SIGTERM consensus at step %d: saving and exiting", state.step)
+                save()
+                result.stopped_by_sigterm = True
+                break
+            if max_steps_this_entry is not None and entry_steps >= max_steps_this_entry:
+                break
+
+        if state.step >= pd.steps:
+            if evaluation is not None and evaluation.is_due(state.step):
+                sync_masters(for_save=False)
+                ev = collectives.average_scalars(evaluation.run(state.step, state, ctx))
+                if sink is not None and ev:
+                    sink.log(state.step, ev, prefix="eval/")
             save()
-
-        batch = sample_batch(step)
-        nt_batch = sample_nontarget_batch(step) if sample_nontarget_batch is not None else None
-        if profiler is not None and entry_steps == 2:
-            profiler.start()
-        metrics = stepper(batch, nt_batch)
-        if profiler is not None and entry_steps == 2 + profile_steps - 1:
-            profiler.stop()
-            (Path(run_dir) / "profile").mkdir(parents=True, exist_ok=True)  # type: ignore[arg-type]
-            profiler.export_chrome_trace(str(Path(run_dir) / "profile" / "trace.json"))  # type: ignore[arg-type]
-            break
-        entry_steps += 1
-
-        if cadence.should_log_train(step) or state.step == pd.steps:
-            check_device_status("at a log step")
-            scalars = {k: v for k, v in metrics.items()}
-            scalars.update(perf.tick(state.step))
-            from param_decomp_b200.core.gauge import uv_norm_ratio_metrics
-
-            if hasattr(state.components_opt, "refresh_full_fp32"):
-                state.components_opt.refresh_full_fp32()  # sharded masters: gather the shards before reading
-            scalars.update(uv_norm_ratio_metrics(state.components))  # drift of the V/U scale symmetry
-            if extra_log is not None:
-                scalars.update(extra_log(step, state, ctx))
-            scalars = collectives.average_scalars(scalars)  # per-batch losses: the global-batch mean, as the reference logs
-            floats = sink.log(step, scalars) if sink is not None else {("train/" + k): float(v) for k, v in scalars.items()}
-            assert_all_finite(step, floats)
-            result.last_metrics = floats
-            log.info("step %d  total=%.4e  step_time=%.3fs", step, floats.get("train/loss/total", float("nan")),
-                     floats.get("train/perf/step_time_s", float("nan")))
-
-        if preempt.consensus():
-            log.info("SIGTERM consensus at step %d: saving and exiting", state.step)
-            save()
-            result.stopped_by_sigterm = True
-            break
-        if max_steps_this_entry is not None and entry_steps >= max_steps_this_entry:
-            break
-
-    if state.step >= pd.steps:
-        if evaluation is not None and evaluation.is_due(state.step):
-            sync_masters(for_save=False)
-            ev = collectives.average_scalars(evaluation.run(state.step, state, ctx))
-            if sink is not None and ev:
-                sink.log(state.step, ev, prefix="eval/")
-        save()
+    finally:
+        stepper.release()  # (also on an exception: a live recording blocks the process group's teardown)
     result.final_step = state.step
     if own_sink and sink is not None:
         sink.close()

@@ -223,8 +223,9 @@ class Topology:
         """Leave the job. A rank that is unwinding from an exception (`failed`) does not wait for the others
         at a barrier they may never reach - their next collective ends with an error instead."""
         if self.owns_process_group and dist.is_initialized():
-            if not failed:
-                dist.barrier(group=self.cpu_group)
+            if failed:
+                return  # no barrier, no communicator teardown (it can block on peers): the process is about to exit
+            dist.barrier(group=self.cpu_group)
             dist.destroy_process_group()
 
 
