@@ -196,6 +196,16 @@ class PretrainedQwen35MoeTarget(BaseConfig):
     run_path: str
 
 
+class Llama3RopeScalingConfig(BaseConfig):
+    """Llama-3.1 long-context rescaling of the RoPE frequencies (`rope_scaling` with `rope_type: llama3` in a
+    HuggingFace `config.json`)."""
+
+    factor: PositiveFloat = 8.0
+    low_freq_factor: PositiveFloat = 1.0
+    high_freq_factor: PositiveFloat = 4.0
+    original_max_position_embeddings: PositiveInt = 8192
+
+
 class TransformerArchConfig(BaseConfig):
     """Inline architecture of a decoder-only LM (addition: the reference always derives this from a
     checkpoint). Covers Llama / Qwen3 / LlamaSimpleMLP shapes and the plain top-k MoE."""
@@ -210,6 +220,7 @@ class TransformerArchConfig(BaseConfig):
     vocab_size: PositiveInt
     max_seq_len: PositiveInt = 2048
     rope_theta: PositiveFloat = 10000.0
+    rope_scaling: Llama3RopeScalingConfig | None = None
     rms_eps: PositiveFloat = 1e-6
     qk_norm: bool = False
     tie_embeddings: bool = False

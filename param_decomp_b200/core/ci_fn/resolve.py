@@ -76,7 +76,8 @@ def build_lm_ci_fn(cfg: Any, model: Any, g: torch.Generator) -> nn.Module:
         widths = tap_widths_for(model, layers, cfg.input_tap)
         cond = None
         if cfg.component_conditioning is not None:
-            cond = {"output_scale_init": cfg.component_conditioning.output_scale_init}
+            cond = {"output_scale_init": cfg.component_conditioning.output_scale_init,
+                    "min_n_tokens": cfg.component_conditioning.calibration.min_n_tokens}
             for s in _sites(model):  # conditioning also reads each site's own input
                 widths.setdefault(site_taps[s.name], s.d_in)
         return GlobalTransformerCIFn(widths, {s.name: s.C for s in _sites(model)}, site_taps, cfg.d_model, cfg.n_blocks,

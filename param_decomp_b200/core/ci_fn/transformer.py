@@ -42,8 +42,36 @@ from param_decomp_b200.models import ports
 FP32_EPS = torch.finfo(torch.float32).eps
 
 
+class FusedLinear(nn.Linear):
+    """`nn.Linear` whose product runs on the hand-written tcgen05 GEMM (bf16 operands, fp32 masters and
+    gradients) once the builder sets `fused` on the sm_100a backend; plain `F.linear` otherwise (CPU, the eager
+    backend, widths that are not multiples of 8 elements - the TMA row pitch)."""
+
+    fused = False
+
+    def forward(self, x: Tensor) -> Tensor:  # type: ignore[override]
+        if self.fused and x.is_cuda:
+            from param_decomp_b200.ops.linear import trainable_linear, trainable_linear_supported
+
+            if trainable_linear_supported(x, self.weight):
+                return trainable_linear(x, self.weight, self.bias)
+        return F.linear(x, self.weight.to(x.dtype), None if self.bias is None else self.bias.to(x.dtype))
+
+
+def _norm(x: Tensor, w: Tensor | None) -> Tensor:
+    """Weightless / learned-scale RMS norm with eps = fp32 eps; the bandwidth kernel on bf16 CUDA activations."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        from param_decomp_b200.ops import native
+
+        if native.available():
+            from param_decomp_b200.ops.elementwise import rms_norm
+
+            return rms_norm(x, None if w is None else w.to(torch.bfloat16), FP32_EPS)
+    return ports.rms_norm(x, w, FP32_EPS)
+
+
 def _linear(d_in: int, d_out: int, g: torch.Generator | None, bias: bool = True) -> nn.Linear:
-    lin = nn.Linear(d_in, d_out, bias=bias)
+    lin = FusedLinear(d_in, d_out, bias=bias)
     with torch.no_grad():
         lin.weight.copy_(torch.randn(d_out, d_in, generator=g) / math.sqrt(d_in))
         if bias:
@@ -106,8 +134,8 @@ class CIBlock(nn.Module):
         self.n2 = nn.Parameter(torch.ones(d_model)) if learned_norm_scale else None
 
     def forward(self, x: Tensor, positions: Tensor, segment_ids: Tensor | None, **ffn_ctx: Any) -> Tensor:
-        x = x + self.attn(ports.rms_norm(x, self.n1, FP32_EPS), positions, segment_ids)
-        return x + self.ffn(ports.rms_norm(x, self.n2, FP32_EPS), **ffn_ctx)
+        x = x + self.attn(_norm(x, self.n1), positions, segment_ids)
+        return x + self.ffn(_norm(x, self.n2), **ffn_ctx)
 
 
 def normed_concat(taps: dict[str, Tensor], keys: tuple[str, ...]) -> Tensor:
@@ -193,6 +221,7 @@ class GlobalTransformerCIFn(nn.Module):
         self.final_norm = final_norm
         self.heads = nn.ModuleDict({ComponentConditioning.key(s): _linear(d_model, c, g) for s, c in site_cs.items()})
         self.conditioning = ComponentConditioning(site_cs, conditioning["output_scale_init"]) if conditioning else None
+        self.calibration_min_tokens = int(conditioning.get("min_n_tokens", 1)) if conditioning else 1
         self.remat = False
 
     def forward(self, taps: dict[str, Tensor], **ctx: Any) -> dict[str, Tensor]:
@@ -204,6 +233,15 @@ class GlobalTransformerCIFn(nn.Module):
             comps = ctx["components"]
             h = {s: comps.component_activations(s, taps[self.site_taps[s]].float()) for s in self.site_cs}
             if not self.conditioning.calibrated:
+                # the first batch calibrates the input scales; it must hold enough tokens for the quantile
+                # (param_decomp/experiments/lm/ci_fn_init.py:70-77 asserts the same on the global batch)
+                import torch.distributed as dist
+
+                first = next(iter(h.values()))
+                n_tokens = first.numel() // first.shape[-1] * (dist.get_world_size() if dist.is_initialized() else 1)
+                assert n_tokens >= self.calibration_min_tokens, (
+                    f"the calibration batch holds {n_tokens} tokens, fewer than calibration.min_n_tokens "
+                    f"{self.calibration_min_tokens}")
                 self.conditioning.calibrate({k: v.detach() for k, v in h.items()})
             out = {s: out[s] + self.conditioning(s, h[s]) for s in self.site_cs}
         return out
@@ -242,10 +280,44 @@ class ChunkwiseTransformerCIFn(nn.Module):
         return sum(fn.useful_flops_per_position() for fn in self.chunk_fns)  # type: ignore[operator]
 
 
+def routed_linear(rows: Tensor, W: Tensor, sel: BlockSelection, per_job: bool, fused: bool) -> Tensor:
+    """`out[n, s] = in[n, s] @ W[e(n, s)]` for the experts `sel.indices [.., k]` each token selected:
+    `rows` is `[N, d]` (one row per token, shared by its `k` jobs) or, with `per_job`, `[N * k, d]` (one row
+    per job, token-major); `W [E, d, h]`; returns `[N * k, h]`. Never gathers per-token weight copies: on the
+    fused backend the jobs are sorted by expert into padded row groups and run as ONE grouped tcgen05 product
+    (`ops/grouped.py`, the layout is shared with the target's own expert products of that routing decision);
+    elsewhere each expert's jobs are one dense product."""
+    idx = sel.indices.reshape(-1, sel.indices.shape[-1])
+    N, k = idx.shape
+    E = W.shape[0]
+    if fused and rows.is_cuda and W.shape[1] % 8 == 0 and W.shape[2] % 8 == 0:
+        from param_decomp_b200.ops.grouped import JobLayout, grouped_linear_trainable
+
+        layout = JobLayout.cached(sel.indices, E)
+        r = rows.to(torch.bfloat16)
+        padded = layout.scatter_rows(r) if per_job else layout.expand_tokens(r.contiguous(), k)
+        return layout.gather_rows(grouped_linear_trainable(padded, W, None, layout))
+    flat_e = idx.reshape(-1)
+    order = flat_e.argsort(stable=True)
+    counts = torch.bincount(flat_e, minlength=E).tolist()
+    src = rows if per_job else rows.repeat_interleave(k, dim=0)
+    pieces, start = [], 0
+    for e, n in enumerate(counts):
+        if n:
+            jobs = order[start:start + n]
+            pieces.append(src[jobs].to(W.dtype) @ W[e])
+            start += n
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=order.device)
+    return torch.cat(pieces)[inv]
+
+
 class RoutedExpertFFN(nn.Module):
     """Concat-wide routed expert bank: for each covered target layer one bank of `E` SwiGLU experts,
     dispatched by that layer's captured routing, plus a dense shared SwiGLU expert. The last block's
     bank also carries per-expert heads that emit CI for the experts' component blocks."""
+
+    fused = False  # set by the builder on the fused sm_100a backend
 
     def __init__(self, d_model: int, n_layers: int, n_experts: int, hidden: int, shared_hidden: int,
                  g: torch.Generator | None) -> None:
@@ -258,19 +330,22 @@ class RoutedExpertFFN(nn.Module):
         self.shared = CIFeedForward(d_model, shared_hidden, "swiglu", g)
 
     def expert_hidden(self, x: Tensor, layer: int, sel: BlockSelection) -> Tensor:
-        """`[B, T, k, hidden]`: SwiGLU hidden of the selected experts of `layer`."""
-        wg, wu = self.w_gate[layer][sel.indices], self.w_up[layer][sel.indices]  # [B,T,k,d,h]
-        xe = x.unsqueeze(-2).unsqueeze(-2)
-        return F.silu((xe @ wg).squeeze(-2)) * (xe @ wu).squeeze(-2)
+        """`[N * k, hidden]` (token-major jobs): SwiGLU hidden of the selected experts of `layer`."""
+        x2 = x.reshape(-1, x.shape[-1])
+        gate = routed_linear(x2, self.w_gate[layer], sel, False, self.fused)
+        up = routed_linear(x2, self.w_up[layer], sel, False, self.fused)
+        return F.silu(gate) * up
 
     def forward(self, x: Tensor, routing: list[BlockSelection] | None = None) -> Tensor:
         out = self.shared(x)
         if routing is None:
             return out
+        lead, d = x.shape[:-1], x.shape[-1]
         for layer, sel in enumerate(routing):
+            k = sel.indices.shape[-1]
             h = self.expert_hidden(x, layer, sel)
-            y = (h.unsqueeze(-2) @ self.w_down[layer][sel.indices]).squeeze(-2)  # [B,T,k,d]
-            out = out + (y * sel.weights.unsqueeze(-1).to(y.dtype)).sum(-2)
+            y = routed_linear(h, self.w_down[layer], sel, True, self.fused).reshape(*lead, k, d)
+            out = out + (y * sel.weights.unsqueeze(-1).to(y.dtype)).sum(-2).to(out.dtype)
         return out
 
 
@@ -322,13 +397,12 @@ class MoEChunkwiseTransformerCIFn(nn.Module):
             for s in ch["dense_sites"]:
                 out[s] = self.dense_heads[ci][ComponentConditioning.key(s)](x)
             last_ffn: RoutedExpertFFN = bb.blocks[-1].ffn  # type: ignore[assignment]
-            xn = ports.rms_norm(x, bb.blocks[-1].n2, FP32_EPS)
+            xn = _norm(x, bb.blocks[-1].n2)
             for s, (layer, c_block) in ch["blocked_sites"].items():
                 sel = routing[layer]
-                h = last_ffn.expert_hidden(xn, layer, sel)  # [B,T,k,hidden]
-                heads = self.expert_heads[head_i][sel.indices]  # [B,T,k,hidden,c]
-                vals = (h.unsqueeze(-2) @ heads).squeeze(-2)  # [B,T,k,c]
-                out[s] = SelectedCI(vals.flatten(-2), sel, self.n_experts)
+                h = last_ffn.expert_hidden(xn, layer, sel)  # [N * k, hidden], token-major jobs
+                vals = routed_linear(h, self.expert_heads[head_i], sel, True, last_ffn.fused)  # [N * k, c]
+                out[s] = SelectedCI(vals.reshape(*sel.indices.shape[:-1], -1), sel, self.n_experts)
                 head_i += 1
         return out
 

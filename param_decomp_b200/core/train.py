@@ -294,12 +294,16 @@ def evaluate_minimality(ctx: StepContext, state: TrainState, ci: CI, step: int, 
     metrics["schedules/gamma"] = gamma if isinstance(gamma, Tensor) else torch.tensor(gamma)
     activity = None
     freq_total = None
-    for name in ci.lower:
-        if ci.activity is not None:
-            f_local = ci.activity[name]
-        else:
-            f_local = loss_fns.component_activity(ci.upper[name], gamma, cfg.normalize_at_one)
-        f = ctx.collectives.mean(f_local)  # global-batch mean BEFORE the log
+    names = list(ci.lower)
+    f_locals = [ci.activity[n] if ci.activity is not None
+                else loss_fns.component_activity(ci.upper[n], gamma, cfg.normalize_at_one) for n in names]
+    if ctx.collectives.world_size > 1:
+        # global-batch mean BEFORE the log, all sites' `[C]` vectors packed into ONE (differentiable) all-reduce
+        flat = ctx.collectives.mean(torch.cat([f.reshape(-1).float() for f in f_locals]))
+        f_globals = [t.view_as(f) for t, f in zip(flat.split([f.numel() for f in f_locals]), f_locals)]
+    else:
+        f_globals = f_locals
+    for name, f in zip(names, f_globals):
         act = f.sum()
         activity = act if activity is None else activity + act
         if cfg.frequency is not None:

@@ -121,9 +121,10 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
     ci_fn = build_ci_fn(cfg.decomposition.ci, model, cfg.pd.seed)
     if backend == "fused_sm100":
         from param_decomp_b200.core.ci_fn.mlp import BlockedSiteMLP, SiteMLP
+        from param_decomp_b200.core.ci_fn.transformer import FusedLinear, RoutedExpertFFN
 
         for m in ci_fn.modules():
-            if isinstance(m, (SiteMLP, BlockedSiteMLP)):
+            if isinstance(m, (SiteMLP, BlockedSiteMLP, FusedLinear, RoutedExpertFFN)):
                 m.fused = True
 
     seq = cfg.data.seq_len

@@ -30,6 +30,22 @@ def optimizer_sharding(cfg: LMExperimentConfig | LMTargetedExperimentConfig, top
     return topo.data_group, backend
 
 
+def warn_inert_options(cfg, log) -> None:
+    """Name every runtime option that parses (the schema is shared with XLA-based configs) and has no effect
+    here, once per run, instead of ignoring it silently."""
+    rt = cfg.runtime
+    if rt.compiler_options != "bare":
+        log.warning("runtime.compiler_options=%r has no effect: there is no tracing compiler, the step is hand-written "
+                    "kernels recorded as a CUDA graph", rt.compiler_options)
+    if "compilation_cache_dir" in rt.model_fields_set:
+        log.warning("runtime.compilation_cache_dir has no effect: nothing is compiled at run time")
+    name = rt.sharding if isinstance(rt.sharding, str) else "table"
+    if name not in ("ddp",) and cfg.runtime.mesh is not None:
+        log.info("runtime.sharding=%s: masters, moments and gradient reduction are sharded over the batch axes "
+                 "(reduce-scatter + AdamW + all-gather in one kernel per step); the bf16 working copy is re-gathered "
+                 "once per step, not per layer", name)
+
+
 def check_runtime_supported(cfg) -> None:
     """Refuse, rather than silently ignore, runtime options this engine does not act on."""
     if cfg.runtime.sequence_sharding != "replicate":
@@ -59,6 +75,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     mode = expert_mode_of(cfg)
     topo = topology.initialize(cfg.runtime.mesh, device, batch_over_tp=mode == "all_to_all")
     log = get_logger(topo.rank)
+    warn_inert_options(cfg, log)
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
                        expert_mode=mode)
     collectives = topo.collectives()

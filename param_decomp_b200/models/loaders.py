@@ -65,8 +65,23 @@ def read_safetensors(paths: list[Path], dtype: torch.dtype, device) -> dict[str,
     return out
 
 
+def _llama3_rope_scaling(cfg: dict[str, Any]):
+    """`rope_scaling: {rope_type: llama3, factor, low_freq_factor, high_freq_factor,
+    original_max_position_embeddings}` of a HuggingFace config, or None."""
+    rs = cfg.get("rope_scaling") or {}
+    if (rs.get("rope_type") or rs.get("type")) != "llama3":
+        return None
+    from param_decomp_b200.config.experiments import Llama3RopeScalingConfig
+
+    return Llama3RopeScalingConfig(
+        factor=rs.get("factor", 8.0), low_freq_factor=rs.get("low_freq_factor", 1.0),
+        high_freq_factor=rs.get("high_freq_factor", 4.0),
+        original_max_position_embeddings=rs.get("original_max_position_embeddings", 8192))
+
+
 def arch_from_hf_config(cfg: dict[str, Any], family: str = "glu_transformer") -> TransformerArchConfig:
     return TransformerArchConfig(
+        rope_scaling=_llama3_rope_scaling(cfg),
         family=family, n_layer=cfg["num_hidden_layers"], d_model=cfg["hidden_size"], n_head=cfg["num_attention_heads"],
         n_kv_head=cfg.get("num_key_value_heads"), head_dim=cfg.get("head_dim"), d_ff=cfg["intermediate_size"],
         vocab_size=cfg["vocab_size"], max_seq_len=cfg.get("max_position_embeddings", 2048),

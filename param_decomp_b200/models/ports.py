@@ -43,11 +43,14 @@ def llama3_scale_inv_freq(inv_freq: Tensor, factor: float = 8.0, low: float = 1.
     return torch.where((wavelen <= low_wl) & (wavelen >= high_wl), mid, scaled)
 
 
-def rope_cos_sin(positions: Tensor, rotary_dim: int, theta: float, llama3_scaling: bool = False) -> tuple[Tensor, Tensor]:
-    """`positions [..., T]` -> `cos, sin [..., T, rotary_dim]` (halves duplicated, rotate-half form)."""
+def rope_cos_sin(positions: Tensor, rotary_dim: int, theta: float, scaling=None) -> tuple[Tensor, Tensor]:
+    """`positions [..., T]` -> `cos, sin [..., T, rotary_dim]` (halves duplicated, rotate-half form). `scaling`:
+    an object with the Llama-3.1 fields `factor`, `low_freq_factor`, `high_freq_factor`,
+    `original_max_position_embeddings`, or None."""
     inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, device=positions.device, dtype=torch.float32) / rotary_dim))
-    if llama3_scaling:
-        inv = llama3_scale_inv_freq(inv)
+    if scaling is not None:
+        inv = llama3_scale_inv_freq(inv, scaling.factor, scaling.low_freq_factor, scaling.high_freq_factor,
+                                    scaling.original_max_position_embeddings)
     ang = positions.float().unsqueeze(-1) * inv
     ang = torch.cat([ang, ang], dim=-1)
     return ang.cos(), ang.sin()
@@ -118,13 +121,15 @@ def sdpa_reference(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, segment
 
 def sdpa(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, segment_ids: Tensor | None = None,
          implementation: str = "flash") -> Tensor:
-    """Attention dispatcher. `flash`: the hand-written sm_100a kernel when available for this shape,
-    otherwise torch's fused SDPA; `xla`: the materialised oracle."""
+    """Attention dispatcher. `flash`: the hand-written sm_100a kernel (shapes outside its native range are padded
+    to it, see `ops/attention.py`; nothing is handed to a library kernel behind the caller's back); `sdpa`: torch's
+    fused attention, the eager backend's explicit choice on a GPU; `xla`: the materialised oracle (and every CPU
+    call)."""
     if implementation == "xla" or not q.is_cuda:
         return sdpa_reference(q, k, v, causal, segment_ids)
-    from param_decomp_b200.ops import attention as attn_ops
+    if implementation != "sdpa":
+        from param_decomp_b200.ops import attention as attn_ops
 
-    if attn_ops.supported(q, k, v, segment_ids):
         return attn_ops.flash_attention(q, k, v, causal, segment_ids)
     mask = attention_mask(q.shape[1], False, segment_ids, q.device) if segment_ids is not None else None
     if mask is not None and causal:

@@ -324,7 +324,7 @@ class TransformerDecomposedModel:
         B, T = tokens.shape
         resid = F.embedding(tokens.long(), self.w["embed.weight"])
         pos = batch.positions if batch.positions is not None else torch.arange(T, device=tokens.device)[None]
-        cos, sin = ports.rope_cos_sin(pos, self.head_dim, a.rope_theta)
+        cos, sin = ports.rope_cos_sin(pos, self.head_dim, a.rope_theta, a.rope_scaling)
         taps: dict[str, Tensor] | None = {} if want_taps else None
         captures: dict[str, Tensor] = {}
         for i in range(a.n_layer):

@@ -110,3 +110,52 @@ class _BmmBias(torch.autograd.Function):
 
 def bmm_bias(x: Tensor, W: Tensor, b: Tensor) -> Tensor:
     return _BmmBias.apply(x, W, b)
+
+
+class _TrainableLinear(torch.autograd.Function):
+    """`y = x W^T + b` for ONE linear with trainable fp32 masters (`W [d_out, d_in]`, torch's layout): bf16
+    operands on the tcgen05 kernel, fp32 weight / bias gradients, the transformer CI functions' linears."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, W: Tensor, b: Tensor | None) -> Tensor:  # type: ignore[override]
+        from param_decomp_b200.ops.elementwise import cast_bf16
+
+        Wb = cast_bf16(W.detach().contiguous())
+        y = torch.empty(x.shape[0], W.shape[0], device=x.device, dtype=torch.bfloat16)
+        nv.gemm(x, Wb, y, bias=None if b is None else b.detach().float().contiguous())
+        ctx.save_for_backward(x, Wb)
+        ctx.has_bias = b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        from param_decomp_b200.ops.elementwise import colsum_bf16
+
+        x, Wb = ctx.saved_tensors
+        dy = dy.contiguous()
+        N, d_in = x.shape
+        d_out = Wb.shape[0]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            nv.gemm(dy, Wb, dx, b_mn=True)  # dx = dy W
+        dW = torch.zeros(d_out, d_in, device=x.device, dtype=torch.float32)
+        tiles = ((d_out + 127) // 128) * ((d_in + 255) // 256)
+        nv.gemm(dy, x, dW, a_mn=True, b_mn=True, accumulate=True, split_k=max(1, min(148 // max(tiles, 1), N // 512)))
+        db = colsum_bf16(dy) if ctx.has_bias else None
+        return dx, dW, db
+
+
+def trainable_linear_supported(x: Tensor, W: Tensor) -> bool:
+    return x.is_cuda and W.shape[0] % 8 == 0 and W.shape[1] % 8 == 0
+
+
+def trainable_linear(x: Tensor, W: Tensor, b: Tensor | None) -> Tensor:
+    """`x [..., d_in]` (any float dtype; computed in bf16) -> `[..., d_out]` bf16."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.dtype != torch.bfloat16:
+        x2 = x2.to(torch.bfloat16)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    return _TrainableLinear.apply(x2, W, b).reshape(*lead, -1)

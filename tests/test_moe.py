@@ -75,3 +75,47 @@ def test_unmasked_with_delta_reproduces_target_and_step_trains():
     assert torch.isfinite(m["loss/total"]) and float(m["loss/StochasticReconLoss"]) > 0
     g = st.components.V["experts_gate"].grad
     assert g is not None and float(g.abs().sum()) > 0
+
+
+def test_moe_chunkwise_ci_fn_steps_and_routed_products_match_gathers():
+    """The block-selected (expert-routed) chunkwise CI transformer: one engine step trains it, it emits narrow
+    `SelectedCI` for expert sites, and its routed products equal the per-token weight-gather formula they replace."""
+    from param_decomp_b200.core.ci_fn.transformer import MoEChunkwiseTransformerCIFn, routed_linear
+    from param_decomp_b200.core.components import SelectedCI
+    from param_decomp_b200.core.objective import build_objective
+    from param_decomp_b200.core.run import init_train_state
+    from param_decomp_b200.core.train import StepContext, run_ci_fn, train_step
+
+    torch.manual_seed(0)
+    sel = BlockSelection(torch.tensor([[[0, 1], [1, 2], [3, 0], [2, 3], [0, 2]]]), torch.rand(1, 5, 2))
+    x, W = torch.randn(1, 5, 8), torch.randn(6, 8, 4)  # experts 4 and 5 receive no job
+    got = routed_linear(x.reshape(5, 8), W, sel, per_job=False, fused=False).reshape(1, 5, 2, 4)
+    ref = (x.unsqueeze(-2).unsqueeze(-2) @ W[sel.indices]).squeeze(-2)
+    assert torch.allclose(got, ref, atol=1e-6)
+    jobs = torch.randn(10, 8)
+    got = routed_linear(jobs, W, sel, per_job=True, fused=False).reshape(1, 5, 2, 4)
+    ref = (jobs.reshape(1, 5, 2, 1, 8) @ W[sel.indices]).squeeze(-2)
+    assert torch.allclose(got, ref, atol=1e-6)
+
+    c = moe_cfg().model_dump(mode="json")
+    c["decomposition"]["ci"] = {
+        "type": "moe_chunkwise_transformer", "d_model": 16, "n_blocks": 1, "blocks_per_chunk": 1,
+        "attention": {"kind": "mha", "n_heads": 2, "implementation": "xla", "mask": "causal"},
+        "expert_ffn_hidden": 8, "shared_ffn_hidden": 16,
+        "expert_implementation": "ragged_dot", "input_tap": "all_block_taps"}
+    cfg = LMExperimentConfig.model_validate(c)
+    run = build_lm_run(cfg, None, "cpu")
+    assert isinstance(run.ci_fn, MoEChunkwiseTransformerCIFn)
+    obj = build_objective(cfg.pd)
+    ctx = StepContext.build(run.model, obj, cfg.pd)
+    st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, "cpu", 3, 8)
+    batch = run.sample_train(0)
+    with torch.no_grad():
+        ci = run_ci_fn(ctx, st, run.model.clean_forward(batch))
+    narrow = ci.lower["layers.0.mlp.experts_gate"]
+    assert isinstance(narrow, SelectedCI) and narrow.values.shape == (3, 8, 2 * 4)
+    assert ci.lower["layers.0.self_attn.q_proj"].shape == (3, 8, 8)
+    before = [p.detach().clone() for p in run.ci_fn.parameters()]
+    m = train_step(ctx, st, batch)
+    assert torch.isfinite(m["loss/total"])
+    assert sum(int(not torch.equal(a, b)) for a, b in zip(before, run.ci_fn.parameters())) > len(before) // 2
