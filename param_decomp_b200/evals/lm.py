@@ -119,4 +119,4 @@ class LMEvaluation:
         return {}
 
     def run(self, step: int, state: TrainState, ctx: StepContext) -> dict[str, Any]:
-        return run_eval_metrics(self.cfg, step, state, ctx, self.sample, extra=self._extra)
+        return run_eval_metrics(self.cfg, step, state, ctx, self.sample, extra=self._extra, run_dir=self.run_dir)

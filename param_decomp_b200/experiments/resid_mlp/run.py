@@ -48,7 +48,7 @@ def run_resid_mlp(cfg: ResidMLPExperimentConfig, data_root: Path | None, run_id:
         return sample_sparse_features(n, cfg.target.n_features, cfg.data.feature_probability,
                                       cfg.data.data_generation_type, g, device, low=-1.0)
 
-    evaluation = ToyEvaluation(cfg.eval, sample_eval, cfg.target.n_features, ("layers.0.mlp_in",))
+    evaluation = ToyEvaluation(cfg.eval, sample_eval, cfg.target.n_features, ("layers.0.mlp_in",), run_dir=run_dir)
     try:
         return run_decomposition_training(model, ci_fn, cfg.pd, cfg.cadence, sample_batch, device=device,
                                           run_dir=run_dir, sink=sink, evaluation=evaluation,

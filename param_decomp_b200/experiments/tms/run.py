@@ -47,7 +47,7 @@ def run_tms(cfg: TMSExperimentConfig, data_root: Path | None, run_id: str | None
         return sample_sparse_features(n, cfg.target.n_features, cfg.data.feature_probability,
                                       cfg.data.data_generation_type, g, device)
 
-    evaluation = ToyEvaluation(cfg.eval, sample_eval, cfg.target.n_features, ("linear1",))
+    evaluation = ToyEvaluation(cfg.eval, sample_eval, cfg.target.n_features, ("linear1",), run_dir=run_dir)
     try:
         return run_decomposition_training(model, ci_fn, cfg.pd, cfg.cadence, sample_batch, device=device,
                                           run_dir=run_dir, sink=sink, evaluation=evaluation,

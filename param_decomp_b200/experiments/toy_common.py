@@ -49,11 +49,12 @@ class ToyEvaluation:
     identity-CI ground truth of the toys."""
 
     def __init__(self, eval_cfg: EvalConfig | None, sample_eval_batch, n_features: int,
-                 identity_sites: tuple[str, ...]) -> None:
+                 identity_sites: tuple[str, ...], run_dir: Any = None) -> None:
         self.cfg = eval_cfg
         self.sample = sample_eval_batch
         self.n_features = n_features
         self.identity_sites = identity_sites
+        self.run_dir = run_dir  # figures of the slow-tier metrics go to `<run_dir>/figures/`
 
     def is_due(self, step: int) -> bool:
         if self.cfg is None:
@@ -64,7 +65,15 @@ class ToyEvaluation:
         from param_decomp_b200.evals.core import run_eval_metrics
 
         assert self.cfg is not None
-        out = run_eval_metrics(self.cfg, step, state, ctx, self.sample)
+        def probe_ci():
+            # one probe per feature (that feature alone, at 0.75): rows = features, columns = components
+            dev = next(state.components.parameters()).device
+            clean = ctx.model.clean_forward(single_feature_probe(self.n_features, device=dev))
+            return run_ci_fn(ctx, state, clean).dense_lower()
+
+        from param_decomp_b200.core.train import run_ci_fn
+
+        out = run_eval_metrics(self.cfg, step, state, ctx, self.sample, run_dir=self.run_dir, probe_ci=probe_ci)
         out.update(identity_metrics(state, ctx, self.n_features, self.identity_sites))
         return out
 

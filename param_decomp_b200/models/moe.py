@@ -303,5 +303,8 @@ def build_moe_model(arch: TransformerArchConfig, weights: dict[str, Tensor], sit
         from param_decomp_b200.parallel.ep import shard_expert_weights
 
         weights = shard_expert_weights(weights, arch.n_experts, ep.rank, ep.world)
-    return MoEDecomposedModel(arch, weights, site_cs, backend=backend, attention=target_cfg.attention_implementation,
+    model = MoEDecomposedModel(arch, weights, site_cs, backend=backend, attention=target_cfg.attention_implementation,
                               ep=ep)
+    edge = getattr(target_cfg, "output_edge", None)
+    model.n_vocab_chunks = getattr(edge, "n_vocab_chunks", None)  # streamed output edge: chunks of positions
+    return model

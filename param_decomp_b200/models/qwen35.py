@@ -416,5 +416,8 @@ def build_qwen35_model(arch: TransformerArchConfig, weights: dict[str, Tensor], 
         weights = shard_expert_weights({k.replace("mlp.experts.", "mlp.experts_"): v for k, v in weights.items()},
                                        arch.n_experts, ep.rank, ep.world)
         weights = {k.replace("mlp.experts_", "mlp.experts."): v for k, v in weights.items()}
-    return Qwen35DecomposedModel(arch, weights, site_cs, backend=backend,
+    model = Qwen35DecomposedModel(arch, weights, site_cs, backend=backend,
                                  attention=target_cfg.attention_implementation, ep=ep)
+    edge = getattr(target_cfg, "output_edge", None)
+    model.n_vocab_chunks = getattr(edge, "n_vocab_chunks", None)  # streamed output edge: chunks of positions
+    return model

@@ -357,11 +357,11 @@ class TransformerDecomposedModel:
     # -- output edge: KL(clean || masked) over the vocabulary ---------------------------------------
     def _clean_logit_stats(self, hidden: Tensor) -> dict[str, Tensor]:
         """Fused backend: the clean logits are formed once per step and reused by every draw."""
-        if self.backend == "fused_sm100" and hidden.is_cuda:
+        if self.backend == "fused_sm100" and hidden.is_cuda and self.n_vocab_chunks is None:
             from param_decomp_b200.ops import vocab_kl
 
             return {"logits": vocab_kl.padded_logits(hidden.reshape(-1, hidden.shape[-1]), self.head_weight())}
-        return {}
+        return {}  # streamed output edge: no `[positions, vocab]` tensor is ever kept
 
     def recon_loss(self, clean: ForwardResult, masked: ForwardResult) -> Tensor:
         """Mean over positions of `KL(softmax(clean logits) || softmax(masked logits))`.
@@ -372,6 +372,9 @@ class TransformerDecomposedModel:
         if self.backend == "fused_sm100" and hm.is_cuda:
             from param_decomp_b200.ops import vocab_kl
 
+            if self.n_vocab_chunks is not None:  # `output_edge: streamed`: chunks of positions, logits never whole
+                rows = (-(-hm.shape[0] // self.n_vocab_chunks) + 127) // 128 * 128
+                return vocab_kl.kl_from_hidden_streamed(hc, hm, self.head_weight(), rows)
             return vocab_kl.kl_from_hidden(clean.aux["clean_stats"]["logits"], hm, self.head_weight())
         return chunked_kl_from_hidden(hc, hm, self.head_weight(), self.kl_token_chunk)
 

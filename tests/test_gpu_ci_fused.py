@@ -102,3 +102,35 @@ def test_routed_linear_grouped_matches_per_expert_loop():
     native.check_status()
     assert rel(out, ref) < 2e-2 and rel(W.grad, We.grad) < 4e-2
     assert float(W.grad[E - 1].abs().sum()) == 0.0
+
+
+def test_streamed_vocab_kl_matches_materialised_and_bounds_memory():
+    """`output_edge: streamed` on the fused backend: same loss and hidden-state gradient as the materialised
+    form, and no `[positions, vocab]` tensor - peak extra memory stays near 3 x chunk x vocab bf16."""
+    from param_decomp_b200.ops import native, vocab_kl
+
+    torch.manual_seed(0)
+    n, d, V, rows = 4096, 256, 50272, 512
+    head = (torch.randn(V, d, device="cuda") / d**0.5).to(torch.bfloat16)
+    hc = torch.randn(n, d, device="cuda", dtype=torch.bfloat16)
+    hm = (hc.float() + 0.3 * torch.randn(n, d, device="cuda")).to(torch.bfloat16)
+    a = hm.clone().requires_grad_(True)
+    la = vocab_kl.kl_from_hidden(vocab_kl.padded_logits(hc, head), a, head)
+    (la * 3.0).backward()
+    del la
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    b = hm.clone().requires_grad_(True)
+    lb = vocab_kl.kl_from_hidden_streamed(hc, b, head, rows)
+    (lb * 3.0).backward()
+    torch.cuda.synchronize()
+    native.check_status()
+    peak = torch.cuda.max_memory_allocated() - base
+    one_full = n * V * 2
+    assert peak < 3.5 * rows * V * 2 + 16 * n * d, (peak, rows * V * 2)
+    assert peak < 0.5 * one_full  # far below even ONE materialised logits tensor
+    la2 = vocab_kl.kl_from_hidden(vocab_kl.padded_logits(hc, head), hm, head)
+    assert float(lb) == pytest.approx(float(la2), rel=2e-3)
+    assert rel(b.grad, a.grad) < 2e-3
