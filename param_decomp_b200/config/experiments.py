@@ -55,6 +55,25 @@ class ExperimentConfigBase(BaseConfig):
     cadence: Cadence
     wandb: WandbConfig | None = None
 
+    @classmethod
+    def from_file(cls, path: Path | str, data_root: Path | None = None):  # type: ignore[override]
+        """Stored-config boundary: a file written under an older schema is migrated in memory
+        (`infra/migrations.py`; the identity on current files) before validation, so pinned launch configs of
+        old runs still load, resume and serve as fine-tune parents."""
+        import json
+
+        import yaml
+
+        from param_decomp_b200.infra.migrations import migrate_raw
+
+        path = Path(path)
+        raw = json.loads(path.read_text()) if path.suffix == ".json" else yaml.safe_load(path.read_text())
+        try:
+            return cls.model_validate(migrate_raw(raw, data_root) if isinstance(raw, dict) else raw)
+        except Exception as err:
+            err.add_note(f"while validating {cls.__name__} from {path.as_posix()}")
+            raise
+
 
 class ExperimentConfig(ExperimentConfigBase):
     pd: PDConfig

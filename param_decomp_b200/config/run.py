@@ -179,7 +179,9 @@ class Cadence(BaseConfig):
 
 class WandbConfig(BaseConfig):
     project: str
-    metric_schema: Literal["legacy", "v2"] = "legacy"
+    metric_schema: Literal["legacy", "grouped", "v2"] = "legacy"
+    """`grouped`: W&B receives two-level `<group>/<chart>` names (`infra/metric_names.py`); `metrics.jsonl` always
+    keeps the local keys. `v2` is the older spelling of `grouped`."""
     entity: str | None = None
     group: str | None = None
     tags: list[str] = Field(default_factory=list)

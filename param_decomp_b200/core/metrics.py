@@ -74,6 +74,7 @@ class MetricsSink:
     rank: int = 0
     wandb_run: Any = None
     _fh: Any = None
+    names: Any = None  # infra.metric_names.MetricNames: local keys -> the names the W&B mirror logs
 
     @classmethod
     def for_run(cls, run_dir: Path, rank: int = 0, wandb_cfg: Any = None, run_name: str = "",
@@ -81,8 +82,17 @@ class MetricsSink:
         sink = cls(Path(run_dir), rank)
         if rank == 0:
             sink.run_dir.mkdir(parents=True, exist_ok=True)
+            reentry = (sink.run_dir / METRICS_FILENAME).exists()
             sink._fh = open(sink.run_dir / METRICS_FILENAME, "a", buffering=1)
             if wandb_cfg is not None:
+                from param_decomp_b200.infra.metric_names import MetricNames, validate_resume_schema
+
+                pinned = sink.run_dir / LAUNCH_CONFIG_FILENAME
+                if reentry and pinned.exists():  # a resumed run keeps the names it was started with
+                    import yaml
+
+                    validate_resume_schema(yaml.safe_load(pinned.read_text()) or {}, wandb_cfg.metric_schema)
+                sink.names = MetricNames(wandb_cfg.metric_schema)
                 sink.wandb_run = try_wandb_init(wandb_cfg, run_name, sink.run_dir, config_dict)
         return sink
 
@@ -92,7 +102,7 @@ class MetricsSink:
             self._fh.write(json.dumps({"step": step, **flat}) + "\n")
             if self.wandb_run is not None:
                 try:
-                    self.wandb_run.log(flat, step=step)
+                    self.wandb_run.log(self.names.record(flat) if self.names is not None else flat, step=step)
                 except Exception as err:  # W&B trouble is never fatal
                     get_logger().warning("wandb.log failed: %s", err)
         return flat

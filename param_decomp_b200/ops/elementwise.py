@@ -287,14 +287,18 @@ def squash_activity_selected(values: Tensor, experts: Tensor, n_blocks: int, gam
     return lower.reshape(*lead, -1), act
 
 
-def vocab_kl_rows(lc: Tensor, lm: Tensor, want_grad: bool) -> tuple[Tensor, Tensor | None]:
+def vocab_kl_rows(lc: Tensor, lm: Tensor, want_grad: bool, grad_out: Tensor | None = None) -> tuple[Tensor, Tensor | None]:
     """Per-row `KL(softmax(lc) || softmax(lm))` and (optionally) `softmax(lm) - softmax(lc)`.
-    `lc`, `lm`: `[rows, V]` bf16 views whose row pitch is a multiple of 8 elements."""
+    `lc`, `lm`: `[rows, V]` bf16 views whose row pitch is a multiple of 8 elements. `grad_out`: a buffer with
+    the same pitch to write the gradient into (re-used across chunks by the streamed form)."""
     rows, V = lc.shape
     assert lc.stride(1) == 1 and lm.stride(1) == 1 and lc.stride(0) == lm.stride(0) and lc.stride(0) % 8 == 0
     kl = torch.empty(rows, device=lc.device, dtype=torch.float32)
     dlm = None
-    if want_grad:
+    if want_grad and grad_out is not None:
+        assert grad_out.stride(0) == lc.stride(0) and grad_out.shape[0] >= rows and grad_out.dtype == torch.bfloat16
+        dlm = grad_out[:rows, :V]
+    elif want_grad:
         dlm = torch.empty(rows, lc.stride(0), device=lc.device, dtype=torch.bfloat16)[:, :V]
     lib = _lib()
     lib.pd_vocab_kl.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong,

@@ -66,6 +66,7 @@ class _StreamedKLFromHidden(torch.autograd.Function):
         lc_buf = torch.empty(rows, vp, device=hm.device, dtype=torch.bfloat16)
         lm_buf = torch.empty(rows, vp, device=hm.device, dtype=torch.bfloat16)
         want_grad = hm.requires_grad
+        dl_buf = torch.empty(rows, vp, device=hm.device, dtype=torch.bfloat16) if want_grad else None
         dh = torch.empty(n, d, device=hm.device, dtype=torch.bfloat16) if want_grad else None
         total = torch.zeros((), device=hm.device, dtype=torch.float32)
         hc, hm = hc.contiguous(), hm.contiguous()
@@ -74,7 +75,7 @@ class _StreamedKLFromHidden(torch.autograd.Function):
             lc, lm = lc_buf[:r, :V], lm_buf[:r, :V]
             nv.gemm(hc[s:s + r], head, lc)
             nv.gemm(hm[s:s + r], head, lm)
-            kl, dlm = vocab_kl_rows(lc, lm, want_grad=want_grad)
+            kl, dlm = vocab_kl_rows(lc, lm, want_grad=want_grad, grad_out=dl_buf)
             total = total + kl.sum()
             if want_grad:
                 nv.gemm(dlm, head, dh[s:s + r], b_mn=True, alpha=1.0 / n)

@@ -110,7 +110,7 @@ def test_streamed_vocab_kl_matches_materialised_and_bounds_memory():
     from param_decomp_b200.ops import native, vocab_kl
 
     torch.manual_seed(0)
-    n, d, V, rows = 4096, 256, 50272, 512
+    n, d, V, rows = 16384, 256, 50272, 512
     head = (torch.randn(V, d, device="cuda") / d**0.5).to(torch.bfloat16)
     hc = torch.randn(n, d, device="cuda", dtype=torch.bfloat16)
     hm = (hc.float() + 0.3 * torch.randn(n, d, device="cuda")).to(torch.bfloat16)
@@ -130,7 +130,7 @@ def test_streamed_vocab_kl_matches_materialised_and_bounds_memory():
     peak = torch.cuda.max_memory_allocated() - base
     one_full = n * V * 2
     assert peak < 3.5 * rows * V * 2 + 16 * n * d, (peak, rows * V * 2)
-    assert peak < 0.5 * one_full  # far below even ONE materialised logits tensor
+    assert peak < 0.15 * one_full  # far below even ONE materialised logits tensor
     la2 = vocab_kl.kl_from_hidden(vocab_kl.padded_logits(hc, head), hm, head)
     assert float(lb) == pytest.approx(float(la2), rel=2e-3)
     assert rel(b.grad, a.grad) < 2e-3
