@@ -95,8 +95,9 @@ def main() -> None:
     ap.add_argument("--impl", type=str, default="ours")
     ap.add_argument("--config", type=Path, default=CONFIG)
     ap.add_argument("--batch", type=int, default=None, help="override the global batch (debugging only)")
-    ap.add_argument("--optim", type=str, default="fused_p2p", choices=["fused_p2p", "collective", "ddp"],
-                    help="N>1: fused reduce-scatter+AdamW+all-gather kernel, NCCL RS/AG, or all-reduce + replicated AdamW")
+    ap.add_argument("--optim", type=str, default=None, choices=["fused_p2p", "collective", "ddp"],
+                    help="N>1: override what the config's placement (`runtime.sharding`) selects - fused reduce-scatter + "
+                         "AdamW + all-gather kernel, NCCL reduce-scatter / all-gather, or all-reduce + replicated AdamW")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--tp", type=int, default=1,
@@ -137,8 +138,14 @@ def main() -> None:
     pd = cfg.pd if args.batch is None else cfg.pd.model_copy(update={"batch_size": args.batch})
     cfg = cfg.model_copy(update={"pd": pd})
     assert world % args.tp == 0, f"--tp {args.tp} does not divide {world} GPUs"
-    topo = topology.initialize(HsdpMeshShape(replicate=1, fsdp=world // args.tp, tp=args.tp), "cuda",
-                               batch_over_tp=args.expert_dispatch == "all_to_all")
+    mesh = HsdpMeshShape(replicate=1, fsdp=world // args.tp, tp=args.tp)  # the config's mesh, sized to this job
+    cfg = cfg.model_copy(update={"runtime": cfg.runtime.model_copy(update={"mesh": mesh})})
+    topo = topology.initialize(mesh, "cuda", batch_over_tp=args.expert_dispatch == "all_to_all")
+    from param_decomp_b200.parallel import layout as layout_mod
+
+    lay = layout_mod.resolve(cfg.runtime, world=world)  # what `runtime.sharding` asks for on this mesh
+    if args.optim is None:
+        args.optim = "fused_p2p" if lay.optimizer_sharded else "ddp"
     run = build_lm_run(cfg, None, topo.device, topo.data_rank, topo.data_world,
                        expert_group=topo.groups.get("tp") if args.tp > 1 else None, expert_mode=args.expert_dispatch)
     objective = build_objective(cfg.pd)
@@ -255,8 +262,10 @@ def main() -> None:
                           + (f" experts{arch.n_experts} top{arch.experts_per_token}" if arch.family == "moe" else "")),
                 "config_file": str(args.config.relative_to(ROOT)) if args.config.is_relative_to(ROOT) else str(args.config),
                 "global_batch": cfg.pd.batch_size, "seq_len": cfg.data.seq_len,
-                "parallelism": ((f"dp{topo.data_world}" + (f" x tp{args.tp}" + (f" {args.expert_dispatch}" if run.ep is not None else "") if args.tp > 1 else "")
-                                 + f" ({'zero1 ' + args.optim if shard_backend else 'ddp all-reduce'})")
+                "parallelism": ((f"fsdp{topo.data_world}" + (f" x tp{args.tp}" + (f" {args.expert_dispatch}" if run.ep is not None else "") if args.tp > 1 else "")
+                                 + (f" (placement {lay.rules.name}: masters, moments and gradient reduction sharded over "
+                                    f"the batch axes, {args.optim}; bf16 compute copy re-gathered once per step)"
+                                    if shard_backend else " (replicated optimizer, gradient all-reduce)"))
                                 if world > 1 else "single"),
                 "decomposition": (", ".join(f"{k}:{v}" for k, v in cfg.decomposition.sites.cs.items())
                                   + f" components per matrix x {arch.n_layer} layers; CI fn {cfg.decomposition.ci.type}"),

@@ -149,6 +149,7 @@ class PerformanceTracker:
     units_per_step: int  # tokens (LM) or samples (toys) in the global batch
     flops_per_step: float = 0.0
     peak_flops: float = 0.0
+    optimizer_flops_per_step: float = 0.0  # contraction FLOPs of the optimizers (Newton-Schulz), counted apart
     t_start: float = field(default_factory=time.perf_counter)
     t_last: float = field(default_factory=time.perf_counter)
     step_last: int = 0
@@ -166,8 +167,12 @@ class PerformanceTracker:
             "perf/eta_s": dt * max(self.total_steps - step, 0),
             "perf/tokens_per_s": self.units_per_step / dt if dt > 0 else 0.0,
         }
+        if self.flops_per_step:
+            out["perf/useful_model_flops"] = self.flops_per_step
+            out["perf/useful_optimizer_flops"] = self.optimizer_flops_per_step
         if self.flops_per_step and self.peak_flops:
             out["perf/mfu"] = self.flops_per_step / dt / self.peak_flops
+            out["perf/mfu_with_optimizer"] = (self.flops_per_step + self.optimizer_flops_per_step) / dt / self.peak_flops
         if torch.cuda.is_available():
             out["perf/cuda_mem_allocated_gb"] = torch.cuda.memory_allocated() / 2**30
             out["perf/cuda_mem_peak_gb"] = torch.cuda.max_memory_allocated() / 2**30

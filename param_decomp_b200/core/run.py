@@ -92,6 +92,13 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
     """Seeded init: `init` / `source` / `run` streams are separated like the reference's
     `split(PRNGKey(seed), 3)`."""
     g = torch.Generator().manual_seed(pd.seed)
+    from param_decomp_b200.config.run import MuonOptimizerConfig
+
+    muon_sharded = shard_backend is not None and isinstance(pd.components_optimizer, MuonOptimizerConfig)
+    if muon_sharded:  # Newton-Schulz work and momentum split along the stack axis: stacks must tile the group
+        import torch.distributed as dist
+
+        stack_multiple = max(stack_multiple, dist.get_world_size(shard_group) if shard_group is not None else 1)
     components = ComponentStacks(model.sites, stack_multiple)
     if expert_shard is not None:
         assert shard_backend is None or expert_shard.by_component, \
@@ -105,11 +112,14 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
     ci_fn.to(device)
     comp_named = [(n, p) for n, p in components.named_parameters()]
     ci_named = [(n, p) for n, p in ci_fn.named_parameters()]
-    if shard_backend is not None:
-        from param_decomp_b200.config.run import AdamWOptimizerConfig
+    if muon_sharded:
+        from param_decomp_b200.parallel.sharded_muon import StackShardedMuon
+
+        comp_opt = StackShardedMuon(pd.components_optimizer, [n for n, _ in comp_named], [p for _, p in comp_named],
+                                    pd.steps, shard_group)
+    elif shard_backend is not None:
         from param_decomp_b200.parallel.sharded_optim import ShardedFlatAdamW
 
-        assert isinstance(pd.components_optimizer, AdamWOptimizerConfig), "the sharded optimizer implements AdamW"
         comp_opt = ShardedFlatAdamW(pd.components_optimizer, ["/".join(n.split(".")) for n, _ in comp_named],
                                     [p for _, p in comp_named], pd.steps, shard_group, backend=shard_backend,
                                     keep_lo=True, norm_group=expert_shard.group if expert_shard is not None else None,
@@ -209,6 +219,7 @@ def run_decomposition_training(
     shard_backend: str | None = None,
     peer_wait_limit_s: float = 30.0,
     record_step: bool = False,
+    stack_multiple: int = 1,
     remat_recon_forwards: bool = False,
     remat_ci_fn: bool = False,
 ) -> RunResult:
@@ -224,7 +235,7 @@ def run_decomposition_training(
                             expert_shard=expert_shard, remat_recon_forwards=remat_recon_forwards,
                             remat_ci_fn=remat_ci_fn)
     rows = batch_rows if batch_rows is not None else pd.batch_size // collectives.world_size
-    state = init_train_state(model, ci_fn, pd, objective, device, rows, positions,
+    state = init_train_state(model, ci_fn, pd, objective, device, rows, positions, stack_multiple=stack_multiple,
                              use_fused_optim=use_fused_optim, init_components=init_components,
                              shard_group=shard_group, shard_backend=shard_backend, expert_shard=expert_shard,
                              data_rank=getattr(collectives, "data_rank", 0), peer_wait_limit_s=peer_wait_limit_s)
@@ -244,7 +255,12 @@ def run_decomposition_training(
     own_sink = sink is None and run_dir is not None
     if own_sink:
         sink = MetricsSink.for_run(run_dir, collectives.rank)  # type: ignore[arg-type]
-    perf = PerformanceTracker(pd.steps, units_per_step or pd.batch_size, flops_per_step, peak_flops)
+    from param_decomp_b200.utils.flops import optimizer_flops
+
+    opt_flops = (optimizer_flops("components", pd.components_optimizer, list(state.components.parameters()))[0]
+                 + optimizer_flops("ci_fn", pd.ci_fn_optimizer, list(ci_fn.parameters()))[0])
+    perf = PerformanceTracker(pd.steps, units_per_step or pd.batch_size, flops_per_step, peak_flops,
+                              optimizer_flops_per_step=opt_flops / max(1, collectives.world_size))
     perf.step_last = state.step
     preempt = PreemptionFlag(collectives)
     preempt.install()

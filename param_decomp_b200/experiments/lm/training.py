@@ -17,14 +17,15 @@ from param_decomp_b200.experiments.lm.build import build_lm_run
 
 
 def optimizer_sharding(cfg: LMExperimentConfig | LMTargetedExperimentConfig, topo) -> tuple[object, str | None]:
-    """Which optimizer layout a placement asks for on this topology: `ddp` keeps replicated masters
-    and all-reduces gradients; every sharded preset (`owner`, `zero1`, the resident family) runs the
-    ZeRO-style flat-sharded AdamW - the fused reduce-scatter + AdamW + all-gather kernel over NVLink
-    peer memory on GPUs, the collective (gloo / NCCL) form elsewhere."""
+    """The optimizer layout the run's placement table asks for on this topology (`parallel/layout.py`): tables whose
+    component optimizer state is sharded over the batch axes (every preset but `ddp`) run the flat-sharded optimizer
+    - the fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory on GPUs, the collective (gloo /
+    NCCL) form elsewhere; `ddp` keeps replicated masters and all-reduces gradients."""
+    from param_decomp_b200.parallel import layout
+
     if topo.data_world <= 1:
         return None, None
-    name = cfg.runtime.sharding if isinstance(cfg.runtime.sharding, str) else "owner"
-    if name == "ddp":
+    if not layout.resolve(cfg.runtime, world=topo.world).optimizer_sharded:
         return None, None
     backend = "fused_p2p" if topo.device.type == "cuda" and getattr(cfg.runtime, "backend", "") == "fused_sm100" else "collective"
     return topo.data_group, backend
@@ -79,6 +80,10 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
                        expert_mode=mode)
     collectives = topo.collectives()
+    from param_decomp_b200.parallel import layout as layout_mod
+
+    lay = layout_mod.resolve(cfg.runtime, sites=getattr(run.model, "global_sites", run.model.sites), world=topo.world)
+    log.info("placement: %s; stacks padded to multiples of %d", lay.label, lay.stack_multiple)
     shard_group, shard_backend = optimizer_sharding(cfg, topo)
     if run.ep is not None:
         shard_group, shard_backend = None, None  # expert blocks differ per tp rank: replicated-optimizer layout
@@ -107,7 +112,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             batch_rows=cfg.pd.batch_size // topo.data_world, positions=cfg.data.seq_len,
             units_per_step=run.tokens_per_step, flops_per_step=flops / topo.world, peak_flops=device_peak_flops(),
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
-            max_steps_this_entry=max_steps_this_entry, state_out=state_out,
+            max_steps_this_entry=max_steps_this_entry, state_out=state_out, stack_multiple=lay.stack_multiple,
             profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
             shard_group=shard_group, shard_backend=shard_backend, peer_wait_limit_s=cfg.runtime.peer_wait_limit_s,
             record_step=fused and cfg.runtime.step_recording == "cuda_graph",

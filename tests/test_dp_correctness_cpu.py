@@ -92,6 +92,8 @@ def _worker(rank: int, world: int, port: int, root: str, kind: str, out):
 
     if kind == "warmup":
         cfg = _cfg(world, BASE, "owner", warmup=2)
+    elif kind == "muon":
+        cfg = _muon_cfg(world)
     else:
         cfg = _cfg(world, _pgd_losses(kind), "ddp", save=True)
     states: list = []
@@ -99,6 +101,12 @@ def _worker(rank: int, world: int, port: int, root: str, kind: str, out):
     st = states[0]
     if kind == "warmup":
         assert hasattr(st.components_opt, "gather_state"), "the config must select the sharded optimizer"
+    if kind == "muon":
+        from param_decomp_b200.parallel.sharded_muon import StackShardedMuon
+
+        assert isinstance(st.components_opt, StackShardedMuon)
+        mom = st.components_opt.state["V.q/mom"]
+        assert mom.shape[0] * world == st.components.V["q"].shape[0]  # momentum of this rank's matrices only
     # the process group is gone after train_lm: the sharded masters were gathered by its final save / log step
     adv = {t: {k: v.detach().clone() for k, v in a._local_state().items()} for t, a in st.adversaries.items()}
     out[rank] = (dict(res.last_metrics), [p.detach().clone() for p in st.components.parameters()], adv)
@@ -181,3 +189,31 @@ def test_lp_minimality_uses_global_mean():
     glob = (means[0] + means[1]) / 2
     got = losses.lp_importance_minimality(halves[0], 0.9, 1e-6, 0.5, world_size=2, mean_over_ranks=lambda m: glob)
     assert float(got) == pytest.approx(float(whole), rel=1e-6)
+
+
+def _muon_cfg(world: int) -> LMExperimentConfig:
+    c = _cfg(world, BASE, "owner", save=True).model_dump(mode="json")
+    c["pd"]["components_optimizer"] = {"type": "muon", "lr_schedule": 1e-2, "ns_dtype": "float32", "grad_clip_norm": 1.0}
+    c["eval"] = None
+    return LMExperimentConfig.model_validate(c)
+
+
+def test_muon_with_newton_schulz_split_over_ranks_matches_replicated_muon():
+    """`sharding: owner` + Muon: each rank orthogonalises and keeps momentum for its slice of every stack; the run
+    follows the single-process Muon run, and the checkpoint holds whole momenta."""
+    from param_decomp_b200.core import checkpoint as ckpt
+
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        mp.spawn(_worker, args=(2, _free_port(), root, "muon", out), nprocs=2, join=True)
+        res, st = _train(_muon_cfg(1), root, "p-0000dddd")
+        ref_metrics, ref_params, _ = _snapshot(res, st)
+        for r in range(2):
+            metrics, params, _ = out[r]
+            assert metrics["train/loss/total"] == pytest.approx(ref_metrics["train/loss/total"], rel=2e-4)
+            for a, b in zip(params, ref_params):
+                assert torch.allclose(a, b, atol=5e-5), float((a - b).abs().max())
+        tensors, _ = ckpt._read(Path(root) / "runs" / "p-0000aaaa" / "ckpts" / str(STEPS) / ckpt.TRAINING_FILE)
+        single, _ = ckpt._read(Path(root) / "runs" / "p-0000dddd" / "ckpts" / str(STEPS) / ckpt.TRAINING_FILE)
+        key = "opt/components/V.q/mom"
+        assert tensors[key].shape == single[key].shape and torch.allclose(tensors[key], single[key], atol=5e-5)
