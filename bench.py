@@ -108,6 +108,9 @@ def main() -> None:
                          "outputs summed, or the batch sharded over it too and jobs stored into their expert's owner")
     ap.add_argument("--no-record", action="store_true",
                     help="issue every step launch by launch from Python instead of replaying the recorded CUDA graph")
+    ap.add_argument("--backend", type=str, default="fused_sm100", choices=["fused_sm100", "eager_torch"],
+                    help="eager_torch: the same step on plain PyTorch ops (cuBLAS GEMMs, torch fused attention, torch "
+                         "optimizer arithmetic) - a context number for the hand-written path, never the headline")
     ap.add_argument("--trace", action="store_true",
                     help="print a time-stamped line per warm-up step / recording / replay on every rank (diagnostics)")
     ap.add_argument("--no-lanes", action="store_true",
@@ -139,13 +142,14 @@ def main() -> None:
     cfg = cfg.model_copy(update={"pd": pd})
     assert world % args.tp == 0, f"--tp {args.tp} does not divide {world} GPUs"
     mesh = HsdpMeshShape(replicate=1, fsdp=world // args.tp, tp=args.tp)  # the config's mesh, sized to this job
-    cfg = cfg.model_copy(update={"runtime": cfg.runtime.model_copy(update={"mesh": mesh})})
+    cfg = cfg.model_copy(update={"runtime": cfg.runtime.model_copy(update={"mesh": mesh, "backend": args.backend})})
+    fused = args.backend == "fused_sm100"
     topo = topology.initialize(mesh, "cuda", batch_over_tp=args.expert_dispatch == "all_to_all")
     from param_decomp_b200.parallel import layout as layout_mod
 
     lay = layout_mod.resolve(cfg.runtime, world=world)  # what `runtime.sharding` asks for on this mesh
     if args.optim is None:
-        args.optim = "fused_p2p" if lay.optimizer_sharded else "ddp"
+        args.optim = ("fused_p2p" if fused else "collective") if lay.optimizer_sharded else "ddp"
     run = build_lm_run(cfg, None, topo.device, topo.data_rank, topo.data_world,
                        expert_group=topo.groups.get("tp") if args.tp > 1 else None, expert_mode=args.expert_dispatch)
     objective = build_objective(cfg.pd)
@@ -154,14 +158,14 @@ def main() -> None:
         from param_decomp_b200.parallel.expert_shard import StackSharding
 
         expert_shard = StackSharding.for_model(run.model)
-    ctx = StepContext.build(run.model, objective, cfg.pd, collectives=topo.collectives(), lazy_masks=True,
+    ctx = StepContext.build(run.model, objective, cfg.pd, collectives=topo.collectives(), lazy_masks=fused,
                             expert_shard=expert_shard)
     rows = cfg.pd.batch_size // topo.data_world
     shard_backend = args.optim if (topo.data_world > 1 and args.optim != "ddp" and args.tp == 1) else None
     if args.tp > 1 and topo.data_world > 1 and args.optim != "ddp" and run.ep is None:
         shard_backend = "collective"  # component slices: sharded AdamW over the batch axes, clip norm summed over tp
     state = init_train_state(run.model, run.ci_fn, cfg.pd, objective, topo.device, rows, cfg.data.seq_len,
-                             use_fused_optim=True, shard_group=topo.data_group, shard_backend=shard_backend,
+                             use_fused_optim=fused, shard_group=topo.data_group, shard_backend=shard_backend,
                              expert_shard=expert_shard, peer_wait_limit_s=5.0)
     tokens_per_step = cfg.pd.batch_size * cfg.data.seq_len
 
@@ -175,7 +179,7 @@ def main() -> None:
     # step is recorded, the recording call and one replay - all untimed.
     from param_decomp_b200.core.recorded_step import RecordedTrainStep
 
-    step_fn = RecordedTrainStep(ctx, state, enabled=not args.no_record, eager_steps=args.warmup,
+    step_fn = RecordedTrainStep(ctx, state, enabled=fused and not args.no_record, eager_steps=args.warmup,
                                 concurrent=not args.no_lanes)
     t_start = time.perf_counter()
 
@@ -255,7 +259,8 @@ def main() -> None:
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "impl": "ours",
+            "vs_baseline": None, "dtype": "bf16",
+            "impl": "ours" if fused else "ours, eager_torch backend (cuBLAS / torch SDPA): context only",
             "data": "synthetic Zipf(1.1) token ids, seeded random-init target weights",
             "config": {
                 "model": (f"{arch.family} {arch.n_layer}L d{arch.d_model} h{arch.n_head} ff{arch.d_ff} vocab{arch.vocab_size}"

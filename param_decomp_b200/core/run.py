@@ -128,11 +128,24 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
         comp_opt = build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim)
     if expert_shard is not None and shard_backend is None:
         comp_opt.norm_fn = expert_shard.grad_norm
+    from param_decomp_b200.config.run import AdamWOptimizerConfig as _AdamW
+
+    if (shard_backend is not None and expert_shard is None and isinstance(pd.ci_fn_optimizer, _AdamW)
+            and not muon_sharded and ci_named):
+        # the CI function's gradients take the same path as the components': reduce-scatter + AdamW + all-gather in
+        # one kernel over its own flat buffers - no separate gradient all-reduce in the step
+        from param_decomp_b200.parallel.sharded_optim import ShardedFlatAdamW
+
+        ci_opt = ShardedFlatAdamW(pd.ci_fn_optimizer, [n for n, _ in ci_named], [p for _, p in ci_named], pd.steps,
+                                  shard_group, backend=shard_backend, keep_lo=True, wait_limit_s=peer_wait_limit_s,
+                                  label="ci_fn")
+    else:
+        ci_opt = build_group_optimizer(pd.ci_fn_optimizer, ci_named, pd.steps, 2, use_fused_optim)
     state = TrainState(
         components=components,
         ci_fn=ci_fn,
         components_opt=comp_opt,
-        ci_fn_opt=build_group_optimizer(pd.ci_fn_optimizer, ci_named, pd.steps, 2, use_fused_optim),
+        ci_fn_opt=ci_opt,
     )
     state.expert_shard = expert_shard  # type: ignore[attr-defined]
     src_key = StepKey(pd.seed ^ 0x5EED, 0)
@@ -294,11 +307,11 @@ def run_decomposition_training(
     def sync_masters(for_save: bool) -> None:
         """A sharded optimizer keeps each rank's slice of the masters: before anything reads the parameters
         (evaluation, checkpoint) gather them - and, for a save, the moments - on every rank."""
-        opt = state.components_opt
-        if for_save and hasattr(opt, "gather_state"):
-            opt.gather_state()
-        elif hasattr(opt, "refresh_full_fp32"):
-            opt.refresh_full_fp32()
+        for opt in (state.components_opt, state.ci_fn_opt):
+            if for_save and hasattr(opt, "gather_state"):
+                opt.gather_state()
+            elif hasattr(opt, "refresh_full_fp32"):
+                opt.refresh_full_fp32()
 
     def save() -> None:
         check_device_status("before a checkpoint")

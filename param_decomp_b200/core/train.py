@@ -451,9 +451,13 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         clean = ctx.model.clean_forward(batch, capture=obj.capture_keys())
     direct = getattr(ctx.model, "backend", "eager_torch") == "fused_sm100"
     sharded = hasattr(state.components_opt, "working_view")  # ZeRO-style optimizer owns grads + working copy
+    ci_sharded = hasattr(state.ci_fn_opt, "working_view")  # the CI function's gradients ride the same fused path
     if sharded:
         state.components_opt.zero_grad()
-    for p in ([] if sharded else state.components_opt.params) + state.ci_fn_opt.params:
+    if ci_sharded:
+        state.ci_fn_opt.zero_grad()
+        state.ci_fn_opt.refresh_compute_fp32()  # this step's values into the modules' own fp32 storage (local)
+    for p in ([] if sharded else state.components_opt.params) + ([] if ci_sharded else state.ci_fn_opt.params):
         if direct and p.grad is not None:
             p.grad.zero_()
         else:
@@ -611,7 +615,8 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
         ctx.collectives.reduce_split_grads(split)
         ctx.collectives.reduce_grads_everywhere(whole + state.ci_fn_opt.params)
     else:
-        ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params) + state.ci_fn_opt.params)
+        ctx.collectives.reduce_grads(([] if sharded else state.components_opt.params)
+                                     + ([] if ci_sharded else state.ci_fn_opt.params))
 
     with phase("optimizer"):
         info_c = state.components_opt.step(step)

@@ -133,7 +133,8 @@ class TransformerDecomposedModel:
         self.arch = arch
         self.w = weights
         self.backend = backend
-        self.attention_impl = attention
+        # the eager backend means library ops end to end: torch's fused attention instead of the hand-written kernel
+        self.attention_impl = "sdpa" if (backend == "eager_torch" and attention == "flash") else attention
         self.n_vocab_chunks = n_vocab_chunks
         self.kl_token_chunk = kl_token_chunk
         self.compute_dtype = weights["embed.weight"].dtype

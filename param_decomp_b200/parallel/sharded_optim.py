@@ -265,6 +265,15 @@ class ShardedFlatAdamW:
         self.applied_learning_rate = self.lr_at(self._step_idx)
         self._full_stale = True
 
+    def refresh_compute_fp32(self) -> None:
+        """Local, no communication: rebuild every parameter's fp32 storage from the published split-precision
+        working copy (`bf16(p) + bf16(p - bf16(p))`, about 16 mantissa bits) so that modules which read their
+        parameters directly see this step's values. The exact fp32 masters stay with their owners
+        (`refresh_full_fp32` gathers those for checkpoints and evaluation)."""
+        assert self.work_lo_flat is not None, "needs the split-precision working copy (keep_lo=True)"
+        self.full_fp32.copy_(self.work_flat)
+        self.full_fp32.add_(self.work_lo_flat)
+
     def refresh_full_fp32(self) -> None:
         """All-gather the fp32 masters into the parameters' own storage (checkpoint / eval time)."""
         if self.world > 1:
