@@ -20,9 +20,20 @@ from param_decomp_b200.experiments.toy_common import ToyEvaluation, build_toy_ci
 from param_decomp_b200.models.tms import TMSDecomposedModel, pretrain_tms, sample_sparse_features
 
 
+def _rows_of_rank(topo, batch: torch.Tensor) -> torch.Tensor:
+    n = batch.shape[0] // topo.data_world
+    return batch[topo.data_rank * n:(topo.data_rank + 1) * n]
+
+
 def run_tms(cfg: TMSExperimentConfig, data_root: Path | None, run_id: str | None = None,
             device: str = "cpu", max_steps_this_entry: int | None = None, state_out: list | None = None) -> RunResult:
-    log = get_logger()
+    from param_decomp_b200.parallel import topology
+
+    # several processes (torchrun): data parallel, `ddp` placement - replicated state, gradients all-reduced,
+    # every rank takes its rows of the one seeded global batch (param_decomp/experiments/tms/run.py:241)
+    topo = topology.initialize(None, device)
+    device = str(topo.device)
+    log = get_logger(topo.rank)
     params = pretrain_tms(cfg.target, cfg.data.feature_probability, cfg.data.data_generation_type, device)
     site_cs = {s.name: s.C for s in cfg.decomposition.sites.sites}
     model = TMSDecomposedModel(params, site_cs).to(device)
@@ -30,31 +41,34 @@ def run_tms(cfg: TMSExperimentConfig, data_root: Path | None, run_id: str | None
 
     run_dir, sink = None, None
     if data_root is not None:
-        run_id = run_id or mint_run_id()
+        run_id = topo.broadcast_object(run_id or mint_run_id())
         run_dir = run_dir_for(data_root, run_id)
-        pin_launch_config(run_dir, cfg.to_yaml())
-        sink = MetricsSink.for_run(run_dir, 0, cfg.wandb, cfg.run_name, cfg.model_dump(mode="json"))
+        if topo.rank == 0:
+            pin_launch_config(run_dir, cfg.to_yaml())
+        sink = MetricsSink.for_run(run_dir, topo.rank, cfg.wandb, cfg.run_name, cfg.model_dump(mode="json"))
         log.info("run dir %s", run_dir)
 
     def sample_batch(step: int) -> torch.Tensor:
         g = torch.Generator().manual_seed((cfg.pd.seed * 1_000_003 + 17) * 1_000_003 + step)
-        return sample_sparse_features(cfg.pd.batch_size, cfg.target.n_features, cfg.data.feature_probability,
-                                      cfg.data.data_generation_type, g, device)
+        return _rows_of_rank(topo, sample_sparse_features(cfg.pd.batch_size, cfg.target.n_features, cfg.data.feature_probability,
+                                      cfg.data.data_generation_type, g, device))
 
     def sample_eval(i: int) -> torch.Tensor:
         g = torch.Generator().manual_seed(cfg.pd.seed * 7919 + 104729 + i)
         n = cfg.eval.batch_size if cfg.eval is not None else cfg.pd.batch_size
-        return sample_sparse_features(n, cfg.target.n_features, cfg.data.feature_probability,
-                                      cfg.data.data_generation_type, g, device)
+        return _rows_of_rank(topo, sample_sparse_features(n, cfg.target.n_features, cfg.data.feature_probability,
+                                      cfg.data.data_generation_type, g, device))
 
     evaluation = ToyEvaluation(cfg.eval, sample_eval, cfg.target.n_features, ("linear1",), run_dir=run_dir)
     try:
         return run_decomposition_training(model, ci_fn, cfg.pd, cfg.cadence, sample_batch, device=device,
                                           run_dir=run_dir, sink=sink, evaluation=evaluation,
+                                          collectives=topo.collectives(),
                                           max_steps_this_entry=max_steps_this_entry, state_out=state_out)
     finally:
         if sink is not None:
             sink.close()
+        topo.shutdown()
 
 
 def main() -> None:

@@ -217,3 +217,44 @@ def test_muon_with_newton_schulz_split_over_ranks_matches_replicated_muon():
         single, _ = ckpt._read(Path(root) / "runs" / "p-0000dddd" / "ckpts" / str(STEPS) / ckpt.TRAINING_FILE)
         key = "opt/components/V.q/mom"
         assert tensors[key].shape == single[key].shape and torch.allclose(tensors[key], single[key], atol=5e-5)
+
+
+def _tms_cfg():
+    import yaml
+
+    from param_decomp_b200.config.experiments import TMSExperimentConfig
+
+    root = Path(ge.__file__).resolve().parent
+    raw = yaml.safe_load((root / "param_decomp_b200/experiments/configs/tms_5-2.yaml").read_text())
+    raw["pd"].update({"steps": 5, "batch_size": 64, "faithfulness_warmup_steps": 0})
+    raw["target"]["pretrain"]["steps"] = 10
+    raw["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "none"}}
+    raw["eval"] = None
+    return TMSExperimentConfig.model_validate(raw)
+
+
+def _tms_worker(rank: int, world: int, port: int, root: str, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from param_decomp_b200.experiments.tms.run import run_tms
+
+    states: list = []
+    res = run_tms(_tms_cfg(), Path(root), run_id="p-0000a7a5", state_out=states)
+    out[rank] = (dict(res.last_metrics), [p.detach().clone() for p in states[0].components.parameters()])
+
+
+def test_toy_root_runs_data_parallel_and_matches_single_process():
+    """The TMS root under a 2-process launch (the form the 2-GPU toy benchmark uses): every rank takes its rows of
+    the seeded global batch, gradients are averaged, and the run follows the single-process run."""
+    from param_decomp_b200.experiments.tms.run import run_tms
+
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        mp.spawn(_tms_worker, args=(2, _free_port(), root, out), nprocs=2, join=True)
+        states: list = []
+        res = run_tms(_tms_cfg(), Path(root), run_id="p-0000a7a6", state_out=states)
+        for r in range(2):
+            metrics, params = out[r]
+            assert metrics["train/loss/total"] == pytest.approx(res.last_metrics["train/loss/total"], rel=1e-4)
+            for a, b in zip(params, states[0].components.parameters()):
+                assert torch.allclose(a, b.detach(), atol=2e-5), float((a - b).abs().max())
