@@ -28,7 +28,7 @@ from param_decomp_b200.ops.site_linear import _split_k_for
 CASES = ("mask_fwd", "site_out", "mask_bwd", "dx", "dV", "dU")
 
 
-def build(case: str, N: int, C: int, din: int, dout: int, cg: int = 0):
+def build(case: str, N: int, C: int, din: int, dout: int, cg: int = 0, epi_tma: int = 0):
     dev, bf = "cuda", torch.bfloat16
     g = torch.Generator(device=dev).manual_seed(0)
 
@@ -41,7 +41,7 @@ def build(case: str, N: int, C: int, din: int, dout: int, cg: int = 0):
     A, H, dy, dH = rn(N, C), rn(N, C), rn(N, dout), rn(N, C)
     if case == "mask_fwd":
         return (lambda: nv.gemm(x, V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci, delta=delta, seed=1,
-                                rng_stream=1, cta_group=cg)), 2.0 * N * C * din, (N * din + din * C + 3 * N * C) * 2
+                                rng_stream=1, cta_group=cg, epi_tma=epi_tma)), 2.0 * N * C * din, (N * din + din * C + 3 * N * C) * 2
     if case == "site_out":
         y = torch.empty(N, dout, device=dev, dtype=bf)
         return (lambda: nv.gemm(A, U, y, b_mn=True, a1=x, b1=W, cta_group=cg)), 2.0 * N * dout * (C + din), \
@@ -49,7 +49,7 @@ def build(case: str, N: int, C: int, din: int, dout: int, cg: int = 0):
     if case == "mask_bwd":
         dci = torch.empty(N, C, device=dev, dtype=bf)
         return (lambda: nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, delta=delta, dci=dci, seed=1,
-                                rng_stream=1, cta_group=cg)), 2.0 * N * C * dout, (N * dout + C * dout + 4 * N * C) * 2
+                                rng_stream=1, cta_group=cg, epi_tma=epi_tma)), 2.0 * N * C * dout, (N * dout + C * dout + 4 * N * C) * 2
     if case == "dx":
         dx = torch.empty(N, din, device=dev, dtype=bf)
         return (lambda: nv.gemm(dH, V, dx, a1=dy, b1=W, b1_mn=True, cta_group=cg)), 2.0 * N * din * (C + dout), \
@@ -92,6 +92,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--cta-group", type=int, default=0, help="1 = single-CTA tiles, 2 = CTA pairs, 0 = library default")
+    ap.add_argument("--epi-tma", type=int, default=0,
+                    help="mask epilogues: 0 = library default, 1 = plain loads / stores, 2 = TMA-fed operand boxes")
     ap.add_argument("--peak", type=float, default=1647.5, help="cuBLAS bf16 burst TFLOP/s to report fractions of")
     ap.add_argument("--hbm", type=float, default=6566.4, help="copy bandwidth GB/s to report fractions of")
     args = ap.parse_args()
@@ -101,9 +103,9 @@ def main() -> None:
         shapes = shapes[:1]
     for din, dout in shapes:
         for case in cases:
-            fn, flops, nbytes = build(case, args.rows, args.c, din, dout, args.cta_group)
+            fn, flops, nbytes = build(case, args.rows, args.c, din, dout, args.cta_group, args.epi_tma)
             ms = time_case(fn, args.iters, args.warmup)
-            print(json.dumps({"case": case, "cta_group": args.cta_group, "rows": args.rows, "C": args.c, "d_in": din, "d_out": dout,
+            print(json.dumps({"case": case, "cta_group": args.cta_group, "epi_tma": args.epi_tma, "rows": args.rows, "C": args.c, "d_in": din, "d_out": dout,
                               "us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
                               "frac_of_measured_gemm_peak": round(flops / ms / 1e9 / args.peak, 3),
                               "algorithmic_gb_per_s": round(nbytes / ms / 1e6, 1),

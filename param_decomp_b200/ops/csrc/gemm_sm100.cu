@@ -30,6 +30,14 @@
 //   EPI_FAITH     out0 = bf16(R - acc) with R read from memory, and *sumsq += sum (R - acc)^2:
 //                 the faithfulness residual W - (VU)^T and its squared norm without a second pass
 //
+// The mask epilogues come in two forms. NOUT = 1 / 2: each epilogue thread reads its row's ci / H values with
+// plain global loads (row-strided: 32 cache lines per warp request) and writes its mask gradient the same way;
+// this form serves row-mapped (routed) products. NOUT = 4, the TMA-fed form for dense sites: ci and H arrive as
+// 32-row x 64-column boxes by TMA into a two-slot ring of shared-memory boxes per epilogue warp (issued one
+// unit ahead), every thread reads its own 128-byte row of the swizzled box, writes its results IN PLACE
+// (ci box -> A or dH, H box -> mask gradient or the H output) and the boxes leave by TMA store. No global
+// load or store instruction is left in the epilogue: L1 wavefronts drop from 32 to 4 per 16-byte request.
+//
 // Every wait is bounded (see common.cuh); on time-out the kernel stores a code to *status and returns.
 #include "common.cuh"
 
@@ -117,11 +125,13 @@ struct SmemPlan {
   static constexpr int kStageBytesB = BN * BK * 2 / CG;  // a CTA pair splits the B tile
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
   static constexpr int kOutBytes = kNumEpiWarps * NOUT * kOutBoxBytes;
-  static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/;
+  static constexpr int kBarrierBytes = 512;  // pipeline + accumulator barriers, then two operand barriers per epilogue warp
+  static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes;
   static constexpr int kStagesRaw = (kBudget - kOutBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + 256 + 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarrierBytes + 1024;
   static_assert(16 * kStages + 40 + 8 * kGatherSlotsMax <= 256, "barrier area");
+  static_assert(kStages >= 2, "the operand pipeline needs at least two stages");
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -182,6 +192,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
             const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
             const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
+            const __grid_constant__ CUtensorMap tmCi, const __grid_constant__ CUtensorMap tmH,
+            const __grid_constant__ CUtensorMap tmDci,
             const __grid_constant__ PeerMaps peerOut, const GemmArgs args) {
   using Plan = SmemPlan<BN, NOUT, CG>;
   constexpr int kStages = Plan::kStages;
@@ -534,6 +546,209 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
   } else {
     // ------------------------------ epilogue ------------------------------
+    if constexpr (NOUT == 4) {
+      // TMA-fed mask epilogue (EPI_MASK_FWD / EPI_MASK_BWD on dense sites). Unit = one 64-column box of this
+      // warp's 32 rows; ring of two slots, slot = {box_a: ci in, A / dH out; box_b: H in (bwd), dci or H out}.
+      static_assert(EPI == EPI_MASK_FWD || EPI == EPI_MASK_BWD, "TMA-fed epilogue is for the mask epilogues");
+      const int ew = warp - 2, q = warp & 3, grp = ew >> 2;
+      const uint32_t ring = smem_out + ew * (4 * kOutBoxBytes);
+      const uint32_t bar_in = smem_bar + 256 + ew * 16;
+      constexpr bool kBwd = (EPI == EPI_MASK_BWD);
+      const bool want_h = kBwd && args.dci != nullptr;           // H comes in, the mask gradient goes out
+      const bool h_out = !kBwd && args.has_out1;                  // forward: H goes out through box_b
+      const uint32_t in_bytes = kOutBoxBytes * (want_h ? 2 : 1);
+      unsigned long long philox_seed = args.seed;
+      if (args.seed_dev != nullptr) philox_seed = *args.seed_dev;
+      if (lane == 0) {
+        mbar_init(bar_in, 1);
+        mbar_init(bar_in + 8, 1);
+        mbar_fence_init();
+      }
+      __syncwarp();
+      constexpr int nboxes = BN / 64;
+      auto tile_is_real = [&](long long t) {
+        if (!args.bgroup_of_mblock) return true;
+        int b2, mb2, nb2, sp2;
+        decode(t, b2, mb2, nb2, sp2);
+        return args.bgroup_of_mblock[mb2] >= 0;
+      };
+      auto next_real_tile = [&](long long t) {
+        while (t < num_tiles && !tile_is_real(t)) t += tstride;
+        return t;
+      };
+      // first unit of this warp at or after tile t (a warp may own no column of a narrow tail tile)
+      auto first_unit_from = [&](long long t) {
+        t = next_real_tile(t);
+        while (t < num_tiles) {
+          int b2, mb2, nb2, sp2;
+          decode(t, b2, mb2, nb2, sp2);
+          if (nb2 * BN + grp * 64 < args.N) break;
+          t = next_real_tile(t + tstride);
+        }
+        return t;
+      };
+      auto issue_load = [&](long long t, int j, int slot) {  // lane 0 only
+        int b2, mb2, nb2, sp2;
+        decode(t, b2, mb2, nb2, sp2);
+        const int crow = mb2 * BM + q * 32, col0 = nb2 * BN + j * 64;
+        const uint32_t bar = bar_in + 8 * slot, box_a = ring + slot * (2 * kOutBoxBytes);
+        mbar_expect_tx(bar, in_bytes);
+        tma_load_3d(box_a, &tmCi, bar, col0, crow, 0);
+        if (want_h) tma_load_3d(box_a + kOutBoxBytes, &tmH, bar, col0, crow, 0);
+      };
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      uint32_t unit = 0;  // units consumed so far by this warp: slot = unit & 1, parity = (unit >> 1) & 1
+      {
+        const long long t0u = first_unit_from(tile0);
+        if (lane == 0 && t0u < num_tiles) issue_load(t0u, grp, 0);
+      }
+      bool failed = false;
+      for (long long t = next_real_tile(tile0); t < num_tiles && !failed; t = next_real_tile(t + tstride)) {
+        int b, mb, nb, sp;
+        decode(t, b, mb, nb, sp);
+        int kb_lo_e, kb_hi_e;
+        tile_krange(b, sp, kb_lo_e, kb_hi_e);
+        const bool empty_k = kb_hi_e <= kb_lo_e;
+        const int row = mb * BM + q * 32 + lane;
+        const bool row_ok = row < args.M;
+        const uint32_t tmem_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+        float delta = 0.0f, rs = 1.0f;
+        if (row_ok) {
+          if (args.delta) delta = args.delta[row];
+          if (args.rowscale) rs = args.rowscale[row];
+        }
+        bool have_acc = false;
+#pragma unroll 1
+        for (int j = grp; j < nboxes && !failed; j += 2) {
+          const int col0 = nb * BN + j * 64;
+          if (col0 >= args.N) break;  // uniform across the warp
+          const int slot = unit & 1;
+          const uint32_t box_a = ring + slot * (2 * kOutBoxBytes), box_b = box_a + kOutBoxBytes;
+          if (!mbar_wait(bar_in + 8 * slot, (unit >> 1) & 1, abort_flag)) {
+            if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+            failed = true;
+            break;
+          }
+          if (!have_acc) {
+            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+              if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+              failed = true;
+              break;
+            }
+            tc_fence_after();
+            have_acc = true;
+          }
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            const int c0 = col0 + 32 * half;
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_row + j * 64 + 32 * half, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t off = lane * 128 + (((half * 4 + g) ^ (lane & 7)) << 4);
+              uint4 ciq, hq = make_uint4(0u, 0u, 0u, 0u);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(ciq.x), "=r"(ciq.y), "=r"(ciq.z), "=r"(ciq.w) : "r"(box_a + off) : "memory");
+              if (want_h)
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(hq.x), "=r"(hq.y), "=r"(hq.z), "=r"(hq.w) : "r"(box_b + off) : "memory");
+              float v[8], cf[8], coef[8], dmdci[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = empty_k ? 0.0f : __uint_as_float(r[8 * g + i]);
+              unpack8(ciq, cf);
+              if (args.mask_mode == 0) {
+                float u[8];
+                philox_uniform8(philox_seed, args.stream, static_cast<uint32_t>(row) + args.row_offset,
+                                static_cast<uint32_t>((c0 >> 3) + g) + (args.philox_col0 >> 3), u);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float om = 1.0f - u[i];
+                  coef[i] = rs * (fmaf(cf[i], om, u[i]) - delta);
+                  dmdci[i] = rs * om;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  coef[i] = rs * (cf[i] - delta);
+                  dmdci[i] = rs;
+                }
+              }
+              if constexpr (kBwd) {
+                if (want_h) {  // mask gradient replaces this thread's H values in box_b
+                  float hf[8];
+                  unpack8(hq, hf);
+                  uint4 pk;
+                  pk.x = pack_bf16(v[0] * hf[0] * dmdci[0], v[1] * hf[1] * dmdci[1]);
+                  pk.y = pack_bf16(v[2] * hf[2] * dmdci[2], v[3] * hf[3] * dmdci[3]);
+                  pk.z = pack_bf16(v[4] * hf[4] * dmdci[4], v[5] * hf[5] * dmdci[5]);
+                  pk.w = pack_bf16(v[6] * hf[6] * dmdci[6], v[7] * hf[7] * dmdci[7]);
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_b + off), "r"(pk.x), "r"(pk.y),
+                               "r"(pk.z), "r"(pk.w) : "memory");
+                }
+              } else {
+                if (h_out) {  // forward: the unmasked product leaves through box_b
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_b + off),
+                               "r"(pack_bf16(v[0], v[1])), "r"(pack_bf16(v[2], v[3])), "r"(pack_bf16(v[4], v[5])),
+                               "r"(pack_bf16(v[6], v[7])) : "memory");
+                }
+              }
+              // masked product replaces this thread's ci values in box_a
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_a + off),
+                           "r"(pack_bf16(v[0] * coef[0], v[1] * coef[1])), "r"(pack_bf16(v[2] * coef[2], v[3] * coef[3])),
+                           "r"(pack_bf16(v[4] * coef[4], v[5] * coef[5])), "r"(pack_bf16(v[6] * coef[6], v[7] * coef[7]))
+                           : "memory");
+            }
+            if (half == 0 && lane == 0) {
+              // The other slot's boxes were handed to TMA stores one unit ago: once those have been read,
+              // request the NEXT unit's operands into it (they land while this unit's second half is computed).
+              tma_store_wait_read<0>();
+              long long tn = t;
+              int jn = j + 2;
+              if (!(jn < nboxes && nb * BN + jn * 64 < args.N)) {
+                tn = first_unit_from(t + tstride);
+                jn = grp;
+              }
+              if (tn < num_tiles) issue_load(tn, jn, slot ^ 1);
+            }
+            __syncwarp();  // (the next tcgen05.ld is warp-aligned)
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int crow = mb * BM + q * 32;
+            if (crow < args.M) {
+              tma_store_3d(&tmOut0, box_a, col0, crow, b);
+              if (want_h) tma_store_3d(&tmDci, box_b, col0, crow, 0);
+              if (h_out) tma_store_3d(&tmOut1, box_b, col0, crow, b);
+            }
+            tma_store_commit();
+          }
+          ++unit;
+        }
+        if (failed) break;
+        if (!have_acc) {  // no column of this tile fell to this warp: still consume the phase
+          if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+            if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
+            break;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CG == 2 && !leader)
+            mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
+          else
+            mbar_arrive(bar_tempty + 8 * acc);
+        }
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+      if (lane == 0) tma_store_wait_all<0>();
+    } else {
     // Work unit = a 32-column half of an output box. Global operands of the mask epilogues
     // (ci / W rows, and H rows in the backward) are requested one unit ahead, across box and tile
     // boundaries, so their latency hides behind the math of the previous unit.
@@ -844,6 +1059,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       if (lane == 0 && args.dci != nullptr) atomicAdd(args.dci, faith_acc);
     }
     if (lane == 0) tma_store_wait_all<0>();
+    }  // NOUT != 4
   }
 
   // Unwind: every role has left its loop (all waits are bounded). A producer that gave up may
@@ -892,6 +1108,7 @@ static int encode_operand(CUtensorMap* tm, const OperandDesc& op, int mn_extent,
 template <int BN, int EPI, int NOUT, int CG>
 static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
                        const CUtensorMap& b1, const CUtensorMap& o0, const CUtensorMap& o1,
+                       const CUtensorMap& mci, const CUtensorMap& mh, const CUtensorMap& mdci,
                        const PeerMaps& peers, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
   using Plan = SmemPlan<BN, NOUT, CG>;
   auto kern = gemm_kernel<BN, EPI, NOUT, CG>;
@@ -935,10 +1152,10 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, o0, o1, peers, launch_args);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, o0, o1, mci, mh, mdci, peers, launch_args);
     return le == cudaSuccess ? 0 : 400 + static_cast<int>(le);
   }
-  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, peers, launch_args);
+  kern<<<grid, kNumThreads, Plan::kTotal, stream>>>(a0, b0, a1, b1, o0, o1, mci, mh, mdci, peers, launch_args);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
@@ -990,6 +1207,7 @@ struct PdGemmCall {
   unsigned int philox_col0;  // global index of mask column 0 in the Philox counter space (multiple of 8)
   const unsigned long long* seed_dev;  // when set, overrides `seed` with the value in device memory at run time
   const float* alpha_dev;              // when set, the plain epilogue's scale is alpha * *alpha_dev
+  int epi_tma;  // mask epilogues: 0 = TMA-fed form where the call allows it and K is short, 1 = never, 2 = whenever allowed
 };
 
 extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
@@ -1102,6 +1320,25 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
     to1 = to0;
   }
 
+  // TMA-fed mask epilogue: dense (no row map), bf16 mask gradient written (not accumulated), real row pitches.
+  // With a long K loop the main loop is the longer half of a tile and wants the pipeline stages the operand
+  // ring would take, so the automatic choice keeps it to short K.
+  CUtensorMap tci = to0, th = to0, tdci = to0;
+  bool epi_tma = false;
+  if ((c->epi == EPI_MASK_FWD || c->epi == EPI_MASK_BWD) && c->epi_tma != 1 && bn == 256 && c->rowmap == nullptr &&
+      c->bgroup_of_mblock == nullptr && c->ag_world <= 1 && c->rs_world <= 1 && c->ld_ci >= c->N &&
+      (c->epi_tma == 2 || c->K0 + c->K1 <= 1536)) {
+    const bool want_h = c->epi == EPI_MASK_BWD && c->dci != nullptr;
+    epi_tma = !(want_h && (!c->dci_bf16 || c->dci_accumulate || c->ld_h < c->N || c->ld_dci < c->N));
+    if (epi_tma) {
+      if ((rc = encode_tmap(&tci, c->ci, 2, false, c->N, c->M, c->ld_ci, 1, 0, 64, 32))) return 8000 + rc;
+      if (want_h) {
+        if ((rc = encode_tmap(&th, c->H, 2, false, c->N, c->M, c->ld_h, 1, 0, 64, 32))) return 8100 + rc;
+        if ((rc = encode_tmap(&tdci, c->dci, 2, false, c->N, c->M, c->ld_dci, 1, 0, 64, 32))) return 8200 + rc;
+      }
+      if (c->epi == EPI_MASK_FWD && nout != 2) to1 = to0;
+    }
+  }
   for (int r = 0; r < kMaxPeers; ++r) peers.m[r] = to0;
   if (c->rs_world > 1) {
     for (int r = 0; r < c->rs_world; ++r)
@@ -1109,9 +1346,13 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
         return 7000 + rc;
   }
 #define PD_LAUNCH(BN_, EPI_, NOUT_) \
-  launch_gemm<BN_, EPI_, NOUT_, 1>(ta0, tb0, ta1, tb1, to0, to1, peers, a, c->max_ctas, stream)
+  launch_gemm<BN_, EPI_, NOUT_, 1>(ta0, tb0, ta1, tb1, to0, to1, tci, th, tdci, peers, a, c->max_ctas, stream)
 #define PD_LAUNCH2(EPI_, NOUT_) \
-  launch_gemm<256, EPI_, NOUT_, 2>(ta0, tb0, ta1, tb1, to0, to1, peers, a, c->max_ctas, stream)
+  launch_gemm<256, EPI_, NOUT_, 2>(ta0, tb0, ta1, tb1, to0, to1, tci, th, tdci, peers, a, c->max_ctas, stream)
+  if (epi_tma) {
+    if (c->epi == EPI_MASK_FWD) return pair ? PD_LAUNCH2(EPI_MASK_FWD, 4) : PD_LAUNCH(256, EPI_MASK_FWD, 4);
+    return pair ? PD_LAUNCH2(EPI_MASK_BWD, 4) : PD_LAUNCH(256, EPI_MASK_BWD, 4);
+  }
   if (pair) {
     if (c->epi == EPI_PLAIN) return PD_LAUNCH2(EPI_PLAIN, 1);
     if (c->epi == EPI_MASK_FWD) return nout == 2 ? PD_LAUNCH2(EPI_MASK_FWD, 2) : PD_LAUNCH2(EPI_MASK_FWD, 1);

@@ -48,7 +48,7 @@ class PdGemmCall(C.Structure):
         ("rs_world", C.c_int), ("rs_rows", C.c_int), ("rs_out", C.c_void_p * 8),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int), ("ag_src", C.c_void_p * 8),
         ("ag_flags", C.c_void_p), ("ag_seq", C.c_uint), ("ag_mode", C.c_int), ("ag_gather_ctas", C.c_int), ("cta_group", C.c_int), ("rowmap", C.c_void_p), ("philox_col0", C.c_uint),
-        ("seed_dev", C.c_void_p), ("alpha_dev", C.c_void_p),
+        ("seed_dev", C.c_void_p), ("alpha_dev", C.c_void_p), ("epi_tma", C.c_int),
     ]  # fmt: skip
 
 
@@ -194,6 +194,7 @@ def gemm(
     philox_col0: int = 0,
     seed_dev: int = 0,
     alpha_dev: torch.Tensor | None = None,
+    epi_tma: int = 0,
 ) -> torch.Tensor:
     """out = epilogue(A @ B [+ A1 @ B1]) on the tcgen05 kernel.
 
@@ -253,6 +254,7 @@ def gemm(
     call.seed, call.rng_stream, call.mask_mode = seed & (2**64 - 1), rng_stream & 0xFFFFFFFF, mask_mode
     call.rng_row_offset = row_offset & 0xFFFFFFFF
     call.philox_col0 = philox_col0
+    call.epi_tma = epi_tma  # mask epilogues: 0 automatic, 1 plain loads / stores, 2 TMA-fed operands where allowed
     # device address of the step's Philox seed word (0: the seed is taken by value)
     call.seed_dev = seed_dev or (step_seed_ptr(seed) if epi in (EPI_MASK_FWD, EPI_MASK_BWD) and mask_mode == 0 else 0)
     if alpha_dev is not None:
