@@ -18,6 +18,7 @@ from pathlib import Path
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))  # the repository root (run as a script)
 
 import argparse
+import ctypes as C
 import json
 
 import torch
@@ -67,6 +68,38 @@ def build(case: str, N: int, C: int, din: int, dout: int, cg: int = 0, epi_tma: 
     raise ValueError(case)
 
 
+def build_library(case: str, N: int, C: int, din: int, dout: int):
+    """The same contraction through `torch.matmul` / `addmm_` (cuBLAS): the comparison arm for the plain cases.
+    Two-phase products are two library calls accumulating into one output."""
+    dev, bf = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rn(*s):
+        return torch.randn(*s, device=dev, generator=g).to(bf)
+
+    x, V, U, W = rn(N, din), rn(din, C), rn(C, dout), rn(dout, din)
+    A, dy, dH = rn(N, C), rn(N, dout), rn(N, C)
+    if case == "site_out":
+        y = torch.empty(N, dout, device=dev, dtype=bf)
+        return lambda: (torch.matmul(A, U, out=y), y.addmm_(x, W.t()))
+    if case == "dx":
+        dx = torch.empty(N, din, device=dev, dtype=bf)
+        return lambda: (torch.matmul(dH, V.t(), out=dx), dx.addmm_(dy, W))
+    if case == "dV":
+        gV = torch.empty(din, C, device=dev, dtype=bf)
+        return lambda: torch.matmul(x.t(), dH, out=gV)
+    if case == "dU":
+        gU = torch.empty(C, dout, device=dev, dtype=bf)
+        return lambda: torch.matmul(A.t(), dy, out=gU)
+    if case == "mask_fwd":  # main loop only: H = x V, no mask arithmetic
+        H = torch.empty(N, C, device=dev, dtype=bf)
+        return lambda: torch.matmul(x, V, out=H)
+    if case == "mask_bwd":  # main loop only: dA = dy U^T
+        dA = torch.empty(N, C, device=dev, dtype=bf)
+        return lambda: torch.matmul(dy, U.t(), out=dA)
+    raise ValueError(case)
+
+
 def time_case(fn, iters: int, warmup: int = 3) -> float:
     flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
     for _ in range(warmup):
@@ -94,22 +127,51 @@ def main() -> None:
     ap.add_argument("--cta-group", type=int, default=0, help="1 = single-CTA tiles, 2 = CTA pairs, 0 = library default")
     ap.add_argument("--epi-tma", type=int, default=0,
                     help="mask epilogues: 0 = library default, 1 = plain loads / stores, 2 = TMA-fed operand boxes")
+    ap.add_argument("--stages", type=int, default=0,
+                    help="probe of pipeline depth: use only this many stages of the operand ring (0 = all)")
+    ap.add_argument("--probe", type=int, default=0,
+                    help="timing probes (results are garbage): 1 = no operand loads, 2 = no MMAs, 3 = neither")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print CTA 0's cycle stamps of the last launch: set-up, per-tile MMA / epilogue / producer marks")
+    ap.add_argument("--library", action="store_true",
+                    help="also time the same contraction through torch.matmul (cuBLAS; bf16 output, no mask arithmetic)")
     ap.add_argument("--peak", type=float, default=1647.5, help="cuBLAS bf16 burst TFLOP/s to report fractions of")
     ap.add_argument("--hbm", type=float, default=6566.4, help="copy bandwidth GB/s to report fractions of")
     args = ap.parse_args()
     shapes = [(768, 768), (768, 3072), (3072, 768)]
+    nv.lib().pd_gemm_set_stage_limit(args.stages)
+    nv.lib().pd_gemm_set_probe(args.probe)
     cases = CASES if args.case is None else (args.case,)
     if args.case is not None:
         shapes = shapes[:1]
     for din, dout in shapes:
         for case in cases:
             fn, flops, nbytes = build(case, args.rows, args.c, din, dout, args.cta_group, args.epi_tma)
+            tl = None
+            if args.timeline:
+                tl = torch.zeros(256, dtype=torch.int64, device="cuda")
+                nv.lib().pd_gemm_set_timeline(C.c_void_p(tl.data_ptr()))
             ms = time_case(fn, args.iters, args.warmup)
-            print(json.dumps({"case": case, "cta_group": args.cta_group, "epi_tma": args.epi_tma, "rows": args.rows, "C": args.c, "d_in": din, "d_out": dout,
+            if tl is not None:
+                nv.lib().pd_gemm_set_timeline(C.c_void_p(0))
+                v = tl.cpu().tolist()
+                rel = lambda x: x - v[0] if x else None
+                print(json.dumps({"case": case, "timeline_cycles": {
+                    "setup_done": rel(v[1]), "teardown_start": rel(v[2]), "exit": rel(v[3]),
+                    "mma_granted_committed": [[rel(v[16 + 2 * i]), rel(v[17 + 2 * i])] for i in range(8) if v[16 + 2 * i]],
+                    "epi_full_drained": [[rel(v[80 + 2 * i]), rel(v[81 + 2 * i])] for i in range(8) if v[80 + 2 * i]],
+                    "producer_tile_issued": [rel(v[144 + i]) for i in range(8) if v[144 + i]]}}), flush=True)
+            del fn
+            lib = {}
+            if args.library:
+                lib_ms = time_case(build_library(case, args.rows, args.c, din, dout), args.iters, args.warmup)
+                lib = {"library_us": round(lib_ms * 1e3, 1), "library_tflops": round(flops / lib_ms / 1e9, 1),
+                       "ours_over_library_time": round(ms / lib_ms, 3)}
+            print(json.dumps({"case": case, "cta_group": args.cta_group, "epi_tma": args.epi_tma, "stages": args.stages, "probe": args.probe, "rows": args.rows, "C": args.c, "d_in": din, "d_out": dout,
                               "us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
                               "frac_of_measured_gemm_peak": round(flops / ms / 1e9 / args.peak, 3),
                               "algorithmic_gb_per_s": round(nbytes / ms / 1e6, 1),
-                              "frac_of_measured_copy_bw": round(nbytes / ms / 1e6 / args.hbm, 3)}), flush=True)
+                              "frac_of_measured_copy_bw": round(nbytes / ms / 1e6 / args.hbm, 3), **lib}), flush=True)
     nv.check_status()
 
 

@@ -118,6 +118,9 @@ struct GemmArgs {
   // First global column of this product's mask columns in the Philox counter space (a rank that holds a
   // column slice of a site draws the same uniforms the whole site would); multiple of 8.
   unsigned int philox_col0;
+  long long* timeline;  // diagnostic: CTA 0 writes clock64() stamps here (256 slots), nullptr = off
+  int probe;        // timing probes (results are garbage): bit 0 = no operand loads, bit 1 = no MMAs, bit 2 (with bit 0) = no operand barriers
+  int stage_limit;  // > 0: use only this many of the operand ring's stages (a tuning probe of pipeline depth)
 };
 
 template <int BN, int NOUT, int CG = 1>
@@ -197,6 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             const __grid_constant__ PeerMaps peerOut, const GemmArgs args) {
   using Plan = SmemPlan<BN, NOUT, CG>;
   constexpr int kStages = Plan::kStages;
+  const int nstages = (args.stage_limit >= 2 && args.stage_limit < kStages) ? args.stage_limit : kStages;
   constexpr int kStageBytesB = Plan::kStageBytesB;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two as tcgen05.alloc requires
   // CG == 2: two CTAs of a cluster share a 256-row tile; rank 0 issues the MMAs for both.
@@ -224,6 +228,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // Diagnostic timeline (CTA 0 only): slot 0 entry, 1 set-up done, 2 before teardown, 3 exit; MMA issuer
+  // 16 + 2i / 17 + 2i = accumulator granted / tile i committed; first epilogue warp 80 + 2i / 81 + 2i =
+  // accumulator full seen / tile i drained; producer 144 + i = last load of tile i issued.
+  auto stamp = [&](int slot) {
+    if (args.timeline != nullptr && blockIdx.x == 0 && slot < 256) args.timeline[slot] = clock64();
+  };
+  if (threadIdx.x == 0) stamp(0);
   const int num_m = (args.M + BM - 1) / BM;
   const int num_n = (args.N + BN - 1) / BN;
   const int kb_total = args.kblocks0 + args.kblocks1;
@@ -272,6 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) stamp(1);
 
   // Tile decode: batch / split outermost, then panels of kGroupM row blocks walked column by column.
   const long long tiles_per_mat = static_cast<long long>(num_m_t) * num_n;
@@ -384,30 +396,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         }
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    } else if (lane == 0) {
+    } else if (!is_gather_cta) {
+      // The whole warp walks the loop with identical values, and one elected lane issues the copies: the
+      // loop state then lives in uniform registers, which is where the TMA instructions take their operands
+      // from. (A loop run by a single diverged lane pays a register-to-uniform move per operand per copy.)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       unsigned long long landed = 0ull;  // mode 1: K slabs (< 64) already seen complete
-      auto wait_block = [&](int idx) {
-        const unsigned long long t0 = globaltimer_ns();
-        while (true) {
-          unsigned int f;
-          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(args.ag_flags + idx) : "memory");
-          if (f == args.ag_seq) break;
-          if (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
-            return false;
+      auto wait_block = [&](int idx) {  // lane 0 polls the flag, the warp takes its verdict
+        int good = 1;
+        if (lane == 0) {
+          const unsigned long long t0 = globaltimer_ns();
+          while (true) {
+            unsigned int f;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(args.ag_flags + idx) : "memory");
+            if (f == args.ag_seq) break;
+            if (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs) {
+              *abort_flag = 1;
+              if (args.status) atomicCAS(args.status, 0, kTimeoutPeerFlag);
+              good = 0;
+              break;
+            }
           }
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // bulk-copy writes -> TMA reads
         }
-        asm volatile("fence.proxy.async.global;" ::: "memory");  // bulk-copy writes -> TMA reads
-        return true;
+        return __shfl_sync(0xffffffffu, good, 0) != 0;
       };
       const bool ag_b = args.ag_world > 1 && args.ag_mode == 1;
       const int ag_per_rank = args.ag_world > 1 ? args.ag_rows / (ag_b ? BK : BM) : 1;
       const int ag_lo = args.ag_rank * ag_per_rank, ag_hi = ag_lo + ag_per_rank;  // this rank's own blocks
-      for (long long t = tile0; t < num_tiles && ok; t += tstride) {
+      int tile_idx = 0;
+      for (long long t = tile0; t < num_tiles && ok; t += tstride, ++tile_idx) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
         int kb_lo, kb_hi;
@@ -423,6 +443,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             break;
           }
         }
+        const int n0 = nb * BN + static_cast<int>(cta_rank) * (BN / CG);  // this CTA's share of the B tile
         for (int kbi = kb_lo; kbi < kb_hi; ++kbi) {
           int kb = kbi;
           if (ag_b) {  // this rank's own K slabs first, then the peers' in the order they arrive
@@ -436,8 +457,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
               if (kb < 64) landed |= 1ull << kb;
             }
           }
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
-            if (args.status) atomicCAS(args.status, 0, kTimeoutProducer);
+          if (args.probe & 4) continue;  // MMA-rate probe: no operand handshake at all
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag))) {
+            if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutProducer);
             ok = false;
             break;
           }
@@ -448,96 +470,125 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           const int a_mn = p1 ? args.a_mn1 : args.a_mn0;
           const int b_mn = p1 ? args.b_mn1 : args.b_mn0;
           const uint32_t full = bar_full + 8 * stage;
-          // pair: the leader's barrier collects the bytes of both CTAs' copies
-          if (leader) mbar_expect_tx(full, (kStageBytesA + kStageBytesB) * CG);
           const uint32_t sa = smem_a + stage * kStageBytesA;
           const uint32_t sb = smem_b + stage * kStageBytesB;
-          auto load = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2) {
-            if constexpr (CG == 2)
-              tma_load_3d_pair(dst, tm, full, c0, c1, c2);
-            else
-              tma_load_3d(dst, tm, full, c0, c1, c2);
-          };
-          if (!a_mn) {
-            load(sa, ta, k0, mb * BM, ab);
-          } else {
+          if (elect_one_sync()) {
+            if (args.probe & 1) {
+              if (leader) mbar_arrive(full);
+            } else {
+              // pair: the leader's barrier collects the bytes of both CTAs' copies
+              if (leader) mbar_expect_tx(full, (kStageBytesA + kStageBytesB) * CG);
+              auto load = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2) {
+                if constexpr (CG == 2)
+                  tma_load_3d_pair(dst, tm, full, c0, c1, c2);
+                else
+                  tma_load_3d(dst, tm, full, c0, c1, c2);
+              };
+              if (!a_mn) {
+                load(sa, ta, k0, mb * BM, ab);
+              } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) load(sa + i * (BK * 128), ta, mb * BM + 64 * i, k0, ab);
-          }
-          const int n0 = nb * BN + static_cast<int>(cta_rank) * (BN / CG);  // this CTA's share of the B tile
-          if (!b_mn) {
-            load(sb, tb, k0, n0, bbatch);
-          } else {
+                for (int i = 0; i < BM / 64; ++i) load(sa + i * (BK * 128), ta, mb * BM + 64 * i, k0, ab);
+              }
+              if (!b_mn) {
+                load(sb, tb, k0, n0, bbatch);
+              } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64 / CG; ++i) load(sb + i * (BK * 128), tb, n0 + 64 * i, k0, bbatch);
+                for (int i = 0; i < BN / 64 / CG; ++i) load(sb + i * (BK * 128), tb, n0 + 64 * i, k0, bbatch);
+              }
+            }
           }
-          if (++stage == kStages) {
+          if (++stage == nstages) {
             stage = 0;
             phase ^= 1;
           }
         }
+        if (lane == 0) stamp(144 + tile_idx);
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0 && leader) {
+    if (leader) {
+      // Warp-uniform loop, one elected lane issues (see the producer): descriptors and barrier addresses
+      // stay in uniform registers.
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (long long t = tile0; t < num_tiles && ok; t += tstride) {
+      // per K phase: instruction descriptor, the descriptor bits above the address, the address step per K = 16.
+      // One instruction covers K = 16: 32 B along a K-major swizzle row, or two 8-row groups (2048 B) of an
+      // MN-major tile. The address field counts 16-byte units.
+      const uint32_t idesc0 = make_idesc_bf16(BM * CG, BN, args.a_mn0, args.b_mn0);
+      const uint32_t idesc1 = make_idesc_bf16(BM * CG, BN, args.a_mn1, args.b_mn1);
+      const uint64_t a_hi0 = make_smem_desc(0, args.a_mn0 ? BK * 128 : 16, 1024);
+      const uint64_t a_hi1 = make_smem_desc(0, args.a_mn1 ? BK * 128 : 16, 1024);
+      const uint64_t b_hi0 = make_smem_desc(0, args.b_mn0 ? BK * 128 : 16, 1024);
+      const uint64_t b_hi1 = make_smem_desc(0, args.b_mn1 ? BK * 128 : 16, 1024);
+      const uint32_t a_step0 = args.a_mn0 ? (2048 >> 4) : (32 >> 4), a_step1 = args.a_mn1 ? (2048 >> 4) : (32 >> 4);
+      const uint32_t b_step0 = args.b_mn0 ? (2048 >> 4) : (32 >> 4), b_step1 = args.b_mn1 ? (2048 >> 4) : (32 >> 4);
+      int tile_idx = 0;
+      for (long long t = tile0; t < num_tiles && ok; t += tstride, ++tile_idx) {
         int b, mb, nb, sp;
         decode(t, b, mb, nb, sp);
         int kb_lo, kb_hi;
         tile_krange(b, sp, kb_lo, kb_hi);
         if (args.bgroup_of_mblock && args.bgroup_of_mblock[mb] < 0) continue;
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) {
-          if (args.status) atomicCAS(args.status, 0, kTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag))) {
+          if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutMma);
           break;
         }
         tc_fence_after();
+        if (lane == 0) stamp(16 + 2 * tile_idx);
         const uint32_t tmem_d = tmem_base + acc * BN;
+        uint32_t accumulate = 0u;
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
-            if (args.status) atomicCAS(args.status, 0, kTimeoutMma);
+          if (!(args.probe & 4) &&
+              !__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase, abort_flag))) {
+            if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after();
           const bool p1 = kb >= args.kblocks0;
-          const int a_mn = p1 ? args.a_mn1 : args.a_mn0;
-          const int b_mn = p1 ? args.b_mn1 : args.b_mn0;
-          const uint32_t idesc = make_idesc_bf16(BM * CG, BN, a_mn, b_mn);
+          const uint32_t idesc = p1 ? idesc1 : idesc0;
           const uint32_t sa = smem_a + stage * kStageBytesA;
           const uint32_t sb = smem_b + stage * kStageBytesB;
-          const uint64_t adesc = make_smem_desc(sa, a_mn ? BK * 128 : 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sb, b_mn ? BK * 128 : 16, 1024);
-          // One instruction covers K = 16: 32 B along a K-major swizzle row, or two 8-row groups
-          // (2048 B) of an MN-major tile. The address field counts 16-byte units.
-          const uint64_t a_step = a_mn ? (2048 >> 4) : (32 >> 4);
-          const uint64_t b_step = b_mn ? (2048 >> 4) : (32 >> 4);
+          const uint64_t adesc = (p1 ? a_hi1 : a_hi0) | static_cast<uint64_t>((sa & 0x3FFFF) >> 4);
+          const uint64_t bdesc = (p1 ? b_hi1 : b_hi0) | static_cast<uint64_t>((sb & 0x3FFFF) >> 4);
+          const uint32_t a_step = p1 ? a_step1 : a_step0;
+          const uint32_t b_step = p1 ? b_step1 : b_step0;
+          if (elect_one_sync()) {
+            if (!(args.probe & 2)) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            if constexpr (CG == 2)
-              umma_bf16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
-            else
-              umma_bf16(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
+              for (int k = 0; k < BK / 16; ++k) {
+                if constexpr (CG == 2)
+                  umma_bf16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, k > 0 ? 1u : accumulate);
+                else
+                  umma_bf16(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, k > 0 ? 1u : accumulate);
+              }
+            }
+            if (!(args.probe & 4)) {
+              if constexpr (CG == 2)
+                umma_commit_pair(bar_empty + 8 * stage);
+              else
+                umma_commit(bar_empty + 8 * stage);
+            }
           }
-          if constexpr (CG == 2)
-            umma_commit_pair(bar_empty + 8 * stage);
-          else
-            umma_commit(bar_empty + 8 * stage);
-          if (++stage == kStages) {
+          accumulate = 1u;
+          if (++stage == nstages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        if constexpr (CG == 2)
-          umma_commit_pair(bar_tfull + 8 * acc);
-        else
-          umma_commit(bar_tfull + 8 * acc);
+        if (elect_one_sync()) {
+          if constexpr (CG == 2)
+            umma_commit_pair(bar_tfull + 8 * acc);
+          else
+            umma_commit(bar_tfull + 8 * acc);
+        }
+        if (lane == 0) stamp(17 + 2 * tile_idx);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -890,13 +941,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             }
           }
           if (!have_acc) {
-            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+            bool got = true;
+            if (args.probe & 16) {  // one lane polls; the others park at the warp shuffle
+              if (lane == 0) got = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag);
+              got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+            } else {
+              got = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag);
+            }
+            if (!got) {
               if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
               failed = true;
               break;
             }
             tc_fence_after();
             have_acc = true;
+            if (args.timeline != nullptr && warp == 2 && lane == 0) stamp(80 + 2 * static_cast<int>((t - tile0) / tstride));
           }
           uint32_t r[32];
           tmem_ld_32x32(tmem_row + j * box_cols + 32 * half, r);
@@ -1047,6 +1106,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));  // the MMA issuer lives in the leader
         else
           mbar_arrive(bar_tempty + 8 * acc);
+        if (args.timeline != nullptr && warp == 2) stamp(81 + 2 * static_cast<int>((t - tile0) / tstride));
       }
       if (++acc == 2) {
         acc = 0;
@@ -1069,6 +1129,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     while (globaltimer_ns() - t0 < 2000000ull) {
     }
   }
+  if (threadIdx.x == 0) stamp(2);
   tc_fence_before();
   __syncthreads();
   // pair: neither CTA may retire while its partner can still signal its barriers or read its smem
@@ -1080,6 +1141,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     else
       tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) stamp(3);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1093,6 +1155,9 @@ struct OperandDesc {
 };
 
 static int g_num_sms = 0;
+static long long* g_timeline = nullptr;  // pd_gemm_set_timeline(ptr): see GemmArgs::timeline
+static int g_probe = 0;             // pd_gemm_set_probe(bits): timing probes, see GemmArgs::probe
+static int g_stage_limit = 0;       // pd_gemm_set_stage_limit(n): probe of pipeline depth, 0 = all stages
 static bool g_pair_default = true;  // pd_gemm_set_pair_default(0) turns automatic pairing off
 
 static int encode_operand(CUtensorMap* tm, const OperandDesc& op, int mn_extent, int k_extent,
@@ -1246,6 +1311,9 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   a.ag_mode = c->ag_mode;
   a.rowmap = static_cast<const int4*>(c->rowmap);
   a.philox_col0 = c->philox_col0;
+  a.stage_limit = g_stage_limit;
+  a.probe = g_probe;
+  a.timeline = g_timeline;
   if (c->philox_col0 % 8 != 0) return kBadArgument;
   if (c->ag_world > 1 && c->ag_mode == 1) {
     a.ag_dst = const_cast<void*>(c->B0); a.ag_ld = c->ldb0; a.ag_k = c->N;
@@ -1370,6 +1438,12 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
 #undef PD_LAUNCH
   return kBadArgument;
 }
+
+extern "C" void pd_gemm_set_timeline(void* dev_ptr) { g_timeline = static_cast<long long*>(dev_ptr); }
+
+extern "C" void pd_gemm_set_probe(int bits) { g_probe = bits; }
+
+extern "C" void pd_gemm_set_stage_limit(int n) { g_stage_limit = n; }
 
 extern "C" void pd_gemm_set_pair_default(int on) { g_pair_default = on != 0; }
 
