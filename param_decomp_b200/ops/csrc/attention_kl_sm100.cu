@@ -85,18 +85,21 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_kl_fwd_kernel(const __gri
   const uint32_t tmem_m = tmem_c + 128;
 
   if (warp == 4) {
-    if (lane == 0) {
+    // whole warp walks the loop, one elected lane issues (operands stay in uniform registers)
+    if (elect_one_sync()) {
       mbar_expect_tx(bar_q, 2 * Plan::kTileBytes);
       for (int c = 0; c < kKB; ++c) {
         tma_load_3d(sm_qc + c * (kTile * 128), &tmQc, bar_q, h * HD + 64 * c, qt * kTile, b);
         tma_load_3d(sm_qm + c * (kTile * 128), &tmQm, bar_q, h * HD + 64 * c, qt * kTile, b);
       }
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j % kStages;
-        if (!mbar_wait(bar_ke + 8 * st, static_cast<uint32_t>(((j / kStages) & 1) ^ 1), abort_flag)) {
-          atomicCAS(args.status, 0, kTimeoutProducer);
-          break;
-        }
+    }
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j % kStages;
+      if (!mbar_wait_warp(bar_ke + 8 * st, static_cast<uint32_t>(((j / kStages) & 1) ^ 1), abort_flag)) {
+        if (lane == 0) atomicCAS(args.status, 0, kTimeoutProducer);
+        break;
+      }
+      if (elect_one_sync()) {
         mbar_expect_tx(bar_kf + 8 * st, 2 * Plan::kTileBytes);
         for (int c = 0; c < kKB; ++c) {
           tma_load_3d(sm_kc + st * Plan::kTileBytes + c * (kTile * 128), &tmKc, bar_kf + 8 * st, hk * HD + 64 * c,
@@ -107,33 +110,35 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_kl_fwd_kernel(const __gri
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc_bf16(kTile, kTile, 0, 0);
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      bool ok = mbar_wait_warp(bar_q, 0, abort_flag);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j % kStages;
-        if (!mbar_wait(bar_kf + 8 * st, static_cast<uint32_t>((j / kStages) & 1), abort_flag) ||
-            !mbar_wait(bar_se, static_cast<uint32_t>((j & 1) ^ 1), abort_flag)) {
+        if (!mbar_wait_warp(bar_kf + 8 * st, static_cast<uint32_t>((j / kStages) & 1), abort_flag) ||
+            !mbar_wait_warp(bar_se, static_cast<uint32_t>((j & 1) ^ 1), abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        if (elect_one_sync()) {
 #pragma unroll
-        for (int c = 0; c < kKB; ++c) {
-          const uint64_t qc = make_smem_desc(sm_qc + c * (kTile * 128), 16, 1024);
-          const uint64_t qm = make_smem_desc(sm_qm + c * (kTile * 128), 16, 1024);
-          const uint64_t kc = make_smem_desc(sm_kc + st * Plan::kTileBytes + c * (kTile * 128), 16, 1024);
-          const uint64_t km = make_smem_desc(sm_km + st * Plan::kTileBytes + c * (kTile * 128), 16, 1024);
+          for (int c = 0; c < kKB; ++c) {
+            const uint64_t qc = make_smem_desc(sm_qc + c * (kTile * 128), 16, 1024);
+            const uint64_t qm = make_smem_desc(sm_qm + c * (kTile * 128), 16, 1024);
+            const uint64_t kc = make_smem_desc(sm_kc + st * Plan::kTileBytes + c * (kTile * 128), 16, 1024);
+            const uint64_t km = make_smem_desc(sm_km + st * Plan::kTileBytes + c * (kTile * 128), 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma_bf16(tmem_c, qc + k * 2, kc + k * 2, idesc, (c > 0 || k > 0) ? 1u : 0u);
-            umma_bf16(tmem_m, qm + k * 2, km + k * 2, idesc, (c > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) {
+              umma_bf16(tmem_c, qc + k * 2, kc + k * 2, idesc, (c > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tmem_m, qm + k * 2, km + k * 2, idesc, (c > 0 || k > 0) ? 1u : 0u);
+            }
           }
+          umma_commit(bar_ke + 8 * st);
+          umma_commit(bar_s);
         }
-        umma_commit(bar_ke + 8 * st);
-        umma_commit(bar_s);
       }
-      if (!ok) atomicCAS(args.status, 0, kTimeoutMma);
+      if (!ok && lane == 0) atomicCAS(args.status, 0, kTimeoutMma);
     }
   } else {
     const int row = threadIdx.x;
@@ -273,20 +278,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_kl_bwd_kernel(const __gri
   const uint32_t tmem_dk = tmem_c + 256;
 
   if (warp == 4) {
-    if (lane == 0) {
+    if (elect_one_sync()) {
       mbar_expect_tx(bar_kv, 2 * Plan::kTileBytes);
       for (int c = 0; c < kKB; ++c) {
         tma_load_3d(sm_kc + c * (kTile * 128), &tmKc, bar_kv, hk * HD + 64 * c, kt * kTile, b);
         tma_load_3d(sm_km + c * (kTile * 128), &tmKm, bar_kv, hk * HD + 64 * c, kt * kTile, b);
       }
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % kStages;
-        if (!mbar_wait(bar_qe + 8 * st, static_cast<uint32_t>(((it / kStages) & 1) ^ 1), abort_flag)) {
-          atomicCAS(args.status, 0, kTimeoutProducer);
-          break;
-        }
-        const int h = hk * group + it / per_head;
-        const int qt = qt_lo + it % per_head;
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % kStages;
+      if (!mbar_wait_warp(bar_qe + 8 * st, static_cast<uint32_t>(((it / kStages) & 1) ^ 1), abort_flag)) {
+        if (lane == 0) atomicCAS(args.status, 0, kTimeoutProducer);
+        break;
+      }
+      const int h = hk * group + it / per_head;
+      const int qt = qt_lo + it % per_head;
+      if (elect_one_sync()) {
         mbar_expect_tx(bar_qf + 8 * st, 2 * Plan::kTileBytes);
         for (int c = 0; c < kKB; ++c) {
           tma_load_3d(sm_qc + st * Plan::kTileBytes + c * (kTile * 128), &tmQc, bar_qf + 8 * st, h * HD + 64 * c,
@@ -297,53 +304,57 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_kl_bwd_kernel(const __gri
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       constexpr uint32_t idesc_t = make_idesc_bf16(kTile, HD, 1, 1);
       constexpr uint32_t idesc_q = make_idesc_bf16(kTile, HD, 0, 1);
-      bool ok = mbar_wait(bar_kv, 0, abort_flag);
+      bool ok = mbar_wait_warp(bar_kv, 0, abort_flag);
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it % kStages;
-        if (!mbar_wait(bar_qf + 8 * st, static_cast<uint32_t>((it / kStages) & 1), abort_flag) ||
-            !mbar_wait(bar_dqe, static_cast<uint32_t>((it & 1) ^ 1), abort_flag)) {
+        if (!mbar_wait_warp(bar_qf + 8 * st, static_cast<uint32_t>((it / kStages) & 1), abort_flag) ||
+            !mbar_wait_warp(bar_dqe, static_cast<uint32_t>((it & 1) ^ 1), abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t qc_s = sm_qc + st * Plan::kTileBytes, qm_s = sm_qm + st * Plan::kTileBytes;
+        if (elect_one_sync()) {
 #pragma unroll
-        for (int c = 0; c < kKB; ++c) {
-          const uint64_t qc = make_smem_desc(qc_s + c * (kTile * 128), 16, 1024);
-          const uint64_t qm = make_smem_desc(qm_s + c * (kTile * 128), 16, 1024);
-          const uint64_t kc = make_smem_desc(sm_kc + c * (kTile * 128), 16, 1024);
-          const uint64_t km = make_smem_desc(sm_km + c * (kTile * 128), 16, 1024);
+          for (int c = 0; c < kKB; ++c) {
+            const uint64_t qc = make_smem_desc(qc_s + c * (kTile * 128), 16, 1024);
+            const uint64_t qm = make_smem_desc(qm_s + c * (kTile * 128), 16, 1024);
+            const uint64_t kc = make_smem_desc(sm_kc + c * (kTile * 128), 16, 1024);
+            const uint64_t km = make_smem_desc(sm_km + c * (kTile * 128), 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma_bf16(tmem_c, qc + k * 2, kc + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
-            umma_bf16(tmem_m, qm + k * 2, km + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) {
+              umma_bf16(tmem_c, qc + k * 2, kc + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tmem_m, qm + k * 2, km + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+            }
           }
+          umma_commit(bar_s);
         }
-        umma_commit(bar_s);
-        if (!mbar_wait(bar_ds, static_cast<uint32_t>(it & 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_ds, static_cast<uint32_t>(it & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t dst = make_smem_desc(sm_ds, kTile * 128, 1024);
-        const uint64_t qb = make_smem_desc(qm_s, kTile * 128, 1024);
+        if (elect_one_sync()) {
+          const uint64_t dst = make_smem_desc(sm_ds, kTile * 128, 1024);
+          const uint64_t qb = make_smem_desc(qm_s, kTile * 128, 1024);
 #pragma unroll
-        for (int k = 0; k < kTile / 16; ++k)
-          umma_bf16(tmem_dk, dst + k * (2048 >> 4), qb + k * (2048 >> 4), idesc_t, (it > 0 || k > 0) ? 1u : 0u);
-        const uint64_t kb_ = make_smem_desc(sm_km, kTile * 128, 1024);
+          for (int k = 0; k < kTile / 16; ++k)
+            umma_bf16(tmem_dk, dst + k * (2048 >> 4), qb + k * (2048 >> 4), idesc_t, (it > 0 || k > 0) ? 1u : 0u);
+          const uint64_t kb_ = make_smem_desc(sm_km, kTile * 128, 1024);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint64_t dsd = make_smem_desc(sm_ds + c * (kTile * 128), 16, 1024);
+          for (int c = 0; c < 2; ++c) {
+            const uint64_t dsd = make_smem_desc(sm_ds + c * (kTile * 128), 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_c, dsd + k * 2, kb_ + (c * 4 + k) * (2048 >> 4), idesc_q, (c > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem_c, dsd + k * 2, kb_ + (c * 4 + k) * (2048 >> 4), idesc_q, (c > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_qe + 8 * st);
+          umma_commit(bar_dqf);
         }
-        umma_commit(bar_qe + 8 * st);
-        umma_commit(bar_dqf);
       }
-      if (ok) umma_commit(bar_fin);
-      if (!ok) atomicCAS(args.status, 0, kTimeoutMma);
+      if (ok && elect_one_sync()) umma_commit(bar_fin);
+      if (!ok && lane == 0) atomicCAS(args.status, 0, kTimeoutMma);
     }
   } else {
     const int row = threadIdx.x;

@@ -124,27 +124,31 @@ __global__ void __launch_bounds__(kFwdThreads, HD == 64 ? 2 : 1) attn_fwd_kernel
   const uint32_t tmem_o = tmem_s + 128;
 
   if (warp == 4) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    // ---------------- TMA producer (whole warp walks the loop, one elected lane issues) ----------------
+    if (elect_one_sync()) {
       mbar_expect_tx(bar_q, Plan::kQBytes);
       for (int c = 0; c < kKB; ++c) tma_load_3d(sm_q + c * (kTile * 128), &tmQ, bar_q, h * HD + 64 * c, qt * kTile, b);
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
-        if (!mbar_wait(bar_ke + 8 * st, ph ^ 1, abort_flag)) {
-          atomicCAS(args.status, 0, kTimeoutProducer);
-          break;
-        }
+    }
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j % kStages;
+      const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+      if (!mbar_wait_warp(bar_ke + 8 * st, ph ^ 1, abort_flag)) {
+        if (lane == 0) atomicCAS(args.status, 0, kTimeoutProducer);
+        break;
+      }
+      if (elect_one_sync()) {
         mbar_expect_tx(bar_kf + 8 * st, Plan::kKVBytes);
         for (int c = 0; c < kKB; ++c)
           tma_load_3d(sm_k + st * Plan::kKVBytes + c * (kTile * 128), &tmK, bar_kf + 8 * st, hk * HD + 64 * c,
                       j * kTile, b);
-        const int vs = j % kVStages;
-        const uint32_t vph = static_cast<uint32_t>((j / kVStages) & 1);
-        if (!mbar_wait(bar_ve + 8 * vs, vph ^ 1, abort_flag)) {
-          atomicCAS(args.status, 0, kTimeoutProducer);
-          break;
-        }
+      }
+      const int vs = j % kVStages;
+      const uint32_t vph = static_cast<uint32_t>((j / kVStages) & 1);
+      if (!mbar_wait_warp(bar_ve + 8 * vs, vph ^ 1, abort_flag)) {
+        if (lane == 0) atomicCAS(args.status, 0, kTimeoutProducer);
+        break;
+      }
+      if (elect_one_sync()) {
         mbar_expect_tx(bar_vf + 8 * vs, Plan::kKVBytes);
         for (int c = 0; c < kKB; ++c)
           tma_load_3d(sm_v + vs * Plan::kKVBytes + c * (kTile * 128), &tmV, bar_vf + 8 * vs, hk * HD + 64 * c,
@@ -152,48 +156,51 @@ __global__ void __launch_bounds__(kFwdThreads, HD == 64 ? 2 : 1) attn_fwd_kernel
       }
     }
   } else if (warp == 5) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // ---------------- MMA issuer (whole warp walks the loop, one elected lane issues) ----------------
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(kTile, HD, 0, 1);
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      bool ok = mbar_wait_warp(bar_q, 0, abort_flag);
       auto issue_s = [&](int j) {
         const int st = j % kStages;
-        if (!mbar_wait(bar_kf + 8 * st, static_cast<uint32_t>((j / kStages) & 1), abort_flag)) return false;
+        if (!mbar_wait_warp(bar_kf + 8 * st, static_cast<uint32_t>((j / kStages) & 1), abort_flag)) return false;
         tc_fence_after();
+        if (elect_one_sync()) {
 #pragma unroll
-        for (int c = 0; c < kKB; ++c) {
-          const uint64_t ad = make_smem_desc(sm_q + c * (kTile * 128), 16, 1024);
-          const uint64_t bd = make_smem_desc(sm_k + st * Plan::kKVBytes + c * (kTile * 128), 16, 1024);
+          for (int c = 0; c < kKB; ++c) {
+            const uint64_t ad = make_smem_desc(sm_q + c * (kTile * 128), 16, 1024);
+            const uint64_t bd = make_smem_desc(sm_k + st * Plan::kKVBytes + c * (kTile * 128), 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, ad + k * 2, bd + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, ad + k * 2, bd + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_ke + 8 * st);
+          umma_commit(bar_s);
         }
-        umma_commit(bar_ke + 8 * st);
-        umma_commit(bar_s);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j % kStages;
         // P_j is in shared memory; the softmax warps are also done with S_j and O_{j-1}
-        if (!mbar_wait(bar_p, static_cast<uint32_t>(j & 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_p, static_cast<uint32_t>(j & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
         const int vs = j % kVStages;
-        if (!mbar_wait(bar_vf + 8 * vs, static_cast<uint32_t>((j / kVStages) & 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_vf + 8 * vs, static_cast<uint32_t>((j / kVStages) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t vd = make_smem_desc(sm_v + vs * Plan::kKVBytes, kTile * 128, 1024);
+        if (elect_one_sync()) {
+          const uint64_t vd = make_smem_desc(sm_v + vs * Plan::kKVBytes, kTile * 128, 1024);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {  // two 64-wide blocks of the key index
-          const uint64_t pd_ = make_smem_desc(sm_p + c * (kTile * 128), 16, 1024);
+          for (int c = 0; c < 2; ++c) {  // two 64-wide blocks of the key index
+            const uint64_t pd_ = make_smem_desc(sm_p + c * (kTile * 128), 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_o, pd_ + k * 2, vd + (c * 4 + k) * (2048 >> 4), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem_o, pd_ + k * 2, vd + (c * 4 + k) * (2048 >> 4), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_ve + 8 * vs);
+          umma_commit(bar_o);
         }
-        umma_commit(bar_ve + 8 * vs);
-        umma_commit(bar_o);
       }
-      if (!ok) atomicCAS(args.status, 0, kTimeoutMma);
+      if (!ok && lane == 0) atomicCAS(args.status, 0, kTimeoutMma);
     }
   } else {
     // ---------------- softmax + output (one query row per thread) ----------------
@@ -428,21 +435,23 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_bwd_kernel(const __grid_c
   const uint32_t tmem_dk = tmem_dv + HD;
 
   if (warp == 4) {
-    if (lane == 0) {
+    if (elect_one_sync()) {
       mbar_expect_tx(bar_kv, 2 * Plan::kTileBytes);
       for (int c = 0; c < kKB; ++c) {
         tma_load_3d(sm_k + c * (kTile * 128), &tmK, bar_kv, hk * HD + 64 * c, kt * kTile, b);
         tma_load_3d(sm_v + c * (kTile * 128), &tmV, bar_kv, hk * HD + 64 * c, kt * kTile, b);
       }
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % kStages;
-        const uint32_t ph = static_cast<uint32_t>((it / kStages) & 1);
-        if (!mbar_wait(bar_qe + 8 * st, ph ^ 1, abort_flag)) {
-          atomicCAS(args.status, 0, kTimeoutProducer);
-          break;
-        }
-        const int h = hk * group + it / per_head;
-        const int qt = qt_lo + it % per_head;
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % kStages;
+      const uint32_t ph = static_cast<uint32_t>((it / kStages) & 1);
+      if (!mbar_wait_warp(bar_qe + 8 * st, ph ^ 1, abort_flag)) {
+        if (lane == 0) atomicCAS(args.status, 0, kTimeoutProducer);
+        break;
+      }
+      const int h = hk * group + it / per_head;
+      const int qt = qt_lo + it % per_head;
+      if (elect_one_sync()) {
         mbar_expect_tx(bar_qf + 8 * st, 2 * Plan::kTileBytes);
         for (int c = 0; c < kKB; ++c) {
           tma_load_3d(sm_q + st * Plan::kTileBytes + c * (kTile * 128), &tmQ, bar_qf + 8 * st, h * HD + 64 * c,
@@ -453,57 +462,61 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_bwd_kernel(const __grid_c
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);   // Q K^T, dO V^T
       constexpr uint32_t idesc_t = make_idesc_bf16(kTile, HD, 1, 1);      // P^T dO, dS^T Q
       constexpr uint32_t idesc_q = make_idesc_bf16(kTile, HD, 0, 1);      // dS K
-      bool ok = mbar_wait(bar_kv, 0, abort_flag);
+      bool ok = mbar_wait_warp(bar_kv, 0, abort_flag);
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it % kStages;
-        if (!mbar_wait(bar_qf + 8 * st, static_cast<uint32_t>((it / kStages) & 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_qf + 8 * st, static_cast<uint32_t>((it / kStages) & 1), abort_flag)) { ok = false; break; }
         // the softmax warps have read dQ of the previous iteration out of the S columns
-        if (!mbar_wait(bar_dqe, static_cast<uint32_t>((it & 1) ^ 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_dqe, static_cast<uint32_t>((it & 1) ^ 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t q_s = sm_q + st * Plan::kTileBytes, do_s = sm_do + st * Plan::kTileBytes;
+        if (elect_one_sync()) {
 #pragma unroll
-        for (int c = 0; c < kKB; ++c) {
-          const uint64_t qd = make_smem_desc(q_s + c * (kTile * 128), 16, 1024);
-          const uint64_t kd = make_smem_desc(sm_k + c * (kTile * 128), 16, 1024);
-          const uint64_t dod = make_smem_desc(do_s + c * (kTile * 128), 16, 1024);
-          const uint64_t vd = make_smem_desc(sm_v + c * (kTile * 128), 16, 1024);
+          for (int c = 0; c < kKB; ++c) {
+            const uint64_t qd = make_smem_desc(q_s + c * (kTile * 128), 16, 1024);
+            const uint64_t kd = make_smem_desc(sm_k + c * (kTile * 128), 16, 1024);
+            const uint64_t dod = make_smem_desc(do_s + c * (kTile * 128), 16, 1024);
+            const uint64_t vd = make_smem_desc(sm_v + c * (kTile * 128), 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma_bf16(tmem_s, qd + k * 2, kd + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
-            umma_bf16(tmem_dp, dod + k * 2, vd + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) {
+              umma_bf16(tmem_s, qd + k * 2, kd + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tmem_dp, dod + k * 2, vd + k * 2, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+            }
           }
+          umma_commit(bar_sdp);
         }
-        umma_commit(bar_sdp);
-        if (!mbar_wait(bar_pds, static_cast<uint32_t>(it & 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_pds, static_cast<uint32_t>(it & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
-        // transposed products: A = P or dS read MN-major (K = query rows), B = dO or Q read MN-major
-        const uint64_t pt = make_smem_desc(sm_p, kTile * 128, 1024);
-        const uint64_t dst = make_smem_desc(sm_ds, kTile * 128, 1024);
-        const uint64_t dob = make_smem_desc(do_s, kTile * 128, 1024);
-        const uint64_t qb = make_smem_desc(q_s, kTile * 128, 1024);
+        if (elect_one_sync()) {
+          // transposed products: A = P or dS read MN-major (K = query rows), B = dO or Q read MN-major
+          const uint64_t pt = make_smem_desc(sm_p, kTile * 128, 1024);
+          const uint64_t dst = make_smem_desc(sm_ds, kTile * 128, 1024);
+          const uint64_t dob = make_smem_desc(do_s, kTile * 128, 1024);
+          const uint64_t qb = make_smem_desc(q_s, kTile * 128, 1024);
 #pragma unroll
-        for (int k = 0; k < kTile / 16; ++k) {
-          umma_bf16(tmem_dv, pt + k * (2048 >> 4), dob + k * (2048 >> 4), idesc_t, (it > 0 || k > 0) ? 1u : 0u);
-          umma_bf16(tmem_dk, dst + k * (2048 >> 4), qb + k * (2048 >> 4), idesc_t, (it > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kTile / 16; ++k) {
+            umma_bf16(tmem_dv, pt + k * (2048 >> 4), dob + k * (2048 >> 4), idesc_t, (it > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_dk, dst + k * (2048 >> 4), qb + k * (2048 >> 4), idesc_t, (it > 0 || k > 0) ? 1u : 0u);
+          }
+          // dQ_i = dS K_j: A = dS K-major in the key index, B = K_j read MN-major (K = key rows)
+          const uint64_t kb_ = make_smem_desc(sm_k, kTile * 128, 1024);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const uint64_t dsd = make_smem_desc(sm_ds + c * (kTile * 128), 16, 1024);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem_s, dsd + k * 2, kb_ + (c * 4 + k) * (2048 >> 4), idesc_q, (c > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_qe + 8 * st);
+          umma_commit(bar_dqf);
         }
-        // dQ_i = dS K_j: A = dS K-major in the key index, B = K_j read MN-major (K = key rows)
-        const uint64_t kb_ = make_smem_desc(sm_k, kTile * 128, 1024);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint64_t dsd = make_smem_desc(sm_ds + c * (kTile * 128), 16, 1024);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_s, dsd + k * 2, kb_ + (c * 4 + k) * (2048 >> 4), idesc_q, (c > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(bar_qe + 8 * st);
-        umma_commit(bar_dqf);
       }
-      if (ok) umma_commit(bar_fin);
-      if (!ok) atomicCAS(args.status, 0, kTimeoutMma);
+      if (ok && elect_one_sync()) umma_commit(bar_fin);
+      if (!ok && lane == 0) atomicCAS(args.status, 0, kTimeoutMma);
     }
   } else {
     const int row = threadIdx.x;

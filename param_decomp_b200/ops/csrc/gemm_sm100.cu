@@ -1360,12 +1360,9 @@ extern "C" int pd_gemm(const PdGemmCall* c, void* stream_v) {
   const bool grouped_pair = c->bgroup_of_mblock == nullptr || (c->cta_group == 2 && c->M % (2 * BM) == 0);
   const bool pair_ok = bn == 256 && grouped_pair && c->ag_world <= 1 && c->rs_world <= 1 &&
                        c->M >= 2 * BM && (c->max_ctas == 0 || c->max_ctas >= 2);
-  // Measured on the flagship shapes: pairs win 5-23% whenever an operand is MN-major (several TMA boxes
-  // per stage); with both operands K-major the single-CTA tiles are as fast or faster, except the
-  // epilogue-bound mask-gradient product at short K (+5%).
-  const bool pair = pair_ok && c->cta_group != 1 &&
-                    (c->cta_group == 2 ||
-                     (g_pair_default && (c->a_mn0 || c->b_mn0 || (c->epi == EPI_MASK_BWD && c->K0 <= 1024))));
+  // Pairs halve each CTA's share of the B tile (less shared-memory fill per MMA) and win on every flagship
+  // shape measured, K-major or MN-major operands alike.
+  const bool pair = pair_ok && c->cta_group != 1 && (c->cta_group == 2 || g_pair_default);
   const int b_box = pair ? bn / 2 : bn;
   if ((rc = encode_operand(&ta0, A0, c->M, c->K0, a_batch, BM))) return 1000 + rc;
   if ((rc = encode_operand(&tb0, B0, c->N, c->K0, b_batch, b_box))) return 2000 + rc;
