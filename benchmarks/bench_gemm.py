@@ -160,7 +160,9 @@ def main() -> None:
                     "setup_done": rel(v[1]), "teardown_start": rel(v[2]), "exit": rel(v[3]),
                     "mma_granted_committed": [[rel(v[16 + 2 * i]), rel(v[17 + 2 * i])] for i in range(8) if v[16 + 2 * i]],
                     "epi_full_drained": [[rel(v[80 + 2 * i]), rel(v[81 + 2 * i])] for i in range(8) if v[80 + 2 * i]],
-                    "producer_tile_issued": [rel(v[144 + i]) for i in range(8) if v[144 + i]]}}), flush=True)
+                    "producer_tile_issued": [rel(v[144 + i]) for i in range(8) if v[144 + i]],
+                    "mask_epilogue_units": [[rel(v[176 + 8 * u + k]) for k in range(7)] for u in range(8) if v[176 + 8 * u]],
+                    "mask_epilogue_tile_top": [rel(v[240 + i]) for i in range(8) if v[240 + i]]}}), flush=True)
             del fn
             lib = {}
             if args.library:

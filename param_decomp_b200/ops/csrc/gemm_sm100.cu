@@ -118,6 +118,8 @@ struct GemmArgs {
   // First global column of this product's mask columns in the Philox counter space (a rank that holds a
   // column slice of a site draws the same uniforms the whole site would); multiple of 8.
   unsigned int philox_col0;
+  // panel decode without a hardware divide: quotient by kGroupM * num_n = (umulhi(n, pg_mul) + n) >> pg_shift
+  unsigned int pg_mul, pg_shift;
   long long* timeline;  // diagnostic: CTA 0 writes clock64() stamps here (256 slots), nullptr = off
   int probe;        // timing probes (results are garbage): bit 0 = no operand loads, bit 1 = no MMAs, bit 2 (with bit 0) = no operand barriers
   int stage_limit;  // > 0: use only this many of the operand ring's stages (a tuning probe of pipeline depth)
@@ -162,6 +164,50 @@ __device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
     f[2 * i] = __uint_as_float(w[i] << 16);
     f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
+}
+
+// Packed fp32 pairs (`.f32x2`, one instruction for two lanes of arithmetic): the mask epilogue is bound by
+// instruction issue, so its per-element arithmetic runs two columns at a time. Each op rounds exactly like
+// its scalar form.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ f32x2 pk2u(uint32_t lo, uint32_t hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_bf16_2(f32x2 v) {  // (lo, hi) -> bf16x2 with lo in the low half
+  uint32_t r;
+  asm("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(v));
+  return r;
+}
+// bf16x2 word -> the two values as an fp32 pair
+__device__ __forceinline__ f32x2 unpack_bf16_2(uint32_t w) { return pk2u(w << 16, w & 0xFFFF0000u); }
+// One Philox word -> its two 16-bit uniforms (b + 0.5) / 65536 as an fp32 pair: the bits go to the top of the
+// mantissa of a float in [1, 2), and 2^-17 - 1 (exact in fp32) is added - the same values as `bits16_to_unit`.
+__device__ __forceinline__ f32x2 philox_word_to_unit2(uint32_t w) {
+  const uint32_t lo = 0x3F800000u | ((w & 0xFFFFu) << 7), hi = 0x3F800000u | ((w >> 9) & 0x007FFF80u);
+  constexpr float kBias = 0.5f / 65536.0f - 1.0f;
+  return add2(pk2u(lo, hi), pk2(kBias, kBias));
 }
 
 // Write 32 bf16 values (half of a 64-column box) of this thread's row into the swizzled staging box.
@@ -230,7 +276,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
 
   // Diagnostic timeline (CTA 0 only): slot 0 entry, 1 set-up done, 2 before teardown, 3 exit; MMA issuer
   // 16 + 2i / 17 + 2i = accumulator granted / tile i committed; first epilogue warp 80 + 2i / 81 + 2i =
-  // accumulator full seen / tile i drained; producer 144 + i = last load of tile i issued.
+  // accumulator full seen / tile i drained; producer 144 + i = last load of tile i issued; TMA-fed mask epilogue, first
+  // epilogue warp, unit u < 8: 176 + 8u .. 182 + 8u = operands landed, accumulator ready, values in registers,
+  // first half done, next operands requested, second half done, stores issued.
   auto stamp = [&](int slot) {
     if (args.timeline != nullptr && blockIdx.x == 0 && slot < 256) args.timeline[slot] = clock64();
   };
@@ -287,18 +335,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
 
   // Tile decode: batch / split outermost, then panels of kGroupM row blocks walked column by column.
   const long long tiles_per_mat = static_cast<long long>(num_m_t) * num_n;
+  // One matrix and no K split (every site product of a train step): the tile index is the panel index and fits
+  // 32 bits, the panel quotient is a multiply-high, a full panel's row / column split is a shift and a mask.
+  // The epilogue warps decode several tiles per unit of work, so this keeps divides off their critical path.
+  const bool single_mat = split == 1 && args.batch == 1;
   auto decode = [&](long long t, int& b, int& mb, int& nb, int& sp) {
-    const long long outer = t / tiles_per_mat;
-    const int pid = static_cast<int>(t % tiles_per_mat);
-    sp = static_cast<int>(outer % split);
-    b = static_cast<int>(outer / split);
-    const int per_group = kGroupM * num_n;
-    const int group = pid / per_group;
-    const int first_m = group * kGroupM;
+    uint32_t pid;
+    if (single_mat) {
+      pid = static_cast<uint32_t>(t);
+      sp = 0;
+      b = 0;
+    } else {
+      const long long outer = t / tiles_per_mat;
+      pid = static_cast<uint32_t>(t % tiles_per_mat);
+      sp = static_cast<int>(outer % split);
+      b = static_cast<int>(outer / split);
+    }
+    const uint32_t per_group = static_cast<uint32_t>(kGroupM * num_n);
+    const uint32_t group = (__umulhi(pid, args.pg_mul) + pid) >> args.pg_shift;
+    const int first_m = static_cast<int>(group) * kGroupM;
     const int gsz = min(num_m_t - first_m, kGroupM);
-    const int in_group = pid % per_group;
-    mb = (first_m + in_group % gsz) * CG + static_cast<int>(cta_rank);
-    nb = in_group / gsz;
+    const uint32_t in_group = pid - group * per_group;
+    uint32_t r_in, c_in;
+    if (gsz == kGroupM) {
+      r_in = in_group & static_cast<uint32_t>(kGroupM - 1);
+      c_in = in_group / static_cast<uint32_t>(kGroupM);
+    } else {
+      c_in = in_group / static_cast<uint32_t>(gsz);
+      r_in = in_group - c_in * static_cast<uint32_t>(gsz);
+    }
+    mb = (first_m + static_cast<int>(r_in)) * CG + static_cast<int>(cta_rank);
+    nb = static_cast<int>(c_in);
     if (args.ag_world > 1 && args.ag_mode == 0) {  // start with the row blocks this rank already holds
       const int per_rank = args.ag_rows / BM;
       mb = (mb + args.ag_rank * per_rank) % num_m;
@@ -638,21 +705,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
         }
         return t;
       };
-      auto issue_load = [&](long long t, int j, int slot) {  // lane 0 only
-        int b2, mb2, nb2, sp2;
-        decode(t, b2, mb2, nb2, sp2);
+      // Called by the whole warp (coordinates in uniform registers); one elected lane issues. `after_stores`:
+      // first wait until the TMA stores that still read the destination slot have finished reading.
+      auto issue_load = [&](long long t, int j, int slot, bool after_stores) {
+        int b2 = 0, mb2 = 0, nb2 = 0, sp2 = 0;
+        const bool real = t < num_tiles;  // past the last tile only the wait remains
+        if (real) decode(t, b2, mb2, nb2, sp2);
         const int crow = mb2 * BM + q * 32, col0 = nb2 * BN + j * 64;
         const uint32_t bar = bar_in + 8 * slot, box_a = ring + slot * (2 * kOutBoxBytes);
-        mbar_expect_tx(bar, in_bytes);
-        tma_load_3d(box_a, &tmCi, bar, col0, crow, 0);
-        if (want_h) tma_load_3d(box_a + kOutBoxBytes, &tmH, bar, col0, crow, 0);
+        if (elect_one_sync()) {
+          if (after_stores) tma_store_wait_read<0>();
+          if (real) {
+            mbar_expect_tx(bar, in_bytes);
+            tma_load_3d(box_a, &tmCi, bar, col0, crow, 0);
+            if (want_h) tma_load_3d(box_a + kOutBoxBytes, &tmH, bar, col0, crow, 0);
+          }
+        }
       };
       int acc = 0;
       uint32_t acc_phase = 0;
       uint32_t unit = 0;  // units consumed so far by this warp: slot = unit & 1, parity = (unit >> 1) & 1
       {
         const long long t0u = first_unit_from(tile0);
-        if (lane == 0 && t0u < num_tiles) issue_load(t0u, grp, 0);
+        issue_load(t0u, grp, 0, false);
       }
       bool failed = false;
       for (long long t = next_real_tile(tile0); t < num_tiles && !failed; t = next_real_tile(t + tstride)) {
@@ -670,6 +745,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           if (args.rowscale) rs = args.rowscale[row];
         }
         bool have_acc = false;
+        if (args.timeline != nullptr && warp == 2 && lane == 0 && unit < 16) stamp(240 + static_cast<int>(unit >> 1));
+        const long long t_next = first_unit_from(t + tstride);  // the tile whose first unit follows this tile's last
 #pragma unroll 1
         for (int j = grp; j < nboxes && !failed; j += 2) {
           const int col0 = nb * BN + j * 64;
@@ -681,6 +758,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             failed = true;
             break;
           }
+          const bool tl_on = args.timeline != nullptr && warp == 2 && lane == 0 && unit < 8;  // slots 176 .. 238
+          if (tl_on) stamp(176 + 8 * static_cast<int>(unit));  // operands of the unit have landed
           if (!have_acc) {
             if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
               if (args.status && lane == 0) atomicCAS(args.status, 0, kTimeoutEpilogue);
@@ -690,81 +769,94 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             tc_fence_after();
             have_acc = true;
           }
-#pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
+          if (tl_on) stamp(177 + 8 * static_cast<int>(unit));  // accumulator ready
+          const f32x2 rs2 = pk2(rs, rs), ndelta2 = pk2(-delta, -delta), one2 = pk2(1.0f, 1.0f), neg2 = pk2(-1.0f, -1.0f);
+          // One half (32 columns) of the unit: all shared-memory loads first, then the arithmetic of the four
+          // 8-column groups as plain code (four independent Philox chains the scheduler can interleave), then all
+          // stores. The loads and stores are `asm volatile` (they must stay behind the barrier waits), so they
+          // are kept in two blocks instead of fencing each group's arithmetic from the next.
+          auto do_half = [&](const int half) {
             const int c0 = col0 + 32 * half;
             uint32_t r[32];
             tmem_ld_32x32(tmem_row + j * 64 + 32 * half, r);
-            tmem_ld_wait();
+            uint4 ciq[4], hq[4];
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               const uint32_t off = lane * 128 + (((half * 4 + g) ^ (lane & 7)) << 4);
-              uint4 ciq, hq = make_uint4(0u, 0u, 0u, 0u);
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(ciq.x), "=r"(ciq.y), "=r"(ciq.z), "=r"(ciq.w) : "r"(box_a + off) : "memory");
+                           : "=r"(ciq[g].x), "=r"(ciq[g].y), "=r"(ciq[g].z), "=r"(ciq[g].w) : "r"(box_a + off) : "memory");
+              hq[g] = make_uint4(0u, 0u, 0u, 0u);
               if (want_h)
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(hq.x), "=r"(hq.y), "=r"(hq.z), "=r"(hq.w) : "r"(box_b + off) : "memory");
-              float v[8], cf[8], coef[8], dmdci[8];
+                             : "=r"(hq[g].x), "=r"(hq[g].y), "=r"(hq[g].z), "=r"(hq[g].w) : "r"(box_b + off) : "memory");
+            }
+            tmem_ld_wait();
+            uint32_t out_a[4][4], out_b[4][4];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = empty_k ? 0.0f : __uint_as_float(r[8 * g + i]);
-              unpack8(ciq, cf);
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t ciw[4] = {ciq[g].x, ciq[g].y, ciq[g].z, ciq[g].w}, hw[4] = {hq[g].x, hq[g].y, hq[g].z, hq[g].w};
+              f32x2 v2[4], coef2[4], dmdci2[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                v2[i] = empty_k ? pk2(0.0f, 0.0f) : pk2u(r[8 * g + 2 * i], r[8 * g + 2 * i + 1]);
               if (args.mask_mode == 0) {
-                float u[8];
-                philox_uniform8(philox_seed, args.stream, static_cast<uint32_t>(row) + args.row_offset,
-                                static_cast<uint32_t>((c0 >> 3) + g) + (args.philox_col0 >> 3), u);
+                const uint4 pr = Philox::run(
+                    make_uint4(static_cast<uint32_t>((c0 >> 3) + g) + (args.philox_col0 >> 3),
+                               static_cast<uint32_t>(row) + args.row_offset, args.stream, 0x5044u),
+                    make_uint2(static_cast<uint32_t>(philox_seed), static_cast<uint32_t>(philox_seed >> 32)));
+                const uint32_t pw[4] = {pr.x, pr.y, pr.z, pr.w};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float om = 1.0f - u[i];
-                  coef[i] = rs * (fmaf(cf[i], om, u[i]) - delta);
-                  dmdci[i] = rs * om;
+                for (int i = 0; i < 4; ++i) {
+                  const f32x2 u2 = philox_word_to_unit2(pw[i]);
+                  const f32x2 om2 = fma2(u2, neg2, one2);                       // 1 - u
+                  const f32x2 m2 = fma2(unpack_bf16_2(ciw[i]), om2, u2);        // ci (1 - u) + u
+                  coef2[i] = mul2(rs2, add2(m2, ndelta2));
+                  dmdci2[i] = mul2(rs2, om2);
                 }
               } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  coef[i] = rs * (cf[i] - delta);
-                  dmdci[i] = rs;
+                for (int i = 0; i < 4; ++i) {
+                  coef2[i] = mul2(rs2, add2(unpack_bf16_2(ciw[i]), ndelta2));
+                  dmdci2[i] = rs2;
                 }
               }
-              if constexpr (kBwd) {
-                if (want_h) {  // mask gradient replaces this thread's H values in box_b
-                  float hf[8];
-                  unpack8(hq, hf);
-                  uint4 pk;
-                  pk.x = pack_bf16(v[0] * hf[0] * dmdci[0], v[1] * hf[1] * dmdci[1]);
-                  pk.y = pack_bf16(v[2] * hf[2] * dmdci[2], v[3] * hf[3] * dmdci[3]);
-                  pk.z = pack_bf16(v[4] * hf[4] * dmdci[4], v[5] * hf[5] * dmdci[5]);
-                  pk.w = pack_bf16(v[6] * hf[6] * dmdci[6], v[7] * hf[7] * dmdci[7]);
-                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_b + off), "r"(pk.x), "r"(pk.y),
-                               "r"(pk.z), "r"(pk.w) : "memory");
-                }
-              } else {
-                if (h_out) {  // forward: the unmasked product leaves through box_b
-                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_b + off),
-                               "r"(pack_bf16(v[0], v[1])), "r"(pack_bf16(v[2], v[3])), "r"(pack_bf16(v[4], v[5])),
-                               "r"(pack_bf16(v[6], v[7])) : "memory");
-                }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                out_a[g][i] = pack_bf16_2(mul2(v2[i], coef2[i]));  // masked product
+                if constexpr (kBwd)
+                  out_b[g][i] = pack_bf16_2(mul2(mul2(v2[i], unpack_bf16_2(hw[i])), dmdci2[i]));  // mask gradient
+                else
+                  out_b[g][i] = pack_bf16_2(v2[i]);  // forward: the unmasked product
               }
-              // masked product replaces this thread's ci values in box_a
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_a + off),
-                           "r"(pack_bf16(v[0] * coef[0], v[1] * coef[1])), "r"(pack_bf16(v[2] * coef[2], v[3] * coef[3])),
-                           "r"(pack_bf16(v[4] * coef[4], v[5] * coef[5])), "r"(pack_bf16(v[6] * coef[6], v[7] * coef[7]))
-                           : "memory");
             }
-            if (half == 0 && lane == 0) {
-              // The other slot's boxes were handed to TMA stores one unit ago: once those have been read,
-              // request the NEXT unit's operands into it (they land while this unit's second half is computed).
-              tma_store_wait_read<0>();
-              long long tn = t;
-              int jn = j + 2;
-              if (!(jn < nboxes && nb * BN + jn * 64 < args.N)) {
-                tn = first_unit_from(t + tstride);
-                jn = grp;
-              }
-              if (tn < num_tiles) issue_load(tn, jn, slot ^ 1);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t off = lane * 128 + (((half * 4 + g) ^ (lane & 7)) << 4);
+              if (kBwd ? want_h : h_out)  // box_b: the mask gradient replaces H (backward), or H goes out (forward)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_b + off), "r"(out_b[g][0]),
+                             "r"(out_b[g][1]), "r"(out_b[g][2]), "r"(out_b[g][3]) : "memory");
+              // box_a: the masked product replaces this thread's ci values
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(box_a + off), "r"(out_a[g][0]),
+                           "r"(out_a[g][1]), "r"(out_a[g][2]), "r"(out_a[g][3]) : "memory");
             }
-            __syncwarp();  // (the next tcgen05.ld is warp-aligned)
+          };
+          do_half(0);
+          if (tl_on) stamp(179 + 8 * static_cast<int>(unit));  // first half computed
+          {
+            // The other slot's boxes were handed to TMA stores one unit ago: once those have been read,
+            // request the NEXT unit's operands into it (they land while this unit's second half is computed).
+            long long tn = t;
+            int jn = j + 2;
+            if (!(jn < nboxes && nb * BN + jn * 64 < args.N)) {
+              tn = t_next;
+              jn = grp;
+            }
+            issue_load(tn, jn, slot ^ 1, true);
           }
+          __syncwarp();
+          if (tl_on) stamp(180 + 8 * static_cast<int>(unit));  // previous stores read, next operands requested
+          do_half(1);
+          if (tl_on) stamp(181 + 8 * static_cast<int>(unit));  // second half computed
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -776,6 +868,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             }
             tma_store_commit();
           }
+          if (tl_on) stamp(182 + 8 * static_cast<int>(unit));  // stores issued
           ++unit;
         }
         if (failed) break;
@@ -1196,6 +1289,13 @@ static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& b0, const CUten
   grid -= grid % CG;
   if (grid <= 0) return 0;
   GemmArgs launch_args = args;
+  {  // magic numbers of the panel quotient (valid for dividends below 2^31)
+    const unsigned long long d = static_cast<unsigned long long>(kGroupM) * ((args.N + BN - 1) / BN);
+    unsigned int sh = 0;
+    while ((1ull << sh) < d) ++sh;
+    launch_args.pg_shift = sh;
+    launch_args.pg_mul = static_cast<unsigned int>(((1ull << 32) * ((1ull << sh) - d)) / d + 1);
+  }
   if (args.ag_world > 1) {
     // every CTA must be resident (producers wait on blocks that gather CTAs deliver): one per SM
     if (max_ctas > 0 && max_ctas < g_num_sms) return kBadArgument;
