@@ -120,6 +120,7 @@ def time_case(fn, iters: int, warmup: int = 3) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", choices=CASES, default=None)
+    ap.add_argument("--shape", type=str, default=None, help="d_in,d_out of the site (default with --case: 768,768)")
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--c", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=10)
@@ -142,7 +143,9 @@ def main() -> None:
     nv.lib().pd_gemm_set_stage_limit(args.stages)
     nv.lib().pd_gemm_set_probe(args.probe)
     cases = CASES if args.case is None else (args.case,)
-    if args.case is not None:
+    if args.shape is not None:
+        shapes = [tuple(int(v) for v in args.shape.split(","))]
+    elif args.case is not None:
         shapes = shapes[:1]
     for din, dout in shapes:
         for case in cases:
