@@ -227,8 +227,10 @@ def main() -> None:
     if args.profile_range:
         torch.cuda.profiler.start()
     e0.record()
+    host_t0 = time.perf_counter()
     for b in dev_batches:
         step_fn(b)
+    host_issue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps  # host time to issue a step (no wait on the device)
     e1.record()
     if args.profile_range:
         torch.cuda.synchronize()
@@ -284,6 +286,7 @@ def main() -> None:
             "e2e": {"value": e2e_tokens_per_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4, "last_loss": loss_host},
             "gpu_launches": launches,
+            "host_issue_ms_per_step": round(host_issue_ms, 3),
         }))
     step_fn.release()  # the recorded graph holds NCCL work: it must go before the process group does
     topo.shutdown()

@@ -148,7 +148,7 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
             m = None
             if sm.mask is not None:
                 flat = sm.mask.reshape(-1, sm.mask.shape[-1])  # [tokens, k*c]
-                m = flat.reshape(flat.shape[0], -1, c)[tok, slot]
+                m = flat.reshape(flat.shape[0], flat.shape[1] // c, c)[tok, slot]
             d = None if sm.delta is None else sm.delta.reshape(-1, 1)[tok]
             r = None if sm.route is None else sm.route.reshape(-1)[tok]
             out[rows] = site_forward(xe, V[e], U[e], W[e], SiteMask(mask=m, delta=d, route=r))
@@ -227,7 +227,8 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
             if t is None:
                 return None
             flat = t.reshape(-1, t.shape[-1]) if width else t.reshape(-1)
-            vals = flat.reshape(flat.shape[0], -1, c)[token_of_job, slot_of_job] if width else flat[token_of_job]
+            # (explicit middle extent: a rank may receive no job at all, and -1 cannot be inferred from 0 elements)
+            vals = flat.reshape(flat.shape[0], flat.shape[1] // c, c)[token_of_job, slot_of_job] if width else flat[token_of_job]
             out = vals.new_zeros(layout.n_rows, *vals.shape[1:])
             return out.index_copy(0, layout.pos, vals)
 

@@ -35,6 +35,16 @@ from torch import Tensor
 from param_decomp_b200.core.masking import SiteMask
 
 
+def _tie(y: Tensor, shipped: list[Tensor]) -> Tensor:
+    """`y` with an autograd edge to every received tensor. The adjoint of each exchange is itself an exchange that
+    every rank must enter; a rank whose local expert computation happens not to depend on one of its received
+    tensors (it received no job at all, or a site ignores an input) would otherwise skip that exchange in the
+    backward pass and leave the other ranks waiting in it. Adds exact zeros."""
+    for t in shipped:
+        y = y + (t.sum() * 0.0).to(y.dtype)
+    return y
+
+
 def padded_experts(n_experts: int, world: int) -> int:
     return (n_experts + world - 1) // world * world
 
@@ -200,8 +210,13 @@ class ExpertParallel:
         dist.all_to_all_single(recv, send, group=self.group)
         send_l, recv_l = send.tolist(), recv.tolist()
 
+        shipped: list[Tensor] = []  # received tensors whose adjoint is a collective (see `_tie`)
+
         def ship(rows: Tensor) -> Tensor:
-            return _AllToAll.apply(rows[order], send_l, recv_l, self.group)
+            out = _AllToAll.apply(rows[order], send_l, recv_l, self.group)
+            if out.requires_grad:
+                shipped.append(out)
+            return out
 
         x_recv = ship(xt[token_of_job])
         e_recv = _AllToAll.apply((expert_of_job % self.e_loc)[order], send_l, recv_l, self.group)
@@ -218,7 +233,7 @@ class ExpertParallel:
                 m = d = r = None
                 if sm.mask is not None:
                     flat = sm.mask.reshape(-1, sm.mask.shape[-1])
-                    m = ship(flat.reshape(flat.shape[0], -1, c)[token_of_job, slot_of_job])
+                    m = ship(flat.reshape(flat.shape[0], flat.shape[1] // c, c)[token_of_job, slot_of_job])
                 if sm.delta is not None:
                     d = ship(sm.delta.reshape(-1, 1)[token_of_job])
                 if sm.route is not None:
@@ -227,6 +242,7 @@ class ExpertParallel:
         Jr = x_recv.shape[0]
         ar = torch.arange(Jr, device=xt.device)
         y_recv = self._local(model, layer, x_recv, e_recv, weights, job_masks if masks is not None else None, ar)
+        y_recv = _tie(y_recv, shipped)
         y_sorted = _AllToAll.apply(y_recv, recv_l, send_l, self.group)
         inv = torch.empty_like(order)
         inv[order] = torch.arange(J, device=order.device)
@@ -297,9 +313,13 @@ class ExpertParallel:
             extra = (-cols) % per16
             return (torch.nn.functional.pad(rows, (0, extra)) if extra else rows), cols
 
+        shipped: list[Tensor] = []
+
         def ship(rows: Tensor, gather: Tensor | None) -> Tensor:
             rows, cols = pad16(rows)
             out = _P2PExchange.apply(rows, p2p, gather, dest, dest_row, R, src_rank_of_row, src_job, cap)
+            if out.requires_grad:
+                shipped.append(out)
             return out[:, :cols]
 
         x_recv = ship(xt, token_of_job)  # the router's gather is applied by the kernel
@@ -314,7 +334,7 @@ class ExpertParallel:
                 m = d = r = None
                 if sm.mask is not None:
                     flat = sm.mask.reshape(-1, sm.mask.shape[-1])
-                    m = ship(flat.reshape(flat.shape[0], -1, c)[token_of_job, slot_of_job], None)
+                    m = ship(flat.reshape(flat.shape[0], flat.shape[1] // c, c)[token_of_job, slot_of_job], None)
                 if sm.delta is not None:
                     d = ship(sm.delta.reshape(-1, 1), token_of_job)
                 if sm.route is not None:
@@ -322,6 +342,7 @@ class ExpertParallel:
                 job_masks[name] = SiteMask(mask=m, delta=d, route=r)
         ar = torch.arange(R, device=xt.device)
         y_recv = self._local(model, layer, x_recv, e_recv, weights, job_masks if masks is not None else None, ar)
+        y_recv = _tie(y_recv, shipped)
         y_rows, cols = pad16(y_recv)
         y = _P2PExchange.apply(y_rows, p2p, None, src_rank_of_row, src_job, J, dest, dest_row, cap)
         return y[:, :cols]
@@ -358,7 +379,7 @@ class ExpertParallel:
                 if sm.mask is not None:
                     flat = share(sm.mask.reshape(-1, sm.mask.shape[-1]))
                     keep_alive = keep_alive + flat.sum() * 0
-                    m = flat.reshape(flat.shape[0], -1, c)[token_of_job[idx], slot_of_job[idx]]
+                    m = flat.reshape(flat.shape[0], flat.shape[1] // c, c)[token_of_job[idx], slot_of_job[idx]]
                 if sm.delta is not None:
                     dl = share(sm.delta.reshape(-1, 1))
                     keep_alive = keep_alive + dl.sum() * 0

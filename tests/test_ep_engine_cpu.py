@@ -20,7 +20,7 @@ STEPS = 4
 SPLIT_ID, SINGLE_ID = "p-0000aaaa", "p-0000bbbb"
 
 
-def _cfg(tp: int, mode: str = "allreduce") -> LMExperimentConfig:
+def _cfg(tp: int, mode: str = "allreduce", n_experts: int = 5, k: int = 2, batch: int = 4) -> LMExperimentConfig:
     c = copy.deepcopy(ge.SMOKE_CONFIG)
     c["runtime"]["backend"] = "eager_torch"
     c["runtime"]["mesh"] = {"replicate": 1, "fsdp": 1, "tp": tp}
@@ -28,12 +28,12 @@ def _cfg(tp: int, mode: str = "allreduce") -> LMExperimentConfig:
     c["target"]["weights_dtype"] = "float32"
     c["target"]["attention_implementation"] = "xla"
     c["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 16,
-                                   "vocab_size": 100, "n_experts": 5, "experts_per_token": 2}  # 5 experts: one dummy
+                                   "vocab_size": 100, "n_experts": n_experts, "experts_per_token": k}  # 5 experts on 2 ranks: one dummy
     c["decomposition"]["sites"] = {"kind": "moe", "layers": {"kind": "all"},
                                    "cs": {"q": 8, "experts_gate": 20, "experts_up": 20, "experts_down": 20}}
     c["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [16]}
     c["data"]["seq_len"] = 8
-    c["pd"]["batch_size"] = 4
+    c["pd"]["batch_size"] = batch
     c["pd"]["steps"] = STEPS
     c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "periodic", "save_every": 2, "retention": {"kind": "keep_all"}}}
     c["eval"] = None
@@ -56,11 +56,11 @@ def _train(cfg, root: Path, run_id: str, max_steps=None):
     return res, states[0]
 
 
-def _worker(rank: int, world: int, port: int, root: str, mode: str, out):
+def _worker(rank: int, world: int, port: int, root: str, mode: str, out, n_experts: int = 5, k: int = 2, batch: int = 4):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
     torch.manual_seed(0)
-    res, state = _train(_cfg(world, mode), Path(root), SPLIT_ID)
+    res, state = _train(_cfg(world, mode, n_experts, k, batch), Path(root), SPLIT_ID)
     shard = state.expert_shard
     assert shard is not None and shard.world == world
     local = {n: p.detach().clone() for n, p in state.components.named_parameters()}
@@ -69,18 +69,21 @@ def _worker(rank: int, world: int, port: int, root: str, mode: str, out):
     assert not dist.is_initialized()  # train_lm tears its own process group down
 
 
-@pytest.mark.parametrize("mode", ["allreduce", "all_to_all"])
-def test_expert_split_engine_matches_single_process(mode):
+@pytest.mark.parametrize("mode,n_experts,k,world,batch", [("allreduce", 5, 2, 2, 4), ("all_to_all", 5, 2, 2, 4),
+                                                         ("all_to_all", 4, 2, 3, 6)])
+def test_expert_split_engine_matches_single_process(mode, n_experts, k, world, batch):
     """`allreduce`: tokens replicated over the pair; `all_to_all`: each rank takes half of the batch and jobs
-    travel to their expert's owner (`target.expert_implementation: all_to_all`)."""
+    travel to their expert's owner (`target.expert_implementation: all_to_all`). With four experts on three ranks (padded to six, two per rank) the
+    last rank owns only a padding expert and receives no job at all (42 experts on 8 ranks do the same to the
+    last rank)."""
     from safetensors import safe_open
 
     with tempfile.TemporaryDirectory() as root:
-        world, port = 2, _free_port()
+        port = _free_port()
         out = mp.Manager().dict()
-        mp.spawn(_worker, args=(world, port, root, mode, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, root, mode, out, n_experts, k, batch), nprocs=world, join=True)
 
-        res, ref = _train(_cfg(1), Path(root), SINGLE_ID)
+        res, ref = _train(_cfg(1, "allreduce", n_experts, k, batch), Path(root), SINGLE_ID)
         ref_params = dict(ref.components.named_parameters())
         for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss",
                   "grad_norm/components", "grad_norm/ci_fn"):
