@@ -102,6 +102,35 @@ def test_mask_epilogues_match_philox_reference(nv):
     assert rel(dci32, dci0 + want_dci) < 1e-5 and rel(dcib, want_dci) < 5e-3
 
 
+@pytest.mark.parametrize("M,C", [(640, 512), (1000, 776), (300, 264)])
+def test_tma_fed_mask_epilogue_equals_plain_load_form(nv, M, C):
+    """`epi_tma=2` (ci / H boxes in by TMA, results written in place, out by TMA, packed arithmetic) and `epi_tma=1`
+    (per-thread global loads, scalar arithmetic) do the same roundings in the same order: identical bits, on shapes
+    with ragged last row blocks and a ragged last column box."""
+    torch.manual_seed(5)
+    D, Dout = 192, 256
+    x = torch.randn(M, D, device="cuda", dtype=bf)
+    V = (torch.randn(D, C, device="cuda") / D**0.5).to(bf)
+    U = (torch.randn(C, Dout, device="cuda") / C**0.5).to(bf)
+    ci = torch.rand(M, C, device="cuda").to(bf)
+    delta = torch.rand(M, device="cuda")
+    rs = (torch.rand(M, device="cuda") > 0.3).float()
+    dy = torch.randn(M, Dout, device="cuda", dtype=bf)
+    outs = {}
+    for form in (1, 2):
+        A, H = torch.zeros(M, C, device="cuda", dtype=bf), torch.zeros(M, C, device="cuda", dtype=bf)
+        nv.gemm(x, V, A, b_mn=True, epi=nv.EPI_MASK_FWD, out1=H, ci=ci, delta=delta, rowscale=rs, seed=99,
+                rng_stream=3, row_offset=17, epi_tma=form)
+        dH, dci = torch.zeros(M, C, device="cuda", dtype=bf), torch.zeros(M, C, device="cuda", dtype=bf)
+        nv.gemm(dy, U, dH, epi=nv.EPI_MASK_BWD, ci=ci, h=H, delta=delta, rowscale=rs, dci=dci, seed=99, rng_stream=3,
+                row_offset=17, epi_tma=form)
+        outs[form] = (A, H, dH, dci)
+    _done(nv)
+    for a, b, name in zip(outs[1], outs[2], ("A", "H", "dH", "dci")):
+        assert torch.equal(a, b), (name, float((a.float() - b.float()).abs().max()))
+    assert float(outs[2][0].float().abs().sum()) > 0 and float(outs[2][3].float().abs().sum()) > 0
+
+
 def test_mask_epilogue_column_slice_draws_the_sites_uniforms(nv):
     """A product over a column slice of a site (tensor-parallel components) with `philox_col0` set to the
     slice's first column reproduces the corresponding columns of the whole-site product, forward and
