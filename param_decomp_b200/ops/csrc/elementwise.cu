@@ -475,7 +475,7 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
     norm = normalize ? 1.f + gamma2 : 1.f;
   }
   // Same tiling as the forward: a thread owns 8 columns (its dcol values stay in registers) and walks
-  // rows with the grid's row stride, two rows in flight per iteration.
+  // rows with the grid's row stride, four rows in flight per iteration.
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int col = (blockIdx.x * 32 + cg) * 8;
   if (col >= C) return;
@@ -484,6 +484,7 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
   const float dc[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
   const float k2 = norm * 2.f * gamma2;
   const long long stride = static_cast<long long>(gridDim.y) * 8;
+  // Branch-free per element (the three regimes of the leaky clamp are selects, not divergent paths).
   auto one = [&](long long r, const uint4 q, const uint4 gq) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
     const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gq);
@@ -496,13 +497,12 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const float xv = x[e];
-        float lg = 0.f, u, du;
-        if (xv > 1.f) { u = 1.f + alpha * (xv - 1.f); du = alpha; }
-        else if (xv > 0.f) { u = xv; du = 1.f; lg = gg[e]; }
-        else { u = 0.f; du = 0.f; lg = gg[e] < 0.f ? alpha * gg[e] : 0.f; }
-        const float den = u * u + gamma2;
-        const float dpsi = __fdividef(k2 * u, den * den);
-        out[e] = lg + dc[2 * k + e] * dpsi * du;
+        const bool above = xv > 1.f, inside = xv > 0.f;
+        const float u = above ? fmaf(alpha, xv - 1.f, 1.f) : fmaxf(xv, 0.f);
+        const float du = above ? alpha : (inside ? 1.f : 0.f);
+        const float lg = above ? 0.f : (inside ? gg[e] : alpha * fminf(gg[e], 0.f));
+        const float den = fmaf(u, u, gamma2);
+        out[e] = fmaf(dc[2 * k + e] * du, __fdividef(k2 * u, den * den), lg);
       }
       o[k] = __floats2bfloat162_rn(out[0], out[1]);
     }
@@ -510,15 +510,17 @@ __global__ void ci_squash_activity_bwd_kernel(const __nv_bfloat16* __restrict__ 
   };
   const uint4 zero = make_uint4(0, 0, 0, 0);
   long long r = static_cast<long long>(blockIdx.y) * 8 + rl;
-  for (; r + stride < rows; r += 2 * stride) {
-    const uint4 qa = *reinterpret_cast<const uint4*>(pre + r * C + col);
-    const uint4 qb = *reinterpret_cast<const uint4*>(pre + (r + stride) * C + col);
-    const uint4 ga = dlower ? *reinterpret_cast<const uint4*>(dlower + r * C + col) : zero;
-    const uint4 gb = dlower ? *reinterpret_cast<const uint4*>(dlower + (r + stride) * C + col) : zero;
-    one(r, qa, ga);
-    one(r + stride, qb, gb);
+  // four rows in flight per thread: eight 16-byte loads issued before the first is consumed
+  for (; r + 3 * stride < rows; r += 4 * stride) {
+    uint4 q[4], g[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = *reinterpret_cast<const uint4*>(pre + (r + j * stride) * C + col);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) g[j] = dlower ? *reinterpret_cast<const uint4*>(dlower + (r + j * stride) * C + col) : zero;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) one(r + j * stride, q[j], g[j]);
   }
-  if (r < rows) {
+  for (; r < rows; r += stride) {
     const uint4 qa = *reinterpret_cast<const uint4*>(pre + r * C + col);
     const uint4 ga = dlower ? *reinterpret_cast<const uint4*>(dlower + r * C + col) : zero;
     one(r, qa, ga);
