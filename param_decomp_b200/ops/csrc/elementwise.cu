@@ -196,7 +196,8 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
 
 // ---- rotary embedding (rotate-half form), in place on [rows = B*T, heads, hd] -------------------
 // cos/sin [T, hd/2] fp32; `inverse` applies the transpose rotation (the backward).
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+// `src` may equal `dst` (in place): every thread reads its pair before it writes it.
+__global__ void rope_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, const float* __restrict__ cs,
                             const float* __restrict__ sn, long long rows, int T, int heads, int hd,
                             int inverse) {
   const int half = hd >> 1;
@@ -209,15 +210,16 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
     const int t = static_cast<int>(row % T);
     const float c = cs[t * half + j];
     const float s = inverse ? -sn[t * half + j] : sn[t * half + j];
-    __nv_bfloat16* p = x + rh * hd;
-    const float a = __bfloat162float(p[j]), b = __bfloat162float(p[j + half]);
+    const __nv_bfloat16* q = src + rh * hd;
+    __nv_bfloat16* p = dst + rh * hd;
+    const float a = __bfloat162float(q[j]), b = __bfloat162float(q[j + half]);
     p[j] = __float2bfloat16(a * c - b * s);
     p[j + half] = __float2bfloat16(b * c + a * s);
   }
 }
 
 // eight rotation pairs per thread (16-byte loads of the low and the high half); needs hd % 16 == 0
-__global__ void rope_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+__global__ void rope_vec_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, const float* __restrict__ cs,
                                 const float* __restrict__ sn, long long rows, int T, int heads, int hd,
                                 int inverse) {
   const int half = hd >> 1, groups = half >> 3;
@@ -227,8 +229,9 @@ __global__ void rope_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __re
     const int g = static_cast<int>(i % groups);
     const long long rh = i / groups;
     const int t = static_cast<int>((rh / heads) % T);
-    __nv_bfloat16* p = x + rh * hd + 8 * g;
-    const uint4 lo = *reinterpret_cast<const uint4*>(p), hi = *reinterpret_cast<const uint4*>(p + half);
+    const __nv_bfloat16* q = src + rh * hd + 8 * g;
+    __nv_bfloat16* p = dst + rh * hd + 8 * g;
+    const uint4 lo = *reinterpret_cast<const uint4*>(q), hi = *reinterpret_cast<const uint4*>(q + half);
     const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
     const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
     const float4* c4 = reinterpret_cast<const float4*>(cs + static_cast<long long>(t) * half + 8 * g);
@@ -934,17 +937,22 @@ extern "C" int pd_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
       static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<__nv_bfloat16*>(dx), rows, d);
   return PD_CHECK_LAUNCH();
 }
-extern "C" int pd_rope(void* x, const float* cs, const float* sn, long long rows, int T, int heads, int hd,
-                       int inverse, void* stream) {
-  if (hd % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(cs) & 15) == 0 &&
-      (reinterpret_cast<uintptr_t>(sn) & 15) == 0) {
+// Rotary embedding from `src` into `dst` (the same pointer rotates in place).
+extern "C" int pd_rope_to(const void* src, void* dst, const float* cs, const float* sn, long long rows, int T,
+                          int heads, int hd, int inverse, void* stream) {
+  if (hd % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(cs) & 15) == 0 && (reinterpret_cast<uintptr_t>(sn) & 15) == 0) {
     rope_vec_kernel<<<blocks_for(rows * heads * (hd / 16), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16*>(x), cs, sn, rows, T, heads, hd, inverse);
+        static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), cs, sn, rows, T, heads, hd, inverse);
     return PD_CHECK_LAUNCH();
   }
   rope_kernel<<<blocks_for(rows * heads * (hd / 2), kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(x), cs, sn, rows, T, heads, hd, inverse);
+      static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), cs, sn, rows, T, heads, hd, inverse);
   return PD_CHECK_LAUNCH();
+}
+extern "C" int pd_rope(void* x, const float* cs, const float* sn, long long rows, int T, int heads, int hd,
+                       int inverse, void* stream) {
+  return pd_rope_to(x, x, cs, sn, rows, T, heads, hd, inverse, stream);
 }
 extern "C" int pd_swiglu_fwd(const void* gate, const void* up, void* out, long long n, void* stream) {
   if (n % 8 != 0) return 5;

@@ -24,6 +24,7 @@ def _lib():
         lib.pd_rmsnorm_fwd.argtypes = [P, P, P, P, LL, I, F, P]
         lib.pd_rmsnorm_bwd.argtypes = [P, P, P, P, P, LL, I, P]
         lib.pd_rope.argtypes = [P, P, P, LL, I, I, I, I, P]
+        lib.pd_rope_to.argtypes = [P, P, P, P, LL, I, I, I, I, P]
         lib.pd_swiglu_fwd.argtypes = [P, P, P, LL, P]
         lib.pd_swiglu_bwd.argtypes = [P, P, P, P, P, LL, P]
         lib.pd_rowscale.argtypes = [P, P, P, LL, I, P]
@@ -134,8 +135,10 @@ class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, cos_half: Tensor, sin_half: Tensor) -> Tensor:  # type: ignore[override]
         B, T, H, hd = x.shape
-        y = x.contiguous().clone()
-        _check(_lib().pd_rope(y.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr(), B * T, T, H, hd, 0, _s()), "rope")
+        x = x.contiguous()
+        y = torch.empty_like(x)  # rotated straight from `x` into `y`: no copy first
+        _check(_lib().pd_rope_to(x.data_ptr(), y.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr(), B * T, T, H, hd, 0,
+                                 _s()), "rope")
         ctx.save_for_backward(cos_half, sin_half)
         return y
 
@@ -143,8 +146,10 @@ class _Rope(torch.autograd.Function):
     def backward(ctx, dy: Tensor):  # type: ignore[override]
         cos_half, sin_half = ctx.saved_tensors
         B, T, H, hd = dy.shape
-        dx = dy.contiguous().clone()
-        _check(_lib().pd_rope(dx.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr(), B * T, T, H, hd, 1, _s()), "rope_bwd")
+        dy = dy.contiguous()
+        dx = torch.empty_like(dy)
+        _check(_lib().pd_rope_to(dy.data_ptr(), dx.data_ptr(), cos_half.data_ptr(), sin_half.data_ptr(), B * T, T, H, hd, 1,
+                                 _s()), "rope_bwd")
         return dx, None, None
 
 
