@@ -343,6 +343,38 @@ def _tp_engine_worker(rank: int, world: int, port: int, fsdp: int, out):
     out[rank] = dict(res.last_metrics)
 
 
+def _dp_engine_worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from param_decomp_b200.experiments.lm.training import train_lm
+    from param_decomp_b200.ops import native
+
+    cfg = _dense_engine_cfg(1, fsdp=world)
+    cfg = cfg.model_copy(update={"pd": cfg.pd.model_copy(update={"steps": 7})})  # 3 eager + recording + replays
+    res = train_lm(cfg, None, device="cuda")
+    torch.cuda.synchronize()
+    native.check_status()
+    out[rank] = dict(res.last_metrics)
+
+
+def test_data_parallel_recorded_step_matches_one_gpu():
+    """One-versus-N loss invariance of the flagship layout: two data-parallel ranks (`runtime.sharding: owner`, the
+    fused reduce-scatter + AdamW + all-gather kernel, the step replayed from its CUDA graph after the eager
+    warm-up) end at the same losses as the same run on one GPU."""
+    _need_two_gpus()
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    world, port = 2, _free_port()
+    out = mp.Manager().dict()
+    mp.spawn(_dp_engine_worker, args=(world, port, out), nprocs=world, join=True)
+    cfg = _dense_engine_cfg(1)
+    cfg = cfg.model_copy(update={"pd": cfg.pd.model_copy(update={"steps": 7})})
+    ref = train_lm(cfg, None, device="cuda").last_metrics
+    for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss"):
+        got, want = sum(out[r]["train/" + k] for r in range(world)) / world, ref["train/" + k]  # (batch shards)
+        assert abs(got - want) <= 2e-2 * abs(want) + 1e-6, (k, got, want)
+
+
 def test_component_split_engine_two_gpus():
     """The engine with every site's component axis split over two GPUs (fused backend: the mask kernels draw
     their slice of the site's uniforms, partial site outputs are summed over the pair) against one GPU."""
