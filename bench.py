@@ -130,7 +130,7 @@ def main() -> None:
     from param_decomp_b200.config.run import HsdpMeshShape
     from param_decomp_b200.core.objective import build_objective
     from param_decomp_b200.core.run import init_train_state
-    from param_decomp_b200.core.train import StepContext, train_step
+    from param_decomp_b200.core.train import StepContext
     from param_decomp_b200.experiments.lm.build import build_lm_run
     from param_decomp_b200.ops import native
     from param_decomp_b200.parallel import topology

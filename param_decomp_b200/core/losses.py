@@ -18,7 +18,7 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from param_decomp_b200.core.components import ComponentStacks, SelectedCI, SiteSpec
+from param_decomp_b200.core.components import ComponentStacks, SelectedCI
 from param_decomp_b200.formats.nonlinearity import Neurons
 
 # ---- output comparisons ------------------------------------------------------------------------

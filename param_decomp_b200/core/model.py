@@ -15,7 +15,7 @@ from typing import Any, Protocol, runtime_checkable
 import torch
 from torch import Tensor
 
-from param_decomp_b200.core.components import ComponentStacks, ComputeWeights, SiteSpec
+from param_decomp_b200.core.components import ComputeWeights, SiteSpec
 from param_decomp_b200.core.masking import Masks
 
 

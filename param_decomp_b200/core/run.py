@@ -43,7 +43,7 @@ from param_decomp_b200.core.model import DecomposedModel
 from param_decomp_b200.core.objective import NontargetObjective, PDObjective, build_objective
 from param_decomp_b200.core.optim import build_group_optimizer
 from param_decomp_b200.core.rng import StepKey
-from param_decomp_b200.core.train import DataCollectives, StepContext, TrainState, faithfulness_warmup, train_step
+from param_decomp_b200.core.train import DataCollectives, StepContext, TrainState, faithfulness_warmup
 
 
 class Evaluation(Protocol):

@@ -15,7 +15,7 @@ import torch
 from torch import nn
 
 from param_decomp_b200.config import experiments as X
-from param_decomp_b200.core.ci_fn.mlp import GlobalMLPCIFn, LayerwiseMLPCIFn
+from param_decomp_b200.core.ci_fn.mlp import LayerwiseMLPCIFn
 from param_decomp_b200.core.components import SiteSpec
 from param_decomp_b200.data.synthetic import ZipfTokenSource
 from param_decomp_b200.models import transformer as tf

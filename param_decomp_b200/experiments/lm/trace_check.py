@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import argparse
 from pathlib import Path
-from typing import Any
 
 from param_decomp_b200.config.experiments import LMExperimentConfig
 

@@ -8,7 +8,6 @@ from __future__ import annotations
 import os
 from pathlib import Path
 
-import torch
 
 from param_decomp_b200.config.experiments import LMExperimentConfig, LMTargetedExperimentConfig
 from param_decomp_b200.core.metrics import MetricsSink, device_peak_flops, get_logger, mint_run_id, pin_launch_config, run_dir_for

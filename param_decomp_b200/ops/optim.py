@@ -5,7 +5,6 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-from param_decomp_b200.ops import native as nv
 import ctypes as C
 
 from param_decomp_b200.ops.elementwise import _check, _lib, _s

@@ -26,7 +26,7 @@ core/placement.py:1040-1048,1552-1566).
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
