@@ -49,10 +49,28 @@ def warn_inert_options(cfg, log) -> None:
 def check_runtime_supported(cfg) -> None:
     """Refuse, rather than silently ignore, runtime options this engine does not act on."""
     if cfg.runtime.sequence_sharding != "replicate":
-        raise NotImplementedError(
-            "runtime.sequence_sharding=sequence_parallel (position-sharded residual stream between sublayers, "
-            "param_decomp/core/placement.py:273-287) is not implemented: the tp axis sums site / expert outputs "
-            "with an all-reduce and keeps the residual stream whole on every rank")
+        family = getattr(getattr(cfg.target.spec, "arch", None), "family", None)
+        kind = getattr(cfg.decomposition.sites, "kind", "")
+        if family in ("moe", "qwen35_moe") or kind in ("moe", "qwen36_moe"):
+            raise NotImplementedError(
+                "runtime.sequence_sharding=sequence_parallel (position-sharded residual stream between blocks, "
+                "param_decomp/core/placement.py:273-287) is built for dense transformer targets whose component "
+                "axis is split over tp; on mixture-of-experts targets the tp axis splits experts and keeps the "
+                "residual stream whole on every rank")
+
+
+def apply_sequence_sharding(cfg, model, topo, log) -> None:
+    """`sequence_parallel`: masked passes of a dense target carry the residual position-sharded over the tp group."""
+    if cfg.runtime.sequence_sharding == "replicate":
+        return
+    if getattr(model, "component_group", None) is None:
+        log.info("runtime.sequence_sharding=sequence_parallel has no effect without a tp axis (tp = %d)", topo.tp_world)
+        return
+    assert cfg.data.seq_len % topo.tp_world == 0, \
+        f"sequence_parallel: seq_len {cfg.data.seq_len} must be a multiple of the tp axis ({topo.tp_world})"
+    model.sequence_parallel = True
+    log.info("sequence-parallel residual: masked passes keep [batch, %d / %d, d_model] per rank between blocks",
+             cfg.data.seq_len, topo.tp_world)
 
 
 def expert_mode_of(cfg) -> str:
@@ -78,6 +96,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     warn_inert_options(cfg, log)
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
                        expert_mode=mode)
+    apply_sequence_sharding(cfg, run.model, topo, log)
     collectives = topo.collectives()
     from param_decomp_b200.parallel import layout as layout_mod
 
@@ -144,6 +163,7 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
     log = get_logger(topo.rank)
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
                        expert_mode=mode)
+    apply_sequence_sharding(cfg, run.model, topo, log)
     pool = PromptPool.build(cfg.prompts, run.arch.vocab_size, data_root, cfg.pd.seed, encode=encode)
     n_target_terms = len(build_objective(cfg.pd).recon)
     nontarget = build_nontarget_objective(cfg.nontarget, first_index=n_target_terms)

@@ -269,7 +269,17 @@ class TransformerDecomposedModel:
                 captures[name + ".out"] = y
             return y
 
+        # Sequence-parallel masked pass: `resid` is this rank's `[B, T / W, d]` positions. Norms and residual adds
+        # run on the shard; each sublayer gathers its normed input to the whole sequence, and takes its own
+        # positions of the sublayer's (group-summed) output back.
+        sp = aux.get("sequence_group")
+        if sp is not None:
+            from param_decomp_b200.parallel.group_ops import gather_sequence, slice_sequence
+
+            T = T * aux["sequence_world"]
         x = self._norm(resid, self.w[f"layers.{i}.attn_norm.weight"])
+        if sp is not None:
+            x = gather_sequence(x, sp)
         if taps is not None:
             taps[f"attn_in.{i}"] = x
         lanes = getattr(self, "lanes", None)
@@ -292,13 +302,17 @@ class TransformerDecomposedModel:
         att = ports.sdpa(q, k, v, True, batch.segment_ids, self.attention_impl).reshape(B, T, a.n_head * self.head_dim)
         if taps is not None:
             taps[f"attn_out.{i}"] = att
-        resid = resid + lin(att, names[3])
+        o = lin(att, names[3])
+        resid = resid + (slice_sequence(o, sp) if sp is not None else o)
         if f"post_attn.{i}" in want:
             captures[f"post_attn.{i}"] = resid
         x = self._norm(resid, self.w[f"layers.{i}.mlp_norm.weight"])
+        if sp is not None:
+            x = gather_sequence(x, sp)
         if taps is not None:
             taps[f"mlp_in.{i}"] = x
-        return resid + self._mlp(i, x, lin, taps, weights, masks, aux)
+        m = self._mlp(i, x, lin, taps, weights, masks, aux)
+        return resid + (slice_sequence(m, sp) if sp is not None else m)
 
     def _mlp(self, i: int, x: Tensor, lin, taps: dict[str, Tensor] | None, weights, masks, aux: dict) -> Tensor:
         if self.arch.family == "simple_mlp":
@@ -328,6 +342,20 @@ class TransformerDecomposedModel:
         cos, sin = ports.rope_cos_sin(pos, self.head_dim, a.rope_theta, a.rope_scaling)
         taps: dict[str, Tensor] | None = {} if want_taps else None
         captures: dict[str, Tensor] = {}
+        sp = None
+        if (masks is not None and getattr(self, "sequence_parallel", False) and not want and not want_taps
+                and getattr(self, "component_group", None) is not None):
+            # `runtime.sequence_sharding: sequence_parallel`: the MASKED passes carry the residual stream
+            # position-sharded over the tp group between blocks; clean passes keep it whole
+            # (param_decomp/core/placement.py:273-287, targets/qwen36_moe.py:3100-3120).
+            import torch.distributed as dist
+
+            from param_decomp_b200.parallel.group_ops import gather_sequence, slice_sequence
+
+            # (a pass that captures activations keeps the whole-sequence residual: tap buffers are whole-sequence)
+            sp = self.component_group
+            aux["sequence_group"], aux["sequence_world"] = sp, dist.get_world_size(sp)
+            resid = slice_sequence(resid, sp)
         for i in range(a.n_layer):
             if taps is not None:
                 taps[f"resid.{i}"] = resid
@@ -339,6 +367,9 @@ class TransformerDecomposedModel:
         if f"resid.{a.n_layer}" in want:
             captures[f"resid.{a.n_layer}"] = resid
         final = self._norm(resid, self.w["final_norm.weight"])
+        if sp is not None:  # the output edge sees the whole sequence: a position-sharded residual never leaves here
+            final = gather_sequence(final, sp)
+            aux.pop("sequence_group"), aux.pop("sequence_world")
         return ForwardResult(output=final, taps=taps or {}, captures=captures, aux=aux)
 
     def clean_forward(self, batch: LMBatch, capture: tuple[str, ...] = ()) -> ForwardResult:

@@ -72,6 +72,59 @@ class SliceColumns(torch.autograd.Function):
         return torch.cat(parts, dim=-1), None
 
 
+class GatherSequence(torch.autograd.Function):
+    """`[B, T / W, d]` position shards -> the whole `[B, T, d]` on every rank. The consumers (the sites of a
+    block) already hand every rank the FULL gradient of their input (their own adjoint sums the partial
+    gradients over the group), so the adjoint here is this rank's slice of it, with no further reduction."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        world = dist.get_world_size(group)
+        ctx.rank, ctx.width = dist.get_rank(group), x.shape[1]
+        x = x.contiguous()
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x, group=group)
+        return torch.cat(parts, dim=1)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        return g[:, ctx.rank * ctx.width:(ctx.rank + 1) * ctx.width], None
+
+
+class SliceSequence(torch.autograd.Function):
+    """This rank's `[B, T / W, d]` positions of a tensor every rank holds whole. Downstream each rank only
+    produces gradients for its own positions while upstream (a site output summed over the group) expects the
+    whole gradient on every rank: the adjoint all-gathers along the sequence."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:  # type: ignore[override]
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        width = x.shape[1] // world
+        assert width * world == x.shape[1], f"{x.shape[1]} positions do not tile {world} ranks"
+        ctx.group, ctx.world = group, world
+        return x[:, rank * width:(rank + 1) * width]
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        g = g.contiguous()
+        parts = [torch.empty_like(g) for _ in range(ctx.world)]
+        dist.all_gather(parts, g, group=ctx.group)
+        return torch.cat(parts, dim=1), None
+
+
+def gather_sequence(x: Tensor, group) -> Tensor:
+    return GatherSequence.apply(x, group)
+
+
+def slice_sequence(x: Tensor, group) -> Tensor:
+    if not x.requires_grad:
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        width = x.shape[1] // world
+        assert width * world == x.shape[1], f"{x.shape[1]} positions do not tile {world} ranks"
+        return x[:, rank * width:(rank + 1) * width]
+    return SliceSequence.apply(x, group)
+
+
 def copy_to_group(x: Tensor, group) -> Tensor:
     return CopyToGroup.apply(x, group) if x.requires_grad else x
 

@@ -76,8 +76,10 @@ def test_flatten_typed_lists():
     assert out["pd.loss_metrics.Faith.coeff"] == 2.0 and "loss_metrics" not in out["pd"]
 
 
-def test_sequence_parallel_is_refused_not_ignored():
-    """`runtime.sequence_sharding: sequence_parallel` parses (schema parity) and the LM roots refuse it at start-up."""
+def test_sequence_parallel_is_accepted_for_dense_targets_and_refused_for_expert_splits():
+    """`runtime.sequence_sharding: sequence_parallel` parses; dense transformer targets run it (position-sharded
+    residual of the masked passes over the tp group, `tests/test_tp_engine_cpu.py`), mixture-of-experts targets,
+    whose tp axis splits experts, refuse it at start-up instead of ignoring it."""
     import copy
 
     import pytest
@@ -88,8 +90,13 @@ def test_sequence_parallel_is_refused_not_ignored():
 
     c = copy.deepcopy(ge.SMOKE_CONFIG)
     c["runtime"]["sequence_sharding"] = "sequence_parallel"
-    cfg = LMExperimentConfig.model_validate(c)
+    check_runtime_supported(LMExperimentConfig.model_validate(c))
+    m = copy.deepcopy(c)
+    m["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 16,
+                                   "vocab_size": 100, "n_experts": 4, "experts_per_token": 2}
+    m["decomposition"]["sites"] = {"kind": "moe", "layers": {"kind": "all"},
+                                   "cs": {"q": 8, "experts_gate": 16, "experts_up": 16, "experts_down": 16}}
     with pytest.raises(NotImplementedError):
-        check_runtime_supported(cfg)
+        check_runtime_supported(LMExperimentConfig.model_validate(m))
     c["runtime"]["sequence_sharding"] = "replicate"
     check_runtime_supported(LMExperimentConfig.model_validate(c))

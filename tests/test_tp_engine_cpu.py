@@ -19,11 +19,13 @@ STEPS = 4
 SPLIT_ID, SINGLE_ID = "p-0000cccc", "p-0000dddd"
 
 
-def _cfg(tp: int, losses: str, fsdp: int = 1) -> LMExperimentConfig:
+def _cfg(tp: int, losses: str, fsdp: int = 1, sp: bool = False) -> LMExperimentConfig:
     c = copy.deepcopy(ge.SMOKE_CONFIG)
     c["runtime"]["backend"] = "eager_torch"
     c["runtime"]["mesh"] = {"replicate": 1, "fsdp": fsdp, "tp": tp}
     c["runtime"]["sharding"] = "owner" if fsdp > 1 else "ddp"  # fsdp > 1: ZeRO-style sharded AdamW over the batch axes
+    if sp:
+        c["runtime"]["sequence_sharding"] = "sequence_parallel"
     c["target"]["weights_dtype"] = "float32"
     c["target"]["attention_implementation"] = "xla"
     c["target"]["spec"]["arch"] = {"family": "glu_transformer", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 48,
@@ -64,10 +66,23 @@ def _train(cfg, root: Path, run_id: str):
     return res, states[0]
 
 
-def _worker(rank: int, world: int, port: int, root: str, losses: str, fsdp: int, out):
+def _worker(rank: int, world: int, port: int, root: str, losses: str, fsdp: int, out, sp: bool = False):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
-    res, state = _train(_cfg(world // fsdp, losses, fsdp), Path(root), SPLIT_ID)
+    from param_decomp_b200.parallel import group_ops
+
+    calls = {"n": 0}
+    real_gather = group_ops.gather_sequence
+
+    def counting_gather(x, group):
+        calls["n"] += 1
+        assert x.shape[1] * 2 == 8  # [B, T / 2, d] shards of the 8-token window
+        return real_gather(x, group)
+
+    group_ops.gather_sequence = counting_gather
+    res, state = _train(_cfg(world // fsdp, losses, fsdp, sp), Path(root), SPLIT_ID)
+    group_ops.gather_sequence = real_gather
+    assert (calls["n"] > 0) == sp, calls
     assert state.expert_shard is not None and state.expert_shard.by_component
     if hasattr(state.components_opt, "gather_state"):
         assert fsdp > 1
@@ -77,17 +92,19 @@ def _worker(rank: int, world: int, port: int, root: str, losses: str, fsdp: int,
                  {n: p.detach().clone() for n, p in state.ci_fn.named_parameters()})
 
 
-@pytest.mark.parametrize("losses,fsdp", [("stochastic", 1), ("pgd", 1), ("stochastic", 2)])
-def test_component_split_engine_matches_single_process(losses, fsdp):
+@pytest.mark.parametrize("losses,fsdp,sp", [("stochastic", 1, False), ("pgd", 1, False), ("stochastic", 2, False),
+                                            ("stochastic", 1, True), ("pgd", 1, True)])
+def test_component_split_engine_matches_single_process(losses, fsdp, sp):
     """`fsdp = 2`: a 2 x 2 mesh - the batch over two data shards with the sharded optimizer, the components over
-    two tp ranks."""
+    two tp ranks. `sp`: `runtime.sequence_sharding: sequence_parallel` - masked passes carry the residual stream
+    position-sharded over the tp pair between blocks; nothing in the results may change."""
     from safetensors import safe_open
 
     with tempfile.TemporaryDirectory() as root:
         tp = 2
         world, port = tp * fsdp, _free_port()
         out = mp.Manager().dict()
-        mp.spawn(_worker, args=(world, port, root, losses, fsdp, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, root, losses, fsdp, out, sp), nprocs=world, join=True)
         res, ref = _train(_cfg(1, losses), Path(root), SINGLE_ID)
         keys = [k for k in res.last_metrics if k.startswith("train/loss/") or k.startswith("train/grad_norm/")]
         assert len(keys) >= 4
