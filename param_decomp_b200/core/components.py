@@ -32,7 +32,7 @@ class SiteC:
 
 @dataclass(frozen=True)
 class SiteSpec:
-    """One decomposed matrix. `n_blocks > 1` marks a blocked (per-expert) factorization where
+    """One decomposed matrix. `n_blocks > 1` (or `routed`) marks a blocked (per-expert) factorization where
     `d_in`/`d_out` are the dimensions of ONE block and `C` is the flat count `n_blocks * C_block`."""
 
     name: str
@@ -42,6 +42,7 @@ class SiteSpec:
     group: str = ""
     n_blocks: int = 1
     alignment: NonlinearityAlignment | None = None
+    routed: bool = False  # an expert bank's matrix: blocked even when this rank holds a single expert of it
 
     def __post_init__(self) -> None:
         assert self.C % self.n_blocks == 0, f"{self.name}: C={self.C} must tile n_blocks={self.n_blocks}"
@@ -54,7 +55,7 @@ class SiteSpec:
 
     @property
     def blocked(self) -> bool:
-        return self.n_blocks > 1
+        return self.n_blocks > 1 or self.routed
 
 
 @dataclass(frozen=True)

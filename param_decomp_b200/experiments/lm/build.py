@@ -99,11 +99,6 @@ def build_lm_run(cfg: X.LMExperimentConfig | X.LMTargetedExperimentConfig, data_
         # direct peer stores on GPUs); `allreduce`: the reference's scheme, tokens replicated over the group
         ep = ExpertParallel(expert_group, arch.n_experts, mode=expert_mode,
                             transport="p2p" if (expert_mode == "all_to_all" and on_gpu) else "collective")
-        if ep.world > 1 and -(-arch.n_experts // ep.world) < 2:
-            # a rank's expert sites are "blocked" (narrow CI, routed taps) because they hold several experts;
-            # with a single local expert they would degenerate into dense sites reading the wrong tap
-            raise ValueError(f"{arch.n_experts} experts over a tp axis of {ep.world} leave one expert per rank: "
-                             "the expert split needs at least two experts per rank (use a smaller tp axis)")
     sites_cfg = cfg.decomposition.sites
     edge = cfg.target.output_edge
     n_chunks = edge.n_vocab_chunks if isinstance(edge, X.StreamedOutputEdgeConfig) else None

@@ -96,7 +96,7 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         W = self.w[name + ".weight"]  # [E, d_out, d_in]
         E = W.shape[0]
         assert C % E == 0, f"{name}: C={C} must be a multiple of n_experts={E} (components are expert-local)"
-        return SiteSpec(name, W.shape[2], W.shape[1], C, group=kind, n_blocks=E)
+        return SiteSpec(name, W.shape[2], W.shape[1], C, group=kind, n_blocks=E, routed=True)
 
     def tap_for_site(self, site: str) -> str:
         layer, kind = self._site_layer_kind[site]
@@ -120,7 +120,7 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
             return self.sites
         E = self.ep.n_experts
         return tuple(s if not s.blocked else SiteSpec(s.name, s.d_in, s.d_out, s.C_block * E, group=s.group, n_blocks=E,
-                                                      alignment=s.alignment) for s in self.sites)
+                                                      alignment=s.alignment, routed=s.routed) for s in self.sites)
 
     # -- expert bank --------------------------------------------------------------------------------
     def _expert_site(self, name: str, x_jobs: Tensor, expert_of_job: Tensor, order: Tensor, bounds: list[int],

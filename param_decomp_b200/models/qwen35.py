@@ -173,7 +173,7 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
             E = W.shape[0]
             assert C % E == 0, f"{name}: C={C} must be a multiple of n_experts={E}"
             return SiteSpec(name, W.shape[2], W.shape[1], C, group=kind, n_blocks=E,
-                            alignment=alignment_for(self.arch, kind))
+                            alignment=alignment_for(self.arch, kind), routed=True)
         return SiteSpec(name, W.shape[1], W.shape[0], C, group=kind, alignment=alignment_for(self.arch, kind))
 
     def tap_for_site(self, site: str) -> str:

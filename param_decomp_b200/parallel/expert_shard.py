@@ -100,7 +100,7 @@ class StackSharding:
             return tuple(SiteSpec(s.name, s.d_in, s.d_out, s.C * self.world, group=s.group, alignment=s.alignment)
                          for s in sites)
         return tuple(s if not s.blocked else SiteSpec(s.name, s.d_in, s.d_out, s.C_block * self.n_experts, group=s.group,
-                                                      n_blocks=self.n_experts, alignment=s.alignment) for s in sites)
+                                                      n_blocks=self.n_experts, alignment=s.alignment, routed=s.routed) for s in sites)
 
     @torch.no_grad()
     def init_components(self, local: ComponentStacks, generator: torch.Generator) -> None:
