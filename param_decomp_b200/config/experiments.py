@@ -243,6 +243,10 @@ class TransformerArchConfig(BaseConfig):
     rms_eps: PositiveFloat = 1e-6
     qk_norm: bool = False
     tie_embeddings: bool = False
+    # GPT-2-style variants of the dense families (the pretrainer's `GPT2Simple`): LayerNorm with bias instead of
+    # RMSNorm (`norm_eps` = `rms_eps`), learned absolute position embeddings instead of RoPE
+    norm_kind: Literal["rms", "layer"] = "rms"
+    positional: Literal["rope", "learned"] = "rope"
     # MoE only
     n_experts: PositiveInt | None = None
     experts_per_token: PositiveInt | None = None

@@ -123,25 +123,57 @@ def load_hf_snapshot(snapshot_dir: Path, dtype: torch.dtype, device) -> tuple[Tr
     return arch, remap_hf_llama(read_safetensors(files, dtype, device), arch)
 
 
+def _cache_model_type(arch: TransformerArchConfig) -> str:
+    if arch.family == "glu_transformer":
+        return "LlamaSimple"
+    return "GPT2Simple" if arch.norm_kind == "layer" else "LlamaSimpleMLP"
+
+
+def _cache_keys(model_type: str, n_layer: int) -> dict[str, str]:
+    """This package's weight key -> the pretrain checkpoint's key, per model type (the key grammars of
+    param_decomp/pretrain/models.py `state_dict`: `h.{i}.attn.q_proj.weight`, `h.{i}.mlp.c_fc.weight` or
+    `gate/up/down_proj`, `h.{i}.rms_1.weight` or `ln_1.{weight,bias}`, `wte.weight`, `wpe.weight`, `ln_f.*`)."""
+    gpt2 = model_type == "GPT2Simple"
+    fam = "glu_transformer" if model_type == "LlamaSimple" else "simple_mlp"
+    n1, n2 = ("ln_1", "ln_2") if gpt2 else ("rms_1", "rms_2")
+    out = {"embed.weight": "wte.weight", "final_norm.weight": "ln_f.weight"}
+    if gpt2:
+        out["final_norm.bias"], out["pos_embed.weight"] = "ln_f.bias", "wpe.weight"
+    for i in range(n_layer):
+        out[f"layers.{i}.attn_norm.weight"], out[f"layers.{i}.mlp_norm.weight"] = f"h.{i}.{n1}.weight", f"h.{i}.{n2}.weight"
+        if gpt2:
+            out[f"layers.{i}.attn_norm.bias"], out[f"layers.{i}.mlp_norm.bias"] = f"h.{i}.{n1}.bias", f"h.{i}.{n2}.bias"
+        if fam == "simple_mlp":
+            for k in tf.SIMPLE_KINDS:
+                out[tf.weight_key(fam, i, k)] = tf.site_name("simple_mlp", i, k) + ".weight"
+        else:
+            for k in ("q", "k", "v", "o"):
+                out[tf.weight_key(fam, i, k)] = f"h.{i}.attn.{k}_proj.weight"
+            for k in ("gate", "up", "down"):
+                out[tf.weight_key(fam, i, k)] = f"h.{i}.mlp.{k}_proj.weight"
+    return out
+
+
 def load_simple_mlp_cache(entry: Path, dtype: torch.dtype, device) -> tuple[TransformerArchConfig, dict[str, Tensor]]:
-    """LlamaSimpleMLP pretrain checkpoints: `h.{i}.attn.q_proj.weight`, `h.{i}.mlp.c_fc.weight`,
-    `h.{i}.rms_1.weight`, `wte.weight`, `ln_f.weight`, `lm_head.weight`."""
+    """Pretrain checkpoints of the in-house dense models: `LlamaSimpleMLP` (RoPE, RMSNorm, two-matrix GELU MLP),
+    `LlamaSimple` (the same with a SwiGLU MLP) and `GPT2Simple` (learned positions, LayerNorm with bias,
+    two-matrix GELU MLP, tied head); `model_config.yaml` names the type."""
     mc = yaml.safe_load((entry / "model_config.yaml").read_text())
     m = mc.get("model", mc)
+    model_type = m.get("model_type", "LlamaSimpleMLP")
+    gpt2 = model_type == "GPT2Simple"
     arch = TransformerArchConfig(
-        family="simple_mlp", n_layer=m["n_layer"], d_model=m["n_embd"], n_head=m["n_head"],
-        n_kv_head=m.get("n_key_value_heads"), d_ff=m["n_intermediate"], vocab_size=m["vocab_size"],
+        family="glu_transformer" if model_type == "LlamaSimple" else "simple_mlp", n_layer=m["n_layer"],
+        d_model=m["n_embd"], n_head=m["n_head"], n_kv_head=None if gpt2 else m.get("n_key_value_heads"),
+        d_ff=m.get("n_intermediate", 4 * m["n_embd"]), vocab_size=m["vocab_size"],
         max_seq_len=m.get("n_ctx", m.get("block_size", 512)), rope_theta=float(m.get("rotary_base", 10000)),
-        rms_eps=float(m.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(m.get("tie_word_embeddings", False)))
+        rms_eps=float(m.get("layer_norm_eps", 1e-5) if gpt2 else m.get("rms_norm_eps", 1e-6)),
+        tie_embeddings=bool(m.get("tie_word_embeddings", gpt2)),
+        norm_kind="layer" if gpt2 else "rms", positional="learned" if gpt2 else "rope")
     raw = read_safetensors([latest_checkpoint(entry)], dtype, device)
-    out = {"embed.weight": raw["wte.weight"], "final_norm.weight": raw["ln_f.weight"]}
+    out = {ours: raw[theirs] for ours, theirs in _cache_keys(model_type, arch.n_layer).items()}
     if "lm_head.weight" in raw and not arch.tie_embeddings:
         out["lm_head.weight"] = raw["lm_head.weight"]
-    for i in range(arch.n_layer):
-        out[f"layers.{i}.attn_norm.weight"] = raw[f"h.{i}.rms_1.weight"]
-        out[f"layers.{i}.mlp_norm.weight"] = raw[f"h.{i}.rms_2.weight"]
-        for k in tf.SIMPLE_KINDS:
-            out[tf.weight_key("simple_mlp", i, k)] = raw[tf.site_name("simple_mlp", i, k) + ".weight"]
     return arch, out
 
 
@@ -150,19 +182,19 @@ def save_simple_mlp_cache(entry: Path, arch: TransformerArchConfig, weights: dic
     from safetensors.torch import save_file
 
     entry.mkdir(parents=True, exist_ok=True)
-    (entry / "model_config.yaml").write_text(yaml.dump({"model": {
-        "model_type": "LlamaSimpleMLP", "n_layer": arch.n_layer, "n_embd": arch.d_model, "n_head": arch.n_head,
-        "n_key_value_heads": arch.n_kv_head or arch.n_head, "n_intermediate": arch.d_ff, "vocab_size": arch.vocab_size,
-        "n_ctx": arch.max_seq_len, "rotary_base": arch.rope_theta, "rms_norm_eps": arch.rms_eps,
-        "tie_word_embeddings": arch.tie_embeddings}}))
-    raw = {"wte.weight": weights["embed.weight"], "ln_f.weight": weights["final_norm.weight"]}
-    if "lm_head.weight" in weights:
+    model_type = _cache_model_type(arch)
+    cfg = {"model_type": model_type, "n_layer": arch.n_layer, "n_embd": arch.d_model, "n_head": arch.n_head,
+           "n_intermediate": arch.d_ff, "vocab_size": arch.vocab_size, "n_ctx": arch.max_seq_len,
+           "tie_word_embeddings": arch.tie_embeddings}
+    if model_type == "GPT2Simple":
+        cfg["layer_norm_eps"] = arch.rms_eps
+    else:
+        cfg.update({"n_key_value_heads": arch.n_kv_head or arch.n_head, "rotary_base": arch.rope_theta,
+                    "rms_norm_eps": arch.rms_eps})
+    (entry / "model_config.yaml").write_text(yaml.dump({"model": cfg}))
+    raw = {theirs: weights[ours] for ours, theirs in _cache_keys(model_type, arch.n_layer).items()}
+    if "lm_head.weight" in weights and not arch.tie_embeddings:
         raw["lm_head.weight"] = weights["lm_head.weight"]
-    for i in range(arch.n_layer):
-        raw[f"h.{i}.rms_1.weight"] = weights[f"layers.{i}.attn_norm.weight"]
-        raw[f"h.{i}.rms_2.weight"] = weights[f"layers.{i}.mlp_norm.weight"]
-        for k in tf.SIMPLE_KINDS:
-            raw[tf.site_name("simple_mlp", i, k) + ".weight"] = weights[tf.weight_key("simple_mlp", i, k)]
     save_file({k: v.detach().cpu().contiguous() for k, v in raw.items()}, str(entry / f"model_step_{step}.safetensors"))
 
 

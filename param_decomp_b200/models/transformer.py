@@ -2,7 +2,7 @@
 
 Per block:  resid -> RMSNorm -> q,k,v (RoPE on q,k; optional per-head QK RMS-norm; GQA) -> causal
 attention -> o -> +resid -> RMSNorm -> gated MLP `down(silu(gate) * up)` or plain MLP
-`down(gelu(c_fc))` -> +resid;  final RMSNorm -> (tied or untied) head.
+`down(gelu_tanh(c_fc))` -> +resid;  final RMSNorm -> (tied or untied) head.
 
 Site names follow the reference's grammars: GLU family `layers.{i}.self_attn.{q,k,v,o}_proj`,
 `layers.{i}.mlp.{gate,up,down}_proj`; simple-MLP family `h.{i}.attn.{q,k,v,o}_proj`,
@@ -81,11 +81,16 @@ def random_init_weights(arch: TransformerArchConfig, seed: int, dtype: torch.dty
         return (torch.randn(rows, cols, generator=g) * std).to(dtype).to(device)
 
     out["embed.weight"] = mat(arch.vocab_size, d)
+    if arch.positional == "learned":
+        out["pos_embed.weight"] = mat(arch.max_seq_len, d)
     resid_std = 0.02 / math.sqrt(2 * arch.n_layer)
     names = (("q_proj", "k_proj", "v_proj", "o_proj") if fam == "simple_mlp" else ("q", "k", "v", "o"))
     for i in range(arch.n_layer):
         out[f"layers.{i}.attn_norm.weight"] = torch.ones(d, dtype=dtype, device=device)
         out[f"layers.{i}.mlp_norm.weight"] = torch.ones(d, dtype=dtype, device=device)
+        if arch.norm_kind == "layer":
+            out[f"layers.{i}.attn_norm.bias"] = torch.zeros(d, dtype=dtype, device=device)
+            out[f"layers.{i}.mlp_norm.bias"] = torch.zeros(d, dtype=dtype, device=device)
         out[weight_key(fam, i, names[0])] = mat(arch.n_head * hd, d)
         out[weight_key(fam, i, names[1])] = mat(kv * hd, d)
         out[weight_key(fam, i, names[2])] = mat(kv * hd, d)
@@ -101,6 +106,8 @@ def random_init_weights(arch: TransformerArchConfig, seed: int, dtype: torch.dty
             out[weight_key(fam, i, "up")] = mat(arch.d_ff, d)
             out[weight_key(fam, i, "down")] = mat(d, arch.d_ff, resid_std)
     out["final_norm.weight"] = torch.ones(d, dtype=dtype, device=device)
+    if arch.norm_kind == "layer":
+        out["final_norm.bias"] = torch.zeros(d, dtype=dtype, device=device)
     if not arch.tie_embeddings:
         out["lm_head.weight"] = mat(arch.vocab_size, d)
     return out
@@ -234,7 +241,15 @@ class TransformerDecomposedModel:
     def _fused(self, x: Tensor) -> bool:
         return self.backend == "fused_sm100" and x.is_cuda and x.dtype == torch.bfloat16
 
-    def _norm(self, x: Tensor, w: Tensor) -> Tensor:
+    def _norm(self, x: Tensor, w: Tensor, b: Tensor | None = None) -> Tensor:
+        if getattr(self.arch, "norm_kind", "rms") == "layer":
+            # LayerNorm with bias (GPT-2 style): statistics in fp32, scale and shift in the activation dtype
+            # (param_decomp/pretrain/models.py:182-188)
+            xf = x.float()
+            mean = xf.mean(-1, keepdim=True)
+            var = (xf - mean).pow(2).mean(-1, keepdim=True)
+            y = ((xf - mean) * torch.rsqrt(var + self.arch.rms_eps)).to(x.dtype) * w.to(x.dtype)
+            return y + b.to(x.dtype) if b is not None else y
         if self._fused(x):
             from param_decomp_b200.ops import elementwise as ew
 
@@ -242,6 +257,8 @@ class TransformerDecomposedModel:
         return ports.rms_norm(x, w, self.arch.rms_eps)
 
     def _rope(self, x: Tensor, cos: Tensor, sin: Tensor, shared_positions: bool) -> Tensor:
+        if getattr(self.arch, "positional", "rope") == "learned":
+            return x  # positions entered with the embeddings
         if self._fused(x) and shared_positions and cos.shape[-1] == x.shape[-1]:
             from param_decomp_b200.ops import elementwise as ew
 
@@ -277,7 +294,7 @@ class TransformerDecomposedModel:
             from param_decomp_b200.parallel.group_ops import gather_sequence, slice_sequence
 
             T = T * aux["sequence_world"]
-        x = self._norm(resid, self.w[f"layers.{i}.attn_norm.weight"])
+        x = self._norm(resid, self.w[f"layers.{i}.attn_norm.weight"], self.w.get(f"layers.{i}.attn_norm.bias"))
         if sp is not None:
             x = gather_sequence(x, sp)
         if taps is not None:
@@ -306,7 +323,7 @@ class TransformerDecomposedModel:
         resid = resid + (slice_sequence(o, sp) if sp is not None else o)
         if f"post_attn.{i}" in want:
             captures[f"post_attn.{i}"] = resid
-        x = self._norm(resid, self.w[f"layers.{i}.mlp_norm.weight"])
+        x = self._norm(resid, self.w[f"layers.{i}.mlp_norm.weight"], self.w.get(f"layers.{i}.mlp_norm.bias"))
         if sp is not None:
             x = gather_sequence(x, sp)
         if taps is not None:
@@ -316,7 +333,7 @@ class TransformerDecomposedModel:
 
     def _mlp(self, i: int, x: Tensor, lin, taps: dict[str, Tensor] | None, weights, masks, aux: dict) -> Tensor:
         if self.arch.family == "simple_mlp":
-            h = F.gelu(lin(x, "c_fc"))
+            h = ports.gelu_tanh(lin(x, "c_fc"))  # the tanh form, as the reference's plain MLP (targets/transformer.py:802-809)
             down = "down_proj"
         else:
             lanes = getattr(self, "lanes", None)
@@ -339,6 +356,8 @@ class TransformerDecomposedModel:
         B, T = tokens.shape
         resid = F.embedding(tokens.long(), self.w["embed.weight"])
         pos = batch.positions if batch.positions is not None else torch.arange(T, device=tokens.device)[None]
+        if getattr(a, "positional", "rope") == "learned":
+            resid = resid + F.embedding(pos.long(), self.w["pos_embed.weight"])
         cos, sin = ports.rope_cos_sin(pos, self.head_dim, a.rope_theta, a.rope_scaling)
         taps: dict[str, Tensor] | None = {} if want_taps else None
         captures: dict[str, Tensor] = {}
@@ -366,7 +385,7 @@ class TransformerDecomposedModel:
             taps[f"resid.{a.n_layer}"] = resid
         if f"resid.{a.n_layer}" in want:
             captures[f"resid.{a.n_layer}"] = resid
-        final = self._norm(resid, self.w["final_norm.weight"])
+        final = self._norm(resid, self.w["final_norm.weight"], self.w.get("final_norm.bias"))
         if sp is not None:  # the output edge sees the whole sequence: a position-sharded residual never leaves here
             final = gather_sequence(final, sp)
             aux.pop("sequence_group"), aux.pop("sequence_world")

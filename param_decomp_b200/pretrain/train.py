@@ -41,11 +41,13 @@ class PretrainModelConfig(BaseConfig):
     n_layer: PositiveInt
     n_head: PositiveInt
     n_embd: PositiveInt
-    n_intermediate: PositiveInt
+    n_intermediate: PositiveInt | None = None  # GPT2Simple: 4 x n_embd
     rotary_base: PositiveFloat = 10000.0
     n_ctx: PositiveInt = 512
     n_key_value_heads: PositiveInt | None = None
     rms_norm_eps: PositiveFloat = 1e-6
+    layer_norm_eps: PositiveFloat = 1e-5
+    tie_word_embeddings: bool = False
 
     def arch(self) -> TransformerArchConfig:
         if self.model_type == "Qwen35Moe":
@@ -54,10 +56,17 @@ class PretrainModelConfig(BaseConfig):
             assert (h.n_layer, h.d_model, h.vocab_size) == (self.n_layer, self.n_embd, self.vocab_size)
             return h
         family = "simple_mlp" if self.model_type in ("LlamaSimpleMLP", "GPT2Simple") else "glu_transformer"
+        if self.model_type == "GPT2Simple":
+            # learned absolute positions, LayerNorm with bias, plain multi-head attention, tied head
+            # (param_decomp/pretrain/models.py:46-62,144-207)
+            return TransformerArchConfig(family=family, n_layer=self.n_layer, d_model=self.n_embd, n_head=self.n_head,
+                                         d_ff=self.n_intermediate or 4 * self.n_embd, vocab_size=self.vocab_size,
+                                         max_seq_len=self.n_ctx, rms_eps=self.layer_norm_eps, tie_embeddings=True, norm_kind="layer",
+                                         positional="learned")
         return TransformerArchConfig(family=family, n_layer=self.n_layer, d_model=self.n_embd, n_head=self.n_head,
-                                     n_kv_head=self.n_key_value_heads, d_ff=self.n_intermediate,
+                                     n_kv_head=self.n_key_value_heads, d_ff=self.n_intermediate or 4 * self.n_embd,
                                      vocab_size=self.vocab_size, max_seq_len=self.n_ctx, rope_theta=self.rotary_base,
-                                     rms_eps=self.rms_norm_eps)
+                                     rms_eps=self.rms_norm_eps, tie_embeddings=self.tie_word_embeddings)
 
 
 class PretrainConfig(BaseConfig):
