@@ -10,7 +10,7 @@ from __future__ import annotations
 from itertools import pairwise
 from typing import Annotated, ClassVar, Literal, Self
 
-from pydantic import ConfigDict, Discriminator, Field, NonNegativeInt, PositiveInt, model_validator
+from pydantic import ConfigDict, Discriminator, Field, NonNegativeInt, PositiveFloat, PositiveInt, model_validator
 
 from param_decomp_b200.config.losses import PGDConfig, ReconstructionAuxiliariesMixin
 from param_decomp_b200.formats.base import BaseConfig, Probability
@@ -125,15 +125,48 @@ class StochasticAttnPatternsReconLossConfig(BaseConfig):
     type: Literal["StochasticAttnPatternsReconLoss"] = "StochasticAttnPatternsReconLoss"
 
 
-class _Strategy(BaseConfig):
-    model_config = ConfigDict(extra="allow", frozen=True)
-    kind: Literal["ci_masked", "stochastic", "fresh_pgd", "persistent"]
+class CIMaskedStrategy(BaseConfig):
+    """Masks = the CI lower values; no weight-delta correction."""
+
+    kind: Literal["ci_masked"] = "ci_masked"
+
+
+class StochasticStrategy(BaseConfig):
+    """One draw of `ci + (1 - ci) U[0,1]` with random weight-delta masks."""
+
+    kind: Literal["stochastic"] = "stochastic"
+
+
+class FreshPGDStrategy(BaseConfig):
+    """Fresh sign-PGD sources (random init, one source per component shared by every token) ascended `n_steps`
+    times against the output KL, composed with the CI."""
+
+    kind: Literal["fresh_pgd"] = "fresh_pgd"
+    n_steps: NonNegativeInt
+    step_size: PositiveFloat
+
+
+class PersistentStrategy(BaseConfig):
+    """The run's persistent-PGD adversary sources, composed with the CI. `state_key` is the instance key of the
+    persistent training term whose sources are read; per-row (`bc` / `bsc`) sources index training rows, so every
+    evaluation sequence draws one of them."""
+
+    kind: Literal["persistent"] = "persistent"
+    state_key: str
+
+
+RouterDivergenceStrategy = Annotated[
+    CIMaskedStrategy | StochasticStrategy | FreshPGDStrategy | PersistentStrategy, Field(discriminator="kind")]
 
 
 class RouterDivergenceConfig(BaseConfig):
+    """Per MoE layer, how far the masked model's expert router drifts from the target's, under each masking
+    strategy (logged under the strategy's kind, so each kind appears once).
+    Parity: param_decomp/experiments/lm/eval_config.py:55-112."""
+
     slow: ClassVar[bool] = True
     type: Literal["RouterDivergence"] = "RouterDivergence"
-    strategies: tuple[_Strategy, ...]
+    strategies: tuple[RouterDivergenceStrategy, ...]
 
     @model_validator(mode="after")
     def _kinds(self) -> Self:
@@ -148,11 +181,40 @@ class WellTemperednessConfig(BaseConfig):
     type: Literal["WellTemperedness"] = "WellTemperedness"
 
 
+class ArithmeticCEKLConfig(BaseConfig):
+    rounding_threshold: Probability = 0.0
+
+
+class ArithmeticCIL0Config(BaseConfig):
+    ci_alive_threshold: Probability = 0.0
+    groups: dict[str, list[str]] | None = None
+
+
+class ArithmeticFreshPGDConfig(BaseConfig):
+    n_steps: NonNegativeInt
+    step_size: PositiveFloat
+
+
+class ArithmeticProbeMetrics(BaseConfig):
+    """Scalar operations evaluated on the arithmetic grid rather than on corpus batches."""
+
+    ce_kl: ArithmeticCEKLConfig = Field(default_factory=ArithmeticCEKLConfig)
+    ci_l0: ArithmeticCIL0Config = Field(default_factory=ArithmeticCIL0Config)
+    fresh_pgd: ArithmeticFreshPGDConfig | None = None
+
+
 class ArithmeticCIGridConfig(BaseConfig):
+    """Per-component causal-importance heat maps over an arithmetic operand grid, plus the probe metrics on it.
+    Parity: param_decomp/experiments/lm/eval_config.py:158-192."""
+
     model_config = ConfigDict(extra="allow", frozen=True)
     slow: ClassVar[bool] = True
     type: Literal["ArithmeticCIGrid"] = "ArithmeticCIGrid"
+    probe_metrics: ArithmeticProbeMetrics | None = None
     operation: Literal["add", "sub", "mul"] = "add"
+    a_range: tuple[int, int] = (1, 100)
+    b_range: tuple[int, int] = (1, 100)
+    thresholds: tuple[Probability, ...] = (0.1,)
     top_k: PositiveInt = 24
 
 

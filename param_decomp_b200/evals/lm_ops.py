@@ -33,11 +33,66 @@ def _router_keys(model: Any) -> tuple[str, ...]:
 
 
 @torch.no_grad()
-def router_divergence(ctx: StepContext, state: TrainState, batch: Any, strategies: tuple[str, ...] = ("ci_masked",),
+def _strategy_masks(ctx: StepContext, state: TrainState, batch: Any, clean, ci, weights, strat) -> dict | None:
+    """Masks of one evaluation masking strategy (`config/evals.py`: `ci_masked`, `stochastic`, `fresh_pgd`,
+    `persistent`); `strat` may also be the bare kind of the two that need no parameters."""
+    from param_decomp_b200.core import adversary as adv_mod
+    from param_decomp_b200.core.objective import ReconTerm
+    from param_decomp_b200.core.train import masked_recon, reduce_source_grads
+
+    kind = strat if isinstance(strat, str) else strat.kind
+    if kind == "ci_masked":
+        return masking.ci_masks(ci.mask_inputs())
+    if kind == "stochastic":
+        return masking.stochastic_masks(ci.mask_inputs(), StepKey(0xE7A3, 0), 0, 0, site_index=ctx.site_index, lazy=False)
+    ci_lower = ci.dense_lower()
+    lead = tuple(next(iter(ci_lower.values())).shape[:-1])
+    positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None
+    device = next(iter(ci_lower.values())).device
+    sites = getattr(ctx.model, "global_sites", ctx.model.sites)
+    if kind == "fresh_pgd":
+        # batch-shared sources, random init, sign ascent against the output loss (param_decomp/core/recon_eval.py:142-257)
+        from types import SimpleNamespace
+
+        leaves = adv_mod.fresh_sources(sites, "random", "c", lead[0], positions, StepKey(0xE7A4, 0), 14, device)
+        term = ReconTerm(name="eval_router_pgd", index=14, strategy="fresh_pgd", cfg=SimpleNamespace(auxiliaries=()))  # type: ignore[arg-type]
+        w_d = weights
+        with torch.enable_grad():
+            for _ in range(strat.n_steps):
+                src, dlt = adv_mod.PersistentAdversary.split(leaves)
+                e2e, _ = masked_recon(ctx, w_d, batch, clean, masking.source_masks(ci_lower, src, dlt), term, 0, with_aux=False)
+                names = list(leaves)
+                gs = torch.autograd.grad(e2e, [leaves[k] for k in names], allow_unused=True)
+                adv_mod.sign_ascent_(leaves, reduce_source_grads(ctx, {
+                    k: (g if g is not None else torch.zeros_like(leaves[k])) for k, g in zip(names, gs)}, True),
+                    strat.step_size)
+        src, dlt = adv_mod.PersistentAdversary.split({k: v.detach() for k, v in leaves.items()})
+        return masking.source_masks(ci_lower, src, dlt)
+    if kind == "persistent":
+        adv = state.adversaries.get(strat.state_key)
+        assert adv is not None, (f"RouterDivergence persistent strategy names state_key {strat.state_key!r}, but the "
+                                 f"run's persistent terms are {sorted(state.adversaries)}")
+        leaves = {k: v.detach() for k, v in adv.leaves().items()}
+        if adv.pool_size > 1:  # one particle per row, as training samples them
+            pick = torch.zeros(next(iter(leaves.values())).shape[0], dtype=torch.long, device=device)
+            leaves = adv.select_particles(leaves, pick)
+        rows = next(iter(leaves.values())).shape[0]
+        if not adv.batch_shared and rows != lead[0]:
+            # per-row sources index TRAINING rows: every evaluation sequence draws one of them, fixed across evaluations
+            g = torch.Generator().manual_seed(0xE7A5)
+            idx = torch.randint(0, rows, (lead[0],), generator=g).to(device)
+            leaves = {k: v.index_select(0, idx) for k, v in leaves.items()}
+        src, dlt = adv_mod.PersistentAdversary.split(leaves)
+        return masking.source_masks(ci_lower, src, dlt)
+    raise ValueError(kind)
+
+
+def router_divergence(ctx: StepContext, state: TrainState, batch: Any, strategies: tuple = ("ci_masked",),
                       ) -> dict[str, float]:
     """Per MoE layer and masking strategy: KL(target router || masked router) per token, the share of
     the target's top-k the masked router would still select (a counterfactual read-out: the forward
-    itself stays pinned to the target's experts), and the L1 distance of the applied mixing weights."""
+    itself stays pinned to the target's experts), and the L1 distance of the applied mixing weights.
+    `strategies`: `config/evals.py` strategy objects (or bare kinds for the parameter-free two)."""
     model = ctx.model
     assert hasattr(model, "expert_site_names"), "router divergence needs a target with an expert router"
     keys = _router_keys(model)
@@ -48,14 +103,9 @@ def router_divergence(ctx: StepContext, state: TrainState, batch: Any, strategie
     ci = run_ci_fn(ctx, state, clean)
     out: dict[str, float] = {}
     k = model.arch.experts_per_token
-    for strat in strategies:
-        if strat == "ci_masked":
-            masks = masking.ci_masks(ci.mask_inputs())
-        elif strat == "stochastic":
-            masks = masking.stochastic_masks(ci.mask_inputs(), StepKey(0xE7A3, 0), 0, 0, site_index=ctx.site_index,
-                                             lazy=False)
-        else:
-            continue  # adversarial strategies need the training adversaries' state
+    for strategy in strategies:
+        strat = strategy if isinstance(strategy, str) else strategy.kind
+        masks = _strategy_masks(ctx, state, batch, clean, ci, weights, strategy)
         res = model.masked_forward(weights, batch, masks, capture=keys, clean=clean)
         per_layer = []
         for i, key in enumerate(keys):
@@ -169,9 +219,13 @@ def build_arithmetic_prompt_grid(encode: Callable[[str], list[int]], a_values: l
 
 @torch.no_grad()
 def arithmetic_ci_grid(ctx: StepContext, state: TrainState, grid: ArithmeticPromptGrid, top_k: int = 24,
-                       run_dir: Any = None) -> dict[str, float]:
+                       run_dir: Any = None, thresholds: tuple[float, ...] = (0.1,), probe_metrics: Any = None,
+                       ) -> dict[str, float]:
     """Per site: CI of every component at the `=` position as an `a x b` heat map; the `top_k`
-    components by mean CI are drawn. Returns alive counts."""
+    components by mean CI are drawn. Returns alive counts (mean CI above 0.01, and above each of `thresholds`)
+    and, with `probe_metrics` (`config/evals.py::ArithmeticProbeMetrics`), the scalar operations evaluated on
+    the grid's prompts instead of corpus batches: the six-mask CE / KL table, CI-L0 per site or group, and
+    optionally a fresh-PGD reconstruction (param_decomp/experiments/lm/arithmetic_eval_operation.py)."""
     from param_decomp_b200.models.transformer import LMBatch
 
     model = ctx.model
@@ -181,10 +235,26 @@ def arithmetic_ci_grid(ctx: StepContext, state: TrainState, grid: ArithmeticProm
     ci = run_ci_fn(ctx, state, clean).dense_lower()
     A, Bn = len(grid.a_values), len(grid.b_values)
     out: dict[str, float] = {}
+    if probe_metrics is not None:
+        from param_decomp_b200.evals.core import ci_l0, fresh_pgd_recon
+        from param_decomp_b200.evals.lm import ce_and_kl
+
+        for k, v in ce_and_kl(ctx, state, batch, probe_metrics.ce_kl.rounding_threshold).items():
+            out[f"ArithmeticCIGrid/probe/{k}"] = v
+        for k, v in ci_l0(ci, probe_metrics.ci_l0.ci_alive_threshold, probe_metrics.ci_l0.groups).items():
+            out[f"ArithmeticCIGrid/probe/{k}"] = v
+        if probe_metrics.fresh_pgd is not None:
+            with torch.enable_grad():
+                res = fresh_pgd_recon(ctx, state, batch, probe_metrics.fresh_pgd.step_size,
+                                      (probe_metrics.fresh_pgd.n_steps,), StepKey(0xE7A6, 0))
+            out[f"ArithmeticCIGrid/probe/PGDReconLoss_{probe_metrics.fresh_pgd.n_steps}step"] = \
+                res[probe_metrics.fresh_pgd.n_steps]["loss"]
     for site, v in ci.items():
         last = v[:, -1].float().reshape(A, Bn, -1)  # [A, B, C]
         mean = last.mean((0, 1))
         out[f"ArithmeticCIGrid/{site}/n_alive"] = float((mean > 0.01).sum())
+        for thr in thresholds:
+            out[f"ArithmeticCIGrid/{site}/n_above_{thr:g}"] = float((last > thr).any(0).any(0).sum())
         top = mean.topk(min(top_k, mean.numel())).indices
         mats = [last[:, :, int(c)].cpu().numpy() for c in top]
         figures.save_figure(run_dir, f"arithmetic_ci_{site}", figures.grid_of_heatmaps(mats),
