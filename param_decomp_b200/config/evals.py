@@ -176,9 +176,18 @@ class RouterDivergenceConfig(BaseConfig):
 
 
 class WellTemperednessConfig(BaseConfig):
+    """Whether higher CI pre-activations mean greater ablation effects: components ablated one at a time at sampled
+    token positions, `n_locations * n_components_per_region` ablations per pre-activation region; `groups` maps names
+    to fnmatch patterns of site names. `ablations_per_forward` is accepted for schema parity (ablations run one per
+    forward here). Parity: param_decomp/experiments/lm/eval_config.py:141-156."""
+
     model_config = ConfigDict(extra="allow", frozen=True)
     slow: ClassVar[bool] = True
     type: Literal["WellTemperedness"] = "WellTemperedness"
+    groups: dict[str, list[str]] | None = None
+    n_locations: PositiveInt = 4
+    n_components_per_region: PositiveInt = 16
+    ablations_per_forward: PositiveInt = 1
 
 
 class ArithmeticCEKLConfig(BaseConfig):

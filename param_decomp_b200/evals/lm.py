@@ -112,8 +112,9 @@ class LMEvaluation:
             return lm_ops.router_divergence(ctx, state, batch, tuple(metric.strategies))
         if isinstance(metric, E.WellTemperednessConfig):
             extra = metric.model_extra or {}
-            return lm_ops.well_temperedness(ctx, state, batch, int(extra.get("n_locations", 4)),
-                                            int(extra.get("n_components", 16)), run_dir=self.run_dir)
+            return lm_ops.well_temperedness(ctx, state, batch, metric.n_locations,
+                                            int(extra.get("n_components", metric.n_components_per_region)),
+                                            run_dir=self.run_dir, groups=metric.groups)
         if isinstance(metric, E.ArithmeticCIGridConfig) and self.arithmetic_grid is not None:
             return lm_ops.arithmetic_ci_grid(ctx, state, self.arithmetic_grid, metric.top_k, run_dir=self.run_dir,
                                              thresholds=tuple(metric.thresholds), probe_metrics=metric.probe_metrics)

@@ -151,9 +151,18 @@ def fraction_well_ordered_pairs(pre: Tensor, damage: Tensor) -> float:
 
 @torch.no_grad()
 def well_temperedness(ctx: StepContext, state: TrainState, batch: Any, n_locations: int = 4,
-                      n_components: int = 16, seed: int = 0, run_dir: Any = None) -> dict[str, float]:
-    """For a few (sequence, position) locations: ablate sampled components one at a time (mask 1
-    everywhere, 0 for that component at that position) and score the output change AT that position."""
+                      n_components: int = 16, seed: int = 0, run_dir: Any = None,
+                      groups: dict[str, list[str]] | None = None) -> dict[str, float]:
+    """Whether higher CI pre-activations mean greater ablation effects. At `n_locations` sampled (sequence,
+    position) locations components are ablated one at a time (mask 1 everywhere, 0 for that component at that
+    position) and the output change AT that position is scored. Sampling is stratified by the pre-activation's
+    region at the location (`below_zero`, `zero_to_one`, `above_one`): every region schedules `n_components`
+    ablations per location and pads a sparse region with out-of-region components whose damage is computed and
+    discarded, so the number of forwards does not depend on the data. `groups` maps names to fnmatch patterns of
+    site names; each group gets its own scores (param_decomp/experiments/lm/well_temperedness.py,
+    eval_config.py:141-156)."""
+    import fnmatch
+
     model = ctx.model
     g = torch.Generator().manual_seed(seed)
     clean = model.clean_forward(batch)
@@ -166,24 +175,40 @@ def well_temperedness(ctx: StepContext, state: TrainState, batch: Any, n_locatio
     ones = {k: torch.ones_like(v) for k, v in lower.items()}
     base = model.masked_forward(weights, batch, masking.ci_masks(ones), clean=clean).output
     B, T = batch.tokens.shape
-    pres, dmg = [], []
+    regions = ("below_zero", "zero_to_one", "above_one")
+    pres, dmg, site_of = [], [], []
     for _ in range(n_locations):
         b, t = int(torch.randint(B, (1,), generator=g)), int(torch.randint(T, (1,), generator=g))
-        for _ in range(n_components):
-            site = dense_sites[int(torch.randint(len(dense_sites), (1,), generator=g))]
-            c = int(torch.randint(site.C, (1,), generator=g))
-            m = {k: v.clone() if k == site.name else v for k, v in ones.items()}
-            m[site.name][b, t, c] = 0.0
-            out = model.masked_forward(weights, batch, masking.ci_masks(m), clean=clean).output
-            a, r = out[b, t].float(), base[b, t].float()
-            dmg.append(float((a - r).pow(2).sum() / r.pow(2).sum().clamp_min(1e-30)))
-            pres.append(float(ci.preactivations[site.name][b, t, c]))
+        pre_here = torch.cat([ci.preactivations[s.name][b, t].float().reshape(-1) for s in dense_sites])
+        owner = torch.cat([torch.full((s.C,), i) for i, s in enumerate(dense_sites)])
+        first = torch.tensor([0] + [s.C for s in dense_sites]).cumsum(0)
+        for region in regions:
+            inside = in_region(pre_here, region).nonzero()[:, 0]
+            take = inside[torch.randperm(inside.numel(), generator=g)[:n_components]]
+            pad = n_components - take.numel()  # a sparse region: its quota is filled with components that do not count
+            padded = torch.cat([take, torch.randint(pre_here.numel(), (pad,), generator=g)]) if pad else take
+            for j, flat in enumerate(padded.tolist()):
+                si = int(owner[flat])
+                site, c = dense_sites[si], flat - int(first[si])
+                m = {k: v.clone() if k == site.name else v for k, v in ones.items()}
+                m[site.name][b, t, c] = 0.0
+                out = model.masked_forward(weights, batch, masking.ci_masks(m), clean=clean).output
+                if j >= take.numel():
+                    continue  # padding: computed, discarded
+                a_, r_ = out[b, t].float(), base[b, t].float()
+                dmg.append(float((a_ - r_).pow(2).sum() / r_.pow(2).sum().clamp_min(1e-30)))
+                pres.append(float(pre_here[flat]))
+                site_of.append(site.name)
     pre_t, dmg_t = torch.tensor(pres), torch.tensor(dmg)
     res = {"WellTemperedness/all": fraction_well_ordered_pairs(pre_t, dmg_t)}
-    for region in ("below_zero", "zero_to_one", "above_one"):
+    for region in regions:
         sel = in_region(pre_t, region)
         res[f"WellTemperedness/{region}"] = fraction_well_ordered_pairs(pre_t[sel], dmg_t[sel])
         res[f"WellTemperedness/{region}/n"] = float(sel.sum())
+    for name, patterns in (groups or {}).items():
+        sel = torch.tensor([any(fnmatch.fnmatch(sn, p) for p in patterns) for sn in site_of], dtype=torch.bool)
+        res[f"WellTemperedness/group/{name}"] = fraction_well_ordered_pairs(pre_t[sel], dmg_t[sel])
+        res[f"WellTemperedness/group/{name}/n"] = float(sel.sum())
     figures.save_figure(run_dir, "well_temperedness_pre_vs_damage",
                         figures.scatter(pre_t.numpy(), np.log10(dmg_t.numpy() + 1e-30)),
                         {"preactivation": pre_t.numpy(), "damage": dmg_t.numpy()})

@@ -30,8 +30,12 @@ def test_router_divergence_and_well_temperedness(tmp_path):
     rd = lm_ops.router_divergence(ctx, state, batch, ("ci_masked", "stochastic"))
     assert "RouterDivergence/ci_masked/kl" in rd and all(math.isfinite(v) for v in rd.values())
     assert all(0.0 <= v <= 1.0 for k, v in rd.items() if "topk_kept" in k)
-    wt = lm_ops.well_temperedness(ctx, state, batch, n_locations=2, n_components=6, run_dir=tmp_path)
+    wt = lm_ops.well_temperedness(ctx, state, batch, n_locations=2, n_components=3, run_dir=tmp_path,
+                                  groups={"attention": ["*self_attn*", "*linear_attn*"], "nothing": ["no_such_site*"]})
     assert 0.0 <= wt["WellTemperedness/all"] <= 1.0
+    n_regions = sum(wt[f"WellTemperedness/{r}/n"] for r in ("below_zero", "zero_to_one", "above_one"))
+    assert 0 < n_regions <= 2 * 3 * 3  # at most locations x regions x quota; padding is discarded
+    assert wt["WellTemperedness/group/nothing/n"] == 0.0 and wt["WellTemperedness/group/attention/n"] <= n_regions
     assert (tmp_path / "figures" / "well_temperedness_pre_vs_damage.png").exists()
 
 
