@@ -48,3 +48,10 @@ def test_gauge_balance_keeps_the_function_and_open_run_restores(tmp_path):
     only = load_run.open_target_and_components(res.run_dir, None, step=meta.steps_saved[0])
     assert only.ci_fn is None and only.step == meta.steps_saved[0]
     assert m1["uv_norm_ratio_mean"] > 0
+    # the stable facts of the run, resolved without a checkpoint (no target tensor is materialised)
+    d = load_run.load_deliverable(res.run_dir)
+    assert [s.name for s in d.sites] == [s.name for s in opened.model.sites] and d.seed == cfg.pd.seed
+    assert all((a.d_in, a.d_out, a.C) == (b.d_in, b.d_out, b.C) for a, b in zip(d.sites, opened.model.sites))
+    assert d.arch.n_layer == opened.model.arch.n_layer and d.data.seq_len == cfg.data.seq_len and d.data.train_dir is None
+    assert d.ci_tap_widths and all(w > 0 for w in d.ci_tap_widths.values())
+
