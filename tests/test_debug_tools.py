@@ -49,3 +49,22 @@ def test_census_counts_collectives(monkeypatch):
         raise RuntimeError("should have refused")
     except AssertionError:
         pass
+
+
+def test_ledger_diff_groups_created_destroyed_resized(tmp_path):
+    from param_decomp_b200.core.debug import ledger_diff
+    from param_decomp_b200.core.debug.memory_ledger import Ledger, Mark
+
+    a = Ledger(marks=[Mark("step", 100, 200, 150, [("(4, 4) float32", 64), ("(8,) float32", 32), ("(8,) float32", 32)]),
+                      Mark("only_a", 1, 1, 1, [])])
+    b = Ledger(marks=[Mark("step", 300, 200, 400, [("(4, 4) float32", 64), ("(8,) float32", 32), ("(16, 16) bfloat16", 512)])])
+    a.save(tmp_path / "a.json"), b.save(tmp_path / "b.json")
+    (d,) = ledger_diff.diff_ledgers(Ledger.load(tmp_path / "a.json"), Ledger.load(tmp_path / "b.json"))
+    assert d.mark == "step" and d.allocated == (100, 300) and d.peak == (150, 400)
+    assert [g.key for g in d.created] == ["(16, 16) bfloat16"] and d.created[0].delta_bytes == 512
+    assert not d.destroyed and [g.key for g in d.resized] == ["(8,) float32"] and d.resized[0].delta_bytes == -32
+    (p,) = ledger_diff.diff_ledgers(a, b, peak_only=True)
+    assert p.mark.startswith("peak (step -> step)")
+    text = ledger_diff.render([d])
+    assert "created" in text and "resized" in text and "+0.0 MiB" in text
+
