@@ -80,13 +80,39 @@ def decomposition_tensors(components: ComponentStacks, ci_fn: nn.Module,
     return out, meta
 
 
+def _stack_extents(components: ComponentStacks) -> dict[str, tuple[int, int]]:
+    """`"V.<key>" / "U.<key>" -> (real entries, padded entries)` of every component stack. Stacks are padded to the
+    multiple the run's layout needs (`ComponentStacks(stack_multiple)`); files hold the real entries only, so a
+    checkpoint written under one padding resumes under another."""
+    out = {}
+    for gname, members in components.groups.items():
+        key = components.param_key(gname)
+        out["V." + key] = out["U." + key] = (len(members), len(members) + components.stack_pads[gname])
+    return out
+
+
+def _strip_stack_pads(extents: dict[str, tuple[int, int]], k: str, v: Tensor) -> Tensor:
+    real, padded = extents.get(k.rsplit("/", 1)[0], (0, 0))
+    return v[:real] if padded > real and v.dim() >= 1 and v.shape[0] == padded else v
+
+
+def _restore_stack_pads(extents: dict[str, tuple[int, int]], k: str, v: Tensor) -> Tensor:
+    real, padded = extents.get(k.rsplit("/", 1)[0], (0, 0))
+    if padded > real and v.dim() >= 1 and v.shape[0] == real:
+        return torch.cat([v, v.new_zeros(padded - real, *v.shape[1:])])
+    return v
+
+
 def training_tensors(state, expert_shard=None) -> tuple[dict[str, Tensor], dict[str, str]]:
     out: dict[str, Tensor] = {"step": torch.tensor(state.step, dtype=torch.int64)}
     uint16_keys = []
+    extents = _stack_extents(state.components)
     for group, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
         for k, v in sorted(opt.state_dict().items()):  # sorted: the gathers below must line up across ranks
             if expert_shard is not None and group == "components" and v.dim() >= 2 and expert_shard.is_split(k):
                 v = expert_shard.gather(v, k)
+            if group == "components":
+                v = _strip_stack_pads(extents, k, v)  # moments of the inert padding matrices never reach the file
             out[f"opt/{group}/{k}"] = _storable(v)
     for term, adv in state.adversaries.items():
         for k, v in adv.state_dict().items():
@@ -185,9 +211,13 @@ def restore_state(run_dir: Path, step: int, state, data_rank: int = 0, data_worl
         return (v.view(torch.uint16) if k in uint16_keys else v).to(dev)
 
     state.step = int(tensors["step"].item())
+    extents = _stack_extents(state.components)
     for group, opt in (("components", state.components_opt), ("ci_fn", state.ci_fn_opt)):
         prefix = f"opt/{group}/"
-        opt.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)})
+        sd = {k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)}
+        if group == "components":  # this run's stacks may be padded differently from the writer's
+            sd = {k: _restore_stack_pads(extents, k, v) for k, v in sd.items()}
+        opt.load_state_dict(sd)
     for term, adv in state.adversaries.items():
         prefix = f"adversaries/{term}/"
         adv.load_state_dict({k[len(prefix):]: get(k) for k in tensors if k.startswith(prefix)}, data_rank, data_world)

@@ -258,3 +258,59 @@ def test_toy_root_runs_data_parallel_and_matches_single_process():
             assert metrics["train/loss/total"] == pytest.approx(res.last_metrics["train/loss/total"], rel=1e-4)
             for a, b in zip(params, states[0].components.parameters()):
                 assert torch.allclose(a, b.detach(), atol=2e-5), float((a - b).abs().max())
+
+
+def _odd_muon_cfg(world: int, steps: int = 4) -> LMExperimentConfig:
+    """Three layers: every stack holds three matrices, padded to four under a two-rank Newton-Schulz split."""
+    c = _muon_cfg(world).model_dump(mode="json")
+    c["target"]["spec"]["arch"]["n_layer"] = 3
+    c["pd"]["steps"] = steps
+    c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "periodic", "save_every": 2, "retention": {"kind": "keep_all"}}}
+    c["eval"] = None
+    return LMExperimentConfig.model_validate(c)
+
+
+def _odd_muon_worker(rank: int, world: int, port: int, root: str, out, run_id: str = "p-0000b0b0", max_steps=3):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    states: list = []
+    # (first entry: checkpoint at step 2, stopped after step 3)
+    res = train_lm(_odd_muon_cfg(world), Path(root), run_id=run_id, device="cpu", max_steps_this_entry=max_steps, state_out=states)
+    st = states[0]
+    out[rank] = (st.components.V["q"].shape[0], st.step, res.last_metrics.get("train/loss/total"),
+                 [p.detach()[:3].clone() for p in st.components.parameters()])
+
+
+def test_padded_stacks_resume_on_another_layout():
+    """Stacks of three matrices are padded to four when two ranks split the Newton-Schulz work; the checkpoint written
+    by that layout holds the three real entries only, so a single process (no padding) resumes it and ends where an
+    uninterrupted single-process run ends."""
+    from param_decomp_b200.core import checkpoint as ckpt
+
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        mp.spawn(_odd_muon_worker, args=(2, _free_port(), root, out), nprocs=2, join=True)
+        assert out[0][:2] == (4, 3) and out[1][:2] == (4, 3)  # padded to the group size while training
+        tensors, _ = ckpt._read(Path(root) / "runs" / "p-0000b0b0" / "ckpts" / "2" / ckpt.TRAINING_FILE)
+        assert tensors["opt/components/V.q/mom"].shape[0] == 3  # pads never reach the file
+        # the same pinned config in a single process: every mesh axis collapses to 1, no padding
+        res, st = _train(_odd_muon_cfg(2), root, "p-0000b0b0")  # resumes at step 2
+        assert st.step == 4 and st.components.V["q"].shape[0] == 3
+        ref_res, ref = _train(_odd_muon_cfg(1), root, "p-0000b0b1")
+        assert res.last_metrics["train/loss/total"] == pytest.approx(ref_res.last_metrics["train/loss/total"], rel=3e-4)
+        for a, b in zip(st.components.parameters(), ref.components.parameters()):
+            assert torch.allclose(a, b, atol=1e-4), float((a - b).abs().max())
+        # and the other way round: a single-process (unpadded) checkpoint resumed by the padded two-rank layout
+        from param_decomp_b200.experiments.lm.training import train_lm
+
+        train_lm(_odd_muon_cfg(2), Path(root), run_id="p-0000b0b2", device="cpu", max_steps_this_entry=3)
+        out2 = mp.Manager().dict()
+        mp.spawn(_odd_muon_worker, args=(2, _free_port(), root, out2, "p-0000b0b2", None), nprocs=2, join=True)
+        for r in range(2):
+            n_stack, step, loss, params = out2[r]
+            assert (n_stack, step) == (4, 4)
+            assert loss == pytest.approx(ref_res.last_metrics["train/loss/total"], rel=3e-4)
+            for a, b in zip(params, ref.components.parameters()):
+                assert torch.allclose(a, b.detach(), atol=1e-4), float((a - b).abs().max())
