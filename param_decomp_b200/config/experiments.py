@@ -656,6 +656,11 @@ class RuntimeConfig(BaseConfig):
     """Addition. How long a kernel that exchanges data with peer GPUs waits for a peer before it gives up and
     reports through the device status word (the engine then stops every rank before the next log line,
     evaluation or checkpoint)."""
+    step_watchdog_s: PositiveFloat | None = None
+    """Addition. When set, a host thread watches the training loop: an iteration (its evaluation and save
+    included) that takes longer than this many seconds is treated as a preemption (all ranks save and exit at
+    the next step boundary); if no boundary is reached within the same time again, the process exits without
+    a checkpoint. Host-side only."""
 
     @model_validator(mode="before")
     @classmethod

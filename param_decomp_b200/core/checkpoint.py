@@ -52,6 +52,33 @@ def latest_step(run_dir: Path) -> int | None:
     return steps[-1] if steps else None
 
 
+def is_readable(run_dir: Path, step: int) -> bool:
+    """Both files of a step open and their headers agree with their sizes (a truncated or half-copied file fails
+    here, before anything is restored from it)."""
+    from safetensors import safe_open
+
+    try:
+        for name in (DECOMPOSITION_FILE, TRAINING_FILE):
+            with safe_open(str(ckpt_root(run_dir) / str(step) / name), framework="pt") as f:
+                for k in f.keys():
+                    f.get_slice(k).get_shape()
+        return True
+    except Exception:  # noqa: BLE001  (any failure to open / parse means: not a usable checkpoint)
+        return False
+
+
+def latest_readable_step(run_dir: Path, log=None) -> int | None:
+    """The newest step whose files can be read; damaged newer ones are named in the log and skipped. Every rank
+    reads the same files, so every rank lands on the same step."""
+    for step in reversed(list_steps(run_dir)):
+        if is_readable(run_dir, step):
+            return step
+        if log is not None:
+            log.warning("checkpoint %s/ckpts/%d is damaged (truncated or unreadable): falling back to an older one",
+                        run_dir, step)
+    return None
+
+
 def _storable(t: Tensor) -> Tensor:
     t = t.detach().cpu().contiguous()
     return t.view(torch.int16) if t.dtype == torch.uint16 else t

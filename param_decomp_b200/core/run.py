@@ -10,6 +10,7 @@ Resume | FineTune start), :747-798 (faithfulness warm-up), :1435-1636 (timed loo
 
 from __future__ import annotations
 
+import os
 import signal
 import threading
 import time
@@ -186,7 +187,7 @@ def _resolve_start(run_dir: Path | None, state: TrainState, cadence: Cadence,
                 refused = bool(any_fn(float(refused)))
             assert not refused, f"{run_dir} ran without checkpoints: re-entering it is refused"
         else:
-            own = ckpt.latest_step(run_dir)
+            own = ckpt.latest_readable_step(run_dir, log)
             if own is not None:
                 ckpt.restore_state(run_dir, own, state, data_rank, data_world)
                 log.info("resumed from %s/ckpts/%d", run_dir, own)
@@ -230,6 +231,7 @@ def run_decomposition_training(
     state_out: list | None = None,
     shard_group: Any = None,
     shard_backend: str | None = None,
+    step_watchdog_s: float | None = None,
     peer_wait_limit_s: float = 30.0,
     record_step: bool = False,
     stack_multiple: int = 1,
@@ -344,9 +346,15 @@ def run_decomposition_training(
         acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
         profiler = profile(activities=acts)
 
+    # A step (or an evaluation / a save between two steps) that takes longer than the limit is treated as a stall:
+    # first as a preemption (the loop saves and exits at its next boundary, all ranks together), then - if no
+    # boundary is reached within another limit - the process leaves without a checkpoint.
+    watchdog = StepWatchdog(step_watchdog_s, on_stall=preempt.set).start() if step_watchdog_s else None
     try:
         while state.step < pd.steps:
             step = state.step
+            if watchdog is not None:
+                watchdog.beat()
             if evaluation is not None and evaluation.is_due(step):
                 check_device_status("before an evaluation")
                 sync_masters(for_save=False)
@@ -387,7 +395,8 @@ def run_decomposition_training(
                          floats.get("train/perf/step_time_s", float("nan")))
 
             if preempt.consensus():
-                log.info("SIGTERM consensus at step %d: saving and exiting", state.step)
+                log.info("%s at step %d: saving and exiting",
+                         "step watchdog fired" if (watchdog is not None and watchdog.fired) else "SIGTERM consensus", state.step)
                 save()
                 result.stopped_by_sigterm = True
                 break
@@ -402,6 +411,8 @@ def run_decomposition_training(
                     sink.log(state.step, ev, prefix="eval/")
             save()
     finally:
+        if watchdog is not None:
+            watchdog.stop()
         stepper.release()  # (also on an exception: a live recording blocks the process group's teardown)
     result.final_step = state.step
     if own_sink and sink is not None:
@@ -410,13 +421,16 @@ def run_decomposition_training(
 
 
 class StepWatchdog:
-    """Host thread that turns a stalled step into a clean abort: if `beat()` is not called for
-    `limit_s`, `on_stall` runs (default: raise SIGTERM in this process so the loop exits at the next
-    boundary, or `os._exit` if it never reaches one)."""
+    """Host thread that turns a stalled step into a clean abort: if `beat()` is not called for `limit_s`,
+    `on_stall` runs (default: raise SIGTERM in this process, which the loop treats as a preemption at its next
+    boundary); if another `limit_s` passes without a beat - the loop never reached a boundary - `on_dead` runs
+    (default: `os._exit(75)`, leaving without a checkpoint). Host-side only: nothing here touches the device."""
 
-    def __init__(self, limit_s: float, on_stall: Callable[[], None] | None = None) -> None:
+    def __init__(self, limit_s: float, on_stall: Callable[[], None] | None = None,
+                 on_dead: Callable[[], None] | None = None) -> None:
         self.limit_s = limit_s
         self.on_stall = on_stall or (lambda: signal.raise_signal(signal.SIGTERM))
+        self.on_dead = on_dead or (lambda: os._exit(75))
         self._last = time.monotonic()
         self._stop = threading.Event()
         self.fired = False
@@ -434,7 +448,10 @@ class StepWatchdog:
 
     def _watch(self) -> None:
         while not self._stop.wait(min(self.limit_s / 4, 1.0)):
-            if time.monotonic() - self._last > self.limit_s:
+            idle = time.monotonic() - self._last
+            if idle > self.limit_s and not self.fired:
                 self.fired = True
                 self.on_stall()
+            elif self.fired and idle > 2 * self.limit_s:
+                self.on_dead()
                 return

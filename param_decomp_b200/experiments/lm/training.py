@@ -134,7 +134,8 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
             shard_group=shard_group, shard_backend=shard_backend, peer_wait_limit_s=cfg.runtime.peer_wait_limit_s,
             record_step=fused and cfg.runtime.step_recording == "cuda_graph",
-            remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn)
+            remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn,
+            step_watchdog_s=cfg.runtime.step_watchdog_s)
     except BaseException:
         if sink is not None:
             sink.close()
@@ -194,6 +195,7 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
         result = run_decomposition_training(
             run.model, run.ci_fn, cfg.pd, cfg.cadence, sample_target, device=topo.device, run_dir=run_dir, sink=sink,
             evaluation=evaluation, collectives=topo.collectives(), nontarget=nontarget,
+            step_watchdog_s=cfg.runtime.step_watchdog_s,
             remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn,
             sample_nontarget_batch=sample_nontarget, batch_rows=max(cfg.pd.batch_size, nt_rows) // topo.data_world,
             positions=max(pool.seq_len, cfg.data.seq_len), units_per_step=(cfg.pd.batch_size * pool.seq_len
