@@ -129,3 +129,53 @@ def test_damaged_and_half_written_checkpoints_are_skipped(tmp_path):
     states: list = []
     res = train_lm(_cfg(steps=6), tmp_path, run_id="p-0000f003", device="cpu", max_steps_this_entry=1, state_out=states)
     assert res.final_step == 3  # resumed from step 2, not from the damaged step 4
+
+
+def _dying_rank_worker(rank: int, world: int, port: int, root: str, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from param_decomp_b200.experiments.lm import training
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    real_build = training.build_lm_run
+
+    def build(*a, **k):
+        run = real_build(*a, **k)
+        sample = run.sample_train
+
+        def failing(step: int):
+            if rank == 1 and step == 3:
+                raise RuntimeError("the data source of rank 1 failed")  # between two steps, nothing in flight
+            return sample(step)
+
+        return run.__class__(**{**run.__dict__, "sample_train": failing})
+
+    training.build_lm_run = build
+    t0 = time.monotonic()
+    try:
+        train_lm(_cfg(steps=1000, world=world, save_every=10**6), Path(root), run_id="p-0000f004", device="cpu")
+        out[rank] = ("finished", time.monotonic() - t0)
+    except BaseException as e:  # noqa: BLE001
+        out[rank] = (type(e).__name__ + ": " + str(e)[:80], time.monotonic() - t0)
+
+
+def test_a_rank_that_raises_between_steps_ends_the_others_quickly():
+    """Rank 1's data source raises before step 3. It leaves without waiting at a barrier; rank 0 learns of it at
+    its next host-side consensus (the peer's connection is gone) and ends with an error within seconds, not after
+    the process group's ten-minute timeout."""
+    with tempfile.TemporaryDirectory() as root:
+        out = mp.Manager().dict()
+        ctx = mp.get_context("spawn")
+        port = _free_port()
+        procs = [ctx.Process(target=_dying_rank_worker, args=(r, 2, port, root, out)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=240)
+        alive = [p.is_alive() for p in procs]
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        assert not any(alive), "a rank was still waiting for its dead peer"
+        assert out[1][0].startswith("RuntimeError: the data source of rank 1 failed")
+        assert out[0][0] != "finished" and out[0][1] < 120, out[0]
