@@ -24,6 +24,7 @@ from pydantic import (
     NonNegativeInt,
     PositiveFloat,
     PositiveInt,
+    Tag,
     field_validator,
     model_validator,
 )
@@ -672,12 +673,47 @@ class RuntimeConfig(BaseConfig):
         return data
 
 
-class LMPromptPoolConfig(BaseConfig):
-    """Target-stream prompts of a targeted (tPD) run: literal prompts or a dataset."""
+class InlinePromptsConfig(BaseConfig):
+    """Addition: target-stream prompts given literally, or drawn from rows of a tokenised dataset. Literal prompts
+    shorter than `seq_len` are left-padded with their first token."""
 
+    kind: Literal["inline"] = "inline"
     prompts: tuple[str, ...] | None = None
     dataset: LMDatasetRef | None = None
     seq_len: PositiveInt | None = None
+
+
+class ArithmeticGridPromptsConfig(BaseConfig):
+    """The `[a_range] x [b_range]` grid (both ends included) of `"<a><op><b>="` prompts as a training pool: the
+    same construction as the `ArithmeticCIGrid` eval probe. Every prompt must tokenise to one length.
+    Parity: param_decomp/experiments/lm/targeted_data.py:20-34."""
+
+    kind: Literal["arithmetic_grid"] = "arithmetic_grid"
+    operation: Literal["add", "sub", "mul"]
+    a_range: tuple[int, int]
+    b_range: tuple[int, int]
+
+
+class PromptsFileConfig(BaseConfig):
+    """One prompt per non-empty line of a text file; every line must tokenise to one length.
+    Parity: param_decomp/experiments/lm/targeted_data.py:37-42."""
+
+    kind: Literal["prompts_file"] = "prompts_file"
+    path: Path
+
+
+def _prompt_pool_kind(v: object) -> str:
+    if isinstance(v, dict):
+        return v.get("kind", "inline")
+    return getattr(v, "kind", "inline")
+
+
+LMPromptPoolConfig = Annotated[
+    Annotated[InlinePromptsConfig, Tag("inline")]
+    | Annotated[ArithmeticGridPromptsConfig, Tag("arithmetic_grid")]
+    | Annotated[PromptsFileConfig, Tag("prompts_file")],
+    Discriminator(_prompt_pool_kind),
+]
 
 
 class LMExperimentConfig(ExperimentConfig):

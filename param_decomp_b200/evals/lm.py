@@ -85,12 +85,34 @@ def attention_pattern_recon(ctx: StepContext, state: TrainState, batch: Any, sto
 
 
 class LMEvaluation:
+    """`encode` (text -> token ids, `experiments/lm/prompt_encoder.py`) builds the operand grid of each
+    `ArithmeticCIGrid` metric on first use; `arithmetic_grid` supplies one ready-made grid instead."""
+
     def __init__(self, cfg: E.EvalConfig, sample_eval: Callable[[int], Any], run_dir: Any = None,
-                 arithmetic_grid: Any = None) -> None:
+                 arithmetic_grid: Any = None, encode: Callable[[str], list[int]] | None = None) -> None:
         self.cfg = cfg
         self.sample = sample_eval
         self.run_dir = run_dir
-        self.arithmetic_grid = arithmetic_grid  # evals.lm_ops.ArithmeticPromptGrid (needs the target's tokenizer)
+        self.arithmetic_grid = arithmetic_grid
+        self.encode = encode
+        self._grids: dict[tuple, Any] = {}
+        if encode is not None and arithmetic_grid is None:  # refuse unequal prompt lengths at startup, not at step N
+            for m in cfg.metrics:
+                if isinstance(m, E.ArithmeticCIGridConfig):
+                    self._grid_for(m)
+
+    def _grid_for(self, metric: E.ArithmeticCIGridConfig) -> Any:
+        if self.arithmetic_grid is not None:
+            return self.arithmetic_grid
+        assert self.encode is not None, "ArithmeticCIGrid needs a prompt encoder (LMEvaluation(encode=...))"
+        from param_decomp_b200.evals import lm_ops
+
+        key = (metric.operation, tuple(metric.a_range), tuple(metric.b_range))
+        if key not in self._grids:
+            self._grids[key] = lm_ops.build_arithmetic_prompt_grid(
+                self.encode, lm_ops.inclusive_range(metric.a_range), lm_ops.inclusive_range(metric.b_range),
+                metric.operation)
+        return self._grids[key]
 
     def is_due(self, step: int) -> bool:
         return any(self.cfg.is_due(m, step) for m in self.cfg.metrics)
@@ -115,8 +137,8 @@ class LMEvaluation:
             return lm_ops.well_temperedness(ctx, state, batch, metric.n_locations,
                                             int(extra.get("n_components", metric.n_components_per_region)),
                                             run_dir=self.run_dir, groups=metric.groups)
-        if isinstance(metric, E.ArithmeticCIGridConfig) and self.arithmetic_grid is not None:
-            return lm_ops.arithmetic_ci_grid(ctx, state, self.arithmetic_grid, metric.top_k, run_dir=self.run_dir,
+        if isinstance(metric, E.ArithmeticCIGridConfig):
+            return lm_ops.arithmetic_ci_grid(ctx, state, self._grid_for(metric), metric.top_k, run_dir=self.run_dir,
                                              thresholds=tuple(metric.thresholds), probe_metrics=metric.probe_metrics)
         return {}
 

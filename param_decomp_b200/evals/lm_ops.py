@@ -225,6 +225,13 @@ class ArithmeticPromptGrid:
     answers: list[int]
 
 
+def inclusive_range(bounds: tuple[int, int]) -> list[int]:
+    """`(lo, hi)` of a config's `a_range` / `b_range` as the operand list `lo..hi`, both ends included."""
+    vals = list(range(int(bounds[0]), int(bounds[1]) + 1))
+    assert vals, f"empty operand range {bounds}"
+    return vals
+
+
 def build_arithmetic_prompt_grid(encode: Callable[[str], list[int]], a_values: list[int], b_values: list[int],
                                  operation: str = "add", modulus: int | None = None) -> ArithmeticPromptGrid:
     """`"<a><symbol><b>="` prompts, one per row, all rows one shared token length (refused otherwise:

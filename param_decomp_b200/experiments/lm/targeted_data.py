@@ -1,9 +1,11 @@
 """The target stream of a targeted (tPD) run: a fixed pool of prompts, sampled by a pure function of
 (seed, step) so every rank and every resume sees the same batches.
 
-Pool sources: literal prompts (tokenised by the target's tokenizer, or by a byte-level encoder when the
-target has none, e.g. random-init targets), a dataset reference (rows of the tokenised store), or an
-arithmetic operand grid (`evals/lm_ops.build_arithmetic_prompt_grid`). All rows share one length.
+Pool sources: an arithmetic operand grid (`kind: arithmetic_grid`, the construction of
+`evals/lm_ops.build_arithmetic_prompt_grid`), a text file with one prompt per line (`kind: prompts_file`), and
+two additions under `kind: inline`: literal prompts and rows of a tokenised dataset. Text is tokenised by the
+encoder `experiments/lm/prompt_encoder.py` finds (the target's tokenizer files, else bytes). All rows share
+one length.
 Parity: param_decomp/experiments/lm/targeted_data.py:1-92, arithmetic_probe.py.
 """
 
@@ -36,8 +38,22 @@ class PromptPool:
     @classmethod
     def build(cls, cfg: Any, vocab_size: int, data_root: Path | None, seed: int,
               encode: Callable[[str], list[int]] | None = None) -> "PromptPool":
+        kind = getattr(cfg, "kind", "inline")
+        enc = encode or byte_encoder(vocab_size)
+        if kind == "arithmetic_grid":
+            from param_decomp_b200.evals.lm_ops import build_arithmetic_prompt_grid, inclusive_range
+
+            grid = build_arithmetic_prompt_grid(enc, inclusive_range(cfg.a_range), inclusive_range(cfg.b_range),
+                                                cfg.operation)
+            return cls(grid.tokens, seed)
+        if kind == "prompts_file":
+            lines = [ln for ln in Path(cfg.path).read_text().splitlines() if ln.strip()]
+            assert lines, f"no prompts in {cfg.path}"
+            rows = [enc(ln) for ln in lines]
+            lengths = sorted({len(r) for r in rows})
+            assert len(lengths) == 1, f"prompts must tokenise to one shared length, got {lengths}"
+            return cls(torch.tensor(rows, dtype=torch.int64), seed)
         if cfg.prompts is not None:
-            enc = encode or byte_encoder(vocab_size)
             rows = [enc(p) for p in cfg.prompts]
             L = cfg.seq_len or max(len(r) for r in rows)
             assert all(len(r) <= L for r in rows), "a prompt is longer than prompts.seq_len"

@@ -120,7 +120,10 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     from param_decomp_b200.evals.lm import LMEvaluation
     from param_decomp_b200.utils.flops import decomposition_step_flops
 
-    evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir) if cfg.eval is not None else None
+    evaluation = None
+    if cfg.eval is not None:
+        evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir,
+                                  encode=prompt_encoder_for(cfg, data_root, run.arch.vocab_size, log))
     fused = getattr(run.model, "backend", "") == "fused_sm100"
     flops = decomposition_step_flops(run.model, run.ci_fn, cfg.pd, cfg.data.seq_len)
     try:
@@ -147,6 +150,20 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
     return result
 
 
+def prompt_encoder_for(cfg, data_root: Path | None, vocab_size: int, log=None):
+    """The run's text-to-token encoder, needed only when something builds prompts from text: an
+    `ArithmeticCIGrid` metric or a text prompt pool. Otherwise None, and no tokenizer is looked for."""
+    from param_decomp_b200.config.evals import ArithmeticCIGridConfig
+    from param_decomp_b200.experiments.lm.prompt_encoder import resolve_prompt_encoder
+
+    wants = cfg.eval is not None and any(isinstance(m, ArithmeticCIGridConfig) for m in cfg.eval.metrics)
+    pool = getattr(cfg, "prompts", None)
+    wants = wants or (pool is not None and (pool.kind != "inline" or pool.prompts is not None))
+    if not wants:
+        return None
+    return resolve_prompt_encoder(cfg.target.spec, cfg.data.train, data_root, vocab_size, log)
+
+
 def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, run_id: str | None = None,
                       device: str | None = None, max_steps_this_entry: int | None = None,
                       state_out: list | None = None, encode=None) -> RunResult:
@@ -165,6 +182,8 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
     run = build_lm_run(cfg, data_root, topo.device, topo.data_rank, topo.data_world, expert_group=expert_group_of(topo),
                        expert_mode=mode)
     apply_sequence_sharding(cfg, run.model, topo, log)
+    if encode is None:
+        encode = prompt_encoder_for(cfg, data_root, run.arch.vocab_size, log)
     pool = PromptPool.build(cfg.prompts, run.arch.vocab_size, data_root, cfg.pd.seed, encode=encode)
     n_target_terms = len(build_objective(cfg.pd).recon)
     nontarget = build_nontarget_objective(cfg.nontarget, first_index=n_target_terms)
@@ -189,7 +208,9 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
         log.info("run dir %s", run_dir)
     from param_decomp_b200.evals.lm import LMEvaluation
 
-    evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir) if cfg.eval is not None else None
+    evaluation = None
+    if cfg.eval is not None:
+        evaluation = LMEvaluation(cfg.eval, run.sample_eval, run_dir=run_dir, encode=encode)
     fused = getattr(run.model, "backend", "") == "fused_sm100"
     try:
         result = run_decomposition_training(

@@ -49,3 +49,70 @@ def test_targeted_lm_runs(tmp_path):
     assert res.final_step == 3
     lines = (res.run_dir / "metrics.jsonl").read_text().strip().splitlines()
     assert lines and "loss/total" in lines[-1]
+
+
+def test_reference_prompt_pool_kinds(tmp_path):
+    """`kind: arithmetic_grid` and `kind: prompts_file`, the two pool forms of the reference's targeted configs."""
+    base = _targeted_config().model_dump(mode="json")
+    base["prompts"] = {"kind": "arithmetic_grid", "operation": "add", "a_range": [1, 4], "b_range": [1, 5]}
+    cfg = LMTargetedExperimentConfig.model_validate(base)
+    pool = PromptPool.build(cfg.prompts, 131, None, seed=0)
+    assert pool.tokens.shape == (20, 4)  # "a+b=" is four bytes for one-digit operands; 4 x 5 prompts, both ends in
+    assert pool.tokens[0].tolist() == byte_encoder(131)("1+1=") and pool.tokens[-1].tolist() == byte_encoder(131)("4+5=")
+
+    path = tmp_path / "prompts.txt"
+    path.write_text("abcd\n\nwxyz\n")
+    base["prompts"] = {"kind": "prompts_file", "path": str(path)}
+    cfg = LMTargetedExperimentConfig.model_validate(base)
+    assert PromptPool.build(cfg.prompts, 131, None, seed=0).tokens.shape == (2, 4)
+    path.write_text("abcd\nabc\n")
+    try:
+        PromptPool.build(cfg.prompts, 131, None, seed=0)
+        raise RuntimeError("unequal prompt lengths were accepted")
+    except AssertionError as e:
+        assert "one shared length" in str(e)
+
+
+def test_prompt_encoder_prefers_staged_tokenizer_files(tmp_path):
+    """A tokenizer staged beside the target's snapshot is used; without one the encoder falls back to bytes."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from param_decomp_b200.config.experiments import HFTarget
+    from param_decomp_b200.experiments.lm.prompt_encoder import resolve_prompt_encoder
+
+    spec = HFTarget(model_class="LlamaForCausalLM", model_name="org/tiny")
+    assert resolve_prompt_encoder(spec, None, tmp_path, 131).source == "bytes"
+
+    vocab = {c: i for i, c in enumerate("0123456789+-*=")}
+    vocab["[UNK]"] = len(vocab)
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", "isolated")
+    snap = tmp_path / "hf_snapshots" / "org--tiny"
+    snap.mkdir(parents=True)
+    PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="[UNK]").save_pretrained(str(snap))
+    enc = resolve_prompt_encoder(spec, None, tmp_path, 131)
+    assert enc.source == str(snap)
+    assert enc("12+3=") == [1, 2, 10, 3, 13]
+
+
+def test_arithmetic_grid_metric_is_built_from_the_run_encoder(tmp_path):
+    """An `ArithmeticCIGrid` metric in a training config is evaluated (its grid built from the run's encoder), and
+    operand ranges whose prompts differ in length are refused when the run starts."""
+    base = _targeted_config().model_dump(mode="json")
+    base["eval"] = {"batch_size": 2, "n_steps": 1, "every": 2, "slow_every": 2,
+                    "metrics": [{"type": "ArithmeticCIGrid", "operation": "add", "a_range": [1, 3], "b_range": [1, 3],
+                                 "top_k": 2}]}
+    base["pd"]["steps"] = 2
+    cfg = LMTargetedExperimentConfig.model_validate(base)
+    res = train_lm_targeted(cfg, tmp_path, device="cpu")
+    text = (res.run_dir / "metrics.jsonl").read_text()
+    assert "ArithmeticCIGrid/" in text and "n_alive" in text
+
+    base["eval"]["metrics"][0]["a_range"] = [1, 12]
+    cfg = LMTargetedExperimentConfig.model_validate(base)
+    try:
+        train_lm_targeted(cfg, tmp_path, device="cpu")
+        raise RuntimeError("a grid with unequal prompt lengths was accepted")
+    except AssertionError as e:
+        assert "different lengths" in str(e)
