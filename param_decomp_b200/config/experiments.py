@@ -607,13 +607,32 @@ class ProfilingDisabled(BaseConfig):
 
 
 class AdHocProfiling(BaseConfig):
+    """An in-process `torch.profiler` run: after a warm-up (long enough for the step to have been recorded into
+    its CUDA graph, where it is) the trainer traces `steps` steps into `<run_dir>/profile/trace.json` and exits:
+    a measurement, not a trajectory. Parity: param_decomp/experiments/lm/runtime.py:247-254."""
+
     kind: Literal["ad_hoc"] = "ad_hoc"
-    n_steps: PositiveInt = 3
+    steps: PositiveInt = 3
+
+    @model_validator(mode="before")
+    @classmethod
+    def _old_key(cls, data: object) -> object:
+        if isinstance(data, dict) and "n_steps" in data and "steps" not in data:
+            data = {**data, "steps": data["n_steps"]}
+            data.pop("n_steps")
+        return data
 
 
 class NsightSystemsProfiling(BaseConfig):
+    """For a run launched under an external `nsys profile --capture-range=cudaProfilerApi`: the trainer brackets
+    `capture_steps` steps after `warmup_steps` with the CUDA profiler start / stop calls (one NVTX range per
+    step) and exits. Without an attached profiler the calls do nothing.
+    Parity: param_decomp/experiments/lm/runtime.py:257-262."""
+
     kind: Literal["nsight_systems"] = "nsight_systems"
     version: str = "2026.4.1"
+    warmup_steps: NonNegativeInt = 5
+    capture_steps: PositiveInt = 3
 
 
 ProfilingConfig = Annotated[ProfilingDisabled | AdHocProfiling | NsightSystemsProfiling, Discriminator("kind")]

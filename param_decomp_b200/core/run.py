@@ -81,6 +81,59 @@ class PreemptionFlag:
         return bool(any_fn(local)) if any_fn is not None else bool(local)
 
 
+class StepProfiler:
+    """Profiles `n_steps` training steps after `warmup` steps of this entry, then asks the loop to stop.
+
+    `trace`: an in-process `torch.profiler` trace written to `<run_dir>/profile/trace.json`.
+    `cuda_profiler_range`: the CUDA profiler start / stop calls around the captured steps, one NVTX range per
+    step, for an external profiler attached with a capture range on that API; nothing is written here."""
+
+    def __init__(self, kind: str, warmup: int, n_steps: int, run_dir: Any) -> None:
+        assert kind in ("trace", "cuda_profiler_range"), kind
+        self.kind, self.warmup, self.n_steps, self.run_dir = kind, warmup, n_steps, run_dir
+        self._trace: Any = None
+        self._range_open = False
+        self.captured: list[int] = []
+
+    def before_step(self, entry_step: int) -> None:
+        if entry_step < self.warmup:
+            return
+        cuda = torch.cuda.is_available()
+        if entry_step == self.warmup:
+            if self.kind == "trace":
+                from torch.profiler import ProfilerActivity, profile
+
+                acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if cuda else [])
+                self._trace = profile(activities=acts)
+                self._trace.start()
+            elif cuda:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
+        if self.kind == "cuda_profiler_range" and cuda:
+            torch.cuda.nvtx.range_push(f"train_step_{entry_step}")
+            self._range_open = True
+        self.captured.append(entry_step)
+
+    def after_step(self, entry_step: int) -> bool:
+        """True once the last captured step has run (the loop then leaves)."""
+        if entry_step < self.warmup:
+            return False
+        if self._range_open:
+            torch.cuda.nvtx.range_pop()
+            self._range_open = False
+        if entry_step < self.warmup + self.n_steps - 1:
+            return False
+        if self.kind == "trace":
+            self._trace.stop()
+            out = Path(self.run_dir) / "profile"
+            out.mkdir(parents=True, exist_ok=True)
+            self._trace.export_chrome_trace(str(out / "trace.json"))
+        elif torch.cuda.is_available():
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        return True
+
+
 # ---- state ------------------------------------------------------------------------------------------
 
 
@@ -228,6 +281,8 @@ def run_decomposition_training(
     extra_log: Callable[[int, TrainState, StepContext], dict[str, Any]] | None = None,
     max_steps_this_entry: int | None = None,
     profile_steps: int = 0,
+    profile_warmup: int | None = None,
+    profile_kind: str = "trace",
     state_out: list | None = None,
     shard_group: Any = None,
     shard_backend: str | None = None,
@@ -340,11 +395,10 @@ def run_decomposition_training(
     result = RunResult(final_step=state.step, stopped_by_sigterm=False, run_dir=run_dir)
     entry_steps = 0
     profiler = None
-    if profile_steps > 0 and run_dir is not None:
-        from torch.profiler import ProfilerActivity, profile
-
-        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
-        profiler = profile(activities=acts)
+    if profile_steps > 0 and (run_dir is not None or profile_kind == "cuda_profiler_range"):
+        # warm-up: past the eager steps that precede the recording of the step, so the trace shows the steady state
+        warm = profile_warmup if profile_warmup is not None else (5 if stepper.eligible else 2)
+        profiler = StepProfiler(profile_kind, warm, profile_steps, run_dir)
 
     # A step (or an evaluation / a save between two steps) that takes longer than the limit is treated as a stall:
     # first as a preemption (the loop saves and exits at its next boundary, all ranks together), then - if no
@@ -366,13 +420,10 @@ def run_decomposition_training(
 
             batch = sample_batch(step)
             nt_batch = sample_nontarget_batch(step) if sample_nontarget_batch is not None else None
-            if profiler is not None and entry_steps == 2:
-                profiler.start()
+            if profiler is not None:
+                profiler.before_step(entry_steps)
             metrics = stepper(batch, nt_batch)
-            if profiler is not None and entry_steps == 2 + profile_steps - 1:
-                profiler.stop()
-                (Path(run_dir) / "profile").mkdir(parents=True, exist_ok=True)  # type: ignore[arg-type]
-                profiler.export_chrome_trace(str(Path(run_dir) / "profile" / "trace.json"))  # type: ignore[arg-type]
+            if profiler is not None and profiler.after_step(entry_steps):
                 break
             entry_steps += 1
 

@@ -134,7 +134,7 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
             units_per_step=run.tokens_per_step, flops_per_step=flops / topo.world, peak_flops=device_peak_flops(),
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
             max_steps_this_entry=max_steps_this_entry, state_out=state_out, stack_multiple=lay.stack_multiple,
-            profile_steps=3 if cfg.runtime.profiling.kind == "ad_hoc" else 0,
+            **profiling_arguments(cfg.runtime.profiling),
             shard_group=shard_group, shard_backend=shard_backend, peer_wait_limit_s=cfg.runtime.peer_wait_limit_s,
             record_step=fused and cfg.runtime.step_recording == "cuda_graph",
             remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn,
@@ -148,6 +148,16 @@ def train_lm(cfg: LMExperimentConfig, data_root: Path | None, run_id: str | None
         sink.close()
     topo.shutdown()
     return result
+
+
+def profiling_arguments(profiling) -> dict:
+    """`runtime.profiling` as the engine's `profile_*` arguments."""
+    if profiling.kind == "ad_hoc":
+        return dict(profile_steps=profiling.steps, profile_kind="trace")
+    if profiling.kind == "nsight_systems":
+        return dict(profile_steps=profiling.capture_steps, profile_warmup=profiling.warmup_steps,
+                    profile_kind="cuda_profiler_range")
+    return {}
 
 
 def prompt_encoder_for(cfg, data_root: Path | None, vocab_size: int, log=None):
