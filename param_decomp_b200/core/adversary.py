@@ -213,17 +213,27 @@ class PersistentAdversary:
 # ---- fresh PGD -----------------------------------------------------------------------------------
 
 
-def fresh_sources(sites: tuple[SiteSpec, ...], init: str, shape: str, batch: int, positions: int | None,
-                  key: StepKey, term: int, device: torch.device | str) -> dict[str, Tensor]:
-    lead = source_lead_shape(shape, batch, positions)
+def fresh_source_rows(shape: str, batch: int, positions: int | None) -> int:
+    """Rows of one rank's fresh sources once the leading axes are flattened (what `row_offset` counts in)."""
     rows = 1
-    for n in lead:
+    for n in source_lead_shape(shape, batch, positions):
         rows *= n
+    return rows
+
+
+def fresh_sources(sites: tuple[SiteSpec, ...], init: str, shape: str, batch: int, positions: int | None,
+                  key: StepKey, term: int, device: torch.device | str, row_offset: int = 0) -> dict[str, Tensor]:
+    """`batch` is this rank's share of the global batch. Per-row shapes draw their random initial values at the
+    GLOBAL row (`row_offset` = this rank's first flattened row), so the sources of a job do not depend on how
+    many ranks split its batch; batch-shared (`c`) sources are the same draw on every rank."""
+    lead = source_lead_shape(shape, batch, positions)
+    rows = fresh_source_rows(shape, batch, positions)
+    off = 0 if shape == "c" else row_offset
     out = {}
     for i, s in enumerate(sites):
         for prefix, width, sub in (("", s.C, 0), ("d:", 1, 1)):
             if init == "random":
-                v = rng.uniform(key, StepKey.stream(rng.PURPOSE_SOURCE_INIT, term, 2 + sub, i), rows, width, 0, device)
+                v = rng.uniform(key, StepKey.stream(rng.PURPOSE_SOURCE_INIT, term, 2 + sub, i), rows, width, off, device)
             elif init == "ones":
                 v = torch.ones(rows, width, device=device)
             else:

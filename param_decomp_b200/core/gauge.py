@@ -8,6 +8,8 @@ Parity: param_decomp/core/gauge.py (activations), core/train.py:234-261 (norm-ra
 
 from __future__ import annotations
 
+from typing import Any
+
 import torch
 from torch import Tensor
 
@@ -29,18 +31,26 @@ def gauge_variant_activation(invariant: Tensor, u_norm: Tensor) -> Tensor:
 
 
 @torch.no_grad()
-def uv_norm_ratio_metrics(components: ComponentStacks) -> dict[str, float]:
-    """Per site `||U||_F / ||V||_F`, plus mean and max: drift of the pair's scale during training."""
-    out: dict[str, float] = {}
-    ratios = []
-    for s in components.sites:
-        V, U = components.site(s.name)
-        r = float(torch.sqrt(U.float().pow(2).sum() / V.float().pow(2).sum().clamp_min(1e-30)))
-        out[f"uv_norm_ratio['{s.name}']"] = r
-        ratios.append(r)
-    if ratios:
-        out["uv_norm_ratio_mean"] = sum(ratios) / len(ratios)
-        out["uv_norm_ratio_max"] = max(ratios)
+def uv_norm_ratio_metrics(components: ComponentStacks, shard: Any = None) -> dict[str, float]:
+    """Per site `||U||_F / ||V||_F`, plus mean and max: drift of the pair's scale during training.
+    `shard` (`parallel/expert_shard.py::StackSharding`): stacks it marks as split hold only this rank's experts or
+    component slice, so their sums of squares are added over its group before the ratio is taken."""
+    if not components.sites:
+        return {}
+    sq = torch.stack([torch.stack([U.float().pow(2).sum(), V.float().pow(2).sum()])
+                      for V, U in (components.site(s.name) for s in components.sites)])  # [sites, (U, V)]
+    if shard is not None:
+        import torch.distributed as dist
+
+        split = torch.tensor([ComponentStacks.param_key(s.group) in shard.blocked_keys for s in components.sites],
+                             device=sq.device)
+        total = sq.clone()
+        dist.all_reduce(total, group=shard.group)
+        sq = torch.where(split[:, None], total, sq)
+    ratios = torch.sqrt(sq[:, 0] / sq[:, 1].clamp_min(1e-30)).tolist()
+    out = {f"uv_norm_ratio['{s.name}']": r for s, r in zip(components.sites, ratios)}
+    out["uv_norm_ratio_mean"] = sum(ratios) / len(ratios)
+    out["uv_norm_ratio_max"] = max(ratios)
     return out
 
 

@@ -435,7 +435,7 @@ def run_decomposition_training(
 
                 if hasattr(state.components_opt, "refresh_full_fp32"):
                     state.components_opt.refresh_full_fp32()  # sharded masters: gather the shards before reading
-                scalars.update(uv_norm_ratio_metrics(state.components))  # drift of the V/U scale symmetry
+                scalars.update(uv_norm_ratio_metrics(state.components, expert_shard))  # drift of the V/U scale symmetry
                 if extra_log is not None:
                     scalars.update(extra_log(step, state, ctx))
                 scalars = collectives.average_scalars(scalars)  # per-batch losses: the global-batch mean, as the reference logs

@@ -652,8 +652,9 @@ def fresh_pgd_sources(ctx: StepContext, term: ReconTerm, weights: ComputeWeights
     lead = _lead_of(ci_lower)
     positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None
     device = next(iter(ci_lower.values())).device
+    off = ctx.collectives.row_offset(adv_mod.fresh_source_rows(cfg.source_shape, lead[0], positions))  # type: ignore[attr-defined]
     leaves = adv_mod.fresh_sources(getattr(ctx.model, "global_sites", ctx.model.sites), cfg.init, cfg.source_shape, lead[0], positions, key,  # type: ignore[attr-defined]
-                                   term.index, device)
+                                   term.index, device, row_offset=off)
     w_d, ci_d = _detach_weights(weights), _detach_ci(ci_lower)
     for _ in range(cfg.n_steps):  # type: ignore[attr-defined]
         masks = build_masks(ctx, term, ci_d, key, 0, leaves, None, step)

@@ -68,8 +68,9 @@ def fresh_pgd_recon(ctx: StepContext, state: TrainState, batch: Any, step_size: 
     lead = tuple(next(iter(ci_lower.values())).shape[:-1])
     positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None
     device = next(iter(ci_lower.values())).device
+    off = ctx.collectives.row_offset(adv_mod.fresh_source_rows(source_shape, lead[0], positions))
     leaves = adv_mod.fresh_sources(getattr(ctx.model, "global_sites", ctx.model.sites), init, source_shape, lead[0],
-                                   positions, key, 15, device)
+                                   positions, key, 15, device, row_offset=off)
     from types import SimpleNamespace
 
     term = ReconTerm(name="eval_pgd", index=15, strategy="fresh_pgd",

@@ -1,0 +1,173 @@
+"""`python -m param_decomp_b200.experiments.lm.invariance_check --world 4 --steps 3 [--tp 2] [--sharding zero1] [--device cuda]`
+
+Rank-count invariance of the trainer on a tiny Llama target: the SAME global batch, seed and objective run once
+in one process and once as `world` data-parallel ranks (gloo on CPU; NCCL with `--device cuda`, one GPU per rank),
+and every logged metric of every step must agree up to floating-point reassociation (relative 1e-4 in fp32:
+the cross-rank reduction order differs, so bitwise equality is not expected for batch-reduced terms). The
+final component matrices are compared too. That is the correctness contract of a layout: how the batch and the
+optimizer state are split must not show in the trajectory. Masks and adversary sources are drawn from a
+counter-based generator keyed on (seed, step, site, GLOBAL row), so the stochastic terms see the same values.
+
+The objective covers the terms whose reductions cross ranks: importance minimality (global-batch mean inside
+the logarithm), stochastic reconstruction, a persistent and a fresh adversary, faithfulness.
+
+Parity: param_decomp/targets/invariance_check.py:1-311 (one layout against all devices of the host).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import sys
+import tempfile
+from pathlib import Path
+from typing import Any
+
+import torch
+import torch.multiprocessing as mp
+
+from param_decomp_b200.config.experiments import LMExperimentConfig
+
+LOSSES = [
+    {"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 1.0},
+    {"type": "StochasticReconLoss", "coeff": 1.0},
+    {"type": "PersistentPGDReconLoss", "coeff": 0.5, "source_shape": "bsc", "n_warmup_steps": 1,
+     "optimizer": {"type": "sgd", "lr_schedule": 0.05}},
+    {"type": "PGDReconLoss", "coeff": 0.5, "init": "random", "source_shape": "bc", "n_steps": 2, "step_size": 0.1},
+    {"type": "FaithfulnessLoss", "coeff": 10.0},
+]
+
+
+def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1) -> LMExperimentConfig:
+    raw: dict[str, Any] = {
+        "run_name": "invariance",
+        "pd": {"seed": 0, "steps": steps, "batch_size": batch,
+               "components_optimizer": {"lr_schedule": 1e-3, "grad_clip_norm": 1.0},
+               "ci_fn_optimizer": {"lr_schedule": 1e-3, "grad_clip_norm": 1.0},
+               "loss_metrics": LOSSES},
+        "cadence": {"train_log_every": 1, "checkpointing": {"kind": "none"}},
+        "runtime": {"mesh": {"replicate": 1, "fsdp": world // tp, "tp": tp}, "sharding": sharding,
+                    "backend": "fused_sm100" if cuda else "eager_torch"},
+        "target": {"spec": {"kind": "random_init", "seed": 0,
+                            "arch": {"family": "glu_transformer", "n_layer": 2, "d_model": 256 if cuda else 64,
+                                     "n_head": 4 if cuda else 2, "d_ff": 512 if cuda else 128,
+                                     "vocab_size": 2000 if cuda else 256}},
+                   "attention_implementation": "flash" if cuda else "xla",
+                   "output_edge": {"kind": "materialized"}, "weights_dtype": "bfloat16" if cuda else "float32"},
+        "decomposition": {"sites": {"kind": "glu_transformer", "layers": {"kind": "all"},
+                                    "cs": {k: (256 if cuda else 64) for k in ("q", "o", "gate", "down")}},
+                          "ci": {"type": "layerwise_mlp", "hidden_dims": [32]}},
+        "data": {"train": {"kind": "synthetic_zipf"}, "eval": {"kind": "synthetic_zipf", "seed": 1},
+                 "layout": "unsegmented_tokens", "seq_len": 128 if cuda else 16},
+    }
+    return LMExperimentConfig.model_validate(raw)
+
+
+def _run(cfg: LMExperimentConfig, root: Path, run_id: str, device: str) -> tuple[Path, list[torch.Tensor]]:
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    states: list = []
+    res = train_lm(cfg, root, run_id=run_id, device=device, state_out=states)
+    st = states[0]
+    return res.run_dir, [p.detach().float().cpu() for p in st.components.parameters()]
+
+
+def _rank(rank: int, world: int, port: int, root: str, raw: str, cuda: bool, out: Any) -> None:
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(max(1, (os.cpu_count() or world) // world))
+    cfg = LMExperimentConfig.model_validate_json(raw)
+    run_dir, params = _run(cfg, Path(root), "p-00000002", f"cuda:{rank}" if cuda else "cpu")
+    if rank == 0:
+        out["run_dir"] = str(run_dir)
+        out["params"] = params
+
+
+def trajectory(run_dir: Path) -> dict[int, dict[str, float]]:
+    steps: dict[int, dict[str, float]] = {}
+    for line in (Path(run_dir) / "metrics.jsonl").read_text().splitlines():
+        rec = json.loads(line)
+        vals = {k: float(v) for k, v in rec.items() if k != "step" and isinstance(v, (int, float))}
+        steps.setdefault(int(rec["step"]), {}).update(vals)
+    return steps
+
+
+# wall-clock and memory readings differ between any two runs
+UNCOMPARED = ("perf/", "time/", "mem/", "throughput", "tokens_per_s", "mfu", "step_ms", "elapsed", "lr/")
+
+
+def compare(one: dict[int, dict[str, float]], many: dict[int, dict[str, float]], rtol: float, atol: float) -> list[str]:
+    bad: list[str] = []
+    assert one.keys() == many.keys(), (sorted(one), sorted(many))
+    for step in sorted(one):
+        keys = [k for k in one[step] if not any(u in k for u in UNCOMPARED)]
+        for k in keys:
+            if k not in many[step]:
+                bad.append(f"step {step} {k}: missing in the multi-rank run")
+                continue
+            a, b = one[step][k], many[step][k]
+            # a gradient norm is a sum of cancelling terms behind kinked functions (hard sigmoid, sign ascent):
+            # reassociation noise is amplified there, so it gets ten times the tolerance of a loss
+            tol = rtol * (10.0 if "grad_norm" in k else 1.0)
+            if abs(a - b) > atol + tol * max(abs(a), abs(b)):
+                bad.append(f"step {step} {k}: {a:.8g} (1 rank) vs {b:.8g}")
+    return bad
+
+
+def check(world: int, steps: int, sharding: str, batch: int, device: str, rtol: float | None = None,
+          verbose: bool = True, tp: int = 1) -> list[str]:
+    """`tp` of the `world` ranks see the same tokens and split every site's component axis; the remaining
+    `world // tp` split the batch."""
+    cuda = device == "cuda"
+    if cuda:
+        assert torch.cuda.device_count() >= world, f"--device cuda needs {world} GPUs"
+    rtol = rtol if rtol is not None else (3e-2 if cuda else 1e-4)  # bf16 operands on the GPU path
+    assert world % tp == 0 and batch % (world // tp) == 0, (batch, world, tp)
+    with tempfile.TemporaryDirectory() as root:
+        one_dir, one_params = _run(tiny_config(1, steps, sharding, batch, cuda), Path(root), "p-00000001",
+                                   "cuda:0" if cuda else "cpu")
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        out = mp.Manager().dict()
+        mp.spawn(_rank, args=(world, port, root, tiny_config(world, steps, sharding, batch, cuda, tp).model_dump_json(),
+                              cuda, out), nprocs=world, join=True)
+        a, b = trajectory(one_dir), trajectory(Path(out["run_dir"]))
+        bad = compare(a, b, rtol, 1e-6)
+        for i, (p, q) in enumerate(zip(one_params, out["params"])):
+            q = q[: p.shape[0]]  # stacks are padded to a multiple of the rank count
+            p = p[tuple(slice(0, n) for n in q.shape)]  # under `tp`, rank 0 holds the leading slice of the component axis
+            err = float((p - q).abs().max() / p.abs().max().clamp_min(1e-12))
+            if err > 10 * rtol:
+                bad.append(f"component stack {i}: max relative difference {err:.3g}")
+        if verbose:
+            last = max(a)
+            for k in sorted(a[last]):
+                if k in b[last] and not any(u in k for u in UNCOMPARED):
+                    print(f"  step {last} {k:55s} {a[last][k]: .8g} {b[last][k]: .8g}")
+    return bad
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[1])
+    ap.add_argument("--world", type=int, default=2)
+    ap.add_argument("--tp", type=int, default=1, help="ranks that share tokens and split the component axis")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--sharding", default="ddp")
+    ap.add_argument("--device", choices=("cpu", "cuda"), default="cpu")
+    ap.add_argument("--rtol", type=float, default=None)
+    a = ap.parse_args()
+    bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp)
+    if bad:
+        print(f"NOT invariant over {a.world} ranks ({a.sharding}):")
+        for line in bad:
+            print("  " + line)
+        sys.exit(1)
+    print(f"invariant: 1 rank == {a.world} ranks ({a.sharding}, {a.steps} steps)")
+
+
+if __name__ == "__main__":
+    main()
