@@ -1,4 +1,5 @@
-"""`python -m param_decomp_b200.experiments.lm.invariance_check --world 4 --steps 3 [--tp 2] [--sharding zero1] [--device cuda]`
+"""`python -m param_decomp_b200.experiments.lm.invariance_check --world 4 --steps 3 [--tp 2] [--sharding zero1] [--objective subset] [--ci global_transformer]
+[--muon] [--device cuda]`
 
 Rank-count invariance of the trainer on a tiny Llama target: the SAME global batch, seed and objective run once
 in one process and once as `world` data-parallel ranks (gloo on CPU; NCCL with `--device cuda`, one GPU per rank),
@@ -40,13 +41,37 @@ LOSSES = [
 ]
 
 
-def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1) -> LMExperimentConfig:
+OBJECTIVES: dict[str, list[dict[str, Any]]] = {
+    "default": LOSSES,
+    "subset": [{"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 2.0},
+               {"type": "StochasticReconSubsetLoss", "coeff": 1.0, "routing": {"type": "uniform_k_subset"}},
+               {"type": "CIMaskedReconLoss", "coeff": 0.5},
+               {"type": "FaithfulnessLoss", "coeff": 10.0}],
+    "lp": [{"type": "LpImportanceMinimalityLoss", "coeff": 1e-3, "p_start": 2.0, "p_end": 1.0, "beta": 0.5},
+           {"type": "StochasticReconLoss", "coeff": 1.0, "n_samples": 2},
+           {"type": "FaithfulnessLoss", "coeff": 10.0}],
+    "frequency": [{"type": "ImportanceMinimalityLoss", "coeff": 1e-3, "gamma": 1.0,
+                   "frequency": {"coeff": 1e-3, "reference_datapoint_count": 64, "ema_halflife_steps": 2.0}},
+                  {"type": "StochasticReconLoss", "coeff": 1.0},
+                  {"type": "FaithfulnessLoss", "coeff": 10.0}],
+}
+CI_FUNCTIONS: dict[str, dict[str, Any]] = {
+    "layerwise_mlp": {"type": "layerwise_mlp", "hidden_dims": [32]},
+    "global_transformer": {"type": "global_transformer", "d_model": 32, "n_blocks": 2,
+                           "attention": {"kind": "mha", "n_heads": 2, "implementation": "xla", "mask": "bidirectional"},
+                           "ffn": {"kind": "gelu", "hidden": 64}, "input_tap": "all_block_taps"},
+}
+
+
+def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1,
+                objective: str = "default", ci: str = "layerwise_mlp", muon: bool = False) -> LMExperimentConfig:
     raw: dict[str, Any] = {
         "run_name": "invariance",
         "pd": {"seed": 0, "steps": steps, "batch_size": batch,
-               "components_optimizer": {"lr_schedule": 1e-3, "grad_clip_norm": 1.0},
+               "components_optimizer": ({"type": "muon", "lr_schedule": 1e-2} if muon
+                                        else {"lr_schedule": 1e-3, "grad_clip_norm": 1.0}),
                "ci_fn_optimizer": {"lr_schedule": 1e-3, "grad_clip_norm": 1.0},
-               "loss_metrics": LOSSES},
+               "loss_metrics": OBJECTIVES[objective]},
         "cadence": {"train_log_every": 1, "checkpointing": {"kind": "none"}},
         "runtime": {"mesh": {"replicate": 1, "fsdp": world // tp, "tp": tp}, "sharding": sharding,
                     "backend": "fused_sm100" if cuda else "eager_torch"},
@@ -58,7 +83,7 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
                    "output_edge": {"kind": "materialized"}, "weights_dtype": "bfloat16" if cuda else "float32"},
         "decomposition": {"sites": {"kind": "glu_transformer", "layers": {"kind": "all"},
                                     "cs": {k: (256 if cuda else 64) for k in ("q", "o", "gate", "down")}},
-                          "ci": {"type": "layerwise_mlp", "hidden_dims": [32]}},
+                          "ci": dict(CI_FUNCTIONS[ci])},
         "data": {"train": {"kind": "synthetic_zipf"}, "eval": {"kind": "synthetic_zipf", "seed": 1},
                  "layout": "unsegmented_tokens", "seq_len": 128 if cuda else 16},
     }
@@ -117,7 +142,7 @@ def compare(one: dict[int, dict[str, float]], many: dict[int, dict[str, float]],
 
 
 def check(world: int, steps: int, sharding: str, batch: int, device: str, rtol: float | None = None,
-          verbose: bool = True, tp: int = 1) -> list[str]:
+          verbose: bool = True, tp: int = 1, **variant: Any) -> list[str]:
     """`tp` of the `world` ranks see the same tokens and split every site's component axis; the remaining
     `world // tp` split the batch."""
     cuda = device == "cuda"
@@ -126,13 +151,13 @@ def check(world: int, steps: int, sharding: str, batch: int, device: str, rtol: 
     rtol = rtol if rtol is not None else (3e-2 if cuda else 1e-4)  # bf16 operands on the GPU path
     assert world % tp == 0 and batch % (world // tp) == 0, (batch, world, tp)
     with tempfile.TemporaryDirectory() as root:
-        one_dir, one_params = _run(tiny_config(1, steps, sharding, batch, cuda), Path(root), "p-00000001",
+        one_dir, one_params = _run(tiny_config(1, steps, sharding, batch, cuda, **variant), Path(root), "p-00000001",
                                    "cuda:0" if cuda else "cpu")
         with socket.socket() as s:
             s.bind(("127.0.0.1", 0))
             port = s.getsockname()[1]
         out = mp.Manager().dict()
-        mp.spawn(_rank, args=(world, port, root, tiny_config(world, steps, sharding, batch, cuda, tp).model_dump_json(),
+        mp.spawn(_rank, args=(world, port, root, tiny_config(world, steps, sharding, batch, cuda, tp, **variant).model_dump_json(),
                               cuda, out), nprocs=world, join=True)
         a, b = trajectory(one_dir), trajectory(Path(out["run_dir"]))
         bad = compare(a, b, rtol, 1e-6)
@@ -159,8 +184,12 @@ def main() -> None:
     ap.add_argument("--sharding", default="ddp")
     ap.add_argument("--device", choices=("cpu", "cuda"), default="cpu")
     ap.add_argument("--rtol", type=float, default=None)
+    ap.add_argument("--objective", choices=sorted(OBJECTIVES), default="default")
+    ap.add_argument("--ci", choices=sorted(CI_FUNCTIONS), default="layerwise_mlp")
+    ap.add_argument("--muon", action="store_true", help="Muon on the component matrices")
     a = ap.parse_args()
-    bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp)
+    bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp, objective=a.objective, ci=a.ci,
+                muon=a.muon)
     if bad:
         print(f"NOT invariant over {a.world} ranks ({a.sharding}):")
         for line in bad:
