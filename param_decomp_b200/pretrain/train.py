@@ -281,7 +281,7 @@ def pretrain(cfg: PretrainConfig, data_root: Path | None = None, run_id: str | N
         if dp.rank == 0:
             snap = {k: v.detach().to(torch.bfloat16 if cfg.dtype == "bfloat16" else torch.float32) for k, v in weights.items()}
             (save_qwen35_cache if hybrid else save_simple_mlp_cache)(entry, arch, snap, step)
-            _prune_model_snapshots(entry, cfg.keep_last)
+            _prune_model_snapshots(entry, 1)  # the cache entry holds exactly one hand-off snapshot, as its readers expect
             save_train_state(entry, step, weights, opt, cfg.keep_last)
         dp.barrier()
 
