@@ -146,7 +146,7 @@ def test_pretrain_cache_roundtrip_feeds_decomposition(tmp_path):
         "log_every": 2, "val_every": 2, "save_every": 2, "dtype": "float32",
         "model": {"vocab_size": 64, "n_layer": 2, "n_head": 2, "n_embd": 32, "n_intermediate": 64, "n_ctx": 16}})
     entry = pretrain(cfg, tmp_path, run_id="t-0000abcd", project="spd")
-    assert (entry / "model_config.yaml").exists() and len(list(entry.glob("model_step_*.safetensors"))) == 2
+    assert (entry / "model_config.yaml").exists() and len(list(entry.glob("model_step_*.safetensors"))) == 1
     spec = PretrainedTarget(model_class="LlamaSimpleMLP", run_path="goodfire/spd/runs/t-0000abcd")
     arch, weights = loaders.load_from_spec(spec, tmp_path, torch.float32, "cpu")
     assert arch.family == "simple_mlp" and arch.n_layer == 2 and "h.0.attn.q_proj.weight" in weights
