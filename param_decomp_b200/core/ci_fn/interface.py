@@ -25,6 +25,21 @@ class TapSpec:
     width: int
 
 
+class MaskInputs(dict):
+    """`{site: importances}` as the mask samplers consume them, plus - for expert-blocked sites, whose values are
+    NARROW - which blocks each position's slots are: `selections[site] = (indices [..., k], n_blocks)`. Samplers
+    that combine the importances with full-width quantities (adversary sources) gather those at the same blocks."""
+
+    selections: dict[str, tuple[Tensor, int]]
+
+    def __init__(self, values: dict[str, Tensor], selections: dict[str, tuple[Tensor, int]] | None = None) -> None:
+        super().__init__(values)
+        self.selections = dict(selections or {})
+
+    def map(self, fn) -> "MaskInputs":
+        return MaskInputs({k: fn(v) for k, v in self.items()}, self.selections)
+
+
 @dataclass
 class CI:
     preactivations: dict[str, Tensor | SelectedCI]
@@ -34,10 +49,12 @@ class CI:
     """Fused backend only: per-component mean smooth-L0 activity `[C]`, produced in the same pass
     as `lower` (then `upper` is not materialised)."""
 
-    def mask_inputs(self) -> dict[str, Tensor]:
+    def mask_inputs(self) -> MaskInputs:
         """What the mask samplers consume: dense `[..., C]` for dense sites, the NARROW
         `[..., k * C_block]` values (slot-major, in routing order) for expert-blocked sites."""
-        return {k: (v.values if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()}
+        return MaskInputs({k: (v.values if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()},
+                          {k: (v.selection.indices, v.n_blocks) for k, v in self.lower.items()
+                           if isinstance(v, SelectedCI)})
 
     def dense_lower(self) -> dict[str, Tensor]:
         return {k: (v.scatter_dense() if isinstance(v, SelectedCI) else v) for k, v in self.lower.items()}

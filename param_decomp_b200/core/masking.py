@@ -152,12 +152,39 @@ def stochastic_masks(ci: dict[str, Tensor], key: StepKey, term: int, draw: int, 
     return out
 
 
+def select_source_blocks(source: Tensor, indices: Tensor, n_blocks: int) -> Tensor:
+    """A full-width source `[*src_lead, n_blocks * c]` (leading axes of size 1 are shared) read at each position's
+    selected blocks: `[*lead, k * c]`, slot-major like the narrow importances. Indexing, not expansion: nothing of
+    size `positions x n_blocks x c` is formed, and the gradient accumulates into the selected blocks only
+    (param_decomp/core/masking.py:43-120, selected source values)."""
+    lead, k = tuple(indices.shape[:-1]), indices.shape[-1]
+    c = source.shape[-1] // n_blocks
+    assert c * n_blocks == source.shape[-1], (source.shape, n_blocks)
+    src_lead = (1,) * (len(lead) - (source.dim() - 1)) + tuple(source.shape[:-1])
+    assert len(src_lead) == len(lead), f"source {tuple(source.shape)} has more leading axes than the importances {lead}"
+    table = source.reshape(*src_lead, n_blocks, c)
+    index: list[Tensor] = []
+    for axis, (have, want) in enumerate(zip(src_lead, lead)):
+        assert have in (1, want), f"source axis {axis} is {have}, the importances have {want}"
+        ix = torch.arange(want, device=source.device) if have == want and want > 1 else torch.zeros(1, dtype=torch.long, device=source.device)
+        shape = [1] * (len(lead) + 1)
+        shape[axis] = ix.numel()
+        index.append(ix.view(shape))
+    picked = table[(*index, indices.long())]  # [*lead, k, c]
+    return picked.reshape(*lead, k * c)
+
+
 def source_masks(ci: dict[str, Tensor], sources: dict[str, Tensor], delta_sources: dict[str, Tensor] | None,
                  routing: dict[str, Tensor | None] | None = None) -> Masks:
-    """`m = ci + (1 - ci) s` with broadcastable sources (`[1,C]`, `[B,C]`, `[B,1,C]`, `[B,T,C]`)."""
+    """`m = ci + (1 - ci) s` with broadcastable sources (`[1,C]`, `[B,C]`, `[B,1,C]`, `[B,T,C]`). Where `ci` carries
+    block selections (`MaskInputs.selections`: narrow importances of expert-blocked sites) the full-width source
+    is read at the selected blocks."""
     out: Masks = {}
+    selections = getattr(ci, "selections", {})
     for name, c in ci.items():
         s = sources[name].to(c.dtype)
+        if name in selections:
+            s = select_source_blocks(s, *selections[name])
         d = None
         if delta_sources is not None:
             d = delta_sources[name].to(c.dtype).expand(*_lead(c), 1)

@@ -353,6 +353,8 @@ def _detach_weights(w: ComputeWeights) -> ComputeWeights:
 
 
 def _detach_ci(ci_lower: dict[str, Tensor]) -> dict[str, Tensor]:
+    if hasattr(ci_lower, "map"):  # keeps the block selections of narrow sites
+        return ci_lower.map(lambda v: v.detach())  # type: ignore[attr-defined]
     return {k: v.detach() for k, v in ci_lower.items()}
 
 
@@ -676,7 +678,7 @@ def _nontarget_pass(ctx: StepContext, state: TrainState, weights: ComputeWeights
     with torch.no_grad():
         clean = ctx.model.clean_forward(batch)
     ci = run_ci_fn(ctx, state, clean)
-    ci_lower = ci.dense_lower()
+    ci_lower = ci.mask_inputs()
     m2: dict[str, Tensor] = {}
     coeff = scheduled_or_constant(nt.impmin_coeff, step, ctx.pd.steps)
     total = evaluate_minimality(ctx, state, ci, step, m2, coeff_override=coeff, update_ema=False)

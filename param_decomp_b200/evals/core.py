@@ -64,7 +64,7 @@ def fresh_pgd_recon(ctx: StepContext, state: TrainState, batch: Any, step_size: 
         keys = tuple(dict.fromkeys(c.capture for a in auxiliaries for c in a.comparisons))
         clean = ctx.model.clean_forward(batch, capture=keys)
         weights = prepare_compute_weights(state.components, ctx.model.compute_dtype)
-        ci_lower = run_ci_fn(ctx, state, clean).dense_lower()
+        ci_lower = run_ci_fn(ctx, state, clean).mask_inputs()  # narrow at expert-blocked sites, with their block selections
     lead = tuple(next(iter(ci_lower.values())).shape[:-1])
     positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None
     device = next(iter(ci_lower.values())).device

@@ -27,7 +27,7 @@ def ce_and_kl(ctx: StepContext, state: TrainState, batch: Any, rounding_threshol
     model = ctx.model
     clean = model.clean_forward(batch)
     weights = prepare_compute_weights(state.components, model.compute_dtype).detached()
-    ci = run_ci_fn(ctx, state, clean).dense_lower()
+    ci = run_ci_fn(ctx, state, clean).mask_inputs()  # masks of expert-blocked sites are narrow (selected blocks only)
     key = StepKey(0xE7A1, 0)
     site_index = ctx.site_index
     variants: dict[str, masking.Masks] = {
@@ -73,7 +73,7 @@ def attention_pattern_recon(ctx: StepContext, state: TrainState, batch: Any, sto
     keys = tuple(f"attn_scores.{i}" for i in range(n_layer))
     clean = model.clean_forward(batch, capture=keys)
     weights = prepare_compute_weights(state.components, model.compute_dtype).detached()
-    ci = run_ci_fn(ctx, state, clean).dense_lower()
+    ci = run_ci_fn(ctx, state, clean).mask_inputs()
     masks = (masking.stochastic_masks(ci, StepKey(0xE7A2, 0), 0, 0, site_index=ctx.site_index, lazy=False)
              if stochastic else masking.ci_masks(ci))
     res = model.masked_forward(weights, batch, masks, capture=keys)

@@ -64,7 +64,10 @@ CI_FUNCTIONS: dict[str, dict[str, Any]] = {
 
 
 def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1,
-                objective: str = "default", ci: str = "layerwise_mlp", muon: bool = False) -> LMExperimentConfig:
+                objective: str = "default", ci: str = "layerwise_mlp", muon: bool = False, family: str = "dense",
+                expert_mode: str = "allreduce") -> LMExperimentConfig:
+    """`family: moe` is a top-2-of-5 mixture of experts (five experts on two ranks leave one padding expert); its
+    `tp` ranks split the experts, and with `expert_mode: all_to_all` the batch too."""
     raw: dict[str, Any] = {
         "run_name": "invariance",
         "pd": {"seed": 0, "steps": steps, "batch_size": batch,
@@ -87,6 +90,14 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
         "data": {"train": {"kind": "synthetic_zipf"}, "eval": {"kind": "synthetic_zipf", "seed": 1},
                  "layout": "unsegmented_tokens", "seq_len": 128 if cuda else 16},
     }
+    if family == "moe":
+        raw["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 16,
+                                         "vocab_size": 100, "n_experts": 5, "experts_per_token": 2}
+        raw["decomposition"]["sites"] = {"kind": "moe", "layers": {"kind": "all"},
+                                         "cs": {"q": 8, "experts_gate": 20, "experts_up": 20, "experts_down": 20}}
+        if expert_mode == "all_to_all":
+            raw["target"]["expert_implementation"] = "all_to_all"
+            raw["runtime"]["mesh"] = {"replicate": 1, "fsdp": world // tp, "tp": tp}
     return LMExperimentConfig.model_validate(raw)
 
 
@@ -187,9 +198,11 @@ def main() -> None:
     ap.add_argument("--objective", choices=sorted(OBJECTIVES), default="default")
     ap.add_argument("--ci", choices=sorted(CI_FUNCTIONS), default="layerwise_mlp")
     ap.add_argument("--muon", action="store_true", help="Muon on the component matrices")
+    ap.add_argument("--family", choices=("dense", "moe"), default="dense")
+    ap.add_argument("--expert-mode", choices=("allreduce", "all_to_all"), default="allreduce")
     a = ap.parse_args()
     bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp, objective=a.objective, ci=a.ci,
-                muon=a.muon)
+                muon=a.muon, family=a.family, expert_mode=a.expert_mode)
     if bad:
         print(f"NOT invariant over {a.world} ranks ({a.sharding}):")
         for line in bad:

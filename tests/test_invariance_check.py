@@ -32,3 +32,38 @@ def test_compare_reports_what_differs():
     many = {0: {"train/loss/total": 1.001, "train/perf/step_ms": 9.0, "train/grad_norm/ci_fn": 1.0005}}
     bad = ic.compare(one, many, rtol=1e-4, atol=0.0)
     assert len(bad) == 1 and "loss/total" in bad[0]
+
+
+def test_full_width_sources_are_read_at_the_selected_blocks():
+    """Expert-blocked sites have narrow importances `[.., k * c]`; an adversary source is full width `[.., E * c]`.
+    The mask must pair every slot with the source values of ITS block, for every source shape."""
+    from param_decomp_b200.core import masking
+    from param_decomp_b200.core.ci_fn.interface import MaskInputs
+    from param_decomp_b200.core.components import BlockSelection, SelectedCI
+
+    torch.manual_seed(0)
+    B, T, E, c, k = 3, 4, 5, 2, 2
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(B * T)]).reshape(B, T, k)
+    narrow = torch.rand(B, T, k * c)
+    dense_ci = SelectedCI(narrow, BlockSelection(idx, torch.ones(B, T, k)), E).scatter_dense()
+    for shape in ((1, E * c), (B, 1, E * c), (B, T, E * c)):
+        src = torch.rand(*shape, requires_grad=True)
+        got = masking.select_source_blocks(src, idx, E)
+        want = torch.gather(src.expand(B, T, E * c).reshape(B, T, E, c), 2,
+                            idx[..., None].expand(B, T, k, c)).reshape(B, T, k * c)
+        assert torch.equal(got, want), shape
+        m = masking.source_masks(MaskInputs({"x": narrow}, {"x": (idx, E)}), {"x": src}, None)["x"].mask
+        dense_m = dense_ci + (1 - dense_ci) * src.expand(B, T, E * c)
+        picked_dense = torch.gather(dense_m.reshape(B, T, E, c), 2, idx[..., None].expand(B, T, k, c)).reshape(B, T, k * c)
+        assert torch.allclose(m, picked_dense, atol=1e-6), shape
+        (g,) = torch.autograd.grad(got.sum(), src)
+        counts = torch.zeros(E).index_add_(0, idx.reshape(-1), torch.ones(idx.numel()))
+        if shape[0] == 1:  # a batch-shared source collects one unit of gradient per (position, slot) of a block
+            assert torch.equal(g.reshape(E, c)[:, 0], counts)
+
+
+def test_adversaries_on_a_mixture_of_experts_are_rank_count_invariant():
+    """Persistent and fresh adversaries on expert-blocked sites (narrow importances), one process against two ranks
+    that split the experts and exchange token jobs."""
+    assert ic.check(world=2, steps=2, sharding="ddp", batch=4, device="cpu", verbose=False, tp=2, family="moe",
+                    expert_mode="all_to_all") == []
