@@ -159,10 +159,18 @@ class MoEDecomposedModel(tf.TransformerDecomposedModel):
         B, T, d = x.shape
         xt = x.reshape(B * T, d)
         pinned = aux.get("pinned_routing")
+        captures, want = aux.get("capture_sink", ({}, ()))
+        logits = None
+        if pinned is None or f"router_logits.{i}" in want:
+            logits = F.linear(xt, self.w[f"layers.{i}.mlp.router.weight"])
+        if f"router_logits.{i}" in want:
+            # what the router WOULD decide on this pass's residual stream (the masked passes keep the clean pass's
+            # choice): the quantity a router-KL auxiliary compares (param_decomp/targets/qwen36_moe.py:473-515)
+            captures[f"router_logits.{i}"] = logits.float().view(B, T, -1)
         if pinned is not None:
             sel = pinned[i]
         else:
-            sel = route_topk(F.linear(xt, self.w[f"layers.{i}.mlp.router.weight"]), a.experts_per_token, a.norm_topk_prob)
+            sel = route_topk(logits, a.experts_per_token, a.norm_topk_prob)
             sel = BlockSelection(sel.indices.reshape(B, T, -1), sel.weights.reshape(B, T, -1))
             aux.setdefault("routing", {})[i] = sel
         k = sel.indices.shape[-1]

@@ -328,6 +328,7 @@ class TransformerDecomposedModel:
             x = gather_sequence(x, sp)
         if taps is not None:
             taps[f"mlp_in.{i}"] = x
+        aux["capture_sink"] = (captures, want)  # for MLP variants that have captures of their own (router logits)
         m = self._mlp(i, x, lin, taps, weights, masks, aux)
         return resid + (slice_sequence(m, sp) if sp is not None else m)
 

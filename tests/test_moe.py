@@ -119,3 +119,63 @@ def test_moe_chunkwise_ci_fn_steps_and_routed_products_match_gathers():
     m = train_step(ctx, st, batch)
     assert torch.isfinite(m["loss/total"])
     assert sum(int(not torch.equal(a, b)) for a, b in zip(before, run.ci_fn.parameters())) > len(before) // 2
+
+
+def test_router_logits_are_captured_in_clean_and_masked_passes():
+    """The quantity a router-KL auxiliary compares: what the router would decide on each pass's own residual
+    stream, although masked passes keep the clean pass's expert choice."""
+    from param_decomp_b200.core import masking
+    from param_decomp_b200.core.components import prepare_compute_weights
+    from param_decomp_b200.core.objective import build_objective
+    from param_decomp_b200.core.run import init_train_state
+    from param_decomp_b200.core.train import StepContext, run_ci_fn
+
+    cfg = moe_cfg()
+    run = build_lm_run(cfg, None, "cpu")
+    obj = build_objective(cfg.pd)
+    ctx = StepContext.build(run.model, obj, cfg.pd)
+    st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, "cpu", 3, 8)
+    batch = run.sample_train(0)
+    keys = ("router_logits.0", "router_logits.1")
+    with torch.no_grad():
+        clean = run.model.clean_forward(batch, capture=keys)
+        assert clean.captures["router_logits.1"].shape == (3, 8, 6)
+        ci = run_ci_fn(ctx, st, clean)
+        w = prepare_compute_weights(st.components, torch.float32)
+        same = run.model.masked_forward(w, batch, masking.unmasked(ci.mask_inputs()), capture=keys, clean=clean)
+        assert torch.allclose(same.captures["router_logits.1"], clean.captures["router_logits.1"], atol=1e-4)
+        zero = run.model.masked_forward(w, batch, masking.constant_masks(ci.mask_inputs(), 0.0, None), capture=keys,
+                                        clean=clean)
+        assert not torch.allclose(zero.captures["router_logits.1"], clean.captures["router_logits.1"], atol=1e-4)
+
+
+def test_adversary_sources_act_only_on_the_selected_expert_blocks():
+    """A per-position full-width source at an expert site influences the output only through the blocks of the
+    experts that position was routed to: its gradient is zero everywhere else."""
+    from param_decomp_b200.core import masking
+    from param_decomp_b200.core.components import prepare_compute_weights
+    from param_decomp_b200.core.objective import build_objective
+    from param_decomp_b200.core.run import init_train_state
+    from param_decomp_b200.core.train import StepContext, run_ci_fn
+
+    cfg = moe_cfg()
+    run = build_lm_run(cfg, None, "cpu")
+    obj = build_objective(cfg.pd)
+    ctx = StepContext.build(run.model, obj, cfg.pd)
+    st = init_train_state(run.model, run.ci_fn, cfg.pd, obj, "cpu", 3, 8)
+    batch = run.sample_train(0)
+    with torch.no_grad():
+        clean = run.model.clean_forward(batch)
+        ci = run_ci_fn(ctx, st, clean)
+        w = prepare_compute_weights(st.components, torch.float32)
+    inputs = ci.mask_inputs().map(lambda v: v * 0.5)
+    site = "layers.0.mlp.experts_up"
+    sources = {n: torch.rand(3, 8, s.C, requires_grad=True) for n, s in ((s.name, s) for s in run.model.sites)}
+    out = run.model.masked_forward(w, batch, masking.source_masks(inputs, sources, None), clean=clean)
+    (g,) = torch.autograd.grad(run.model.recon_loss(clean, out), sources[site])
+    idx, E = inputs.selections[site]
+    c = g.shape[-1] // E
+    chosen = torch.zeros(3, 8, E, dtype=torch.bool).scatter_(-1, idx, True)
+    per_block = g.reshape(3, 8, E, c).abs().sum(-1)
+    assert float(per_block[~chosen].sum()) == 0.0
+    assert bool((per_block[chosen] > 0).all())
