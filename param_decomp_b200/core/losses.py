@@ -163,15 +163,24 @@ def faithfulness_terms(stacks: ComponentStacks, target_weights: dict[str, Tensor
 
 
 def nonlinearity_locality(stacks: ComponentStacks, relative_threshold: float,
-                          unit_kind_coefficients: dict[str, float | None], normalize_at_one: bool) -> Tensor:
+                          unit_kind_coefficients: dict[str, float | None], normalize_at_one: bool,
+                          expert_shard=None, split_grad_scale: float = 1.0) -> Tensor:
     """Soft count of nonlinearity units each component touches, averaged per unit kind.
 
     For a site whose `alignment.side` faces a nonlinearity, take the component vectors on that side
     (`U` rows for "output", `V` columns for "input"), split them into units (neurons, or contiguous
     head blocks), form each unit's energy share `e_u = ||v_u||^2 / ||v||^2`, and count units softly
     with `e^2 / (e^2 + tau^2)`, `tau = relative_threshold / n_units` (relative to the uniform share).
+
+    `expert_shard` (`parallel/expert_shard.py::StackSharding`, expert mode): this rank holds only its experts'
+    blocks of the blocked sites (padding experts excluded here) and every component of the other sites. A kind's
+    mean is then taken over ALL of the job's components: split sums and counts are added over the group. The
+    returned value is that job-wide mean; its gradient is the local part's, with the split sites' share scaled by
+    `split_grad_scale` (see `DistCollectives.split_grad_scale`).
     """
+    by_expert = expert_shard is not None and not expert_shard.by_component
     per_kind: dict[str, list[Tensor]] = {}
+    per_kind_split: dict[str, list[Tensor]] = {}
     for s in stacks.sites:
         al = s.alignment
         if al is None:
@@ -193,8 +202,27 @@ def nonlinearity_locality(stacks: ComponentStacks, relative_threshold: float,
         if normalize_at_one:
             count = count * (1 + tau * tau)
         mult = getattr(al.partition, "use_multiplicity", 1)
-        per_kind.setdefault(kind, []).append(count * mult)
+        if by_expert and s.blocked:
+            real = expert_shard.n_real * s.C_block  # blocks of padding experts sit at the end and are not components
+            per_kind_split.setdefault(kind, []).append(count[:real] * mult)
+        else:
+            per_kind.setdefault(kind, []).append(count * mult)
     total = None
+    if by_expert:
+        kinds = sorted(set(per_kind) | set(per_kind_split))
+        if kinds:
+            dev = next(stacks.parameters()).device
+            zero = torch.zeros((), device=dev)
+            rep = torch.stack([torch.cat(per_kind[k]).sum() if k in per_kind else zero for k in kinds])
+            spl = torch.stack([torch.cat(per_kind_split[k]).sum() if k in per_kind_split else zero for k in kinds])
+            n_rep = torch.tensor([sum(c.numel() for c in per_kind.get(k, [])) for k in kinds], device=dev, dtype=rep.dtype)
+            n_spl = torch.tensor([sum(c.numel() for c in per_kind_split.get(k, [])) for k in kinds], device=dev, dtype=rep.dtype)
+            group_wide = expert_shard.sum_over_group(torch.stack([spl.detach(), n_spl]))
+            n_all = (n_rep + group_wide[1]).clamp_min(1.0)
+            coeffs = torch.tensor([float(unit_kind_coefficients[k]) for k in kinds], device=dev, dtype=rep.dtype)  # type: ignore[arg-type]
+            value = (((rep.detach() + group_wide[0]) / n_all) * coeffs).sum()
+            local = (((rep + split_grad_scale * spl) / n_all) * coeffs).sum()
+            return value + (local - local.detach())
     for kind, counts in per_kind.items():
         val = torch.cat(counts).mean() * float(unit_kind_coefficients[kind])  # type: ignore[arg-type]
         total = val if total is None else total + val

@@ -536,7 +536,9 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     if obj.nonlinearity is not None:
         nl = obj.nonlinearity
         thr = get_scheduled_value(step, total, nl.relative_threshold)
-        val = loss_fns.nonlinearity_locality(state.components, thr, dict(nl.unit_kind_coefficients), nl.normalize_at_one)
+        val = loss_fns.nonlinearity_locality(state.components, thr, dict(nl.unit_kind_coefficients), nl.normalize_at_one,
+                                             expert_shard=ctx.expert_shard,
+                                             split_grad_scale=ctx.collectives.split_grad_scale)
         metrics["loss/" + nl.instance_key] = val.detach()
         add(scheduled_or_constant(nl.coeff, step, total) * val)
 

@@ -179,3 +179,60 @@ def test_adversary_sources_act_only_on_the_selected_expert_blocks():
     per_block = g.reshape(3, 8, E, c).abs().sum(-1)
     assert float(per_block[~chosen].sum()) == 0.0
     assert bool((per_block[chosen] > 0).all())
+
+
+def test_locality_loss_is_job_wide_when_experts_are_split():
+    """A unit kind's mean runs over every component of the job. With the expert blocks dealt to two ranks (and a
+    padding expert on the second) each rank must report the one-process value, and give its own blocks the
+    one-process gradient."""
+    from types import SimpleNamespace
+
+    from param_decomp_b200.core import losses
+    from param_decomp_b200.core.components import ComponentStacks, SiteSpec
+    from param_decomp_b200.formats.nonlinearity import Neurons, NonlinearityAlignment
+
+    al = NonlinearityAlignment(side="output", partition=Neurons())
+    E, e_loc, c = 3, 2, 2  # three experts on two ranks: rank 1 holds one real expert and one padding expert
+
+    def stacks(n_blocks: int) -> ComponentStacks:
+        return ComponentStacks((SiteSpec("shared_up", 6, 8, 4, alignment=al),
+                                SiteSpec("experts_up", 6, 8, n_blocks * c, n_blocks=n_blocks, alignment=al, routed=True)))
+
+    torch.manual_seed(0)
+    whole = stacks(E)
+    whole.init_random()
+    coeffs = {"neuron": 2.0}
+    ref = losses.nonlinearity_locality(whole, 4.0, coeffs, True)
+    ref.backward()
+    key = ComponentStacks.param_key(whole.site_by_name["experts_up"].group)
+
+    parts = []
+    for r in range(2):
+        st = stacks(e_loc)
+        with torch.no_grad():
+            for name in ("V", "U"):
+                getattr(st, name)[ComponentStacks.param_key(st.site_by_name["shared_up"].group)].copy_(
+                    getattr(whole, name)[ComponentStacks.param_key(whole.site_by_name["shared_up"].group)])
+                src = getattr(whole, name)[key][:, r * e_loc:(r + 1) * e_loc]
+                getattr(st, name)[ComponentStacks.param_key(st.site_by_name["experts_up"].group)][:, :src.shape[1]].copy_(src)
+        parts.append(st)
+    sent: dict[int, torch.Tensor] = {}
+    for second_pass in (False, True):  # first pass records what each rank would send, second adds the peer's
+        for r, st in enumerate(parts):
+            def add(t, r=r):
+                if not second_pass:
+                    sent[r] = t.clone()
+                    return t
+                return t + sent[1 - r]
+            shard = SimpleNamespace(by_component=False, n_real=min(E, (r + 1) * e_loc) - r * e_loc, sum_over_group=add)
+            st.zero_grad()
+            val = losses.nonlinearity_locality(st, 4.0, coeffs, True, expert_shard=shard)
+            if second_pass:
+                assert torch.allclose(val, ref, atol=1e-6), (r, float(val), float(ref))
+                val.backward()
+                k2 = ComponentStacks.param_key(st.site_by_name["experts_up"].group)
+                n = shard.n_real
+                assert torch.allclose(st.U[k2].grad[:, :n], whole.U[key].grad[:, r * e_loc:r * e_loc + n], atol=1e-7)
+                assert float(st.U[k2].grad[:, n:].abs().sum()) == 0.0  # the padding expert is not a component
+                ks = ComponentStacks.param_key(st.site_by_name["shared_up"].group)
+                assert torch.allclose(st.U[ks].grad, whole.U[ComponentStacks.param_key(whole.site_by_name["shared_up"].group)].grad, atol=1e-7)
