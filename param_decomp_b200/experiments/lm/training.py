@@ -228,9 +228,9 @@ def train_lm_targeted(cfg: LMTargetedExperimentConfig, data_root: Path | None, r
             evaluation=evaluation, collectives=topo.collectives(), nontarget=nontarget,
             step_watchdog_s=cfg.runtime.step_watchdog_s,
             remat_recon_forwards=cfg.runtime.remat_recon_forwards, remat_ci_fn=cfg.runtime.remat_ci_fn,
-            sample_nontarget_batch=sample_nontarget, batch_rows=max(cfg.pd.batch_size, nt_rows) // topo.data_world,
-            positions=max(pool.seq_len, cfg.data.seq_len), units_per_step=(cfg.pd.batch_size * pool.seq_len
-                                                                          + nt_rows * cfg.data.seq_len),
+            # adversary sources exist for the TARGET stream only: its rows per rank and its prompt length
+            sample_nontarget_batch=sample_nontarget, batch_rows=cfg.pd.batch_size // topo.data_world,
+            positions=pool.seq_len, units_per_step=(cfg.pd.batch_size * pool.seq_len + nt_rows * cfg.data.seq_len),
             lazy_masks=fused, use_fused_optim=fused, init_components=run.init_components,
             max_steps_this_entry=max_steps_this_entry, state_out=state_out)
     except BaseException:

@@ -116,3 +116,17 @@ def test_arithmetic_grid_metric_is_built_from_the_run_encoder(tmp_path):
         raise RuntimeError("a grid with unequal prompt lengths was accepted")
     except AssertionError as e:
         assert "different lengths" in str(e)
+
+
+def test_per_position_adversary_follows_the_prompt_length(tmp_path):
+    """Adversary sources of a targeted run live on the target stream: with per-position (`bsc`) sources their
+    position axis is the prompt length (here 4), not the broad stream's sequence length (16)."""
+    base = _targeted_config().model_dump(mode="json")
+    base["prompts"] = {"kind": "arithmetic_grid", "operation": "add", "a_range": [1, 4], "b_range": [1, 5]}
+    base["pd"]["loss_metrics"].append({"type": "PersistentPGDReconLoss", "coeff": 0.5, "source_shape": "bsc",
+                                       "n_warmup_steps": 1, "optimizer": {"type": "sgd", "lr_schedule": 0.05}})
+    states: list = []
+    res = train_lm_targeted(LMTargetedExperimentConfig.model_validate(base), tmp_path, device="cpu", state_out=states)
+    assert res.final_step == 3
+    adv = next(iter(states[0].adversaries.values()))
+    assert next(iter(adv.sources.values())).shape[:2] == (4, 4)  # [rows, prompt positions, C]
