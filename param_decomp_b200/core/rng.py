@@ -52,6 +52,11 @@ def uniform(key: StepKey, stream: int, rows: int, cols: int, row_offset: int = 0
 
             return philox_uniform(key.seed64, stream, rows, cols, row_offset, device)
     padded = ((cols + 7) // 8) * 8
+    if torch.device(device).type == "cpu":
+        from param_decomp_b200.ops import host_native
+
+        if host_native.available():  # the same stream from one native loop instead of a dozen tensor ops per round
+            return host_native.philox_uniform(key.seed64, stream, rows, padded, row_offset)[:, :cols]
     u = philox_ref.uniform(key.seed64, stream, rows, padded, row_offset, device)
     return u[:, :cols]
 

@@ -90,5 +90,35 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB_PATH
 
 
+HOST_SRC = OPS_DIR / "csrc_host"
+HOST_LIB_PATH = LIB_DIR / "libpdhost.so"
+HOST_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-shared", "-fno-math-errno"]
+
+
+def build_host(force: bool = False) -> Path:
+    """The host-side native pieces (`csrc_host/*.cpp`: the CPU twin of the device mask stream) into
+    `ops/_lib/libpdhost.so` with the system C++ compiler. Plain C ABI, loaded with `ctypes` (`host_native.py`);
+    callers fall back to the pure-torch forms when it has not been built."""
+    LIB_DIR.mkdir(exist_ok=True)
+    sources = sorted(HOST_SRC.glob("*.cpp"))
+    h = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    for src in sources:
+        h.update(src.read_bytes())
+    stamp = LIB_DIR / "libpdhost.digest"
+    digest = h.hexdigest()
+    if not force and HOST_LIB_PATH.exists() and stamp.exists() and stamp.read_text() == digest:
+        return HOST_LIB_PATH
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("no C++ compiler found: the host library cannot be built")
+    res = subprocess.run([cxx, *HOST_FLAGS, *map(str, sources), "-o", str(HOST_LIB_PATH)], capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("host library build failed")
+    stamp.write_text(digest)
+    return HOST_LIB_PATH
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))
+    print(build_host(force="--force" in sys.argv))

@@ -15,14 +15,10 @@ ROUNDS = 7
 
 
 def _mulhilo(a: int, b: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    # b holds uint32 values in int64; a*b < 2^64 overflows int64, so split b into 16-bit halves.
-    lo16, hi16 = b & 0xFFFF, b >> 16
-    p_lo = a * lo16  # < 2^48
-    p_hi = a * hi16  # < 2^48
-    full_lo = (p_lo + ((p_hi & 0xFFFF) << 16))
-    lo = full_lo & _MASK
-    hi = ((p_hi >> 16) + (full_lo >> 32)) & _MASK
-    return hi, lo
+    # b holds uint32 values in int64. a * b < 2^64 wraps in int64, but two's-complement wrapping keeps all 64 bits
+    # of the product: the low word is `p & MASK`, the high word the (sign-extending) shift masked back to 32 bits.
+    p = b * a
+    return (p >> 32) & _MASK, p & _MASK
 
 
 def philox4x32(c0, c1, c2, c3, k0: int, k1: int):

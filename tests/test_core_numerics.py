@@ -173,3 +173,31 @@ def test_compute_weights_grads_reach_masters():
     V, U = w.site("a")
     (torch.randn(5, 4).to(torch.bfloat16) @ V @ U).float().sum().backward()
     assert st.V["g"].grad is not None and st.V["g"].grad.dtype == torch.float32
+
+
+def test_host_library_draws_the_reference_stream():
+    """The native CPU loop and the pure-torch statement give the same bits for every (seed, stream, row, column),
+    including seeds and row offsets that use the top bits."""
+    import shutil
+
+    import pytest
+
+    from param_decomp_b200.ops import build, host_native
+
+    if shutil.which("g++") is None and shutil.which("c++") is None:
+        pytest.skip("no C++ compiler")
+    build.build_host()
+    host_native._tried = False  # the library may have been built after the first probe
+    assert host_native.available()
+    for seed, stream, rows, cols, off in ((123, 4, 17, 24, 0), (2**63 + 5, 2**31 + 3, 100, 8, 2**31 - 50),
+                                          (0, 0, 1, 4096, 7), (987654321987, 77, 513, 24, 123456)):
+        assert torch.equal(host_native.philox_uniform(seed, stream, rows, cols, off),
+                           philox_ref.uniform(seed, stream, rows, cols, off)), (seed, stream)
+    from param_decomp_b200.core import rng
+    from param_decomp_b200.core.rng import StepKey
+
+    key = StepKey(11, 5)
+    u = rng.uniform(key, 9, 33, 20, 4, "cpu")  # a width that is not a multiple of 8 is cut from the padded draw
+    assert torch.equal(u, philox_ref.uniform(key.seed64, 9, 33, 24, 4)[:, :20])
+    with pytest.raises(ValueError):
+        host_native.philox_uniform(1, 1, 4, 12)
