@@ -81,6 +81,12 @@ class PreemptionFlag:
         return bool(any_fn(local)) if any_fn is not None else bool(local)
 
 
+def _finalized(evaluation: Any, averaged: dict) -> dict:
+    """Evaluations may form quantities that are not linear in the batch (ratios) from the averaged metrics."""
+    fin = getattr(evaluation, "finalize", None)
+    return fin(averaged) if fin is not None else averaged
+
+
 class StepProfiler:
     """Profiles `n_steps` training steps after `warmup` steps of this entry, then asks the loop to stop.
 
@@ -412,7 +418,7 @@ def run_decomposition_training(
             if evaluation is not None and evaluation.is_due(step):
                 check_device_status("before an evaluation")
                 sync_masters(for_save=False)
-                ev = collectives.average_scalars(evaluation.run(step, state, ctx))
+                ev = _finalized(evaluation, collectives.average_scalars(evaluation.run(step, state, ctx)))
                 if sink is not None and ev:
                     sink.log(step, ev, prefix="eval/")
             if saving and step > 0 and step % cadence.checkpointing.save_every == 0 and ckpt.latest_step(run_dir) != step:  # type: ignore[union-attr,arg-type]
@@ -457,7 +463,7 @@ def run_decomposition_training(
         if state.step >= pd.steps:
             if evaluation is not None and evaluation.is_due(state.step):
                 sync_masters(for_save=False)
-                ev = collectives.average_scalars(evaluation.run(state.step, state, ctx))
+                ev = _finalized(evaluation, collectives.average_scalars(evaluation.run(state.step, state, ctx)))
                 if sink is not None and ev:
                     sink.log(state.step, ev, prefix="eval/")
             save()

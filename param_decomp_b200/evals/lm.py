@@ -30,12 +30,13 @@ def ce_and_kl(ctx: StepContext, state: TrainState, batch: Any, rounding_threshol
     ci = run_ci_fn(ctx, state, clean).mask_inputs()  # masks of expert-blocked sites are narrow (selected blocks only)
     key = StepKey(0xE7A1, 0)
     site_index = ctx.site_index
+    off = global_row_offset(ctx, ci)  # draws are keyed on the global row: the same masks however the batch is split
     variants: dict[str, masking.Masks] = {
         "ci_masked": masking.ci_masks(ci),
         "unmasked": masking.unmasked_no_delta(ci),
-        "stoch_masked": masking.stochastic_masks(ci, key, 0, 0, site_index=site_index, lazy=False),
+        "stoch_masked": masking.stochastic_masks(ci, key, 0, 0, site_index=site_index, row_offset=off, lazy=False),
         "random_masked": masking.stochastic_masks({k: torch.zeros_like(v) for k, v in ci.items()}, key, 1, 0,
-                                                  site_index=site_index, with_delta=False, lazy=False),
+                                                  site_index=site_index, row_offset=off, with_delta=False, lazy=False),
         "rounded_masked": masking.ci_masks({k: (v > rounding_threshold).to(v.dtype) for k, v in ci.items()}),
         "zero_masked": masking.constant_masks(ci, 0.0, None),
     }
@@ -48,10 +49,35 @@ def ce_and_kl(ctx: StepContext, state: TrainState, batch: Any, rounding_threshol
         out[f"kl/{name}"] = float(model.recon_loss(clean, res))
         ce[name] = float(model.ce_loss(res, batch.tokens))
         out[f"ce/{name}"] = ce[name]
-    denom = ce["zero_masked"] - target_ce
     for name in variants:
-        out[f"ce_unrecovered/{name}"] = (ce[name] - target_ce) / denom if abs(denom) > 1e-12 else 0.0
+        if name != "zero_masked":  # linear in the batch, so batch and rank averages commute with it
+            out[f"ce_difference/{name}"] = ce[name] - target_ce
+    out.update(ce_unrecovered(out))
     return out
+
+
+def ce_unrecovered(values: dict[str, float], prefix: str = "") -> dict[str, float]:
+    """`(ce_v - ce_target) / (ce_zero - ce_target)` per mask variant, from whatever CE values `values` holds under
+    `<prefix>ce/...`. A ratio does not commute with averaging: the engine calls this again on the values averaged
+    over evaluation batches and ranks (`LMEvaluation.finalize`), so the logged fraction is the ratio of the means."""
+    target, zero = values.get(prefix + "ce/target"), values.get(prefix + "ce/zero_masked")
+    if target is None or zero is None:
+        return {}
+    denom = zero - target
+    out = {}
+    for k, v in values.items():
+        if k.startswith(prefix + "ce/") and k != prefix + "ce/target":
+            name = k[len(prefix) + 3:]
+            out[f"{prefix}ce_unrecovered/{name}"] = (v - target) / denom if abs(denom) > 1e-12 else 0.0
+    return out
+
+
+def global_row_offset(ctx: StepContext, ci: dict[str, Tensor]) -> int:
+    first = next(iter(ci.values()))
+    rows = 1
+    for n in first.shape[:-1]:
+        rows *= n
+    return ctx.collectives.row_offset(rows)
 
 
 @torch.no_grad()
@@ -74,7 +100,8 @@ def attention_pattern_recon(ctx: StepContext, state: TrainState, batch: Any, sto
     clean = model.clean_forward(batch, capture=keys)
     weights = prepare_compute_weights(state.components, model.compute_dtype).detached()
     ci = run_ci_fn(ctx, state, clean).mask_inputs()
-    masks = (masking.stochastic_masks(ci, StepKey(0xE7A2, 0), 0, 0, site_index=ctx.site_index, lazy=False)
+    masks = (masking.stochastic_masks(ci, StepKey(0xE7A2, 0), 0, 0, site_index=ctx.site_index,
+                                      row_offset=global_row_offset(ctx, ci), lazy=False)
              if stochastic else masking.ci_masks(ci))
     res = model.masked_forward(weights, batch, masks, capture=keys)
     vals = [float(attention_pattern_kl(clean.captures[k], res.captures[k])) for k in keys]
@@ -144,3 +171,11 @@ class LMEvaluation:
 
     def run(self, step: int, state: TrainState, ctx: StepContext) -> dict[str, Any]:
         return run_eval_metrics(self.cfg, step, state, ctx, self.sample, extra=self._extra, run_dir=self.run_dir)
+
+    def finalize(self, averaged: dict[str, Any]) -> dict[str, Any]:
+        """Called by the engine on the metrics averaged over evaluation batches and ranks: quantities that are not
+        linear in the batch are formed here, from the averages."""
+        out = dict(averaged)
+        out.update(ce_unrecovered(out))
+        out.update(ce_unrecovered(out, prefix="ArithmeticCIGrid/probe/"))
+        return out

@@ -44,7 +44,11 @@ def _strategy_masks(ctx: StepContext, state: TrainState, batch: Any, clean, ci, 
     if kind == "ci_masked":
         return masking.ci_masks(ci.mask_inputs())
     if kind == "stochastic":
-        return masking.stochastic_masks(ci.mask_inputs(), StepKey(0xE7A3, 0), 0, 0, site_index=ctx.site_index, lazy=False)
+        from param_decomp_b200.evals.lm import global_row_offset
+
+        inputs = ci.mask_inputs()
+        return masking.stochastic_masks(inputs, StepKey(0xE7A3, 0), 0, 0, site_index=ctx.site_index,
+                                        row_offset=global_row_offset(ctx, inputs), lazy=False)
     ci_lower = ci.mask_inputs()
     lead = tuple(next(iter(ci_lower.values())).shape[:-1])
     positions = lead[1] if ctx.model.has_position_axis and len(lead) > 1 else None

@@ -70,7 +70,7 @@ CI_FUNCTIONS: dict[str, dict[str, Any]] = {
 
 def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1,
                 objective: str = "default", ci: str = "layerwise_mlp", muon: bool = False, family: str = "dense",
-                expert_mode: str = "allreduce") -> LMExperimentConfig:
+                expert_mode: str = "allreduce", with_eval: bool = False) -> LMExperimentConfig:
     """`family: moe` is a top-2-of-5 mixture of experts (five experts on two ranks leave one padding expert); its
     `tp` ranks split the experts, and with `expert_mode: all_to_all` the batch too."""
     raw: dict[str, Any] = {
@@ -95,6 +95,13 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
         "data": {"train": {"kind": "synthetic_zipf"}, "eval": {"kind": "synthetic_zipf", "seed": 1},
                  "layout": "unsegmented_tokens", "seq_len": 128 if cuda else 16},
     }
+    if with_eval:  # evaluated on the last step: every rank scores its rows of the evaluation batch
+        raw["eval"] = {"batch_size": batch, "n_steps": 2, "every": steps - 1 if steps > 1 else 1,
+                       "slow_every": steps - 1 if steps > 1 else 1, "slow_on_first_step": False,
+                       "metrics": [{"type": "CI_L0", "groups": None}, {"type": "CEandKLLosses", "rounding_threshold": 0.1},
+                                   {"type": "PGDReconLoss", "init": "random", "source_shape": "c", "n_steps": 3,
+                                    "step_size": 0.1},
+                                   {"type": "CIMeanPerComponent"}, {"type": "CIActiveCountsPerPosition"}]}
     if family == "moe":
         raw["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 16,
                                          "vocab_size": 100, "n_experts": 5, "experts_per_token": 2}
@@ -243,11 +250,13 @@ def main() -> None:
     ap.add_argument("--muon", action="store_true", help="Muon on the component matrices")
     ap.add_argument("--noise-floor", action="store_true",
                     help="also rerun the one-process arm with another summation order and allow three times its drift")
+    ap.add_argument("--with-eval", action="store_true", help="also compare the evaluation metrics of the last step")
     ap.add_argument("--family", choices=("dense", "moe"), default="dense")
     ap.add_argument("--expert-mode", choices=("allreduce", "all_to_all"), default="allreduce")
     a = ap.parse_args()
     bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp, objective=a.objective, ci=a.ci,
-                muon=a.muon, family=a.family, expert_mode=a.expert_mode, with_noise_floor=a.noise_floor)
+                muon=a.muon, family=a.family, expert_mode=a.expert_mode, with_noise_floor=a.noise_floor,
+                with_eval=a.with_eval)
     if bad:
         print(f"NOT invariant over {a.world} ranks ({a.sharding}):")
         for line in bad:

@@ -124,7 +124,7 @@ def grouped_metric_key(key: str) -> MetricKey:
             return named(("eval", "ci", "l0", "per_position"), f"{thr}-{stat}")
         case ("eval", "l0", site_or_group):
             return MetricKey("eval-ci-l0", site_label(site_or_group))
-        case ("eval", ("ce" | "kl" | "ce_unrecovered") as measure, variant) if variant in _CE_VARIANTS:
+        case ("eval", ("ce" | "kl" | "ce_unrecovered" | "ce_difference") as measure, variant) if variant in _CE_VARIANTS:
             return named(("eval", "reconstruction", measure), variant)
         case ("eval", ("ci_hist" | "ci_mean" | "activation_density") as family, site, stat):
             return MetricKey(f"eval-ci-{label(family[3:] if family.startswith('ci_') else family)}-{label(stat)}",

@@ -67,3 +67,19 @@ def test_adversaries_on_a_mixture_of_experts_are_rank_count_invariant():
     that split the experts and exchange token jobs."""
     assert ic.check(world=2, steps=2, sharding="ddp", batch=4, device="cpu", verbose=False, tp=2, family="moe",
                     expert_mode="all_to_all") == []
+
+
+def test_evaluation_metrics_do_not_depend_on_the_rank_count():
+    """CE / KL under the six mask variants (stochastic draws keyed on global rows), the CE-unrecovered fraction
+    (a ratio, formed from the averaged values), CI statistics and the fresh-PGD probe: one process against two."""
+    assert ic.check(world=2, steps=2, sharding="ddp", batch=4, device="cpu", verbose=False, with_eval=True) == []
+
+
+def test_ce_unrecovered_is_formed_from_averages():
+    from param_decomp_b200.evals.lm import ce_unrecovered
+
+    a = {"ce/target": 1.0, "ce/zero_masked": 3.0, "ce/ci_masked": 2.0}
+    b = {"ce/target": 1.0, "ce/zero_masked": 2.0, "ce/ci_masked": 2.0}
+    mean = {k: (a[k] + b[k]) / 2 for k in a}
+    assert ce_unrecovered(mean)["ce_unrecovered/ci_masked"] == (2.0 - 1.0) / (2.5 - 1.0)  # not (0.5 + 1.0) / 2
+    assert ce_unrecovered({"kl/x": 1.0}) == {}
