@@ -101,7 +101,10 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
                        "metrics": [{"type": "CI_L0", "groups": None}, {"type": "CEandKLLosses", "rounding_threshold": 0.1},
                                    {"type": "PGDReconLoss", "init": "random", "source_shape": "c", "n_steps": 3,
                                     "step_size": 0.1},
-                                   {"type": "CIMeanPerComponent"}, {"type": "CIActiveCountsPerPosition"}]}
+                                   {"type": "CIMeanPerComponent"}, {"type": "CIActiveCountsPerPosition"},
+                                   {"type": "CIHistograms", "n_batches_accum": 2}, {"type": "ComponentActivationDensity"},
+                                   {"type": "CIMaskedAttnPatternsReconLoss"},
+                                   {"type": "StochasticAttnPatternsReconLoss"}]}
     if family == "moe":
         raw["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 16,
                                          "vocab_size": 100, "n_experts": 5, "experts_per_token": 2}
@@ -143,7 +146,10 @@ def trajectory(run_dir: Path) -> dict[int, dict[str, float]]:
 
 
 # wall-clock and memory readings differ between any two runs
-UNCOMPARED = ("perf/", "time/", "mem/", "throughput", "tokens_per_s", "mfu", "step_ms", "elapsed", "lr/")
+# ... and `ce_unrecovered` is a ratio of CE differences already compared one by one; on a random-init target its
+# denominator is near zero and multiplies rounding differences a thousandfold
+UNCOMPARED = ("perf/", "time/", "mem/", "throughput", "tokens_per_s", "mfu", "step_ms", "elapsed", "lr/",
+              "ce_unrecovered/")
 
 
 def relative_gaps(one: dict[int, dict[str, float]], other: dict[int, dict[str, float]]) -> dict[tuple[int, str], float]:
