@@ -168,7 +168,8 @@ def well_temperedness(ctx: StepContext, state: TrainState, batch: Any, n_locatio
     import fnmatch
 
     model = ctx.model
-    g = torch.Generator().manual_seed(seed)
+    B, T = batch.tokens.shape
+    g = torch.Generator().manual_seed(seed + ctx.collectives.row_offset(B))  # every batch shard samples its own rows
     clean = model.clean_forward(batch)
     ci = run_ci_fn(ctx, state, clean)
     dense_sites = [s for s in model.sites if not s.blocked]
@@ -178,7 +179,6 @@ def well_temperedness(ctx: StepContext, state: TrainState, batch: Any, n_locatio
     lower = ci.mask_inputs()
     ones = {k: torch.ones_like(v) for k, v in lower.items()}
     base = model.masked_forward(weights, batch, masking.ci_masks(ones), clean=clean).output
-    B, T = batch.tokens.shape
     regions = ("below_zero", "zero_to_one", "above_one")
     pres, dmg, site_of = [], [], []
     for _ in range(n_locations):
@@ -203,7 +203,20 @@ def well_temperedness(ctx: StepContext, state: TrainState, batch: Any, n_locatio
                 dmg.append(float((a_ - r_).pow(2).sum() / r_.pow(2).sum().clamp_min(1e-30)))
                 pres.append(float(pre_here[flat]))
                 site_of.append(site.name)
-    pre_t, dmg_t = torch.tensor(pres), torch.tensor(dmg)
+    # The score is a statistic of PAIRS, so it is formed once from every batch shard's ablations together (a mean
+    # over ranks of per-rank pair fractions would weight ranks equally whatever they sampled, and one rank with
+    # fewer than two ablations would turn it into NaN). Shards contribute a fixed-size, NaN-padded table.
+    site_names = [s.name for s in dense_sites]
+    quota = n_locations * len(regions) * n_components
+    table = torch.full((quota, 3), float("nan"), dtype=torch.float64)
+    if pres:
+        table[:len(pres)] = torch.tensor([[p, d, float(site_names.index(sn))] for p, d, sn in zip(pres, dmg, site_of)],
+                                         dtype=torch.float64)
+    dev = next(state.components.parameters()).device
+    table = ctx.collectives.gather_rows(table.to(dev)).cpu()
+    table = table[~table[:, 0].isnan()]
+    pre_t, dmg_t = table[:, 0].float(), table[:, 1].float()
+    site_of = [site_names[int(i)] for i in table[:, 2].tolist()]
     res = {"WellTemperedness/all": fraction_well_ordered_pairs(pre_t, dmg_t)}
     for region in regions:
         sel = in_region(pre_t, region)
