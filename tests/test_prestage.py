@@ -117,3 +117,41 @@ def test_row_shuffle_is_seeded_and_uses_worker_processes(tmp_path):
     pos = np.array([index[tuple(r)] for r in rows["a"].tolist()])
     assert (np.abs(np.diff(pos)) == 1).mean() < 0.01
     assert not (tmp_path / "a" / ".row_shuffle_staging").exists()
+
+
+def test_a_prestaged_dataset_trains_with_document_boundaries(tmp_path):
+    """Text -> tokenize -> finish -> a decomposition run that reads the published dataset by name with
+    `layout: documents`: attention and losses stay inside a document, and the prompt encoder finds the tokenizer
+    the dataset names under `<data_root>/tokenizers/`."""
+    import copy
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.config.experiments import LMExperimentConfig
+    from param_decomp_b200.experiments.lm.prompt_encoder import resolve_prompt_encoder
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    root = tmp_path / "root"
+    tok_dir = root / "tokenizers" / "tiny-chars"
+    tok_dir.mkdir(parents=True)
+    _tiny_tokenizer(tok_dir)
+    _write_sources(tmp_path / "src")
+    prestage.tokenize(tmp_path / "src", tok_dir, tmp_path / "staging", seq_len=17, tokenizer_name="tiny-chars")
+    prestage.finish(tmp_path / "staging", root / "datasets" / "tiny", seed=1)
+
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"].update(backend="eager_torch", sharding="ddp")
+    c["target"].update(weights_dtype="float32", attention_implementation="xla")
+    c["target"]["spec"]["arch"] = {"family": "glu_transformer", "n_layer": 1, "d_model": 32, "n_head": 2, "d_ff": 48,
+                                   "vocab_size": 30}
+    c["decomposition"]["sites"]["cs"] = {"q": 8, "down": 8}
+    c["decomposition"]["ci"] = {"type": "layerwise_mlp", "hidden_dims": [8]}
+    c["data"] = {"train": {"kind": "name", "name": "tiny"}, "eval": {"kind": "name", "name": "tiny"},
+                 "layout": "documents", "seq_len": 16}
+    c["pd"].update(batch_size=4, steps=2)
+    c["cadence"] = {"train_log_every": 1, "checkpointing": {"kind": "none"}}
+    c["eval"] = None
+    cfg = LMExperimentConfig.model_validate(c)
+    res = train_lm(cfg, root, device="cpu")
+    assert res.final_step == 2 and res.last_metrics["train/loss/total"] == res.last_metrics["train/loss/total"]
+    enc = resolve_prompt_encoder(cfg.target.spec, cfg.data.train, root, 30)
+    assert enc.source.endswith("tokenizers/tiny-chars") and enc("ab") == [0, 1]
