@@ -70,7 +70,7 @@ CI_FUNCTIONS: dict[str, dict[str, Any]] = {
 
 def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1,
                 objective: str = "default", ci: str = "layerwise_mlp", muon: bool = False, family: str = "dense",
-                expert_mode: str = "allreduce", with_eval: bool = False) -> LMExperimentConfig:
+                expert_mode: str = "allreduce", with_eval: bool = False, documents: bool = False) -> LMExperimentConfig:
     """`family: moe` is a top-2-of-5 mixture of experts (five experts on two ranks leave one padding expert); its
     `tp` ranks split the experts, and with `expert_mode: all_to_all` the batch too."""
     raw: dict[str, Any] = {
@@ -95,6 +95,9 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
         "data": {"train": {"kind": "synthetic_zipf"}, "eval": {"kind": "synthetic_zipf", "seed": 1},
                  "layout": "unsegmented_tokens", "seq_len": 128 if cuda else 16},
     }
+    if documents:  # packed rows with document boundaries (`write_documents_dataset`): segment-confined attention and losses
+        raw["data"].update(train={"kind": "name", "name": DOCUMENTS_DATASET}, eval={"kind": "name", "name": DOCUMENTS_DATASET},
+                           layout="documents")
     if with_eval:  # evaluated on the last step: every rank scores its rows of the evaluation batch
         raw["eval"] = {"batch_size": batch, "n_steps": 2, "every": steps - 1 if steps > 1 else 1,
                        "slow_every": steps - 1 if steps > 1 else 1, "slow_on_first_step": False,
@@ -114,6 +117,23 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
             raw["target"]["expert_implementation"] = "all_to_all"
             raw["runtime"]["mesh"] = {"replicate": 1, "fsdp": world // tp, "tp": tp}
     return LMExperimentConfig.model_validate(raw)
+
+
+DOCUMENTS_DATASET = "invariance-documents"
+
+
+def write_documents_dataset(root: Path, vocab_size: int, seq_len: int, rows: int = 96) -> None:
+    """A small packed corpus under `<root>/datasets/`: random tokens, a new document every few positions."""
+    import numpy as np
+
+    from param_decomp_b200.data.shards import write_token_dataset
+
+    rng = np.random.default_rng(0)
+    tok = rng.integers(0, vocab_size, (rows, seq_len)).astype(np.int32)
+    starts = rng.random((rows, seq_len)) < 0.2
+    starts[:, 0] = False
+    doc = np.cumsum(starts, axis=1).astype(np.int32)
+    write_token_dataset(root / "datasets" / DOCUMENTS_DATASET, tok, doc, "none", rows_per_group=32, rows_per_shard=48)
 
 
 def _run(cfg: LMExperimentConfig, root: Path, run_id: str, device: str) -> tuple[Path, list[torch.Tensor]]:
@@ -211,6 +231,9 @@ def check(world: int, steps: int, sharding: str, batch: int, device: str, rtol: 
     rtol = rtol if rtol is not None else (3e-2 if cuda else 1e-4)  # bf16 operands on the GPU path
     assert world % tp == 0 and batch % (world // tp) == 0, (batch, world, tp)
     with tempfile.TemporaryDirectory() as root:
+        if variant.get("documents"):
+            first = tiny_config(1, steps, sharding, batch, cuda, **variant)
+            write_documents_dataset(Path(root), first.target.spec.arch.vocab_size, first.data.seq_len)
         one_dir, one_params = _run(tiny_config(1, steps, sharding, batch, cuda, **variant), Path(root), "p-00000001",
                                    "cuda:0" if cuda else "cpu")
         with socket.socket() as s:
@@ -256,13 +279,14 @@ def main() -> None:
     ap.add_argument("--muon", action="store_true", help="Muon on the component matrices")
     ap.add_argument("--noise-floor", action="store_true",
                     help="also rerun the one-process arm with another summation order and allow three times its drift")
+    ap.add_argument("--documents", action="store_true", help="train on packed rows with document boundaries")
     ap.add_argument("--with-eval", action="store_true", help="also compare the evaluation metrics of the last step")
     ap.add_argument("--family", choices=("dense", "moe"), default="dense")
     ap.add_argument("--expert-mode", choices=("allreduce", "all_to_all"), default="allreduce")
     a = ap.parse_args()
     bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp, objective=a.objective, ci=a.ci,
                 muon=a.muon, family=a.family, expert_mode=a.expert_mode, with_noise_floor=a.noise_floor,
-                with_eval=a.with_eval)
+                with_eval=a.with_eval, documents=a.documents)
     if bad:
         print(f"NOT invariant over {a.world} ranks ({a.sharding}):")
         for line in bad:
