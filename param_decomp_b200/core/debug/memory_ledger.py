@@ -39,7 +39,7 @@ class Ledger:
                     torch.cuda.max_memory_allocated(self.device))
         return 0, 0, 0
 
-    def _live_tensors(self) -> list[tuple[str, int]]:
+    def _live_tensors(self, with_total: bool = False):
         seen: dict[int, tuple[str, int]] = {}
         for obj in gc.get_objects():
             try:
@@ -50,11 +50,16 @@ class Ledger:
                         seen[key] = (f"{tuple(obj.shape)} {str(obj.dtype).replace('torch.', '')}", st.nbytes())
             except Exception:  # noqa: BLE001  (objects mid-destruction)
                 continue
-        return sorted(seen.values(), key=lambda kv: -kv[1])[: self.top_n]
+        top = sorted(seen.values(), key=lambda kv: -kv[1])[: self.top_n]
+        return (top, sum(b for _, b in seen.values())) if with_total else top
 
     def mark(self, name: str) -> Mark:
         a, r, p = self._stats()
-        m = Mark(name, a, r, p, self._live_tensors())
+        top, total = self._live_tensors(with_total=True)
+        if not torch.cuda.is_available():  # no allocator counters on the host: the live tensors' storages stand in
+            a = r = total
+            p = max([total] + [m.peak_allocated for m in self.marks])
+        m = Mark(name, a, r, p, top)
         self.marks.append(m)
         return m
 
@@ -84,7 +89,29 @@ class Ledger:
         return "\n".join(lines)
 
 
+def main() -> None:
+    """`python -m param_decomp_b200.core.debug.memory_ledger <run_dir | ledger.json> [--top N]`: the peak, every mark,
+    and the largest live tensors at the peak mark. A run started with `runtime.profiling: {kind: ad_hoc, ...}` leaves
+    its ledger at `<run_dir>/profile/memory_ledger.json` (one mark per phase of the first profiled step)."""
+    import argparse
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("path", type=Path)
+    ap.add_argument("--top", type=int, default=12)
+    a = ap.parse_args()
+    path = a.path / "profile" / "memory_ledger.json" if a.path.is_dir() else a.path
+    assert path.exists(), f"no ledger at {path}"
+    led = Ledger.load(path)
+    for m in led.marks:
+        m.top_tensors = m.top_tensors[: a.top]
+    print(led.report())
+
+
 def diff(a: Ledger, b: Ledger) -> list[tuple[str, int]]:
     """Per shared mark: bytes allocated in `b` minus `a` (what a change cost, where)."""
     bm = {m.name: m for m in b.marks}
     return [(m.name, bm[m.name].allocated - m.allocated) for m in a.marks if m.name in bm]
+
+
+if __name__ == "__main__":
+    main()

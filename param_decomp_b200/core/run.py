@@ -106,6 +106,12 @@ class StepProfiler:
             return
         cuda = torch.cuda.is_available()
         if entry_step == self.warmup:
+            if self.run_dir is not None:  # attribute the first profiled step's memory to its phases
+                from param_decomp_b200.core.debug.memory_ledger import Ledger
+                from param_decomp_b200.core.train import phase
+
+                phase.ledger = Ledger()
+                phase.ledger.mark("step_begin")
             if self.kind == "trace":
                 from torch.profiler import ProfilerActivity, profile
 
@@ -127,6 +133,15 @@ class StepProfiler:
         if self._range_open:
             torch.cuda.nvtx.range_pop()
             self._range_open = False
+        if entry_step == self.warmup and self.run_dir is not None:
+            from param_decomp_b200.core.train import phase
+
+            if phase.ledger is not None:
+                phase.ledger.mark("step_end")
+                out = Path(self.run_dir) / "profile"
+                out.mkdir(parents=True, exist_ok=True)
+                phase.ledger.save(out / "memory_ledger.json")
+                phase.ledger = None
         if entry_step < self.warmup + self.n_steps - 1:
             return False
         if self.kind == "trace":

@@ -49,6 +49,9 @@ class phase:
     (the reference labels the same phases with `jax.named_scope`, param_decomp/core/train.py:1247)."""
 
     enabled = torch.cuda.is_available()
+    ledger = None
+    """A `core/debug/memory_ledger.py::Ledger` while a profiled step is being attributed: every phase leaves a mark
+    (allocator counters and the largest live tensors) as it ends."""
 
     def __init__(self, name: str) -> None:
         self.name = name
@@ -60,6 +63,8 @@ class phase:
     def __exit__(self, *exc) -> None:
         if phase.enabled:
             torch.cuda.nvtx.range_pop()
+        if phase.ledger is not None:
+            phase.ledger.mark(self.name)
 
 
 class DataCollectives:

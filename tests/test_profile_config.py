@@ -86,3 +86,28 @@ def test_ad_hoc_profiling_run_traces_and_leaves(tmp_path):
     res = train_lm(LMExperimentConfig.model_validate(c), tmp_path, device="cpu")
     assert (res.run_dir / "profile" / "trace.json").stat().st_size > 0
     assert res.final_step == 4  # two warm-up steps (nothing is recorded on this backend) and the two traced ones
+
+
+def test_profiled_run_leaves_a_memory_ledger_with_phase_marks(tmp_path):
+    import copy
+    import subprocess
+    import sys
+
+    import __graft_entry__ as ge
+    from param_decomp_b200.core.debug.memory_ledger import Ledger
+    from param_decomp_b200.experiments.lm.training import train_lm
+
+    c = copy.deepcopy(ge.SMOKE_CONFIG)
+    c["runtime"].update(backend="eager_torch", sharding="ddp", profiling={"kind": "ad_hoc", "steps": 1})
+    c["target"].update(weights_dtype="float32", attention_implementation="xla")
+    c["data"]["seq_len"] = 8
+    c["pd"].update(batch_size=4, steps=50)
+    c["eval"] = None
+    res = train_lm(LMExperimentConfig.model_validate(c), tmp_path, device="cpu")
+    led = Ledger.load(res.run_dir / "profile" / "memory_ledger.json")
+    names = [m.name for m in led.marks]
+    assert names[0] == "step_begin" and names[-1] == "step_end" and {"ci_fn", "losses", "optimizer"} <= set(names)
+    assert all(m.allocated > 0 and m.top_tensors for m in led.marks)
+    out = subprocess.run([sys.executable, "-m", "param_decomp_b200.core.debug.memory_ledger", str(res.run_dir), "--top", "3"],
+                         capture_output=True, text=True)
+    assert out.returncode == 0 and "peak" in out.stdout and "largest live tensors" in out.stdout
