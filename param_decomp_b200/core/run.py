@@ -99,6 +99,8 @@ class StepProfiler:
         self.kind, self.warmup, self.n_steps, self.run_dir = kind, warmup, n_steps, run_dir
         self._trace: Any = None
         self._range_open = False
+        self._census_cm: Any = None
+        self._census: Any = None
         self.captured: list[int] = []
 
     def before_step(self, entry_step: int) -> None:
@@ -112,6 +114,10 @@ class StepProfiler:
 
                 phase.ledger = Ledger()
                 phase.ledger.mark("step_begin")
+                from param_decomp_b200.core.debug.census import census
+
+                self._census_cm = census()  # what the step launches: native entry points and collectives by kind
+                self._census = self._census_cm.__enter__()
             if self.kind == "trace":
                 from torch.profiler import ProfilerActivity, profile
 
@@ -142,6 +148,12 @@ class StepProfiler:
                 out.mkdir(parents=True, exist_ok=True)
                 phase.ledger.save(out / "memory_ledger.json")
                 phase.ledger = None
+                if self._census_cm is not None:
+                    import json
+
+                    self._census_cm.__exit__(None, None, None)
+                    (out / "census.json").write_text(json.dumps(self._census.summary(), indent=1))
+                    self._census_cm = None
         if entry_step < self.warmup + self.n_steps - 1:
             return False
         if self.kind == "trace":

@@ -111,3 +111,7 @@ def test_profiled_run_leaves_a_memory_ledger_with_phase_marks(tmp_path):
     out = subprocess.run([sys.executable, "-m", "param_decomp_b200.core.debug.memory_ledger", str(res.run_dir), "--top", "3"],
                          capture_output=True, text=True)
     assert out.returncode == 0 and "peak" in out.stdout and "largest live tensors" in out.stdout
+    import json
+
+    counted = json.loads((res.run_dir / "profile" / "census.json").read_text())
+    assert set(counted) == {"native_launches", "native", "collectives", "collective_bytes"}
