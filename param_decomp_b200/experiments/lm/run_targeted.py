@@ -14,11 +14,18 @@ from pathlib import Path
 def main(argv: list[str] | None = None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("config", type=Path)
-    ap.add_argument("--data-root", type=Path, required=True)
-    ap.add_argument("--run-id", type=str, default=None)
+    ap.add_argument("--data-root", "--data_root", type=Path, required=True)
+    ap.add_argument("--run-id", "--run_id", type=str, default=None)
     ap.add_argument("--device", type=str, default=None)
-    ap.add_argument("--max-steps", type=int, default=None)
+    ap.add_argument("--local-device-count", "--local_device_count", type=int, default=None,
+                    help="accepted for command lines written for the reference (one process per GPU here: the "
+                         "launcher sets the process count); checked against LOCAL_WORLD_SIZE when both are known")
+    ap.add_argument("--max-steps", "--max_steps", type=int, default=None)
     args = ap.parse_args(argv)
+    local = os.environ.get("LOCAL_WORLD_SIZE")
+    if args.local_device_count is not None and local is not None:
+        assert int(local) == args.local_device_count, (
+            f"--local-device-count {args.local_device_count}, but the launcher started {local} processes on this node")
 
     from param_decomp_b200.config.experiments import LMTargetedExperimentConfig
 

@@ -75,8 +75,8 @@ def run_resid_mlp(cfg: ResidMLPExperimentConfig, data_root: Path | None, run_id:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("config", type=Path)
-    ap.add_argument("--data-root", type=Path, required=True)
-    ap.add_argument("--run-id", type=str, default=None)
+    ap.add_argument("--data-root", "--data_root", type=Path, required=True)
+    ap.add_argument("--run-id", "--run_id", type=str, default=None)
     ap.add_argument("--device", type=str, default="cpu")
     args = ap.parse_args()
     cfg = ResidMLPExperimentConfig.from_file(args.config)

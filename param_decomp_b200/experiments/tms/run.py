@@ -74,8 +74,8 @@ def run_tms(cfg: TMSExperimentConfig, data_root: Path | None, run_id: str | None
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("config", type=Path)
-    ap.add_argument("--data-root", type=Path, required=True)
-    ap.add_argument("--run-id", type=str, default=None)
+    ap.add_argument("--data-root", "--data_root", type=Path, required=True)
+    ap.add_argument("--run-id", "--run_id", type=str, default=None)
     ap.add_argument("--device", type=str, default="cpu")
     args = ap.parse_args()
     cfg = TMSExperimentConfig.from_file(args.config)

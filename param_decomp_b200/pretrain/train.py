@@ -324,8 +324,8 @@ def pretrain(cfg: PretrainConfig, data_root: Path | None = None, run_id: str | N
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("config", type=Path)
-    ap.add_argument("--data-root", type=Path, default=None)
-    ap.add_argument("--run-id", type=str, default=None)
+    ap.add_argument("--data-root", "--data_root", type=Path, default=None)
+    ap.add_argument("--run-id", "--run_id", type=str, default=None)
     ap.add_argument("--device", type=str, default=None)
     args = ap.parse_args()
     device = args.device
