@@ -391,6 +391,8 @@ class Qwen35DecomposedModel(moe.MoEDecomposedModel):
             resid = self._block(i, resid, cos, sin, batch, weights, masks, taps, captures, want, aux)
         if taps is not None:
             taps[f"resid.{a.n_layer}"] = resid
+        if f"resid.{a.n_layer}" in want:  # the boundary that leaves the last block, as the dense transformer captures it
+            captures[f"resid.{a.n_layer}"] = resid
         final = self._norm(resid, self.w["final_norm.weight"])
         return ForwardResult(output=final, taps=taps or {}, captures=captures, aux=aux)
 
