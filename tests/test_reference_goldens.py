@@ -137,3 +137,56 @@ def test_recorded_huggingface_logits_and_residual_streams(tmp_path, fixture, ext
         assert torch.allclose(got, want, atol=5e-4, rtol=1e-3), (i, float((got - want).abs().max()))
     want = torch.from_numpy(np.asarray(f["logits"]))
     assert torch.allclose(logits, want, atol=5e-4, rtol=1e-3), float((logits - want).abs().max())
+
+
+def test_gqa_suffix_with_scaled_rope_matches_recorded_clean_and_masked_logits():
+    """Five Llama blocks (grouped-query attention, Llama-3.1 rescaled RoPE) fed a recorded residual stream, gated-MLP
+    sites of the first three decomposed with recorded `V`, `U`, component masks and delta masks: recorded clean
+    logits, every site's input, every weight delta and the all-sites masked logits."""
+    from param_decomp_b200.config.experiments import Llama3RopeScalingConfig
+    from param_decomp_b200.core.masking import SiteMask
+
+    f = dict(np.load(TARGETS / "stacked_parity" / "stacked_fixtures.npz"))
+    t = lambda k: torch.from_numpy(np.asarray(f[k])).float()  # noqa: E731
+    first, last, C = int(f["_scalar_FIRST_LAYER"]), int(f["_scalar_LAST_LAYER"]), int(f["_scalar_C"])
+    B, T, n_layer_total = int(f["_scalar_B"]), int(f["_scalar_T"]), 8
+    resid = t("resid")
+    d = resid.shape[-1]
+    arch = TransformerArchConfig(
+        family="glu_transformer", n_layer=n_layer_total - first, d_model=d, n_head=4, n_kv_head=2, d_ff=64,
+        vocab_size=B * T, rms_eps=1e-5, rope_theta=500000.0, max_seq_len=512,
+        rope_scaling=Llama3RopeScalingConfig(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                             original_max_position_embeddings=128))
+    w = tf.random_init_weights(arch, 0, torch.float32)
+    w["embed.weight"] = resid.reshape(B * T, d)
+    for i in range(arch.n_layer):
+        src = f"tgt::layers.{i + first}."
+        w[f"layers.{i}.attn_norm.weight"], w[f"layers.{i}.mlp_norm.weight"] = t(src + "ln1"), t(src + "ln2")
+        for ours, theirs in (("q", "wq"), ("k", "wk"), ("v", "wv"), ("o", "wo")):
+            w[f"layers.{i}.self_attn.{ours}_proj.weight"] = t(src + theirs)
+        for ours, theirs in (("gate", "Wg"), ("up", "Wu"), ("down", "Wd")):
+            w[f"layers.{i}.mlp.{ours}_proj.weight"] = t(src + theirs)
+    w["final_norm.weight"], w["lm_head.weight"] = t("tgt::norm"), t("tgt::lm_head")
+
+    theirs_of = {tf.site_name("glu_transformer", i - first, k): f"layers.{i}.mlp.{k}_proj"
+                 for i in range(first, last + 1) for k in ("gate", "up", "down")}
+    model = tf.TransformerDecomposedModel(arch, w, {n: C for n in theirs_of}, backend="eager_torch", attention="xla")
+    stacks = ComponentStacks(model.sites)
+    for ours, theirs in theirs_of.items():
+        stacks.set_site(ours, t(f"vu::V::{theirs}"), t(f"vu::U::{theirs}"))
+    batch = tf.LMBatch(torch.arange(B * T).reshape(B, T))
+    close = lambda a, b: torch.allclose(a, b, rtol=1e-4, atol=2e-5)  # noqa: E731
+    with torch.no_grad():
+        clean = model.clean_forward(batch)
+        assert close(model.logits(clean.output), t("out::clean"))
+        for ours, theirs in theirs_of.items():
+            layer = int(ours.split(".")[1])
+            tap = clean.taps[f"mlp_hidden.{layer}" if ours.endswith("down_proj") else f"mlp_in.{layer}"]
+            assert close(tap, t(f"out::site_input::{theirs}")), ours
+            V, U = stacks.site(ours)
+            assert close(losses.weight_delta(w[ours + ".weight"], V, U), t(f"out::wd::{theirs}")), ours
+        masks = {ours: SiteMask(mask=t(f"mask::{theirs}"), delta=t(f"delta_mask::{theirs}").unsqueeze(-1))
+                 for ours, theirs in theirs_of.items()}
+        weights = prepare_compute_weights(stacks, torch.float32)
+        masked = model.masked_forward(weights, batch, masks, clean=clean)
+        assert close(model.logits(masked.output), t("out::masked_all"))
