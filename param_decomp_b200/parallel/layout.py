@@ -59,4 +59,11 @@ def resolve(runtime_cfg: Any, sites: tuple | None = None, world: int | None = No
         rules.shard_factor(rules.components.operands, "C", tp_mesh) > 1
     if sites is not None:
         pl.validate_sites(rules, mesh, sites)
-    return RuntimeLayout(rules, mesh, sharded, c_split, pl.stack_multiple(rules, mesh))
+    # this runtime's sharded optimizers split a group's stack (Muon: whole matrices for Newton-Schulz) or its flat
+    # buffer over EVERY batch rank, so stacks tile the batch axes' product whenever the state is sharded
+    batch_world = 1
+    for a in batch:
+        batch_world *= mesh[a]
+    splits_ns = bool(rules.components.ns_compute.get("stack"))  # a table with replicated Newton-Schulz needs no tiling
+    multiple = max(pl.stack_multiple(rules, mesh), batch_world if (sharded and splits_ns) else 1)
+    return RuntimeLayout(rules, mesh, sharded, c_split, multiple)

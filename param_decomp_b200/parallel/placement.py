@@ -89,15 +89,19 @@ class PlacementRules:
         return n
 
 
-def _target(batch: tuple[str, ...], fsdp: tuple[str, ...]) -> TargetPlacement:
+def _target(batch: tuple[str, ...], fsdp: tuple[str, ...], tensor_parallel: bool = True) -> TargetPlacement:
+    """The frozen target's rows: column / row parallel linears over `tp` (persisted further over `fsdp` where the
+    mesh has that axis), embedding and output head persisted over `fsdp` along `d_model` and used whole. `ddp`
+    keeps the target whole on every rank (`tensor_parallel=False`)."""
+    tp = ("tp",) if tensor_parallel else ()
     return TargetPlacement(
-        embedding_persist=_rule(vocab=fsdp, d_model="tp"),
-        column_persist=_rule(d_in=fsdp, d_out="tp"),
-        row_persist=_rule(d_in="tp", d_out=fsdp),
-        column_operand=_rule(d_out="tp"),
-        row_operand=_rule(d_in="tp"),
+        embedding_persist=_rule(d_model=fsdp),
+        column_persist=_rule(d_in=fsdp, d_out=tp),
+        row_persist=_rule(d_in=tp, d_out=fsdp),
+        column_operand=_rule(d_out=tp),
+        row_operand=_rule(d_in=tp),
         output_persist=_rule(d_model=fsdp),
-        intermediate=_rule(batch=batch, feature="tp", q_head="tp", kv_head="tp"),
+        intermediate=_rule(batch=batch, feature=tp, q_head=tp, kv_head=tp),
     )
 
 
@@ -106,18 +110,20 @@ def _preset(name: str) -> PlacementRules:
     ext_h = _rule(batch=hs_batch)
     ext_r = _rule(batch=rs_batch)
     comp_h, comp_r = _rule(batch=hs_batch, C="tp"), _rule(batch=rs_batch, C="tp")
+    # The rows below restate the reference's preset tables (param_decomp/core/placement.py:1011-1116); the resolved
+    # rules of the dense presets are compared with its recorded tables in tests/test_reference_goldens.py.
     if name == "ddp":
         rep = _rule()
-        c = ComponentsPlacement(rep, rep, rep, rep, rep, rep)
-        return PlacementRules(name, HSDP_AXES, c, ext_h, _rule(batch=hs_batch), _target(hs_batch, ()), "ddp")
+        c = ComponentsPlacement(rep, rep, rep, rep, rep, ns_compute=_rule(stack="replicate"))
+        return PlacementRules(name, HSDP_AXES, c, ext_h, comp_h, _target(hs_batch, (), tensor_parallel=False), "ddp")
     if name == "owner":
         c = ComponentsPlacement(
             optimizer_state=_rule(stack="replicate", d_in="fsdp", d_out="fsdp", C="tp"),
             compute_weights=_rule(d_in="fsdp", d_out="fsdp", C="tp"),
             faithfulness_weights=_rule(stack="replicate", d_in="fsdp", d_out="fsdp", C="tp"),
-            faithfulness_deltas=_rule(stack="replicate", d_out="fsdp", d_in="tp"),
+            faithfulness_deltas=_rule(stack="replicate", d_out="fsdp"),
             operands=_rule(C="tp"),
-            ns_compute=_rule(stack=("replicate", "fsdp")),
+            ns_compute=_rule(stack="replicate"),
         )
         return PlacementRules(name, HSDP_AXES, c, ext_h, comp_h, _target(hs_batch, ("fsdp",)), "owner")
     if name == "zero1":
@@ -127,7 +133,7 @@ def _preset(name: str) -> PlacementRules:
             faithfulness_weights=_rule(d_in="fsdp", d_out="fsdp", C=("tp", "replicate")),
             faithfulness_deltas=_rule(d_out="fsdp", d_in=("tp", "replicate")),
             operands=_rule(C="tp"),
-            ns_compute=_rule(stack=("replicate", "fsdp")),
+            ns_compute=_rule(stack="replicate"),
         )
         return PlacementRules(name, HSDP_AXES, c, ext_h, comp_h, _target(hs_batch, ("fsdp",)), "zero1")
     resident = {
@@ -139,14 +145,19 @@ def _preset(name: str) -> PlacementRules:
     }
     if name in resident:
         kind, moe, rep_ns = resident[name]
-        if kind == "zero1":
-            opt = _rule(d_in="data", d_out="data", C="tp", C_block="data" if moe else None, expert="tp" if moe else None)
+        if kind == "zero1" and moe:
+            opt = _rule(d_in="data", d_out="data", C="tp", C_block="data", expert="tp")
+        elif kind == "zero1":
+            opt = _rule(C=("tp", "data"))  # intra-matrix: the component axis carries both splits
         else:
             opt = _rule(stack="data", C="tp", expert="tp" if moe else None)
         working = _rule(C="tp", expert="tp" if moe else None)
+        if kind == "owner":
+            deltas = _rule(stack="data")
+        else:
+            deltas = _rule(d_out="data", d_in="tp") if moe else _rule(d_in=("tp", "data"))
         c = ComponentsPlacement(
-            optimizer_state=opt, compute_weights=working, faithfulness_weights=opt,
-            faithfulness_deltas=_rule(stack="data") if kind == "owner" else _rule(d_out="data", d_in="tp"),
+            optimizer_state=opt, compute_weights=working, faithfulness_weights=opt, faithfulness_deltas=deltas,
             operands=working, ns_compute=_rule() if rep_ns else _rule(stack="data"),
         )
         return PlacementRules(name, RESIDENT_AXES, c, ext_r, comp_r, _target(rs_batch, ()), name,
@@ -195,11 +206,10 @@ def from_config(spec: str | PlacementTableConfig, mesh: dict[str, int]) -> Place
 
 
 def stack_multiple(rules: PlacementRules, mesh: dict[str, int]) -> int:
-    """Stack lengths are padded to this multiple so the `stack` axis tiles every role that shards it."""
-    n = 1
-    for role in (rules.components.optimizer_state, rules.components.ns_compute):
-        n = max(n, rules.shard_factor(role, "stack", mesh))
-    return n
+    """The multiple the placement itself asks stacks to be padded to: the factor by which the persisted state
+    splits the `stack` axis (param_decomp/core/placement.py:183-220). What this runtime adds on top (its sharded
+    optimizers deal whole matrices or flat ranges to every batch rank) is `layout.resolve`'s business."""
+    return rules.shard_factor(rules.components.optimizer_state, "stack", mesh)
 
 
 @dataclass

@@ -190,3 +190,49 @@ def test_gqa_suffix_with_scaled_rope_matches_recorded_clean_and_masked_logits():
         weights = prepare_compute_weights(stacks, torch.float32)
         masked = model.masked_forward(weights, batch, masks, clean=clean)
         assert close(model.logits(masked.output), t("out::masked_all"))
+
+
+def test_dense_placement_presets_match_the_recorded_tables():
+    """Every dense preset on every recorded mesh: the resolved rules of the component roles, the activations and the
+    target rows, the stack padding of the recorded site groups, and a refusal wherever the preset's axis vocabulary
+    is not the mesh's."""
+    from param_decomp_b200.parallel import placement as pl
+
+    gold = json.loads((TARGETS.parent / "core" / "placement_goldens.json").read_text())
+    presets = {"ddp": "ddp", "owner": "owner", "zero1": "zero1", "owner_replicated_resident": "owner-replicated-resident",
+               "zero1_replicated_resident": "zero1-replicated-resident"}
+
+    def norm(rule) -> dict:
+        return {k: tuple(v) for k, v in rule.items() if tuple(v)}
+
+    checked = 0
+    for key, entry in gold.items():
+        head, mesh_name, _sites = (key.split("|") + ["", ""])[:3]
+        if not head.startswith("preset_") or head[7:] not in presets:
+            continue
+        mesh = {m.rstrip("0123456789"): int(m[len(m.rstrip("0123456789")):]) for m in mesh_name.split("_")}
+        name = presets[head[7:]]
+        if "refused" in entry:
+            with pytest.raises(AssertionError):
+                pl.from_config(name, mesh)
+            checked += 1
+            continue
+        rules = pl.from_config(name, mesh)
+        want = entry["rules"]
+        for role in ("optimizer_state", "compute_weights", "faithfulness_weights", "faithfulness_deltas", "operands",
+                     "ns_compute"):
+            assert norm(getattr(rules.components, role)) == norm(want["components"][role]["rule"]), (key, role)
+        assert norm(rules.activations_external) == norm(want["activations"]["external"]["rule"]), key
+        assert norm(rules.activations_component) == norm(want["activations"]["component"]["rule"]), key
+        t = want["target"]
+        for ours, theirs in (("embedding_persist", t["embedding"]["persist"]), ("column_persist", t["column"]["persist"]),
+                             ("row_persist", t["row"]["persist"]), ("column_operand", t["column"]["operand"]),
+                             ("row_operand", t["row"]["operand"]), ("output_persist", t["output"]["persist"]),
+                             ("intermediate", t["intermediate"])):
+            assert norm(getattr(rules.target, ours)) == norm(theirs["rule"]), (key, ours)
+        assert rules.ci_fn_preset == want["ci_fn"]
+        multiple = pl.stack_multiple(rules, mesh)
+        for group, census in want["components"]["group_census"].items():
+            assert (-census["stack_len"]) % multiple == census["stack_pad"], (key, group)
+        checked += 1
+    assert checked >= 25
