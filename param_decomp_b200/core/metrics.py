@@ -97,15 +97,19 @@ class MetricsSink:
         return sink
 
     def log(self, step: int, scalars: dict[str, Any], prefix: str = "train/") -> dict[str, float]:
+        """Writes one record and returns it as written. The file and the `legacy` W&B mirror use the reference's
+        key spellings (`infra/reference_keys.py`); the `grouped` names are derived from the internal keys."""
         flat = {prefix + k: to_float(v) for k, v in scalars.items()}
+        written = public_record(flat)
         if self.rank == 0 and self._fh is not None:
-            self._fh.write(json.dumps({"step": step, **flat}) + "\n")
+            self._fh.write(json.dumps({"step": step, **written}) + "\n")
             if self.wandb_run is not None:
                 try:
-                    self.wandb_run.log(self.names.record(flat) if self.names is not None else flat, step=step)
+                    grouped = self.names is not None and self.names.schema != "legacy"
+                    self.wandb_run.log(self.names.record(flat) if grouped else written, step=step)
                 except Exception as err:  # W&B trouble is never fatal
                     get_logger().warning("wandb.log failed: %s", err)
-        return flat
+        return written
 
     def close(self) -> None:
         if self._fh is not None:
@@ -116,6 +120,13 @@ class MetricsSink:
                 self.wandb_run.finish()
             except Exception:
                 pass
+
+
+def public_record(flat: dict[str, float]) -> dict[str, float]:
+    """Internal keys -> the keys that are written (also what a run without a sink reports as its last metrics)."""
+    from param_decomp_b200.infra.reference_keys import reference_keys
+
+    return reference_keys(flat)
 
 
 def try_wandb_init(cfg: Any, run_name: str, run_dir: Path, config_dict: dict | None) -> Any:

@@ -39,6 +39,7 @@ from param_decomp_b200.core.metrics import (
     PerformanceTracker,
     assert_all_finite,
     get_logger,
+    public_record,
 )
 from param_decomp_b200.core.model import DecomposedModel
 from param_decomp_b200.core.objective import NontargetObjective, PDObjective, build_objective
@@ -463,6 +464,9 @@ def run_decomposition_training(
             if cadence.should_log_train(step) or state.step == pd.steps:
                 check_device_status("at a log step")
                 scalars = {k: v for k, v in metrics.items()}
+                if "grad_norm/components" in scalars and "grad_norm/ci_fn" in scalars:
+                    scalars["grad_norm/total"] = (float(scalars["grad_norm/components"]) ** 2
+                                                  + float(scalars["grad_norm/ci_fn"]) ** 2) ** 0.5
                 scalars.update(perf.tick(state.step))
                 from param_decomp_b200.core.gauge import uv_norm_ratio_metrics
 
@@ -472,7 +476,7 @@ def run_decomposition_training(
                 if extra_log is not None:
                     scalars.update(extra_log(step, state, ctx))
                 scalars = collectives.average_scalars(scalars)  # per-batch losses: the global-batch mean, as the reference logs
-                floats = sink.log(step, scalars) if sink is not None else {("train/" + k): float(v) for k, v in scalars.items()}
+                floats = sink.log(step, scalars) if sink is not None else public_record({("train/" + k): float(v) for k, v in scalars.items()})
                 assert_all_finite(step, floats)
                 result.last_metrics = floats
                 log.info("step %d  total=%.4e  step_time=%.3fs", step, floats.get("train/loss/total", float("nan")),

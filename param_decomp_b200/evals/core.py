@@ -27,9 +27,10 @@ from param_decomp_b200.core.train import StepContext, TrainState, masked_recon, 
 def ci_l0(ci_lower: dict[str, Tensor], threshold: float, groups: dict[str, list[str]] | None) -> dict[str, float]:
     """Mean number of components with CI > threshold per position, per site and per group."""
     per_site = {s: float((c > threshold).float().sum(-1).mean()) for s, c in ci_lower.items()}
-    out = {f"l0/{s}": v for s, v in per_site.items()}
+    thr = str(float(threshold))  # keyed `l0/<threshold>_<site>` (param_decomp/core/ci_l0_eval.py:89)
+    out = {f"l0/{thr}_{s}": v for s, v in per_site.items()}
     for g, pats in (groups or {}).items():
-        out[f"l0/{g}"] = sum(v for s, v in per_site.items() if any(fnmatch(s, p) for p in pats))
+        out[f"l0/{thr}_{g}"] = sum(v for s, v in per_site.items() if any(fnmatch(s, p) for p in pats))
     return out
 
 

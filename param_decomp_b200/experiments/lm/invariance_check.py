@@ -169,7 +169,7 @@ def trajectory(run_dir: Path) -> dict[int, dict[str, float]]:
 # ... and `ce_unrecovered` is a ratio of CE differences already compared one by one; on a random-init target its
 # denominator is near zero and multiplies rounding differences a thousandfold
 UNCOMPARED = ("perf/", "time/", "mem/", "throughput", "tokens_per_s", "mfu", "step_ms", "elapsed", "lr/",
-              "ce_unrecovered/")
+              "ce_unrecovered")
 
 
 def relative_gaps(one: dict[int, dict[str, float]], other: dict[int, dict[str, float]]) -> dict[tuple[int, str], float]:

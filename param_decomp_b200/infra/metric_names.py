@@ -94,7 +94,15 @@ def _strip_brackets(chart: str) -> tuple[str, str | None]:
 
 
 def grouped_metric_key(key: str) -> MetricKey:
-    """The grouped name of a local key. Raises `ValueError` for keys outside the grammar."""
+    """The grouped name of a local key (internal or as written to `metrics.jsonl`, `infra/reference_keys.py`).
+    Raises `ValueError` for keys outside the grammar."""
+    from param_decomp_b200.infra.reference_keys import internal_key
+
+    key = internal_key(key)
+    pretrain = {"pretrain/loss": ("pretrain-loss", "train"), "pretrain/val_loss": ("pretrain-loss", "validation"),
+                "pretrain/lr": ("pretrain-schedules", "lr"), "pretrain/step_time_s": ("pretrain-performance", "step-time-s")}
+    if key in pretrain:
+        return MetricKey(*pretrain[key])
     parts = tuple(key.split("/"))
     match parts:
         case ("train", "loss", "total"):
@@ -123,6 +131,10 @@ def grouped_metric_key(key: str) -> MetricKey:
         case ("eval", "l0", "per_position", thr, stat):
             return named(("eval", "ci", "l0", "per_position"), f"{thr}-{stat}")
         case ("eval", "l0", site_or_group):
+            thr = re.match(r"^(\d+(?:\.\d+)?(?:e-?\d+)?)_(.+)$", site_or_group)  # `<threshold>_<site or group>`
+            if thr is not None:
+                tag = thr.group(1).replace(".", "p")
+                return MetricKey(f"eval-ci-l0-gt-{tag}", site_label(thr.group(2)))
             return MetricKey("eval-ci-l0", site_label(site_or_group))
         case ("eval", ("ce" | "kl" | "ce_unrecovered" | "ce_difference") as measure, variant) if variant in _CE_VARIANTS:
             return named(("eval", "reconstruction", measure), variant)

@@ -21,6 +21,7 @@ import os
 import re
 import signal
 import threading
+import time
 from pathlib import Path
 from typing import Any, Literal
 
@@ -265,7 +266,7 @@ def pretrain(cfg: PretrainConfig, data_root: Path | None = None, run_id: str | N
     start = restore_latest_train_state(entry, weights, opt)
     if start:
         log.info("pretrain resumed from iteration %d", start)
-    sink = MetricsSink.for_run(entry, dp.rank)
+    sink = MetricsSink.for_run(entry, dp.rank, cfg.wandb, cfg.run_name, cfg.model_dump(mode="json"))
 
     def loss_on(batch) -> torch.Tensor:
         cls = qwen35.Qwen35DecomposedModel if hybrid else tf.TransformerDecomposedModel
@@ -286,6 +287,7 @@ def pretrain(cfg: PretrainConfig, data_root: Path | None = None, run_id: str | N
         dp.barrier()
 
     n_iter = min(cfg.num_iterations, max_iterations or cfg.num_iterations)
+    last_log = (start, time.perf_counter())
     with _SigtermFlag() as preempt:
         for it in range(start, n_iter):
             for g in opt.param_groups:
@@ -300,7 +302,10 @@ def pretrain(cfg: PretrainConfig, data_root: Path | None = None, run_id: str | N
             last = it == n_iter - 1
             if it % cfg.log_every == 0 or last:
                 mean_loss = dp.mean(float(loss.detach()), device)
-                sink.log(it, {"loss": mean_loss, "lr": lr_at(cfg, it)}, prefix="pretrain/")
+                now = time.perf_counter()
+                step_time = (now - last_log[1]) / max(1, it - last_log[0]) if it > last_log[0] else 0.0
+                last_log = (it, now)
+                sink.log(it, {"loss": mean_loss, "lr": lr_at(cfg, it), "step_time_s": step_time}, prefix="pretrain/")
                 log.info("pretrain it %d loss %.4f", it, mean_loss)
             if (it + 1) % cfg.val_every == 0 or last:
                 with torch.no_grad():  # the fixed evaluation set: the first `val_steps` batches, the same at every eval

@@ -120,9 +120,9 @@ def test_sharded_optimizer_trains_after_faithfulness_warmup():
         ref_metrics, ref_params, _ = _snapshot(res, st)
         for r in range(2):
             metrics, params, _ = out[r]
-            assert metrics["train/grad_norm/components"] > 0.0
+            assert metrics["train/grad_norms/summary/components"] > 0.0
             assert metrics["train/loss/total"] == pytest.approx(ref_metrics["train/loss/total"], rel=1e-4)
-            assert metrics["train/grad_norm/components"] == pytest.approx(ref_metrics["train/grad_norm/components"], rel=1e-3)
+            assert metrics["train/grad_norms/summary/components"] == pytest.approx(ref_metrics["train/grad_norms/summary/components"], rel=1e-3)
 
 
 def _eval_value(root, run_id: str, key: str) -> float:
@@ -144,8 +144,8 @@ def test_adversary_sources_under_data_parallel(shape):
         res, st = _train(_cfg(1, _pgd_losses(shape), "ddp", save=True), root, "p-0000cccc")
         ref_metrics, ref_params, ref_adv = _snapshot(res, st)
         # evaluation probe with batch-shared sources: the ranks ascend ONE source on the global-batch gradient
-        assert _eval_value(root, "p-0000aaaa", "eval/PGDReconLoss_3step") == pytest.approx(
-            _eval_value(root, "p-0000cccc", "eval/PGDReconLoss_3step"), rel=2e-3)  # sign steps amplify rounding
+        assert _eval_value(root, "p-0000aaaa", "eval/loss/PGDReconLoss_3step") == pytest.approx(
+            _eval_value(root, "p-0000cccc", "eval/loss/PGDReconLoss_3step"), rel=2e-3)  # sign steps amplify rounding
         (term,) = ref_adv.keys()
         for key, ref in ref_adv[term].items():
             a, b = out[0][2][term][key], out[1][2][term][key]

@@ -34,8 +34,8 @@ def test_tms_runs_and_writes_run_dir(tmp_path):
     lines = [json.loads(l) for l in (rd / "metrics.jsonl").read_text().splitlines()]
     train = [l for l in lines if "train/loss/total" in l]
     assert {"train/loss/FaithfulnessLoss", "train/loss/StochasticReconLoss", "train/perf/step_time_s",
-            "train/grad_norm/components", "train/schedules/lr_components"} <= set(train[0])
-    assert any("eval/l0/linear1" in l for l in lines) and any("eval/PGDReconLoss_2step" in l for l in lines)
+            "train/grad_norms/summary/components", "train/schedules/lr/components"} <= set(train[0])
+    assert any("eval/l0/0.0_linear1" in l for l in lines) and any("eval/loss/PGDReconLoss_2step" in l for l in lines)
     assert ckpt.list_steps(rd) == [20, 30]  # keep_last 2
     assert train[-1]["train/loss/total"] < train[0]["train/loss/total"]
 

@@ -87,7 +87,7 @@ def test_expert_split_engine_matches_single_process(mode, n_experts, k, world, b
         res, ref = _train(_cfg(1, "allreduce", n_experts, k, batch), Path(root), SINGLE_ID)
         ref_params = dict(ref.components.named_parameters())
         for k in ("loss/total", "loss/FaithfulnessLoss", "loss/StochasticReconLoss", "loss/ImportanceMinimalityLoss",
-                  "grad_norm/components", "grad_norm/ci_fn"):
+                  "grad_norms/summary/components", "grad_norms/summary/ci_fns"):
             got = sum(out[r][0]["train/" + k] for r in range(world)) / world  # (per-rank batch shards under all_to_all)
             want = res.last_metrics["train/" + k]
             assert abs(got - want) <= 2e-4 * abs(want) + 1e-7, (k, got, want)

@@ -88,7 +88,7 @@ def test_tms_slow_evals_write_figures_and_scalars():
         keys = {k for l in lines for k in l}
         for want in ("eval/ci_hist/linear1/frac_above_0.5", "eval/ci_mean/linear1/n_dead",
                      "eval/activation_density/linear2/alive_frac", "eval/identity_ci_error/linear1",
-                     "eval/PGDReconLoss_2step", "eval/l0/linear1"):
+                     "eval/loss/PGDReconLoss_2step", "eval/l0/0.0_linear1"):
             assert want in keys, (want, sorted(k for k in keys if k.startswith("eval/"))[:40])
         figs = {p.name for p in (res.run_dir / "figures").iterdir()}
         assert any(n.startswith("ci_histograms_step4") for n in figs) and any(n.startswith("mean_ci_step4") for n in figs)

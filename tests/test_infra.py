@@ -117,3 +117,32 @@ def test_ci_attention_checkpoint_migration():
         save_file({k: v.contiguous() for k, v in old.items()}, str(src / "decomposition.safetensors"), metadata={"format": "x"})
         MG.migrate_checkpoint_step(src, dst)
         assert set(load_file(str(dst / "decomposition.safetensors"))) == set(new)
+
+
+def test_written_keys_use_the_reference_spellings():
+    from param_decomp_b200.infra.reference_keys import reference_key, reference_keys
+
+    pairs = {
+        "train/loss/total": "train/loss/total",
+        "train/loss/FaithfulnessLoss": "train/loss/FaithfulnessLoss",
+        "train/grad_norm/components": "train/grad_norms/summary/components",
+        "train/grad_norm/ci_fn": "train/grad_norms/summary/ci_fns",
+        "train/grad_norm/total": "train/grad_norms/summary/total",
+        "train/schedules/gamma": "train/schedules/gamma_imp",
+        "train/schedules/lr_components": "train/schedules/lr/components",
+        "train/schedules/lr_ci_fn": "train/schedules/lr/ci_fn",
+        "train/perf/step_time_s": "train/perf/step_time_s",
+        "eval/kl/ci_masked": "eval/ce_kl/kl_ci_masked",
+        "eval/ce_difference/stoch_masked": "eval/ce_kl/ce_difference_stoch_masked",
+        "eval/ce/target": "eval/ce_kl/ce_target",
+        "eval/PGDReconLoss_20step": "eval/loss/PGDReconLoss_20step",
+        "eval/SlowPGDReconLoss_640step/hidden_acts_reconstruction": "eval/loss/SlowPGDReconLoss_640step/hidden_acts_reconstruction",
+        "eval/l0/0.0_layers.0.mlp.up_proj": "eval/l0/0.0_layers.0.mlp.up_proj",
+        "eval/ArithmeticCIGrid/probe/kl/ci_masked": "eval/ArithmeticCIGrid/probe/ce_kl/kl_ci_masked",
+    }
+    for ours, theirs in pairs.items():
+        assert reference_key(ours) == theirs, ours
+    assert set(reference_keys(dict.fromkeys(pairs, 1.0))) == set(pairs.values())
+    # the grouped names are derived from the internal keys, thresholded L0 keys included
+    k = MN.grouped_metric_key
+    assert k("eval/l0/0.1_layers.2.self_attn.q_proj").path == "eval-ci-l0-gt-0p1/layer-02-01-attn-q"

@@ -46,7 +46,7 @@ def test_resume_is_exact_and_old_files_are_pruned(tmp_path):
 
 def test_validation_without_a_held_out_split_reads_the_train_rows(tmp_path):
     entry = pretrain(_cfg(val_data=None, num_iterations=3), tmp_path, run_id="t-00000002")
-    assert "pretrain/val_loss" in (entry / "metrics.jsonl").read_text()
+    assert "\"val_loss\"" in (entry / "metrics.jsonl").read_text()
 
 
 def test_sigterm_saves_state_at_the_next_iteration_boundary(tmp_path):

@@ -91,7 +91,7 @@ def test_pretrained_hybrid_target_roundtrip(tmp_path):
     import json
 
     lines = [json.loads(x) for x in (entry / "metrics.jsonl").read_text().splitlines()]
-    losses = [r["pretrain/loss"] for r in lines if "pretrain/loss" in r]
+    losses = [r["train_loss"] for r in lines if "train_loss" in r]
     assert len(losses) == 3 and all(math.isfinite(v) for v in losses)
 
     cfg = _config({"gdn_q": 8, "attn_o": 8, "experts_down": 12, "shared_up": 8})

@@ -106,7 +106,7 @@ def test_component_split_engine_matches_single_process(losses, fsdp, sp):
         out = mp.Manager().dict()
         mp.spawn(_worker, args=(world, port, root, losses, fsdp, out, sp), nprocs=world, join=True)
         res, ref = _train(_cfg(1, losses), Path(root), SINGLE_ID)
-        keys = [k for k in res.last_metrics if k.startswith("train/loss/") or k.startswith("train/grad_norm/")]
+        keys = [k for k in res.last_metrics if k.startswith("train/loss/") or k.startswith("train/grad_norms/")]
         assert len(keys) >= 4
         for k in keys:
             got = sum(out[r][0][k] for r in range(world)) / world  # (data shards see their own rows)
@@ -131,7 +131,7 @@ def test_component_split_engine_matches_single_process(losses, fsdp, sp):
                 return [{k: v for k, v in r.items() if k.startswith("eval/")} for r in rows if any(k.startswith("eval/") for k in r)][-1]
 
             a, b = last_eval(SPLIT_ID), last_eval(SINGLE_ID)
-            assert set(a) == set(b) and any(k.startswith("eval/l0/") for k in a) and "eval/PGDReconLoss_2step" in a
+            assert set(a) == set(b) and any(k.startswith("eval/l0/") for k in a) and "eval/loss/PGDReconLoss_2step" in a
             for k in a:
                 assert abs(a[k] - b[k]) <= 1e-3 * abs(b[k]) + 1e-6, (k, a[k], b[k])
         for item in (DECOMPOSITION_FILE, TRAINING_FILE):
