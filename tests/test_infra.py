@@ -146,3 +146,30 @@ def test_written_keys_use_the_reference_spellings():
     # the grouped names are derived from the internal keys, thresholded L0 keys included
     k = MN.grouped_metric_key
     assert k("eval/l0/0.1_layers.2.self_attn.q_proj").path == "eval-ci-l0-gt-0p1/layer-02-01-attn-q"
+
+
+def test_sink_mirrors_the_written_keys_or_the_grouped_names(tmp_path, monkeypatch):
+    """`legacy`: W&B receives what `metrics.jsonl` receives (the reference's spellings); `grouped`: the two-level
+    names derived from the internal keys."""
+    import sys
+    import types
+
+    from param_decomp_b200.config.run import WandbConfig
+    from param_decomp_b200.core.metrics import MetricsSink
+
+    logged: list[dict] = []
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kw: types.SimpleNamespace(log=lambda rec, step=None: logged.append(dict(rec)), finish=lambda: None)
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    monkeypatch.setenv("WANDB_MODE", "offline")
+    record = {"loss/total": 2.5, "grad_norm/ci_fn": 0.5, "schedules/lr_components": 1e-3}
+    for schema, want in (("legacy", {"train/loss/total", "train/grad_norms/summary/ci_fns", "train/schedules/lr/components"}),
+                         ("grouped", {"train-loss/total", "train-grad-norm/ci-fn", "train-schedules/lr-components"})):
+        logged.clear()
+        run_dir = tmp_path / schema
+        sink = MetricsSink.for_run(run_dir, 0, WandbConfig(project="p", metric_schema=schema), "r", {})
+        written = sink.log(3, record)
+        sink.close()
+        assert set(written) == {"train/loss/total", "train/grad_norms/summary/ci_fns", "train/schedules/lr/components"}
+        assert set(json.loads((run_dir / "metrics.jsonl").read_text())) == set(written) | {"step"}
+        assert len(logged) == 1 and set(logged[0]) == want, logged
