@@ -175,6 +175,8 @@ class PerformanceTracker:
         out = {
             "perf/step_time_s": dt,
             "perf/elapsed_s": now - self.t_start,
+            "perf/runtime_s": now - self.t_start,
+            "perf/n_completed_steps": float(step),
             "perf/eta_s": dt * max(self.total_steps - step, 0),
             "perf/tokens_per_s": self.units_per_step / dt if dt > 0 else 0.0,
         }
@@ -187,6 +189,7 @@ class PerformanceTracker:
         if torch.cuda.is_available():
             out["perf/cuda_mem_allocated_gb"] = torch.cuda.memory_allocated() / 2**30
             out["perf/cuda_mem_peak_gb"] = torch.cuda.max_memory_allocated() / 2**30
+            out["mem/peak_gb_per_rank"] = torch.cuda.max_memory_allocated() / 1e9  # decimal GB, as the reference logs it
         return out
 
 

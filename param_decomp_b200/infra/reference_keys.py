@@ -24,6 +24,8 @@ _TRAIN = {
     "train/schedules/lr_components": "train/schedules/lr/components",
     "train/schedules/lr_ci_fn": "train/schedules/lr/ci_fn",
     "train/schedules/lr_src": "train/schedules/lr/src",
+    "train/perf/mfu": "train/perf/step_mfu_without_optimizer",
+    "train/perf/mfu_with_optimizer": "train/perf/step_mfu_with_optimizer",
 }
 _PRETRAIN = {  # the pretrainer's records carry no prefix in the reference (param_decomp/pretrain/train.py:217-262)
     "pretrain/loss": "train_loss",
