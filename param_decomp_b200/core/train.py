@@ -541,6 +541,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     if obj.nonlinearity is not None:
         nl = obj.nonlinearity
         thr = get_scheduled_value(step, total, nl.relative_threshold)
+        metrics["schedules/nonlinearity_relative_threshold"] = torch.tensor(thr)
         val = loss_fns.nonlinearity_locality(state.components, thr, dict(nl.unit_kind_coefficients), nl.normalize_at_one,
                                              expert_shard=ctx.expert_shard,
                                              split_grad_scale=ctx.collectives.split_grad_scale)
@@ -647,6 +648,7 @@ def train_step(ctx: StepContext, state: TrainState, batch: Any, nontarget_batch:
     for term, grads in final_grads:
         lr = get_scheduled_value(step, total, term.cfg.optimizer.lr_schedule)  # type: ignore[attr-defined]
         state.adversaries[term.name].ascend(grads, lr, final_key)
+        metrics["schedules/lr_src"] = torch.tensor(lr)  # written as `train/schedules/lr/src`
 
     if ctx.scalars is not None:
         native.set_step_seed(None)
