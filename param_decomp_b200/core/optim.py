@@ -62,6 +62,27 @@ def newton_schulz(G: Tensor, steps: int = 5, dtype: torch.dtype = torch.bfloat16
     return X.to(G.dtype)
 
 
+def newton_schulz_of_slice(name: str, mix: Tensor, split, steps: int, dtype: torch.dtype) -> tuple[Tensor, int, int]:
+    """Orthogonalise the matrix a leaf is a slice of. `split` (`parallel/expert_shard.py::StackSharding` in
+    component mode) says that every rank of its group holds a slice of the component axis of `name` (the last axis
+    of a `V`, the one before last of a `U`): the slices are gathered, the WHOLE matrix is orthogonalised - the
+    orthogonal factor of a slice is not the slice of the orthogonal factor - and this rank's slice of the result
+    is returned with the whole matrix's `(fan_in, fan_out)`. Without a split this is plain `newton_schulz`.
+    Parity: the reference's Newton-Schulz row names no component axis, i.e. it sees whole matrices
+    (param_decomp/core/placement.py:1011-1116, `components/ns_compute`)."""
+    if split is None or not getattr(split, "by_component", False) or not split.is_split(name) or split.world == 1:
+        return newton_schulz(mix, steps, dtype), mix.shape[-2], mix.shape[-1]
+    import torch.distributed as dist
+
+    axis = split._axis(name) % mix.dim()
+    parts = [torch.empty_like(mix) for _ in range(split.world)]
+    dist.all_gather(parts, mix.contiguous(), group=split.group)
+    whole = torch.cat(parts, dim=axis)
+    O = newton_schulz(whole, steps, dtype)
+    n = mix.shape[axis]
+    return O.narrow(axis, split.rank * n, n), whole.shape[-2], whole.shape[-1]
+
+
 def _native_ns_ok(X: Tensor) -> bool:
     if not (X.is_cuda and X.dtype == torch.bfloat16 and X.dim() in (2, 3)):
         return False
@@ -107,6 +128,7 @@ class GroupOptimizer:
     last_grad_norm: float = 0.0
     use_fused: bool = False
     norm_fn: Any = None  # (names, grads) -> global L2 norm, for leaves that are split over a process group
+    column_split: Any = None  # `StackSharding` in component mode: Muon orthogonalises the gathered whole matrices
     scalars: Any = None  # ops.step_scalars.StepScalars: learning rate and bias corrections live in device memory
     label: str = "group"
 
@@ -196,8 +218,7 @@ class GroupOptimizer:
             mom = self._get(n + "/mom", p)
             mom.mul_(b).add_(g, alpha=1 - b)
             nesterov = (b / (1 - b ** (t + 1))) * mom + ((1 - b) / (1 - b**t)) * g
-            O = newton_schulz(nesterov, cfg.ns_steps, ns_dtype)
-            fan_out, fan_in = p.shape[-1], p.shape[-2]
+            O, fan_in, fan_out = newton_schulz_of_slice(n, nesterov, self.column_split, cfg.ns_steps, ns_dtype)
             if cfg.consistent_rms is not None:
                 s = math.sqrt(max(fan_in, fan_out)) * cfg.consistent_rms
             else:

@@ -214,8 +214,10 @@ def init_train_state(model: DecomposedModel, ci_fn: nn.Module, pd: PDConfig | Ta
                                     wait_limit_s=peer_wait_limit_s)
     else:
         comp_opt = build_group_optimizer(pd.components_optimizer, comp_named, pd.steps, 2, use_fused_optim)
-    if expert_shard is not None and shard_backend is None:
-        comp_opt.norm_fn = expert_shard.grad_norm
+    if expert_shard is not None and (shard_backend is None or muon_sharded):
+        comp_opt.norm_fn = expert_shard.grad_norm  # split leaves contribute their group-wide sum of squares
+    if expert_shard is not None and hasattr(comp_opt, "column_split"):
+        comp_opt.column_split = expert_shard  # Muon: slices of the component axis are gathered for Newton-Schulz
     from param_decomp_b200.config.run import AdamWOptimizerConfig as _AdamW
 
     if (shard_backend is not None and expert_shard is None and isinstance(pd.ci_fn_optimizer, _AdamW)

@@ -255,7 +255,8 @@ def check(world: int, steps: int, sharding: str, batch: int, device: str, rtol: 
             q = q[: p.shape[0]]  # stacks are padded to a multiple of the rank count
             p = p[tuple(slice(0, n) for n in q.shape)]  # under `tp`, rank 0 holds the leading slice of the component axis
             err = float((p - q).abs().max() / p.abs().max().clamp_min(1e-12))
-            if err > 10 * rtol:
+            # Newton-Schulz runs in bf16 by default: its products round differently on a gathered matrix
+            if err > (1e-2 if variant.get("muon") else 10 * rtol):
                 bad.append(f"component stack {i}: max relative difference {err:.3g}")
         if verbose:
             last = max(a)

@@ -27,7 +27,7 @@ from torch import Tensor
 
 from param_decomp_b200.config.run import MuonOptimizerConfig
 from param_decomp_b200.config.schedule import get_scheduled_value
-from param_decomp_b200.core.optim import clip_scale, global_norm, newton_schulz
+from param_decomp_b200.core.optim import clip_scale, global_norm, newton_schulz_of_slice
 
 
 @dataclass
@@ -41,7 +41,8 @@ class StackShardedMuon:
     count: int = 0
     applied_learning_rate: float = 0.0
     last_grad_norm_t: Tensor | None = None
-    norm_fn: Any = None
+    norm_fn: Any = None  # (names, grads) -> global L2 norm where leaves are split over a process group
+    column_split: Any = None  # `StackSharding` in component mode: whole matrices are gathered for Newton-Schulz
 
     def __post_init__(self) -> None:
         self.world = dist.get_world_size(self.group) if self.group is not None else 1
@@ -77,7 +78,10 @@ class StackShardedMuon:
         if grads is None:
             grads = [p.grad for p in self.params]
         live = [(n, p, g) for n, p, g in zip(self.names, self.params, grads) if g is not None]
-        norm = global_norm([g for _, _, g in live])
+        if self.norm_fn is not None and live:
+            norm = self.norm_fn([n for n, _, _ in live], [g for _, _, g in live])
+        else:
+            norm = global_norm([g for _, _, g in live])
         scale = clip_scale(norm, cfg.grad_clip_norm)
         lr = self.lr_at(step_idx)
         self.count += 1
@@ -103,8 +107,7 @@ class StackShardedMuon:
         mom = self._get(n + "/mom", p[own])
         mom.mul_(b).add_(g[own], alpha=1 - b)
         mix = (b / (1 - b ** (t + 1))) * mom + ((1 - b) / (1 - b**t)) * g[own]
-        O = newton_schulz(mix, cfg.ns_steps, ns_dtype)
-        fan_in, fan_out = p.shape[-2], p.shape[-1]
+        O, fan_in, fan_out = newton_schulz_of_slice(n, mix, self.column_split, cfg.ns_steps, ns_dtype)
         s = (math.sqrt(max(fan_in, fan_out)) * cfg.consistent_rms if cfg.consistent_rms is not None
              else math.sqrt(max(1.0, fan_out / fan_in)))
         if cfg.weight_decay:

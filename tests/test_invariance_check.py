@@ -83,3 +83,10 @@ def test_ce_unrecovered_is_formed_from_averages():
     mean = {k: (a[k] + b[k]) / 2 for k in a}
     assert ce_unrecovered(mean)["ce_unrecovered/ci_masked"] == (2.0 - 1.0) / (2.5 - 1.0)  # not (0.5 + 1.0) / 2
     assert ce_unrecovered({"kl/x": 1.0}) == {}
+
+
+def test_muon_orthogonalises_whole_matrices_when_the_component_axis_is_split():
+    """Two ranks that each hold half of every site's components must take the step one process takes: the
+    Newton-Schulz factor of a slice is not the slice of the factor, and the clip norm covers both halves."""
+    assert ic.check(world=2, steps=2, sharding="ddp", batch=4, device="cpu", verbose=False, tp=2, muon=True,
+                    with_noise_floor=True) == []
