@@ -70,7 +70,8 @@ CI_FUNCTIONS: dict[str, dict[str, Any]] = {
 
 def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, tp: int = 1,
                 objective: str = "default", ci: str = "layerwise_mlp", muon: bool = False, family: str = "dense",
-                expert_mode: str = "allreduce", with_eval: bool = False, documents: bool = False) -> LMExperimentConfig:
+                expert_mode: str = "allreduce", with_eval: bool = False, documents: bool = False,
+                resident: bool = False) -> LMExperimentConfig:
     """`family: moe` is a top-2-of-5 mixture of experts (five experts on two ranks leave one padding expert); its
     `tp` ranks split the experts, and with `expert_mode: all_to_all` the batch too."""
     raw: dict[str, Any] = {
@@ -95,6 +96,8 @@ def tiny_config(world: int, steps: int, sharding: str, batch: int, cuda: bool, t
         "data": {"train": {"kind": "synthetic_zipf"}, "eval": {"kind": "synthetic_zipf", "seed": 1},
                  "layout": "unsegmented_tokens", "seq_len": 128 if cuda else 16},
     }
+    if resident:  # the `*-replicated-resident` presets are written for a (data, tp) mesh
+        raw["runtime"]["mesh"] = {"data": world // tp, "tp": tp}
     if documents:  # packed rows with document boundaries (`write_documents_dataset`): segment-confined attention and losses
         raw["data"].update(train={"kind": "name", "name": DOCUMENTS_DATASET}, eval={"kind": "name", "name": DOCUMENTS_DATASET},
                            layout="documents")
@@ -280,6 +283,8 @@ def main() -> None:
     ap.add_argument("--muon", action="store_true", help="Muon on the component matrices")
     ap.add_argument("--noise-floor", action="store_true",
                     help="also rerun the one-process arm with another summation order and allow three times its drift")
+    ap.add_argument("--resident", action="store_true",
+                    help="use the (data, tp) mesh of the *-replicated-resident sharding presets")
     ap.add_argument("--documents", action="store_true", help="train on packed rows with document boundaries")
     ap.add_argument("--with-eval", action="store_true", help="also compare the evaluation metrics of the last step")
     ap.add_argument("--family", choices=("dense", "moe"), default="dense")
@@ -287,7 +292,7 @@ def main() -> None:
     a = ap.parse_args()
     bad = check(a.world, a.steps, a.sharding, a.batch, a.device, a.rtol, tp=a.tp, objective=a.objective, ci=a.ci,
                 muon=a.muon, family=a.family, expert_mode=a.expert_mode, with_noise_floor=a.noise_floor,
-                with_eval=a.with_eval, documents=a.documents)
+                with_eval=a.with_eval, documents=a.documents, resident=a.resident)
     if bad:
         print(f"NOT invariant over {a.world} ranks ({a.sharding}):")
         for line in bad:
