@@ -34,6 +34,7 @@ _PRETRAIN = {  # the pretrainer's records carry no prefix in the reference (para
     "pretrain/step_time_s": "step_time_s",
 }
 _TRAIN.update(_PRETRAIN)
+_NONTARGET = "train/nontarget/loss/"
 _CE_KL = re.compile(r"^(?P<head>(?:eval/)(?:ArithmeticCIGrid/probe/)?)(?P<measure>kl|ce|ce_difference|ce_unrecovered)/(?P<variant>[a-z_]+)$")
 _PGD = re.compile(r"^(?P<head>eval/(?:ArithmeticCIGrid/probe/)?)(?P<probe>(?:Slow)?PGDReconLoss_\d+step)(?P<rest>(?:/.*)?)$")
 
@@ -42,6 +43,9 @@ def reference_key(key: str) -> str:
     """Internal key (with its `train/` / `eval/` prefix) -> the key that is written."""
     if key in _TRAIN:
         return _TRAIN[key]
+    if key.startswith(_NONTARGET):  # the broad stream of a targeted run (param_decomp/core/train.py:1749-1770)
+        name = key[len(_NONTARGET):]
+        return "train/loss/nontarget/" + ("imp" if name.endswith("ImportanceMinimalityLoss") else name)
     m = _CE_KL.match(key)
     if m is not None:
         return f"{m['head']}ce_kl/{m['measure']}_{m['variant']}"
@@ -66,6 +70,9 @@ def internal_key(key: str) -> str:
     """Inverse of `reference_key`: a written key -> the internal key (identity on internal keys)."""
     if key in _TRAIN_BACK:
         return _TRAIN_BACK[key]
+    if key.startswith("train/loss/nontarget/"):
+        name = key[len("train/loss/nontarget/"):]
+        return _NONTARGET + ("ImportanceMinimalityLoss" if name == "imp" else name)
     m = _CE_KL_BACK.match(key)
     if m is not None:
         return f"{m['head']}{m['measure']}/{m['variant']}"

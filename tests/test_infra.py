@@ -139,10 +139,15 @@ def test_written_keys_use_the_reference_spellings():
         "eval/SlowPGDReconLoss_640step/hidden_acts_reconstruction": "eval/loss/SlowPGDReconLoss_640step/hidden_acts_reconstruction",
         "eval/l0/0.0_layers.0.mlp.up_proj": "eval/l0/0.0_layers.0.mlp.up_proj",
         "eval/ArithmeticCIGrid/probe/kl/ci_masked": "eval/ArithmeticCIGrid/probe/ce_kl/kl_ci_masked",
+        "train/nontarget/loss/ImportanceMinimalityLoss": "train/loss/nontarget/imp",
+        "train/nontarget/loss/StochasticReconSubsetLoss": "train/loss/nontarget/StochasticReconSubsetLoss",
     }
     for ours, theirs in pairs.items():
         assert reference_key(ours) == theirs, ours
     assert set(reference_keys(dict.fromkeys(pairs, 1.0))) == set(pairs.values())
+    from param_decomp_b200.infra.reference_keys import internal_key
+
+    assert all(internal_key(theirs) == ours for ours, theirs in pairs.items())
     # the grouped names are derived from the internal keys, thresholded L0 keys included
     k = MN.grouped_metric_key
     assert k("eval/l0/0.1_layers.2.self_attn.q_proj").path == "eval-ci-l0-gt-0p1/layer-02-01-attn-q"
