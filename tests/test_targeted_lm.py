@@ -130,3 +130,23 @@ def test_per_position_adversary_follows_the_prompt_length(tmp_path):
     assert res.final_step == 3
     adv = next(iter(states[0].adversaries.values()))
     assert next(iter(adv.sources.values())).shape[:2] == (4, 4)  # [rows, prompt positions, C]
+
+
+def test_targeted_run_on_a_mixture_of_experts_with_an_adversary(tmp_path):
+    """Both streams on expert-blocked sites: narrow importances on the target stream's persistent adversary and on
+    the broad stream's subset-routed masks; the broad stream's keys are written as `train/loss/nontarget/*`."""
+    raw = _targeted_config().model_dump(mode="json")
+    raw["target"]["spec"]["arch"] = {"family": "moe", "n_layer": 2, "d_model": 32, "n_head": 2, "d_ff": 16,
+                                     "vocab_size": 131, "n_experts": 4, "experts_per_token": 2, "max_seq_len": 16}
+    raw["decomposition"]["sites"] = {"kind": "moe", "layers": {"kind": "all"},
+                                     "cs": {"q": 8, "experts_gate": 16, "experts_up": 16, "experts_down": 16}}
+    raw["pd"]["loss_metrics"].append({"type": "PersistentPGDReconLoss", "coeff": 0.5, "source_shape": "bsc",
+                                      "n_warmup_steps": 1, "optimizer": {"type": "sgd", "lr_schedule": 0.05}})
+    raw["nontarget"]["recon"] = [{"type": "CIMaskedReconLoss", "coeff": 1.0},
+                                 {"type": "StochasticReconSubsetLoss", "coeff": 0.5, "routing": {"type": "uniform_k_subset"}}]
+    res = train_lm_targeted(LMTargetedExperimentConfig.model_validate(raw), tmp_path, device="cpu")
+    assert res.final_step == 3
+    m = res.last_metrics
+    assert {"train/loss/PersistentPGDReconLoss", "train/loss/nontarget/imp", "train/loss/nontarget/CIMaskedReconLoss",
+            "train/loss/nontarget/StochasticReconSubsetLoss", "train/schedules/lr/src"} <= set(m)
+    assert all(v == v for v in m.values())
