@@ -54,3 +54,15 @@ def test_every_shipped_yaml_parses():
     for f in files:
         cls = next(c for p, c in by_prefix.items() if f.name.startswith(p))
         cls.from_file(f)
+
+
+def test_every_module_main_named_in_the_docs_exists():
+    """`python -m <module>` lines of the README, the guide and the Makefile name importable modules."""
+    import importlib.util
+
+    root = PKG.parent
+    text = "\n".join((root / f).read_text() for f in ("README.md", "docs/guide.md", "Makefile"))
+    modules = set(re.findall(r"-m (param_decomp_b200(?:\.\w+)+)", text))
+    assert len(modules) >= 10
+    missing = sorted(m for m in modules if importlib.util.find_spec(m) is None)
+    assert not missing, missing
